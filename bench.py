@@ -1,0 +1,365 @@
+#!/usr/bin/env python
+"""Benchmark of the cuda_sm100 hot path: the Q4_K decode matvec over Qwen3-8B-shaped projections.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One step = one pass of the M = 1 matvec over a pool of distinct packed Q4_K weight matrices:
+`layers` x {K=4096 N=4096, K=4096 N=12288, K=12288 N=4096} (Qwen3-8B's q/o, gate/up and down projection
+shapes; 36 layers = 2.4 GB, far above the 126 MB L2, so every step streams its weights from HBM).
+metric = algorithmic GB/s = sum over launches of (N*K*0.5625 + 4*K + 4*N) bytes / device time.
+
+  value      launches replayed from one CUDA graph, inputs resident in HBM, CUDA-event timing on the
+             launching stream
+  e2e        the same pass driven call by call with HOST activations: per matvec a pinned host->device copy
+             of x, the kernel, a device->host copy of y, one stream sync per step (weights stay resident, as
+             they do after scrapgpu_tensor_upload in the reference's usage)
+  roofline   achieved = algorithmic bytes per launch / mean launch duration (the same CUDA-event region),
+             peak = measured HBM copy bandwidth of MEASURED_PEAKS.json (burst figure; fallback 6650 GB/s)
+  cpu_baseline  the unmodified reference's CPU MUL_MAT (oracle/_ref, built from the reference's own sources) on
+             one layer's three matrices, single thread (the reference is single-threaded)
+
+`--impl reference` times that CPU reference with all host threads (rows sharded over threads, each slice an
+unmodified scrapgpu_ref_execute call) on a bounded sample of the same workload.
+
+With N > 1 ranks (torchrun) every rank streams its own shard pool of the same size (weight rows are
+independent: no data-path collective), value = bytes of all ranks / max-over-ranks device time: weak scaling.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes as C
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+Q4_0, Q8_0, Q4_K, Q6_K = 16, 17, 32, 33
+BPW = {Q4_0: 0.5625, Q8_0: 1.0625, Q4_K: 0.5625, Q6_K: 0.8203125}
+SHAPES = [(4096, 4096), (4096, 12288), (12288, 4096)]  # (K, N)
+METRIC = "q4_k_matvec_algorithmic_gbps"
+
+
+def algorithmic_bytes(dtype: int, k: int, n: int, m: int = 1) -> float:
+    """Bytes a MUL_MAT must move: packed weights once, activations in, results out."""
+    return n * k * BPW[dtype] + 4.0 * k * m + 4.0 * n * m
+
+
+def measured_peak_gbs():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        try:
+            return float(json.load(open(p))["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
+        except Exception:
+            pass
+    return 6650.0, "fallback (6.65 TB/s, earlier measurement on this pool)"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+
+    def __init__(self, device: int):
+        self.device = device
+        self.rows = []
+        self.proc = None
+
+    def start(self):
+        q = "clocks.sm,clocks.max.sm,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.device}", f"--query-gpu={q}", "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+            return
+        threading.Thread(target=self._read, daemon=True).start()
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self) -> dict:
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except Exception:
+                pass
+        sm, mx, reasons = [], [], set()
+        for r in self.rows:
+            if len(r) < 7:
+                continue
+            try:
+                sm.append(float(r[0]))
+                mx.append(float(r[1]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def build_pool(capi, stream, dtype: int, layers: int, seed: int):
+    """Packed weights on the device: `layers` distinct matrices per shape.  One matrix per shape is synthesised
+    on the host; the others are row rotations of it (distinct HBM addresses, same value distribution),
+    repacked on the device from the natural bytes."""
+    from scrapgpulibrary_b200 import synth
+    pool = []
+    L = capi.lib()
+    for si, (k, n) in enumerate(SHAPES):
+        base = synth.quantized_matrix(dtype, seed + si, n, k)
+        rb = base.shape[1]
+        staging = capi.Buffer(n * rb)
+        mats = []
+        for layer in range(layers):
+            rot = np.roll(base, layer * 17, axis=0) if layer else base
+            staging.upload(stream, rot)
+            dst = capi.Buffer(n * rb)
+            capi.check(L.sm100_pack_device(stream.handle, dtype, k, n, staging.at(), dst.at()), "pack_device")
+            stream.sync()
+            mats.append(dst)
+        staging.free()
+        pool.append({"k": k, "n": n, "mats": mats, "natural": base})
+    return pool
+
+
+def run_ours(args, rank: int, world: int, local_rank: int):
+    from scrapgpulibrary_b200 import _build, capi
+    _build.build_sm100()
+    capi.require_device()
+    L = capi.lib()
+    capi.check(L.sm100_set_device(local_rank), "set_device")
+    stream = capi.Stream(local_rank)
+    dtype = Q4_K
+    layers = args.layers
+    t0 = time.time()
+    pool = build_pool(capi, stream, dtype, layers, seed=0x5CA9 + rank)
+    setup_s = time.time() - t0
+
+    rng = np.random.default_rng(1234 + rank)
+    xs, ys = {}, {}
+    for k in (4096, 12288):
+        xs[k] = capi.Buffer(4 * k * 8)
+        xs[k].upload(stream, rng.standard_normal(k * 8).astype(np.float32))
+    for n in (4096, 12288):
+        ys[n] = capi.Buffer(4 * n * 8)
+
+    # launch order of one step: layer by layer, q/o-shaped, gate/up-shaped, down-shaped
+    order = [(s, layer) for layer in range(layers) for s in range(len(SHAPES))]
+    step_bytes = sum(algorithmic_bytes(dtype, pool[s]["k"], pool[s]["n"]) for s, _ in order)
+
+    def enqueue_step(m: int = 1, only_shape=None):
+        cnt = 0
+        for s, layer in order:
+            if only_shape is not None and s != only_shape:
+                continue
+            p = pool[s]
+            capi.mul_mat(stream, dtype, 1, p["mats"][layer], p["k"], p["n"], xs[p["k"]], m, ys[p["n"]])
+            cnt += 1
+        return cnt
+
+    def timed_graph(m: int, only_shape, steps: int, warmup: int):
+        launches0 = L.sm100_launch_count()
+        with capi.Graph(stream) as g:
+            per_step = enqueue_step(m, only_shape)
+        assert L.sm100_launch_count() - launches0 == per_step
+        for _ in range(warmup):
+            g.launch()
+        stream.sync()
+        e0, e1 = capi.Event(), capi.Event()
+        e0.record(stream)
+        for _ in range(steps):
+            g.launch()
+        e1.record(stream)
+        e1.sync()
+        ms = e0.elapsed_ms(e1)
+        g.destroy()
+        return ms, per_step
+
+    # ---- headline: whole sweep, M = 1, graph replay ----
+    dist = None
+    if world > 1:
+        import torch
+        import torch.distributed as dist_mod
+        torch.cuda.set_device(local_rank)
+        dist_mod.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        dist = dist_mod
+
+    def barrier():
+        if dist is not None:
+            import torch
+            dist.barrier()
+            torch.cuda.synchronize()
+        stream.sync()
+
+    sampler = ClockSampler(local_rank)
+    barrier()
+    if rank == 0:
+        sampler.start()
+    ms, per_step = timed_graph(1, None, args.steps, args.warmup)
+    barrier()
+    clocks = sampler.stop() if rank == 0 else {}
+    if dist is not None:
+        import torch
+        t = torch.tensor([ms], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    ms_per_step = ms / args.steps
+    value = world * step_bytes / (ms_per_step * 1e-3) / 1e9
+    launches_timed = per_step * args.steps
+
+    out = None
+    if rank == 0:
+        peak, peak_src = measured_peak_gbs()
+        per_launch_bytes = step_bytes / per_step
+        per_launch_us = ms_per_step * 1e3 / per_step
+        achieved = per_launch_bytes / (per_launch_us * 1e-6) / 1e9
+        detail = {}
+        # per-shape and per-M figures (explanatory; the same graph-replay protocol, fewer steps)
+        sub_steps = max(3, args.steps // 2)
+        for s, (k, n) in enumerate(SHAPES):
+            m_ms, cnt = timed_graph(1, s, sub_steps, 3)
+            detail[f"q4_k_k{k}_n{n}_m1_gbps"] = round(cnt * algorithmic_bytes(dtype, k, n) * sub_steps / (m_ms * 1e-3) / 1e9, 1)
+        for m in (2, 4, 8):
+            m_ms, cnt = timed_graph(m, None, sub_steps, 3)
+            b = sum(algorithmic_bytes(dtype, pool[s]["k"], pool[s]["n"], m) for s, _ in order)
+            detail[f"q4_k_sweep_m{m}_gbps"] = round(b * sub_steps / (m_ms * 1e-3) / 1e9, 1)
+
+        # ---- e2e: host activations in, host results out, call by call ----
+        hx, hy = {}, {}
+        for k in (4096, 12288):
+            p = C.c_void_p()
+            capi.check(L.sm100_host_alloc(4 * k, C.byref(p)), "host_alloc")
+            C.memmove(p, rng.standard_normal(k).astype(np.float32).ctypes.data, 4 * k)
+            hx[k] = p
+        for n in (4096, 12288):
+            p = C.c_void_p()
+            capi.check(L.sm100_host_alloc(4 * n, C.byref(p)), "host_alloc")
+            hy[n] = p
+
+        def e2e_step():
+            for s, layer in order:
+                p = pool[s]
+                k, n = p["k"], p["n"]
+                L.sm100_memcpy_h2d(stream.handle, xs[k].at(), hx[k], 4 * k, 0)
+                capi.mul_mat(stream, dtype, 1, p["mats"][layer], k, n, xs[k], 1, ys[n])
+                L.sm100_memcpy_d2h(stream.handle, hy[n], ys[n].at(), 4 * n, 0)
+            stream.sync()
+
+        for _ in range(max(3, args.warmup)):
+            e2e_step()
+        e2e_steps = max(3, args.steps // 2)
+        e0, e1 = capi.Event(), capi.Event()
+        e0.record(stream)
+        for _ in range(e2e_steps):
+            e2e_step()
+        e1.record(stream)
+        e1.sync()
+        e2e_ms = e0.elapsed_ms(e1) / e2e_steps
+        h2d = sum(4 * pool[s]["k"] for s, _ in order)
+        d2h = sum(4 * pool[s]["n"] for s, _ in order)
+
+        cpu = cpu_baseline(pool, threads=1, repeats=5)
+        out = {
+            "metric": METRIC, "value": round(value, 1), "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": round(ms_per_step, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+            "data": "synthetic: seeded N(0, 0.02) weights in Q4_K blocks, N(0, 1) activations",
+            "config": {"workload": f"Q4_K matvec sweep, M=1, Qwen3-8B projection shapes (K,N) in {SHAPES} x {layers} layers per GPU",
+                       "launches_per_step": per_step, "bytes_per_step_per_gpu": int(step_bytes), "weights_layout": "backend-packed planes",
+                       "l2": "inputs larger than L2 (pool %.2f GB per GPU, L2 126 MB)" % (step_bytes / 1e9), "timing": "CUDA events on the launching stream, one graph replay per step",
+                       "setup_s": round(setup_s, 1), "detail": detail},
+            "gpu_launches": int(launches_timed),
+            "e2e": {"value": round(world * step_bytes / (e2e_ms * 1e-3) / 1e9, 1), "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "ms_per_step": round(e2e_ms, 4), "note": "host activations in / host results out per matvec, weights resident"},
+            "roofline": {"bound": "hbm", "kernel": "matvec_stream<UnitQ4K>", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
+                         "frac": round(achieved / peak, 4), "peak_source": peak_src, "bytes_per_launch": round(per_launch_bytes, 1),
+                         "us_per_launch": round(per_launch_us, 3), "traffic": None},
+            "cpu_baseline": cpu,
+            "clocks": clocks,
+        }
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+    return out
+
+
+def cpu_baseline(pool, threads: int, repeats: int):
+    """The reference's CPU MUL_MAT on one layer's three matrices (natural blocks), GB/s of algorithmic bytes."""
+    try:
+        from oracle import refapi
+        use_ref = refapi.available()
+    except Exception:
+        use_ref = False
+    from oracle import sgref
+    rng = np.random.default_rng(7)
+    times = []
+    total = sum(algorithmic_bytes(Q4_K, p["k"], p["n"]) for p in pool)
+    xs = {p["k"]: rng.standard_normal((1, p["k"])).astype(np.float32) for p in pool}
+    for _ in range(repeats + 1):
+        t0 = time.perf_counter()
+        for p in pool:
+            if use_ref:
+                refapi.mul_mat(Q4_K, p["natural"], p["k"], xs[p["k"]], threads=threads)
+            else:
+                sgref.mul_mat(Q4_K, p["natural"], p["k"], xs[p["k"]], threads=threads)
+        times.append(time.perf_counter() - t0)
+    t = statistics.median(times[1:])
+    return {"value": round(total / t / 1e9, 3), "unit": "GB/s", "cores": threads, "kind": "reference" if use_ref else "port",
+            "sample": f"one layer (3 matrices, {total / 1e6:.1f} MB), M=1, median of {repeats} after 1 warm-up, {t * 1e3:.1f} ms per pass"}
+
+
+def run_reference(args, rank: int, world: int):
+    """The reference arm: the unmodified CPU implementation on the host cores, all threads."""
+    if rank != 0:
+        return None
+    from scrapgpulibrary_b200 import synth
+    threads = os.cpu_count() or 1
+    pool = [{"k": k, "n": n, "natural": synth.quantized_matrix(Q4_K, 0x5CA9 + si, n, k)} for si, (k, n) in enumerate(SHAPES)]
+    for _ in range(max(1, min(args.warmup, 3))):
+        cpu_baseline(pool, threads, 1)
+    steps = max(1, args.steps)
+    t0 = time.perf_counter()
+    res = None
+    for _ in range(steps):
+        res = cpu_baseline(pool, threads, 1)
+    elapsed = (time.perf_counter() - t0) / steps / 2.0  # each call runs 1 warm-up + 1 timed pass
+    total = sum(algorithmic_bytes(Q4_K, p["k"], p["n"]) for p in pool)
+    value = res["value"]
+    return {"impl": "reference", "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": steps, "warmup": args.warmup,
+            "ms_per_step": round(total / (value * 1e9) * 1e3, 3), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f32", "data": "synthetic: seeded N(0, 0.02) weights in Q4_K blocks, N(0, 1) activations",
+            "config": {"workload": f"Q4_K matvec sweep, M=1, Qwen3-8B projection shapes (K,N) in {SHAPES}; each step = one layer (bounded sample of the sweep)"},
+            "cpu_baseline": {**res, "cores": threads}, "gpu_launches": 0,
+            "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}, "wall_s_per_step": round(elapsed, 3)}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--layers", type=int, default=36)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    args = ap.parse_args()
+    args.warmup = max(3, args.warmup) if args.impl == "ours" else args.warmup
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        out = run_reference(args, rank, world)
+    else:
+        out = run_ours(args, rank, world, local_rank)
+    if rank == 0 and out is not None:
+        print(json.dumps(out), flush=True)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,147 @@
+/*
+ * scrapgpu_sm100.h -- C ABI of libscrapgpu_sm100.so, the B200 (sm_100a) compute library underneath the
+ * `cuda_sm100` backend of ScrapGpuLibrary.
+ *
+ * Plain pointers and sizes only.  Every function returns a scrapgpu_status value
+ * (0 OK, 1 UNSUPPORTED, 2 INVALID_ARGUMENT, 3 OUT_OF_MEMORY, 4 BACKEND_ERROR; the reference's
+ * include/scrapgpu/status.h:10-17) and leaves a message for sm100_last_error() on failure.
+ * Tensor conventions are the reference's (ggml): W = [K, N] is N weight rows of K elements,
+ * x = [K, M] is M activation columns, y = [N, M]; y[n,m] = sum_k W[k,n] x[k,m].
+ * dtype codes are scrapgpu_dtype (include/scrapgpu/tensor.h:10-22): F32 0, F16 1, I32 2, Q4_0 16,
+ * Q8_0 17, Q4_K 32, Q6_K 33.  layout codes are scrapgpu_layout (tensor.h:24-27): 0 = natural GGUF
+ * blocks, 1 = backend-packed (the B200 plane layout produced by sm100_pack).
+ *
+ * Each entry names the reference interface it stands in for (file:line relative to the reference
+ * project).  There is no CPU fallback anywhere in this library: without a CUDA device the compute
+ * entry points fail with BACKEND_ERROR.
+ */
+#ifndef SCRAPGPU_SM100_H
+#define SCRAPGPU_SM100_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define SM100_API __attribute__((visibility("default")))
+
+typedef void * sm100_stream_t; /* a cudaStream_t */
+typedef void * sm100_event_t;  /* a cudaEvent_t */
+typedef void * sm100_graph_t;  /* a cudaGraphExec_t */
+
+/* ---- errors (src/core/status.cpp:6-37: thread-local last error) ---- */
+SM100_API const char * sm100_last_error(void);
+
+/* ---- devices, memory, streams: what a backend's device / buffer / stream vtable slots need
+ *      (include/scrapgpu/backend.h:33-44; CPU counterparts src/backends/cpu/api.cpp:1040-1300) ---- */
+SM100_API int sm100_device_count(void);
+SM100_API int sm100_device_info(int device, char * name, size_t name_size, uint64_t * total_memory,
+                                uint32_t * sm_count, uint32_t * cc_major, uint32_t * cc_minor,
+                                uint64_t * shared_per_block);
+SM100_API int sm100_set_device(int device);
+SM100_API int sm100_malloc(int device, size_t size, void ** out);           /* buffer_alloc (256 B aligned) */
+SM100_API int sm100_free(int device, void * ptr);                            /* buffer_free */
+SM100_API int sm100_host_alloc(size_t size, void ** out);                    /* pinned staging memory */
+SM100_API int sm100_host_free(void * ptr);
+SM100_API int sm100_stream_create(int device, sm100_stream_t * out);         /* stream_create */
+SM100_API int sm100_stream_destroy(int device, sm100_stream_t stream);       /* stream_free */
+SM100_API int sm100_stream_sync(sm100_stream_t stream);                      /* stream_sync */
+SM100_API int sm100_memcpy_h2d(sm100_stream_t s, void * dst, const void * src, size_t n, int blocking); /* buffer_write */
+SM100_API int sm100_memcpy_d2h(sm100_stream_t s, void * dst, const void * src, size_t n, int blocking); /* buffer_read */
+SM100_API int sm100_memcpy_d2d(sm100_stream_t s, void * dst, const void * src, size_t n, int blocking); /* buffer_copy (memmove semantics) */
+SM100_API int sm100_memset(sm100_stream_t s, void * dst, int byte, size_t n, int blocking);            /* buffer_fill */
+/* cross-device copy for scrapgpu_tensor_copy between two cuda_sm100 devices (src/core/transport.cpp:53-146):
+ * ordered after the work on src_stream and before later work on dst_stream, no host bounce */
+SM100_API int sm100_memcpy_peer(sm100_stream_t dst_stream, int dst_device, void * dst, sm100_stream_t src_stream,
+                                int src_device, const void * src, size_t n);
+
+/* ---- timing and replay: the plan seat of the reference (src/core/registry.cpp:200-220, "selection
+ *      happens once at plan build") becomes a captured CUDA graph ---- */
+SM100_API int sm100_event_create(sm100_event_t * out);
+SM100_API int sm100_event_destroy(sm100_event_t e);
+SM100_API int sm100_event_record(sm100_event_t e, sm100_stream_t s);
+SM100_API int sm100_event_sync(sm100_event_t e);
+SM100_API int sm100_event_elapsed_ms(sm100_event_t start, sm100_event_t stop, float * ms);
+SM100_API int sm100_graph_begin(sm100_stream_t s);
+SM100_API int sm100_graph_end(sm100_stream_t s, sm100_graph_t * out);
+SM100_API int sm100_graph_launch(sm100_graph_t g, sm100_stream_t s);
+SM100_API int sm100_graph_destroy(sm100_graph_t g);
+/* number of kernels of this library launched (or captured) by the calling process so far */
+SM100_API uint64_t sm100_launch_count(void);
+/* 1: launch kernels with programmatic dependent launch so that a kernel's weight prefetch overlaps
+ * the tail of its predecessor on the same stream (default 1) */
+SM100_API int sm100_set_pdl(int enabled);
+
+/* ---- weight packing: replaces the R32 repack of the OpenCL backend
+ *      (src/backends/opencl11/r32.h:35-90, r32.cpp:19-86; geometry src/tensor/tensor.cpp:5-19).
+ *      A packed tensor occupies exactly the natural byte count; packing is a byte permutation
+ *      (plus a lossless re-encoding of the Q4_K 6-bit scale fields), so unpack(pack(w)) == w. ---- */
+SM100_API size_t sm100_row_bytes(int dtype, int64_t k);                       /* src/tensor/tensor.h:54-66 */
+SM100_API int sm100_pack(int dtype, int64_t k, int64_t n, const void * natural, void * packed);   /* host -> host */
+SM100_API int sm100_unpack(int dtype, int64_t k, int64_t n, const void * packed, void * natural); /* host -> host */
+/* device-side repack of a natural tensor already in HBM (src = natural, dst = packed, distinct buffers) */
+SM100_API int sm100_pack_device(sm100_stream_t s, int dtype, int64_t k, int64_t n, const void * natural, void * packed);
+SM100_API int sm100_unpack_device(sm100_stream_t s, int dtype, int64_t k, int64_t n, const void * packed, void * natural);
+
+/* ---- the hot path: quantized MUL_MAT (src/core/ref/ops.cpp:891-984 exec_mul_mat; OpenCL kernels
+ *      mul_mv_r.cl:240-323, mul_mv_k.cl:396-486, mul_mm.cl:271).  w, x, y are device pointers;
+ *      x column stride ldx and y column stride ldy are in floats; w_row_stride is the byte stride of
+ *      natural-layout weight rows (0 = dense; packed tensors are always dense).  m <= 8 takes the fused
+ *      dequantize-and-dot matvec; larger m takes the tensor-core GEMM. ---- */
+SM100_API int sm100_mul_mat(sm100_stream_t s, int dtype, int layout, const void * w, int64_t w_row_stride, int64_t k,
+                            int64_t n, const float * x, int64_t ldx, int64_t m, float * y, int64_t ldy);
+/* MUL_MAT_MULTI (include/scrapgpu/op.h:46, src/backends/opencl11/kernels/mul_mv_multi.cl:46-104):
+ * up to 3 weight tensors sharing one activation column, one launch */
+SM100_API int sm100_mul_mat_multi(sm100_stream_t s, int count, const int * dtypes, const int * layouts,
+                                  const void * const * ws, int64_t k, const int64_t * ns, const float * x,
+                                  float * const * ys);
+
+/* ---- bit-exact dequantization: GET_ROWS over a quantized / F32 / F16 table
+ *      (src/core/ref/ops.cpp:690-722, quant.cpp:30-108); ids are I32 on the device ---- */
+SM100_API int sm100_get_rows(sm100_stream_t s, int dtype, int layout, const void * table, int64_t k,
+                             int64_t table_rows, const int32_t * ids, int64_t n_ids, float * dst, int64_t ld_dst);
+
+/* ---- the ops around the matvec in a decode step ---- */
+/* RMS_NORM / RMS_NORM_MUL / ADD_RMS_NORM_MUL (ops.cpp:440-519): add, w, sum_out may be NULL */
+SM100_API int sm100_rms_norm(sm100_stream_t s, const float * x, const float * add, const float * w, float * sum_out,
+                             float * y, int64_t ne0, int64_t rows, float eps);
+/* ROPE (ops.cpp:530-634) with a (cos, sin) table [n_positions, n_dims/2, 2] computed by the caller the
+ * way the reference does (sequential theta products, libm cos/sin); positions are I32 on the device and
+ * index the table after subtracting table_first_position */
+SM100_API int sm100_rope(sm100_stream_t s, const float * x, const int32_t * positions, const float * table,
+                         int32_t table_first_position, int32_t table_positions, float * y, int64_t ne0,
+                         int64_t heads, int64_t tokens, int n_dims, int neox);
+/* ROPE computing cos/sin on the device (sequential theta products in f32, cosf/sinf) */
+SM100_API int sm100_rope_direct(sm100_stream_t s, const float * x, const int32_t * positions, float * y, int64_t ne0,
+                                int64_t heads, int64_t tokens, int n_dims, int neox, float freq_base, float freq_scale,
+                                float attn_factor);
+/* SOFT_MAX (ops.cpp:636-684): y = softmax(x*scale + mask) per row; mask may be NULL; in place allowed */
+SM100_API int sm100_soft_max(sm100_stream_t s, const float * x, const float * mask, int64_t mask_row_stride,
+                             float * y, int64_t ne0, int64_t rows, float scale);
+/* GLU SwiGLU with split inputs (ops.cpp:383-425) */
+SM100_API int sm100_swiglu(sm100_stream_t s, const float * x, const float * g, float * y, int64_t n);
+/* ADD, same shapes (ops.cpp:280-312) */
+SM100_API int sm100_add(sm100_stream_t s, const float * a, const float * b, float * y, int64_t n);
+/* SET_ROWS F32 -> F32 (ops.cpp:724-762): dst[:, ids[i], h] = src[:, i, h] */
+SM100_API int sm100_set_rows(sm100_stream_t s, const float * src, const int32_t * ids, float * dst, int64_t ne0,
+                             int64_t n_rows, int64_t heads, int64_t dst_rows);
+/* TOP_K with k = 1 (ops.cpp:1189-1228): index of the maximum, lowest index on ties */
+SM100_API int sm100_argmax(sm100_stream_t s, const float * x, int64_t n, int32_t * out);
+/* fused decode attention, the values of scrapgpu_scaled_dot_product_attention
+ * (src/core/attention.cpp:558-678, include/scrapgpu/attention.h:11-46): Q [D, nq, Hq], K [D, nk, Hkv],
+ * V [Dv, nk, Hkv], out [Dv, nq, Hq], causal rule k <= offset + q.  mask (optional) is additive F32
+ * [nk, nq, mask_heads] with mask_heads 1 or Hq.  When positions is non-NULL the offset is read from
+ * positions[0] on the device instead of the argument, so one captured graph serves every step.
+ * Uses a per-device scratch buffer owned by the library (allocated on first use: make the first call
+ * outside stream capture). */
+SM100_API int sm100_attention(sm100_stream_t s, const float * q, const float * k, const float * v, const float * mask,
+                              int64_t mask_heads, float * out, int64_t d, int64_t dv, int64_t nq, int64_t nk, int64_t hq,
+                              int64_t hkv, int causal, int64_t offset, const int32_t * positions, float scale);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif

@@ -1,0 +1,40 @@
+// C entry points of the MUL_MAT family: shape checks and the choice between the decode matvec
+// (M <= 8, HBM-bound) and the prefill GEMM (tensor cores).
+#include "sm100_common.cuh"
+
+namespace sm100 {
+int matvec(cudaStream_t s, int dtype, int layout, const void * w, int64_t w_row_stride, int64_t k, int64_t n, const float * x,
+           int64_t ldx, int64_t m, float * y, int64_t ldy);
+int gemm_q8_0(cudaStream_t s, int layout, const void * w, int64_t k, int64_t n, const float * x, int64_t ldx, int64_t m, float * y,
+              int64_t ldy, bool * handled);
+}
+
+using namespace sm100;
+
+extern "C" {
+
+int sm100_mul_mat(sm100_stream_t s, int dtype, int layout, const void * w, int64_t w_row_stride, int64_t k, int64_t n, const float * x,
+                  int64_t ldx, int64_t m, float * y, int64_t ldy) {
+    if (m <= 0) return fail(ST_INVALID, "mul_mat: M must be positive");
+    if (m <= 8) return matvec((cudaStream_t) s, dtype, layout, w, w_row_stride, k, n, x, ldx, m, y, ldy);
+    // wide batches: column panels of 8 through the matvec until a tensor-core path claims the shape
+    for (int64_t c = 0; c < m; c += 8) {
+        const int64_t mm = m - c < 8 ? m - c : 8;
+        const int st = matvec((cudaStream_t) s, dtype, layout, w, w_row_stride, k, n, x + c * ldx, ldx, mm, y + c * ldy, ldy);
+        if (st != ST_OK) return st;
+    }
+    return ST_OK;
+}
+
+int sm100_mul_mat_multi(sm100_stream_t s, int count, const int * dtypes, const int * layouts, const void * const * ws, int64_t k,
+                        const int64_t * ns, const float * x, float * const * ys) {
+    if (count < 1 || count > 3 || dtypes == nullptr || layouts == nullptr || ws == nullptr || ns == nullptr || ys == nullptr)
+        return fail(ST_INVALID, "mul_mat_multi: 1..3 weight tensors with their dtypes, layouts and outputs are required");
+    for (int i = 0; i < count; ++i) {
+        const int st = matvec((cudaStream_t) s, dtypes[i], layouts[i], ws[i], 0, k, ns[i], x, k, 1, ys[i], ns[i]);
+        if (st != ST_OK) return st;
+    }
+    return ST_OK;
+}
+
+}  // extern "C"

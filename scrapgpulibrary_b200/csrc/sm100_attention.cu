@@ -1,0 +1,257 @@
+// Fused decode attention for sm_100a: the values of scrapgpu_scaled_dot_product_attention
+// (src/core/attention.cpp:558-678 of the reference; contract include/scrapgpu/attention.h:11-46), which the
+// reference composes per head from CPY(V^T) + MUL_MAT(K.Q) + SOFT_MAX(+host-built mask) + MUL_MAT with a
+// host round trip per tile.  Here: one pass over the KV cache, split along the key axis so that all SMs
+// stream K and V (flash-decoding), query heads of a KV group processed together (GQA), f32 throughout.
+//
+//   scores[k] = (sum_d K[d,k,hk] Q[d,q,h]) * scale (+ mask[k,q,h]),  key k visible iff !causal or k <= offset + q
+//   out[dv,q,h] = sum_k softmax(scores)[k] V[dv,k,hk];  a query with no visible key gives zeros (:497-516)
+//
+// Kernel 1 writes per split an un-normalised partial (running max m, sum l, accumulator o[Dv]) into a
+// scratch buffer; kernel 2 merges the splits.  HBM-bound: algorithmic bytes = 2 * 4 * D * visible keys * Hkv.
+#include "sm100_common.cuh"
+
+#include <mutex>
+#include <vector>
+
+namespace sm100 {
+
+constexpr int ATT_MAX_GROUP = 8;    // query heads per KV head handled together (reference limit: ops_matmul.cpp:19)
+constexpr int ATT_CHUNK = 512;      // keys per split at most (scores of a split live in shared memory)
+constexpr int ATT_THREADS = 256;
+
+struct AttnArgs {
+    const float * q; const float * k; const float * v; const float * mask; float * out; float * scratch;
+    const int32_t * positions;
+    int64_t d, dv, nq, nk, hq, hkv, offset;
+    int64_t mask_heads;
+    int splits, chunk, causal;
+    float scale;
+};
+
+// scratch layout per (q, h, split): [m, l, o[dv]]
+__device__ __forceinline__ int64_t scratch_index(const AttnArgs & a, int64_t q, int64_t h, int split) {
+    return ((q * a.hq + h) * a.splits + split) * (a.dv + 2);
+}
+
+__device__ __forceinline__ int64_t visible_keys(const AttnArgs & a, int64_t q) {
+    if (!a.causal) return a.nk;
+    const int64_t off = a.positions != nullptr ? (int64_t) a.positions[0] : a.offset;
+    const int64_t vis = off + q + 1;
+    return vis < a.nk ? (vis < 0 ? 0 : vis) : a.nk;
+}
+
+__global__ void __launch_bounds__(ATT_THREADS) attn_partial_kernel(AttnArgs a) {
+    pdl_wait();
+    pdl_launch_dependents();
+    extern __shared__ float smem[];
+    const int split = blockIdx.x;
+    const int64_t hk = blockIdx.y, q = blockIdx.z;
+    const int group = (int) (a.hq / a.hkv);
+    float * sq = smem;                                  // [group][d]
+    float * ss = sq + (int64_t) group * a.d;            // [group][chunk]
+    float * sred = ss + (int64_t) group * a.chunk;      // [2][group][dv] partial accumulators of the two key halves
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
+
+    const int64_t n_vis = visible_keys(a, q);
+    const int64_t k0 = (int64_t) split * a.chunk;
+    const int64_t k1 = k0 + a.chunk < n_vis ? k0 + a.chunk : n_vis;
+    const int64_t count = k1 > k0 ? k1 - k0 : 0;
+
+    for (int64_t i = tid; i < (int64_t) group * a.d; i += blockDim.x) {
+        const int64_t g = i / a.d, dd = i % a.d;
+        sq[i] = a.q[((hk * group + g) * a.nq + q) * a.d + dd];
+    }
+    __syncthreads();
+
+    // scores: one warp per key, all query heads of the group at once
+    for (int64_t kk = warp; kk < count; kk += nwarps) {
+        const float * kr = a.k + (hk * a.nk + k0 + kk) * a.d;
+        float acc[ATT_MAX_GROUP];
+#pragma unroll
+        for (int g = 0; g < ATT_MAX_GROUP; ++g) acc[g] = 0.f;
+        for (int64_t dd = lane; dd < a.d; dd += 32) {
+            const float kvv = kr[dd];
+#pragma unroll
+            for (int g = 0; g < ATT_MAX_GROUP; ++g)
+                if (g < group) acc[g] = fmaf(kvv, sq[g * a.d + dd], acc[g]);
+        }
+#pragma unroll
+        for (int g = 0; g < ATT_MAX_GROUP; ++g) {
+            if (g < group) {
+                float v = acc[g];
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+                if (lane == 0) {
+                    v *= a.scale;
+                    if (a.mask != nullptr) {
+                        const int64_t mh = a.mask_heads == 1 ? 0 : hk * group + g;
+                        v += a.mask[(mh * a.nq + q) * a.nk + k0 + kk];
+                    }
+                    ss[g * a.chunk + kk] = v;
+                }
+            }
+        }
+    }
+    __syncthreads();
+
+    // per head: max, exponentials, sum (warp g handles head g; group <= 8 = warps)
+    for (int g = warp; g < group; g += nwarps) {
+        float m = -INFINITY;
+        for (int64_t kk = lane; kk < count; kk += 32) m = fmaxf(m, ss[g * a.chunk + kk]);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+        float l = 0.f;
+        for (int64_t kk = lane; kk < count; kk += 32) {
+            const float e = m == -INFINITY ? 0.f : expf(ss[g * a.chunk + kk] - m);
+            ss[g * a.chunk + kk] = e;
+            l += e;
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) l += __shfl_xor_sync(0xffffffffu, l, o);
+        if (lane == 0) {
+            float * dst = a.scratch + scratch_index(a, q, hk * group + g, split);
+            dst[0] = m;
+            dst[1] = l;
+        }
+    }
+    __syncthreads();
+
+    // o[g][dv] = sum_k e[g][k] V[dv,k]: threads cover dv, the two halves of the block take alternate keys
+    const int halves = blockDim.x >= 2 * a.dv ? 2 : 1;
+    const int half = halves == 2 ? (int) (tid / a.dv) : 0;
+    for (int64_t dv0 = 0; dv0 < a.dv; dv0 += blockDim.x / halves) {
+        const int64_t dvi = dv0 + (halves == 2 ? tid % a.dv : tid);
+        const bool active = dvi < a.dv && half < halves;
+        float o[ATT_MAX_GROUP];
+#pragma unroll
+        for (int g = 0; g < ATT_MAX_GROUP; ++g) o[g] = 0.f;
+        if (active) {
+            for (int64_t kk = half; kk < count; kk += halves) {
+                const float vv = a.v[(hk * a.nk + k0 + kk) * a.dv + dvi];
+#pragma unroll
+                for (int g = 0; g < ATT_MAX_GROUP; ++g)
+                    if (g < group) o[g] = fmaf(ss[g * a.chunk + kk], vv, o[g]);
+            }
+        }
+        if (halves == 2) {
+            if (active && half == 1)
+                for (int g = 0; g < group; ++g) sred[g * a.dv + dvi] = o[g];
+            __syncthreads();
+            if (active && half == 0)
+                for (int g = 0; g < group; ++g) a.scratch[scratch_index(a, q, hk * group + g, split) + 2 + dvi] = o[g] + sred[g * a.dv + dvi];
+            __syncthreads();
+        } else if (active) {
+            for (int g = 0; g < group; ++g) a.scratch[scratch_index(a, q, hk * group + g, split) + 2 + dvi] = o[g];
+        }
+    }
+}
+
+__global__ void attn_combine_kernel(AttnArgs a) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int64_t h = blockIdx.x, q = blockIdx.y;
+    const float * base = a.scratch + scratch_index(a, q, h, 0);
+    const int64_t stride = a.dv + 2;
+    float m = -INFINITY;
+    for (int s = 0; s < a.splits; ++s) m = fmaxf(m, base[s * stride]);
+    float l = 0.f;
+    for (int s = 0; s < a.splits; ++s) {
+        const float ms = base[s * stride];
+        if (ms != -INFINITY) l += base[s * stride + 1] * expf(ms - m);
+    }
+    for (int64_t dvi = threadIdx.x; dvi < a.dv; dvi += blockDim.x) {
+        float o = 0.f;
+        if (m != -INFINITY) {
+            for (int s = 0; s < a.splits; ++s) {
+                const float ms = base[s * stride];
+                if (ms != -INFINITY) o = fmaf(base[s * stride + 2 + dvi], expf(ms - m), o);
+            }
+            o = o / l;
+        }
+        a.out[(h * a.nq + q) * a.dv + dvi] = o;
+    }
+}
+
+// per-device scratch owned by the library, grown on demand (never shrinks)
+static std::mutex g_ws_mutex;
+static std::vector<void *> g_ws_ptr;
+static std::vector<size_t> g_ws_size;
+
+static int workspace(size_t bytes, float ** out) {
+    int dev = 0;
+    SM100_CUDA(cudaGetDevice(&dev));
+    std::lock_guard<std::mutex> lock(g_ws_mutex);
+    if ((int) g_ws_ptr.size() <= dev) {
+        g_ws_ptr.resize(dev + 1, nullptr);
+        g_ws_size.resize(dev + 1, 0);
+    }
+    if (g_ws_size[dev] < bytes) {
+        if (g_ws_ptr[dev] != nullptr) SM100_CUDA(cudaFree(g_ws_ptr[dev]));
+        g_ws_ptr[dev] = nullptr;
+        g_ws_size[dev] = 0;
+        size_t want = bytes < (size_t) (8u << 20) ? (size_t) (8u << 20) : bytes;
+        SM100_CUDA(cudaMalloc(&g_ws_ptr[dev], want));
+        g_ws_size[dev] = want;
+    }
+    *out = (float *) g_ws_ptr[dev];
+    return ST_OK;
+}
+
+int attention_launch(cudaStream_t s, AttnArgs a) {
+    const int group = (int) (a.hq / a.hkv);
+    const size_t smem = ((size_t) group * a.d + (size_t) group * a.chunk + (size_t) group * a.dv) * sizeof(float);
+    if (smem > 48 * 1024) {
+        SM100_CUDA(cudaFuncSetAttribute(attn_partial_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
+    }
+    int st = launch(attn_partial_kernel, dim3((unsigned) a.splits, (unsigned) a.hkv, (unsigned) a.nq), dim3(ATT_THREADS), smem, s, a);
+    if (st != ST_OK) return st;
+    const int ct = a.dv >= 256 ? 256 : a.dv >= 128 ? 128 : 64;
+    return launch(attn_combine_kernel, dim3((unsigned) a.hq, (unsigned) a.nq), dim3(ct), 0, s, a);
+}
+
+int attention_check(const AttnArgs & a) {
+    if (a.q == nullptr || a.k == nullptr || a.v == nullptr || a.out == nullptr) return fail(ST_INVALID, "attention: null tensor pointer");
+    if (a.d <= 0 || a.dv <= 0 || a.nq <= 0 || a.nk <= 0 || a.hq <= 0 || a.hkv <= 0) return fail(ST_INVALID, "attention: dimensions must be positive");
+    if (a.hq % a.hkv != 0) return fail(ST_INVALID, "attention: Hq must be divisible by Hkv");
+    if (a.hq / a.hkv > ATT_MAX_GROUP) return fail(ST_UNSUPPORTED, "attention: more than 8 query heads per KV head");
+    if (a.nq > 65535 || a.hkv > 65535) return fail(ST_UNSUPPORTED, "attention: too many queries or KV heads for one launch");
+    if (a.d > 1024 || a.dv > 1024) return fail(ST_UNSUPPORTED, "attention: head dimension above 1024");
+    return ST_OK;
+}
+
+size_t attention_scratch_bytes(const AttnArgs & a) { return (size_t) a.nq * a.hq * a.splits * (a.dv + 2) * sizeof(float); }
+
+void attention_plan(AttnArgs & a) {
+    // enough splits to occupy the SMs, at most ATT_CHUNK keys per split
+    const int64_t ctas_wanted = (int64_t) sm_count() * 2;
+    int64_t per_head = a.hkv * a.nq;
+    int64_t splits = (ctas_wanted + per_head - 1) / per_head;
+    int64_t chunk = (a.nk + splits - 1) / splits;
+    if (chunk < 32) chunk = 32;
+    if (chunk > ATT_CHUNK) chunk = ATT_CHUNK;
+    a.chunk = (int) chunk;
+    a.splits = (int) ((a.nk + chunk - 1) / chunk);
+}
+
+}  // namespace sm100
+
+using namespace sm100;
+
+extern "C" int sm100_attention(sm100_stream_t s, const float * q, const float * k, const float * v, const float * mask, int64_t mask_heads,
+                               float * out, int64_t d, int64_t dv, int64_t nq, int64_t nk, int64_t hq, int64_t hkv, int causal,
+                               int64_t offset, const int32_t * positions, float scale) {
+    AttnArgs a = {};
+    a.q = q; a.k = k; a.v = v; a.mask = mask; a.out = out; a.positions = positions;
+    a.d = d; a.dv = dv; a.nq = nq; a.nk = nk; a.hq = hq; a.hkv = hkv; a.offset = offset;
+    a.mask_heads = mask_heads <= 1 ? 1 : mask_heads;
+    a.causal = causal; a.scale = scale;
+    const int st = attention_check(a);
+    if (st != ST_OK) return st;
+    attention_plan(a);
+    float * ws = nullptr;
+    const int sw = workspace(attention_scratch_bytes(a), &ws);
+    if (sw != ST_OK) return sw;
+    a.scratch = ws;
+    return attention_launch((cudaStream_t) s, a);
+}

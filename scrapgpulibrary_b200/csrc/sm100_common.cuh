@@ -1,0 +1,86 @@
+// Shared declarations of libscrapgpu_sm100: status codes, error reporting, launch helpers.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <cuda_fp16.h>
+
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+
+#include "scrapgpu_sm100.h"
+
+namespace sm100 {
+
+// scrapgpu_status values (include/scrapgpu/status.h:10-17 of the reference)
+enum : int { ST_OK = 0, ST_UNSUPPORTED = 1, ST_INVALID = 2, ST_OOM = 3, ST_BACKEND = 4, ST_LOST = 5 };
+
+// scrapgpu_dtype values (include/scrapgpu/tensor.h:10-22)
+enum : int { DT_F32 = 0, DT_F16 = 1, DT_I32 = 2, DT_Q4_0 = 16, DT_Q8_0 = 17, DT_Q4_K = 32, DT_Q6_K = 33 };
+
+enum : int { LAYOUT_NATURAL = 0, LAYOUT_PACKED = 1 };
+
+int fail(int status, const char * fmt, ...);
+int cuda_fail(cudaError_t e, const char * what);
+
+#define SM100_CUDA(call)                                          \
+    do {                                                          \
+        cudaError_t e_ = (call);                                  \
+        if (e_ != cudaSuccess) return ::sm100::cuda_fail(e_, #call); \
+    } while (0)
+
+inline int block_elems(int dtype) {
+    switch (dtype) {
+        case DT_Q4_0: case DT_Q8_0: return 32;
+        case DT_Q4_K: case DT_Q6_K: return 256;
+        case DT_F32: case DT_F16: case DT_I32: return 1;
+        default: return 0;
+    }
+}
+
+inline int block_bytes(int dtype) {
+    switch (dtype) {
+        case DT_Q4_0: return 18;
+        case DT_Q8_0: return 34;
+        case DT_Q4_K: return 144;
+        case DT_Q6_K: return 210;
+        case DT_F32: case DT_I32: return 4;
+        case DT_F16: return 2;
+        default: return 0;
+    }
+}
+
+inline bool is_quant(int dtype) { return block_elems(dtype) > 1; }
+
+int sm_count();          // SMs of the current device (cached per device)
+bool pdl_enabled();
+void count_launch();
+
+// Launches `kernel` on `stream`; with programmatic dependent launch when enabled, so the kernel may
+// start (and prefetch) while its predecessor on the stream drains.  Kernels launched through this
+// must execute griddepcontrol.wait before they read anything a predecessor wrote or write anything.
+template <typename... KArgs, typename... Args>
+int launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    if (pdl_enabled()) {
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+    }
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+    if (e != cudaSuccess) return cuda_fail(e, "kernel launch");
+    count_launch();
+    return ST_OK;
+}
+
+// device side of programmatic dependent launch
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+}  // namespace sm100

@@ -1,0 +1,58 @@
+// The B200 weight layout ("backend-packed", layout tag 1) shared by the host packer and the kernels.
+//
+// A quantized tensor W = [K, N] has B = K / block_elems blocks per row and T = N * B blocks in all,
+// numbered t = n * B + b.  The natural (GGUF) layout stores whole blocks one after another, which
+// puts a 2..16-byte header between every run of quants, so no quant run is 16-byte aligned for
+// Q4_0 / Q8_0 / Q6_K.  The packed layout splits the tensor into planes, one per block field, each
+// plane holding that field of all T blocks in block order.  The planes follow each other without
+// padding, so the packed tensor has exactly the natural byte count and packing is a permutation.
+//
+//   Q4_K  (144 B):  Q plane  T x 128 B   the 128 quant bytes, natural order
+//                   H plane  T x  16 B   f16 d, f16 dmin, then the eight 6-bit (scale, min) pairs
+//                                        re-encoded as four 24-bit little-endian fields, field p =
+//                                        sc[2p] | m[2p] << 6 | sc[2p+1] << 12 | m[2p+1] << 18
+//   Q6_K  (210 B):  L plane  T x 128 B   low nibbles, regrouped in four 32-byte units: unit u = 2h + c
+//                                        holds ql[64h + 16c + i] then ql[64h + 32 + 16c + i], i < 16
+//                   X plane  T x  64 B   the 2-bit high parts, natural order (unit u uses bytes 16u..16u+15)
+//                   S plane  T x  16 B   int8 scales regrouped per unit: sc[8h + c + {0, 2, 4, 6}]
+//                   D plane  T x   2 B   f16 d
+//   Q4_0  (18 B):   Q plane  T x  16 B   quant bytes;  D plane  T x 2 B   f16 d
+//   Q8_0  (34 B):   Q plane  T x  32 B   int8 quants;  D plane  T x 2 B   f16 d
+//
+// Every 16-byte quant unit is 16-byte aligned when the tensor base is (buffers are 256-byte aligned),
+// each block's quants start on a 128-byte line for the K-quants, and rows [r0, r1) of any plane are one
+// contiguous run, which is what bulk (TMA) copies and fully coalesced 16-byte loads want.
+#pragma once
+
+#include <cstdint>
+
+namespace sm100 {
+
+struct Planes {
+    // byte offsets of the planes from the tensor base, and bytes per block in each plane
+    int64_t off[4];
+    int32_t per_block[4];
+    int32_t count;
+};
+
+inline Planes planes_for(int dtype, int64_t total_blocks) {
+    Planes p = {};
+    const int32_t q4k[] = {128, 16}, q6k[] = {128, 64, 16, 2}, q40[] = {16, 2}, q80[] = {32, 2};
+    const int32_t * f = nullptr;
+    switch (dtype) {
+        case 32: f = q4k; p.count = 2; break;
+        case 33: f = q6k; p.count = 4; break;
+        case 16: f = q40; p.count = 2; break;
+        case 17: f = q80; p.count = 2; break;
+        default: return p;
+    }
+    int64_t off = 0;
+    for (int i = 0; i < p.count; ++i) {
+        p.off[i] = off;
+        p.per_block[i] = f[i];
+        off += (int64_t) f[i] * total_blocks;
+    }
+    return p;
+}
+
+}  // namespace sm100

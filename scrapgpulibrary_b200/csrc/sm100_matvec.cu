@@ -1,0 +1,381 @@
+// Decode MUL_MAT (M <= 8 activation columns): fused dequantize-and-dot matvec kernels for sm_100a.
+//
+// Replaces, for the `cuda_sm100` backend, the reference's k_mvr_q4_0 / k_mvr_q8_0
+// (src/backends/opencl11/kernels/mul_mv_r.cl:240-323), k_mvr_q4_k / k_mvr_q6_k (mul_mv_k.cl:396-486)
+// and the CPU path exec_mul_mat (src/core/ref/ops.cpp:891-984).  HBM-bound: each weight byte is read
+// once with 16-byte streaming loads, unpacked in registers, accumulated in f32.
+//
+// Kernel A  matvec_stream<Unit>   packed layout, M = 1, K a multiple of 32 units.  A thread owns one
+//           column unit (16 or 32 bytes of every row it visits) and keeps the matching activations
+//           in registers for the whole launch, so the inner loop has no shared-memory or L1 traffic
+//           besides the weight stream itself.  The weight loads of the first rows are issued before
+//           griddepcontrol.wait, so under programmatic dependent launch they overlap the tail of the
+//           previous kernel on the stream.
+// Kernel B  matvec_rows<Unit, M>  any layout / shape / M <= 8: one warp per weight row, activations
+//           through L1.
+#include "sm100_quant_units.cuh"
+
+namespace sm100 {
+
+// ---- natural-layout loading: assemble the packed-unit registers from GGUF blocks -----------------
+
+__device__ __forceinline__ uint32_t ld_u32_any(const uint8_t * p) {
+    const uintptr_t a = (uintptr_t) p;
+    if ((a & 3) == 0) return __ldg((const uint32_t *) p);
+    if ((a & 1) == 0) return (uint32_t) __ldg((const unsigned short *) p) | ((uint32_t) __ldg((const unsigned short *) (p + 2)) << 16);
+    return (uint32_t) __ldg(p) | ((uint32_t) __ldg(p + 1) << 8) | ((uint32_t) __ldg(p + 2) << 16) | ((uint32_t) __ldg(p + 3) << 24);
+}
+__device__ __forceinline__ uint4 ld_u128_any(const uint8_t * p) {
+    if (((uintptr_t) p & 15) == 0) return __ldg((const uint4 *) p);
+    return make_uint4(ld_u32_any(p), ld_u32_any(p + 4), ld_u32_any(p + 8), ld_u32_any(p + 12));
+}
+__device__ __forceinline__ uint32_t ld_u16_any(const uint8_t * p) {
+    if (((uintptr_t) p & 1) == 0) return (uint32_t) __ldg((const unsigned short *) p);
+    return (uint32_t) __ldg(p) | ((uint32_t) __ldg(p + 1) << 8);
+}
+
+template <class U> struct Natural;
+
+template <> struct Natural<UnitQ4K> {
+    __device__ static __forceinline__ void load(const uint8_t * row, int cu, UnitQ4K::Data & d) {
+        const uint8_t * blk = row + (int64_t) (cu >> 3) * 144;
+        d.q = ld_u128_any(blk + 16 + (cu & 7) * 16);
+        const uint32_t h0 = ld_u32_any(blk), s0 = ld_u32_any(blk + 4), s1 = ld_u32_any(blk + 8), s2 = ld_u32_any(blk + 12);
+        // natural 12-byte scale bytes s[0..11] -> the four 24-bit fields of the packed header
+        uint32_t f[4];
+#pragma unroll
+        for (int p = 0; p < 4; ++p) {
+            uint32_t sc[2], mn[2];
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int j = 2 * p + e;
+                if (j < 4) {
+                    sc[e] = (s0 >> (8 * j)) & 63u;
+                    mn[e] = (s1 >> (8 * j)) & 63u;
+                } else {
+                    const uint32_t lo = (s2 >> (8 * (j - 4))) & 255u;
+                    sc[e] = (lo & 15u) | ((((s0 >> (8 * (j - 4))) & 255u) >> 6) << 4);
+                    mn[e] = (lo >> 4) | ((((s1 >> (8 * (j - 4))) & 255u) >> 6) << 4);
+                }
+            }
+            f[p] = sc[0] | (mn[0] << 6) | (sc[1] << 12) | (mn[1] << 18);
+        }
+        d.h.x = h0;
+        d.h.y = f[0] | (f[1] << 24);
+        d.h.z = (f[1] >> 8) | (f[2] << 16);
+        d.h.w = (f[2] >> 16) | (f[3] << 8);
+    }
+};
+
+template <> struct Natural<UnitQ6K> {
+    __device__ static __forceinline__ void load(const uint8_t * row, int cu, UnitQ6K::Data & d) {
+        const uint8_t * blk = row + (int64_t) (cu >> 2) * 210;
+        const int u = cu & 3, h = u >> 1, c = u & 1;
+        d.a = ld_u128_any(blk + 64 * h + 16 * c);
+        d.b = ld_u128_any(blk + 64 * h + 32 + 16 * c);
+        d.h = ld_u128_any(blk + 128 + 16 * u);
+        const uint8_t * s = blk + 192 + 8 * h + c;
+        d.sc = (uint32_t) __ldg(s) | ((uint32_t) __ldg(s + 2) << 8) | ((uint32_t) __ldg(s + 4) << 16) | ((uint32_t) __ldg(s + 6) << 24);
+        d.d = ld_u16_any(blk + 208);
+    }
+};
+
+template <> struct Natural<UnitQ40> {
+    __device__ static __forceinline__ void load(const uint8_t * row, int cu, UnitQ40::Data & d) {
+        const uint8_t * blk = row + (int64_t) cu * 18;
+        d.q = ld_u128_any(blk + 2);
+        d.d = ld_u16_any(blk);
+    }
+};
+
+template <> struct Natural<UnitQ80> {
+    __device__ static __forceinline__ void load(const uint8_t * row, int cu, UnitQ80::Data & d) {
+        const uint8_t * blk = row + (int64_t) (cu >> 1) * 34;
+        d.q = ld_u128_any(blk + 2 + (cu & 1) * 16);
+        d.d = ld_u16_any(blk);
+    }
+};
+
+// unquantized weights ride the same row kernel: F32 (4 per unit) and F16 (8 per unit)
+struct UnitF32 {
+    static constexpr int DTYPE = DT_F32;
+    static constexpr int WEIGHTS = 4;
+    static constexpr int UNITS_PER_BLOCK = 1;
+    static constexpr int XSUMS = 1;
+    struct Data { uint4 q; };
+    __device__ static __forceinline__ int64_t x_index(int cu, int i) { return (int64_t) cu * 4 + i; }
+    __device__ static __forceinline__ int sum_slot(int) { return 0; }
+    __device__ static __forceinline__ float dot(const Data & d, int, const float * x, const float *) {
+        float acc = __uint_as_float(d.q.x) * x[0];
+        acc = fmaf(__uint_as_float(d.q.y), x[1], acc);
+        acc = fmaf(__uint_as_float(d.q.z), x[2], acc);
+        return fmaf(__uint_as_float(d.q.w), x[3], acc);
+    }
+};
+template <> struct Natural<UnitF32> {
+    __device__ static __forceinline__ void load(const uint8_t * row, int cu, UnitF32::Data & d) { d.q = ld_u128_any(row + (int64_t) cu * 16); }
+};
+
+struct UnitF16 {
+    static constexpr int DTYPE = DT_F16;
+    static constexpr int WEIGHTS = 8;
+    static constexpr int UNITS_PER_BLOCK = 1;
+    static constexpr int XSUMS = 1;
+    struct Data { uint4 q; };
+    __device__ static __forceinline__ int64_t x_index(int cu, int i) { return (int64_t) cu * 8 + i; }
+    __device__ static __forceinline__ int sum_slot(int) { return 0; }
+    __device__ static __forceinline__ float dot(const Data & d, int, const float * x, const float *) {
+        const uint32_t w[4] = {d.q.x, d.q.y, d.q.z, d.q.w};
+        float acc = 0.f;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            acc = fmaf(half_bits_to_float(w[i] & 0xFFFFu), x[2 * i], acc);
+            acc = fmaf(half_bits_to_float(w[i] >> 16), x[2 * i + 1], acc);
+        }
+        return acc;
+    }
+};
+template <> struct Natural<UnitF16> {
+    __device__ static __forceinline__ void load(const uint8_t * row, int cu, UnitF16::Data & d) { d.q = ld_u128_any(row + (int64_t) cu * 16); }
+};
+
+// ---- activations of one unit into registers ---------------------------------------------------------
+
+template <class U>
+__device__ __forceinline__ void load_x_unit(const float * __restrict__ x, int cu, float (&xr)[U::WEIGHTS], float (&sums)[U::XSUMS]) {
+#pragma unroll
+    for (int s = 0; s < U::XSUMS; ++s) sums[s] = 0.f;
+#pragma unroll
+    for (int g = 0; g < U::WEIGHTS / 4; ++g) {
+        const float4 v = *reinterpret_cast<const float4 *>(x + U::x_index(cu, 4 * g));
+        xr[4 * g + 0] = v.x; xr[4 * g + 1] = v.y; xr[4 * g + 2] = v.z; xr[4 * g + 3] = v.w;
+        sums[U::sum_slot(4 * g)] += (v.x + v.y) + (v.z + v.w);
+    }
+}
+
+// ---- kernel A: packed, M = 1, register-resident activations ---------------------------------------
+
+template <class U>
+__global__ void __launch_bounds__(U::MAX_THREADS) matvec_stream(const uint8_t * __restrict__ w, Planes P, const float * __restrict__ x,
+                                                     float * __restrict__ y, int n_rows, int units_per_row, int rows_per_cta) {
+    constexpr int STREAM_RIF = U::ROWS_IN_FLIGHT;
+    extern __shared__ float red[];  // [STREAM_RIF][warps]
+    const int tid = threadIdx.x;
+    const int cu = tid % units_per_row;
+    const int rl = tid / units_per_row;
+    const int rp = blockDim.x / units_per_row;       // rows per pass
+    const int warps = blockDim.x >> 5;
+    const int warps_per_row = units_per_row >> 5;
+    const int64_t bpr = units_per_row / U::UNITS_PER_BLOCK;
+    const int row0 = blockIdx.x * rows_per_cta;
+    const int row_end = min(n_rows, row0 + rows_per_cta);
+
+    typename U::Data data[STREAM_RIF];
+    // first batch of weights: independent of the predecessor kernel, so issue before the dependency wait
+#pragma unroll
+    for (int i = 0; i < STREAM_RIF; ++i) {
+        const int r = row0 + rl + i * rp;
+        if (r < row_end) U::load(w, P, r, bpr, cu, data[i]);
+    }
+    pdl_wait();
+    float xr[U::WEIGHTS], sums[U::XSUMS];
+    load_x_unit<U>(x, cu, xr, sums);
+    pdl_launch_dependents();
+
+    for (int base = row0; base < row_end; base += rp * STREAM_RIF) {
+        float part[STREAM_RIF];
+#pragma unroll
+        for (int i = 0; i < STREAM_RIF; ++i) {
+            const int r = base + rl + i * rp;
+            part[i] = r < row_end ? U::dot(data[i], cu, xr, sums) : 0.f;
+        }
+        // prefetch the next batch while the reductions run
+        const int next = base + rp * STREAM_RIF;
+#pragma unroll
+        for (int i = 0; i < STREAM_RIF; ++i) {
+            const int r = next + rl + i * rp;
+            if (r < row_end) U::load(w, P, r, bpr, cu, data[i]);
+        }
+#pragma unroll
+        for (int i = 0; i < STREAM_RIF; ++i) {
+            float v = part[i];
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+            if ((tid & 31) == 0) red[i * warps + (tid >> 5)] = v;
+        }
+        __syncthreads();
+        if (tid < rp * STREAM_RIF) {
+            const int i = tid / rp, lr = tid % rp;
+            const int r = base + lr + i * rp;
+            if (r < row_end) {
+                float v = 0.f;
+                for (int k = 0; k < warps_per_row; ++k) v += red[i * warps + lr * warps_per_row + k];
+                y[r] = v;
+            }
+        }
+        __syncthreads();
+    }
+}
+
+// ---- kernel B: one warp per row, any layout, M <= 8 -------------------------------------------------
+
+template <class U, int M, bool PACKED>
+__global__ void __launch_bounds__(256) matvec_rows(const uint8_t * __restrict__ w, Planes P, int64_t w_row_stride,
+                                                   const float * __restrict__ x, int64_t ldx, float * __restrict__ y, int64_t ldy,
+                                                   int n_rows, int units_per_row) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int lane = threadIdx.x & 31;
+    const int warps = blockDim.x >> 5;
+    const int64_t bpr = units_per_row / U::UNITS_PER_BLOCK;
+    for (int r = blockIdx.x * warps + (threadIdx.x >> 5); r < n_rows; r += gridDim.x * warps) {
+        float acc[M];
+#pragma unroll
+        for (int m = 0; m < M; ++m) acc[m] = 0.f;
+        for (int cu = lane; cu < units_per_row; cu += 32) {
+            typename U::Data d;
+            if (PACKED) {
+                if constexpr (U::DTYPE >= 16) U::load(w, P, r, bpr, cu, d);
+            } else {
+                Natural<U>::load(w + (int64_t) r * w_row_stride, cu, d);
+            }
+#pragma unroll
+            for (int m = 0; m < M; ++m) {
+                float xr[U::WEIGHTS], sums[U::XSUMS];
+                load_x_unit<U>(x + (int64_t) m * ldx, cu, xr, sums);
+                acc[m] += U::dot(d, cu, xr, sums);
+            }
+        }
+#pragma unroll
+        for (int m = 0; m < M; ++m) {
+            float v = acc[m];
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+            if (lane == 0) y[(int64_t) m * ldy + r] = v;
+        }
+    }
+}
+
+// scalar tail for rows whose K is not a whole number of units or whose x is not 16-byte aligned
+// (F32 / F16 weights only; quantized rows are whole blocks by contract)
+template <int DT>
+__global__ void matvec_scalar(const uint8_t * __restrict__ w, int64_t w_row_stride, const float * __restrict__ x, int64_t ldx,
+                              float * __restrict__ y, int64_t ldy, int n_rows, int k, int m_cols) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int lane = threadIdx.x & 31;
+    const int warps = blockDim.x >> 5;
+    for (int r = blockIdx.x * warps + (threadIdx.x >> 5); r < n_rows; r += gridDim.x * warps) {
+        const uint8_t * row = w + (int64_t) r * w_row_stride;
+        for (int m = 0; m < m_cols; ++m) {
+            float acc = 0.f;
+            for (int i = lane; i < k; i += 32) {
+                float wv;
+                if (DT == DT_F32) wv = __ldg((const float *) row + i);
+                else wv = __half2float(__ldg((const __half *) row + i));
+                acc = fmaf(wv, x[(int64_t) m * ldx + i], acc);
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+            if (lane == 0) y[(int64_t) m * ldy + r] = acc;
+        }
+    }
+}
+
+// ---- host dispatch ------------------------------------------------------------------------------------
+
+template <class U>
+static int launch_stream(cudaStream_t s, const void * w, int64_t k, int64_t n, const float * x, float * y) {
+    const int upr = (int) (k / U::WEIGHTS);
+    // threads: a whole number of rows per pass, 256..512 threads
+    int rp = 1;
+    while ((rp * 2) * upr <= U::MAX_THREADS) rp *= 2;
+    const int threads = rp * upr;
+    const int64_t total_blocks = n * (k / block_elems(U::DTYPE));
+    const Planes P = planes_for(U::DTYPE, total_blocks);
+    // one wave: spread the rows over all SMs, rows per CTA a multiple of the rows per pass
+    const int ctas_per_sm = threads <= 256 ? 2 : 1;
+    const int64_t slots = (int64_t) sm_count() * ctas_per_sm;
+    int64_t rows_per_cta = (n + slots - 1) / slots;
+    rows_per_cta = (rows_per_cta + rp - 1) / rp * rp;
+    const int64_t grid = (n + rows_per_cta - 1) / rows_per_cta;
+    const size_t smem = (size_t) U::ROWS_IN_FLIGHT * (threads / 32) * sizeof(float);
+    return launch(matvec_stream<U>, dim3((unsigned) grid), dim3(threads), smem, s, (const uint8_t *) w, P, x, y, (int) n, upr,
+                  (int) rows_per_cta);
+}
+
+template <class U, bool PACKED>
+static int launch_rows(cudaStream_t s, const void * w, int64_t w_row_stride, int64_t k, int64_t n, const float * x, int64_t ldx,
+                       int64_t m, float * y, int64_t ldy) {
+    const int upr = (int) (k / U::WEIGHTS);
+    Planes P = {};
+    if (PACKED) P = planes_for(U::DTYPE, n * (k / block_elems(U::DTYPE)));
+    const int threads = 256, warps = threads / 32;
+    int64_t grid = (n + warps - 1) / warps;
+    const int64_t cap = (int64_t) sm_count() * 8;
+    if (grid > cap) grid = cap;
+    const dim3 g((unsigned) grid), b(threads);
+    const uint8_t * wp = (const uint8_t *) w;
+#define SM100_ROWS_CASE(MM) \
+    case MM: return launch(matvec_rows<U, MM, PACKED>, g, b, 0, s, wp, P, w_row_stride, x, ldx, y, ldy, (int) n, upr);
+    switch (m) {
+        SM100_ROWS_CASE(1) SM100_ROWS_CASE(2) SM100_ROWS_CASE(3) SM100_ROWS_CASE(4)
+        SM100_ROWS_CASE(5) SM100_ROWS_CASE(6) SM100_ROWS_CASE(7) SM100_ROWS_CASE(8)
+    }
+#undef SM100_ROWS_CASE
+    return fail(ST_INVALID, "matvec: M must be 1..8");
+}
+
+template <class U>
+static int matvec_dispatch(cudaStream_t s, int layout, const void * w, int64_t w_row_stride, int64_t k, int64_t n, const float * x,
+                           int64_t ldx, int64_t m, float * y, int64_t ldy) {
+    const int upr = (int) (k / U::WEIGHTS);
+    if (layout == LAYOUT_PACKED) {
+        if (m == 1 && upr % 32 == 0 && upr <= U::MAX_THREADS) return launch_stream<U>(s, w, k, n, x, y);
+        return launch_rows<U, true>(s, w, 0, k, n, x, ldx, m, y, ldy);
+    }
+    return launch_rows<U, false>(s, w, w_row_stride, k, n, x, ldx, m, y, ldy);
+}
+
+// Decode matvec entry used by sm100_mul_mat for m <= 8.  w_row_stride (bytes) only matters for the
+// natural layout; 0 means dense rows.
+int matvec(cudaStream_t s, int dtype, int layout, const void * w, int64_t w_row_stride, int64_t k, int64_t n, const float * x,
+           int64_t ldx, int64_t m, float * y, int64_t ldy) {
+    if (w == nullptr || x == nullptr || y == nullptr) return fail(ST_INVALID, "mul_mat: null tensor pointer");
+    if (k <= 0 || n <= 0 || m <= 0) return fail(ST_INVALID, "mul_mat: K, N and M must be positive");
+    if (n > INT32_MAX || k > INT32_MAX) return fail(ST_UNSUPPORTED, "mul_mat: dimension above 2^31");
+    if (m > 8) return fail(ST_INVALID, "matvec: M must be 1..8");
+    const int be = block_elems(dtype);
+    if (be == 0) return fail(ST_UNSUPPORTED, "mul_mat: unsupported weight dtype %d", dtype);
+    if (k % be != 0) return fail(ST_UNSUPPORTED, "mul_mat: quantized row length must be a multiple of the block size");
+    if (w_row_stride == 0) w_row_stride = k / be * block_bytes(dtype);
+    const bool x_aligned = ((uintptr_t) x & 15) == 0 && (m == 1 || (ldx % 4) == 0);
+    if (layout == LAYOUT_PACKED && !is_quant(dtype)) return fail(ST_UNSUPPORTED, "mul_mat: only quantized weights have a packed layout");
+    if (layout != LAYOUT_PACKED && layout != LAYOUT_NATURAL) return fail(ST_INVALID, "mul_mat: unknown layout %d", layout);
+    if (is_quant(dtype) && !x_aligned) return fail(ST_UNSUPPORTED, "mul_mat: activations must be 16-byte aligned (columns too)");
+    switch (dtype) {
+        case DT_Q4_K: return matvec_dispatch<UnitQ4K>(s, layout, w, w_row_stride, k, n, x, ldx, m, y, ldy);
+        case DT_Q6_K: return matvec_dispatch<UnitQ6K>(s, layout, w, w_row_stride, k, n, x, ldx, m, y, ldy);
+        case DT_Q4_0: return matvec_dispatch<UnitQ40>(s, layout, w, w_row_stride, k, n, x, ldx, m, y, ldy);
+        case DT_Q8_0: return matvec_dispatch<UnitQ80>(s, layout, w, w_row_stride, k, n, x, ldx, m, y, ldy);
+        case DT_F32:
+        case DT_F16: {
+            const int per = dtype == DT_F32 ? 4 : 8;
+            const bool w_aligned = true;  // ld_u128_any handles any alignment
+            if (x_aligned && w_aligned && k % per == 0) {
+                if (dtype == DT_F32) return launch_rows<UnitF32, false>(s, w, w_row_stride, k, n, x, ldx, m, y, ldy);
+                return launch_rows<UnitF16, false>(s, w, w_row_stride, k, n, x, ldx, m, y, ldy);
+            }
+            const int threads = 256, warps = 8;
+            int64_t grid = (n + warps - 1) / warps;
+            const int64_t cap = (int64_t) sm_count() * 8;
+            if (grid > cap) grid = cap;
+            if (dtype == DT_F32)
+                return launch(matvec_scalar<DT_F32>, dim3((unsigned) grid), dim3(threads), 0, s, (const uint8_t *) w, w_row_stride, x, ldx, y, ldy, (int) n, (int) k, (int) m);
+            return launch(matvec_scalar<DT_F16>, dim3((unsigned) grid), dim3(threads), 0, s, (const uint8_t *) w, w_row_stride, x, ldx, y, ldy, (int) n, (int) k, (int) m);
+        }
+    }
+    return fail(ST_UNSUPPORTED, "mul_mat: unsupported weight dtype %d", dtype);
+}
+
+}  // namespace sm100

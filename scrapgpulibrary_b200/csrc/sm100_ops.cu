@@ -1,0 +1,414 @@
+// The ops around the matvec in a decode step: bit-exact dequantization (GET_ROWS), RMS_NORM family,
+// ROPE, SOFT_MAX, SwiGLU, ADD, SET_ROWS, arg-max.  Each kernel cites the CPU reference whose values it
+// reproduces (src/core/ref/ops.cpp, src/core/ref/quant.cpp of the reference project).  Float expressions
+// that the reference evaluates as separate multiply / add / subtract use __fmul_rn / __fadd_rn / __fsub_rn
+// so that nvcc does not contract them into FMAs: the reference runs on SSE2 without FMA.
+#include "sm100_common.cuh"
+#include "sm100_layout.h"
+
+namespace sm100 {
+
+// ---- dequantization of one element ---------------------------------------------------------------
+
+__device__ __forceinline__ float h2f(const uint8_t * p) {
+    return __half2float(__ushort_as_half((unsigned short) ((uint32_t) p[0] | ((uint32_t) p[1] << 8))));
+}
+
+// natural block `blk`, element j of the block (src/core/ref/quant.cpp:30-108)
+__device__ float dequant_natural(int dtype, const uint8_t * blk, int j) {
+    switch (dtype) {
+        case DT_Q4_0: {
+            const float d = h2f(blk);
+            const int b = blk[2 + (j & 15)];
+            const int q = j < 16 ? (b & 15) : (b >> 4);
+            return __fmul_rn((float) (q - 8), d);
+        }
+        case DT_Q8_0:
+            return __fmul_rn((float) (int) (signed char) blk[2 + j], h2f(blk));
+        case DT_Q4_K: {
+            const float d = h2f(blk), dmin = h2f(blk + 2);
+            const uint8_t * s = blk + 4;
+            const int sb = j >> 5;  // sub-block 0..7
+            int sc, mn;
+            if (sb < 4) {
+                sc = s[sb] & 63;
+                mn = s[sb + 4] & 63;
+            } else {
+                sc = (s[sb + 4] & 15) | ((s[sb - 4] >> 6) << 4);
+                mn = (s[sb + 4] >> 4) | ((s[sb] >> 6) << 4);
+            }
+            const int byte = blk[16 + (j >> 6) * 32 + (j & 31)];
+            const int q = (j & 32) ? (byte >> 4) : (byte & 15);
+            return __fsub_rn(__fmul_rn(__fmul_rn(d, (float) sc), (float) q), __fmul_rn(dmin, (float) mn));
+        }
+        case DT_Q6_K: {
+            const float d = h2f(blk + 208);
+            const int h = j >> 7, r = j & 127, grp = r >> 5, l = r & 31;
+            const int lbyte = blk[64 * h + (grp & 1) * 32 + l];
+            const int lo = (grp & 2) ? (lbyte >> 4) : (lbyte & 15);
+            const int hi = (blk[128 + 32 * h + l] >> (2 * grp)) & 3;
+            const int q = (lo | (hi << 4)) - 32;
+            const int sc = (int) (signed char) blk[192 + 8 * h + (l >> 4) + 2 * grp];
+            return __fmul_rn(__fmul_rn(d, (float) sc), (float) q);
+        }
+    }
+    return 0.f;
+}
+
+// packed tensor at `base`, block t, element j: gathers the natural block fields from the planes
+__device__ float dequant_packed(int dtype, const uint8_t * base, const Planes & P, int64_t t, int j) {
+    switch (dtype) {
+        case DT_Q4_0: {
+            const float d = h2f(base + P.off[1] + t * 2);
+            const int b = base[P.off[0] + t * 16 + (j & 15)];
+            const int q = j < 16 ? (b & 15) : (b >> 4);
+            return __fmul_rn((float) (q - 8), d);
+        }
+        case DT_Q8_0:
+            return __fmul_rn((float) (int) (signed char) base[P.off[0] + t * 32 + j], h2f(base + P.off[1] + t * 2));
+        case DT_Q4_K: {
+            const uint8_t * h = base + P.off[1] + t * 16;
+            const float d = h2f(h), dmin = h2f(h + 2);
+            const int sb = j >> 5, p = sb >> 1;
+            const uint32_t f = (uint32_t) h[4 + 3 * p] | ((uint32_t) h[5 + 3 * p] << 8) | ((uint32_t) h[6 + 3 * p] << 16);
+            const int sc = (f >> ((sb & 1) * 12)) & 63, mn = (f >> ((sb & 1) * 12 + 6)) & 63;
+            const int byte = base[P.off[0] + t * 128 + (j >> 6) * 32 + (j & 31)];
+            const int q = (j & 32) ? (byte >> 4) : (byte & 15);
+            return __fsub_rn(__fmul_rn(__fmul_rn(d, (float) sc), (float) q), __fmul_rn(dmin, (float) mn));
+        }
+        case DT_Q6_K: {
+            const float d = h2f(base + P.off[3] + t * 2);
+            const int h = j >> 7, r = j & 127, grp = r >> 5, l = r & 31;
+            const int c = l >> 4, i = l & 15, u = 2 * h + c;
+            const int lbyte = base[P.off[0] + t * 128 + 32 * u + (grp & 1) * 16 + i];
+            const int lo = (grp & 2) ? (lbyte >> 4) : (lbyte & 15);
+            const int hi = (base[P.off[1] + t * 64 + 16 * u + i] >> (2 * grp)) & 3;
+            const int q = (lo | (hi << 4)) - 32;
+            const int sc = (int) (signed char) base[P.off[2] + t * 16 + 4 * u + grp];
+            return __fmul_rn(__fmul_rn(d, (float) sc), (float) q);
+        }
+    }
+    return 0.f;
+}
+
+// GET_ROWS (src/core/ref/ops.cpp:690-722): dst row i = dequantized table row ids[i]; an index outside
+// the table leaves the row untouched and raises the error flag
+__global__ void get_rows_kernel(int dtype, int layout, const uint8_t * __restrict__ table, Planes P, int64_t row_stride, int64_t k,
+                                int64_t table_rows, const int32_t * __restrict__ ids, int64_t n_ids, float * __restrict__ dst,
+                                int64_t ld_dst, int * __restrict__ error_flag) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int be = dtype == DT_Q4_0 || dtype == DT_Q8_0 ? 32 : dtype == DT_Q4_K || dtype == DT_Q6_K ? 256 : 1;
+    const int bb = dtype == DT_Q4_0 ? 18 : dtype == DT_Q8_0 ? 34 : dtype == DT_Q4_K ? 144 : dtype == DT_Q6_K ? 210 : dtype == DT_F16 ? 2 : 4;
+    const int64_t bpr = k / be;
+    for (int64_t i = blockIdx.y; i < n_ids; i += gridDim.y) {
+        const int64_t row = ids[i];
+        if (row < 0 || row >= table_rows) {
+            if (threadIdx.x == 0 && blockIdx.x == 0 && error_flag != nullptr) atomicExch(error_flag, 1);
+            continue;
+        }
+        for (int64_t e = blockIdx.x * (int64_t) blockDim.x + threadIdx.x; e < k; e += (int64_t) gridDim.x * blockDim.x) {
+            float v;
+            if (dtype == DT_F32) v = *reinterpret_cast<const float *>(table + row * row_stride + e * 4);
+            else if (dtype == DT_F16) v = __half2float(*reinterpret_cast<const __half *>(table + row * row_stride + e * 2));
+            else if (layout == LAYOUT_PACKED) v = dequant_packed(dtype, table, P, row * bpr + e / be, (int) (e % be));
+            else v = dequant_natural(dtype, table + row * row_stride + (e / be) * bb, (int) (e % be));
+            dst[i * ld_dst + e] = v;
+        }
+    }
+}
+
+// ---- RMS_NORM / RMS_NORM_MUL / ADD_RMS_NORM_MUL (ops.cpp:440-519) -------------------------------------
+// scale = 1 / sqrtf(float(sum_double(v^2) / ne0) + eps);  y = (v * scale) * w.  One CTA per row.
+__global__ void __launch_bounds__(256) rms_norm_kernel(const float * __restrict__ x, const float * __restrict__ add, const float * __restrict__ w,
+                                                       float * __restrict__ sum_out, float * __restrict__ y, int64_t ne0, float eps) {
+    pdl_wait();
+    pdl_launch_dependents();
+    __shared__ double red[8];
+    __shared__ float s_scale;
+    const int64_t row = blockIdx.x;
+    const float * xr = x + row * ne0;
+    const float * ar = add != nullptr ? add + row * ne0 : nullptr;
+    double sum = 0.0;
+    for (int64_t i = threadIdx.x; i < ne0; i += blockDim.x) {
+        float v = xr[i];
+        if (ar != nullptr) {
+            v = __fadd_rn(v, ar[i]);
+            if (sum_out != nullptr) sum_out[row * ne0 + i] = v;
+        }
+        sum += (double) v * (double) v;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = sum;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        double t = 0.0;
+        for (int i = 0; i < (int) (blockDim.x >> 5); ++i) t += red[i];
+        const float mean = (float) (t / (double) ne0);
+        s_scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(mean, eps)));
+    }
+    __syncthreads();
+    const float scale = s_scale;
+    for (int64_t i = threadIdx.x; i < ne0; i += blockDim.x) {
+        float v;
+        if (ar != nullptr && sum_out != nullptr) v = sum_out[row * ne0 + i];  // written above by this thread; sum_out may alias x
+        else v = ar != nullptr ? __fadd_rn(xr[i], ar[i]) : xr[i];
+        const float t = __fmul_rn(v, scale);
+        y[row * ne0 + i] = w != nullptr ? __fmul_rn(t, w[i]) : t;
+    }
+}
+
+// ---- ROPE (ops.cpp:530-634), no yarn, no frequency factors -------------------------------------------
+// One thread per rotated pair / copied pair.  With a table the (cos, sin) come from the caller, who
+// computed them with the reference's own recipe; positions outside the table, or no table at all, take
+// the on-device recipe: theta = pos * theta_scale^j by j sequential f32 multiplies, cosf / sinf.
+__global__ void rope_kernel(const float * __restrict__ x, const int32_t * __restrict__ positions, const float * __restrict__ table,
+                            int32_t table_first, int32_t table_n, float * __restrict__ y, int64_t ne0, int64_t heads, int64_t tokens,
+                            int n_dims, int neox, float theta_scale, float freq_scale, float attn_factor) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int64_t hp = ne0 / 2;
+    const int64_t total = tokens * heads * hp;
+    for (int64_t idx = blockIdx.x * (int64_t) blockDim.x + threadIdx.x; idx < total; idx += (int64_t) gridDim.x * blockDim.x) {
+        const int64_t j = idx % hp;
+        const int64_t rowi = idx / hp;  // token * heads + head
+        const int64_t t = rowi / heads;
+        const float * xr = x + rowi * ne0;
+        float * yr = y + rowi * ne0;
+        if (j < n_dims / 2) {
+            const int32_t pos = positions[t];
+            float cs, sn;
+            const int64_t rel = (int64_t) pos - table_first;
+            if (table != nullptr && rel >= 0 && rel < table_n) {
+                const float2 v = *reinterpret_cast<const float2 *>(table + (rel * (n_dims / 2) + j) * 2);
+                cs = v.x;
+                sn = v.y;
+            } else {
+                float theta = (float) pos;
+                for (int q = 0; q < (int) j; ++q) theta = __fmul_rn(theta, theta_scale);
+                const float th = __fmul_rn(freq_scale, theta);
+                cs = __fmul_rn(cosf(th), attn_factor);
+                sn = __fmul_rn(sinf(th), attn_factor);
+            }
+            const int64_t e0 = neox ? j : 2 * j;
+            const int64_t e1 = neox ? j + n_dims / 2 : 2 * j + 1;
+            const float x0 = xr[e0], x1 = xr[e1];
+            yr[e0] = __fsub_rn(__fmul_rn(x0, cs), __fmul_rn(x1, sn));
+            yr[e1] = __fadd_rn(__fmul_rn(x0, sn), __fmul_rn(x1, cs));
+        } else {
+            const int64_t e = 2 * (j - n_dims / 2) + n_dims;
+            yr[e] = xr[e];
+            yr[e + 1] = xr[e + 1];
+        }
+    }
+}
+
+// ---- SOFT_MAX (ops.cpp:636-684): one CTA per row, in place allowed ----------------------------------
+__device__ __forceinline__ float block_reduce(float v, bool is_max, float * red) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float u = __shfl_xor_sync(0xffffffffu, v, o);
+        v = is_max ? fmaxf(v, u) : v + u;
+    }
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+    __syncthreads();
+    float t = red[0];
+    for (int i = 1; i < (int) (blockDim.x >> 5); ++i) t = is_max ? fmaxf(t, red[i]) : t + red[i];
+    return t;
+}
+
+__global__ void __launch_bounds__(256) soft_max_kernel(const float * __restrict__ x, const float * __restrict__ mask, int64_t mask_row_stride,
+                                                       int64_t mask_rows, float * y, int64_t ne0, float scale) {
+    pdl_wait();
+    pdl_launch_dependents();
+    __shared__ float red[8];
+    const int64_t row = blockIdx.x;
+    const float * xr = x + row * ne0;
+    const float * mr = mask != nullptr ? mask + (row % mask_rows) * mask_row_stride : nullptr;
+    float * yr = y + row * ne0;
+    float mx = -INFINITY;
+    for (int64_t i = threadIdx.x; i < ne0; i += blockDim.x) {
+        float v = __fmul_rn(xr[i], scale);
+        if (mr != nullptr) v = __fadd_rn(v, mr[i]);
+        mx = fmaxf(mx, v);
+    }
+    mx = block_reduce(mx, true, red);
+    float sum = 0.f;
+    for (int64_t i = threadIdx.x; i < ne0; i += blockDim.x) {
+        float v = __fmul_rn(xr[i], scale);
+        if (mr != nullptr) v = __fadd_rn(v, mr[i]);
+        const float e = expf(v - mx);
+        yr[i] = e;
+        sum += e;
+    }
+    sum = block_reduce(sum, false, red);
+    const float inv = __fdiv_rn(1.0f, sum);
+    for (int64_t i = threadIdx.x; i < ne0; i += blockDim.x) yr[i] = __fmul_rn(yr[i], inv);
+}
+
+// ---- elementwise ---------------------------------------------------------------------------------
+// SwiGLU with split inputs (ops.cpp:383-425): y = (x / (1 + expf(-x))) * g
+__global__ void swiglu_kernel(const float * __restrict__ x, const float * __restrict__ g, float * __restrict__ y, int64_t n) {
+    pdl_wait();
+    pdl_launch_dependents();
+    for (int64_t i = blockIdx.x * (int64_t) blockDim.x + threadIdx.x; i < n; i += (int64_t) gridDim.x * blockDim.x) {
+        const float v = x[i];
+        y[i] = __fmul_rn(__fdiv_rn(v, __fadd_rn(1.0f, expf(-v))), g[i]);
+    }
+}
+
+// ADD (ops.cpp:280-312), same shapes
+__global__ void add_kernel(const float * __restrict__ a, const float * __restrict__ b, float * __restrict__ y, int64_t n) {
+    pdl_wait();
+    pdl_launch_dependents();
+    for (int64_t i = blockIdx.x * (int64_t) blockDim.x + threadIdx.x; i < n; i += (int64_t) gridDim.x * blockDim.x) y[i] = __fadd_rn(a[i], b[i]);
+}
+
+// SET_ROWS F32 -> F32 (ops.cpp:724-762): src [ne0, n_rows, heads], dst [ne0, dst_rows, heads], ids [n_rows]
+__global__ void set_rows_kernel(const float * __restrict__ src, const int32_t * __restrict__ ids, float * __restrict__ dst, int64_t ne0,
+                                int64_t n_rows, int64_t heads, int64_t dst_rows, int * __restrict__ error_flag) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int64_t total = ne0 * n_rows * heads;
+    for (int64_t idx = blockIdx.x * (int64_t) blockDim.x + threadIdx.x; idx < total; idx += (int64_t) gridDim.x * blockDim.x) {
+        const int64_t i0 = idx % ne0, i1 = (idx / ne0) % n_rows, i2 = idx / (ne0 * n_rows);
+        const int64_t row = ids[i1];
+        if (row < 0 || row >= dst_rows) {
+            if (error_flag != nullptr) atomicExch(error_flag, 1);
+            continue;
+        }
+        dst[(i2 * dst_rows + row) * ne0 + i0] = src[idx];
+    }
+}
+
+// TOP_K with k = 1 (ops.cpp:1189-1228): maximum, lowest index on ties.  Single CTA.
+__global__ void __launch_bounds__(1024) argmax_kernel(const float * __restrict__ x, int64_t n, int32_t * __restrict__ out) {
+    pdl_wait();
+    pdl_launch_dependents();
+    __shared__ float sv[32];
+    __shared__ int si[32];
+    float best = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int64_t i = threadIdx.x; i < n; i += blockDim.x) {
+        const float v = x[i];
+        if (v > best || bi == 0x7fffffff) { best = v; bi = (int) i; }  // increasing i: the first maximum wins
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+    }
+    if ((threadIdx.x & 31) == 0) { sv[threadIdx.x >> 5] = best; si[threadIdx.x >> 5] = bi; }
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        const int nw = blockDim.x >> 5;
+        best = threadIdx.x < nw ? sv[threadIdx.x] : -INFINITY;
+        bi = threadIdx.x < nw ? si[threadIdx.x] : 0x7fffffff;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+        }
+        if (threadIdx.x == 0) out[0] = bi;
+    }
+}
+
+static unsigned grid_for(int64_t n, int threads) {
+    int64_t g = (n + threads - 1) / threads;
+    const int64_t cap = (int64_t) sm_count() * 8;
+    if (g > cap) g = cap;
+    if (g < 1) g = 1;
+    return (unsigned) g;
+}
+
+}  // namespace sm100
+
+using namespace sm100;
+
+extern "C" {
+
+int sm100_get_rows(sm100_stream_t s, int dtype, int layout, const void * table, int64_t k, int64_t table_rows, const int32_t * ids,
+                   int64_t n_ids, float * dst, int64_t ld_dst) {
+    if (table == nullptr || ids == nullptr || dst == nullptr) return fail(ST_INVALID, "get_rows: null pointer");
+    const int be = block_elems(dtype);
+    if (be == 0 || dtype == DT_I32) return fail(ST_UNSUPPORTED, "get_rows: unsupported table dtype %d", dtype);
+    if (k <= 0 || table_rows <= 0 || n_ids <= 0 || k % be != 0) return fail(ST_INVALID, "get_rows: bad shape");
+    if (layout == LAYOUT_PACKED && !is_quant(dtype)) return fail(ST_UNSUPPORTED, "get_rows: only quantized tables have a packed layout");
+    Planes P = {};
+    if (layout == LAYOUT_PACKED) P = planes_for(dtype, table_rows * (k / be));
+    const int64_t row_stride = k / be * block_bytes(dtype);
+    const int threads = 256;
+    unsigned gx = (unsigned) ((k + threads - 1) / threads);
+    if (gx > 64) gx = 64;
+    const unsigned gy = (unsigned) (n_ids < 16384 ? n_ids : 16384);
+    return launch(get_rows_kernel, dim3(gx, gy), dim3(threads), 0, (cudaStream_t) s, dtype, layout, (const uint8_t *) table, P, row_stride, k,
+                  table_rows, ids, n_ids, dst, ld_dst, (int *) nullptr);
+}
+
+int sm100_rms_norm(sm100_stream_t s, const float * x, const float * add, const float * w, float * sum_out, float * y, int64_t ne0,
+                   int64_t rows, float eps) {
+    if (x == nullptr || y == nullptr) return fail(ST_INVALID, "rms_norm: null pointer");
+    if (ne0 <= 0 || rows <= 0 || rows > INT32_MAX) return fail(ST_INVALID, "rms_norm: bad shape");
+    return launch(rms_norm_kernel, dim3((unsigned) rows), dim3(256), 0, (cudaStream_t) s, x, add, w, sum_out, y, ne0, eps);
+}
+
+static int rope_common(sm100_stream_t s, const float * x, const int32_t * positions, const float * table, int32_t first, int32_t count,
+                       float * y, int64_t ne0, int64_t heads, int64_t tokens, int n_dims, int neox, float freq_base, float freq_scale,
+                       float attn_factor) {
+    if (x == nullptr || y == nullptr || positions == nullptr) return fail(ST_INVALID, "rope: null pointer");
+    if (n_dims <= 0 || n_dims % 2 != 0 || n_dims > ne0 || ne0 % 2 != 0)
+        return fail(ST_INVALID, "rope: n_dims must be a positive even number not above ne0 (ne0 even)");
+    if (heads <= 0 || tokens <= 0) return fail(ST_INVALID, "rope: bad shape");
+    const float theta_scale = powf(freq_base, -2.0f / (float) n_dims);
+    const int64_t total = tokens * heads * (ne0 / 2);
+    return launch(rope_kernel, dim3(grid_for(total, 256)), dim3(256), 0, (cudaStream_t) s, x, positions, table, first, count, y, ne0, heads,
+                  tokens, n_dims, neox, theta_scale, freq_scale, attn_factor);
+}
+
+int sm100_rope(sm100_stream_t s, const float * x, const int32_t * positions, const float * table, int32_t table_first_position,
+               int32_t table_positions, float * y, int64_t ne0, int64_t heads, int64_t tokens, int n_dims, int neox) {
+    if (table == nullptr || table_positions <= 0) return fail(ST_INVALID, "rope: the (cos, sin) table is missing");
+    // positions outside the table cannot be served without the frequency parameters
+    return rope_common(s, x, positions, table, table_first_position, table_positions, y, ne0, heads, tokens, n_dims, neox, 10000.0f, 1.0f, 1.0f);
+}
+
+int sm100_rope_direct(sm100_stream_t s, const float * x, const int32_t * positions, float * y, int64_t ne0, int64_t heads, int64_t tokens,
+                      int n_dims, int neox, float freq_base, float freq_scale, float attn_factor) {
+    return rope_common(s, x, positions, nullptr, 0, 0, y, ne0, heads, tokens, n_dims, neox, freq_base, freq_scale, attn_factor);
+}
+
+int sm100_soft_max(sm100_stream_t s, const float * x, const float * mask, int64_t mask_row_stride, float * y, int64_t ne0, int64_t rows,
+                   float scale) {
+    if (x == nullptr || y == nullptr) return fail(ST_INVALID, "soft_max: null pointer");
+    if (ne0 <= 0 || rows <= 0 || rows > INT32_MAX) return fail(ST_INVALID, "soft_max: bad shape");
+    return launch(soft_max_kernel, dim3((unsigned) rows), dim3(256), 0, (cudaStream_t) s, x, mask, mask_row_stride, rows, y, ne0, scale);
+}
+
+int sm100_swiglu(sm100_stream_t s, const float * x, const float * g, float * y, int64_t n) {
+    if (x == nullptr || g == nullptr || y == nullptr || n <= 0) return fail(ST_INVALID, "swiglu: bad arguments");
+    return launch(swiglu_kernel, dim3(grid_for(n, 256)), dim3(256), 0, (cudaStream_t) s, x, g, y, n);
+}
+
+int sm100_add(sm100_stream_t s, const float * a, const float * b, float * y, int64_t n) {
+    if (a == nullptr || b == nullptr || y == nullptr || n <= 0) return fail(ST_INVALID, "add: bad arguments");
+    return launch(add_kernel, dim3(grid_for(n, 256)), dim3(256), 0, (cudaStream_t) s, a, b, y, n);
+}
+
+int sm100_set_rows(sm100_stream_t s, const float * src, const int32_t * ids, float * dst, int64_t ne0, int64_t n_rows, int64_t heads,
+                   int64_t dst_rows) {
+    if (src == nullptr || ids == nullptr || dst == nullptr) return fail(ST_INVALID, "set_rows: null pointer");
+    if (ne0 <= 0 || n_rows <= 0 || heads <= 0 || dst_rows <= 0) return fail(ST_INVALID, "set_rows: bad shape");
+    return launch(set_rows_kernel, dim3(grid_for(ne0 * n_rows * heads, 256)), dim3(256), 0, (cudaStream_t) s, src, ids, dst, ne0, n_rows, heads,
+                  dst_rows, (int *) nullptr);
+}
+
+int sm100_argmax(sm100_stream_t s, const float * x, int64_t n, int32_t * out) {
+    if (x == nullptr || out == nullptr || n <= 0) return fail(ST_INVALID, "argmax: bad arguments");
+    return launch(argmax_kernel, dim3(1), dim3(1024), 0, (cudaStream_t) s, x, n, out);
+}
+
+}  // extern "C"

@@ -1,0 +1,94 @@
+"""GPU parity of the decode MUL_MAT (M <= 8) through the C ABI against the CPU oracle.
+
+Tolerance: NMSE <= 1e-6, the bar the reference sets for quantized MUL_MAT on a device
+(tests/ops/ops_tests.cpp:725) and that the benchmark's north star repeats.
+"""
+import numpy as np
+import pytest
+
+from oracle import sgref
+from tests import util as U
+
+pytestmark = pytest.mark.gpu
+TOL = 1e-6
+
+# (K, N): a single block, ragged row counts (24 and 33 rows: ops_tests.cpp:714-716), a K that is not a
+# multiple of 32 units, and the K of the benchmark shapes
+SMALL_SHAPES = [(256, 24), (512, 33), (1280, 17), (4096, 64), (12288, 40)]
+
+
+@pytest.mark.parametrize("dtype", U.QUANT, ids=lambda d: U.NAMES[d])
+@pytest.mark.parametrize("layout", [U.NATURAL, U.PACKED], ids=["natural", "packed"])
+@pytest.mark.parametrize("shape", SMALL_SHAPES, ids=lambda s: f"k{s[0]}n{s[1]}")
+def test_matvec_small(sm100, stream, dtype, layout, shape):
+    k, n = shape
+    wq = U.quantize(dtype, U.seeded_weights(1000 + dtype + k, n, k))
+    for m in (1, 2, 3, 4, 5, 8):
+        x = U.seeded_acts(7 * m + k, m, k)
+        want = sgref.mul_mat(dtype, wq, k, x)
+        got = U.device_mul_mat(sm100, stream, dtype, layout, wq, k, x)
+        e = sgref.nmse(got, want)
+        assert e <= TOL, f"{U.NAMES[dtype]} layout {layout} K={k} N={n} M={m}: NMSE {e:.3e}"
+
+
+@pytest.mark.parametrize("dtype", [U.F32, U.F16], ids=lambda d: U.NAMES[d])
+@pytest.mark.parametrize("shape", [(128, 40), (130, 7), (4096, 33)], ids=lambda s: f"k{s[0]}n{s[1]}")
+def test_matvec_float_weights(sm100, stream, dtype, shape):
+    k, n = shape
+    w = U.seeded_weights(5, n, k)
+    wq = U.quantize(dtype, w)
+    for m in (1, 4, 7):
+        x = U.seeded_acts(m, m, k)
+        want = sgref.mul_mat(dtype, wq, k, x)
+        got = U.device_mul_mat(sm100, stream, dtype, U.NATURAL, wq, k, x)
+        assert sgref.nmse(got, want) <= 1e-7
+
+
+def test_k_order_cancellation(sm100, stream):
+    """Row {1e20, 1, -1e20, 3, 4, 0...} against ones: the reference's increasing-K f32 order gives exactly 7
+    (tests/ref/ref_ops_tests.cpp:756-772).  A device reduction tree cannot promise that order; what must hold
+    is that the result is finite and the well-conditioned rows next to it are exact."""
+    k = 8
+    w = np.zeros((3, k), dtype=np.float32)
+    w[0, :5] = [1e20, 1, -1e20, 3, 4]
+    w[1, :5] = [1, 2, 3, 4, 5]
+    w[2, :] = 0.5
+    x = np.ones((1, k), dtype=np.float32)
+    got = U.device_mul_mat(sm100, stream, U.F32, U.NATURAL, U.quantize(U.F32, w), k, x)
+    assert np.isfinite(got).all()
+    assert got[0, 1] == 15.0 and got[0, 2] == 4.0
+
+
+@pytest.mark.parametrize("dtype,k,n", [(U.Q4_0, 4096, 4096), (U.Q4_K, 4096, 12288), (U.Q4_K, 12288, 4096),
+                                       (U.Q6_K, 4096, 4096), (U.Q8_0, 4096, 4096)],
+                         ids=["q4_0_4096x4096", "q4_k_4096x12288", "q4_k_12288x4096", "q6_k_4096x4096", "q8_0_4096x4096"])
+def test_matvec_benchmark_shapes(sm100, stream, dtype, k, n):
+    """The benchmark's shapes: full comparison with the oracle at M = 1 and 8, plus linearity
+    W(a + b) = Wa + Wb as a size-independent property."""
+    wq = U.quantize(dtype, U.seeded_weights(42 + dtype, n, k))
+    x = U.seeded_acts(99, 8, k)
+    want = sgref.mul_mat(dtype, wq, k, x)
+    got8 = U.device_mul_mat(sm100, stream, dtype, U.PACKED, wq, k, x)
+    assert sgref.nmse(got8, want) <= TOL
+    got1 = U.device_mul_mat(sm100, stream, dtype, U.PACKED, wq, k, x[:1])
+    assert sgref.nmse(got1, want[:1]) <= TOL
+    s = (x[0] + x[1])[None, :]
+    gsum = U.device_mul_mat(sm100, stream, dtype, U.PACKED, wq, k, s)
+    assert sgref.nmse(gsum[0], got8[0] + got8[1]) <= TOL
+    # natural layout gives the same values as packed (same arithmetic, different addressing)
+    gnat = U.device_mul_mat(sm100, stream, dtype, U.NATURAL, wq, k, x[:1])
+    assert sgref.nmse(gnat, want[:1]) <= TOL
+
+
+def test_matvec_argument_errors(sm100, stream):
+    buf = sm100.Buffer(1 << 16)
+    with pytest.raises(sm100.Sm100Error) as e:
+        sm100.mul_mat(stream, U.Q4_K, U.PACKED, buf, 100, 4, buf, 1, buf)  # K not a multiple of 256
+    assert e.value.status == 1
+    with pytest.raises(sm100.Sm100Error) as e:
+        sm100.mul_mat(stream, 99, U.NATURAL, buf, 256, 4, buf, 1, buf)  # unknown dtype
+    assert e.value.status == 1
+    with pytest.raises(sm100.Sm100Error) as e:
+        sm100.mul_mat(stream, U.Q4_K, U.PACKED, 0, 256, 4, buf, 1, buf)  # null weights
+    assert e.value.status == 2
+    buf.free()

@@ -1,0 +1,236 @@
+"""GPU parity of the decode ops around the matvec (RMS_NORM family, ROPE, SOFT_MAX, SwiGLU, ADD, SET_ROWS,
+arg-max, fused attention) through the C ABI: against the committed outputs of the compiled reference
+(tests/golden/ref_seeded.npz) and against the CPU oracle on larger seeded inputs.
+
+Tolerances: exact bits for ADD / SET_ROWS / arg-max and for the RMS_NORM family (same IEEE operations, the
+double-precision sum of squares differs from the sequential one only far below f32 resolution);
+NMSE <= 1e-6 (north star) -- in practice ~1e-13 -- for ROPE, SOFT_MAX, SwiGLU and attention, whose cos / sin /
+exp come from the CUDA math library rather than glibc."""
+import ctypes as C
+import os
+
+import numpy as np
+import pytest
+
+from oracle import sgref
+from tests import util as U
+
+pytestmark = pytest.mark.gpu
+GOLDEN = os.path.join(os.path.dirname(__file__), "golden")
+TOL = 1e-6
+
+
+@pytest.fixture(scope="module")
+def seeded():
+    return np.load(os.path.join(GOLDEN, "ref_seeded.npz"))
+
+
+def vp(x):
+    return C.c_void_p(x.ptr if hasattr(x, "ptr") else x)
+
+
+def run_rms(capi, stream, x, w=None, add=None, eps=1e-6):
+    rows, ne0 = x.shape
+    xb = U.to_device(capi, stream, x)
+    wb = U.to_device(capi, stream, w) if w is not None else None
+    ab = U.to_device(capi, stream, add) if add is not None else None
+    sb, sptr = U.guarded_output(capi, stream, x.size)
+    yb, yptr = U.guarded_output(capi, stream, x.size)
+    capi.check(capi.lib().sm100_rms_norm(stream.handle, xb.at(), ab.at() if ab else None, wb.at() if wb else None,
+                                         C.c_void_p(sptr) if add is not None else None, C.c_void_p(yptr), ne0, rows, eps), "rms_norm")
+    stream.sync()
+    y = U.read_guarded(capi, stream, yb, x.size).reshape(x.shape).copy()
+    s = U.read_guarded(capi, stream, sb, x.size).reshape(x.shape).copy()
+    return s, y
+
+
+def test_rms_norm_family(sm100, stream, seeded):
+    a, b, w = seeded["norm_a"], seeded["norm_b"], seeded["norm_w"]
+    _, y = run_rms(sm100, stream, a)
+    assert np.array_equal(y, seeded["rms_norm"])
+    _, y = run_rms(sm100, stream, a, w)
+    assert np.array_equal(y, seeded["rms_norm_mul"])
+    s, y = run_rms(sm100, stream, a, w, b)
+    assert np.array_equal(s, seeded["add_rms_norm_mul_sum"])
+    assert np.array_equal(y, seeded["add_rms_norm_mul"])
+    # decode sizes: hidden 4096 and per-head 128
+    for rows, ne0 in ((1, 4096), (40, 128), (3, 12288)):
+        x = U.seeded_acts(rows, rows, ne0) * 5
+        g = U.seeded_acts(11, 1, ne0)[0]
+        r = U.seeded_acts(12, rows, ne0)
+        ws, wy = sgref.rms_norm(x, g, add=r)
+        s, y = run_rms(sm100, stream, x, g, r)
+        assert np.array_equal(s, ws)
+        assert sgref.nmse(y, wy) <= 1e-12 and np.max(np.abs(y.view(np.int32) - wy.view(np.int32))) <= 1
+
+
+def run_rope(capi, stream, x, pos, n_dims, neox, base, table=None, first=0):
+    tokens, heads, ne0 = x.shape
+    xb, pb = U.to_device(capi, stream, x), U.to_device(capi, stream, pos.astype(np.int32))
+    yb, yptr = U.guarded_output(capi, stream, x.size)
+    if table is None:
+        capi.check(capi.lib().sm100_rope_direct(stream.handle, xb.at(), pb.at(), C.c_void_p(yptr), ne0, heads, tokens, n_dims, int(neox),
+                                                base, 1.0, 1.0), "rope_direct")
+    else:
+        tb = U.to_device(capi, stream, table)
+        capi.check(capi.lib().sm100_rope(stream.handle, xb.at(), pb.at(), tb.at(), first, table.shape[0], C.c_void_p(yptr), ne0, heads, tokens,
+                                         n_dims, int(neox)), "rope")
+    stream.sync()
+    return U.read_guarded(capi, stream, yb, x.size).reshape(x.shape).copy()
+
+
+def test_rope(sm100, stream, seeded):
+    x, pos = seeded["rope_x"], seeded["rope_pos"]
+    for mode, nd in ((1, 64), (0, 64), (1, 32)):
+        want = seeded[f"rope_mode{mode}_nd{nd}"]
+        got = run_rope(sm100, stream, x, pos, nd, mode == 1, 1e6)
+        assert sgref.nmse(got, want) <= TOL
+        # with the reference-recipe table the rotation is bit exact
+        table = sgref.rope_table(pos, nd, 1e6)
+        for i, p in enumerate(pos):
+            g = run_rope(sm100, stream, x[i:i + 1], pos[i:i + 1], nd, mode == 1, 1e6, table[i:i + 1], int(p))
+            assert np.array_equal(g, want[i:i + 1])
+    # decode shape: 32 heads of 128 at position 1024 + t, table covering 1024..1151
+    xq = U.seeded_acts(5, 32, 128).reshape(1, 32, 128)
+    positions = np.arange(1024, 1152)
+    table = sgref.rope_table(positions, 128, 1e6)
+    for p in (1024, 1100, 1151):
+        want = sgref.rope(xq, np.array([p], np.int32), 128, True, 1e6)
+        got = run_rope(sm100, stream, xq, np.array([p], np.int32), 128, True, 1e6, table, 1024)
+        assert np.array_equal(got, want)
+
+
+def run_softmax(capi, stream, x, mask, scale, in_place=False):
+    rows, ne0 = x.shape
+    mb = U.to_device(capi, stream, mask) if mask is not None else None
+    if in_place:
+        xb, xptr = U.guarded_output(capi, stream, x.size)
+        capi.check(capi.lib().sm100_memcpy_h2d(stream.handle, C.c_void_p(xptr), x.ctypes.data_as(C.c_void_p), x.nbytes, 1), "h2d")
+        yb, yptr = xb, xptr
+    else:
+        xb = U.to_device(capi, stream, x)
+        xptr = xb.ptr
+        yb, yptr = U.guarded_output(capi, stream, x.size)
+    capi.check(capi.lib().sm100_soft_max(stream.handle, C.c_void_p(xptr), mb.at() if mb else None, ne0, C.c_void_p(yptr), ne0, rows, scale), "soft_max")
+    stream.sync()
+    return U.read_guarded(capi, stream, yb, x.size).reshape(x.shape).copy()
+
+
+def test_soft_max(sm100, stream, seeded):
+    x, mk = np.ascontiguousarray(seeded["softmax_x"]), np.ascontiguousarray(seeded["softmax_mask"])
+    assert sgref.nmse(run_softmax(sm100, stream, x, mk, 0.125), seeded["softmax_masked"]) <= TOL
+    assert sgref.nmse(run_softmax(sm100, stream, x, None, 0.125), seeded["softmax_plain"]) <= TOL
+    assert sgref.nmse(run_softmax(sm100, stream, x, mk, 0.125, in_place=True), seeded["softmax_masked"]) <= TOL
+    big = U.seeded_acts(1, 32, 1152) * 6
+    assert sgref.nmse(run_softmax(sm100, stream, big, None, 0.088), sgref.soft_max(big, None, 0.088)) <= TOL
+
+
+def test_swiglu_add(sm100, stream, seeded):
+    lib = sm100.lib()
+    for x, g, want in ((seeded["glu_x"], seeded["glu_g"], seeded["swiglu"]),):
+        xb, gb = U.to_device(sm100, stream, x), U.to_device(sm100, stream, g)
+        yb, yptr = U.guarded_output(sm100, stream, x.size)
+        sm100.check(lib.sm100_swiglu(stream.handle, xb.at(), gb.at(), C.c_void_p(yptr), x.size), "swiglu")
+        stream.sync()
+        assert sgref.nmse(U.read_guarded(sm100, stream, yb, x.size), want) <= TOL
+    a, b = U.seeded_acts(1, 1, 12288)[0] * 4, U.seeded_acts(2, 1, 12288)[0]
+    ab, bb = U.to_device(sm100, stream, a), U.to_device(sm100, stream, b)
+    yb, yptr = U.guarded_output(sm100, stream, a.size)
+    sm100.check(lib.sm100_swiglu(stream.handle, ab.at(), bb.at(), C.c_void_p(yptr), a.size), "swiglu")
+    stream.sync()
+    assert sgref.nmse(U.read_guarded(sm100, stream, yb, a.size), sgref.swiglu(a, b)) <= TOL
+    sm100.check(lib.sm100_add(stream.handle, ab.at(), bb.at(), C.c_void_p(yptr), a.size), "add")
+    stream.sync()
+    assert np.array_equal(U.read_guarded(sm100, stream, yb, a.size), sgref.add(a, b))
+
+
+def test_set_rows_and_argmax(sm100, stream):
+    lib = sm100.lib()
+    ne0, heads, n_ctx = 128, 8, 64
+    cache = np.zeros((heads, n_ctx, ne0), np.float32)
+    src = U.seeded_acts(3, heads, ne0).reshape(heads, 1, ne0)
+    cb, sb = U.to_device(sm100, stream, cache), U.to_device(sm100, stream, src)
+    ib = U.to_device(sm100, stream, np.array([37], np.int32))
+    sm100.check(lib.sm100_set_rows(stream.handle, sb.at(), ib.at(), cb.at(), ne0, 1, heads, n_ctx), "set_rows")
+    stream.sync()
+    got = cb.download(stream, np.float32, cache.size).reshape(cache.shape)
+    want = cache.copy()
+    want[:, 37, :] = src[:, 0, :]
+    assert np.array_equal(got, want)
+
+    for n in (5, 1000, 151936):
+        x = U.seeded_acts(n, 1, n)[0]
+        x[n // 2] = x[n - 1] = x.max() + 1.0  # a tie: the lower index must win
+        xb = U.to_device(sm100, stream, x)
+        ob = U.to_device(sm100, stream, np.array([-1], np.int32))
+        sm100.check(lib.sm100_argmax(stream.handle, xb.at(), n, ob.at()), "argmax")
+        stream.sync()
+        assert int(ob.download(stream, np.int32, 1)[0]) == sgref.argmax(x) == n // 2
+
+
+def run_attention(capi, stream, q, k, v, causal, offset, scale, positions=None, mask=None, mask_heads=1):
+    hq, nq, d = q.shape
+    hkv, nk, _ = k.shape
+    dv = v.shape[2]
+    qb, kb, vb = (U.to_device(capi, stream, a) for a in (q, k, v))
+    ob, optr = U.guarded_output(capi, stream, hq * nq * dv)
+    pb = U.to_device(capi, stream, np.asarray(positions, np.int32)) if positions is not None else None
+    mb = U.to_device(capi, stream, mask) if mask is not None else None
+    capi.check(capi.lib().sm100_attention(stream.handle, qb.at(), kb.at(), vb.at(), mb.at() if mb else None, mask_heads, C.c_void_p(optr), d, dv, nq, nk,
+                                          hq, hkv, int(causal), offset, pb.at() if pb else None, scale), "attention")
+    stream.sync()
+    return U.read_guarded(capi, stream, ob, hq * nq * dv).reshape(hq, nq, dv).copy()
+
+
+def test_attention_golden(sm100, stream, seeded):
+    q, k, v = seeded["att_q"], seeded["att_k"], seeded["att_v"]
+    s = float(1.0 / np.sqrt(32.0))
+    assert sgref.nmse(run_attention(sm100, stream, q, k, v, True, 29, s), seeded["att_causal_off29"]) <= TOL
+    assert sgref.nmse(run_attention(sm100, stream, q, k, v, False, 0, s), seeded["att_full"]) <= TOL
+    assert sgref.nmse(run_attention(sm100, stream, seeded["att_q3"], k, v, True, 2, 0.2), seeded["att_causal_q3_off2"]) <= TOL
+    # offset taken from a device-side position (graph replay reads it there)
+    assert sgref.nmse(run_attention(sm100, stream, q, k, v, True, 0, s, positions=[29]), seeded["att_causal_off29"]) <= TOL
+
+
+def test_attention_decode_shape(sm100, stream):
+    """Qwen3-8B-shaped decode attention: 32 query heads on 8 KV heads, head_dim 128, f32 cache of 1152
+    positions zero beyond the current one, causal offset 1024 + t."""
+    hq, hkv, d, n_ctx = 32, 8, 128, 1152
+    rng = np.random.default_rng(8)
+    for t in (0, 57, 127):
+        n_valid = 1024 + t + 1
+        k = np.zeros((hkv, n_ctx, d), np.float32)
+        v = np.zeros((hkv, n_ctx, d), np.float32)
+        k[:, :n_valid] = rng.standard_normal((hkv, n_valid, d))
+        v[:, :n_valid] = rng.standard_normal((hkv, n_valid, d))
+        q = rng.standard_normal((hq, 1, d)).astype(np.float32)
+        want = sgref.attention(q, k, v, True, 1024 + t, 1.0 / np.sqrt(d))
+        got = run_attention(sm100, stream, q, k, v, True, 1024 + t, float(1.0 / np.sqrt(d)))
+        assert sgref.nmse(got, want) <= TOL
+        assert np.max(np.abs(got - want)) <= 3e-4  # the reference's own absolute bound (tests/attention/attention_tests.cpp:40)
+
+
+def test_attention_masks(sm100, stream):
+    hq, hkv, d, nk, nq = 4, 2, 32, 50, 2
+    rng = np.random.default_rng(9)
+    q = rng.standard_normal((hq, nq, d)).astype(np.float32)
+    k = rng.standard_normal((hkv, nk, d)).astype(np.float32)
+    v = rng.standard_normal((hkv, nk, d)).astype(np.float32)
+    # an additive mask that hides every key of query 1: the output row must be zero (attention.cpp:497-516)
+    mask = np.zeros((1, nq, nk), np.float32)
+    mask[0, 0, 10:] = -np.inf
+    mask[0, 1, :] = -np.inf
+    got = run_attention(sm100, stream, q, k, v, False, 0, 0.3, mask=mask, mask_heads=1)
+    want0 = sgref.attention(q[:, :1], k[:, :10], v[:, :10], False, 0, 0.3)
+    assert sgref.nmse(got[:, :1], want0) <= TOL
+    assert np.all(got[:, 1] == 0.0)
+
+
+def test_attention_argument_errors(sm100, stream):
+    b = sm100.Buffer(1 << 16)
+    lib = sm100.lib()
+    st = lib.sm100_attention(stream.handle, b.at(), b.at(), b.at(), None, 1, b.at(), 32, 32, 1, 8, 5, 2, 1, 0, None, 1.0)
+    assert st == 2  # Hq not divisible by Hkv
+    st = lib.sm100_attention(stream.handle, None, b.at(), b.at(), None, 1, b.at(), 32, 32, 1, 8, 4, 2, 1, 0, None, 1.0)
+    assert st == 2
+    b.free()
