@@ -31,6 +31,14 @@ typedef void * sm100_stream_t; /* a cudaStream_t */
 typedef void * sm100_event_t;  /* a cudaEvent_t */
 typedef void * sm100_graph_t;  /* a cudaGraphExec_t */
 
+/* A tensor as the backend vtable sees it (scrapgpu_tensor_desc, include/scrapgpu/tensor.h:29-37, with the
+ * buffer already resolved to a device address): extents ne[4] (ne[0] contiguous-most) and byte strides nb[4]. */
+typedef struct sm100_view {
+    void * data;
+    int64_t ne[4];
+    int64_t nb[4];
+} sm100_view;
+
 /* ---- errors (src/core/status.cpp:6-37: thread-local last error) ---- */
 SM100_API const char * sm100_last_error(void);
 
@@ -84,6 +92,11 @@ SM100_API int sm100_unpack(int dtype, int64_t k, int64_t n, const void * packed,
 /* device-side repack of a natural tensor already in HBM (src = natural, dst = packed, distinct buffers) */
 SM100_API int sm100_pack_device(sm100_stream_t s, int dtype, int64_t k, int64_t n, const void * natural, void * packed);
 SM100_API int sm100_unpack_device(sm100_stream_t s, int dtype, int64_t k, int64_t n, const void * packed, void * natural);
+/* partial transfers on block boundaries (the chunked R32 transfer of src/backends/opencl11/r32.cpp:56-70):
+ * `natural_chunk` holds blocks [first_block, first_block + block_count) of the tensor; to_packed != 0 scatters
+ * them into the packed tensor at `packed`, 0 gathers them back */
+SM100_API int sm100_pack_device_range(sm100_stream_t s, int dtype, int64_t k, int64_t n, int64_t first_block, int64_t block_count,
+                                      void * natural_chunk, void * packed, int to_packed);
 
 /* ---- the hot path: quantized MUL_MAT (src/core/ref/ops.cpp:891-984 exec_mul_mat; OpenCL kernels
  *      mul_mv_r.cl:240-323, mul_mv_k.cl:396-486, mul_mm.cl:271).  w, x, y are device pointers;
@@ -99,9 +112,11 @@ SM100_API int sm100_mul_mat_multi(sm100_stream_t s, int count, const int * dtype
                                   float * const * ys);
 
 /* ---- bit-exact dequantization: GET_ROWS over a quantized / F32 / F16 table
- *      (src/core/ref/ops.cpp:690-722, quant.cpp:30-108); ids are I32 on the device ---- */
-SM100_API int sm100_get_rows(sm100_stream_t s, int dtype, int layout, const void * table, int64_t k,
-                             int64_t table_rows, const int32_t * ids, int64_t n_ids, float * dst, int64_t ld_dst);
+ *      (src/core/ref/ops.cpp:690-722, quant.cpp:30-108); ids are I32 on the device; table_row_stride is the
+ *      byte stride of natural-layout rows (0 = dense) ---- */
+SM100_API int sm100_get_rows(sm100_stream_t s, int dtype, int layout, const void * table, int64_t table_row_stride,
+                             int64_t k, int64_t table_rows, const int32_t * ids, int64_t n_ids, float * dst,
+                             int64_t ld_dst);
 
 /* ---- the ops around the matvec in a decode step ---- */
 /* RMS_NORM / RMS_NORM_MUL / ADD_RMS_NORM_MUL (ops.cpp:440-519): add, w, sum_out may be NULL */
@@ -139,6 +154,27 @@ SM100_API int sm100_argmax(sm100_stream_t s, const float * x, int64_t n, int32_t
 SM100_API int sm100_attention(sm100_stream_t s, const float * q, const float * k, const float * v, const float * mask,
                               int64_t mask_heads, float * out, int64_t d, int64_t dv, int64_t nq, int64_t nk, int64_t hq,
                               int64_t hkv, int causal, int64_t offset, const int32_t * positions, float scale);
+
+
+/* ---- the same ops over strided views (arbitrary nb[1..3], broadcast operands, transposed CPY sources): what
+ *      op_execute needs to honour every descriptor the reference's CPU backend accepts
+ *      (src/backends/cpu/api.cpp:394-830) ---- */
+SM100_API int sm100_binary(sm100_stream_t s, int op /* 0 ADD 1 SUB 2 MUL 3 DIV */, const sm100_view * a, const sm100_view * b,
+                           const sm100_view * y);                                          /* ops.cpp:280-312 */
+SM100_API int sm100_glu(sm100_stream_t s, int kind /* 0 SwiGLU 1 ReGLU */, const sm100_view * x, const sm100_view * g /* NULL: fused halves */,
+                        int swapped, const sm100_view * y);                                 /* ops.cpp:383-425 */
+SM100_API int sm100_rms_norm_view(sm100_stream_t s, const sm100_view * x, const sm100_view * add, const float * w,
+                                  const sm100_view * sum_out, const sm100_view * y, float eps); /* ops.cpp:440-519 */
+SM100_API int sm100_rope_view(sm100_stream_t s, const sm100_view * x, const int32_t * positions, const float * table,
+                              int32_t table_first_position, int32_t table_positions, const float * freq_factors,
+                              const sm100_view * y, int n_dims, int neox, float freq_base, float freq_scale,
+                              float attn_factor);                                           /* ops.cpp:530-634 */
+SM100_API int sm100_soft_max_view(sm100_stream_t s, const sm100_view * x, const sm100_view * mask, int mask_is_f16,
+                                  const sm100_view * y, float scale);                       /* ops.cpp:636-684 */
+SM100_API int sm100_cpy(sm100_stream_t s, const sm100_view * src, int src_dtype, const sm100_view * dst, int dst_dtype); /* ops.cpp:764-800 */
+SM100_API int sm100_set_rows_view(sm100_stream_t s, const sm100_view * src, int src_dtype, const sm100_view * ids, int ids_are_i64,
+                                  const sm100_view * dst, int dst_dtype);                   /* ops.cpp:724-762 */
+SM100_API int sm100_top1_view(sm100_stream_t s, const sm100_view * x, const sm100_view * out);   /* ops.cpp:1189-1228, k = 1 */
 
 #ifdef __cplusplus
 }

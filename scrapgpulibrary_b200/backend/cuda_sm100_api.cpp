@@ -1,0 +1,1343 @@
+// The `cuda_sm100` backend of ScrapGpuLibrary: host layer between the library's backend vtable
+// (include/scrapgpu/backend.h:29-57 of the reference) and the CUDA compute library libscrapgpu_sm100.so
+// (include/scrapgpu_sm100.h).  C++17, no CUDA headers: every device action goes through that C ABI.
+//
+// Contract followed (where the reference states it):
+//   - every object handed out starts with a scrapgpu_object_header pointing at this backend's static vtable
+//     (backend.h:22-27); foreign or NULL objects are answered with INVALID_ARGUMENT, never dereferenced further
+//     (tests/cpu/cpu_tests.cpp:279-338)
+//   - ops are enqueued on the stream's CUDA stream; results are visible after stream_sync or a blocking read
+//     (include/scrapgpu/op.h:190-194); failures of enqueued work surface at the next stream_sync
+//   - tensor_upload / tensor_download move natural bytes; a tensor whose layout tag is SCRAPGPU_LAYOUT_R32 is
+//     packed / unpacked on the way (include/scrapgpu/tensor.h:45-53); here the tag selects the B200 plane layout
+//   - UNSUPPORTED always carries a reason (reason out-parameter and last error)
+//   - no exception crosses the C ABI
+//   - plans deep-copy their descriptors and pin the buffers they reference: buffer_free is refused while a plan
+//     lives (docs/API_CONTRACT.md:43)
+// There is no CPU fallback: an op this backend does not implement is reported UNSUPPORTED.
+#include "scrapgpu/cuda_sm100.h"
+
+#include "scrapgpu_sm100.h"
+
+#include <algorithm>
+#include <cmath>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <limits>
+#include <map>
+#include <memory>
+#include <mutex>
+#include <new>
+#include <string>
+#include <tuple>
+#include <unordered_map>
+#include <vector>
+
+// Symbols of the ScrapGpuLibrary core.  They are weak so that the plugin also loads stand-alone (its vtable can be
+// driven directly); inside a ScrapGpuLibrary process they resolve to the core's definitions.
+#pragma weak scrapgpu_register_backend
+#pragma weak scrapgpu_op_desc_validate
+#pragma weak scrapgpu_set_last_error
+#pragma weak scrapgpu_last_error
+#pragma weak scrapgpu_get_device_count
+#pragma weak scrapgpu_get_device
+
+namespace {
+
+constexpr int kQ4_0 = SCRAPGPU_DTYPE_Q4_0, kQ8_0 = SCRAPGPU_DTYPE_Q8_0, kQ4_K = SCRAPGPU_DTYPE_Q4_K, kQ6_K = SCRAPGPU_DTYPE_Q6_K;
+
+// ---------------------------------------------------------------------------------------------------------
+// objects
+// ---------------------------------------------------------------------------------------------------------
+
+struct Device {
+    scrapgpu_object_header hdr;  // first member
+    int ordinal = 0;
+    std::string name, driver;
+    uint64_t total_memory = 0, shared_per_block = 0;
+    uint32_t sms = 0, cc_major = 0, cc_minor = 0;
+    // (cos, sin) tables of ROPE, keyed by the parameters that determine them; built on the host with the
+    // reference's recipe so that the rotation is bit-identical to the CPU backend
+    std::mutex rope_mutex;
+    std::map<std::tuple<int, uint32_t, uint32_t, uint32_t>, std::pair<void *, int32_t>> rope_tables;
+};
+
+struct Buffer {
+    scrapgpu_object_header hdr;
+    Device * dev = nullptr;
+    void * ptr = nullptr;
+    size_t size = 0;
+};
+
+struct Stream {
+    scrapgpu_object_header hdr;
+    Device * dev = nullptr;
+    sm100_stream_t cuda = nullptr;
+    scrapgpu_status sticky = SCRAPGPU_STATUS_OK;  // failure of enqueued work, reported at the next sync
+    std::string sticky_message;
+};
+
+struct PlanNode {
+    scrapgpu_op_desc desc;
+    std::vector<scrapgpu_tensor_desc> inputs, outputs;
+    std::vector<uint8_t> params;
+};
+
+struct Plan {
+    scrapgpu_object_header hdr;
+    Device * dev = nullptr;
+    std::vector<PlanNode> nodes;
+    std::vector<Buffer *> pinned;
+};
+
+extern const scrapgpu_backend_vtable g_vtable;
+
+std::mutex g_registry_mutex;
+std::vector<std::unique_ptr<Device>> g_devices;
+bool g_devices_probed = false;
+
+std::mutex g_pin_mutex;
+std::unordered_map<Buffer *, size_t> g_pins;  // live plans referencing each buffer
+
+thread_local std::string t_local_error;  // used when the core is not loaded
+
+// ---------------------------------------------------------------------------------------------------------
+// errors
+// ---------------------------------------------------------------------------------------------------------
+
+void set_error(const char * message) {
+    if (scrapgpu_set_last_error != nullptr) scrapgpu_set_last_error(message);
+    else t_local_error = message;
+}
+
+scrapgpu_status invalid(const char * message) {
+    set_error(message);
+    return SCRAPGPU_STATUS_INVALID_ARGUMENT;
+}
+
+scrapgpu_status unsupported(const char * message, const char ** reason = nullptr) {
+    if (reason != nullptr) *reason = message;
+    set_error(message);
+    return SCRAPGPU_STATUS_UNSUPPORTED;
+}
+
+scrapgpu_status bad(const char * message, const char ** reason) {
+    if (reason != nullptr) *reason = message;
+    set_error(message);
+    return SCRAPGPU_STATUS_INVALID_ARGUMENT;
+}
+
+// status of a libscrapgpu_sm100 call -> status of the vtable call (the codes are shared; the message is copied)
+scrapgpu_status from_sm100(int st) {
+    if (st == 0) return SCRAPGPU_STATUS_OK;
+    const char * m = sm100_last_error();
+    set_error(m != nullptr && *m != '\0' ? m : "cuda_sm100: device call failed");
+    return st >= 1 && st <= 5 ? static_cast<scrapgpu_status>(st) : SCRAPGPU_STATUS_BACKEND_ERROR;
+}
+
+template <typename F>
+scrapgpu_status guard(F && fn) noexcept {
+    try {
+        return fn();
+    } catch (const std::bad_alloc &) {
+        try { set_error("out of host memory"); } catch (...) {}
+        return SCRAPGPU_STATUS_OUT_OF_MEMORY;
+    } catch (...) {
+        try { set_error("the cuda_sm100 backend threw an exception"); } catch (...) {}
+        return SCRAPGPU_STATUS_BACKEND_ERROR;
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// object checks
+// ---------------------------------------------------------------------------------------------------------
+
+template <typename T, typename H>
+T * own(H * handle) {
+    auto * o = reinterpret_cast<T *>(handle);
+    return o != nullptr && o->hdr.backend == &g_vtable ? o : nullptr;
+}
+
+Device * as_device(scrapgpu_device_t * d) {
+    Device * dev = own<Device>(d);
+    if (dev == nullptr) return nullptr;
+    for (const auto & known : g_devices) if (known.get() == dev) return dev;
+    return nullptr;
+}
+Buffer * as_buffer(scrapgpu_buffer_t * b) { return own<Buffer>(b); }
+Stream * as_stream(scrapgpu_stream_t * s) { return own<Stream>(s); }
+Plan * as_plan(scrapgpu_plan_t * p) { return own<Plan>(p); }
+
+// ---------------------------------------------------------------------------------------------------------
+// descriptor math (the public definitions of include/scrapgpu/tensor.h; the core's sgt:: helpers are internal)
+// ---------------------------------------------------------------------------------------------------------
+
+size_t type_size(int dtype) {
+    switch (dtype) {
+        case SCRAPGPU_DTYPE_F32: case SCRAPGPU_DTYPE_I32: return 4;
+        case SCRAPGPU_DTYPE_F16: case SCRAPGPU_DTYPE_I16: case SCRAPGPU_DTYPE_BF16: return 2;
+        case SCRAPGPU_DTYPE_I64: return 8;
+        case kQ4_0: return 18;
+        case kQ8_0: return 34;
+        case kQ4_K: return 144;
+        case kQ6_K: return 210;
+        default: return 0;
+    }
+}
+
+size_t block_size(int dtype) {
+    switch (dtype) {
+        case kQ4_0: case kQ8_0: return 32;
+        case kQ4_K: case kQ6_K: return 256;
+        default: return type_size(dtype) != 0 ? 1 : 0;
+    }
+}
+
+bool is_quant(int dtype) { return block_size(dtype) > 1; }
+
+scrapgpu_tensor_desc load_desc(const scrapgpu_tensor_desc & in) {
+    scrapgpu_tensor_desc out = {};
+    if (in.struct_size >= sizeof(size_t)) {
+        std::memcpy(&out, &in, std::min(in.struct_size, sizeof(out)));
+        out.struct_size = sizeof(out);
+    }
+    return out;
+}
+
+int64_t ne(const scrapgpu_tensor_desc & t, int i) { return t.ne[i] > 0 ? t.ne[i] : 1; }
+
+uint64_t sat_mul(uint64_t a, uint64_t b) { return a != 0 && b > UINT64_MAX / a ? UINT64_MAX : a * b; }
+uint64_t sat_add(uint64_t a, uint64_t b) { return b > UINT64_MAX - a ? UINT64_MAX : a + b; }
+
+// bytes from the tensor's first byte to one past its last (0 for an empty or unknown tensor)
+uint64_t span_bytes(const scrapgpu_tensor_desc & t) {
+    const size_t bs = block_size(t.dtype), ts = type_size(t.dtype);
+    if (bs == 0 || ts == 0) return 0;
+    for (int i = 0; i < 4; ++i) if (t.ne[i] <= 0) return 0;
+    uint64_t n = bs == 1 ? ts : sat_mul((uint64_t) t.ne[0], t.nb[0]) / bs;
+    for (int i = bs == 1 ? 0 : 1; i < 4; ++i) n = sat_add(n, sat_mul((uint64_t) (t.ne[i] - 1), t.nb[i]));
+    return n;
+}
+
+bool span_ok(const scrapgpu_tensor_desc & t) {
+    const uint64_t half = UINT64_MAX / 2;
+    if (t.offset > half) return false;
+    uint64_t span = t.offset;
+    for (int i = 0; i < 4; ++i) {
+        const uint64_t count = (uint64_t) (ne(t, i) - 1);
+        if (t.nb[i] != 0 && count > (half - span) / t.nb[i]) return false;
+        span += count * t.nb[i];
+        if (span > half) return false;
+    }
+    return true;
+}
+
+// ggml contiguity: dims of size 1 (and nb[0] of a single-block row) are unconstrained
+bool contiguous(const scrapgpu_tensor_desc & t) {
+    const size_t bs = block_size(t.dtype), ts = type_size(t.dtype);
+    if (bs == 0 || ts == 0) return false;
+    uint64_t next = ts;
+    if (t.ne[0] != (int64_t) bs && t.nb[0] != next) return false;
+    next *= (uint64_t) (t.ne[0] / (int64_t) bs);
+    for (int i = 1; i < 4; ++i) {
+        if (t.ne[i] != 1 && t.nb[i] != next) return false;
+        next = sat_mul(next, (uint64_t) t.ne[i]);
+    }
+    return next != UINT64_MAX;
+}
+
+bool same_shape(const scrapgpu_tensor_desc & a, const scrapgpu_tensor_desc & b) {
+    for (int i = 0; i < 4; ++i) if (ne(a, i) != ne(b, i)) return false;
+    return true;
+}
+
+bool elements(const scrapgpu_tensor_desc & t, int64_t & out) {
+    int64_t n = 1;
+    for (int i = 0; i < 4; ++i) {
+        const int64_t d = ne(t, i);
+        if (n > std::numeric_limits<int64_t>::max() / d) return false;
+        n *= d;
+    }
+    out = n;
+    return true;
+}
+
+template <typename T>
+T load_params(const scrapgpu_op_desc * desc) {
+    T p = {};
+    if (desc->params != nullptr) std::memcpy(&p, desc->params, std::min(desc->params_size, sizeof(T)));
+    return p;
+}
+
+template <typename E>
+uint32_t enum_bits(const E & e) {
+    uint32_t v = 0;
+    std::memcpy(&v, &e, std::min(sizeof(e), sizeof(v)));
+    return v;
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// op_supported: descriptor-only checks; the shape rules are the reference's (src/backends/cpu/api.cpp:394-830,
+// src/core/ref/ops.cpp), the dtype / layout coverage is this backend's
+// ---------------------------------------------------------------------------------------------------------
+
+bool f32(const scrapgpu_tensor_desc & t) { return t.dtype == SCRAPGPU_DTYPE_F32; }
+
+scrapgpu_status check_tensor_meta(const scrapgpu_tensor_desc & raw, bool weight_slot, const char ** reason) {
+    const scrapgpu_tensor_desc t = load_desc(raw);
+    if (type_size(t.dtype) == 0) return unsupported("unknown tensor dtype", reason);
+    for (int i = 0; i < 4; ++i) if (t.ne[i] <= 0) return bad("non-positive tensor dim", reason);
+    if (!span_ok(t)) return unsupported("tensor strides or offset overflow the address space", reason);
+    if (t.layout != SCRAPGPU_LAYOUT_NATURAL) {
+        if (t.layout != SCRAPGPU_LAYOUT_R32) return unsupported("unknown tensor layout", reason);
+        if (!weight_slot || !is_quant(t.dtype)) return unsupported("only quantized weight tensors can use the backend-packed layout", reason);
+        if (!contiguous(t) || ne(t, 2) * ne(t, 3) != 1) return unsupported("a backend-packed tensor must be a whole contiguous 2-D tensor (no views)", reason);
+        if (t.ne[0] % (int64_t) block_size(t.dtype) != 0) return unsupported("quantized row length must be a multiple of the block size", reason);
+        if (t.offset % 32 != 0) return unsupported("a backend-packed tensor must start on a 32-byte boundary of its buffer", reason);
+    }
+    return SCRAPGPU_STATUS_OK;
+}
+
+scrapgpu_status require_rows(const scrapgpu_tensor_desc & t, const char * what, const char ** reason) {
+    if (t.nb[0] != type_size(t.dtype)) return unsupported(what, reason);
+    if (is_quant(t.dtype) && t.ne[0] % (int64_t) block_size(t.dtype) != 0) return unsupported("quantized row length must be a multiple of the block size", reason);
+    return SCRAPGPU_STATUS_OK;
+}
+
+bool mm_weight(int dtype) {
+    return dtype == SCRAPGPU_DTYPE_F32 || dtype == SCRAPGPU_DTYPE_F16 || is_quant(dtype);
+}
+
+scrapgpu_status mul_mat_shapes(const scrapgpu_tensor_desc & w, const scrapgpu_tensor_desc & x, const scrapgpu_tensor_desc & d, int allow_broadcast,
+                               const char ** reason) {
+    if (!f32(x) || !f32(d)) return unsupported("MUL_MAT expects an F32 src1 and destination", reason);
+    if (!mm_weight(w.dtype)) return unsupported("MUL_MAT weights must be F32, F16, Q4_0, Q8_0, Q4_K or Q6_K on cuda_sm100", reason);
+    scrapgpu_status st = require_rows(w, "MUL_MAT needs contiguous rows of src0 (nb0 == element size)", reason);
+    if (st != SCRAPGPU_STATUS_OK) return st;
+    if (x.nb[0] != 4 || d.nb[0] != 4) return unsupported("MUL_MAT needs contiguous rows of src1 and dst (nb0 == element size)", reason);
+    if (ne(w, 0) != ne(x, 0)) return bad("MUL_MAT: the inner dimensions of src0 and src1 differ", reason);
+    if (ne(x, 2) % ne(w, 2) != 0 || ne(x, 3) % ne(w, 3) != 0) return bad("MUL_MAT: src1 dims 2 and 3 must be multiples of the src0 dims", reason);
+    if (allow_broadcast == 0 && (ne(x, 2) != ne(w, 2) || ne(x, 3) != ne(w, 3))) return unsupported("MUL_MAT: broadcasting over dims 2/3 is not allowed", reason);
+    if (ne(d, 0) != ne(w, 1) || ne(d, 1) != ne(x, 1) || ne(d, 2) != ne(x, 2) || ne(d, 3) != ne(x, 3)) return bad("MUL_MAT: dst must be [ne01, ne11, ne12, ne13]", reason);
+    if (is_quant(w.dtype) && ((x.offset % 16) != 0 || (x.nb[1] % 16) != 0 || (x.nb[2] % 16) != 0 || (x.nb[3] % 16) != 0))
+        return unsupported("MUL_MAT over quantized weights needs 16-byte aligned activation columns", reason);
+    if (w.layout == SCRAPGPU_LAYOUT_NATURAL && is_quant(w.dtype) && ((w.offset % 2) != 0 || (w.nb[1] % 2) != 0))
+        return unsupported("natural quantized weights must be 2-byte aligned", reason);
+    return SCRAPGPU_STATUS_OK;
+}
+
+scrapgpu_status supports(const scrapgpu_op_desc * desc, const char ** reason) {
+    const char * local = nullptr;
+    if (reason == nullptr) reason = &local;
+    *reason = nullptr;
+    if (desc == nullptr || desc->struct_size < sizeof(scrapgpu_op_desc)) return bad("op descriptor is too small", reason);
+    if (desc->input_count > 32 || desc->output_count > 32 || (desc->input_count != 0 && desc->inputs == nullptr) ||
+        (desc->output_count != 0 && desc->outputs == nullptr))
+        return bad("invalid tensor descriptor arrays", reason);
+    for (size_t i = 0; i < desc->input_count; ++i)
+        if (desc->inputs[i].struct_size < sizeof(scrapgpu_tensor_desc)) return bad("input tensor descriptor is too small", reason);
+    for (size_t i = 0; i < desc->output_count; ++i)
+        if (desc->outputs[i].struct_size < sizeof(scrapgpu_tensor_desc)) return bad("output tensor descriptor is too small", reason);
+    if (scrapgpu_op_desc_validate != nullptr) {
+        const scrapgpu_status valid = scrapgpu_op_desc_validate(desc);
+        if (valid != SCRAPGPU_STATUS_OK) {
+            *reason = scrapgpu_last_error != nullptr ? scrapgpu_last_error() : "op descriptor failed validation";
+            return valid;
+        }
+    }
+    switch (desc->op) {
+        case SCRAPGPU_OP_NONE: case SCRAPGPU_OP_RESHAPE: case SCRAPGPU_OP_VIEW: case SCRAPGPU_OP_PERMUTE: case SCRAPGPU_OP_TRANSPOSE:
+            return SCRAPGPU_STATUS_OK;
+        default: break;
+    }
+    if (desc->input_count < 1 || desc->output_count < 1) return bad("op needs at least one input and one output", reason);
+    const bool multi = desc->op == SCRAPGPU_OP_MUL_MAT_MULTI;
+    for (size_t i = 0; i < desc->input_count; ++i) {
+        const bool weight_slot = (desc->op == SCRAPGPU_OP_MUL_MAT && i == 0) || (desc->op == SCRAPGPU_OP_GET_ROWS && i == 0) || (multi && i + 1 < desc->input_count);
+        const scrapgpu_status st = check_tensor_meta(desc->inputs[i], weight_slot, reason);
+        if (st != SCRAPGPU_STATUS_OK) return st;
+    }
+    for (size_t i = 0; i < desc->output_count; ++i) {
+        const scrapgpu_status st = check_tensor_meta(desc->outputs[i], false, reason);
+        if (st != SCRAPGPU_STATUS_OK) return st;
+    }
+
+    const auto s0 = load_desc(desc->inputs[0]);
+    const auto s1 = desc->input_count > 1 ? load_desc(desc->inputs[1]) : scrapgpu_tensor_desc{};
+    const auto s2 = desc->input_count > 2 ? load_desc(desc->inputs[2]) : scrapgpu_tensor_desc{};
+    const auto dd = load_desc(desc->outputs[0]);
+
+    switch (desc->op) {
+        case SCRAPGPU_OP_ADD: case SCRAPGPU_OP_SUB: case SCRAPGPU_OP_MUL: case SCRAPGPU_OP_DIV:
+            if (desc->input_count != 2) return bad("binary ops take two inputs", reason);
+            if (!f32(s0) || !f32(s1) || !f32(dd)) return unsupported("binary ops need F32 tensors", reason);
+            if (!same_shape(s0, dd)) return bad("binary op: src0 must have the shape of dst", reason);
+            for (int i = 0; i < 4; ++i) if (ne(s1, i) > ne(dd, i)) return bad("binary op: src1 cannot be larger than dst", reason);
+            return SCRAPGPU_STATUS_OK;
+
+        case SCRAPGPU_OP_GLU: {
+            const auto p = load_params<scrapgpu_glu_params>(desc);
+            const bool split = desc->input_count == 2;
+            if (split != (p.split_inputs != 0)) return bad("GLU: split_inputs does not match the number of inputs", reason);
+            if (!f32(s0) || !f32(dd) || (split && !f32(s1))) return unsupported("GLU expects F32 tensors", reason);
+            if (enum_bits(p.kind) > (uint32_t) SCRAPGPU_GLU_REGLU) return unsupported("unknown GLU kind", reason);
+            if (split) return same_shape(s0, dd) && same_shape(s1, dd) ? SCRAPGPU_STATUS_OK : bad("GLU with split inputs needs src0, src1 and dst of the same shape", reason);
+            for (int i = 1; i < 4; ++i) if (ne(s0, i) != ne(dd, i)) return bad("GLU: src0 and dst differ outside of dim 0", reason);
+            return ne(s0, 0) == 2 * ne(dd, 0) ? SCRAPGPU_STATUS_OK : bad("GLU: src0 dim 0 must be twice the dst dim 0", reason);
+        }
+
+        case SCRAPGPU_OP_RMS_NORM:
+            if (!f32(s0) || !f32(dd)) return unsupported("RMS_NORM expects F32 tensors", reason);
+            return same_shape(s0, dd) ? SCRAPGPU_STATUS_OK : bad("RMS_NORM: src0 must have the shape of dst", reason);
+
+        case SCRAPGPU_OP_RMS_NORM_MUL:
+            if (desc->input_count != 2) return bad("RMS_NORM_MUL takes 2 inputs and 1 output", reason);
+            if (!f32(s0) || !f32(s1) || !f32(dd)) return unsupported("RMS_NORM_MUL expects F32 tensors", reason);
+            if (s1.nb[0] != 4) return unsupported("RMS_NORM_MUL needs a contiguous weight row", reason);
+            return same_shape(s0, dd) && ne(s1, 0) == ne(s0, 0) ? SCRAPGPU_STATUS_OK : bad("RMS_NORM_MUL: dst must match src0 and the weight must be a row vector", reason);
+
+        case SCRAPGPU_OP_ADD_RMS_NORM_MUL: {
+            if (desc->input_count != 3 || desc->output_count != 2) return bad("ADD_RMS_NORM_MUL takes 3 inputs and 2 outputs", reason);
+            const auto o1 = load_desc(desc->outputs[1]);
+            if (!f32(s0) || !f32(s1) || !f32(s2) || !f32(dd) || !f32(o1)) return unsupported("ADD_RMS_NORM_MUL expects F32 tensors", reason);
+            if (s2.nb[0] != 4) return unsupported("ADD_RMS_NORM_MUL needs a contiguous weight row", reason);
+            return same_shape(s0, s1) && same_shape(s0, dd) && same_shape(s0, o1) && ne(s2, 0) == ne(s0, 0)
+                       ? SCRAPGPU_STATUS_OK : bad("ADD_RMS_NORM_MUL: a, b, the outputs and the weight row must have matching shapes", reason);
+        }
+
+        case SCRAPGPU_OP_ROPE: {
+            const auto p = load_params<scrapgpu_rope_params>(desc);
+            if (enum_bits(p.mode) > (uint32_t) SCRAPGPU_ROPE_MODE_NEOX) return unsupported("unknown ROPE mode", reason);
+            if (desc->input_count < 2) return bad("ROPE needs the positions tensor as inputs[1]", reason);
+            if (!f32(s0) || !f32(dd)) return unsupported("ROPE is implemented for F32 tensors on cuda_sm100", reason);
+            if (s1.dtype != SCRAPGPU_DTYPE_I32) return unsupported("ROPE positions must be I32", reason);
+            if (p.n_offs != nullptr) return unsupported("ROPE n_offs is not supported", reason);
+            if (p.freq_factors != nullptr && desc->input_count != 3) return unsupported("ROPE params->freq_factors must be NULL or describe inputs[2]", reason);
+            if (p.ext_factor != 0.0f) return unsupported("ROPE with yarn extrapolation (ext_factor != 0) is not implemented on cuda_sm100", reason);
+            if (!same_shape(s0, dd)) return bad("ROPE: src0 must have the shape of dst", reason);
+            if (s0.nb[0] != 4 || dd.nb[0] != 4) return unsupported("ROPE needs contiguous rows (nb0 == element size)", reason);
+            if (p.n_dims <= 0 || p.n_dims % 2 != 0 || p.n_dims > s0.ne[0] || s0.ne[0] % 2 != 0) return bad("ROPE: n_dims must be a positive even number not above ne0 (ne0 even)", reason);
+            if (ne(s1, 0) < ne(dd, 2)) return bad("ROPE: not enough positions for the sequence dimension", reason);
+            if (s1.nb[0] != 4) return unsupported("ROPE positions must be contiguous", reason);
+            if (desc->input_count == 3 && (s2.dtype != SCRAPGPU_DTYPE_F32 || ne(s2, 0) < p.n_dims / 2 || s2.nb[0] != 4))
+                return bad("ROPE: freq factors must be contiguous F32 with at least n_dims/2 entries", reason);
+            return SCRAPGPU_STATUS_OK;
+        }
+
+        case SCRAPGPU_OP_SOFT_MAX: {
+            const auto p = load_params<scrapgpu_soft_max_params>(desc);
+            if (!f32(s0) || !f32(dd)) return unsupported("SOFT_MAX expects F32 tensors", reason);
+            if (!same_shape(s0, dd)) return bad("SOFT_MAX: src0 must have the shape of dst", reason);
+            if (p.mask != nullptr && desc->input_count != 2) return unsupported("SOFT_MAX params->mask must be NULL or describe inputs[1]", reason);
+            if (desc->input_count == 2 && ((!f32(s1) && s1.dtype != SCRAPGPU_DTYPE_F16) || ne(s1, 0) != ne(s0, 0) || ne(s1, 1) < ne(s0, 1)))
+                return bad("SOFT_MAX mask must be F32/F16, as long as a row and cover the rows of src0", reason);
+            return SCRAPGPU_STATUS_OK;
+        }
+
+        case SCRAPGPU_OP_GET_ROWS: {
+            if (desc->input_count != 2) return bad("GET_ROWS takes two inputs", reason);
+            if (s1.dtype != SCRAPGPU_DTYPE_I32 || !f32(dd)) return unsupported("GET_ROWS expects I32 indices and an F32 destination", reason);
+            if (s0.dtype != SCRAPGPU_DTYPE_F32 && s0.dtype != SCRAPGPU_DTYPE_F16 && !is_quant(s0.dtype)) return unsupported("GET_ROWS dtype is not implemented", reason);
+            const scrapgpu_status st = require_rows(s0, "GET_ROWS needs contiguous rows (nb0 == element size)", reason);
+            if (st != SCRAPGPU_STATUS_OK) return st;
+            if (s1.nb[0] != 4 || dd.nb[0] != 4) return unsupported("GET_ROWS needs contiguous indices and destination rows", reason);
+            return ne(s1, 3) == 1 && ne(s1, 1) <= ne(s0, 2) && ne(s1, 2) <= ne(s0, 3) && ne(dd, 0) == ne(s0, 0) && ne(dd, 1) == ne(s1, 0) &&
+                           ne(dd, 2) == ne(s1, 1) && ne(dd, 3) == ne(s1, 2)
+                       ? SCRAPGPU_STATUS_OK : bad("GET_ROWS: dst must be [ne00, ids] over the slices of src0", reason);
+        }
+
+        case SCRAPGPU_OP_SET_ROWS: {
+            if (desc->input_count != 2) return bad("SET_ROWS takes two inputs", reason);
+            const auto okdt = [](const scrapgpu_tensor_desc & t) { return t.dtype == SCRAPGPU_DTYPE_F32 || t.dtype == SCRAPGPU_DTYPE_F16; };
+            if (!okdt(s0) || !okdt(dd)) return unsupported("SET_ROWS expects F32/F16 values and destination", reason);
+            if (s1.dtype != SCRAPGPU_DTYPE_I32 && s1.dtype != SCRAPGPU_DTYPE_I64) return unsupported("SET_ROWS indices must be I32 or I64", reason);
+            const scrapgpu_status st = require_rows(s0, "SET_ROWS needs contiguous rows (nb0 == element size)", reason);
+            if (st != SCRAPGPU_STATUS_OK) return st;
+            return ne(s0, 0) == ne(dd, 0) && ne(s0, 2) == ne(dd, 2) && ne(s0, 3) == ne(dd, 3) && ne(dd, 1) >= 1 && ne(s1, 0) >= ne(s0, 1) &&
+                           ne(s0, 2) % ne(s1, 1) == 0 && ne(s0, 3) % ne(s1, 2) == 0
+                       ? SCRAPGPU_STATUS_OK : bad("SET_ROWS: dst must match src0 except along dim 1 and the index tensor must cover its rows", reason);
+        }
+
+        case SCRAPGPU_OP_CPY: case SCRAPGPU_OP_DUP: case SCRAPGPU_OP_CONT: {
+            const auto okdt = [](const scrapgpu_tensor_desc & t) { return t.dtype == SCRAPGPU_DTYPE_F32 || t.dtype == SCRAPGPU_DTYPE_F16 || t.dtype == SCRAPGPU_DTYPE_BF16; };
+            if (!okdt(s0) || !okdt(dd)) return unsupported("CPY/DUP/CONT support F32, F16 and BF16 only", reason);
+            int64_t ns = 0, nd = 0;
+            if (!elements(s0, ns) || !elements(dd, nd) || ns != nd) return bad("CPY/DUP/CONT: src0 and dst must have the same number of elements", reason);
+            return SCRAPGPU_STATUS_OK;
+        }
+
+        case SCRAPGPU_OP_MUL_MAT: {
+            if (desc->input_count != 2) return bad("MUL_MAT takes two inputs", reason);
+            const auto p = load_params<scrapgpu_mul_mat_params>(desc);
+            return mul_mat_shapes(s0, s1, dd, p.allow_broadcast, reason);
+        }
+
+        case SCRAPGPU_OP_MUL_MAT_MULTI: {
+            // inputs [w_0 .. w_{n-1}, x], outputs [d_0 .. d_{n-1}], one F32 activation column shared by all
+            const size_t n = desc->output_count;
+            if (n < 2 || n > 3 || desc->input_count != n + 1) return bad("MUL_MAT_MULTI takes n+1 inputs and n outputs (2 <= n <= 3)", reason);
+            const auto x = load_desc(desc->inputs[n]);
+            if (ne(x, 1) != 1 || ne(x, 2) != 1 || ne(x, 3) != 1) return unsupported("MUL_MAT_MULTI shares a single activation column", reason);
+            for (size_t i = 0; i < n; ++i) {
+                const scrapgpu_status st = mul_mat_shapes(load_desc(desc->inputs[i]), x, load_desc(desc->outputs[i]), 0, reason);
+                if (st != SCRAPGPU_STATUS_OK) return st;
+            }
+            return SCRAPGPU_STATUS_OK;
+        }
+
+        case SCRAPGPU_OP_ARGSORT:
+            return unsupported("ARGSORT is not implemented on cuda_sm100 (TOP_K with k = 1 is)", reason);
+        case SCRAPGPU_OP_TOP_K: {
+            const auto p = load_params<scrapgpu_argsort_params>(desc);
+            if (!f32(s0) || dd.dtype != SCRAPGPU_DTYPE_I32) return unsupported("TOP_K expects F32 keys and I32 indices", reason);
+            if (ne(dd, 1) != ne(s0, 1) || ne(dd, 2) != ne(s0, 2) || ne(dd, 3) != ne(s0, 3)) return bad("TOP_K: dst must have the rows of src0", reason);
+            if (p.top_k != 0 && (int64_t) p.top_k != ne(dd, 0)) return bad("TOP_K: params top_k does not match dst ne0", reason);
+            if (ne(dd, 0) != 1) return unsupported("TOP_K is implemented for k = 1 (greedy arg-max) on cuda_sm100", reason);
+            return SCRAPGPU_STATUS_OK;
+        }
+
+        default:
+            return unsupported("op is not implemented by the cuda_sm100 backend", reason);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// tensor resolution and aliasing
+// ---------------------------------------------------------------------------------------------------------
+
+struct Ref {
+    Buffer * buf = nullptr;
+    scrapgpu_tensor_desc d = {};
+    char * base() const { return static_cast<char *>(buf->ptr) + d.offset; }
+};
+
+scrapgpu_status resolve(Stream * s, const scrapgpu_tensor_desc & raw, Ref & out) {
+    const scrapgpu_tensor_desc td = load_desc(raw);
+    Buffer * b = as_buffer(td.buffer);
+    if (b == nullptr) return invalid("tensor desc has no cuda_sm100 buffer");
+    if (b->dev != s->dev) return invalid("tensor buffer and stream belong to different devices");
+    const uint64_t nbytes = span_bytes(td);
+    if (td.offset > (uint64_t) b->size || nbytes > (uint64_t) b->size - td.offset) return invalid("tensor exceeds its buffer");
+    out.buf = b;
+    out.d = td;
+    return SCRAPGPU_STATUS_OK;
+}
+
+bool overlap(const Ref & a, const Ref & b) {
+    if (a.buf != b.buf) return false;
+    const uint64_t a0 = a.d.offset, a1 = a0 + span_bytes(a.d), b0 = b.d.offset, b1 = b0 + span_bytes(b.d);
+    return a0 < b1 && b0 < a1;
+}
+
+bool same_view(const Ref & a, const Ref & b) {
+    if (a.buf != b.buf || a.d.offset != b.d.offset || a.d.dtype != b.d.dtype) return false;
+    for (int i = 0; i < 4; ++i) if (a.d.ne[i] != b.d.ne[i] || a.d.nb[i] != b.d.nb[i]) return false;
+    return true;
+}
+
+// in-place is sound only where a thread reads an element before it writes the same element
+bool in_place_ok(scrapgpu_op op) {
+    switch (op) {
+        case SCRAPGPU_OP_ADD: case SCRAPGPU_OP_SUB: case SCRAPGPU_OP_MUL: case SCRAPGPU_OP_DIV: case SCRAPGPU_OP_GLU:
+        case SCRAPGPU_OP_RMS_NORM: case SCRAPGPU_OP_SOFT_MAX: case SCRAPGPU_OP_RMS_NORM_MUL: case SCRAPGPU_OP_ADD_RMS_NORM_MUL:
+        case SCRAPGPU_OP_CPY: case SCRAPGPU_OP_DUP: case SCRAPGPU_OP_CONT:
+            return true;
+        default:
+            return false;
+    }
+}
+
+scrapgpu_status check_aliasing(scrapgpu_op op, const std::vector<Ref> & in, const std::vector<Ref> & out) {
+    for (size_t i = 0; i < out.size(); ++i)
+        for (size_t j = i + 1; j < out.size(); ++j)
+            if (overlap(out[i], out[j])) return invalid("op outputs overlap each other");
+    for (size_t i = 0; i < out.size(); ++i) {
+        for (size_t j = 0; j < in.size(); ++j) {
+            if (!overlap(out[i], in[j])) continue;
+            if (!in_place_ok(op)) return invalid("the output overlaps an input and this op is not in-place safe");
+            if (!same_view(out[i], in[j])) return invalid("a partially overlapping output/input view is not in-place safe");
+            if ((op == SCRAPGPU_OP_RMS_NORM_MUL && j == 1) || (op == SCRAPGPU_OP_ADD_RMS_NORM_MUL && j == 2)) return invalid("normalization outputs must not alias the weight input");
+            // a GLU over fused halves reads two elements per output: in place would overwrite a later input
+            if (op == SCRAPGPU_OP_GLU && in.size() == 1) return invalid("GLU over fused halves cannot run in place");
+        }
+    }
+    return SCRAPGPU_STATUS_OK;
+}
+
+sm100_view view_of(const Ref & r) {
+    sm100_view v;
+    v.data = r.base();
+    for (int i = 0; i < 4; ++i) {
+        v.ne[i] = ne(r.d, i);
+        v.nb[i] = (int64_t) r.d.nb[i];
+    }
+    return v;
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// ROPE tables
+// ---------------------------------------------------------------------------------------------------------
+
+uint32_t float_bits(float f) {
+    uint32_t u;
+    std::memcpy(&u, &f, 4);
+    return u;
+}
+
+// (cos, sin) for positions [0, n) and pairs [0, n_dims/2): theta = position * theta_scale^j by sequential f32
+// multiplies, theta_scale = powf(base, -2/n_dims), libm cosf/sinf, times attn_factor (src/core/ref/ops.cpp:559-601).
+// volatile keeps the compiler from contracting or reassociating the products.
+scrapgpu_status rope_table(Device * dev, Stream * s, int n_dims, float base, float freq_scale, float attn_factor, const float ** out, int32_t * count) {
+    static const int32_t kPositions = [] {
+        const char * v = std::getenv("SCRAPGPU_SM100_ROPE_TABLE");
+        const long n = v != nullptr ? std::atol(v) : 4096;
+        return (int32_t) (n < 0 ? 0 : n > (1 << 20) ? (1 << 20) : n);
+    }();
+    *out = nullptr;
+    *count = 0;
+    if (kPositions == 0) return SCRAPGPU_STATUS_OK;
+    const auto key = std::make_tuple(n_dims, float_bits(base), float_bits(freq_scale), float_bits(attn_factor));
+    std::lock_guard<std::mutex> lock(dev->rope_mutex);
+    auto it = dev->rope_tables.find(key);
+    if (it == dev->rope_tables.end()) {
+        const int half = n_dims / 2;
+        std::vector<float> host((size_t) kPositions * half * 2);
+        const float theta_scale = std::pow(base, -2.0f / (float) n_dims);
+        for (int32_t p = 0; p < kPositions; ++p) {
+            volatile float theta = (float) p;
+            for (int j = 0; j < half; ++j) {
+                const float th = freq_scale * (theta / 1.0f);
+                host[((size_t) p * half + j) * 2 + 0] = std::cos(th) * attn_factor;
+                host[((size_t) p * half + j) * 2 + 1] = std::sin(th) * attn_factor;
+                theta = theta * theta_scale;
+            }
+        }
+        void * devp = nullptr;
+        scrapgpu_status st = from_sm100(sm100_malloc(dev->ordinal, host.size() * sizeof(float), &devp));
+        if (st != SCRAPGPU_STATUS_OK) return st;
+        st = from_sm100(sm100_memcpy_h2d(s->cuda, devp, host.data(), host.size() * sizeof(float), 1));
+        if (st != SCRAPGPU_STATUS_OK) {
+            sm100_free(dev->ordinal, devp);
+            return st;
+        }
+        it = dev->rope_tables.emplace(key, std::make_pair(devp, kPositions)).first;
+    }
+    *out = static_cast<const float *>(it->second.first);
+    *count = it->second.second;
+    return SCRAPGPU_STATUS_OK;
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// op dispatch
+// ---------------------------------------------------------------------------------------------------------
+
+bool dense_rows(const scrapgpu_tensor_desc & t) {
+    // rows follow each other without gaps across all outer dims
+    uint64_t next = t.nb[0] * (uint64_t) t.ne[0];
+    if (t.nb[0] != type_size(t.dtype)) return false;
+    for (int i = 1; i < 4; ++i) {
+        if (t.ne[i] != 1 && t.nb[i] != next) return false;
+        next *= (uint64_t) t.ne[i];
+    }
+    return true;
+}
+
+scrapgpu_status run_mul_mat(Stream * s, const Ref & w, const Ref & x, const Ref & d) {
+    const int64_t k = ne(w.d, 0), n = ne(w.d, 1), m = ne(x.d, 1);
+    const int64_t r2 = ne(x.d, 2) / ne(w.d, 2), r3 = ne(x.d, 3) / ne(w.d, 3);
+    const int layout = w.d.layout == SCRAPGPU_LAYOUT_R32 ? 1 : 0;
+    for (int64_t i3 = 0; i3 < ne(x.d, 3); ++i3) {
+        for (int64_t i2 = 0; i2 < ne(x.d, 2); ++i2) {
+            const char * wp = w.base() + (i2 / r2) * w.d.nb[2] + (i3 / r3) * w.d.nb[3];
+            const float * xp = reinterpret_cast<const float *>(x.base() + i2 * x.d.nb[2] + i3 * x.d.nb[3]);
+            float * yp = reinterpret_cast<float *>(d.base() + i2 * d.d.nb[2] + i3 * d.d.nb[3]);
+            const scrapgpu_status st = from_sm100(sm100_mul_mat(s->cuda, w.d.dtype, layout, wp, layout ? 0 : (int64_t) w.d.nb[1], k, n, xp,
+                                                                (int64_t) (x.d.nb[1] / 4), m, yp, (int64_t) (d.d.nb[1] / 4)));
+            if (st != SCRAPGPU_STATUS_OK) return st;
+        }
+    }
+    return SCRAPGPU_STATUS_OK;
+}
+
+scrapgpu_status execute(Stream * s, const scrapgpu_op_desc * desc) {
+    const char * why = nullptr;
+    scrapgpu_status st = supports(desc, &why);
+    if (st != SCRAPGPU_STATUS_OK) return st;
+    switch (desc->op) {
+        case SCRAPGPU_OP_NONE: case SCRAPGPU_OP_RESHAPE: case SCRAPGPU_OP_VIEW: case SCRAPGPU_OP_PERMUTE: case SCRAPGPU_OP_TRANSPOSE:
+            return SCRAPGPU_STATUS_OK;  // metadata only
+        default: break;
+    }
+    std::vector<Ref> in(desc->input_count), out(desc->output_count);
+    for (size_t i = 0; i < desc->input_count; ++i) {
+        st = resolve(s, desc->inputs[i], in[i]);
+        if (st != SCRAPGPU_STATUS_OK) return st;
+    }
+    for (size_t i = 0; i < desc->output_count; ++i) {
+        st = resolve(s, desc->outputs[i], out[i]);
+        if (st != SCRAPGPU_STATUS_OK) return st;
+    }
+    st = check_aliasing(desc->op, in, out);
+    if (st != SCRAPGPU_STATUS_OK) return st;
+    st = from_sm100(sm100_set_device(s->dev->ordinal));
+    if (st != SCRAPGPU_STATUS_OK) return st;
+
+    switch (desc->op) {
+        case SCRAPGPU_OP_ADD: case SCRAPGPU_OP_SUB: case SCRAPGPU_OP_MUL: case SCRAPGPU_OP_DIV: {
+            int64_t n = 0;
+            if (desc->op == SCRAPGPU_OP_ADD && same_shape(in[0].d, in[1].d) && dense_rows(in[0].d) && dense_rows(in[1].d) && dense_rows(out[0].d) &&
+                elements(out[0].d, n))
+                return from_sm100(sm100_add(s->cuda, (const float *) in[0].base(), (const float *) in[1].base(), (float *) out[0].base(), n));
+            const sm100_view a = view_of(in[0]), b = view_of(in[1]), y = view_of(out[0]);
+            return from_sm100(sm100_binary(s->cuda, (int) desc->op - (int) SCRAPGPU_OP_ADD, &a, &b, &y));
+        }
+        case SCRAPGPU_OP_GLU: {
+            const auto p = load_params<scrapgpu_glu_params>(desc);
+            const sm100_view x = view_of(in[0]), y = view_of(out[0]);
+            if (desc->input_count == 2) {
+                int64_t n = 0;
+                if (p.kind == SCRAPGPU_GLU_SWIGLU && dense_rows(in[0].d) && dense_rows(in[1].d) && dense_rows(out[0].d) && elements(out[0].d, n))
+                    return from_sm100(sm100_swiglu(s->cuda, (const float *) in[0].base(), (const float *) in[1].base(), (float *) out[0].base(), n));
+                const sm100_view g = view_of(in[1]);
+                return from_sm100(sm100_glu(s->cuda, (int) p.kind, &x, &g, 0, &y));
+            }
+            return from_sm100(sm100_glu(s->cuda, (int) p.kind, &x, nullptr, p.swapped != 0, &y));
+        }
+        case SCRAPGPU_OP_RMS_NORM: case SCRAPGPU_OP_RMS_NORM_MUL: {
+            const auto p = load_params<scrapgpu_rms_norm_params>(desc);
+            const float * w = desc->op == SCRAPGPU_OP_RMS_NORM_MUL ? (const float *) in[1].base() : nullptr;
+            const sm100_view x = view_of(in[0]), y = view_of(out[0]);
+            return from_sm100(sm100_rms_norm_view(s->cuda, &x, nullptr, w, nullptr, &y, p.eps));
+        }
+        case SCRAPGPU_OP_ADD_RMS_NORM_MUL: {
+            const auto p = load_params<scrapgpu_rms_norm_params>(desc);
+            const sm100_view a = view_of(in[0]), b = view_of(in[1]), sum = view_of(out[0]), y = view_of(out[1]);
+            return from_sm100(sm100_rms_norm_view(s->cuda, &a, &b, (const float *) in[2].base(), &sum, &y, p.eps));
+        }
+        case SCRAPGPU_OP_ROPE: {
+            const auto p = load_params<scrapgpu_rope_params>(desc);
+            const float * table = nullptr;
+            int32_t count = 0;
+            const float * ff = desc->input_count > 2 ? (const float *) in[2].base() : nullptr;
+            if (ff == nullptr) {
+                st = rope_table(s->dev, s, p.n_dims, p.freq_base, p.freq_scale, p.attn_factor, &table, &count);
+                if (st != SCRAPGPU_STATUS_OK) return st;
+            }
+            const sm100_view x = view_of(in[0]), y = view_of(out[0]);
+            return from_sm100(sm100_rope_view(s->cuda, &x, (const int32_t *) in[1].base(), table, 0, count, ff, &y, p.n_dims,
+                                              p.mode == SCRAPGPU_ROPE_MODE_NEOX, p.freq_base, p.freq_scale, p.attn_factor));
+        }
+        case SCRAPGPU_OP_SOFT_MAX: {
+            const auto p = load_params<scrapgpu_soft_max_params>(desc);
+            const sm100_view x = view_of(in[0]), y = view_of(out[0]);
+            if (desc->input_count == 2) {
+                const sm100_view m = view_of(in[1]);
+                return from_sm100(sm100_soft_max_view(s->cuda, &x, &m, in[1].d.dtype == SCRAPGPU_DTYPE_F16, &y, p.scale));
+            }
+            return from_sm100(sm100_soft_max_view(s->cuda, &x, nullptr, 0, &y, p.scale));
+        }
+        case SCRAPGPU_OP_GET_ROWS: {
+            const Ref & t = in[0];
+            const Ref & ids = in[1];
+            const int layout = t.d.layout == SCRAPGPU_LAYOUT_R32 ? 1 : 0;
+            for (int64_t i12 = 0; i12 < ne(ids.d, 2); ++i12) {
+                for (int64_t i11 = 0; i11 < ne(ids.d, 1); ++i11) {
+                    const char * tp = t.base() + i11 * t.d.nb[2] + i12 * t.d.nb[3];
+                    const int32_t * ip = (const int32_t *) (ids.base() + i11 * ids.d.nb[1] + i12 * ids.d.nb[2]);
+                    float * dp = (float *) (out[0].base() + i11 * out[0].d.nb[2] + i12 * out[0].d.nb[3]);
+                    st = from_sm100(sm100_get_rows(s->cuda, t.d.dtype, layout, tp, layout ? 0 : (int64_t) t.d.nb[1], ne(t.d, 0), ne(t.d, 1), ip, ne(ids.d, 0), dp,
+                                                   (int64_t) (out[0].d.nb[1] / 4)));
+                    if (st != SCRAPGPU_STATUS_OK) return st;
+                }
+            }
+            return SCRAPGPU_STATUS_OK;
+        }
+        case SCRAPGPU_OP_SET_ROWS: {
+            const sm100_view src = view_of(in[0]), ids = view_of(in[1]), dst = view_of(out[0]);
+            return from_sm100(sm100_set_rows_view(s->cuda, &src, in[0].d.dtype, &ids, in[1].d.dtype == SCRAPGPU_DTYPE_I64, &dst, out[0].d.dtype));
+        }
+        case SCRAPGPU_OP_CPY: case SCRAPGPU_OP_DUP: case SCRAPGPU_OP_CONT: {
+            const sm100_view src = view_of(in[0]), dst = view_of(out[0]);
+            return from_sm100(sm100_cpy(s->cuda, &src, in[0].d.dtype, &dst, out[0].d.dtype));
+        }
+        case SCRAPGPU_OP_MUL_MAT:
+            return run_mul_mat(s, in[0], in[1], out[0]);
+        case SCRAPGPU_OP_MUL_MAT_MULTI: {
+            const size_t n = desc->output_count;
+            bool fusable = true;
+            int dtypes[3], layouts[3];
+            const void * ws[3];
+            int64_t ns[3];
+            float * ys[3];
+            for (size_t i = 0; i < n; ++i) {
+                const Ref & w = in[i];
+                dtypes[i] = w.d.dtype;
+                layouts[i] = w.d.layout == SCRAPGPU_LAYOUT_R32 ? 1 : 0;
+                ws[i] = w.base();
+                ns[i] = ne(w.d, 1);
+                ys[i] = (float *) out[i].base();
+                fusable = fusable && (layouts[i] == 1 || w.d.nb[1] == (uint64_t) (ne(w.d, 0) / (int64_t) block_size(w.d.dtype)) * type_size(w.d.dtype)) && ne(w.d, 2) * ne(w.d, 3) == 1;
+            }
+            if (fusable) return from_sm100(sm100_mul_mat_multi(s->cuda, (int) n, dtypes, layouts, ws, ne(in[n].d, 0), ns, (const float *) in[n].base(), ys));
+            for (size_t i = 0; i < n; ++i) {
+                st = run_mul_mat(s, in[i], in[n], out[i]);
+                if (st != SCRAPGPU_STATUS_OK) return st;
+            }
+            return SCRAPGPU_STATUS_OK;
+        }
+        case SCRAPGPU_OP_TOP_K: {
+            const sm100_view x = view_of(in[0]), o = view_of(out[0]);
+            return from_sm100(sm100_top1_view(s->cuda, &x, &o));
+        }
+        default:
+            return unsupported("op is not implemented by the cuda_sm100 backend");
+    }
+}
+
+// failures of enqueued work are remembered on the stream and reported at the next sync as well
+scrapgpu_status enqueue_result(Stream * s, scrapgpu_status st) {
+    if (st == SCRAPGPU_STATUS_BACKEND_ERROR || st == SCRAPGPU_STATUS_DEVICE_LOST) {
+        s->sticky = st;
+        const char * m = sm100_last_error();
+        s->sticky_message = m != nullptr ? m : "";
+    }
+    return st;
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// vtable: devices
+// ---------------------------------------------------------------------------------------------------------
+
+void probe_devices() {
+    if (g_devices_probed) return;
+    g_devices_probed = true;
+    const int n = sm100_device_count();
+    for (int i = 0; i < n; ++i) {
+        char name[128] = {};
+        uint64_t mem = 0, shared = 0;
+        uint32_t sms = 0, major = 0, minor = 0;
+        if (sm100_device_info(i, name, sizeof(name), &mem, &sms, &major, &minor, &shared) != 0) continue;
+        if (major != 10) continue;  // kernels are built for sm_100a only
+        auto d = std::make_unique<Device>();
+        d->hdr.backend = &g_vtable;
+        d->ordinal = i;
+        d->name = name;
+        d->total_memory = mem;
+        d->shared_per_block = shared;
+        d->sms = sms;
+        d->cc_major = major;
+        d->cc_minor = minor;
+        g_devices.push_back(std::move(d));
+    }
+}
+
+size_t v_get_device_count(void *) {
+    std::lock_guard<std::mutex> lock(g_registry_mutex);
+    probe_devices();
+    return g_devices.size();
+}
+
+scrapgpu_status v_get_device(void *, size_t index, scrapgpu_device_t ** out_device) {
+    return guard([&]() -> scrapgpu_status {
+        if (out_device == nullptr) return invalid("out_device is null");
+        std::lock_guard<std::mutex> lock(g_registry_mutex);
+        probe_devices();
+        if (index >= g_devices.size()) return invalid("device index out of range");
+        *out_device = reinterpret_cast<scrapgpu_device_t *>(g_devices[index].get());
+        return SCRAPGPU_STATUS_OK;
+    });
+}
+
+scrapgpu_status v_device_get_info(scrapgpu_device_t * device, scrapgpu_device_info * info) {
+    return guard([&]() -> scrapgpu_status {
+        Device * d = as_device(device);
+        if (d == nullptr) return invalid("not a cuda_sm100 device");
+        if (info == nullptr || info->struct_size < sizeof(size_t)) return invalid("device info struct is too small");
+        static const std::string used = "CUDA runtime, kernels built for sm_100a";
+        scrapgpu_device_info full = {};
+        full.struct_size = sizeof(full);
+        full.name = d->name.c_str();
+        full.vendor = "NVIDIA";
+        full.platform_name = "CUDA";
+        full.driver_version = "";
+        full.backend_name = "cuda_sm100";
+        full.reported_api_version = d->cc_minor == 0 ? "compute capability 10.0" : "compute capability 10.x";
+        full.used_api_version = used.c_str();
+        full.generation = SCRAPGPU_DEVICE_GENERATION_UNKNOWN;
+        full.generation_reason = "NVIDIA Blackwell (sm_100a); newer than the generations the enum names";
+        full.total_memory_bytes = d->total_memory;
+        full.max_allocation_reported_bytes = d->total_memory;
+        full.max_allocation_used_bytes = d->total_memory;
+        full.max_work_group_size = 1024;
+        full.local_memory_bytes = d->shared_per_block;
+        full.compute_units = d->sms;
+        full.warp_or_wave_width = 32;
+        full.quirks = 0;
+        full.probed_quirks = 0;
+        full.tuning_profile_name = "b200";
+        full.tuning_overrides = "";
+        const size_t caller = info->struct_size;
+        std::memcpy(info, &full, std::min(caller, sizeof(full)));
+        info->struct_size = caller;
+        return SCRAPGPU_STATUS_OK;
+    });
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// vtable: buffers
+// ---------------------------------------------------------------------------------------------------------
+
+scrapgpu_status v_buffer_alloc(scrapgpu_device_t * device, size_t size, scrapgpu_buffer_t ** out_buffer) {
+    return guard([&]() -> scrapgpu_status {
+        Device * d = as_device(device);
+        if (d == nullptr || out_buffer == nullptr) return invalid("device or out_buffer is null");
+        *out_buffer = nullptr;
+        auto b = std::make_unique<Buffer>();
+        b->hdr.backend = &g_vtable;
+        b->dev = d;
+        b->size = size;
+        const scrapgpu_status st = from_sm100(sm100_malloc(d->ordinal, size == 0 ? 1 : size, &b->ptr));  // cudaMalloc: >= 256-byte aligned
+        if (st != SCRAPGPU_STATUS_OK) return st;
+        *out_buffer = reinterpret_cast<scrapgpu_buffer_t *>(b.release());
+        return SCRAPGPU_STATUS_OK;
+    });
+}
+
+scrapgpu_status v_buffer_free(scrapgpu_buffer_t * buffer) {
+    return guard([&]() -> scrapgpu_status {
+        Buffer * b = as_buffer(buffer);
+        if (b == nullptr) return invalid("not a cuda_sm100 buffer");
+        {
+            std::lock_guard<std::mutex> lock(g_pin_mutex);
+            if (g_pins.find(b) != g_pins.end()) return invalid("buffer is still referenced by a live plan");
+        }
+        const scrapgpu_status st = from_sm100(sm100_free(b->dev->ordinal, b->ptr));
+        b->hdr.backend = nullptr;
+        delete b;
+        return st;
+    });
+}
+
+struct Io {
+    Stream * s;
+    Buffer * b;
+};
+
+scrapgpu_status io_check(scrapgpu_stream_t * stream, scrapgpu_buffer_t * buffer, uint64_t offset, size_t size, const char * what, Io & io) {
+    io.s = as_stream(stream);
+    io.b = as_buffer(buffer);
+    if (io.s == nullptr || io.b == nullptr) return invalid("stream or buffer is not a cuda_sm100 object");
+    if (io.b->dev != io.s->dev) return invalid("buffer and stream belong to different devices");
+    if (size != 0 && (offset > (uint64_t) io.b->size || size > io.b->size - (size_t) offset)) return invalid(what);
+    return from_sm100(sm100_set_device(io.s->dev->ordinal));
+}
+
+scrapgpu_status v_buffer_write(scrapgpu_stream_t * stream, scrapgpu_buffer_t * buffer, uint64_t offset, const void * data, size_t size, int blocking) {
+    return guard([&]() -> scrapgpu_status {
+        Io io;
+        const scrapgpu_status st = io_check(stream, buffer, offset, size, "write exceeds the buffer", io);
+        if (st != SCRAPGPU_STATUS_OK || size == 0) return st;
+        if (data == nullptr) return invalid("data is null");
+        // the host pointer may be pageable and reused by the caller right away: a non-blocking write still
+        // has to have consumed it, so pageable sources are copied synchronously by the runtime either way
+        (void) blocking;
+        return enqueue_result(io.s, from_sm100(sm100_memcpy_h2d(io.s->cuda, static_cast<char *>(io.b->ptr) + offset, data, size, 1)));
+    });
+}
+
+scrapgpu_status v_buffer_read(scrapgpu_stream_t * stream, scrapgpu_buffer_t * buffer, uint64_t offset, void * data, size_t size, int blocking) {
+    return guard([&]() -> scrapgpu_status {
+        Io io;
+        const scrapgpu_status st = io_check(stream, buffer, offset, size, "read exceeds the buffer", io);
+        if (st != SCRAPGPU_STATUS_OK || size == 0) return st;
+        if (data == nullptr) return invalid("data is null");
+        (void) blocking;  // the caller may read `data` as soon as the call returns
+        return enqueue_result(io.s, from_sm100(sm100_memcpy_d2h(io.s->cuda, data, static_cast<char *>(io.b->ptr) + offset, size, 1)));
+    });
+}
+
+scrapgpu_status v_buffer_copy(scrapgpu_stream_t * stream, scrapgpu_buffer_t * dst, uint64_t dst_offset, scrapgpu_buffer_t * src, uint64_t src_offset, size_t size,
+                              int blocking) {
+    return guard([&]() -> scrapgpu_status {
+        Io a, b;
+        scrapgpu_status st = io_check(stream, dst, dst_offset, size, "copy exceeds a buffer", a);
+        if (st != SCRAPGPU_STATUS_OK) return st;
+        st = io_check(stream, src, src_offset, size, "copy exceeds a buffer", b);
+        if (st != SCRAPGPU_STATUS_OK || size == 0) return st;
+        return enqueue_result(a.s, from_sm100(sm100_memcpy_d2d(a.s->cuda, static_cast<char *>(a.b->ptr) + dst_offset, static_cast<char *>(b.b->ptr) + src_offset, size,
+                                                              blocking)));
+    });
+}
+
+scrapgpu_status v_buffer_fill(scrapgpu_stream_t * stream, scrapgpu_buffer_t * buffer, uint64_t offset, size_t size, uint8_t byte, int blocking) {
+    return guard([&]() -> scrapgpu_status {
+        Io io;
+        const scrapgpu_status st = io_check(stream, buffer, offset, size, "fill exceeds the buffer", io);
+        if (st != SCRAPGPU_STATUS_OK || size == 0) return st;
+        return enqueue_result(io.s, from_sm100(sm100_memset(io.s->cuda, static_cast<char *>(io.b->ptr) + offset, byte, size, blocking)));
+    });
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// vtable: streams
+// ---------------------------------------------------------------------------------------------------------
+
+scrapgpu_status v_stream_create(scrapgpu_device_t * device, scrapgpu_stream_t ** out_stream) {
+    return guard([&]() -> scrapgpu_status {
+        Device * d = as_device(device);
+        if (d == nullptr || out_stream == nullptr) return invalid("device or out_stream is null");
+        *out_stream = nullptr;
+        auto s = std::make_unique<Stream>();
+        s->hdr.backend = &g_vtable;
+        s->dev = d;
+        const scrapgpu_status st = from_sm100(sm100_stream_create(d->ordinal, &s->cuda));
+        if (st != SCRAPGPU_STATUS_OK) return st;
+        *out_stream = reinterpret_cast<scrapgpu_stream_t *>(s.release());
+        return SCRAPGPU_STATUS_OK;
+    });
+}
+
+scrapgpu_status v_stream_free(scrapgpu_stream_t * stream) {
+    return guard([&]() -> scrapgpu_status {
+        Stream * s = as_stream(stream);
+        if (s == nullptr) return invalid("not a cuda_sm100 stream");
+        sm100_stream_sync(s->cuda);
+        const scrapgpu_status st = from_sm100(sm100_stream_destroy(s->dev->ordinal, s->cuda));
+        s->hdr.backend = nullptr;
+        delete s;
+        return st;
+    });
+}
+
+scrapgpu_status v_stream_sync(scrapgpu_stream_t * stream) {
+    return guard([&]() -> scrapgpu_status {
+        Stream * s = as_stream(stream);
+        if (s == nullptr) return invalid("not a cuda_sm100 stream");
+        const scrapgpu_status st = from_sm100(sm100_stream_sync(s->cuda));
+        if (st != SCRAPGPU_STATUS_OK) return st;
+        if (s->sticky != SCRAPGPU_STATUS_OK) {
+            const scrapgpu_status sticky = s->sticky;
+            set_error(s->sticky_message.empty() ? "an operation enqueued on this stream failed" : s->sticky_message.c_str());
+            s->sticky = SCRAPGPU_STATUS_OK;
+            return sticky;
+        }
+        return SCRAPGPU_STATUS_OK;
+    });
+}
+
+scrapgpu_device_t * v_stream_device(scrapgpu_stream_t * stream) {
+    Stream * s = as_stream(stream);
+    return s == nullptr ? nullptr : reinterpret_cast<scrapgpu_device_t *>(s->dev);
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// vtable: tensor transfers
+// ---------------------------------------------------------------------------------------------------------
+
+scrapgpu_status transfer(scrapgpu_stream_t * stream, const scrapgpu_tensor_desc * raw, void * host, size_t size, bool to_device) {
+    Stream * s = as_stream(stream);
+    if (s == nullptr || raw == nullptr) return invalid("stream or tensor desc is null");
+    if (raw->struct_size < offsetof(scrapgpu_tensor_desc, offset) + sizeof(raw->offset)) return invalid("tensor desc is too small");
+    const scrapgpu_tensor_desc td = load_desc(*raw);
+    Buffer * b = as_buffer(td.buffer);
+    if (b == nullptr) return invalid("tensor desc has no cuda_sm100 buffer");
+    if (b->dev != s->dev) return invalid("tensor buffer and stream belong to different devices");
+    if (td.offset > (uint64_t) b->size || size > b->size - (size_t) td.offset) return invalid("transfer exceeds the buffer");
+    if (size > span_bytes(td)) return invalid("transfer size exceeds the tensor");
+    if (size == 0) return SCRAPGPU_STATUS_OK;
+    if (host == nullptr) return invalid("host pointer is null");
+    if (!contiguous(td)) return unsupported("tensor is not contiguous; use buffer_read / buffer_write for raw strided transfers");
+    scrapgpu_status st = from_sm100(sm100_set_device(s->dev->ordinal));
+    if (st != SCRAPGPU_STATUS_OK) return st;
+    char * dev_ptr = static_cast<char *>(b->ptr) + td.offset;
+    if (td.layout == SCRAPGPU_LAYOUT_NATURAL) {
+        return enqueue_result(s, from_sm100(to_device ? sm100_memcpy_h2d(s->cuda, dev_ptr, host, size, 1) : sm100_memcpy_d2h(s->cuda, host, dev_ptr, size, 1)));
+    }
+    if (td.layout != SCRAPGPU_LAYOUT_R32) return unsupported("unknown tensor layout");
+    // backend-packed: the host side is natural bytes, the device side the plane layout (whole blocks only)
+    if (!is_quant(td.dtype)) return unsupported("only quantized tensors have a backend-packed layout");
+    if (ne(td, 2) * ne(td, 3) != 1) return unsupported("a backend-packed tensor must be 2-D");
+    if (td.offset % 32 != 0) return unsupported("a backend-packed tensor must start on a 32-byte boundary of its buffer");
+    const size_t bb = type_size(td.dtype);
+    if (size % bb != 0) return unsupported("a transfer of a backend-packed tensor must cover whole blocks");
+    if (span_bytes(td) > (uint64_t) b->size - td.offset) return invalid("tensor exceeds its buffer");
+    void * staging = nullptr;
+    st = from_sm100(sm100_malloc(s->dev->ordinal, size, &staging));
+    if (st != SCRAPGPU_STATUS_OK) return st;
+    const int64_t blocks = (int64_t) (size / bb);
+    if (to_device) {
+        st = from_sm100(sm100_memcpy_h2d(s->cuda, staging, host, size, 0));
+        if (st == SCRAPGPU_STATUS_OK) st = from_sm100(sm100_pack_device_range(s->cuda, td.dtype, td.ne[0], td.ne[1], 0, blocks, staging, dev_ptr, 1));
+        if (st == SCRAPGPU_STATUS_OK) st = from_sm100(sm100_stream_sync(s->cuda));
+    } else {
+        st = from_sm100(sm100_pack_device_range(s->cuda, td.dtype, td.ne[0], td.ne[1], 0, blocks, staging, dev_ptr, 0));
+        if (st == SCRAPGPU_STATUS_OK) st = from_sm100(sm100_memcpy_d2h(s->cuda, host, staging, size, 1));
+    }
+    sm100_free(s->dev->ordinal, staging);
+    return enqueue_result(s, st);
+}
+
+scrapgpu_status v_tensor_upload(scrapgpu_stream_t * stream, const scrapgpu_tensor_desc * desc, const void * host, size_t size) {
+    return guard([&]() -> scrapgpu_status { return transfer(stream, desc, const_cast<void *>(host), size, true); });
+}
+
+scrapgpu_status v_tensor_download(scrapgpu_stream_t * stream, const scrapgpu_tensor_desc * desc, void * host, size_t size) {
+    return guard([&]() -> scrapgpu_status { return transfer(stream, desc, host, size, false); });
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// vtable: ops and plans
+// ---------------------------------------------------------------------------------------------------------
+
+scrapgpu_status v_op_supported(scrapgpu_device_t * device, const scrapgpu_op_desc * desc, const char ** reason) {
+    if (as_device(device) == nullptr) {
+        if (reason != nullptr) *reason = "not a cuda_sm100 device";
+        return invalid("not a cuda_sm100 device");
+    }
+    return guard([&]() -> scrapgpu_status { return supports(desc, reason); });
+}
+
+scrapgpu_status v_op_execute(scrapgpu_stream_t * stream, const scrapgpu_op_desc * desc) {
+    return guard([&]() -> scrapgpu_status {
+        Stream * s = as_stream(stream);
+        if (s == nullptr) return invalid("not a cuda_sm100 stream");
+        if (desc == nullptr) return invalid("op desc is null");
+        return enqueue_result(s, execute(s, desc));
+    });
+}
+
+const char * op_name(int op) {
+    switch (op) {
+        case SCRAPGPU_OP_ADD: return "ADD";
+        case SCRAPGPU_OP_MUL: return "MUL";
+        case SCRAPGPU_OP_GLU: return "GLU";
+        case SCRAPGPU_OP_RMS_NORM: return "RMS_NORM";
+        case SCRAPGPU_OP_ROPE: return "ROPE";
+        case SCRAPGPU_OP_SOFT_MAX: return "SOFT_MAX";
+        case SCRAPGPU_OP_GET_ROWS: return "GET_ROWS";
+        case SCRAPGPU_OP_SET_ROWS: return "SET_ROWS";
+        case SCRAPGPU_OP_CPY: return "CPY";
+        case SCRAPGPU_OP_MUL_MAT: return "MUL_MAT";
+        case SCRAPGPU_OP_TOP_K: return "TOP_K";
+        case SCRAPGPU_OP_RMS_NORM_MUL: return "RMS_NORM_MUL";
+        case SCRAPGPU_OP_ADD_RMS_NORM_MUL: return "ADD_RMS_NORM_MUL";
+        case SCRAPGPU_OP_MUL_MAT_MULTI: return "MUL_MAT_MULTI";
+        default: return "OP";
+    }
+}
+
+scrapgpu_status v_plan_build(scrapgpu_device_t * device, const scrapgpu_plan_desc * desc, scrapgpu_plan_t ** out_plan) {
+    return guard([&]() -> scrapgpu_status {
+        Device * d = as_device(device);
+        if (d == nullptr || desc == nullptr || out_plan == nullptr || desc->struct_size < offsetof(scrapgpu_plan_desc, node_count) + sizeof(desc->node_count) ||
+            desc->node_count > 4096 || (desc->node_count > 0 && desc->nodes == nullptr))
+            return invalid("device, plan desc or node list is invalid");
+        *out_plan = nullptr;
+        auto plan = std::make_unique<Plan>();
+        plan->hdr.backend = &g_vtable;
+        plan->dev = d;
+        plan->nodes.resize(desc->node_count);
+        for (size_t i = 0; i < desc->node_count; ++i) {
+            const scrapgpu_plan_node & src = desc->nodes[i];
+            if (src.struct_size < offsetof(scrapgpu_plan_node, op) + sizeof(src.op)) return invalid("plan node is too small");
+            const char * why = nullptr;
+            const scrapgpu_status st = supports(&src.op, &why);  // a plan fails to build rather than midway through execution
+            if (st != SCRAPGPU_STATUS_OK) {
+                char buf[256];
+                std::snprintf(buf, sizeof(buf), "plan node %zu (%s): %s", i, op_name((int) src.op.op), why != nullptr ? why : "not supported");
+                set_error(buf);
+                return st;
+            }
+            PlanNode & n = plan->nodes[i];
+            n.desc = src.op;
+            n.desc.struct_size = sizeof(n.desc);
+            for (size_t j = 0; j < src.op.input_count; ++j) n.inputs.push_back(load_desc(src.op.inputs[j]));
+            for (size_t j = 0; j < src.op.output_count; ++j) n.outputs.push_back(load_desc(src.op.outputs[j]));
+            if (src.op.params != nullptr && src.op.params_size > 0) {
+                const uint8_t * p = static_cast<const uint8_t *>(src.op.params);
+                n.params.assign(p, p + src.op.params_size);
+            }
+            n.desc.inputs = n.inputs.data();
+            n.desc.outputs = n.outputs.data();
+            n.desc.params = n.params.empty() ? nullptr : n.params.data();
+            // descriptor pointers inside the params must point at the plan's own copies
+            if (src.op.op == SCRAPGPU_OP_ROPE && n.params.size() >= sizeof(scrapgpu_rope_params)) {
+                auto * p = reinterpret_cast<scrapgpu_rope_params *>(n.params.data());
+                p->freq_factors = p->freq_factors != nullptr && n.inputs.size() > 2 ? &n.inputs[2] : nullptr;
+                p->n_offs = p->n_offs != nullptr && n.inputs.size() > 3 ? &n.inputs[3] : nullptr;
+            }
+            if (src.op.op == SCRAPGPU_OP_SOFT_MAX && n.params.size() >= sizeof(scrapgpu_soft_max_params)) {
+                auto * p = reinterpret_cast<scrapgpu_soft_max_params *>(n.params.data());
+                p->mask = p->mask != nullptr && n.inputs.size() > 1 ? &n.inputs[1] : nullptr;
+            }
+            for (const auto & t : n.inputs) if (Buffer * rb = as_buffer(t.buffer)) plan->pinned.push_back(rb);
+            for (const auto & t : n.outputs) if (Buffer * rb = as_buffer(t.buffer)) plan->pinned.push_back(rb);
+        }
+        {
+            std::lock_guard<std::mutex> lock(g_pin_mutex);
+            for (Buffer * rb : plan->pinned) ++g_pins[rb];
+        }
+        *out_plan = reinterpret_cast<scrapgpu_plan_t *>(plan.release());
+        return SCRAPGPU_STATUS_OK;
+    });
+}
+
+scrapgpu_status v_plan_execute(scrapgpu_stream_t * stream, scrapgpu_plan_t * plan_) {
+    return guard([&]() -> scrapgpu_status {
+        Stream * s = as_stream(stream);
+        Plan * plan = as_plan(plan_);
+        if (s == nullptr || plan == nullptr) return invalid("stream or plan is not a cuda_sm100 object");
+        if (plan->dev != s->dev) return invalid("plan and stream belong to different devices");
+        for (auto & node : plan->nodes) {
+            const scrapgpu_status st = enqueue_result(s, execute(s, &node.desc));
+            if (st != SCRAPGPU_STATUS_OK) return st;
+        }
+        return SCRAPGPU_STATUS_OK;
+    });
+}
+
+scrapgpu_status v_plan_free(scrapgpu_plan_t * plan_) {
+    return guard([&]() -> scrapgpu_status {
+        Plan * plan = as_plan(plan_);
+        if (plan == nullptr) return invalid("not a cuda_sm100 plan");
+        {
+            std::lock_guard<std::mutex> lock(g_pin_mutex);
+            for (Buffer * rb : plan->pinned) {
+                auto it = g_pins.find(rb);
+                if (it != g_pins.end() && --it->second == 0) g_pins.erase(it);
+            }
+        }
+        plan->hdr.backend = nullptr;
+        delete plan;
+        return SCRAPGPU_STATUS_OK;
+    });
+}
+
+const scrapgpu_backend_vtable g_vtable = {
+    /* struct_size      */ sizeof(scrapgpu_backend_vtable),
+    /* name             */ "cuda_sm100",
+    /* userdata         */ nullptr,
+    /* get_device_count */ v_get_device_count,
+    /* get_device       */ v_get_device,
+    /* device_get_info  */ v_device_get_info,
+    /* buffer_alloc     */ v_buffer_alloc,
+    /* buffer_free      */ v_buffer_free,
+    /* buffer_write     */ v_buffer_write,
+    /* buffer_read      */ v_buffer_read,
+    /* buffer_copy      */ v_buffer_copy,
+    /* buffer_fill      */ v_buffer_fill,
+    /* stream_sync      */ v_stream_sync,
+    /* op_supported     */ v_op_supported,
+    /* plan_build       */ v_plan_build,
+    /* plan_execute     */ v_plan_execute,
+    /* plan_free        */ v_plan_free,
+    /* stream_create    */ v_stream_create,
+    /* stream_free      */ v_stream_free,
+    /* tensor_upload    */ v_tensor_upload,
+    /* tensor_download  */ v_tensor_download,
+    /* op_execute       */ v_op_execute,
+    /* stream_device    */ v_stream_device,
+};
+
+// ---------------------------------------------------------------------------------------------------------
+// fused attention entry
+// ---------------------------------------------------------------------------------------------------------
+
+bool strict_contiguous(const scrapgpu_tensor_desc & t) {
+    uint64_t next = 4;
+    for (int i = 0; i < 4; ++i) {
+        if (t.nb[i] != next) return false;
+        next *= (uint64_t) ne(t, i);
+    }
+    return true;
+}
+
+scrapgpu_status attention(scrapgpu_device_t * device, scrapgpu_stream_t * stream, const scrapgpu_attention_params * params, const scrapgpu_tensor_desc * position) {
+    Device * d = as_device(device);
+    Stream * s = as_stream(stream);
+    if (d == nullptr || s == nullptr) return invalid("device or stream is not a cuda_sm100 object");
+    if (s->dev != d) return invalid("stream and device differ");
+    if (params == nullptr || params->struct_size < sizeof(scrapgpu_attention_params)) return invalid("attention params are missing or too small");
+    if (params->query == nullptr || params->key == nullptr || params->value == nullptr || params->output == nullptr) return invalid("attention needs query, key, value and output");
+    if (!std::isfinite(params->scale)) return invalid("attention scale must be finite");
+    Ref q, k, v, o, m, pos;
+    scrapgpu_status st;
+    if ((st = resolve(s, *params->query, q)) != SCRAPGPU_STATUS_OK) return st;
+    if ((st = resolve(s, *params->key, k)) != SCRAPGPU_STATUS_OK) return st;
+    if ((st = resolve(s, *params->value, v)) != SCRAPGPU_STATUS_OK) return st;
+    if ((st = resolve(s, *params->output, o)) != SCRAPGPU_STATUS_OK) return st;
+    const bool has_mask = params->mask != nullptr;
+    if (has_mask && (st = resolve(s, *params->mask, m)) != SCRAPGPU_STATUS_OK) return st;
+    if (position != nullptr) {
+        if ((st = resolve(s, *position, pos)) != SCRAPGPU_STATUS_OK) return st;
+        if (pos.d.dtype != SCRAPGPU_DTYPE_I32) return unsupported("the attention position tensor must be I32");
+    }
+    for (const Ref * r : {&q, &k, &v, &o}) {
+        if (!f32(r->d) || r->d.layout != SCRAPGPU_LAYOUT_NATURAL) return unsupported("attention tensors must be F32 in the natural layout");
+        if (!strict_contiguous(r->d)) return unsupported("attention tensors must be contiguous");
+    }
+    const int64_t D = ne(q.d, 0), Q = ne(q.d, 1), Hq = ne(q.d, 2), B = ne(q.d, 3);
+    const int64_t Kn = ne(k.d, 1), Hkv = ne(k.d, 2), Dv = ne(v.d, 0);
+    if (ne(k.d, 0) != D || ne(k.d, 3) != B || ne(v.d, 1) != Kn || ne(v.d, 2) != Hkv || ne(v.d, 3) != B) return invalid("attention: key/value shapes do not match the query");
+    if (ne(o.d, 0) != Dv || ne(o.d, 1) != Q || ne(o.d, 2) != Hq || ne(o.d, 3) != B) return invalid("attention: output must be [Dv, Q, Hq, B]");
+    if (Hkv <= 0 || Hq % Hkv != 0) return invalid("attention: Hq must be divisible by Hkv");
+    int64_t mask_heads = 1, mask_batches = 1;
+    if (has_mask) {
+        if (!f32(m.d) || !strict_contiguous(m.d)) return unsupported("the attention mask must be contiguous F32");
+        if (ne(m.d, 0) != Kn || ne(m.d, 1) != Q || (ne(m.d, 2) != 1 && ne(m.d, 2) != Hq) || (ne(m.d, 3) != 1 && ne(m.d, 3) != B)) return invalid("attention: mask must be [K, Q, 1 or Hq, 1 or B]");
+        mask_heads = ne(m.d, 2);
+        mask_batches = ne(m.d, 3);
+    }
+    for (const Ref * r : {&q, &k, &v}) if (overlap(o, *r)) return invalid("attention output overlaps an input");
+    if ((st = from_sm100(sm100_set_device(d->ordinal))) != SCRAPGPU_STATUS_OK) return st;
+    const uint64_t off = params->query_position_offset > (uint64_t) std::numeric_limits<int64_t>::max() / 2 ? (uint64_t) std::numeric_limits<int64_t>::max() / 2
+                                                                                                             : params->query_position_offset;
+    for (int64_t b = 0; b < B; ++b) {
+        const float * mp = has_mask ? (const float *) (m.base() + (mask_batches == 1 ? 0 : b) * m.d.nb[3]) : nullptr;
+        st = from_sm100(sm100_attention(s->cuda, (const float *) (q.base() + b * q.d.nb[3]), (const float *) (k.base() + b * k.d.nb[3]),
+                                        (const float *) (v.base() + b * v.d.nb[3]), mp, mask_heads, (float *) (o.base() + b * o.d.nb[3]), D, Dv, Q, Kn, Hq, Hkv,
+                                        params->causal != 0, (int64_t) off, position != nullptr ? (const int32_t *) pos.base() : nullptr, params->scale));
+        if (st != SCRAPGPU_STATUS_OK) return enqueue_result(s, st);
+    }
+    return SCRAPGPU_STATUS_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+SCRAPGPU_API const scrapgpu_backend_vtable * scrapgpu_cuda_sm100_vtable(void) { return &g_vtable; }
+
+SCRAPGPU_API scrapgpu_status scrapgpu_cuda_sm100_register(void) {
+    return guard([&]() -> scrapgpu_status {
+        if (scrapgpu_register_backend == nullptr) return unsupported("the ScrapGpuLibrary core is not loaded: scrapgpu_register_backend is unresolved");
+        static std::mutex reg_mutex;
+        std::lock_guard<std::mutex> lock(reg_mutex);
+        {
+            std::lock_guard<std::mutex> lock2(g_registry_mutex);
+            probe_devices();
+        }
+        static bool registered = false;
+        if (registered) return SCRAPGPU_STATUS_OK;
+        const scrapgpu_status st = scrapgpu_register_backend(&g_vtable);
+        registered = st == SCRAPGPU_STATUS_OK;
+        return st;
+    });
+}
+
+SCRAPGPU_API scrapgpu_status scrapgpu_cuda_sm100_attention(scrapgpu_device_t * device, scrapgpu_stream_t * stream, const scrapgpu_attention_params * params) {
+    return guard([&]() -> scrapgpu_status { return attention(device, stream, params, nullptr); });
+}
+
+SCRAPGPU_API scrapgpu_status scrapgpu_cuda_sm100_attention_at(scrapgpu_device_t * device, scrapgpu_stream_t * stream, const scrapgpu_attention_params * params,
+                                                             const scrapgpu_tensor_desc * position) {
+    return guard([&]() -> scrapgpu_status {
+        if (position == nullptr) return invalid("position tensor is null");
+        return attention(device, stream, params, position);
+    });
+}
+
+SCRAPGPU_API uint64_t scrapgpu_cuda_sm100_launch_count(void) { return sm100_launch_count(); }
+
+}  // extern "C"

@@ -14,6 +14,9 @@
 // Kernel B  matvec_rows<Unit, M>  any layout / shape / M <= 8: one warp per weight row, activations
 //           through L1.
 #include "sm100_quant_units.cuh"
+#include "sm100_wide_units.cuh"
+
+#include <cstdlib>
 
 namespace sm100 {
 
@@ -217,6 +220,96 @@ __global__ void __launch_bounds__(U::MAX_THREADS) matvec_stream(const uint8_t * 
     }
 }
 
+// ---- kernel A2: packed, M = 1, 32-byte wide units, conversion-free unpack, packed f32x2 FMAs ------------
+//
+// threads = units_per_row * rows_per_pass; a thread keeps the 32 or 64 activations of its column unit in
+// registers and walks down the rows of its CTA with ROWS weight rows in flight.  Per batch of ROWS rows the
+// per-thread partials are reduced with a transposing shuffle (6 shuffles for 4 rows instead of 20), then
+// across the warps of a row through shared memory.
+
+template <int ROWS>
+__device__ __forceinline__ float transpose_reduce(const float (&v)[ROWS], int lane);
+
+// 4 values per lane -> lane 8*r holds the warp-wide sum of value r
+template <>
+__device__ __forceinline__ float transpose_reduce<4>(const float (&v)[4], int lane) {
+    const bool up16 = lane & 16, up8 = lane & 8;
+    const float s0 = __shfl_xor_sync(0xffffffffu, up16 ? v[0] : v[2], 16);
+    const float s1 = __shfl_xor_sync(0xffffffffu, up16 ? v[1] : v[3], 16);
+    const float w0 = (up16 ? v[2] : v[0]) + s0;   // rows 0/2
+    const float w1 = (up16 ? v[3] : v[1]) + s1;   // rows 1/3
+    const float s2 = __shfl_xor_sync(0xffffffffu, up8 ? w0 : w1, 8);
+    float u = (up8 ? w1 : w0) + s2;                // row = 2 * bit4 + bit3
+    u += __shfl_xor_sync(0xffffffffu, u, 4);
+    u += __shfl_xor_sync(0xffffffffu, u, 2);
+    u += __shfl_xor_sync(0xffffffffu, u, 1);
+    return u;
+}
+
+template <class W, int ROWS, int MAXT, int MINB>
+__global__ void __launch_bounds__(MAXT, MINB) matvec_wide(const uint8_t * __restrict__ w, Planes P, const float * __restrict__ x,
+                                                          float * __restrict__ y, int n_rows, int units_per_row, int rows_per_cta) {
+    static_assert(ROWS == 4, "the transposing reduction is written for 4 rows in flight");
+    extern __shared__ float red[];  // [ROWS][warps]
+    const int tid = threadIdx.x, lane = tid & 31;
+    const int cu = tid % units_per_row;
+    const int rl = tid / units_per_row;
+    const int rp = blockDim.x / units_per_row;
+    const int warps = blockDim.x >> 5;
+    const int warps_per_row = units_per_row >> 5;
+    const int64_t bpr = W::UNITS_PER_BLOCK > 0 ? units_per_row / W::UNITS_PER_BLOCK : (int64_t) units_per_row * -W::UNITS_PER_BLOCK;
+    const int row0 = blockIdx.x * rows_per_cta;
+    const int row_end = min(n_rows, row0 + rows_per_cta);
+
+    typename W::Data data[ROWS];
+#pragma unroll
+    for (int i = 0; i < ROWS; ++i) {
+        const int r = row0 + rl + i * rp;
+        if (r < row_end) W::load(w, P, r, bpr, cu, data[i]);
+    }
+    pdl_wait();
+    float2 xr[W::WEIGHTS / 2];
+    float sums[W::XSUMS];
+#pragma unroll
+    for (int s = 0; s < W::XSUMS; ++s) sums[s] = 0.f;
+#pragma unroll
+    for (int g = 0; g < W::WEIGHTS / 4; ++g) {
+        const float4 v = __ldg(reinterpret_cast<const float4 *>(x + W::x_index(cu, g)));
+        xr[2 * g] = make_float2(v.x, v.y);
+        xr[2 * g + 1] = make_float2(v.z, v.w);
+        sums[W::sum_slot(g)] += (v.x + v.y) + (v.z + v.w);
+    }
+    pdl_launch_dependents();
+
+    for (int base = row0; base < row_end; base += rp * ROWS) {
+        float part[ROWS];
+#pragma unroll
+        for (int i = 0; i < ROWS; ++i) {
+            const int r = base + rl + i * rp;
+            part[i] = r < row_end ? W::dot(data[i], cu, xr, sums) : 0.f;
+        }
+        const int next = base + rp * ROWS;
+#pragma unroll
+        for (int i = 0; i < ROWS; ++i) {
+            const int r = next + rl + i * rp;
+            if (r < row_end) W::load(w, P, r, bpr, cu, data[i]);
+        }
+        const float u = transpose_reduce<ROWS>(part, lane);
+        if ((lane & 7) == 0) red[(lane >> 3) * warps + (tid >> 5)] = u;
+        __syncthreads();
+        if (tid < rp * ROWS) {
+            const int i = tid / rp, lr = tid % rp;
+            const int r = base + lr + i * rp;
+            if (r < row_end) {
+                float v = 0.f;
+                for (int k = 0; k < warps_per_row; ++k) v += red[i * warps + lr * warps_per_row + k];
+                y[r] = v;
+            }
+        }
+        __syncthreads();
+    }
+}
+
 // ---- kernel B: one warp per row, any layout, M <= 8 -------------------------------------------------
 
 template <class U, int M, bool PACKED>
@@ -304,6 +397,40 @@ static int launch_stream(cudaStream_t s, const void * w, int64_t k, int64_t n, c
                   (int) rows_per_cta);
 }
 
+// tuning knobs of the wide kernel, overridable from the environment for experiments:
+// SM100_MV_THREADS (target CTA size), SM100_MV_CTAS (CTAs per SM used to size the grid)
+static int env_int(const char * name, int fallback) {
+    const char * v = std::getenv(name);
+    return v != nullptr && *v != '\0' ? std::atoi(v) : fallback;
+}
+
+template <class W>
+static int launch_wide(cudaStream_t s, const void * w, int64_t k, int64_t n, const float * x, float * y) {
+    static const int target_threads = env_int("SM100_MV_THREADS", 192);
+    static const int ctas_per_sm = env_int("SM100_MV_CTAS", 2);
+    const int upr = (int) (k / W::WEIGHTS);
+    // a whole number of rows per pass; CTAs of at most 192 threads leave room for 168 registers per thread
+    // at two CTAs per SM (64 activations + 4 rows of quants in flight do not fit in 128)
+    const int rp = upr >= target_threads ? 1 : target_threads / upr;
+    const int threads = rp * upr;
+    const Planes P = planes_for(W::DTYPE, n * (k / block_elems(W::DTYPE)));
+    const int64_t slots = (int64_t) sm_count() * ctas_per_sm;
+    int64_t rows_per_cta = (n + slots - 1) / slots;
+    rows_per_cta = (rows_per_cta + rp - 1) / rp * rp;
+    const int64_t grid = (n + rows_per_cta - 1) / rows_per_cta;
+    const size_t smem = (size_t) 4 * (threads / 32) * sizeof(float);
+    const uint8_t * wp = (const uint8_t *) w;
+    if (threads <= 192) return launch(matvec_wide<W, 4, 192, 2>, dim3((unsigned) grid), dim3(threads), smem, s, wp, P, x, y, (int) n, upr, (int) rows_per_cta);
+    if (threads <= 384) return launch(matvec_wide<W, 4, 384, 1>, dim3((unsigned) grid), dim3(threads), smem, s, wp, P, x, y, (int) n, upr, (int) rows_per_cta);
+    return launch(matvec_wide<W, 4, 512, 1>, dim3((unsigned) grid), dim3(threads), smem, s, wp, P, x, y, (int) n, upr, (int) rows_per_cta);
+}
+
+template <class W>
+static bool wide_ok(int64_t k, int64_t m) {
+    const int64_t upr = k / W::WEIGHTS;
+    return m == 1 && k % W::WEIGHTS == 0 && upr % 32 == 0 && upr <= 512;
+}
+
 template <class U, bool PACKED>
 static int launch_rows(cudaStream_t s, const void * w, int64_t w_row_stride, int64_t k, int64_t n, const float * x, int64_t ldx,
                        int64_t m, float * y, int64_t ldy) {
@@ -353,6 +480,15 @@ int matvec(cudaStream_t s, int dtype, int layout, const void * w, int64_t w_row_
     if (layout == LAYOUT_PACKED && !is_quant(dtype)) return fail(ST_UNSUPPORTED, "mul_mat: only quantized weights have a packed layout");
     if (layout != LAYOUT_PACKED && layout != LAYOUT_NATURAL) return fail(ST_INVALID, "mul_mat: unknown layout %d", layout);
     if (is_quant(dtype) && !x_aligned) return fail(ST_UNSUPPORTED, "mul_mat: activations must be 16-byte aligned (columns too)");
+    static const int use_wide = env_int("SM100_MV_WIDE", 1);
+    if (use_wide && layout == LAYOUT_PACKED) {
+        switch (dtype) {
+            case DT_Q4_K: if (wide_ok<WideQ4K>(k, m)) return launch_wide<WideQ4K>(s, w, k, n, x, y); break;
+            case DT_Q6_K: if (wide_ok<WideQ6K>(k, m)) return launch_wide<WideQ6K>(s, w, k, n, x, y); break;
+            case DT_Q4_0: if (wide_ok<WideQ40>(k, m)) return launch_wide<WideQ40>(s, w, k, n, x, y); break;
+            case DT_Q8_0: if (wide_ok<WideQ80>(k, m)) return launch_wide<WideQ80>(s, w, k, n, x, y); break;
+        }
+    }
     switch (dtype) {
         case DT_Q4_K: return matvec_dispatch<UnitQ4K>(s, layout, w, w_row_stride, k, n, x, ldx, m, y, ldy);
         case DT_Q6_K: return matvec_dispatch<UnitQ6K>(s, layout, w, w_row_stride, k, n, x, ldx, m, y, ldy);

@@ -331,8 +331,8 @@ using namespace sm100;
 
 extern "C" {
 
-int sm100_get_rows(sm100_stream_t s, int dtype, int layout, const void * table, int64_t k, int64_t table_rows, const int32_t * ids,
-                   int64_t n_ids, float * dst, int64_t ld_dst) {
+int sm100_get_rows(sm100_stream_t s, int dtype, int layout, const void * table, int64_t table_row_stride, int64_t k, int64_t table_rows,
+                   const int32_t * ids, int64_t n_ids, float * dst, int64_t ld_dst) {
     if (table == nullptr || ids == nullptr || dst == nullptr) return fail(ST_INVALID, "get_rows: null pointer");
     const int be = block_elems(dtype);
     if (be == 0 || dtype == DT_I32) return fail(ST_UNSUPPORTED, "get_rows: unsupported table dtype %d", dtype);
@@ -340,7 +340,7 @@ int sm100_get_rows(sm100_stream_t s, int dtype, int layout, const void * table, 
     if (layout == LAYOUT_PACKED && !is_quant(dtype)) return fail(ST_UNSUPPORTED, "get_rows: only quantized tables have a packed layout");
     Planes P = {};
     if (layout == LAYOUT_PACKED) P = planes_for(dtype, table_rows * (k / be));
-    const int64_t row_stride = k / be * block_bytes(dtype);
+    const int64_t row_stride = table_row_stride != 0 && layout != LAYOUT_PACKED ? table_row_stride : k / be * block_bytes(dtype);
     const int threads = 256;
     unsigned gx = (unsigned) ((k + threads - 1) / threads);
     if (gx > 64) gx = 64;

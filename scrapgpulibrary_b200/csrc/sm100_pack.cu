@@ -119,11 +119,13 @@ __host__ __device__ inline void unpack_block(int dtype, const Planes & P, int64_
     }
 }
 
-__global__ void pack_kernel(int dtype, Planes P, int64_t total, int bb, const uint8_t * natural, uint8_t * packed, int to_packed) {
+// blocks [first, first + count): natural holds them contiguously starting at its byte 0
+__global__ void pack_kernel(int dtype, Planes P, int64_t first, int64_t count, int bb, const uint8_t * natural, uint8_t * packed, int to_packed) {
     pdl_wait();
-    for (int64_t t = blockIdx.x * (int64_t) blockDim.x + threadIdx.x; t < total; t += (int64_t) gridDim.x * blockDim.x) {
-        if (to_packed) pack_block(dtype, P, t, natural + t * bb, packed);
-        else unpack_block(dtype, P, t, packed, const_cast<uint8_t *>(natural) + t * bb);
+    pdl_launch_dependents();
+    for (int64_t i = blockIdx.x * (int64_t) blockDim.x + threadIdx.x; i < count; i += (int64_t) gridDim.x * blockDim.x) {
+        if (to_packed) pack_block(dtype, P, first + i, natural + i * bb, packed);
+        else unpack_block(dtype, P, first + i, packed, const_cast<uint8_t *>(natural) + i * bb);
     }
 }
 
@@ -168,26 +170,34 @@ int sm100_unpack(int dtype, int64_t k, int64_t n, const void * packed, void * na
     return ST_OK;
 }
 
-static int pack_device(sm100_stream_t s, int dtype, int64_t k, int64_t n, const void * natural, void * packed, int to_packed) {
+static int pack_device(sm100_stream_t s, int dtype, int64_t k, int64_t n, int64_t first, int64_t count, const void * natural, void * packed,
+                       int to_packed) {
     if (natural == nullptr || packed == nullptr) return fail(ST_INVALID, "sm100_pack_device: null pointer");
     const int st = check_shape(dtype, k, n, "sm100_pack_device");
     if (st != ST_OK) return st;
     const int64_t total = n * (k / block_elems(dtype));
+    if (first < 0 || count < 0 || first + count > total) return fail(ST_INVALID, "sm100_pack_device: block range outside the tensor");
+    if (count == 0) return ST_OK;
     const Planes P = planes_for(dtype, total);
     const int threads = 128;
-    int64_t blocks = (total + threads - 1) / threads;
+    int64_t blocks = (count + threads - 1) / threads;
     const int64_t cap = (int64_t) sm_count() * 16;
     if (blocks > cap) blocks = cap;
-    return launch(pack_kernel, dim3((unsigned) blocks), dim3(threads), 0, (cudaStream_t) s, dtype, P, total,
+    return launch(pack_kernel, dim3((unsigned) blocks), dim3(threads), 0, (cudaStream_t) s, dtype, P, first, count,
                   block_bytes(dtype), (const uint8_t *) natural, (uint8_t *) packed, to_packed);
 }
 
 int sm100_pack_device(sm100_stream_t s, int dtype, int64_t k, int64_t n, const void * natural, void * packed) {
-    return pack_device(s, dtype, k, n, natural, packed, 1);
+    return pack_device(s, dtype, k, n, 0, n * (k / (block_elems(dtype) > 0 ? block_elems(dtype) : 1)), natural, packed, 1);
 }
 
 int sm100_unpack_device(sm100_stream_t s, int dtype, int64_t k, int64_t n, const void * packed, void * natural) {
-    return pack_device(s, dtype, k, n, natural, const_cast<void *>(packed), 0);
+    return pack_device(s, dtype, k, n, 0, n * (k / (block_elems(dtype) > 0 ? block_elems(dtype) : 1)), natural, const_cast<void *>(packed), 0);
+}
+
+int sm100_pack_device_range(sm100_stream_t s, int dtype, int64_t k, int64_t n, int64_t first_block, int64_t block_count, void * natural_chunk,
+                            void * packed, int to_packed) {
+    return pack_device(s, dtype, k, n, first_block, block_count, natural_chunk, packed, to_packed);
 }
 
 }  // extern "C"

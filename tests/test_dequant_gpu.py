@@ -20,7 +20,7 @@ def device_get_rows(capi, stream, dtype, layout, table: np.ndarray, k: int, ids:
     tb = U.to_device(capi, stream, img)
     ib = U.to_device(capi, stream, ids.astype(np.int32))
     ob, optr = U.guarded_output(capi, stream, ids.size * k)
-    capi.check(capi.lib().sm100_get_rows(stream.handle, dtype, layout, tb.at(), k, n, ib.at(), ids.size, C.c_void_p(optr), k), "get_rows")
+    capi.check(capi.lib().sm100_get_rows(stream.handle, dtype, layout, tb.at(), 0, k, n, ib.at(), ids.size, C.c_void_p(optr), k), "get_rows")
     stream.sync()
     out = U.read_guarded(capi, stream, ob, ids.size * k).reshape(ids.size, k).copy()
     for b in (tb, ib, ob):
