@@ -169,8 +169,9 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     def timed_graph(m: int, only_shape, steps: int, warmup: int):
         launches0 = L.sm100_launch_count()
         with capi.Graph(stream) as g:
-            per_step = enqueue_step(m, only_shape)
-        assert L.sm100_launch_count() - launches0 == per_step
+            matvecs = enqueue_step(m, only_shape)
+        per_step = int(L.sm100_launch_count() - launches0)   # kernels of this library captured for one step
+        assert per_step >= matvecs
         for _ in range(warmup):
             g.launch()
         stream.sync()

@@ -28,6 +28,16 @@ def build() -> bool:
     return os.path.exists(SO)
 
 
+EXAMPLE = os.path.join(_HERE, "_ref", "standalone_matmul")
+
+
+def build_example() -> bool:
+    """The reference's unchanged standalone_matmul example linked against the plugin; True if the binary exists."""
+    if os.path.isdir(os.path.join(REFERENCE_DIR, "examples")):
+        subprocess.run(["make", "-C", _HERE, "example", f"REF={REFERENCE_DIR}"], check=True, capture_output=True)
+    return os.path.exists(EXAMPLE)
+
+
 def available() -> bool:
     return os.path.exists(SO)
 

@@ -20,6 +20,10 @@
 
 namespace sm100 {
 
+int matvec_q4k_tiles(cudaStream_t s, const void * w, int64_t k, int64_t n, const float * x, int64_t ldx, int64_t m, float * y, int64_t ldy,
+                     bool * handled);
+int q4k_pass_width(int64_t k, int64_t m);
+
 // ---- natural-layout loading: assemble the packed-unit registers from GGUF blocks -----------------
 
 __device__ __forceinline__ uint32_t ld_u32_any(const uint8_t * p) {
@@ -315,13 +319,13 @@ __global__ void __launch_bounds__(MAXT, MINB) matvec_wide(const uint8_t * __rest
 template <class U, int M, bool PACKED>
 __global__ void __launch_bounds__(256) matvec_rows(const uint8_t * __restrict__ w, Planes P, int64_t w_row_stride,
                                                    const float * __restrict__ x, int64_t ldx, float * __restrict__ y, int64_t ldy,
-                                                   int n_rows, int units_per_row) {
+                                                   int row_begin, int n_rows, int units_per_row) {
     pdl_wait();
     pdl_launch_dependents();
     const int lane = threadIdx.x & 31;
     const int warps = blockDim.x >> 5;
     const int64_t bpr = units_per_row / U::UNITS_PER_BLOCK;
-    for (int r = blockIdx.x * warps + (threadIdx.x >> 5); r < n_rows; r += gridDim.x * warps) {
+    for (int r = row_begin + blockIdx.x * warps + (threadIdx.x >> 5); r < n_rows; r += gridDim.x * warps) {
         float acc[M];
 #pragma unroll
         for (int m = 0; m < M; ++m) acc[m] = 0.f;
@@ -384,8 +388,7 @@ static int launch_stream(cudaStream_t s, const void * w, int64_t k, int64_t n, c
     int rp = 1;
     while ((rp * 2) * upr <= U::MAX_THREADS) rp *= 2;
     const int threads = rp * upr;
-    const int64_t total_blocks = n * (k / block_elems(U::DTYPE));
-    const Planes P = planes_for(U::DTYPE, total_blocks);
+    const Planes P = planes_for(U::DTYPE, n, k);
     // one wave: spread the rows over all SMs, rows per CTA a multiple of the rows per pass
     const int ctas_per_sm = threads <= 256 ? 2 : 1;
     const int64_t slots = (int64_t) sm_count() * ctas_per_sm;
@@ -413,7 +416,7 @@ static int launch_wide(cudaStream_t s, const void * w, int64_t k, int64_t n, con
     // at two CTAs per SM (64 activations + 4 rows of quants in flight do not fit in 128)
     const int rp = upr >= target_threads ? 1 : target_threads / upr;
     const int threads = rp * upr;
-    const Planes P = planes_for(W::DTYPE, n * (k / block_elems(W::DTYPE)));
+    const Planes P = planes_for(W::DTYPE, n, k);
     const int64_t slots = (int64_t) sm_count() * ctas_per_sm;
     int64_t rows_per_cta = (n + slots - 1) / slots;
     rows_per_cta = (rows_per_cta + rp - 1) / rp * rp;
@@ -433,18 +436,18 @@ static bool wide_ok(int64_t k, int64_t m) {
 
 template <class U, bool PACKED>
 static int launch_rows(cudaStream_t s, const void * w, int64_t w_row_stride, int64_t k, int64_t n, const float * x, int64_t ldx,
-                       int64_t m, float * y, int64_t ldy) {
+                       int64_t m, float * y, int64_t ldy, int64_t row_begin = 0) {
     const int upr = (int) (k / U::WEIGHTS);
     Planes P = {};
-    if (PACKED) P = planes_for(U::DTYPE, n * (k / block_elems(U::DTYPE)));
+    if (PACKED) P = planes_for(U::DTYPE, n, k);
     const int threads = 256, warps = threads / 32;
-    int64_t grid = (n + warps - 1) / warps;
+    int64_t grid = (n - row_begin + warps - 1) / warps;
     const int64_t cap = (int64_t) sm_count() * 8;
     if (grid > cap) grid = cap;
     const dim3 g((unsigned) grid), b(threads);
     const uint8_t * wp = (const uint8_t *) w;
 #define SM100_ROWS_CASE(MM) \
-    case MM: return launch(matvec_rows<U, MM, PACKED>, g, b, 0, s, wp, P, w_row_stride, x, ldx, y, ldy, (int) n, upr);
+    case MM: return launch(matvec_rows<U, MM, PACKED>, g, b, 0, s, wp, P, w_row_stride, x, ldx, y, ldy, (int) row_begin, (int) n, upr);
     switch (m) {
         SM100_ROWS_CASE(1) SM100_ROWS_CASE(2) SM100_ROWS_CASE(3) SM100_ROWS_CASE(4)
         SM100_ROWS_CASE(5) SM100_ROWS_CASE(6) SM100_ROWS_CASE(7) SM100_ROWS_CASE(8)
@@ -480,10 +483,31 @@ int matvec(cudaStream_t s, int dtype, int layout, const void * w, int64_t w_row_
     if (layout == LAYOUT_PACKED && !is_quant(dtype)) return fail(ST_UNSUPPORTED, "mul_mat: only quantized weights have a packed layout");
     if (layout != LAYOUT_PACKED && layout != LAYOUT_NATURAL) return fail(ST_INVALID, "mul_mat: unknown layout %d", layout);
     if (is_quant(dtype) && !x_aligned) return fail(ST_UNSUPPORTED, "mul_mat: activations must be 16-byte aligned (columns too)");
+    static const int use_mma = env_int("SM100_Q4K_MMA", 1);
+    if (use_mma && layout == LAYOUT_PACKED && dtype == DT_Q4_K && x_aligned) {
+        // tensor-core tile kernel over the full 16-row tiles, up to 4 columns per pass; leftover rows take the row kernel
+        bool all = true;
+        int64_t width = k % 256 == 0 ? q4k_pass_width(k, m) : 0;
+        if (width == 0) { all = false; width = 4; }
+        for (int64_t c0 = 0; c0 < m && all; c0 += width) {
+            const int64_t mm = m - c0 < width ? m - c0 : width;
+            bool handled = false;
+            const int st = matvec_q4k_tiles(s, w, k, n, x + c0 * ldx, ldx, mm, y + c0 * ldy, ldy, &handled);
+            if (st != ST_OK) return st;
+            if (!handled) {
+                if (c0 != 0) return fail(ST_BACKEND, "mul_mat: the Q4_K tile kernel accepted the first column pass but not a later one");
+                all = false;
+            }
+        }
+        if (all) {
+            const int64_t full = (n / 16) * 16;
+            if (full < n) return launch_rows<UnitQ4K, true>(s, w, 0, k, n, x, ldx, m, y, ldy, full);
+            return ST_OK;
+        }
+    }
     static const int use_wide = env_int("SM100_MV_WIDE", 1);
     if (use_wide && layout == LAYOUT_PACKED) {
         switch (dtype) {
-            case DT_Q4_K: if (wide_ok<WideQ4K>(k, m)) return launch_wide<WideQ4K>(s, w, k, n, x, y); break;
             case DT_Q6_K: if (wide_ok<WideQ6K>(k, m)) return launch_wide<WideQ6K>(s, w, k, n, x, y); break;
             case DT_Q4_0: if (wide_ok<WideQ40>(k, m)) return launch_wide<WideQ40>(s, w, k, n, x, y); break;
             case DT_Q8_0: if (wide_ok<WideQ80>(k, m)) return launch_wide<WideQ80>(s, w, k, n, x, y); break;

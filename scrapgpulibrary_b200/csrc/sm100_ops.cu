@@ -72,7 +72,7 @@ __device__ float dequant_packed(int dtype, const uint8_t * base, const Planes & 
             const int sb = j >> 5, p = sb >> 1;
             const uint32_t f = (uint32_t) h[4 + 3 * p] | ((uint32_t) h[5 + 3 * p] << 8) | ((uint32_t) h[6 + 3 * p] << 16);
             const int sc = (f >> ((sb & 1) * 12)) & 63, mn = (f >> ((sb & 1) * 12 + 6)) & 63;
-            const int byte = base[P.off[0] + t * 128 + (j >> 6) * 32 + (j & 31)];
+            const int byte = base[P.off[0] + q4k_q_offset(P, t / P.blocks_per_row, t % P.blocks_per_row, (j >> 6) * 32 + (j & 31))];
             const int q = (j & 32) ? (byte >> 4) : (byte & 15);
             return __fsub_rn(__fmul_rn(__fmul_rn(d, (float) sc), (float) q), __fmul_rn(dmin, (float) mn));
         }
@@ -339,7 +339,7 @@ int sm100_get_rows(sm100_stream_t s, int dtype, int layout, const void * table, 
     if (k <= 0 || table_rows <= 0 || n_ids <= 0 || k % be != 0) return fail(ST_INVALID, "get_rows: bad shape");
     if (layout == LAYOUT_PACKED && !is_quant(dtype)) return fail(ST_UNSUPPORTED, "get_rows: only quantized tables have a packed layout");
     Planes P = {};
-    if (layout == LAYOUT_PACKED) P = planes_for(dtype, table_rows * (k / be));
+    if (layout == LAYOUT_PACKED) P = planes_for(dtype, table_rows, k);
     const int64_t row_stride = table_row_stride != 0 && layout != LAYOUT_PACKED ? table_row_stride : k / be * block_bytes(dtype);
     const int threads = 256;
     unsigned gx = (unsigned) ((k + threads - 1) / threads);

@@ -12,9 +12,9 @@ namespace sm100 {
 // One block, natural -> packed.  `dst` is the tensor base of the packed image, t the block number.
 __host__ __device__ inline void pack_block(int dtype, const Planes & P, int64_t t, const uint8_t * blk, uint8_t * dst) {
     if (dtype == DT_Q4_K) {
-        uint8_t * q = dst + P.off[0] + t * 128;
         uint8_t * h = dst + P.off[1] + t * 16;
-        for (int i = 0; i < 128; ++i) q[i] = blk[16 + i];
+        const int64_t row = t / P.blocks_per_row, b = t % P.blocks_per_row;
+        for (int i = 0; i < 128; ++i) dst[P.off[0] + q4k_q_offset(P, row, b, i)] = blk[16 + i];
         h[0] = blk[0]; h[1] = blk[1]; h[2] = blk[2]; h[3] = blk[3];
         const uint8_t * s = blk + 4;
         for (int p = 0; p < 4; ++p) {
@@ -69,9 +69,9 @@ __host__ __device__ inline void pack_block(int dtype, const Planes & P, int64_t 
 // One block, packed -> natural.
 __host__ __device__ inline void unpack_block(int dtype, const Planes & P, int64_t t, const uint8_t * src, uint8_t * blk) {
     if (dtype == DT_Q4_K) {
-        const uint8_t * q = src + P.off[0] + t * 128;
         const uint8_t * h = src + P.off[1] + t * 16;
-        for (int i = 0; i < 128; ++i) blk[16 + i] = q[i];
+        const int64_t row = t / P.blocks_per_row, b = t % P.blocks_per_row;
+        for (int i = 0; i < 128; ++i) blk[16 + i] = src[P.off[0] + q4k_q_offset(P, row, b, i)];
         blk[0] = h[0]; blk[1] = h[1]; blk[2] = h[2]; blk[3] = h[3];
         uint32_t sc[8], mn[8];
         for (int p = 0; p < 4; ++p) {
@@ -153,7 +153,7 @@ int sm100_pack(int dtype, int64_t k, int64_t n, const void * natural, void * pac
     const int st = check_shape(dtype, k, n, "sm100_pack");
     if (st != ST_OK) return st;
     const int64_t total = n * (k / block_elems(dtype));
-    const Planes P = planes_for(dtype, total);
+    const Planes P = planes_for(dtype, n, k);
     const int bb = block_bytes(dtype);
     for (int64_t t = 0; t < total; ++t) pack_block(dtype, P, t, (const uint8_t *) natural + t * bb, (uint8_t *) packed);
     return ST_OK;
@@ -164,7 +164,7 @@ int sm100_unpack(int dtype, int64_t k, int64_t n, const void * packed, void * na
     const int st = check_shape(dtype, k, n, "sm100_unpack");
     if (st != ST_OK) return st;
     const int64_t total = n * (k / block_elems(dtype));
-    const Planes P = planes_for(dtype, total);
+    const Planes P = planes_for(dtype, n, k);
     const int bb = block_bytes(dtype);
     for (int64_t t = 0; t < total; ++t) unpack_block(dtype, P, t, (const uint8_t *) packed, (uint8_t *) natural + t * bb);
     return ST_OK;
@@ -178,7 +178,7 @@ static int pack_device(sm100_stream_t s, int dtype, int64_t k, int64_t n, int64_
     const int64_t total = n * (k / block_elems(dtype));
     if (first < 0 || count < 0 || first + count > total) return fail(ST_INVALID, "sm100_pack_device: block range outside the tensor");
     if (count == 0) return ST_OK;
-    const Planes P = planes_for(dtype, total);
+    const Planes P = planes_for(dtype, n, k);
     const int threads = 128;
     int64_t blocks = (count + threads - 1) / threads;
     const int64_t cap = (int64_t) sm_count() * 16;

@@ -42,7 +42,10 @@ struct UnitQ4K {
 
     __device__ static __forceinline__ void load(const uint8_t * base, const Planes & P, int64_t row, int64_t blocks_per_row, int cu, Data & d) {
         const int64_t t = row * blocks_per_row + (cu >> 3);
-        d.q = ldg_stream(base + P.off[0] + t * 128 + (cu & 7) * 16);
+        // the unit's 16 quant bytes are four words of the tile-ordered Q plane (one per lane slot t)
+        const uint8_t * q0 = base + P.off[0] + q4k_q_offset(P, row, cu >> 3, (cu & 7) * 16);
+        const int64_t step = row < (P.n_rows / 16) * 16 ? 16 : 4;
+        d.q = make_uint4(ldg_u32(q0), ldg_u32(q0 + step), ldg_u32(q0 + 2 * step), ldg_u32(q0 + 3 * step));
         d.h = __ldg((const uint4 *) (base + P.off[1] + t * 16));
     }
     // element index of the i-th activation this unit multiplies (i < 32: 16 low then 16 high)

@@ -41,46 +41,6 @@ __device__ __forceinline__ float half_bits_fast(uint32_t h) {
 __device__ __forceinline__ float small_uint_to_float(uint32_t v) { return __uint_as_float(v | 0x4B000000u) - 8388608.0f; }
 
 // ---------------------------------------------------------------------------------------------
-// Q4_K: 32 bytes = one pair of sub-blocks (32 low-nibble weights of sub-block 2p, 32 high-nibble weights
-// of sub-block 2p+1); 4 units per block.
-// ---------------------------------------------------------------------------------------------
-struct WideQ4K {
-    static constexpr int DTYPE = DT_Q4_K;
-    static constexpr int WEIGHTS = 64;
-    static constexpr int UNITS_PER_BLOCK = 4;
-    static constexpr int XSUMS = 2;
-    struct Data { uint4 a, b, h; };
-
-    __device__ static __forceinline__ void load(const uint8_t * base, const Planes & P, int64_t row, int64_t bpr, int cu, Data & d) {
-        const int64_t t = row * bpr + (cu >> 2);
-        ldg_stream32(base + P.off[0] + t * 128 + (cu & 3) * 32, d.a, d.b);
-        d.h = __ldg((const uint4 *) (base + P.off[1] + t * 16));
-    }
-    // float4 group g (0..15) of the unit's activations: groups 0..7 low sub-block, 8..15 high sub-block
-    __device__ static __forceinline__ int64_t x_index(int cu, int g) { return (int64_t) (cu >> 2) * 256 + (cu & 3) * 64 + g * 4; }
-    __device__ static __forceinline__ int sum_slot(int g) { return g >> 3; }
-
-    __device__ static __forceinline__ float dot(const Data & d, int cu, const float2 * x, const float * sums) {
-        const uint32_t w[8] = {d.a.x, d.a.y, d.a.z, d.a.w, d.b.x, d.b.y, d.b.z, d.b.w};
-        float2 l0 = make_float2(-128.f * sums[0], 0.f), l1 = make_float2(0.f, 0.f);
-        float2 h0 = make_float2(-128.f * sums[1], 0.f), h1 = make_float2(0.f, 0.f);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            const uint32_t wl = w[i] & 0x0F0F0F0Fu, wh = (w[i] >> 4) & 0x0F0F0F0Fu;
-            fma_word(wl, x + 2 * i, l0, l1);
-            fma_word(wh, x + 16 + 2 * i, h0, h1);
-        }
-        const float lo = (l0.x + l0.y) + (l1.x + l1.y), hi = (h0.x + h0.y) + (h1.x + h1.y);
-        const float dd = half_bits_fast(d.h.x & 0xFFFFu), dmin = half_bits_fast(d.h.x >> 16);
-        const int p = cu & 3;
-        const uint32_t f = p == 0 ? d.h.y : p == 1 ? __funnelshift_r(d.h.y, d.h.z, 24) : p == 2 ? __funnelshift_r(d.h.z, d.h.w, 16) : (d.h.w >> 8);
-        const float s0 = small_uint_to_float(f & 63u), m0 = small_uint_to_float((f >> 6) & 63u);
-        const float s1 = small_uint_to_float((f >> 12) & 63u), m1 = small_uint_to_float((f >> 18) & 63u);
-        return dd * (s0 * lo + s1 * hi) - dmin * (m0 * sums[0] + m1 * sums[1]);
-    }
-};
-
-// ---------------------------------------------------------------------------------------------
 // Q4_0: 32 bytes = two blocks (low nibble i -> element i, high nibble -> element 16 + i of each block)
 // ---------------------------------------------------------------------------------------------
 struct WideQ40 {

@@ -1,0 +1,301 @@
+"""Layer-stack decode harness: a Qwen3-8B-shaped transformer decode step built from the backend's ops, one
+process per GPU, tensor-parallel over `torch.distributed`.
+
+The reference has no model runner of its own (models run through llama.cpp on top of its ggml adapter); the
+closest thing is examples/pipeline_mlp.c:124-300, which builds per-layer descriptors once and then issues one
+scrapgpu_op_execute per op and token.  This harness does the same for the decode step the benchmark names --
+GET_ROWS -> per layer { RMS_NORM_MUL -> Q/K/V MUL_MAT -> per-head q/k RMS_NORM_MUL -> ROPE -> SET_ROWS into the
+f32 KV cache -> causal GQA attention -> o MUL_MAT -> ADD_RMS_NORM_MUL -> gate/up MUL_MAT -> SwiGLU -> down
+MUL_MAT } -> ADD_RMS_NORM_MUL -> head MUL_MAT -> TOP_K(1) -- straight on the C ABI of libscrapgpu_sm100, with the
+whole step recorded once in a CUDA graph (the plan seat of the reference API) and replayed per token: position,
+token id and KV write index all live on the device.
+
+Tensor parallelism (new: the reference only splits layers across devices, docs/MULTI_GPU.md): weight rows are
+sharded column-parallel for Q/K/V/gate/up and the vocabulary head, row-parallel (K shards) for o and down with
+an all-reduce of the 4096-float partial after each, attention by KV head.  PyTorch supplies device memory, the
+stream, graph capture and the NCCL process group; every kernel on the path is this repository's.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import zlib
+from dataclasses import dataclass
+
+import numpy as np
+import torch
+
+from . import capi, synth
+
+Q4_K, Q6_K = 32, 33
+
+
+@dataclass
+class DecodeConfig:
+    """Defaults: Qwen3-8B shapes (36 layers, hidden 4096, 32 query / 8 KV heads of 128, FFN 12288, vocab 151936)."""
+    layers: int = 36
+    hidden: int = 4096
+    heads: int = 32
+    kv_heads: int = 8
+    head_dim: int = 128
+    ffn: int = 12288
+    vocab: int = 151936
+    n_ctx: int = 1152
+    start_pos: int = 1024
+    rope_base: float = 1e6
+    eps: float = 1e-6
+    qk_norm: bool = True
+
+    def more_bits(self, layer: int) -> bool:
+        """Which layers keep attn_v and ffn_down in Q6_K in a Q4_K_M mix: the published rule of llama.cpp's
+        quantizer (first and last eighth, and every third layer in between)."""
+        n = self.layers
+        return layer < n // 8 or layer >= 7 * n // 8 or (layer - n // 8) % 3 == 2
+
+
+def _dev(t: torch.Tensor) -> C.c_void_p:
+    return C.c_void_p(t.data_ptr())
+
+
+class Weight:
+    """A quantized weight matrix [K, N] resident on the device in the backend-packed layout."""
+
+    def __init__(self, model: "DecodeModel", dtype: int, natural: np.ndarray, k: int):
+        self.dtype, self.k, self.n = dtype, k, natural.shape[0]
+        nat = torch.from_numpy(np.ascontiguousarray(natural)).to(model.device)
+        self.data = torch.empty(nat.numel(), dtype=torch.uint8, device=model.device)
+        capi.check(model.L.sm100_pack_device(model.stream, dtype, k, self.n, _dev(nat), _dev(self.data)), "pack_device")
+        torch.cuda.synchronize(model.device)
+        self.nbytes = nat.numel()
+
+
+class DecodeModel:
+    def __init__(self, cfg: DecodeConfig, rank: int = 0, world: int = 1, device_index: int = 0, seed: int = 0x5CA9,
+                 weights: dict | None = None, allreduce=None):
+        """weights: optional dict name -> (dtype, natural uint8 [N_global, row_bytes], K_global) with GLOBAL matrices
+        (sharded here); otherwise seeded synthetic shards are generated per rank.  allreduce / allgather: callables
+        on torch tensors (default: torch.distributed when world > 1)."""
+        assert cfg.heads % cfg.kv_heads == 0 and cfg.kv_heads % world == 0 and cfg.ffn % (256 * world) == 0
+        self.cfg, self.rank, self.world = cfg, rank, world
+        self.device = torch.device("cuda", device_index)
+        torch.cuda.set_device(self.device)
+        self.L = capi.lib()
+        capi.check(self.L.sm100_set_device(device_index), "set_device")
+        self.tstream = torch.cuda.Stream(self.device)
+        self.stream = C.c_void_p(self.tstream.cuda_stream)
+        self.allreduce = allreduce
+        c = cfg
+        self.hq, self.hkv = c.heads // world, c.kv_heads // world
+        self.q_dim, self.kv_dim, self.ffn = self.hq * c.head_dim, self.hkv * c.head_dim, c.ffn // world
+        self.vocab_shard = -(-c.vocab // world)
+        self.vocab_lo = min(c.vocab, rank * self.vocab_shard)
+        self.vocab_n = max(0, min(c.vocab, self.vocab_lo + self.vocab_shard) - self.vocab_lo)
+        self.weight_bytes = 0
+        self._base = {}
+        f32 = dict(dtype=torch.float32, device=self.device)
+        with torch.cuda.stream(self.tstream):
+            self.embed = self._weight("embed", Q4_K, c.vocab, c.hidden, weights, seed, shard=None)
+            self.layers = []
+            rng = np.random.default_rng(seed + 17)
+            for i in range(c.layers):
+                vdt = Q6_K if c.more_bits(i) else Q4_K
+                lw = {
+                    "attn_norm": torch.from_numpy(self._norm_w(weights, f"l{i}.attn_norm", c.hidden, rng)).to(self.device),
+                    "ffn_norm": torch.from_numpy(self._norm_w(weights, f"l{i}.ffn_norm", c.hidden, rng)).to(self.device),
+                    "q_norm": torch.from_numpy(self._norm_w(weights, f"l{i}.q_norm", c.head_dim, rng)).to(self.device),
+                    "k_norm": torch.from_numpy(self._norm_w(weights, f"l{i}.k_norm", c.head_dim, rng)).to(self.device),
+                    "wq": self._weight(f"l{i}.wq", Q4_K, c.heads * c.head_dim, c.hidden, weights, seed + i, shard=("rows", self.hq * c.head_dim)),
+                    "wk": self._weight(f"l{i}.wk", Q4_K, c.kv_heads * c.head_dim, c.hidden, weights, seed + i, shard=("rows", self.hkv * c.head_dim)),
+                    "wv": self._weight(f"l{i}.wv", vdt, c.kv_heads * c.head_dim, c.hidden, weights, seed + i, shard=("rows", self.hkv * c.head_dim)),
+                    "wo": self._weight(f"l{i}.wo", Q4_K, c.hidden, c.heads * c.head_dim, weights, seed + i, shard=("cols", self.q_dim)),
+                    "wgate": self._weight(f"l{i}.wgate", Q4_K, c.ffn, c.hidden, weights, seed + i, shard=("rows", self.ffn)),
+                    "wup": self._weight(f"l{i}.wup", Q4_K, c.ffn, c.hidden, weights, seed + i, shard=("rows", self.ffn)),
+                    "wdown": self._weight(f"l{i}.wdown", vdt, c.hidden, c.ffn, weights, seed + i, shard=("cols", self.ffn)),
+                    "k_cache": torch.zeros(self.hkv, c.n_ctx, c.head_dim, **f32),
+                    "v_cache": torch.zeros(self.hkv, c.n_ctx, c.head_dim, **f32),
+                }
+                self.layers.append(lw)
+            self.out_norm = torch.from_numpy(self._norm_w(weights, "out_norm", c.hidden, rng)).to(self.device)
+            self.head = self._weight("head", Q6_K, c.vocab, c.hidden, weights, seed + 999, shard=("rows", self.vocab_n, self.vocab_lo))
+            # activations
+            self.token = torch.zeros(1, dtype=torch.int32, device=self.device)
+            self.pos = torch.full((1,), c.start_pos, dtype=torch.int32, device=self.device)
+            self.x = torch.zeros(c.hidden, **f32)          # residual stream
+            self.xn = torch.zeros(c.hidden, **f32)         # normalised
+            self.q = torch.zeros(self.q_dim, **f32)
+            self.k = torch.zeros(self.kv_dim, **f32)
+            self.v = torch.zeros(self.kv_dim, **f32)
+            self.att = torch.zeros(self.q_dim, **f32)
+            self.proj = torch.zeros(c.hidden, **f32)       # o / down output (partial under TP)
+            self.gate = torch.zeros(self.ffn, **f32)
+            self.up = torch.zeros(self.ffn, **f32)
+            self.act = torch.zeros(self.ffn, **f32)
+            self.logits = torch.zeros(max(1, self.vocab_n), **f32)
+            self.best = torch.zeros(1, dtype=torch.int32, device=self.device)
+            self.cand = torch.zeros(2, **f32)              # (best logit, global index) of this rank
+            self.cands = torch.zeros(world, 2, **f32)
+            positions = np.arange(c.n_ctx)
+            self.rope = torch.from_numpy(self._rope_table(positions)).to(self.device)
+            self.tokens_out = torch.zeros(4096, dtype=torch.int32, device=self.device)
+            self.step_index = torch.zeros(1, dtype=torch.int64, device=self.device)
+        torch.cuda.synchronize(self.device)
+        self.graph = None
+        self.kv_bytes_per_pos = 2 * 4 * c.head_dim * self.hkv * c.layers
+
+    # ---- construction helpers -------------------------------------------------------------------------
+    def _norm_w(self, weights, name, n, rng):
+        if weights is not None and name in weights:
+            return np.ascontiguousarray(weights[name], dtype=np.float32)
+        return (1.0 + 0.1 * rng.standard_normal(n)).astype(np.float32)
+
+    def _rope_table(self, positions) -> np.ndarray:
+        """(cos, sin) with the reference's recipe (src/core/ref/ops.cpp:559-601): sequential f32 products, libm."""
+        c = self.cfg
+        half = c.head_dim // 2
+        out = np.empty((len(positions), half, 2), np.float32)
+        ts = np.float32(np.power(np.float32(c.rope_base), np.float32(-2.0) / np.float32(c.head_dim), dtype=np.float32))
+        theta = positions.astype(np.float32)
+        import math
+        for j in range(half):
+            for i in range(len(positions)):
+                out[i, j, 0] = np.float32(math.cos(float(theta[i])))
+                out[i, j, 1] = np.float32(math.sin(float(theta[i])))
+            theta = (theta * ts).astype(np.float32)
+        return out
+
+    def _weight(self, name, dtype, n_global, k_global, weights, seed, shard):
+        """shard: None (replicated), ("rows", n_local[, lo]) or ("cols", k_local)."""
+        if weights is not None and name in weights:
+            dt, nat, kg = weights[name]
+            assert dt == dtype and kg == k_global
+            nat = np.asarray(nat)
+            if shard is None:
+                loc, k = nat, k_global
+            elif shard[0] == "rows":
+                lo = shard[2] if len(shard) > 2 else self.rank * shard[1]
+                loc, k = nat[lo:lo + shard[1]], k_global
+            else:
+                be, bb = (256, 144) if dtype == Q4_K else (256, 210)
+                b0 = self.rank * shard[1] // be
+                loc = nat.reshape(n_global, k_global // be, bb)[:, b0:b0 + shard[1] // be].reshape(n_global, -1)
+                k = shard[1]
+        else:
+            if shard is None:
+                n, k = n_global, k_global
+            elif shard[0] == "rows":
+                n, k = shard[1], k_global
+            else:
+                n, k = n_global, shard[1]
+            key = (dtype, n, k)
+            if key not in self._base:      # one synthetic matrix per (dtype, shape); layers use row rotations of it
+                self._base[key] = synth.quantized_matrix(dtype, seed * 31 + self.rank + len(self._base), min(n, 16384), k)
+            base = self._base[key]
+            reps = -(-n // base.shape[0])
+            loc = np.roll(np.tile(base, (reps, 1))[:n], (zlib.crc32(name.encode()) % 977) * 3, axis=0) if n > 0 else base[:0]
+        if loc.shape[0] == 0:
+            return None
+        w = Weight(self, dtype, loc, k)
+        self.weight_bytes += w.nbytes
+        return w
+
+    # ---- one decode step ------------------------------------------------------------------------------
+    def _mm(self, w: Weight, x: torch.Tensor, y: torch.Tensor):
+        capi.check(self.L.sm100_mul_mat(self.stream, w.dtype, 1, _dev(w.data), 0, w.k, w.n, _dev(x), w.k, 1, _dev(y), w.n), "mul_mat")
+
+    def _reduce(self, t: torch.Tensor):
+        if self.world > 1:
+            if self.allreduce is not None:
+                self.allreduce(t)
+            else:
+                torch.distributed.all_reduce(t)
+
+    def enqueue_step(self):
+        """Enqueues one token on self.tstream (must be the current torch stream)."""
+        c, L, s = self.cfg, self.L, self.stream
+        chk = capi.check
+        chk(L.sm100_get_rows(s, self.embed.dtype, 1, _dev(self.embed.data), 0, c.hidden, c.vocab, _dev(self.token), 1, _dev(self.x), c.hidden), "get_rows")
+        scale = float(1.0 / np.sqrt(c.head_dim))
+        for i, lw in enumerate(self.layers):
+            if i == 0:
+                chk(L.sm100_rms_norm(s, _dev(self.x), None, _dev(lw["attn_norm"]), None, _dev(self.xn), c.hidden, 1, c.eps), "rms_norm")
+            else:   # residual add of the previous layer's FFN output fused with this norm
+                chk(L.sm100_rms_norm(s, _dev(self.x), _dev(self.proj), _dev(lw["attn_norm"]), _dev(self.x), _dev(self.xn), c.hidden, 1, c.eps), "add_rms_norm")
+            self._mm(lw["wq"], self.xn, self.q)
+            self._mm(lw["wk"], self.xn, self.k)
+            self._mm(lw["wv"], self.xn, self.v)
+            if c.qk_norm:
+                chk(L.sm100_rms_norm(s, _dev(self.q), None, _dev(lw["q_norm"]), None, _dev(self.q), c.head_dim, self.hq, c.eps), "q_norm")
+                chk(L.sm100_rms_norm(s, _dev(self.k), None, _dev(lw["k_norm"]), None, _dev(self.k), c.head_dim, self.hkv, c.eps), "k_norm")
+            chk(L.sm100_rope(s, _dev(self.q), _dev(self.pos), _dev(self.rope), 0, c.n_ctx, _dev(self.q), c.head_dim, self.hq, 1, c.head_dim, 1), "rope q")
+            chk(L.sm100_rope(s, _dev(self.k), _dev(self.pos), _dev(self.rope), 0, c.n_ctx, _dev(self.k), c.head_dim, self.hkv, 1, c.head_dim, 1), "rope k")
+            chk(L.sm100_set_rows(s, _dev(self.k), _dev(self.pos), _dev(lw["k_cache"]), c.head_dim, 1, self.hkv, c.n_ctx), "set_rows k")
+            chk(L.sm100_set_rows(s, _dev(self.v), _dev(self.pos), _dev(lw["v_cache"]), c.head_dim, 1, self.hkv, c.n_ctx), "set_rows v")
+            chk(L.sm100_attention(s, _dev(self.q), _dev(lw["k_cache"]), _dev(lw["v_cache"]), None, 1, _dev(self.att), c.head_dim, c.head_dim, 1, c.n_ctx,
+                                  self.hq, self.hkv, 1, 0, _dev(self.pos), scale), "attention")
+            self._mm(lw["wo"], self.att, self.proj)
+            self._reduce(self.proj)
+            chk(L.sm100_rms_norm(s, _dev(self.x), _dev(self.proj), _dev(lw["ffn_norm"]), _dev(self.x), _dev(self.xn), c.hidden, 1, c.eps), "add_rms_norm")
+            self._mm(lw["wgate"], self.xn, self.gate)
+            self._mm(lw["wup"], self.xn, self.up)
+            chk(L.sm100_swiglu(s, _dev(self.gate), _dev(self.up), _dev(self.act), self.ffn), "swiglu")
+            self._mm(lw["wdown"], self.act, self.proj)
+            self._reduce(self.proj)
+        chk(L.sm100_rms_norm(s, _dev(self.x), _dev(self.proj), _dev(self.out_norm), _dev(self.x), _dev(self.xn), c.hidden, 1, c.eps), "out_norm")
+        if self.head is not None:
+            self._mm(self.head, self.xn, self.logits)
+            chk(L.sm100_argmax(s, _dev(self.logits), self.vocab_n, _dev(self.best)), "argmax")
+        if self.world == 1:
+            self.token.copy_(self.best)
+        else:
+            # (best logit, global index) per rank; highest logit wins, lowest index on ties
+            self.cand[0] = self.logits[self.best.long()][0] if self.head is not None else float("-inf")
+            self.cand[1] = (self.best + self.vocab_lo).float()[0]
+            torch.distributed.all_gather_into_tensor(self.cands.view(-1), self.cand)
+            top = self.cands[:, 0].max()
+            idx = torch.where(self.cands[:, 0] == top, self.cands[:, 1], torch.full_like(self.cands[:, 1], 3e9)).min()
+            self.token.copy_(idx.to(torch.int32).view(1))
+        self.tokens_out.index_copy_(0, self.step_index, self.token)
+        self.step_index.add_(1)
+        self.pos.add_(1)
+
+    # ---- driving --------------------------------------------------------------------------------------
+    def reset(self, token: int, prefill_seed: int | None = None):
+        c = self.cfg
+        with torch.cuda.stream(self.tstream):
+            self.token.fill_(token)
+            self.pos.fill_(c.start_pos)
+            self.step_index.zero_()
+            if prefill_seed is not None:
+                g = torch.Generator(device="cpu").manual_seed(prefill_seed)
+                for i, lw in enumerate(self.layers):
+                    for name in ("k_cache", "v_cache"):
+                        full = torch.randn(c.kv_heads, c.start_pos, c.head_dim, generator=g)
+                        lw[name].zero_()
+                        lw[name][:, :c.start_pos] = full[self.rank * self.hkv:(self.rank + 1) * self.hkv].to(self.device)
+        torch.cuda.synchronize(self.device)
+
+    def capture(self):
+        """Records one step in a CUDA graph (the first eager step also creates the library's attention scratch)."""
+        with torch.cuda.stream(self.tstream):
+            self.enqueue_step()
+        torch.cuda.synchronize(self.device)
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph, stream=self.tstream):
+            self.enqueue_step()
+        torch.cuda.synchronize(self.device)
+
+    def run(self, steps: int):
+        with torch.cuda.stream(self.tstream):
+            for _ in range(steps):
+                if self.graph is not None:
+                    self.graph.replay()
+                else:
+                    self.enqueue_step()
+
+    def tokens(self, n: int) -> np.ndarray:
+        torch.cuda.synchronize(self.device)
+        return self.tokens_out[:n].cpu().numpy()
+
+    def bytes_per_token(self, pos: int) -> float:
+        """Algorithmic bytes one decode step must move on this rank: every weight once, the visible KV cache, the
+        embedding row."""
+        return float(self.weight_bytes - (self.embed.nbytes if self.embed is not None else 0) + self.kv_bytes_per_pos * (pos + 1) + self.cfg.hidden * 0.5625)

@@ -49,25 +49,49 @@ def test_q8_0_byte_positions():
         assert np.array_equal(p[32 * n + 2 * t:32 * n + 2 * t + 2], raw[t, :2])
 
 
+def q4k_q_offset(n_rows, bpr, r, b, i):
+    """Position of quant byte i of block b of row r in the tile-ordered Q plane (sm100_layout.h)."""
+    full = n_rows // 16 * 16
+    if r >= full:
+        return full * bpr * 128 + ((r - full) * bpr + b) * 128 + i
+    c = b * 4 + i // 32
+    i32 = i % 32
+    lane = (r % 8) * 4 + (i32 % 16) // 4
+    return ((r // 16) * bpr * 4 + c) * 512 + lane * 16 + ((r // 8) % 2) * 8 + (i32 // 16) * 4 + i32 % 4
+
+
 def test_q4_k_planes_and_scale_fields():
-    k, n = 256, 2
-    raw = np.random.default_rng(1).integers(0, 256, size=(n, 144), dtype=np.uint8)
+    k, n = 512, 19   # one full 16-row tile plus 3 leftover rows, two blocks per row
+    raw = np.random.default_rng(1).integers(0, 256, size=(n, 288), dtype=np.uint8)
     p = capi.pack(32, k, raw)
-    for t in range(n):
-        assert np.array_equal(p[128 * t:128 * t + 128], raw[t, 16:])
-        h = p[128 * n + 16 * t:128 * n + 16 * t + 16]
-        assert np.array_equal(h[:4], raw[t, :4])
-        s = raw[t, 4:16].astype(int)
-        for pair in range(4):
-            f = int(h[4 + 3 * pair]) | int(h[5 + 3 * pair]) << 8 | int(h[6 + 3 * pair]) << 16
-            for e in range(2):
-                j = 2 * pair + e
-                if j < 4:
-                    sc, mn = s[j] & 63, s[j + 4] & 63
-                else:
-                    sc = (s[j + 4] & 15) | ((s[j - 4] >> 6) << 4)
-                    mn = (s[j + 4] >> 4) | ((s[j] >> 6) << 4)
-                assert (f >> (12 * e)) & 63 == sc and (f >> (12 * e + 6)) & 63 == mn
+    blocks = raw.reshape(n, 2, 144)
+    T = n * 2
+    for r in range(n):
+        for b in range(2):
+            for i in (0, 1, 3, 4, 15, 16, 31, 32, 77, 127):
+                assert p[q4k_q_offset(n, 2, r, b, i)] == blocks[r, b, 16 + i], (r, b, i)
+            h = p[128 * T + 16 * (r * 2 + b):128 * T + 16 * (r * 2 + b) + 16]
+            assert np.array_equal(h[:4], blocks[r, b, :4])
+            s = blocks[r, b, 4:16].astype(int)
+            for pair in range(4):
+                f = int(h[4 + 3 * pair]) | int(h[5 + 3 * pair]) << 8 | int(h[6 + 3 * pair]) << 16
+                for e in range(2):
+                    j = 2 * pair + e
+                    if j < 4:
+                        sc, mn = s[j] & 63, s[j + 4] & 63
+                    else:
+                        sc = (s[j + 4] & 15) | ((s[j - 4] >> 6) << 4)
+                        mn = (s[j + 4] >> 4) | ((s[j] >> 6) << 4)
+                    assert (f >> (12 * e)) & 63 == sc and (f >> (12 * e + 6)) & 63 == mn
+    # a warp's tile: 512 contiguous bytes, lane 4g + t = row g bytes [4t, 4t+4), [16+4t, 16+4t+4), then row g + 8
+    tile = p[512 * 5:512 * 6]          # row tile 0, pair 5 = block 1, pair 1
+    for g in range(8):
+        for t in range(4):
+            lane = tile[(4 * g + t) * 16:(4 * g + t) * 16 + 16]
+            for half, row in ((0, g), (1, g + 8)):
+                qs = blocks[row, 1, 16 + 32:16 + 64]
+                assert np.array_equal(lane[8 * half:8 * half + 4], qs[4 * t:4 * t + 4])
+                assert np.array_equal(lane[8 * half + 4:8 * half + 8], qs[16 + 4 * t:16 + 4 * t + 4])
 
 
 def test_q6_k_planes():

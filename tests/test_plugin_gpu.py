@@ -441,3 +441,18 @@ def test_decode_attention_qwen_shape(both):
     want = attention_case(cpu, q, k, v, True, 1024 + t, scale, fused=False)
     fused = attention_case(gpu, q, k, v, True, 1024 + t, scale, fused=True)
     assert np.max(np.abs(fused - want)) <= 3e-4 and sgref.nmse(fused, want) <= 1e-6
+
+
+def test_unmodified_reference_example_runs_on_cuda_sm100():
+    """examples/standalone_matmul.c of the reference, compiled byte-for-byte unchanged (oracle/Makefile `example`) and
+    linked against the plugin through a one-function registration shim: Q4_0 weights uploaded with the packed-layout
+    tag, MUL_MAT on the device, NMSE against scrapgpu_ref_execute printed by the program itself."""
+    import re
+    import subprocess
+    if not os.path.exists(refapi.EXAMPLE):
+        pytest.fail("oracle/_ref/standalone_matmul is missing on the GPU box: run `make -C oracle example` where the reference is checked out")
+    r = subprocess.run([refapi.EXAMPLE], capture_output=True, text=True, timeout=120)
+    assert r.returncode == 0, r.stdout + r.stderr
+    assert "(b200)" in r.stdout, r.stdout
+    m = re.search(r"NMSE ([0-9.e+-]+)", r.stdout)
+    assert m and float(m.group(1)) <= 1e-6, r.stdout
