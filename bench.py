@@ -73,7 +73,7 @@ class ClockSampler:
     def start(self):
         q = "clocks.sm,clocks.max.sm,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
         try:
-            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.device}", f"--query-gpu={q}", "--format=csv,noheader,nounits", "-lms", "100"],
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.device}", f"--query-gpu={q}", "--format=csv,noheader,nounits", "-lms", "20"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             self.proc = None
@@ -217,6 +217,14 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     value = world * step_bytes / (ms_per_step * 1e-3) / 1e9
     launches_timed = per_step * args.steps
 
+    # ---- the other half of the metric: Qwen3-8B-shaped decode tok/s, tensor-parallel over all ranks ----
+    decode = None
+    if not args.no_decode and not args.quick:
+        try:
+            decode = run_decode(args, rank, world, local_rank, dist, stream_sync=stream.sync)
+        except Exception as e:  # the headline line must survive a failure of the secondary measurement
+            decode = {"error": f"{type(e).__name__}: {e}"[:300]}
+
     out = None
     if rank == 0:
         peak, peak_src = measured_peak_gbs()
@@ -224,6 +232,10 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         per_launch_us = ms_per_step * 1e3 / per_step
         achieved = per_launch_bytes / (per_launch_us * 1e-6) / 1e9
         detail = {}
+        if args.quick:
+            print(json.dumps({"metric": METRIC, "value": round(value, 1), "unit": "GB/s", "quick": True, "ms_per_step": round(ms_per_step, 4),
+                              "launches_per_step": per_step}), flush=True)
+            return None
         # per-shape and per-M figures (explanatory; the same graph-replay protocol, fewer steps)
         sub_steps = max(3, args.steps // 2)
         for s, (k, n) in enumerate(SHAPES):
@@ -276,11 +288,11 @@ def run_ours(args, rank: int, world: int, local_rank: int):
             "config": {"workload": f"Q4_K matvec sweep, M=1, Qwen3-8B projection shapes (K,N) in {SHAPES} x {layers} layers per GPU",
                        "launches_per_step": per_step, "bytes_per_step_per_gpu": int(step_bytes), "weights_layout": "backend-packed planes",
                        "l2": "inputs larger than L2 (pool %.2f GB per GPU, L2 126 MB)" % (step_bytes / 1e9), "timing": "CUDA events on the launching stream, one graph replay per step",
-                       "setup_s": round(setup_s, 1), "detail": detail},
+                       "setup_s": round(setup_s, 1), "detail": detail, "decode": decode},
             "gpu_launches": int(launches_timed),
             "e2e": {"value": round(world * step_bytes / (e2e_ms * 1e-3) / 1e9, 1), "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "ms_per_step": round(e2e_ms, 4), "note": "host activations in / host results out per matvec, weights resident"},
-            "roofline": {"bound": "hbm", "kernel": "matvec_stream<UnitQ4K>", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
+            "roofline": {"bound": "hbm", "kernel": "matvec_q4k_mma<1,true>", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
                          "frac": round(achieved / peak, 4), "peak_source": peak_src, "bytes_per_launch": round(per_launch_bytes, 1),
                          "us_per_launch": round(per_launch_us, 3), "traffic": None},
             "cpu_baseline": cpu,
@@ -290,6 +302,48 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         dist.barrier()
         dist.destroy_process_group()
     return out
+
+
+def run_decode(args, rank: int, world: int, local_rank: int, dist, stream_sync):
+    """Qwen3-8B-shaped layer-stack decode (BASELINE config 5): 36 layers, hidden 4096, 32/8 heads of 128, FFN 12288,
+    vocab 151936, random Q4_K_M-style weights, f32 KV cache pre-filled to position 1024, batch 1, greedy; one CUDA
+    graph per token, tensor-parallel over `world` ranks with NCCL all-reduces.  Returns tok/s and the roofline view."""
+    import torch
+    from scrapgpulibrary_b200.decode import DecodeConfig, DecodeModel
+    cfg = DecodeConfig()
+    steps = args.decode_steps
+    model = DecodeModel(cfg, rank=rank, world=world, device_index=local_rank, seed=0x5CA9)
+    model.reset(token=1234, prefill_seed=7)
+    model.capture()
+    model.reset(token=1234, prefill_seed=None)
+    model.run(8)                                   # warm-up tokens
+    torch.cuda.synchronize()
+    model.reset(token=1234, prefill_seed=None)
+    if dist is not None:
+        dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with torch.cuda.stream(model.tstream):
+        e0.record()
+    model.run(steps)
+    with torch.cuda.stream(model.tstream):
+        e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1)
+    if dist is not None:
+        t = torch.tensor([ms], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    tokens = model.tokens(steps)
+    peak, _ = measured_peak_gbs()
+    mid_pos = cfg.start_pos + steps // 2
+    bytes_tok = model.bytes_per_token(mid_pos)      # this rank's share
+    tok_s = steps / (ms * 1e-3)
+    return {"tok_s": round(tok_s, 1), "ms_per_token": round(ms / steps, 4), "steps": steps, "tp": world,
+            "bytes_per_token_per_gpu": int(bytes_tok), "hbm_gbps_per_gpu": round(bytes_tok * tok_s / 1e9, 1),
+            "hbm_frac_of_measured": round(bytes_tok * tok_s / 1e9 / peak, 4),
+            "model": "Qwen3-8B shape, random Q4_K_M-style weights (Q6_K for attn_v / ffn_down in the more-bits layers and the head)",
+            "first_tokens": [int(x) for x in tokens[:4]]}
 
 
 def cpu_baseline(pool, threads: int, repeats: int):
@@ -345,10 +399,13 @@ def run_reference(args, rank: int, world: int):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=300)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--layers", type=int, default=36)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--decode-steps", type=int, default=128)
+    ap.add_argument("--no-decode", action="store_true", help="skip the layer-stack decode measurement")
+    ap.add_argument("--quick", action="store_true", help="headline sweep only (no per-shape detail, e2e, CPU baseline, decode): for profiler runs")
     args = ap.parse_args()
     args.warmup = max(3, args.warmup) if args.impl == "ours" else args.warmup
     rank = int(os.environ.get("RANK", "0"))

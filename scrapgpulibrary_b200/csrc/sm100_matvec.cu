@@ -149,12 +149,12 @@ template <> struct Natural<UnitF16> {
 // ---- activations of one unit into registers ---------------------------------------------------------
 
 template <class U>
-__device__ __forceinline__ void load_x_unit(const float * __restrict__ x, int cu, float (&xr)[U::WEIGHTS], float (&sums)[U::XSUMS]) {
+__device__ __forceinline__ void load_x_unit(const float * x, int cu, float (&xr)[U::WEIGHTS], float (&sums)[U::XSUMS]) {
 #pragma unroll
     for (int s = 0; s < U::XSUMS; ++s) sums[s] = 0.f;
 #pragma unroll
     for (int g = 0; g < U::WEIGHTS / 4; ++g) {
-        const float4 v = *reinterpret_cast<const float4 *>(x + U::x_index(cu, 4 * g));
+        const float4 v = __ldcg(reinterpret_cast<const float4 *>(x + U::x_index(cu, 4 * g)));   // coherent load, see matvec_wide
         xr[4 * g + 0] = v.x; xr[4 * g + 1] = v.y; xr[4 * g + 2] = v.z; xr[4 * g + 3] = v.w;
         sums[U::sum_slot(4 * g)] += (v.x + v.y) + (v.z + v.w);
     }
@@ -163,8 +163,8 @@ __device__ __forceinline__ void load_x_unit(const float * __restrict__ x, int cu
 // ---- kernel A: packed, M = 1, register-resident activations ---------------------------------------
 
 template <class U>
-__global__ void __launch_bounds__(U::MAX_THREADS) matvec_stream(const uint8_t * __restrict__ w, Planes P, const float * __restrict__ x,
-                                                     float * __restrict__ y, int n_rows, int units_per_row, int rows_per_cta) {
+__global__ void __launch_bounds__(U::MAX_THREADS) matvec_stream(const uint8_t * __restrict__ w, Planes P, const float * x,
+                                                     float * y, int n_rows, int units_per_row, int rows_per_cta) {
     constexpr int STREAM_RIF = U::ROWS_IN_FLIGHT;
     extern __shared__ float red[];  // [STREAM_RIF][warps]
     const int tid = threadIdx.x;
@@ -251,8 +251,8 @@ __device__ __forceinline__ float transpose_reduce<4>(const float (&v)[4], int la
 }
 
 template <class W, int ROWS, int MAXT, int MINB>
-__global__ void __launch_bounds__(MAXT, MINB) matvec_wide(const uint8_t * __restrict__ w, Planes P, const float * __restrict__ x,
-                                                          float * __restrict__ y, int n_rows, int units_per_row, int rows_per_cta) {
+__global__ void __launch_bounds__(MAXT, MINB) matvec_wide(const uint8_t * __restrict__ w, Planes P, const float * x,
+                                                          float * y, int n_rows, int units_per_row, int rows_per_cta) {
     static_assert(ROWS == 4, "the transposing reduction is written for 4 rows in flight");
     extern __shared__ float red[];  // [ROWS][warps]
     const int tid = threadIdx.x, lane = tid & 31;
@@ -278,7 +278,7 @@ __global__ void __launch_bounds__(MAXT, MINB) matvec_wide(const uint8_t * __rest
     for (int s = 0; s < W::XSUMS; ++s) sums[s] = 0.f;
 #pragma unroll
     for (int g = 0; g < W::WEIGHTS / 4; ++g) {
-        const float4 v = __ldg(reinterpret_cast<const float4 *>(x + W::x_index(cu, g)));
+        const float4 v = __ldcg(reinterpret_cast<const float4 *>(x + W::x_index(cu, g)));   // coherent: x may come from the kernel we overlap with
         xr[2 * g] = make_float2(v.x, v.y);
         xr[2 * g + 1] = make_float2(v.z, v.w);
         sums[W::sum_slot(g)] += (v.x + v.y) + (v.z + v.w);
@@ -318,7 +318,7 @@ __global__ void __launch_bounds__(MAXT, MINB) matvec_wide(const uint8_t * __rest
 
 template <class U, int M, bool PACKED>
 __global__ void __launch_bounds__(256) matvec_rows(const uint8_t * __restrict__ w, Planes P, int64_t w_row_stride,
-                                                   const float * __restrict__ x, int64_t ldx, float * __restrict__ y, int64_t ldy,
+                                                   const float * x, int64_t ldx, float * y, int64_t ldy,
                                                    int row_begin, int n_rows, int units_per_row) {
     pdl_wait();
     pdl_launch_dependents();
@@ -356,8 +356,8 @@ __global__ void __launch_bounds__(256) matvec_rows(const uint8_t * __restrict__ 
 // scalar tail for rows whose K is not a whole number of units or whose x is not 16-byte aligned
 // (F32 / F16 weights only; quantized rows are whole blocks by contract)
 template <int DT>
-__global__ void matvec_scalar(const uint8_t * __restrict__ w, int64_t w_row_stride, const float * __restrict__ x, int64_t ldx,
-                              float * __restrict__ y, int64_t ldy, int n_rows, int k, int m_cols) {
+__global__ void matvec_scalar(const uint8_t * __restrict__ w, int64_t w_row_stride, const float * x, int64_t ldx,
+                              float * y, int64_t ldy, int n_rows, int k, int m_cols) {
     pdl_wait();
     pdl_launch_dependents();
     const int lane = threadIdx.x & 31;
@@ -370,7 +370,7 @@ __global__ void matvec_scalar(const uint8_t * __restrict__ w, int64_t w_row_stri
                 float wv;
                 if (DT == DT_F32) wv = __ldg((const float *) row + i);
                 else wv = __half2float(__ldg((const __half *) row + i));
-                acc = fmaf(wv, x[(int64_t) m * ldx + i], acc);
+                acc = fmaf(wv, __ldcg(x + (int64_t) m * ldx + i), acc);
             }
 #pragma unroll
             for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);

@@ -146,7 +146,7 @@ __global__ void __launch_bounds__(Q4K_THREADS, 1) matvec_q4k_mma(Q4KArgs p) {
 #pragma unroll
         for (int m = 0; m < 4; ++m) {
             if (m < M) {
-                const float4 v = *reinterpret_cast<const float4 *>(p.x + (int64_t) m * p.ldx + (int64_t) item * 4);
+                const float4 v = __ldcg(reinterpret_cast<const float4 *>(p.x + (int64_t) m * p.ldx + (int64_t) item * 4));   // coherent: the producer may still be running when this kernel starts
                 // k-slots of the fragment: bytes (0, 2) -> b0b1, bytes (1, 3) -> b2b3
                 const __half2 h02 = __floats2half2_rn(v.x, v.z), h13 = __floats2half2_rn(v.y, v.w);
                 const float2 f02 = __half22float2(h02), f13 = __half22float2(h13);

@@ -8,6 +8,11 @@
 
 namespace sm100 {
 
+// Activation pointers are deliberately NOT __restrict__ / __ldg: kernels are launched with programmatic dependent
+// launch, so a kernel may start while the kernel that produces its inputs is still running.  The non-coherent
+// read-only path (ld.global.nc) is only valid for data that does not change during the kernel's lifetime, which
+// under early launch includes the producer's writes; only weights (constant across the stream) use it.
+
 // ---- dequantization of one element ---------------------------------------------------------------
 
 __device__ __forceinline__ float h2f(const uint8_t * p) {
@@ -93,9 +98,9 @@ __device__ float dequant_packed(int dtype, const uint8_t * base, const Planes & 
 
 // GET_ROWS (src/core/ref/ops.cpp:690-722): dst row i = dequantized table row ids[i]; an index outside
 // the table leaves the row untouched and raises the error flag
-__global__ void get_rows_kernel(int dtype, int layout, const uint8_t * __restrict__ table, Planes P, int64_t row_stride, int64_t k,
-                                int64_t table_rows, const int32_t * __restrict__ ids, int64_t n_ids, float * __restrict__ dst,
-                                int64_t ld_dst, int * __restrict__ error_flag) {
+__global__ void get_rows_kernel(int dtype, int layout, const uint8_t * table, Planes P, int64_t row_stride, int64_t k,
+                                int64_t table_rows, const int32_t * ids, int64_t n_ids, float * dst,
+                                int64_t ld_dst, int * error_flag) {
     pdl_wait();
     pdl_launch_dependents();
     const int be = dtype == DT_Q4_0 || dtype == DT_Q8_0 ? 32 : dtype == DT_Q4_K || dtype == DT_Q6_K ? 256 : 1;
@@ -120,8 +125,8 @@ __global__ void get_rows_kernel(int dtype, int layout, const uint8_t * __restric
 
 // ---- RMS_NORM / RMS_NORM_MUL / ADD_RMS_NORM_MUL (ops.cpp:440-519) -------------------------------------
 // scale = 1 / sqrtf(float(sum_double(v^2) / ne0) + eps);  y = (v * scale) * w.  One CTA per row.
-__global__ void __launch_bounds__(256) rms_norm_kernel(const float * __restrict__ x, const float * __restrict__ add, const float * __restrict__ w,
-                                                       float * __restrict__ sum_out, float * __restrict__ y, int64_t ne0, float eps) {
+__global__ void __launch_bounds__(256) rms_norm_kernel(const float * x, const float * add, const float * w,
+                                                       float * sum_out, float * y, int64_t ne0, float eps) {
     pdl_wait();
     pdl_launch_dependents();
     __shared__ double red[8];
@@ -163,8 +168,8 @@ __global__ void __launch_bounds__(256) rms_norm_kernel(const float * __restrict_
 // One thread per rotated pair / copied pair.  With a table the (cos, sin) come from the caller, who
 // computed them with the reference's own recipe; positions outside the table, or no table at all, take
 // the on-device recipe: theta = pos * theta_scale^j by j sequential f32 multiplies, cosf / sinf.
-__global__ void rope_kernel(const float * __restrict__ x, const int32_t * __restrict__ positions, const float * __restrict__ table,
-                            int32_t table_first, int32_t table_n, float * __restrict__ y, int64_t ne0, int64_t heads, int64_t tokens,
+__global__ void rope_kernel(const float * x, const int32_t * positions, const float * table,
+                            int32_t table_first, int32_t table_n, float * y, int64_t ne0, int64_t heads, int64_t tokens,
                             int n_dims, int neox, float theta_scale, float freq_scale, float attn_factor) {
     pdl_wait();
     pdl_launch_dependents();
@@ -219,7 +224,7 @@ __device__ __forceinline__ float block_reduce(float v, bool is_max, float * red)
     return t;
 }
 
-__global__ void __launch_bounds__(256) soft_max_kernel(const float * __restrict__ x, const float * __restrict__ mask, int64_t mask_row_stride,
+__global__ void __launch_bounds__(256) soft_max_kernel(const float * x, const float * mask, int64_t mask_row_stride,
                                                        int64_t mask_rows, float * y, int64_t ne0, float scale) {
     pdl_wait();
     pdl_launch_dependents();
@@ -250,7 +255,7 @@ __global__ void __launch_bounds__(256) soft_max_kernel(const float * __restrict_
 
 // ---- elementwise ---------------------------------------------------------------------------------
 // SwiGLU with split inputs (ops.cpp:383-425): y = (x / (1 + expf(-x))) * g
-__global__ void swiglu_kernel(const float * __restrict__ x, const float * __restrict__ g, float * __restrict__ y, int64_t n) {
+__global__ void swiglu_kernel(const float * x, const float * g, float * y, int64_t n) {
     pdl_wait();
     pdl_launch_dependents();
     for (int64_t i = blockIdx.x * (int64_t) blockDim.x + threadIdx.x; i < n; i += (int64_t) gridDim.x * blockDim.x) {
@@ -260,15 +265,15 @@ __global__ void swiglu_kernel(const float * __restrict__ x, const float * __rest
 }
 
 // ADD (ops.cpp:280-312), same shapes
-__global__ void add_kernel(const float * __restrict__ a, const float * __restrict__ b, float * __restrict__ y, int64_t n) {
+__global__ void add_kernel(const float * a, const float * b, float * y, int64_t n) {
     pdl_wait();
     pdl_launch_dependents();
     for (int64_t i = blockIdx.x * (int64_t) blockDim.x + threadIdx.x; i < n; i += (int64_t) gridDim.x * blockDim.x) y[i] = __fadd_rn(a[i], b[i]);
 }
 
 // SET_ROWS F32 -> F32 (ops.cpp:724-762): src [ne0, n_rows, heads], dst [ne0, dst_rows, heads], ids [n_rows]
-__global__ void set_rows_kernel(const float * __restrict__ src, const int32_t * __restrict__ ids, float * __restrict__ dst, int64_t ne0,
-                                int64_t n_rows, int64_t heads, int64_t dst_rows, int * __restrict__ error_flag) {
+__global__ void set_rows_kernel(const float * src, const int32_t * ids, float * dst, int64_t ne0,
+                                int64_t n_rows, int64_t heads, int64_t dst_rows, int * error_flag) {
     pdl_wait();
     pdl_launch_dependents();
     const int64_t total = ne0 * n_rows * heads;
@@ -284,7 +289,7 @@ __global__ void set_rows_kernel(const float * __restrict__ src, const int32_t * 
 }
 
 // TOP_K with k = 1 (ops.cpp:1189-1228): maximum, lowest index on ties.  Single CTA.
-__global__ void __launch_bounds__(1024) argmax_kernel(const float * __restrict__ x, int64_t n, int32_t * __restrict__ out) {
+__global__ void __launch_bounds__(1024) argmax_kernel(const float * x, int64_t n, int32_t * out) {
     pdl_wait();
     pdl_launch_dependents();
     __shared__ float sv[32];

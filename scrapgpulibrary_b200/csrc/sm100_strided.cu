@@ -8,6 +8,11 @@
 
 namespace sm100 {
 
+// Activation pointers are deliberately NOT __restrict__ / __ldg: kernels are launched with programmatic dependent
+// launch, so a kernel may start while the kernel that produces its inputs is still running.  The non-coherent
+// read-only path (ld.global.nc) is only valid for data that does not change during the kernel's lifetime, which
+// under early launch includes the producer's writes; only weights (constant across the stream) use it.
+
 struct V4 {
     char * p;
     int64_t ne[4];
@@ -79,7 +84,7 @@ __global__ void glu_kernel(int kind, V4 x, V4 g, int split, int swapped, V4 y, i
 }
 
 // RMS_NORM family (ops.cpp:440-519), one CTA per row (i1, i2, i3)
-__global__ void __launch_bounds__(256) rms_norm_view_kernel(V4 x, V4 add, int has_add, const float * __restrict__ w, V4 sum_out, int has_sum, V4 y, float eps) {
+__global__ void __launch_bounds__(256) rms_norm_view_kernel(V4 x, V4 add, int has_add, const float * w, V4 sum_out, int has_sum, V4 y, float eps) {
     pdl_wait();
     pdl_launch_dependents();
     __shared__ double red[8];
@@ -121,8 +126,8 @@ __global__ void __launch_bounds__(256) rms_norm_view_kernel(V4 x, V4 add, int ha
 
 // ROPE (ops.cpp:530-634) over a view [ne0, heads, tokens, batch]; optional frequency factors; yarn is left to
 // the caller to reject
-__global__ void rope_view_kernel(V4 x, const int32_t * __restrict__ positions, const float * __restrict__ table, int32_t table_first,
-                                 int32_t table_n, const float * __restrict__ freq_factors, V4 y, int n_dims, int neox, float theta_scale,
+__global__ void rope_view_kernel(V4 x, const int32_t * positions, const float * table, int32_t table_first,
+                                 int32_t table_n, const float * freq_factors, V4 y, int n_dims, int neox, float theta_scale,
                                  float freq_scale, float attn_factor, int64_t total) {
     pdl_wait();
     pdl_launch_dependents();
@@ -253,7 +258,7 @@ __global__ void cpy_kernel(V4 s, int sdt, V4 d, int ddt, int64_t total) {
 }
 
 // SET_ROWS (ops.cpp:724-762): dst[:, ids[i1, i2 % ine1, i3 % ine2], i2, i3] = src[:, i1, i2, i3]
-__global__ void set_rows_view_kernel(V4 s, int sdt, V4 ids, int ids_i64, V4 d, int ddt, int64_t total, int * __restrict__ error_flag) {
+__global__ void set_rows_view_kernel(V4 s, int sdt, V4 ids, int ids_i64, V4 d, int ddt, int64_t total, int * error_flag) {
     pdl_wait();
     pdl_launch_dependents();
     for (int64_t idx = blockIdx.x * (int64_t) blockDim.x + threadIdx.x; idx < total; idx += (int64_t) gridDim.x * blockDim.x) {
