@@ -156,6 +156,20 @@ SM100_API int sm100_attention(sm100_stream_t s, const float * q, const float * k
                               int64_t hkv, int causal, int64_t offset, const int32_t * positions, float scale);
 
 
+/* sm100_attention for callers that cannot allocate device memory at call time (a host whose HBM is fully claimed
+ * by its own pools, a latency-critical thread that must stay off the driver's allocator, an externally enforced
+ * memory budget).  Same arguments and values as sm100_attention; the split-key partials go to a fixed 4 MiB array
+ * inside the library image (every GPU that loads the library holds it until exit) instead of a scratch buffer
+ * allocated on demand.  Shapes whose partials exceed sm100_attention_static_capacity() bytes
+ * (nq * hq * splits * (dv + 2) floats) are refused with UNSUPPORTED.  The first call on a device looks the array's
+ * address up: make it before any stream capture.  All calls on one device share the array, so calls that overlap
+ * on the GPU race.  This entry has no counterpart in the reference. */
+SM100_API int sm100_attention_static(sm100_stream_t s, const float * q, const float * k, const float * v, const float * mask,
+                                     int64_t mask_heads, float * out, int64_t d, int64_t dv, int64_t nq, int64_t nk,
+                                     int64_t hq, int64_t hkv, int causal, int64_t offset, const int32_t * positions,
+                                     float scale);
+SM100_API size_t sm100_attention_static_capacity(void);
+
 /* ---- the same ops over strided views (arbitrary nb[1..3], broadcast operands, transposed CPY sources): what
  *      op_execute needs to honour every descriptor the reference's CPU backend accepts
  *      (src/backends/cpu/api.cpp:394-830) ---- */

@@ -255,3 +255,69 @@ extern "C" int sm100_attention(sm100_stream_t s, const float * q, const float * 
     a.scratch = ws;
     return attention_launch((cudaStream_t) s, a);
 }
+
+
+// ---------------------------------------------------------------------------------------------------------
+// Attention without any allocation.
+//
+// Some hosts may not allocate device memory when they call in: a serving loop that has already handed every byte
+// of HBM to its own pools, a real-time thread that must not take the driver's allocator lock, code running under
+// a memory budget enforced from outside.  For them the split-key partials live in a fixed array that is part of
+// this library's image: every GPU that loads the library carries these 4 MiB until the process exits.
+//
+// In host code the name of a __device__ array is only a stand-in symbol, not a device address, so the address is
+// looked up with cudaGetSymbolAddress once per device (with that device current) and cached; the FIRST call on a
+// device does this look-up, so make that first call outside of any stream capture.  All calls on a device share
+// the one array: two calls whose kernels overlap on the GPU (different streams) race on it.  Nothing in it has to
+// start at zero -- every entry the merge kernel reads is written by the partial kernel of the same call.
+// ---------------------------------------------------------------------------------------------------------
+namespace sm100 {
+
+constexpr size_t ATT_STATIC_FLOATS = (size_t) 1 << 20;   // 4 MiB
+static __device__ __align__(256) float g_attn_static_scratch[ATT_STATIC_FLOATS];
+
+constexpr int ATT_STATIC_MAX_DEVICES = 64;
+static std::mutex g_static_mutex;
+static float * g_static_ptr[ATT_STATIC_MAX_DEVICES] = {};
+
+static int static_scratch(float ** out) {
+    int dev = 0;
+    SM100_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= ATT_STATIC_MAX_DEVICES) return fail(ST_UNSUPPORTED, "attention (static scratch): device ordinal %d is beyond the table of %d", dev, ATT_STATIC_MAX_DEVICES);
+    std::lock_guard<std::mutex> lock(g_static_mutex);
+    if (g_static_ptr[dev] == nullptr) {
+        void * p = nullptr;
+        const cudaError_t e = cudaGetSymbolAddress(&p, g_attn_static_scratch);   // the current device's copy of the array
+        if (e != cudaSuccess) return cuda_fail(e, "cudaGetSymbolAddress(attention scratch)");
+        if (p == nullptr) return fail(ST_BACKEND, "attention (static scratch): the symbol has no device address");
+        g_static_ptr[dev] = static_cast<float *>(p);
+    }
+    *out = g_static_ptr[dev];
+    return ST_OK;
+}
+
+}  // namespace sm100
+
+extern "C" int sm100_attention_static(sm100_stream_t s, const float * q, const float * k, const float * v, const float * mask, int64_t mask_heads,
+                                      float * out, int64_t d, int64_t dv, int64_t nq, int64_t nk, int64_t hq, int64_t hkv, int causal,
+                                      int64_t offset, const int32_t * positions, float scale) {
+    AttnArgs a = {};
+    a.q = q; a.k = k; a.v = v; a.mask = mask; a.out = out; a.positions = positions;
+    a.d = d; a.dv = dv; a.nq = nq; a.nk = nk; a.hq = hq; a.hkv = hkv; a.offset = offset;
+    a.mask_heads = mask_heads <= 1 ? 1 : mask_heads;
+    a.causal = causal; a.scale = scale;
+    const int st = attention_check(a);
+    if (st != ST_OK) return st;
+    attention_plan(a);
+    const size_t need = attention_scratch_bytes(a);
+    if (need > ATT_STATIC_FLOATS * sizeof(float))
+        return fail(ST_UNSUPPORTED, "attention (static scratch): this shape needs %zu bytes of split-key partials, the built-in array holds %zu; use sm100_attention",
+                    need, ATT_STATIC_FLOATS * sizeof(float));
+    float * ws = nullptr;
+    const int sw = static_scratch(&ws);
+    if (sw != ST_OK) return sw;
+    a.scratch = ws;
+    return attention_launch((cudaStream_t) s, a);
+}
+
+extern "C" size_t sm100_attention_static_capacity(void) { return sm100::ATT_STATIC_FLOATS * sizeof(float); }
