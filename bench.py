@@ -79,6 +79,11 @@ class ClockSampler:
             self.proc = None
             return
         threading.Thread(target=self._read, daemon=True).start()
+        # nvidia-smi needs a moment to attach: wait for its first sample so that the timed region is covered
+        t0 = time.time()
+        while not self.rows and time.time() - t0 < 5.0:
+            time.sleep(0.02)
+        self.rows.clear()
 
     def _read(self):
         for line in self.proc.stdout:
@@ -136,7 +141,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     _build.build_sm100()
     capi.require_device()
     L = capi.lib()
-    capi.check(L.sm100_set_device(local_rank), "set_device")
+    capi.set_default_device(local_rank)
     stream = capi.Stream(local_rank)
     dtype = Q4_K
     layers = args.layers
@@ -294,13 +299,14 @@ def run_ours(args, rank: int, world: int, local_rank: int):
                     "ms_per_step": round(e2e_ms, 4), "note": "host activations in / host results out per matvec, weights resident"},
             "roofline": {"bound": "hbm", "kernel": "matvec_q4k_mma<1,true>", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
                          "frac": round(achieved / peak, 4), "peak_source": peak_src, "bytes_per_launch": round(per_launch_bytes, 1),
-                         "us_per_launch": round(per_launch_us, 3), "traffic": None},
+                         "us_per_launch": round(per_launch_us, 3),
+                         # dram__bytes_read + write per launch, mean of the three shapes of one ncu capture (profiles/matvec_q4k_mma_q4k_sweep.md)
+                         "traffic": 22071125},
             "cpu_baseline": cpu,
             "clocks": clocks,
         }
     if dist is not None:
         dist.barrier()
-        dist.destroy_process_group()
     return out
 
 
@@ -417,6 +423,13 @@ def main():
         out = run_ours(args, rank, world, local_rank)
     if rank == 0 and out is not None:
         print(json.dumps(out), flush=True)
+    if world > 1:
+        # Leave without tearing the NCCL communicator down: destroy_process_group() was seen to block for minutes
+        # on this pool while captured CUDA graphs still reference the communicator.  All ranks have passed the
+        # final barrier, nothing is in flight.
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
 
 
 if __name__ == "__main__":

@@ -84,6 +84,16 @@ def check(status: int, what: str = "sm100") -> None:
         raise Sm100Error(status, what, (lib().sm100_last_error() or b"").decode())
 
 
+_DEFAULT_DEVICE = 0
+
+
+def set_default_device(device: int) -> None:
+    """Device used by Stream() / Buffer() when none is given (one process per GPU: the local rank)."""
+    global _DEFAULT_DEVICE
+    _DEFAULT_DEVICE = int(device)
+    check(lib().sm100_set_device(_DEFAULT_DEVICE), "set_device")
+
+
 def device_count() -> int:
     return lib().sm100_device_count()
 
@@ -94,8 +104,8 @@ def require_device() -> None:
 
 
 class Stream:
-    def __init__(self, device: int = 0):
-        self.device = device
+    def __init__(self, device: int | None = None):
+        self.device = device = _DEFAULT_DEVICE if device is None else device
         h = C.c_void_p()
         check(lib().sm100_stream_create(device, C.byref(h)), "stream_create")
         self.handle = h
@@ -130,8 +140,8 @@ class Event:
 class Buffer:
     """A device allocation (the backend's buffer_alloc)."""
 
-    def __init__(self, nbytes: int, device: int = 0):
-        self.device = device
+    def __init__(self, nbytes: int, device: int | None = None):
+        self.device = device = _DEFAULT_DEVICE if device is None else device
         self.nbytes = int(nbytes)
         p = C.c_void_p()
         check(lib().sm100_malloc(device, max(1, self.nbytes), C.byref(p)), "malloc")

@@ -24,7 +24,7 @@ from dataclasses import dataclass
 import numpy as np
 import torch
 
-from . import capi, synth
+from . import capi, synth, tp
 
 Q4_K, Q6_K = 32, 33
 
@@ -86,9 +86,7 @@ class DecodeModel:
         c = cfg
         self.hq, self.hkv = c.heads // world, c.kv_heads // world
         self.q_dim, self.kv_dim, self.ffn = self.hq * c.head_dim, self.hkv * c.head_dim, c.ffn // world
-        self.vocab_shard = -(-c.vocab // world)
-        self.vocab_lo = min(c.vocab, rank * self.vocab_shard)
-        self.vocab_n = max(0, min(c.vocab, self.vocab_lo + self.vocab_shard) - self.vocab_lo)
+        self.vocab_lo, self.vocab_n = tp.vocab_shard(c.vocab, rank, world)
         self.weight_bytes = 0
         self._base = {}
         f32 = dict(dtype=torch.float32, device=self.device)
@@ -172,12 +170,9 @@ class DecodeModel:
                 loc, k = nat, k_global
             elif shard[0] == "rows":
                 lo = shard[2] if len(shard) > 2 else self.rank * shard[1]
-                loc, k = nat[lo:lo + shard[1]], k_global
+                loc, k = tp.shard_rows(nat, lo, shard[1]), k_global
             else:
-                be, bb = (256, 144) if dtype == Q4_K else (256, 210)
-                b0 = self.rank * shard[1] // be
-                loc = nat.reshape(n_global, k_global // be, bb)[:, b0:b0 + shard[1] // be].reshape(n_global, -1)
-                k = shard[1]
+                loc, k = tp.shard_cols(nat, dtype, k_global, self.rank, shard[1]), shard[1]
         else:
             if shard is None:
                 n, k = n_global, k_global

@@ -1,0 +1,37 @@
+"""Tensor-parallel decode on 2 GPUs (one process per GPU, NCCL): greedy tokens identical to the CPU oracle's and to
+the single-GPU run, eager and under CUDA-graph replay.  Needs two GPUs; on a single-GPU box the test is skipped."""
+import json
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+
+from oracle import decode_ref
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_tp2_decode_tokens_match_oracle(sm100, tmp_path):
+    if sm100.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    from scrapgpulibrary_b200.decode import DecodeConfig
+    steps = 8
+    cfg = DecodeConfig(layers=3, hidden=1024, heads=8, kv_heads=2, head_dim=128, ffn=2048, vocab=4096, n_ctx=64, start_pos=8)
+    weights = decode_ref.random_weights(cfg, 7)
+    rng = np.random.default_rng(11)
+    kp = [rng.standard_normal((cfg.kv_heads, cfg.start_pos, cfg.head_dim)).astype(np.float32) for _ in range(cfg.layers)]
+    vp = [rng.standard_normal((cfg.kv_heads, cfg.start_pos, cfg.head_dim)).astype(np.float32) for _ in range(cfg.layers)]
+    want, _ = decode_ref.decode_reference(cfg, weights, 123, steps, kp, vp)
+    out = tmp_path / "tokens.json"
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+                        "--master-port", "29731", os.path.join(ROOT, "tests", "tp_decode_worker.py"), str(out), str(steps)],
+                       capture_output=True, text=True, timeout=600, env=env)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-4000:]
+    got = json.loads(out.read_text())
+    assert got["world"] == 2
+    assert got["eager"] == want.tolist()
+    assert got["replay"] == want.tolist()
