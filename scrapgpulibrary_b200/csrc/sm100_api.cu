@@ -2,11 +2,13 @@
 // (M <= 8, HBM-bound) and the prefill GEMM (tensor cores).
 #include "sm100_common.cuh"
 
+#include <cstdlib>
+
 namespace sm100 {
 int matvec(cudaStream_t s, int dtype, int layout, const void * w, int64_t w_row_stride, int64_t k, int64_t n, const float * x,
            int64_t ldx, int64_t m, float * y, int64_t ldy);
-int gemm_q8_0(cudaStream_t s, int layout, const void * w, int64_t k, int64_t n, const float * x, int64_t ldx, int64_t m, float * y,
-              int64_t ldy, bool * handled);
+int gemm_tc_mul_mat(cudaStream_t s, int dtype, int layout, const void * w, int64_t w_row_stride, int64_t k, int64_t n, const float * x,
+                    int64_t ldx, int64_t m, float * y, int64_t ldy, bool * handled);
 }
 
 using namespace sm100;
@@ -17,7 +19,15 @@ int sm100_mul_mat(sm100_stream_t s, int dtype, int layout, const void * w, int64
                   int64_t ldx, int64_t m, float * y, int64_t ldy) {
     if (m <= 0) return fail(ST_INVALID, "mul_mat: M must be positive");
     if (m <= 8) return matvec((cudaStream_t) s, dtype, layout, w, w_row_stride, k, n, x, ldx, m, y, ldy);
-    // wide batches: column panels of 8 through the matvec until a tensor-core path claims the shape
+    static const int min_m = [] { const char * e = getenv("SM100_GEMM_MIN_M"); return e != nullptr ? atoi(e) : 33; }();
+    if (m >= min_m) {
+        if (w == nullptr || x == nullptr || y == nullptr) return fail(ST_INVALID, "mul_mat: null tensor pointer");
+        if (k <= 0 || n <= 0) return fail(ST_INVALID, "mul_mat: K, N and M must be positive");
+        bool handled = false;
+        const int st = gemm_tc_mul_mat((cudaStream_t) s, dtype, layout, w, w_row_stride, k, n, x, ldx, m, y, ldy, &handled);
+        if (st != ST_OK || handled) return st;
+    }
+    // narrow batches, and shapes or dtypes the tensor-core path leaves alone: column panels of 8 through the matvec
     for (int64_t c = 0; c < m; c += 8) {
         const int64_t mm = m - c < 8 ? m - c : 8;
         const int st = matvec((cudaStream_t) s, dtype, layout, w, w_row_stride, k, n, x + c * ldx, ldx, mm, y + c * ldy, ldy);

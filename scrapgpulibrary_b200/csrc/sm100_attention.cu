@@ -173,29 +173,13 @@ __global__ void attn_combine_kernel(AttnArgs a) {
     }
 }
 
-// per-device scratch owned by the library, grown on demand (never shrinks)
-static std::mutex g_ws_mutex;
-static std::vector<void *> g_ws_ptr;
-static std::vector<size_t> g_ws_size;
+int device_scratch(int slot, size_t bytes, void ** out);
 
 static int workspace(size_t bytes, float ** out) {
-    int dev = 0;
-    SM100_CUDA(cudaGetDevice(&dev));
-    std::lock_guard<std::mutex> lock(g_ws_mutex);
-    if ((int) g_ws_ptr.size() <= dev) {
-        g_ws_ptr.resize(dev + 1, nullptr);
-        g_ws_size.resize(dev + 1, 0);
-    }
-    if (g_ws_size[dev] < bytes) {
-        if (g_ws_ptr[dev] != nullptr) SM100_CUDA(cudaFree(g_ws_ptr[dev]));
-        g_ws_ptr[dev] = nullptr;
-        g_ws_size[dev] = 0;
-        size_t want = bytes < (size_t) (8u << 20) ? (size_t) (8u << 20) : bytes;
-        SM100_CUDA(cudaMalloc(&g_ws_ptr[dev], want));
-        g_ws_size[dev] = want;
-    }
-    *out = (float *) g_ws_ptr[dev];
-    return ST_OK;
+    void * p = nullptr;
+    const int st = device_scratch(0, bytes, &p);
+    *out = (float *) p;
+    return st;
 }
 
 int attention_launch(cudaStream_t s, AttnArgs a) {

@@ -47,6 +47,34 @@ int sm_count() {
     return cache[dev];
 }
 
+// Per-device scratch owned by the library, one buffer per slot (0 = attention partials, 1 = GEMM
+// activations), grown on demand and never shrunk.  Calls that use the same slot must be ordered on one
+// stream; growing frees the old buffer, which waits for the device to go idle.
+int device_scratch(int slot, size_t bytes, void ** out) {
+    constexpr int SLOTS = 2;
+    struct Entry { void * ptr[SLOTS] = {nullptr, nullptr}; size_t size[SLOTS] = {0, 0}; };
+    static std::mutex mu;
+    static std::vector<Entry> table;
+    if (slot < 0 || slot >= SLOTS) return fail(ST_INVALID, "device_scratch: bad slot");
+    int dev = 0;
+    SM100_CUDA(cudaGetDevice(&dev));
+    std::lock_guard<std::mutex> lock(mu);
+    if ((int) table.size() <= dev) table.resize(dev + 1);
+    Entry & e = table[dev];
+    if (e.size[slot] < bytes) {
+        if (e.ptr[slot] != nullptr) SM100_CUDA(cudaFree(e.ptr[slot]));
+        e.ptr[slot] = nullptr;
+        e.size[slot] = 0;
+        const size_t want = bytes < (size_t) (8u << 20) ? (size_t) (8u << 20) : bytes;
+        SM100_CUDA(cudaMalloc(&e.ptr[slot], want));
+        e.size[slot] = want;
+    }
+    *out = e.ptr[slot];
+    return ST_OK;
+}
+
+int gemm_poll_fault();
+
 }  // namespace sm100
 
 using namespace sm100;
@@ -129,7 +157,7 @@ int sm100_stream_destroy(int device, sm100_stream_t stream) {
 
 int sm100_stream_sync(sm100_stream_t stream) {
     SM100_CUDA(cudaStreamSynchronize((cudaStream_t) stream));
-    return ST_OK;
+    return gemm_poll_fault();
 }
 
 int sm100_memcpy_h2d(sm100_stream_t s, void * dst, const void * src, size_t n, int blocking) {
