@@ -251,6 +251,9 @@ def run_ours(args, rank: int, world: int, local_rank: int):
             b = sum(algorithmic_bytes(dtype, pool[s]["k"], pool[s]["n"], m) for s, _ in order)
             detail[f"q4_k_sweep_m{m}_gbps"] = round(b * sub_steps / (m_ms * 1e-3) / 1e9, 1)
 
+        # ---- prefill GEMM (tensor cores): Q8_0, M = 512 tokens, K = 4096, N in {4096, 12288} ----
+        detail.update(prefill_gemm(capi, stream))
+
         # ---- e2e: host activations in, host results out, call by call ----
         hx, hy = {}, {}
         for k in (4096, 12288):
@@ -307,6 +310,39 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         }
     if dist is not None:
         dist.barrier()
+    return out
+
+
+def prefill_gemm(capi, stream, reps: int = 20):
+    """Q8_0 prefill MUL_MAT at M = 512: dense TFLOP/s (2 M K N / time) of the tensor-core path, weights rotating
+    through four tensors per shape so that successive launches do not find them in L2."""
+    from scrapgpulibrary_b200 import synth
+    out = {}
+    m, k = 512, 4096
+    x = capi.Buffer(4 * m * k)
+    x.upload(stream, np.random.default_rng(5).standard_normal(m * k).astype(np.float32))
+    for n in (4096, 12288):
+        img = capi.pack(17, k, synth.quantized_matrix(17, 9, n, k))
+        ws = []
+        for _ in range(4):
+            b = capi.Buffer(img.nbytes)
+            b.upload(stream, img)
+            ws.append(b)
+        y = capi.Buffer(4 * m * n)
+        for i in range(3):
+            capi.mul_mat(stream, 17, 1, ws[i], k, n, x, m, y)
+        e0, e1 = capi.Event(), capi.Event()
+        e0.record(stream)
+        for i in range(reps):
+            capi.mul_mat(stream, 17, 1, ws[i % 4], k, n, x, m, y)
+        e1.record(stream)
+        e1.sync()
+        ms = e0.elapsed_ms(e1) / reps
+        out[f"q8_0_gemm_m{m}_k{k}_n{n}_tflops"] = round(2.0 * m * k * n / (ms * 1e-3) / 1e12, 1)
+        out[f"q8_0_gemm_m{m}_k{k}_n{n}_us"] = round(ms * 1e3, 1)
+        for b in ws + [y]:
+            b.free()
+    x.free()
     return out
 
 

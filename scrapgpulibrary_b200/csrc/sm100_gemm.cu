@@ -40,14 +40,12 @@ int device_scratch(int slot, size_t bytes, void ** out);
 namespace {
 
 constexpr int TM = 128;            // weight rows per CTA = rows of one tcgen05.mma = TMEM lanes
-constexpr int KC = 64;             // K elements per pipeline stage (two 32-weight blocks)
 // Warp roles.  The MMA warp is warp 0: the scheduler favours older warps, and a young MMA warp was starved
 // by the polling producers (each of its instructions took 50-80 cycles to issue).
 constexpr int WARP_MMA = 0;        // owns TMEM and issues the MMAs
 constexpr int WARP_BULK = 1;       // issues the bulk copies of the activation stages
 constexpr int FIRST_PRODUCER = 2;  // warps 2-17 dequantize, then run the epilogue
-constexpr int GROUP_WARPS = 8;     // one producer group covers the 128 rows x 2 blocks of a chunk
-constexpr int PRODUCER_WARPS = 16; // two groups, taking even and odd chunks
+constexpr int PRODUCER_WARPS = 16; // 512 threads = 512 (row, 32-weight block) tasks: one chunk of 128 K, or two of 64
 constexpr int GEMM_THREADS = 32 * (FIRST_PRODUCER + PRODUCER_WARPS);
 constexpr float W_PRESCALE = 256.0f;  // applied to quantized weights before they are rounded to f16
 constexpr uint32_t WAIT_LIMIT = 1u << 21;  // polls of one mbarrier wait before the CTA gives up (~1 s)
@@ -323,7 +321,7 @@ struct SrcTraits<SrcQ4K> {
 // ---------------------------------------------------------------------------------------------
 // Shared memory of one CTA
 // ---------------------------------------------------------------------------------------------
-template <int TN, int STAGES>
+template <int TN, int KC, int STAGES>
 struct GemmSmem {
     static constexpr int A_BYTES = TM * KC * 2;
     static constexpr int B_BYTES = TN * KC * 2;
@@ -344,16 +342,20 @@ struct GemmArgs {
     float * y;
     int64_t ldy;
     int n, m;      // weight rows; tokens of this pass
-    int nchunks;   // ceil(K / 64)
+    int nchunks;   // ceil(K / KC)
     int kblocks;   // K / 32
     int m_tiles;
 };
 
-template <typename S, int TN, int STAGES>
+template <typename S, int TN, int KC, int STAGES>
 __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc(const GemmArgs g) {
-    static_assert(STAGES % 2 == 0, "the two producer groups own the even and the odd stages");
+    // a chunk of KC weights per row is 4 KC tasks; the 512 producer threads form 512 / (4 KC) groups that
+    // take the chunks in turn
+    constexpr int GROUPS = PRODUCER_WARPS * 32 / (4 * KC);
+    constexpr int GROUP_WARPS = PRODUCER_WARPS / GROUPS;
+    static_assert(GROUPS >= 1 && STAGES % GROUPS == 0, "each producer group owns every GROUPS-th stage");
     extern __shared__ __align__(128) uint8_t smem_raw[];
-    using Smem = GemmSmem<TN, STAGES>;
+    using Smem = GemmSmem<TN, KC, STAGES>;
     Smem & sm = *reinterpret_cast<Smem *>(smem_raw);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int mt = blockIdx.x % g.m_tiles, nt = blockIdx.x / g.m_tiles;
@@ -362,7 +364,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc(const GemmArgs g) {
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
-            mbar_init(smem_addr(&sm.full[s]), GROUP_WARPS + 1);  // 8 producer warps + the bulk copy's expect_tx
+            mbar_init(smem_addr(&sm.full[s]), GROUP_WARPS + 1);  // the group's warps + the bulk copy's expect_tx
             mbar_init(smem_addr(&sm.empty[s]), 1);
         }
         mbar_init(smem_addr(&sm.accum), 1);
@@ -385,34 +387,38 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc(const GemmArgs g) {
     pdl_wait();
 
     if (warp >= FIRST_PRODUCER) {
-        // ---- A operand.  A task is (row, 32-weight block); a chunk has 128 x 2 of them, one per thread of a
-        // producer group.  Group 0 (warps 2-9) takes the even chunks, group 1 the odd ones, so each group has
-        // two chunk times for its convert-store-fence sequence.  Warp w of a group owns rows 16 w .. 16 w + 15:
-        // lane l takes row (l & 7) + 8 (l >> 4), block (l >> 3) & 1, so one warp-wide load touches the 16 rows'
-        // adjacent halves (whole 32/64-byte runs per row) and every group of 8 lanes stores one complete
-        // 128-byte core matrix (no bank conflicts).  DEPTH of the group's chunks are kept in flight in
-        // registers to cover the L2/HBM latency.
+        // ---- A operand.  A task is (row, 32-weight block), one per thread of a producer group; with 64-wide
+        // chunks group 0 (warps 2-9) takes the even chunks and group 1 the odd ones, so each has two chunk times
+        // for its convert-store-fence sequence.  Eight warps cover the 128 rows for two adjacent blocks: warp w
+        // owns rows 16 w .. 16 w + 15, lane l takes row (l & 7) + 8 (l >> 4), block (l >> 3) & 1, so one warp-wide
+        // load touches the 16 rows' adjacent halves (whole 32/64-byte runs per row) and every group of 8 lanes
+        // stores one complete 128-byte core matrix (no bank conflicts).  DEPTH of the group's chunks are kept
+        // in flight in registers to cover the L2/HBM latency.
         constexpr int DEPTH = 2;
+        constexpr int BLOCKS = KC / 32;  // 32-weight blocks per row and chunk
         const int pw = warp - FIRST_PRODUCER;
         const int group = pw / GROUP_WARPS;
-        const int row_in = 16 * (pw % GROUP_WARPS) + (lane & 7) + 8 * (lane >> 4);
-        const int half = (lane >> 3) & 1;
+        const int gw = pw % GROUP_WARPS;
+        const int row_in = 16 * (gw & 7) + (lane & 7) + 8 * (lane >> 4);
+        const int blk = ((lane >> 3) & 1) + 2 * (gw >> 3);
         const int64_t row = n0 + row_in;
         const bool row_ok = row < g.n;
-        const uint32_t dst0 = a_smem + (half * 4) * (TM * 16) + row_in * 16;
+        const uint32_t dst0 = a_smem + (blk * 4) * (TM * 16) + row_in * 16;
         typename S::Regs ring[DEPTH];
 #pragma unroll
-        for (int d = 0; d < DEPTH; ++d)
-            if (row_ok && 2 * (2 * d + group) + half < g.kblocks) S::load(ring[d], g.w, row, 2 * (2 * d + group) + half);
+        for (int d = 0; d < DEPTH; ++d) {
+            const int kb = (GROUPS * d + group) * BLOCKS + blk;
+            if (row_ok && kb < g.kblocks) S::load(ring[d], g.w, row, kb);
+        }
         bool alive = true;
-        int s = group;  // this group's stage: advances by 2, wraps at STAGES
+        int s = group;  // this group's stage: advances by GROUPS, wraps at STAGES
         uint32_t phase = 0;
-        for (int c0 = group; c0 < g.nchunks && alive; c0 += 2 * DEPTH) {
+        for (int c0 = group; c0 < g.nchunks && alive; c0 += GROUPS * DEPTH) {
 #pragma unroll
             for (int d = 0; d < DEPTH; ++d) {
-                const int c = c0 + 2 * d;
+                const int c = c0 + GROUPS * d;
                 if (c >= g.nchunks) break;
-                const int kb = 2 * c + half;
+                const int kb = c * BLOCKS + blk;
                 uint32_t out[16];
                 if (row_ok && kb < g.kblocks) {
                     SrcTraits<S>::convert(ring[d], kb, out);
@@ -420,7 +426,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc(const GemmArgs g) {
 #pragma unroll
                     for (int i = 0; i < 16; ++i) out[i] = 0u;
                 }
-                const int kb_next = kb + 4 * DEPTH;
+                const int kb_next = kb + GROUPS * DEPTH * BLOCKS;
                 if (row_ok && kb_next < g.kblocks) S::load(ring[d], g.w, row, kb_next);
                 // the stage is free once the MMAs of the chunk that used it last have retired
                 bool ok = mbar_try_wait(empty0 + 8 * s, phase ^ 1u);
@@ -435,7 +441,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc(const GemmArgs g) {
                 fence_proxy_async();  // generic-proxy stores -> visible to the tensor core's async proxy
                 __syncwarp();
                 if (lane == 0) mbar_arrive(full0 + 8 * s);
-                s += 2;
+                s += GROUPS;
                 if (s >= STAGES) { s -= STAGES; phase ^= 1u; }
             }
         }
@@ -487,8 +493,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc(const GemmArgs g) {
         __syncwarp();
     } else {
         // ---- MMA warp (warp 0).  This loop is one warp's serial instruction stream and bounds the kernel,
-        // so it is kept lean: one barrier per stage, all lanes poll it (no divergence around the wait),
-        // descriptors are a base plus compile-time offsets in their low word, stage and phase are counters. ----
+        // so it is kept lean: one barrier per stage, descriptors are a base plus compile-time offsets in
+        // their low word, stage and phase are counters. ----
         constexpr uint32_t IDESC = instr_desc_f16(TM, TN);
         constexpr uint32_t DESC_HI = (128u >> 4) | (1u << 14);  // 128 bytes between 8-row groups; descriptor version 1
         const uint32_t a_lo0 = (a_smem >> 4) | ((uint32_t) (TM * 16) >> 4) << 16;  // start address | bytes between K halves
@@ -534,7 +540,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc(const GemmArgs g) {
 // ---------------------------------------------------------------------------------------------
 // Activation preparation: f32 [M, K] (column stride ldx) -> normalised f16 stage images + token factors
 // ---------------------------------------------------------------------------------------------
-template <int TN>
+template <int TN, int KC>
 __global__ void __launch_bounds__(256) gemm_prep_x(const float * x, int64_t ldx, int m, int k, int nchunks, int kslices, float * tokscale,
                                                    __half * xh) {
     pdl_wait();
@@ -568,7 +574,8 @@ __global__ void __launch_bounds__(256) gemm_prep_x(const float * x, int64_t ldx,
     const int t = threadIdx.x & 7;
     const int tok = group * 8 + t;
     const float scale = s_scale[t];
-    const int units = nchunks * 8;  // 8-element K units per token, K padded to whole chunks
+    constexpr int UPC = KC / 8;       // 8-element K units per chunk
+    const int units = nchunks * UPC;  // per token, K padded to whole chunks
     const int per_slice = (units + kslices - 1) / kslices;
     const int u_end = (slice + 1) * per_slice < units ? (slice + 1) * per_slice : units;
     const int mt = tok / TN, tt = tok % TN;
@@ -582,17 +589,17 @@ __global__ void __launch_bounds__(256) gemm_prep_x(const float * x, int64_t ldx,
         }
         const __half2 h0 = __floats2half2_rn(a.x * scale, a.y * scale), h1 = __floats2half2_rn(a.z * scale, a.w * scale);
         const __half2 h2 = __floats2half2_rn(b.x * scale, b.y * scale), h3 = __floats2half2_rn(b.z * scale, b.w * scale);
-        __half * dst = xh + ((int64_t) mt * nchunks + (u >> 3)) * (TN * KC) + (u & 7) * (TN * 8) + tt * 8;
+        __half * dst = xh + ((int64_t) mt * nchunks + u / UPC) * (TN * KC) + (u % UPC) * (TN * 8) + tt * 8;
         *reinterpret_cast<uint4 *>(dst) = make_uint4(h2_bits(h0), h2_bits(h1), h2_bits(h2), h2_bits(h3));
     }
 }
 
 std::atomic<bool> g_gemm_launched{false};
 
-template <typename S, int TN, int STAGES>
+template <typename S, int TN, int KC, int STAGES>
 int launch_gemm(cudaStream_t s, GemmArgs g, int n_tiles) {
     g.out_scale = 1.0f / S::PRESCALE;
-    using Smem = GemmSmem<TN, STAGES>;
+    using Smem = GemmSmem<TN, KC, STAGES>;
     static std::mutex mu;
     static std::vector<char> configured;
     int dev = 0;
@@ -601,28 +608,31 @@ int launch_gemm(cudaStream_t s, GemmArgs g, int n_tiles) {
         std::lock_guard<std::mutex> lock(mu);
         if ((int) configured.size() <= dev) configured.resize(dev + 1, 0);
         if (!configured[dev]) {
-            SM100_CUDA(cudaFuncSetAttribute(gemm_tc<S, TN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) sizeof(Smem)));
+            SM100_CUDA(cudaFuncSetAttribute(gemm_tc<S, TN, KC, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) sizeof(Smem)));
             configured[dev] = 1;
         }
     }
     g_gemm_launched.store(true, std::memory_order_relaxed);
-    return launch(gemm_tc<S, TN, STAGES>, dim3((unsigned) (n_tiles * g.m_tiles)), dim3(GEMM_THREADS), sizeof(Smem), s, g);
+    return launch(gemm_tc<S, TN, KC, STAGES>, dim3((unsigned) (n_tiles * g.m_tiles)), dim3(GEMM_THREADS), sizeof(Smem), s, g);
 }
 
-template <int TN, int STAGES>
+template <int TN, int KC, int STAGES>
 int launch_gemm_dtype(cudaStream_t s, int dtype, int layout, const GemmArgs & g, int n_tiles) {
     const bool packed = layout == LAYOUT_PACKED;
     switch (dtype) {
-        case DT_Q8_0: return packed ? launch_gemm<SrcQ80<true>, TN, STAGES>(s, g, n_tiles) : launch_gemm<SrcQ80<false>, TN, STAGES>(s, g, n_tiles);
-        case DT_Q4_0: return packed ? launch_gemm<SrcQ40<true>, TN, STAGES>(s, g, n_tiles) : launch_gemm<SrcQ40<false>, TN, STAGES>(s, g, n_tiles);
-        case DT_Q4_K: return launch_gemm<SrcQ4K, TN, STAGES>(s, g, n_tiles);
-        case DT_F16: return launch_gemm<SrcF16, TN, STAGES>(s, g, n_tiles);
+        case DT_Q8_0:
+            return packed ? launch_gemm<SrcQ80<true>, TN, KC, STAGES>(s, g, n_tiles) : launch_gemm<SrcQ80<false>, TN, KC, STAGES>(s, g, n_tiles);
+        case DT_Q4_0:
+            return packed ? launch_gemm<SrcQ40<true>, TN, KC, STAGES>(s, g, n_tiles) : launch_gemm<SrcQ40<false>, TN, KC, STAGES>(s, g, n_tiles);
+        case DT_Q4_K: return launch_gemm<SrcQ4K, TN, KC, STAGES>(s, g, n_tiles);
+        case DT_F16: return launch_gemm<SrcF16, TN, KC, STAGES>(s, g, n_tiles);
     }
     return fail(ST_UNSUPPORTED, "gemm: no tensor-core source for dtype %d", dtype);
 }
 
-template <int TN, int STAGES>
+template <int TN, int KC, int STAGES>
 int gemm_passes(cudaStream_t s, int dtype, int layout, GemmArgs g, const float * x, int64_t ldx, int64_t m, int64_t k, float * y, int n_tiles) {
+    g.nchunks = (int) ((k + KC - 1) / KC);
     // tokens per pass: the prepared activations of one pass stay below 64 MiB
     int64_t pass = ((int64_t) 64 << 20) / ((int64_t) g.nchunks * KC * 2) / TN * TN;
     if (pass < TN) pass = TN;
@@ -641,7 +651,7 @@ int gemm_passes(cudaStream_t s, int dtype, int layout, GemmArgs g, const float *
         int kslices = (2 * sm_count() + groups - 1) / groups;
         if (kslices < 1) kslices = 1;
         if (kslices > g.nchunks) kslices = g.nchunks;
-        st = launch(gemm_prep_x<TN>, dim3((unsigned) (groups * kslices)), dim3(256), 0, s, x + c0 * ldx, ldx, (int) mm, (int) k, g.nchunks,
+        st = launch(gemm_prep_x<TN, KC>, dim3((unsigned) (groups * kslices)), dim3(256), 0, s, x + c0 * ldx, ldx, (int) mm, (int) k, g.nchunks,
                     kslices, tokscale, xh);
         if (st != ST_OK) return st;
         g.xh = xh;
@@ -649,7 +659,7 @@ int gemm_passes(cudaStream_t s, int dtype, int layout, GemmArgs g, const float *
         g.y = y + c0 * g.ldy;
         g.m = (int) mm;
         g.m_tiles = m_tiles;
-        st = launch_gemm_dtype<TN, STAGES>(s, dtype, layout, g, n_tiles);
+        st = launch_gemm_dtype<TN, KC, STAGES>(s, dtype, layout, g, n_tiles);
         if (st != ST_OK) return st;
     }
     return ST_OK;
@@ -676,13 +686,12 @@ int gemm_tc_mul_mat(cudaStream_t s, int dtype, int layout, const void * w, int64
     const bool packed = layout == LAYOUT_PACKED;
     if (!(dtype == DT_Q8_0 || dtype == DT_Q4_0 || dtype == DT_F16 || (dtype == DT_Q4_K && packed))) return ST_OK;
     if (k % 32 != 0 || (dtype == DT_Q4_K && k % 256 != 0)) return ST_OK;
-    if (n > INT32_MAX - TM || k > INT32_MAX - KC || m > INT32_MAX / 2) return ST_OK;
+    if (n > INT32_MAX - TM || k > INT32_MAX - 128 || m > INT32_MAX / 2) return ST_OK;
     if ((((uintptr_t) x) & 15) != 0 || ldx % 4 != 0) return ST_OK;
     if (packed && (((uintptr_t) w) & 31) != 0) return ST_OK;
     const int be = block_elems(dtype);
     if (w_row_stride == 0) w_row_stride = k / be * block_bytes(dtype);
 
-    const int nchunks = (int) ((k + KC - 1) / KC);
     const int n_tiles = (int) ((n + TM - 1) / TM);
     GemmArgs g = {};
     g.w.base = (const uint8_t *) w;
@@ -690,7 +699,6 @@ int gemm_tc_mul_mat(cudaStream_t s, int dtype, int layout, const void * w, int64
     g.w.row_stride = w_row_stride;
     g.w.blocks_per_row = k / be;
     g.n = (int) n;
-    g.nchunks = nchunks;
     g.kblocks = (int) (k / 32);
     g.ldy = ldy;
     // 256-token tiles halve the dequantization work and the weight traffic per output, but a CTA then owns
@@ -698,8 +706,8 @@ int gemm_tc_mul_mat(cudaStream_t s, int dtype, int layout, const void * w, int64
     static const int forced_tn = [] { const char * e = getenv("SM100_GEMM_TN"); return e != nullptr ? atoi(e) : 0; }();
     const int64_t tiles256 = (int64_t) n_tiles * ((m + 255) / 256);
     const bool wide = forced_tn != 0 ? forced_tn == 256 : tiles256 >= (int64_t) sm_count();
-    const int st = wide ? gemm_passes<256, 4>(s, dtype, layout, g, x, ldx, m, k, y, n_tiles)
-                        : gemm_passes<128, 6>(s, dtype, layout, g, x, ldx, m, k, y, n_tiles);
+    const int st = wide ? gemm_passes<256, 64, 4>(s, dtype, layout, g, x, ldx, m, k, y, n_tiles)
+                        : gemm_passes<128, 64, 6>(s, dtype, layout, g, x, ldx, m, k, y, n_tiles);
     if (st != ST_OK) return st;
     *handled = true;
     return ST_OK;
