@@ -143,6 +143,13 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     L = capi.lib()
     capi.set_default_device(local_rank)
     stream = capi.Stream(local_rank)
+    if args.no_pdl:
+        L.sm100_set_pdl(0)
+    if args.decode_only:
+        # profiler runs of the layer-stack decode alone (single GPU): a few tokens, one line
+        d = run_decode(args, rank, world, local_rank, None, stream_sync=stream.sync)
+        print(json.dumps({"decode_only": True, **d}), flush=True)
+        return None
     dtype = Q4_K
     layers = args.layers
     t0 = time.time()
@@ -447,6 +454,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--decode-steps", type=int, default=128)
     ap.add_argument("--no-decode", action="store_true", help="skip the layer-stack decode measurement")
+    ap.add_argument("--no-pdl", action="store_true", help="launch without programmatic dependent launch (profiler runs)")
+    ap.add_argument("--decode-only", action="store_true", help="layer-stack decode only, single GPU: for profiler runs")
     ap.add_argument("--quick", action="store_true", help="headline sweep only (no per-shape detail, e2e, CPU baseline, decode): for profiler runs")
     args = ap.parse_args()
     args.warmup = max(3, args.warmup) if args.impl == "ours" else args.warmup

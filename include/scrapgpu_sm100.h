@@ -142,6 +142,17 @@ SM100_API int sm100_add(sm100_stream_t s, const float * a, const float * b, floa
 /* SET_ROWS F32 -> F32 (ops.cpp:724-762): dst[:, ids[i], h] = src[:, i, h] */
 SM100_API int sm100_set_rows(sm100_stream_t s, const float * src, const int32_t * ids, float * dst, int64_t ne0,
                              int64_t n_rows, int64_t heads, int64_t dst_rows);
+/* One decode token's head post-processing in one launch: RMS_NORM_MUL per head of Q and K (weights may be NULL: no
+ * norm), ROPE of Q and K (full head rotated; NEOX or NORMAL pairing; (cos, sin) from the table, positions outside
+ * it take the on-device recipe), and SET_ROWS_PAIR of K and V into the caches [kv_heads][cache_rows][head_dim]
+ * (include/scrapgpu/op.h:43-45 RMS_NORM_MUL / SET_ROWS_PAIR, src/core/ref/ops.cpp:440-519, 530-634, 690-760).
+ * Same values as the separate ops; Q and K are updated in place; positions is one I32 on the device. */
+SM100_API int sm100_head_post(sm100_stream_t s, float * q, float * k, const float * v, const float * q_norm_w,
+                              const float * k_norm_w, const int32_t * positions, const float * table,
+                              int32_t table_first_position, int32_t table_positions, float * k_cache, float * v_cache,
+                              int64_t head_dim, int64_t q_heads, int64_t kv_heads, int64_t cache_rows, float eps,
+                              float freq_base, int neox);
+
 /* TOP_K with k = 1 (ops.cpp:1189-1228): index of the maximum, lowest index on ties */
 SM100_API int sm100_argmax(sm100_stream_t s, const float * x, int64_t n, int32_t * out);
 /* fused decode attention, the values of scrapgpu_scaled_dot_product_attention

@@ -7,6 +7,8 @@
 namespace sm100 {
 int matvec(cudaStream_t s, int dtype, int layout, const void * w, int64_t w_row_stride, int64_t k, int64_t n, const float * x,
            int64_t ldx, int64_t m, float * y, int64_t ldy);
+int matvec_q4k_imma_multi(cudaStream_t s, int count, const void * const * ws, const int64_t * ns, int64_t k, const float * x, int64_t ldx,
+                          int64_t m, float * const * ys, const int64_t * ldys, bool * handled);
 int gemm_tc_mul_mat(cudaStream_t s, int dtype, int layout, const void * w, int64_t w_row_stride, int64_t k, int64_t n, const float * x,
                     int64_t ldx, int64_t m, float * y, int64_t ldy, bool * handled);
 }
@@ -40,7 +42,30 @@ int sm100_mul_mat_multi(sm100_stream_t s, int count, const int * dtypes, const i
                         const int64_t * ns, const float * x, float * const * ys) {
     if (count < 1 || count > 3 || dtypes == nullptr || layouts == nullptr || ws == nullptr || ns == nullptr || ys == nullptr)
         return fail(ST_INVALID, "mul_mat_multi: 1..3 weight tensors with their dtypes, layouts and outputs are required");
+    // packed Q4_K tensors of whole 16-row tiles go out together in one launch; everything else one by one
+    const void * gw[3];
+    int64_t gn[3], gld[3];
+    float * gy[3];
+    int grouped = 0;
+    bool in_group[3] = {false, false, false};
     for (int i = 0; i < count; ++i) {
+        if (ws[i] == nullptr || ys[i] == nullptr || ns[i] <= 0) return fail(ST_INVALID, "mul_mat_multi: null tensor or empty shape");
+        if (dtypes[i] == DT_Q4_K && layouts[i] == LAYOUT_PACKED && ns[i] % 16 == 0) {
+            gw[grouped] = ws[i]; gn[grouped] = ns[i]; gy[grouped] = ys[i]; gld[grouped] = ns[i];
+            in_group[i] = true;
+            ++grouped;
+        }
+    }
+    if (grouped >= 2 && x != nullptr && k > 0) {
+        bool handled = false;
+        const int st = matvec_q4k_imma_multi((cudaStream_t) s, grouped, gw, gn, k, x, k, 1, gy, gld, &handled);
+        if (st != ST_OK) return st;
+        if (!handled) in_group[0] = in_group[1] = in_group[2] = false;
+    } else {
+        in_group[0] = in_group[1] = in_group[2] = false;
+    }
+    for (int i = 0; i < count; ++i) {
+        if (in_group[i]) continue;
         const int st = matvec((cudaStream_t) s, dtypes[i], layouts[i], ws[i], 0, k, ns[i], x, k, 1, ys[i], ns[i]);
         if (st != ST_OK) return st;
     }

@@ -147,25 +147,53 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_partial_kernel(AttnArgs a) {
     }
 }
 
+// Merge of the splits of one (query, head): thread s first turns split s's (m, l) into its weight
+// exp(m_s - m) / l in shared memory (one round of independent loads), then the threads cover dv and sum the
+// weighted partial accumulators, again with independent loads.
+constexpr int ATT_MAX_SPLITS = 1024;
+
 __global__ void attn_combine_kernel(AttnArgs a) {
     pdl_wait();
     pdl_launch_dependents();
+    __shared__ float s_w[ATT_MAX_SPLITS];
+    __shared__ float s_red[2][32];
     const int64_t h = blockIdx.x, q = blockIdx.y;
     const float * base = a.scratch + scratch_index(a, q, h, 0);
     const int64_t stride = a.dv + 2;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
+    // block-wide max of m, then sum of l exp(m_s - m)
     float m = -INFINITY;
-    for (int s = 0; s < a.splits; ++s) m = fmaxf(m, base[s * stride]);
-    float l = 0.f;
-    for (int s = 0; s < a.splits; ++s) {
+    for (int s = tid; s < a.splits; s += blockDim.x) {
         const float ms = base[s * stride];
-        if (ms != -INFINITY) l += base[s * stride + 1] * expf(ms - m);
+        s_w[s] = ms;
+        m = fmaxf(m, ms);
     }
-    for (int64_t dvi = threadIdx.x; dvi < a.dv; dvi += blockDim.x) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    if (lane == 0) s_red[0][warp] = m;
+    __syncthreads();
+    m = -INFINITY;
+    for (int w = 0; w < nwarps; ++w) m = fmaxf(m, s_red[0][w]);
+    float l = 0.f;
+    for (int s = tid; s < a.splits; s += blockDim.x) {
+        const float ms = s_w[s];
+        const float e = ms != -INFINITY ? expf(ms - m) : 0.f;
+        s_w[s] = e;
+        if (ms != -INFINITY) l += base[s * stride + 1] * e;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) l += __shfl_xor_sync(0xffffffffu, l, o);
+    if (lane == 0) s_red[1][warp] = l;
+    __syncthreads();
+    l = 0.f;
+    for (int w = 0; w < nwarps; ++w) l += s_red[1][w];
+    for (int64_t dvi = tid; dvi < a.dv; dvi += blockDim.x) {
         float o = 0.f;
         if (m != -INFINITY) {
+#pragma unroll 8
             for (int s = 0; s < a.splits; ++s) {
-                const float ms = base[s * stride];
-                if (ms != -INFINITY) o = fmaf(base[s * stride + 2 + dvi], expf(ms - m), o);
+                const float e = s_w[s];
+                if (e != 0.f) o = fmaf(base[s * stride + 2 + dvi], e, o);
             }
             o = o / l;
         }
@@ -198,6 +226,7 @@ int attention_check(const AttnArgs & a) {
     if (a.q == nullptr || a.k == nullptr || a.v == nullptr || a.out == nullptr) return fail(ST_INVALID, "attention: null tensor pointer");
     if (a.d <= 0 || a.dv <= 0 || a.nq <= 0 || a.nk <= 0 || a.hq <= 0 || a.hkv <= 0) return fail(ST_INVALID, "attention: dimensions must be positive");
     if (a.hq % a.hkv != 0) return fail(ST_INVALID, "attention: Hq must be divisible by Hkv");
+    if (a.nk > (int64_t) ATT_CHUNK * ATT_MAX_SPLITS) return fail(ST_UNSUPPORTED, "attention: more than %d keys", ATT_CHUNK * ATT_MAX_SPLITS);
     if (a.hq / a.hkv > ATT_MAX_GROUP) return fail(ST_UNSUPPORTED, "attention: more than 8 query heads per KV head");
     if (a.nq > 65535 || a.hkv > 65535) return fail(ST_UNSUPPORTED, "attention: too many queries or KV heads for one launch");
     if (a.d > 1024 || a.dv > 1024) return fail(ST_UNSUPPORTED, "attention: head dimension above 1024");
@@ -213,7 +242,7 @@ void attention_plan(AttnArgs & a) {
     int64_t splits = (ctas_wanted + per_head - 1) / per_head;
     int64_t chunk = (a.nk + splits - 1) / splits;
     if (chunk < 32) chunk = 32;
-    if (chunk > ATT_CHUNK) chunk = ATT_CHUNK;
+    if (chunk > ATT_CHUNK) chunk = ATT_CHUNK;   // attention_check bounds nk so that this leaves at most ATT_MAX_SPLITS splits
     a.chunk = (int) chunk;
     a.splits = (int) ((a.nk + chunk - 1) / chunk);
 }

@@ -22,6 +22,9 @@
 // blocks; weight tiles are prefetched one chunk ahead and the first chunk is issued before griddepcontrol.wait.
 #include "sm100_quant_units.cuh"
 
+#include <atomic>
+#include <cstdlib>
+
 namespace sm100 {
 
 namespace {
@@ -29,41 +32,38 @@ namespace {
 constexpr int IQ_WARPS = 8;    // warps that share one row tile (they split K)
 constexpr int IQ_GROUPS = 2;   // row tiles a CTA works on at a time
 constexpr int IQ_THREADS = IQ_WARPS * IQ_GROUPS * 32;
-constexpr int IQ_TILES = 8;    // pair tiles (64 weights each) per chunk = two 256-weight blocks
+
+// Up to three weight tensors that share the activations (MUL_MAT_MULTI: Q/K/V, gate/up) are handled as one
+// concatenation of row tiles, so one launch quantizes x once and fills the machine even when a tensor is small.
+constexpr int IQ_MAX_TENSORS = 3;
 
 struct IqArgs {
-    const uint8_t * w;   // packed tensor base
-    int64_t h_off;       // byte offset of the header plane
+    const uint8_t * w[IQ_MAX_TENSORS];   // packed tensor bases
+    int64_t h_off[IQ_MAX_TENSORS];       // byte offset of each header plane
+    float * y[IQ_MAX_TENSORS];           // [N_i, M], column stride ldy[i] floats
+    int64_t ldy[IQ_MAX_TENSORS];
+    int tile_end[IQ_MAX_TENSORS];        // row tiles of tensors 0..i together (INT32_MAX for unused slots)
     const float * x;     // [K, M], column stride ldx floats
-    float * y;           // [N, M], column stride ldy floats
-    int64_t ldx, ldy;
-    int n_tiles;         // full 16-row tiles
+    int64_t ldx;
+    int n_tiles;         // full 16-row tiles of all tensors
     int pairs;           // K / 64
     int blocks;          // K / 256
-    int chunks;          // ceil(blocks / 2)
+    int chunks;          // ceil(blocks / blocks per chunk)
+    int ring;            // slots per warp of the shared-memory ring
 };
+
+__device__ __forceinline__ int nsb_of(const IqArgs & p) { return p.pairs * 2; }
+
+// tensor of a global row tile and the tile's index inside it
+__device__ __forceinline__ void iq_locate(const IqArgs & p, int rt, int & tensor, int & local) {
+    tensor = (rt >= p.tile_end[0] ? 1 : 0) + (rt >= p.tile_end[1] ? 1 : 0);
+    local = rt - (tensor == 0 ? 0 : p.tile_end[tensor - 1]);
+}
 
 __device__ __forceinline__ void imma_16832(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
     asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                  : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-
-struct IqStage {
-    uint4 a[IQ_TILES];   // weight tiles of the chunk
-    uint4 h;             // one block header per lane: row (lane & 15), block 2 * chunk + (lane >> 4)
-};
-
-__device__ __forceinline__ void iq_load_stage(const IqArgs & p, int rt, int chunk, int lane, IqStage & st) {
-    const uint8_t * tiles = p.w + ((int64_t) rt * p.pairs + (int64_t) chunk * IQ_TILES) * 512 + lane * 16;
-#pragma unroll
-    for (int j = 0; j < IQ_TILES; ++j) {
-        if (chunk * IQ_TILES + j < p.pairs) st.a[j] = ldg_stream(tiles + j * 512);
-        else st.a[j] = make_uint4(0, 0, 0, 0);
-    }
-    const int blk = 2 * chunk + (lane >> 4);
-    if (blk < p.blocks) st.h = __ldg((const uint4 *) (p.w + p.h_off + (((int64_t) rt * 16 + (lane & 15)) * p.blocks + blk) * 16));
-    else st.h = make_uint4(0, 0, 0, 0);
 }
 
 // One row's share of a block for lane t: header words -> d, dmin and the scale field of sub-blocks 2t, 2t+1;
@@ -84,35 +84,133 @@ __device__ __forceinline__ float iq_row_term(const uint4 & h, int t, int clo_h, 
     return fmaf(df.x, dot, -df.y * mins);
 }
 
+// ---- shared-memory ring fed by the copy engine ----
+__device__ __forceinline__ uint32_t iq_smem_addr(const void * p) { return (uint32_t) __cvta_generic_to_shared(p); }
+__device__ __forceinline__ void iq_bar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void iq_bar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool iq_bar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// global -> shared bulk copy (TMA unit); addresses and size are multiples of 16
+__device__ __forceinline__ void iq_bulk_g2s(uint32_t dst, const void * src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(src),
+                 "r"(bytes), "r"(bar)
+                 : "memory");
+}
+// per-thread 16-byte asynchronous copy and its arrival on the slot's barrier
+__device__ __forceinline__ void iq_cp_async16(uint32_t dst, const void * src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void iq_cp_async_arrive(uint32_t bar) {
+    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ uint4 iq_lds128(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
+}
+// first MMA of a block: the accumulator starts at zero
+__device__ __forceinline__ void imma_16832_zero(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+                 : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
+}
+
+constexpr uint32_t IQ_WAIT_LIMIT = 1u << 22;         // polls of one barrier before the warp gives up
+
+__device__ int g_iq_fault;
+
 // Shared memory of one CTA:
-//   xq   [M][K/32][64 B]      quantized activations in B-fragment order: per sub-block the h plane then the l plane,
-//                             each as [t][b0 (k = 4t..4t+3), b1 (k = 16+4t..)] bytes
-//   xs   [M][K/64] float4     (s, sum x) of the low and of the high sub-block of each pair
-//   hdr  [warp][2 blocks][16 rows] uint4   raw headers of the warp's current chunk
-//   red  [warp][16 rows][4] float          partial outputs of the warps of one row tile
-template <int M>
-__global__ void __launch_bounds__(IQ_THREADS, 1) matvec_q4k_imma(IqArgs p) {
-    extern __shared__ __align__(16) uint8_t smem[];
-    const int nsb = p.pairs * 2;
+//   xq    [M][K/64][128 B]    quantized activations in B-fragment order: per pair [plane h, l][t][low sub-block b0, b1,
+//                             high sub-block b0, b1], b0 = bytes of k = 4t..4t+3, b1 of k = 16+4t..; 16 zero bytes follow
+//                             for the lanes whose fragment column holds no activation
+//   xs    [M][K/64] float4    (s, sum x) of the low and of the high sub-block of each pair
+//   red   [warp][16 rows][4] float   partial outputs of the warps of one row tile
+//   bars  [warp][R] mbarrier
+//   hdr   [warp][R][2 blocks][16 rows] uint4   block headers of the chunks in flight
+//   ring  [warp][R][8 tiles][512 B]            weight tiles of the chunks in flight
+// A warp owns R slots.  Lane 0 fills a slot with one bulk copy (the chunk's tiles are contiguous in the packed
+// layout), all lanes add one 16-byte asynchronous copy of a block header, and both complete on the slot's barrier.
+// The first R chunks are requested before griddepcontrol.wait: weights do not depend on the predecessor kernel.
+// NB = 256-weight blocks per chunk: 2 with one CTA per SM, or 1 with two CTAs per SM (more warps to hide latencies,
+// and one CTA's barriers overlap the other's arithmetic).
+template <int M, int NB>
+__global__ void __launch_bounds__(IQ_THREADS, NB == 1 ? 2 : 1) matvec_q4k_imma(IqArgs p) {
+    constexpr int IQ_TILES = 4 * NB;                    // pair tiles (64 weights each) per chunk
+    constexpr uint32_t IQ_SLOT_BYTES = IQ_TILES * 512;  // weight tiles of one chunk
+    constexpr uint32_t IQ_HDR_BYTES = 256 * NB;         // its NB x 16 block headers
+    extern __shared__ __align__(128) uint8_t smem[];
+    const int R = p.ring;
+    const uint32_t xq_bytes = (uint32_t) M * p.pairs * 128;
     uint32_t * xq = reinterpret_cast<uint32_t *>(smem);
-    float2 * xs2 = reinterpret_cast<float2 *>(smem + (size_t) M * nsb * 64);
-    uint4 * hdr = reinterpret_cast<uint4 *>(reinterpret_cast<uint8_t *>(xs2) + (size_t) M * nsb * 8);
-    float * red = reinterpret_cast<float *>(hdr + IQ_WARPS * IQ_GROUPS * 32);
+    float2 * xs2 = reinterpret_cast<float2 *>(smem + xq_bytes + 16);
+    float * red = reinterpret_cast<float *>(smem + xq_bytes + 16 + (uint32_t) M * p.pairs * 16);
+    uint64_t * bars = reinterpret_cast<uint64_t *>(red + IQ_WARPS * IQ_GROUPS * 64);
+    uint8_t * hdr = reinterpret_cast<uint8_t *>(bars + IQ_WARPS * IQ_GROUPS * R);
+    hdr += (128 - (iq_smem_addr(hdr) & 127)) & 127;
+    uint8_t * ring = hdr + (uint32_t) IQ_WARPS * IQ_GROUPS * R * IQ_HDR_BYTES;
 
     const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
     const int group = wid / IQ_WARPS, warp = wid % IQ_WARPS;
     const int g = lane >> 2, t = lane & 3;
+    const int rt_step = gridDim.x * IQ_GROUPS;
+    const uint32_t bar0 = iq_smem_addr(bars + wid * R);
+    const uint32_t hdr0 = iq_smem_addr(hdr) + (uint32_t) wid * R * IQ_HDR_BYTES;
+    const uint32_t ring0 = iq_smem_addr(ring) + (uint32_t) wid * R * IQ_SLOT_BYTES;
 
-    // first chunk of weights: independent of the predecessor kernel
-    IqStage cur, nxt;
-    int rt = blockIdx.x * IQ_GROUPS + group, chunk = warp;
-    if (rt < p.n_tiles && chunk < p.chunks) iq_load_stage(p, rt, chunk, lane, cur);
+    if (lane == 0) {
+        for (int s = 0; s < R; ++s) iq_bar_init(bar0 + 8 * s, 33);   // lane 0's expect_tx + 32 header copies
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncwarp();
+
+    // requests the chunk (rt, chunk) into slot s
+    auto request = [&](int rt_global, int chunk, int s) {
+        const int tiles = p.pairs - chunk * IQ_TILES < IQ_TILES ? p.pairs - chunk * IQ_TILES : IQ_TILES;
+        int ti, rt;
+        iq_locate(p, rt_global, ti, rt);
+        const uint8_t * wbase = p.w[ti];
+        if (lane == 0) {
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // earlier reads of the slot precede the copy's writes
+            iq_bar_expect_tx(bar0 + 8 * s, (uint32_t) tiles * 512);
+            iq_bulk_g2s(ring0 + s * IQ_SLOT_BYTES, wbase + ((int64_t) rt * p.pairs + (int64_t) chunk * IQ_TILES) * 512, (uint32_t) tiles * 512,
+                        bar0 + 8 * s);
+        }
+        const int blk = NB * chunk + (lane >> 4);
+        if (lane < 16 * NB && blk < p.blocks)
+            iq_cp_async16(hdr0 + s * IQ_HDR_BYTES + lane * 16, wbase + p.h_off[ti] + (((int64_t) rt * 16 + (lane & 15)) * p.blocks + blk) * 16);
+        iq_cp_async_arrive(bar0 + 8 * s);
+    };
+
+    // issue cursor: runs R chunks ahead of the consume cursor over the same sequence
+    int irt = blockIdx.x * IQ_GROUPS + group, ichunk = warp, islot = 0;
+    for (int i = 0; i < R; ++i) {
+        if (irt < p.n_tiles && ichunk < p.chunks) {
+            request(irt, ichunk, islot);
+            if (++islot == R) islot = 0;
+            ichunk += IQ_WARPS;
+            if (ichunk >= p.chunks) { ichunk = warp; irt += rt_step; }
+        }
+    }
 
     pdl_wait();
 
     // activations -> 16-bit integers per 32-element sub-block.  One item = 4 consecutive elements; the 8 items of
     // a sub-block sit in 8 consecutive lanes.
     const int items = p.pairs * 16;
+    if (tid < 4) xq[xq_bytes / 4 + tid] = 0u;
     for (int it0 = tid; it0 < M * items; it0 += IQ_THREADS) {
         const int m = it0 / items, it = it0 - m * items;
         const int sb = it >> 3, q = it & 7;
@@ -136,73 +234,86 @@ __global__ void __launch_bounds__(IQ_THREADS, 1) matvec_q4k_imma(IqArgs p) {
             hp |= ((uint32_t) hi & 255u) << (8 * e);
             lp |= ((uint32_t) lo & 255u) << (8 * e);
         }
-        uint32_t * dst = xq + ((size_t) m * nsb + sb) * 16 + (q & 3) * 2 + (q >> 2);
+        // word of the pair: plane * 16 + t * 4 + (high sub-block ? 2 : 0) + (k >= 16 ? 1 : 0)
+        uint32_t * dst = xq + ((size_t) m * p.pairs + (sb >> 1)) * 32 + (q & 3) * 4 + (sb & 1) * 2 + (q >> 2);
         dst[0] = hp;
-        dst[8] = lp;
-        if (q == 0) xs2[(size_t) m * nsb + sb] = make_float2(s, sum);
+        dst[16] = lp;
+        if (q == 0) xs2[(size_t) m * nsb_of(p) + sb] = make_float2(s, sum);
     }
     __syncthreads();
     pdl_launch_dependents();
 
     // per-lane views.  Pair j of a block feeds B columns 2j (h plane) and 2j+1 (l plane): lane (g, t) supplies
-    // column g, so it reads plane g & 1 of pair g >> 1 and zeros for the other pairs.
-    const uint2 * xq_lane = reinterpret_cast<const uint2 *>(xq) + (g & 1) * 4 + t;   // uint2 units: 8 per sub-block
-    const float4 * xs_lane = reinterpret_cast<const float4 *>(xs2) + t;
-    uint4 * my_hdr = hdr + wid * 32;
-    const int rt_step = gridDim.x * IQ_GROUPS;
+    // column g, so it reads plane g & 1 of pair g >> 1 and the zero bytes for the other pairs.
+    const uint32_t xq0 = iq_smem_addr(xq);
+    const uint32_t zero_addr = xq0 + xq_bytes;
+    const uint32_t xq_live = xq0 + (uint32_t) (g >> 1) * 128 + (g & 1) * 64 + t * 16;   // + m * pairs * 128 + blk * 512
+    const int live_pair = g >> 1;
+    const uint32_t xs0 = iq_smem_addr(xs2) + t * 16;
     float * my_red = red + group * (IQ_WARPS * 64);
     const int gtid = tid - group * (IQ_WARPS * 32);
+
+    int rt = blockIdx.x * IQ_GROUPS + group, chunk = warp, cslot = 0;
+    uint32_t cphase = 0;
+    bool alive = true;
 
     // every group runs the same number of rounds so that the CTA-wide barriers match
     for (int round = blockIdx.x * IQ_GROUPS; round < p.n_tiles; round += rt_step) {
         float acc0[M], acc1[M];   // rows g and g + 8 of the tile
 #pragma unroll
         for (int m = 0; m < M; ++m) acc0[m] = acc1[m] = 0.f;
-        for (; rt < p.n_tiles && chunk < p.chunks; chunk += IQ_WARPS) {
-            // prefetch the next work item of this warp
-            int nrt = rt, nchunk = chunk + IQ_WARPS;
-            if (nchunk >= p.chunks) { nrt = rt + rt_step; nchunk = warp; }
-            if (nrt < p.n_tiles && nchunk < p.chunks) iq_load_stage(p, nrt, nchunk, lane, nxt);
-
-            __syncwarp();
-            my_hdr[lane] = cur.h;   // [block of the chunk][row]
-            __syncwarp();
-
-#pragma unroll
-            for (int b2 = 0; b2 < 2; ++b2) {
-                const int blk = chunk * 2 + b2;
-                int clo[M][4], chi[M][4];
-#pragma unroll
-                for (int m = 0; m < M; ++m)
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) clo[m][i] = chi[m][i] = 0;
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const uint4 wt = cur.a[b2 * 4 + j];   // x, y: row g k-halves 0, 1; z, w: row g + 8
-                    const bool live = (g >> 1) == j;
-#pragma unroll
-                    for (int m = 0; m < M; ++m) {
-                        uint2 blo = make_uint2(0u, 0u), bhi = make_uint2(0u, 0u);
-                        if (live && blk < p.blocks) {
-                            const uint2 * src = xq_lane + ((size_t) m * nsb + (size_t) (blk * 4 + j) * 2) * 8;
-                            blo = src[0];
-                            bhi = src[8];
-                        }
-                        imma_16832(clo[m], wt.x & 0x0F0F0F0Fu, wt.z & 0x0F0F0F0Fu, wt.y & 0x0F0F0F0Fu, wt.w & 0x0F0F0F0Fu, blo.x, blo.y);
-                        imma_16832(chi[m], wt.x & 0xF0F0F0F0u, wt.z & 0xF0F0F0F0u, wt.y & 0xF0F0F0F0u, wt.w & 0xF0F0F0F0u, bhi.x, bhi.y);
-                    }
+        for (; alive && rt < p.n_tiles && chunk < p.chunks; chunk += IQ_WARPS) {
+            // wait for the slot (bounded: a copy that never lands must not hang the GPU)
+            {
+                const uint32_t bar = bar0 + 8 * cslot;
+                bool ok = iq_bar_try_wait(bar, cphase);
+                for (uint32_t i = 0; !ok && i < IQ_WAIT_LIMIT; ++i) ok = iq_bar_try_wait(bar, cphase);
+                if (!__all_sync(0xffffffffu, ok)) {
+                    if (lane == 0) atomicExch(&g_iq_fault, 1);
+                    alive = false;
+                    break;
                 }
+            }
+            const uint32_t tiles_lane = ring0 + cslot * IQ_SLOT_BYTES + lane * 16;
+            const uint32_t hdr_lane = hdr0 + cslot * IQ_HDR_BYTES + g * 16;
+#pragma unroll
+            for (int b2 = 0; b2 < NB; ++b2) {
+                const int blk = chunk * NB + b2;
                 if (blk < p.blocks) {
-                    const uint4 h0 = my_hdr[b2 * 16 + g], h1 = my_hdr[b2 * 16 + g + 8];
+                    int clo[M][4], chi[M][4];
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const uint4 wt = iq_lds128(tiles_lane + (b2 * 4 + j) * 512);   // x, y: row g k-halves 0, 1; z, w: row g + 8
+#pragma unroll
+                        for (int m = 0; m < M; ++m) {
+                            const uint4 bf = iq_lds128(j == live_pair ? xq_live + (uint32_t) (m * p.pairs + blk * 4) * 128 : zero_addr);
+                            if (j == 0) {
+                                imma_16832_zero(clo[m], wt.x & 0x0F0F0F0Fu, wt.z & 0x0F0F0F0Fu, wt.y & 0x0F0F0F0Fu, wt.w & 0x0F0F0F0Fu, bf.x, bf.y);
+                                imma_16832_zero(chi[m], wt.x & 0xF0F0F0F0u, wt.z & 0xF0F0F0F0u, wt.y & 0xF0F0F0F0u, wt.w & 0xF0F0F0F0u, bf.z, bf.w);
+                            } else {
+                                imma_16832(clo[m], wt.x & 0x0F0F0F0Fu, wt.z & 0x0F0F0F0Fu, wt.y & 0x0F0F0F0Fu, wt.w & 0x0F0F0F0Fu, bf.x, bf.y);
+                                imma_16832(chi[m], wt.x & 0xF0F0F0F0u, wt.z & 0xF0F0F0F0u, wt.y & 0xF0F0F0F0u, wt.w & 0xF0F0F0F0u, bf.z, bf.w);
+                            }
+                        }
+                    }
+                    const uint4 h0 = iq_lds128(hdr_lane + b2 * 256), h1 = iq_lds128(hdr_lane + b2 * 256 + 128);
 #pragma unroll
                     for (int m = 0; m < M; ++m) {
-                        const float4 sq = xs_lane[((size_t) m * nsb >> 1) + blk * 4];
+                        const uint4 sqb = iq_lds128(xs0 + (uint32_t) (m * p.pairs + blk * 4) * 16);
+                        const float4 sq = make_float4(__uint_as_float(sqb.x), __uint_as_float(sqb.y), __uint_as_float(sqb.z), __uint_as_float(sqb.w));
                         acc0[m] += iq_row_term(h0, t, clo[m][0], clo[m][1], chi[m][0], chi[m][1], sq);
                         acc1[m] += iq_row_term(h1, t, clo[m][2], clo[m][3], chi[m][2], chi[m][3], sq);
                     }
                 }
             }
-            cur = nxt;
+            // the slot is consumed (its values sit in registers that the MMAs above have read): refill it
+            __syncwarp();
+            if (irt < p.n_tiles && ichunk < p.chunks) {
+                request(irt, ichunk, cslot);
+                ichunk += IQ_WARPS;
+                if (ichunk >= p.chunks) { ichunk = warp; irt += rt_step; }
+            }
+            if (++cslot == R) { cslot = 0; cphase ^= 1u; }
         }
         // sum over the four lanes of a row (each held other sub-blocks), then over the warps (each held other chunks)
 #pragma unroll
@@ -227,55 +338,111 @@ __global__ void __launch_bounds__(IQ_THREADS, 1) matvec_q4k_imma(IqArgs p) {
                 float v = 0.f;
 #pragma unroll
                 for (int w = 0; w < IQ_WARPS; ++w) v += my_red[(w * 16 + row) * 4 + col];
-                p.y[(int64_t) col * p.ldy + (int64_t) rt * 16 + row] = v;
+                int ti, lrt;
+                iq_locate(p, rt, ti, lrt);
+                p.y[ti][(int64_t) col * p.ldy[ti] + (int64_t) lrt * 16 + row] = v;
             }
         }
         __syncthreads();
         rt += rt_step;
         chunk = warp;
     }
+
+    // copies that were requested but never consumed (only after a fault) must land before the CTA's memory goes away
+    if (!alive) {
+        for (int s = 0; s < R; ++s)
+            for (uint32_t i = 0; i < IQ_WAIT_LIMIT && !iq_bar_try_wait(bar0 + 8 * s, cphase); ++i) {}
+    }
 }
 
-size_t iq_smem_bytes(int pairs, int m) {
-    return (size_t) m * pairs * 2 * (64 + 8) + (size_t) IQ_WARPS * IQ_GROUPS * 32 * 16 + (size_t) IQ_WARPS * IQ_GROUPS * 16 * 4 * 4;
+size_t iq_smem_bytes(int pairs, int m, int ring, int nb) {
+    return (size_t) m * pairs * (128 + 16) + 16 + (size_t) IQ_WARPS * IQ_GROUPS * 64 * 4 + (size_t) IQ_WARPS * IQ_GROUPS * ring * 8 + 128 +
+           (size_t) IQ_WARPS * IQ_GROUPS * ring * nb * (256 + 2048);
 }
 
-template <int M>
+template <int M, int NB>
 int launch_iq(cudaStream_t s, const IqArgs & a, size_t smem, int grid) {
-    if (smem > 48 * 1024) SM100_CUDA(cudaFuncSetAttribute(matvec_q4k_imma<M>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
-    return launch(matvec_q4k_imma<M>, dim3((unsigned) grid), dim3(IQ_THREADS), smem, s, a);
+    // always the device maximum: a smaller value set by a later launch would undercut kernel nodes already
+    // recorded in a graph when a tool re-launches them
+    if (smem > 48 * 1024)
+        SM100_CUDA(cudaFuncSetAttribute(matvec_q4k_imma<M, NB>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+    return launch(matvec_q4k_imma<M, NB>, dim3((unsigned) grid), dim3(IQ_THREADS), smem, s, a);
 }
+
+std::atomic<bool> g_iq_launched{false};
 
 }  // namespace
 
-// Q4_K packed matvec (1 or 2 activation columns) over the full 16-row tiles of the tensor; *handled = false when
-// the shape is left to the caller's other kernels.
-int matvec_q4k_imma_tiles(cudaStream_t s, const void * w, int64_t k, int64_t n, const float * x, int64_t ldx, int64_t m, float * y, int64_t ldy,
-                          bool * handled) {
+// Reads and clears the kernel's fault flag on the current device (set when a warp gave up waiting for a copy);
+// called after a stream synchronisation.
+int iq_poll_fault() {
+    if (!g_iq_launched.exchange(false, std::memory_order_relaxed)) return ST_OK;
+    int v = 0;
+    SM100_CUDA(cudaMemcpyFromSymbol(&v, g_iq_fault, sizeof(v)));
+    if (v == 0) return ST_OK;
+    const int zero = 0;
+    SM100_CUDA(cudaMemcpyToSymbol(g_iq_fault, &zero, sizeof(zero)));
+    return fail(ST_BACKEND, "mul_mat: the Q4_K matvec gave up waiting for a weight copy; its output is incomplete");
+}
+
+// Q4_K packed matvec (1 or 2 activation columns) over the full 16-row tiles of up to three tensors that share
+// the activations; *handled = false when the shapes are left to the caller's other kernels.
+int matvec_q4k_imma_multi(cudaStream_t s, int count, const void * const * ws, const int64_t * ns, int64_t k, const float * x, int64_t ldx,
+                          int64_t m, float * const * ys, const int64_t * ldys, bool * handled) {
     *handled = false;
-    const int64_t tiles = n / 16;
-    if (tiles == 0 || m < 1 || m > 2 || k % 256 != 0 || k / 64 > 4096) return ST_OK;
+    if (count < 1 || count > IQ_MAX_TENSORS || m < 1 || m > 2 || k % 256 != 0 || k / 64 > 4096) return ST_OK;
+    if (((uintptr_t) x & 15) != 0 || (m > 1 && (ldx & 3) != 0)) return ST_OK;
+    int64_t tiles = 0;
+    for (int i = 0; i < count; ++i) {
+        if (ns[i] / 16 == 0 || ((uintptr_t) ws[i] & 15) != 0) return ST_OK;
+        if (count > 1 && ns[i] % 16 != 0) return ST_OK;   // leftover rows are the single-tensor caller's business
+        tiles += ns[i] / 16;
+    }
+    if (tiles > INT32_MAX / 2) return ST_OK;
     const int pairs = (int) (k / 64);
-    const size_t smem = iq_smem_bytes(pairs, (int) m);
-    if (smem > 227 * 1024) return ST_OK;
-    if (((uintptr_t) w & 15) != 0 || ((uintptr_t) x & 15) != 0 || (m > 1 && (ldx & 3) != 0)) return ST_OK;
-    IqArgs a;
-    a.w = (const uint8_t *) w;
-    a.h_off = n * (k / 256) * 128;
+    // two CTAs per SM with one-block chunks on request, else one CTA per SM with two-block chunks
+    static const int forced_nb = [] { const char * e = getenv("SM100_Q4K_NB"); return e != nullptr ? atoi(e) : 0; }();
+    const int nb = forced_nb == 1 ? 1 : 2;
+    int ring = 4;
+    const size_t per_cta = nb == 1 ? (size_t) 113 * 1024 : (size_t) 227 * 1024;
+    while (ring >= 2 && iq_smem_bytes(pairs, (int) m, ring, nb) > per_cta) --ring;
+    if (ring < 2) return ST_OK;
+    const size_t smem = iq_smem_bytes(pairs, (int) m, ring, nb);
+    IqArgs a = {};
+    int end = 0;
+    for (int i = 0; i < IQ_MAX_TENSORS; ++i) {
+        if (i < count) {
+            a.w[i] = (const uint8_t *) ws[i];
+            a.h_off[i] = ns[i] * (k / 256) * 128;
+            a.y[i] = ys[i];
+            a.ldy[i] = ldys[i];
+            end += (int) (ns[i] / 16);
+            a.tile_end[i] = end;
+        } else {
+            a.tile_end[i] = INT32_MAX;
+        }
+    }
     a.x = x;
-    a.y = y;
     a.ldx = ldx;
-    a.ldy = ldy;
     a.n_tiles = (int) tiles;
     a.pairs = pairs;
     a.blocks = (int) (k / 256);
-    a.chunks = (a.blocks + 1) / 2;
-    int64_t grid = sm_count();   // one CTA per SM: the activations are quantized once per SM
+    a.chunks = (a.blocks + nb - 1) / nb;
+    a.ring = ring;
+    int64_t grid = (int64_t) sm_count() * (nb == 1 ? 2 : 1);   // resident CTAs: each quantizes the activations once
     const int64_t rounds = (tiles + IQ_GROUPS - 1) / IQ_GROUPS;
     if (grid > rounds) grid = rounds;
-    const int st = m == 1 ? launch_iq<1>(s, a, smem, (int) grid) : launch_iq<2>(s, a, smem, (int) grid);
+    g_iq_launched.store(true, std::memory_order_relaxed);
+    int st;
+    if (nb == 1) st = m == 1 ? launch_iq<1, 1>(s, a, smem, (int) grid) : launch_iq<2, 1>(s, a, smem, (int) grid);
+    else st = m == 1 ? launch_iq<1, 2>(s, a, smem, (int) grid) : launch_iq<2, 2>(s, a, smem, (int) grid);
     *handled = st == ST_OK;
     return st;
+}
+
+int matvec_q4k_imma_tiles(cudaStream_t s, const void * w, int64_t k, int64_t n, const float * x, int64_t ldx, int64_t m, float * y, int64_t ldy,
+                          bool * handled) {
+    return matvec_q4k_imma_multi(s, 1, &w, &n, k, x, ldx, m, &y, &ldy, handled);
 }
 
 }  // namespace sm100

@@ -164,6 +164,164 @@ __global__ void __launch_bounds__(256) rms_norm_kernel(const float * x, const fl
     }
 }
 
+// Same values with the row held in registers: every thread owns up to VPT float4 pieces, so the row is read once,
+// the loads are independent 16-byte loads, and the second pass needs no memory.  Used when ne0 is a multiple of 4,
+// the rows are 16-byte aligned and a row fits 1024 threads x VPT pieces.
+template <int VPT>
+__global__ void __launch_bounds__(1024) rms_norm_vec_kernel(const float * x, const float * add, const float * w, float * sum_out, float * y,
+                                                            int64_t ne0, float eps) {
+    pdl_wait();
+    pdl_launch_dependents();
+    __shared__ double red[32];
+    __shared__ float s_scale;
+    const int64_t row = blockIdx.x;
+    const int n4 = (int) (ne0 >> 2);
+    const float4 * xr = reinterpret_cast<const float4 *>(x + row * ne0);
+    const float4 * ar = add != nullptr ? reinterpret_cast<const float4 *>(add + row * ne0) : nullptr;
+    float4 v[VPT];
+    double sum = 0.0;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+        const int idx = threadIdx.x + i * blockDim.x;
+        v[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (idx < n4) {
+            v[i] = xr[idx];
+            if (ar != nullptr) {
+                const float4 a4 = ar[idx];
+                v[i] = make_float4(__fadd_rn(v[i].x, a4.x), __fadd_rn(v[i].y, a4.y), __fadd_rn(v[i].z, a4.z), __fadd_rn(v[i].w, a4.w));
+                if (sum_out != nullptr) reinterpret_cast<float4 *>(sum_out + row * ne0)[idx] = v[i];
+            }
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < VPT; ++i)
+        sum += ((double) v[i].x * (double) v[i].x + (double) v[i].y * (double) v[i].y) + ((double) v[i].z * (double) v[i].z + (double) v[i].w * (double) v[i].w);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    const int warps = (blockDim.x + 31) >> 5;
+    if (warps > 1) {
+        if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = sum;
+        __syncthreads();
+        if (threadIdx.x < 32) {
+            double t = threadIdx.x < warps ? red[threadIdx.x] : 0.0;
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+            if (threadIdx.x == 0) s_scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn((float) (t / (double) ne0), eps)));
+        }
+        __syncthreads();
+    } else if (threadIdx.x == 0) {
+        s_scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn((float) (sum / (double) ne0), eps)));
+    }
+    if (warps == 1) __syncwarp();
+    const float scale = *(volatile float *) &s_scale;
+    const float4 * wr = reinterpret_cast<const float4 *>(w);
+    float4 * yr = reinterpret_cast<float4 *>(y + row * ne0);
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+        const int idx = threadIdx.x + i * blockDim.x;
+        if (idx < n4) {
+            float4 t = make_float4(__fmul_rn(v[i].x, scale), __fmul_rn(v[i].y, scale), __fmul_rn(v[i].z, scale), __fmul_rn(v[i].w, scale));
+            if (w != nullptr) {
+                const float4 w4 = wr[idx];
+                t = make_float4(__fmul_rn(t.x, w4.x), __fmul_rn(t.y, w4.y), __fmul_rn(t.z, w4.z), __fmul_rn(t.w, w4.w));
+            }
+            yr[idx] = t;
+        }
+    }
+}
+
+// ---- one decode token's head post-processing in one launch -----------------------------------------------
+// RMS_NORM_MUL per head of Q and K (optional), ROPE of Q and K from the (cos, sin) table, SET_ROWS_PAIR of K and V
+// into the cache (include/scrapgpu/op.h:43-45; ops.cpp:440-519, 530-634, 690-760 of the reference): the values
+// of those separate ops, one warp per head.  Q and K are updated in place.
+struct HeadPostArgs {
+    float * q; float * k; const float * v;
+    const float * q_w; const float * k_w;     // norm weights [d] or null (no norm)
+    const int32_t * positions;                // one token
+    const float * table; int32_t table_first, table_n;
+    float * k_cache; float * v_cache;         // [hkv][ctx_rows][d]
+    int d, hq, hkv, neox;
+    int64_t ctx_rows;
+    float eps, theta_scale;
+};
+
+__global__ void __launch_bounds__(128) head_post_kernel(HeadPostArgs a) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int lane = threadIdx.x & 31;
+    const int task = blockIdx.x * 4 + (threadIdx.x >> 5);
+    if (task >= a.hq + 2 * a.hkv) return;
+    const int32_t pos = a.positions[0];
+    const bool row_ok = pos >= 0 && pos < a.ctx_rows;
+    if (task >= a.hq + a.hkv) {   // V head: copy into the cache
+        const int h = task - a.hq - a.hkv;
+        if (!row_ok) return;
+        const float * src = a.v + (int64_t) h * a.d;
+        float * dst = a.v_cache + ((int64_t) h * a.ctx_rows + pos) * a.d;
+        for (int e = lane; e < a.d; e += 32) dst[e] = src[e];
+        return;
+    }
+    const bool is_k = task >= a.hq;
+    const int h = is_k ? task - a.hq : task;
+    float * xr = is_k ? a.k + (int64_t) h * a.d : a.q + (int64_t) h * a.d;
+    const float * w = is_k ? a.k_w : a.q_w;
+    const int hp = a.d / 2;
+    // this lane's pairs: j = lane, lane + 32, ...; elements (j, j + d/2) for NEOX, (2j, 2j+1) otherwise
+    constexpr int MAXP = 4;   // d <= 256
+    float x0[MAXP], x1[MAXP];
+    double sum = 0.0;
+#pragma unroll
+    for (int i = 0; i < MAXP; ++i) {
+        const int j = lane + 32 * i;
+        x0[i] = x1[i] = 0.f;
+        if (j < hp) {
+            x0[i] = xr[a.neox ? j : 2 * j];
+            x1[i] = xr[a.neox ? j + hp : 2 * j + 1];
+            sum += (double) x0[i] * (double) x0[i] + (double) x1[i] * (double) x1[i];
+        }
+    }
+    float scale = 1.0f;
+    if (w != nullptr) {
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+        scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn((float) (sum / (double) a.d), a.eps)));
+    }
+    float * cache = is_k && row_ok ? a.k_cache + ((int64_t) h * a.ctx_rows + pos) * a.d : nullptr;
+    const int64_t rel = (int64_t) pos - a.table_first;
+    const bool in_table = a.table != nullptr && rel >= 0 && rel < a.table_n;
+#pragma unroll
+    for (int i = 0; i < MAXP; ++i) {
+        const int j = lane + 32 * i;
+        if (j < hp) {
+            const int e0 = a.neox ? j : 2 * j, e1 = a.neox ? j + hp : 2 * j + 1;
+            float v0 = x0[i], v1 = x1[i];
+            if (w != nullptr) {
+                v0 = __fmul_rn(__fmul_rn(v0, scale), w[e0]);
+                v1 = __fmul_rn(__fmul_rn(v1, scale), w[e1]);
+            }
+            float cs, sn;
+            if (in_table) {
+                const float2 t = *reinterpret_cast<const float2 *>(a.table + (rel * hp + j) * 2);
+                cs = t.x;
+                sn = t.y;
+            } else {
+                float theta = (float) pos;
+                for (int q = 0; q < j; ++q) theta = __fmul_rn(theta, a.theta_scale);
+                cs = cosf(theta);
+                sn = sinf(theta);
+            }
+            const float y0 = __fsub_rn(__fmul_rn(v0, cs), __fmul_rn(v1, sn));
+            const float y1 = __fadd_rn(__fmul_rn(v0, sn), __fmul_rn(v1, cs));
+            xr[e0] = y0;
+            xr[e1] = y1;
+            if (cache != nullptr) {
+                cache[e0] = y0;
+                cache[e1] = y1;
+            }
+        }
+    }
+}
+
 // ---- ROPE (ops.cpp:530-634), no yarn, no frequency factors -------------------------------------------
 // One thread per rotated pair / copied pair.  With a table the (cos, sin) come from the caller, who
 // computed them with the reference's own recipe; positions outside the table, or no table at all, take
@@ -358,6 +516,20 @@ int sm100_rms_norm(sm100_stream_t s, const float * x, const float * add, const f
                    int64_t rows, float eps) {
     if (x == nullptr || y == nullptr) return fail(ST_INVALID, "rms_norm: null pointer");
     if (ne0 <= 0 || rows <= 0 || rows > INT32_MAX) return fail(ST_INVALID, "rms_norm: bad shape");
+    const uintptr_t ptrs = (uintptr_t) x | (uintptr_t) y | (uintptr_t) add | (uintptr_t) w | (uintptr_t) sum_out;
+    if (ne0 % 4 == 0 && (ptrs & 15) == 0 && ne0 <= 4 * 1024 * 4) {
+        const int n4 = (int) (ne0 / 4);
+        int threads = n4 < 1024 ? (n4 + 31) / 32 * 32 : 1024;
+        // prefer 2 pieces per thread once a row has that many: fewer warps to reduce over
+        if (n4 >= 512 && n4 <= 2048) threads = (n4 / 2 + 31) / 32 * 32;
+        const int vpt = (n4 + threads - 1) / threads;
+        const dim3 grid((unsigned) rows), block((unsigned) threads);
+        switch (vpt) {
+            case 1: return launch(rms_norm_vec_kernel<1>, grid, block, 0, (cudaStream_t) s, x, add, w, sum_out, y, ne0, eps);
+            case 2: return launch(rms_norm_vec_kernel<2>, grid, block, 0, (cudaStream_t) s, x, add, w, sum_out, y, ne0, eps);
+            case 3: case 4: return launch(rms_norm_vec_kernel<4>, grid, block, 0, (cudaStream_t) s, x, add, w, sum_out, y, ne0, eps);
+        }
+    }
     return launch(rms_norm_kernel, dim3((unsigned) rows), dim3(256), 0, (cudaStream_t) s, x, add, w, sum_out, y, ne0, eps);
 }
 
@@ -409,6 +581,25 @@ int sm100_set_rows(sm100_stream_t s, const float * src, const int32_t * ids, flo
     if (ne0 <= 0 || n_rows <= 0 || heads <= 0 || dst_rows <= 0) return fail(ST_INVALID, "set_rows: bad shape");
     return launch(set_rows_kernel, dim3(grid_for(ne0 * n_rows * heads, 256)), dim3(256), 0, (cudaStream_t) s, src, ids, dst, ne0, n_rows, heads,
                   dst_rows, (int *) nullptr);
+}
+
+int sm100_head_post(sm100_stream_t s, float * q, float * k, const float * v, const float * q_norm_w, const float * k_norm_w,
+                    const int32_t * positions, const float * table, int32_t table_first_position, int32_t table_positions, float * k_cache,
+                    float * v_cache, int64_t head_dim, int64_t q_heads, int64_t kv_heads, int64_t cache_rows, float eps, float freq_base,
+                    int neox) {
+    if (q == nullptr || k == nullptr || v == nullptr || positions == nullptr || k_cache == nullptr || v_cache == nullptr)
+        return fail(ST_INVALID, "head_post: null pointer");
+    if (head_dim <= 0 || head_dim % 2 != 0 || head_dim > 256) return fail(ST_UNSUPPORTED, "head_post: head_dim must be even and at most 256");
+    if (q_heads <= 0 || kv_heads <= 0 || cache_rows <= 0 || q_heads + 2 * kv_heads > (1 << 20)) return fail(ST_INVALID, "head_post: bad shape");
+    HeadPostArgs a;
+    a.q = q; a.k = k; a.v = v; a.q_w = q_norm_w; a.k_w = k_norm_w; a.positions = positions;
+    a.table = table; a.table_first = table_first_position; a.table_n = table != nullptr ? table_positions : 0;
+    a.k_cache = k_cache; a.v_cache = v_cache;
+    a.d = (int) head_dim; a.hq = (int) q_heads; a.hkv = (int) kv_heads; a.neox = neox; a.ctx_rows = cache_rows;
+    a.eps = eps;
+    a.theta_scale = powf(freq_base, -2.0f / (float) head_dim);
+    const int tasks = (int) (q_heads + 2 * kv_heads);
+    return launch(head_post_kernel, dim3((unsigned) ((tasks + 3) / 4)), dim3(128), 0, (cudaStream_t) s, a);
 }
 
 int sm100_argmax(sm100_stream_t s, const float * x, int64_t n, int32_t * out) {

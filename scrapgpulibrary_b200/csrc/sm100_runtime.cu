@@ -74,6 +74,7 @@ int device_scratch(int slot, size_t bytes, void ** out) {
 }
 
 int gemm_poll_fault();
+int iq_poll_fault();
 
 }  // namespace sm100
 
@@ -157,7 +158,8 @@ int sm100_stream_destroy(int device, sm100_stream_t stream) {
 
 int sm100_stream_sync(sm100_stream_t stream) {
     SM100_CUDA(cudaStreamSynchronize((cudaStream_t) stream));
-    return gemm_poll_fault();
+    const int st = gemm_poll_fault();
+    return st != ST_OK ? st : iq_poll_fault();
 }
 
 int sm100_memcpy_h2d(sm100_stream_t s, void * dst, const void * src, size_t n, int blocking) {

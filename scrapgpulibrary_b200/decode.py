@@ -196,6 +196,18 @@ class DecodeModel:
     def _mm(self, w: Weight, x: torch.Tensor, y: torch.Tensor):
         capi.check(self.L.sm100_mul_mat(self.stream, w.dtype, 1, _dev(w.data), 0, w.k, w.n, _dev(x), w.k, 1, _dev(y), w.n), "mul_mat")
 
+    def _mm_multi(self, ws, x: torch.Tensor, ys):
+        """MUL_MAT_MULTI: weight tensors that share the activation column go out in one launch where the library can."""
+        n = len(ws)
+        k = ws[0].k
+        assert all(w.k == k for w in ws)
+        dts = (C.c_int * n)(*[w.dtype for w in ws])
+        lays = (C.c_int * n)(*([1] * n))
+        wp = (C.c_void_p * n)(*[w.data.data_ptr() for w in ws])
+        yp = (C.c_void_p * n)(*[y.data_ptr() for y in ys])
+        ns = (C.c_int64 * n)(*[w.n for w in ws])
+        capi.check(self.L.sm100_mul_mat_multi(self.stream, n, dts, lays, wp, k, ns, _dev(x), yp), "mul_mat_multi")
+
     def _reduce(self, t: torch.Tensor):
         if self.world > 1:
             if self.allreduce is not None:
@@ -214,23 +226,16 @@ class DecodeModel:
                 chk(L.sm100_rms_norm(s, _dev(self.x), None, _dev(lw["attn_norm"]), None, _dev(self.xn), c.hidden, 1, c.eps), "rms_norm")
             else:   # residual add of the previous layer's FFN output fused with this norm
                 chk(L.sm100_rms_norm(s, _dev(self.x), _dev(self.proj), _dev(lw["attn_norm"]), _dev(self.x), _dev(self.xn), c.hidden, 1, c.eps), "add_rms_norm")
-            self._mm(lw["wq"], self.xn, self.q)
-            self._mm(lw["wk"], self.xn, self.k)
-            self._mm(lw["wv"], self.xn, self.v)
-            if c.qk_norm:
-                chk(L.sm100_rms_norm(s, _dev(self.q), None, _dev(lw["q_norm"]), None, _dev(self.q), c.head_dim, self.hq, c.eps), "q_norm")
-                chk(L.sm100_rms_norm(s, _dev(self.k), None, _dev(lw["k_norm"]), None, _dev(self.k), c.head_dim, self.hkv, c.eps), "k_norm")
-            chk(L.sm100_rope(s, _dev(self.q), _dev(self.pos), _dev(self.rope), 0, c.n_ctx, _dev(self.q), c.head_dim, self.hq, 1, c.head_dim, 1), "rope q")
-            chk(L.sm100_rope(s, _dev(self.k), _dev(self.pos), _dev(self.rope), 0, c.n_ctx, _dev(self.k), c.head_dim, self.hkv, 1, c.head_dim, 1), "rope k")
-            chk(L.sm100_set_rows(s, _dev(self.k), _dev(self.pos), _dev(lw["k_cache"]), c.head_dim, 1, self.hkv, c.n_ctx), "set_rows k")
-            chk(L.sm100_set_rows(s, _dev(self.v), _dev(self.pos), _dev(lw["v_cache"]), c.head_dim, 1, self.hkv, c.n_ctx), "set_rows v")
+            self._mm_multi([lw["wq"], lw["wk"], lw["wv"]], self.xn, [self.q, self.k, self.v])
+            chk(L.sm100_head_post(s, _dev(self.q), _dev(self.k), _dev(self.v), _dev(lw["q_norm"]) if c.qk_norm else None,
+                                  _dev(lw["k_norm"]) if c.qk_norm else None, _dev(self.pos), _dev(self.rope), 0, c.n_ctx, _dev(lw["k_cache"]),
+                                  _dev(lw["v_cache"]), c.head_dim, self.hq, self.hkv, c.n_ctx, c.eps, c.rope_base, 1), "head_post")
             chk(L.sm100_attention(s, _dev(self.q), _dev(lw["k_cache"]), _dev(lw["v_cache"]), None, 1, _dev(self.att), c.head_dim, c.head_dim, 1, c.n_ctx,
                                   self.hq, self.hkv, 1, 0, _dev(self.pos), scale), "attention")
             self._mm(lw["wo"], self.att, self.proj)
             self._reduce(self.proj)
             chk(L.sm100_rms_norm(s, _dev(self.x), _dev(self.proj), _dev(lw["ffn_norm"]), _dev(self.x), _dev(self.xn), c.hidden, 1, c.eps), "add_rms_norm")
-            self._mm(lw["wgate"], self.xn, self.gate)
-            self._mm(lw["wup"], self.xn, self.up)
+            self._mm_multi([lw["wgate"], lw["wup"]], self.xn, [self.gate, self.up])
             chk(L.sm100_swiglu(s, _dev(self.gate), _dev(self.up), _dev(self.act), self.ffn), "swiglu")
             self._mm(lw["wdown"], self.act, self.proj)
             self._reduce(self.proj)

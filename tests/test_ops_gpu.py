@@ -234,3 +234,47 @@ def test_attention_argument_errors(sm100, stream):
     st = lib.sm100_attention(stream.handle, None, b.at(), b.at(), None, 1, b.at(), 32, 32, 1, 8, 4, 2, 1, 0, None, 1.0)
     assert st == 2
     b.free()
+
+
+@pytest.mark.parametrize("with_norm", [True, False], ids=["qk_norm", "no_norm"])
+def test_head_post_matches_separate_reference_ops(sm100, stream, with_norm):
+    """The fused decode step (per-head RMS_NORM_MUL, ROPE from the table, SET_ROWS_PAIR into the caches) against the
+    oracle's separate ops: 32 query heads, 8 KV heads of 128, cache of 64 rows, positions inside and outside the table."""
+    d, hq, hkv, rows = 128, 32, 8, 64
+    rng = np.random.default_rng(77)
+    qw = rng.standard_normal(d).astype(np.float32)
+    kw = rng.standard_normal(d).astype(np.float32)
+    table_pos = np.arange(16, 48)
+    table = sgref.rope_table(table_pos, d, 1e6)
+    for pos in (16, 40, 47, 5, 63):
+        q = (rng.standard_normal((hq, d)) * 3).astype(np.float32)
+        k = (rng.standard_normal((hkv, d)) * 3).astype(np.float32)
+        v = rng.standard_normal((hkv, d)).astype(np.float32)
+        kc = rng.standard_normal((hkv, rows, d)).astype(np.float32)
+        vc = rng.standard_normal((hkv, rows, d)).astype(np.float32)
+        qn = sgref.rms_norm(q, qw) if with_norm else q
+        kn = sgref.rms_norm(k, kw) if with_norm else k
+        p = np.array([pos], np.int32)
+        want_q = sgref.rope(qn.reshape(1, hq, d), p, d, True, 1e6)[0]
+        want_k = sgref.rope(kn.reshape(1, hkv, d), p, d, True, 1e6)[0]
+        bufs = {n: U.to_device(sm100, stream, a) for n, a in dict(q=q, k=k, v=v, kc=kc, vc=vc, qw=qw, kw=kw, t=table, p=p).items()}
+        sm100.check(sm100.lib().sm100_head_post(stream.handle, bufs["q"].at(), bufs["k"].at(), bufs["v"].at(),
+                                                bufs["qw"].at() if with_norm else None, bufs["kw"].at() if with_norm else None,
+                                                bufs["p"].at(), bufs["t"].at(), 16, len(table_pos), bufs["kc"].at(), bufs["vc"].at(),
+                                                d, hq, hkv, rows, 1e-6, 1e6, 1), "head_post")
+        stream.sync()
+        got_q = bufs["q"].download(stream, np.float32, q.size).reshape(q.shape)
+        got_k = bufs["k"].download(stream, np.float32, k.size).reshape(k.shape)
+        got_kc = bufs["kc"].download(stream, np.float32, kc.size).reshape(kc.shape)
+        got_vc = bufs["vc"].download(stream, np.float32, vc.size).reshape(vc.shape)
+        in_table = 16 <= pos < 48
+        tol = 1e-12 if in_table else TOL   # outside the table the device evaluates cosf / sinf itself
+        assert sgref.nmse(got_q, want_q) <= tol and sgref.nmse(got_k, want_k) <= tol
+        if in_table and not with_norm:
+            assert np.array_equal(got_q, want_q) and np.array_equal(got_k, want_k)
+        want_kc, want_vc = kc.copy(), vc.copy()
+        want_kc[:, pos] = got_k
+        want_vc[:, pos] = v
+        assert np.array_equal(got_kc, want_kc) and np.array_equal(got_vc, want_vc)
+        for b in bufs.values():
+            b.free()
