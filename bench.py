@@ -145,6 +145,9 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     stream = capi.Stream(local_rank)
     if args.no_pdl:
         L.sm100_set_pdl(0)
+    if args.gemm_only:
+        print(json.dumps({"gemm_only": True, **prefill_gemm(capi, stream, reps=5)}), flush=True)
+        return None
     if args.decode_only:
         # profiler runs of the layer-stack decode alone (single GPU): a few tokens, one line
         d = run_decode(args, rank, world, local_rank, None, stream_sync=stream.sync)
@@ -307,11 +310,11 @@ def run_ours(args, rank: int, world: int, local_rank: int):
             "gpu_launches": int(launches_timed),
             "e2e": {"value": round(world * step_bytes / (e2e_ms * 1e-3) / 1e9, 1), "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "ms_per_step": round(e2e_ms, 4), "note": "host activations in / host results out per matvec, weights resident"},
-            "roofline": {"bound": "hbm", "kernel": "matvec_q4k_mma<1,true>", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
+            "roofline": {"bound": "hbm", "kernel": "matvec_q4k_imma<1,2>", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
                          "frac": round(achieved / peak, 4), "peak_source": peak_src, "bytes_per_launch": round(per_launch_bytes, 1),
                          "us_per_launch": round(per_launch_us, 3),
-                         # dram__bytes_read + write per launch, mean of the three shapes of one ncu capture (profiles/matvec_q4k_mma_q4k_sweep.md)
-                         "traffic": 22071125},
+                         # dram__bytes_read + write per launch, mean of the three shapes of one ncu capture (profiles/matvec_q4k_imma_q4k_sweep.md)
+                         "traffic": 22069760},
             "cpu_baseline": cpu,
             "clocks": clocks,
         }
@@ -455,6 +458,7 @@ def main():
     ap.add_argument("--decode-steps", type=int, default=128)
     ap.add_argument("--no-decode", action="store_true", help="skip the layer-stack decode measurement")
     ap.add_argument("--no-pdl", action="store_true", help="launch without programmatic dependent launch (profiler runs)")
+    ap.add_argument("--gemm-only", action="store_true", help="Q8_0 prefill GEMM shapes only, single GPU: for profiler runs")
     ap.add_argument("--decode-only", action="store_true", help="layer-stack decode only, single GPU: for profiler runs")
     ap.add_argument("--quick", action="store_true", help="headline sweep only (no per-shape detail, e2e, CPU baseline, decode): for profiler runs")
     args = ap.parse_args()
