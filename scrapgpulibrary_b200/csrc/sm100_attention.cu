@@ -11,6 +11,7 @@
 // scratch buffer; kernel 2 merges the splits.  HBM-bound: algorithmic bytes = 2 * 4 * D * visible keys * Hkv.
 #include "sm100_common.cuh"
 
+#include <cstdlib>
 #include <mutex>
 #include <vector>
 
@@ -23,6 +24,7 @@ constexpr int ATT_THREADS = 256;
 struct AttnArgs {
     const float * q; const float * k; const float * v; const float * mask; float * out; float * scratch;
     const int32_t * positions;
+    int * counters;   // one per (query, KV head): splits that have delivered their partial (fused merge), or null
     int64_t d, dv, nq, nk, hq, hkv, offset;
     int64_t mask_heads;
     int splits, chunk, causal;
@@ -53,9 +55,12 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_partial_kernel(AttnArgs a) {
     float * sred = ss + (int64_t) group * a.chunk;      // [2][group][dv] partial accumulators of the two key halves
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
 
+    // the visible keys (known only on the device when the offset comes from `positions`) are spread evenly over
+    // the splits; the planned chunk is the upper bound the shared memory was sized for
     const int64_t n_vis = visible_keys(a, q);
-    const int64_t k0 = (int64_t) split * a.chunk;
-    const int64_t k1 = k0 + a.chunk < n_vis ? k0 + a.chunk : n_vis;
+    const int64_t chunk = (n_vis + a.splits - 1) / a.splits;
+    const int64_t k0 = (int64_t) split * chunk;
+    const int64_t k1 = k0 + chunk < n_vis ? k0 + chunk : n_vis;
     const int64_t count = k1 > k0 ? k1 - k0 : 0;
 
     for (int64_t i = tid; i < (int64_t) group * a.d; i += blockDim.x) {
@@ -147,24 +152,20 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_partial_kernel(AttnArgs a) {
     }
 }
 
-// Merge of the splits of one (query, head): thread s first turns split s's (m, l) into its weight
-// exp(m_s - m) / l in shared memory (one round of independent loads), then the threads cover dv and sum the
-// weighted partial accumulators, again with independent loads.
+// Merge of the splits of one (query, head), by one CTA: thread s first turns split s's (m, l) into its weight
+// exp(m_s - m) in shared memory (one round of independent loads), then the threads cover dv and sum the weighted
+// partial accumulators, again with independent loads.  Loads bypass L1: the partials may come from other CTAs of
+// the same launch.
 constexpr int ATT_MAX_SPLITS = 1024;
 
-__global__ void attn_combine_kernel(AttnArgs a) {
-    pdl_wait();
-    pdl_launch_dependents();
-    __shared__ float s_w[ATT_MAX_SPLITS];
-    __shared__ float s_red[2][32];
-    const int64_t h = blockIdx.x, q = blockIdx.y;
+__device__ __forceinline__ void attn_merge_head(const AttnArgs & a, int64_t q, int64_t h, float * s_w, float (*s_red)[32]) {
     const float * base = a.scratch + scratch_index(a, q, h, 0);
     const int64_t stride = a.dv + 2;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
-    // block-wide max of m, then sum of l exp(m_s - m)
+    __syncthreads();   // s_w / s_red may still be read from a previous head
     float m = -INFINITY;
     for (int s = tid; s < a.splits; s += blockDim.x) {
-        const float ms = base[s * stride];
+        const float ms = __ldcg(base + s * stride);
         s_w[s] = ms;
         m = fmaxf(m, ms);
     }
@@ -179,7 +180,7 @@ __global__ void attn_combine_kernel(AttnArgs a) {
         const float ms = s_w[s];
         const float e = ms != -INFINITY ? expf(ms - m) : 0.f;
         s_w[s] = e;
-        if (ms != -INFINITY) l += base[s * stride + 1] * e;
+        if (ms != -INFINITY) l += __ldcg(base + s * stride + 1) * e;
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) l += __shfl_xor_sync(0xffffffffu, l, o);
@@ -190,15 +191,206 @@ __global__ void attn_combine_kernel(AttnArgs a) {
     for (int64_t dvi = tid; dvi < a.dv; dvi += blockDim.x) {
         float o = 0.f;
         if (m != -INFINITY) {
+            // unconditional loads (every split wrote its accumulator, zeros if it had no key): they pipeline
 #pragma unroll 8
-            for (int s = 0; s < a.splits; ++s) {
-                const float e = s_w[s];
-                if (e != 0.f) o = fmaf(base[s * stride + 2 + dvi], e, o);
-            }
+            for (int s = 0; s < a.splits; ++s) o = fmaf(__ldcg(base + s * stride + 2 + dvi), s_w[s], o);
             o = o / l;
         }
         a.out[(h * a.nq + q) * a.dv + dvi] = o;
     }
+}
+
+// The same merge for the G heads of a KV group at once, by the CTA that delivered the group's last partial
+// (splits <= ATT_FUSED_SPLITS): warp g reduces head g's (m, l) over the splits, then the threads cover (head, dv).
+constexpr int ATT_FUSED_SPLITS = 128;
+
+template <int G>
+__device__ __forceinline__ void attn_merge_group(const AttnArgs & a, int64_t q, int64_t hk, float * s_w, float * s_l) {
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int64_t stride = a.dv + 2;
+    if (warp < G) {
+        const float * base = a.scratch + scratch_index(a, q, hk * G + warp, 0);
+        float m = -INFINITY;
+        for (int s = lane; s < a.splits; s += 32) {
+            const float ms = __ldcg(base + s * stride);
+            s_w[warp * ATT_FUSED_SPLITS + s] = ms;
+            m = fmaxf(m, ms);
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+        float l = 0.f;
+        for (int s = lane; s < a.splits; s += 32) {
+            const float ms = s_w[warp * ATT_FUSED_SPLITS + s];
+            const float e = ms != -INFINITY ? expf(ms - m) : 0.f;
+            s_w[warp * ATT_FUSED_SPLITS + s] = e;
+            l = fmaf(__ldcg(base + s * stride + 1), e, l);
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) l += __shfl_xor_sync(0xffffffffu, l, o);
+        if (lane == 0) s_l[warp] = m == -INFINITY ? 0.f : l;   // 0: no visible key at all
+    }
+    __syncthreads();
+    for (int item = tid; item < G * (int) a.dv; item += blockDim.x) {
+        const int g = item / (int) a.dv, dvi = item - g * (int) a.dv;
+        const float * base = a.scratch + scratch_index(a, q, hk * G + g, 0) + 2 + dvi;
+        const float l = s_l[g];
+        float o = 0.f;
+        if (l != 0.f) {
+#pragma unroll 8
+            for (int s = 0; s < a.splits; ++s) o = fmaf(__ldcg(base + s * stride), s_w[g * ATT_FUSED_SPLITS + s], o);
+            o = o / l;
+        }
+        a.out[((hk * G + g) * a.nq + q) * a.dv + dvi] = o;
+    }
+}
+
+__global__ void attn_combine_kernel(AttnArgs a) {
+    pdl_wait();
+    pdl_launch_dependents();
+    __shared__ float s_w[ATT_MAX_SPLITS];
+    __shared__ float s_red[2][32];
+    attn_merge_head(a, blockIdx.y, blockIdx.x, s_w, s_red);
+}
+
+// Single-pass partial for head dimensions that are multiples of 128 (D = Dv = 128 D4) and G = 1, 2, 4 or 8 query
+// heads per KV head.  A warp takes every 8th key of the split: the key's K and V rows are requested together
+// (one float4 per lane and 128 elements), the scores of the G heads are warp-reduced, and a running
+// (max, sum, accumulator) per head is updated in registers (online softmax) - one trip to memory per key instead of
+// the three phases of the generic kernel.  The 8 warps are merged through shared memory into the split's partial;
+// the CTA that delivers the last partial of a (query, KV head) merges the splits right away (counter in global
+// memory, reset for the next call), so no second launch is needed.
+template <int G, int D4>
+__global__ void __launch_bounds__(ATT_THREADS) attn_fast_kernel(AttnArgs a) {
+    pdl_wait();
+    pdl_launch_dependents();
+    constexpr int D = 128 * D4;
+    extern __shared__ float smem[];   // [8 warps][G][D + 2]
+    __shared__ float s_w[ATT_MAX_SPLITS];
+    __shared__ float s_red[2][32];
+    __shared__ int s_last;
+    const int split = blockIdx.x;
+    const int64_t hk = blockIdx.y, q = blockIdx.z;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    constexpr int NW = ATT_THREADS / 32;
+
+    // the visible keys (known only on the device when the offset comes from `positions`) are spread evenly over the splits
+    const int64_t n_vis = visible_keys(a, q);
+    const int64_t chunk = (n_vis + a.splits - 1) / a.splits;
+    const int64_t k0 = (int64_t) split * chunk;
+    const int64_t k1 = k0 + chunk < n_vis ? k0 + chunk : n_vis;
+    const int count = k1 > k0 ? (int) (k1 - k0) : 0;
+
+    float4 qr[G][D4];
+#pragma unroll
+    for (int g = 0; g < G; ++g)
+#pragma unroll
+        for (int i = 0; i < D4; ++i) qr[g][i] = reinterpret_cast<const float4 *>(a.q + ((hk * G + g) * a.nq + q) * D)[lane + 32 * i];
+
+    float m[G], l[G];
+    float4 o[G][D4];
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+        m[g] = -INFINITY;
+        l[g] = 0.f;
+#pragma unroll
+        for (int i = 0; i < D4; ++i) o[g][i] = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    const float4 * kbase = reinterpret_cast<const float4 *>(a.k + (hk * a.nk + k0) * D) + lane;
+    const float4 * vbase = reinterpret_cast<const float4 *>(a.v + (hk * a.nk + k0) * D) + lane;
+    for (int kk = warp; kk < count; kk += 2 * NW) {
+        // two keys per trip: four independent row requests in flight
+        const bool second = kk + NW < count;
+        float4 kv[2][D4], vv[2][D4];
+#pragma unroll
+        for (int i = 0; i < D4; ++i) {
+            kv[0][i] = kbase[(int64_t) kk * (D / 4) + 32 * i];
+            vv[0][i] = vbase[(int64_t) kk * (D / 4) + 32 * i];
+            kv[1][i] = second ? kbase[(int64_t) (kk + NW) * (D / 4) + 32 * i] : make_float4(0.f, 0.f, 0.f, 0.f);
+            vv[1][i] = second ? vbase[(int64_t) (kk + NW) * (D / 4) + 32 * i] : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            if (u == 1 && !second) break;
+            const int key = kk + u * NW;
+#pragma unroll
+            for (int g = 0; g < G; ++g) {
+                float sc = 0.f;
+#pragma unroll
+                for (int i = 0; i < D4; ++i)
+                    sc += (kv[u][i].x * qr[g][i].x + kv[u][i].y * qr[g][i].y) + (kv[u][i].z * qr[g][i].z + kv[u][i].w * qr[g][i].w);
+#pragma unroll
+                for (int sh = 16; sh > 0; sh >>= 1) sc += __shfl_xor_sync(0xffffffffu, sc, sh);
+                sc *= a.scale;
+                if (a.mask != nullptr) {
+                    const int64_t mh = a.mask_heads == 1 ? 0 : hk * G + g;
+                    sc += a.mask[(mh * a.nq + q) * a.nk + k0 + key];
+                }
+                if (sc > m[g]) {   // warp-uniform: every lane holds the same score
+                    const float corr = m[g] == -INFINITY ? 0.f : expf(m[g] - sc);
+                    l[g] *= corr;
+#pragma unroll
+                    for (int i = 0; i < D4; ++i) {
+                        o[g][i].x *= corr; o[g][i].y *= corr; o[g][i].z *= corr; o[g][i].w *= corr;
+                    }
+                    m[g] = sc;
+                }
+                const float pr = sc == -INFINITY ? 0.f : expf(sc - m[g]);
+                l[g] += pr;
+#pragma unroll
+                for (int i = 0; i < D4; ++i) {
+                    o[g][i].x = fmaf(pr, vv[u][i].x, o[g][i].x);
+                    o[g][i].y = fmaf(pr, vv[u][i].y, o[g][i].y);
+                    o[g][i].z = fmaf(pr, vv[u][i].z, o[g][i].z);
+                    o[g][i].w = fmaf(pr, vv[u][i].w, o[g][i].w);
+                }
+            }
+        }
+    }
+    // warps -> shared memory
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+        float * dst = smem + (warp * G + g) * (D + 2);
+        if (lane == 0) {
+            dst[0] = m[g];
+            dst[1] = l[g];
+        }
+#pragma unroll
+        for (int i = 0; i < D4; ++i) {
+            const int e = (lane + 32 * i) * 4;
+            dst[2 + e] = o[g][i].x; dst[3 + e] = o[g][i].y; dst[4 + e] = o[g][i].z; dst[5 + e] = o[g][i].w;
+        }
+    }
+    __syncthreads();
+    // merge the warps into the split's partial [m, l, o[D]] per head
+    for (int item = tid; item < G * D; item += ATT_THREADS) {
+        const int g = item / D, e = item - g * D;
+        float mm = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < NW; ++w) mm = fmaxf(mm, smem[(w * G + g) * (D + 2)]);
+        float ll = 0.f, oo = 0.f;
+#pragma unroll
+        for (int w = 0; w < NW; ++w) {
+            const float * src = smem + (w * G + g) * (D + 2);
+            const float f = src[0] == -INFINITY ? 0.f : expf(src[0] - mm);
+            ll = fmaf(src[1], f, ll);
+            oo = fmaf(src[2 + e], f, oo);
+        }
+        float * dst = a.scratch + scratch_index(a, q, hk * G + g, split);
+        if (e == 0) {
+            dst[0] = mm;
+            dst[1] = ll;
+        }
+        dst[2 + e] = oo;
+    }
+    if (a.counters == nullptr) return;   // the caller merges with a second launch
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) s_last = atomicAdd(a.counters + q * a.hkv + hk, 1) == a.splits - 1 ? 1 : 0;
+    __syncthreads();
+    if (s_last == 0) return;
+    __threadfence();
+    attn_merge_group<G>(a, q, hk, s_w, &s_red[0][0]);
+    if (tid == 0) a.counters[q * a.hkv + hk] = 0;
 }
 
 int device_scratch(int slot, size_t bytes, void ** out);
@@ -210,14 +402,46 @@ static int workspace(size_t bytes, float ** out) {
     return st;
 }
 
-int attention_launch(cudaStream_t s, AttnArgs a) {
+constexpr int ATT_COUNTER_SLOTS = 16384;   // ints at the start of the scratch: one per (query, KV head) of a call
+
+template <int G, int D4>
+static int launch_fast(cudaStream_t s, const AttnArgs & a) {
+    const size_t smem = (size_t) (ATT_THREADS / 32) * G * (128 * D4 + 2) * sizeof(float);
+    if (smem > 48 * 1024) SM100_CUDA(cudaFuncSetAttribute(attn_fast_kernel<G, D4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024));
+    return launch(attn_fast_kernel<G, D4>, dim3((unsigned) a.splits, (unsigned) a.hkv, (unsigned) a.nq), dim3(ATT_THREADS), smem, s, a);
+}
+
+// `scratch` is the raw scratch area: counters first, partials behind them
+int attention_launch(cudaStream_t s, AttnArgs a, float * scratch) {
     const int group = (int) (a.hq / a.hkv);
-    const size_t smem = ((size_t) group * a.d + (size_t) group * a.chunk + (size_t) group * a.dv) * sizeof(float);
-    if (smem > 48 * 1024) {
-        SM100_CUDA(cudaFuncSetAttribute(attn_partial_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
+    a.counters = nullptr;
+    a.scratch = scratch + ATT_COUNTER_SLOTS;
+    static const int use_fast = [] { const char * e = getenv("SM100_ATTN_FAST"); return e != nullptr ? atoi(e) : 1; }();
+    const bool aligned = (((uintptr_t) a.q | (uintptr_t) a.k | (uintptr_t) a.v) & 15) == 0;
+    if (use_fast && a.d == a.dv && (a.d == 128 || a.d == 256) && aligned && (group == 1 || group == 2 || group == 4 || group == 8)) {
+        const bool fused = a.nq * a.hkv <= ATT_COUNTER_SLOTS && a.splits <= ATT_FUSED_SPLITS;
+        if (fused) a.counters = reinterpret_cast<int *>(scratch);
+        int st;
+        const int d4 = (int) (a.d / 128);
+        switch (group * 10 + d4) {
+            case 11: st = launch_fast<1, 1>(s, a); break;
+            case 12: st = launch_fast<1, 2>(s, a); break;
+            case 21: st = launch_fast<2, 1>(s, a); break;
+            case 22: st = launch_fast<2, 2>(s, a); break;
+            case 41: st = launch_fast<4, 1>(s, a); break;
+            case 42: st = launch_fast<4, 2>(s, a); break;
+            case 81: st = launch_fast<8, 1>(s, a); break;
+            default: st = launch_fast<8, 2>(s, a); break;
+        }
+        if (st != ST_OK || fused) return st;
+    } else {
+        const size_t smem = ((size_t) group * a.d + (size_t) group * a.chunk + (size_t) group * a.dv) * sizeof(float);
+        if (smem > 48 * 1024) {
+            SM100_CUDA(cudaFuncSetAttribute(attn_partial_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
+        }
+        const int st = launch(attn_partial_kernel, dim3((unsigned) a.splits, (unsigned) a.hkv, (unsigned) a.nq), dim3(ATT_THREADS), smem, s, a);
+        if (st != ST_OK) return st;
     }
-    int st = launch(attn_partial_kernel, dim3((unsigned) a.splits, (unsigned) a.hkv, (unsigned) a.nq), dim3(ATT_THREADS), smem, s, a);
-    if (st != ST_OK) return st;
     const int ct = a.dv >= 256 ? 256 : a.dv >= 128 ? 128 : 64;
     return launch(attn_combine_kernel, dim3((unsigned) a.hq, (unsigned) a.nq), dim3(ct), 0, s, a);
 }
@@ -233,7 +457,9 @@ int attention_check(const AttnArgs & a) {
     return ST_OK;
 }
 
-size_t attention_scratch_bytes(const AttnArgs & a) { return (size_t) a.nq * a.hq * a.splits * (a.dv + 2) * sizeof(float); }
+size_t attention_scratch_bytes(const AttnArgs & a) {
+    return ((size_t) ATT_COUNTER_SLOTS + (size_t) a.nq * a.hq * a.splits * (a.dv + 2)) * sizeof(float);
+}
 
 void attention_plan(AttnArgs & a) {
     // enough splits to occupy the SMs, at most ATT_CHUNK keys per split
@@ -265,8 +491,7 @@ extern "C" int sm100_attention(sm100_stream_t s, const float * q, const float * 
     float * ws = nullptr;
     const int sw = workspace(attention_scratch_bytes(a), &ws);
     if (sw != ST_OK) return sw;
-    a.scratch = ws;
-    return attention_launch((cudaStream_t) s, a);
+    return attention_launch((cudaStream_t) s, a, ws);
 }
 
 
@@ -329,8 +554,7 @@ extern "C" int sm100_attention_static(sm100_stream_t s, const float * q, const f
     float * ws = nullptr;
     const int sw = static_scratch(&ws);
     if (sw != ST_OK) return sw;
-    a.scratch = ws;
-    return attention_launch((cudaStream_t) s, a);
+    return attention_launch((cudaStream_t) s, a, ws);
 }
 
 extern "C" size_t sm100_attention_static_capacity(void) { return sm100::ATT_STATIC_FLOATS * sizeof(float); }

@@ -67,6 +67,7 @@ int device_scratch(int slot, size_t bytes, void ** out) {
         e.size[slot] = 0;
         const size_t want = bytes < (size_t) (8u << 20) ? (size_t) (8u << 20) : bytes;
         SM100_CUDA(cudaMalloc(&e.ptr[slot], want));
+        SM100_CUDA(cudaMemset(e.ptr[slot], 0, want));   // the attention kernels keep counters in it that start at zero
         e.size[slot] = want;
     }
     *out = e.ptr[slot];

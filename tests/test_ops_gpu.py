@@ -278,3 +278,25 @@ def test_head_post_matches_separate_reference_ops(sm100, stream, with_norm):
         assert np.array_equal(got_kc, want_kc) and np.array_equal(got_vc, want_vc)
         for b in bufs.values():
             b.free()
+
+
+@pytest.mark.parametrize("hq,hkv,d,nk,nq", [(8, 8, 128, 300, 1), (8, 4, 128, 777, 2), (32, 8, 128, 1500, 1), (16, 2, 256, 130, 3), (4, 4, 256, 64, 1)],
+                         ids=lambda v: str(v))
+def test_attention_single_pass_kernel(sm100, stream, hq, hkv, d, nk, nq):
+    """Head dimensions 128 / 256 with 1, 2, 4, 8 query heads per KV head take the single-pass kernel with the merge
+    of the splits folded in: causal with an offset (from the host and from the device), full, and masked."""
+    rng = np.random.default_rng(hq * 1000 + nk)
+    q = rng.standard_normal((hq, nq, d)).astype(np.float32)
+    k = rng.standard_normal((hkv, nk, d)).astype(np.float32)
+    v = rng.standard_normal((hkv, nk, d)).astype(np.float32)
+    s = float(1.0 / np.sqrt(d))
+    off = nk - nq - 7
+    want = sgref.attention(q, k, v, True, off, s)
+    assert sgref.nmse(run_attention(sm100, stream, q, k, v, True, off, s), want) <= TOL
+    assert sgref.nmse(run_attention(sm100, stream, q, k, v, True, 0, s, positions=[off]), want) <= TOL
+    # twice in a row: the merge counters of the first call must be back at zero
+    assert sgref.nmse(run_attention(sm100, stream, q, k, v, False, 0, s), sgref.attention(q, k, v, False, 0, s)) <= TOL
+    mask = np.zeros((1, nq, nk), np.float32)
+    mask[0, :, nk // 3:] = -np.inf
+    got = run_attention(sm100, stream, q, k, v, False, 0, s, mask=mask, mask_heads=1)
+    assert sgref.nmse(got, sgref.attention(q, k[:, :nk // 3], v[:, :nk // 3], False, 0, s)) <= TOL
