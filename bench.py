@@ -261,6 +261,9 @@ def run_ours(args, rank: int, world: int, local_rank: int):
             b = sum(algorithmic_bytes(dtype, pool[s]["k"], pool[s]["n"], m) for s, _ in order)
             detail[f"q4_k_sweep_m{m}_gbps"] = round(b * sub_steps / (m_ms * 1e-3) / 1e9, 1)
 
+        # ---- the other decode formats: Q6_K over the same shapes, the Q4_0 case, the Q6_K vocabulary head ----
+        detail.update(other_formats(capi, stream))
+
         # ---- prefill GEMM (tensor cores): Q8_0, M = 512 tokens, K = 4096, N in {4096, 12288} ----
         detail.update(prefill_gemm(capi, stream))
 
@@ -320,6 +323,51 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         }
     if dist is not None:
         dist.barrier()
+    return out
+
+
+def other_formats(capi, stream, reps: int = 20):
+    """Algorithmic GB/s at M = 1 of the formats beside the headline: Q6_K on the three projection shapes, Q4_0
+    4096 x 4096, and the Q6_K vocabulary head (4096 x 151936).  Weights rotate through enough distinct tensors to
+    exceed L2 (the head is 510 MB on its own); graph replay of `reps` rounds."""
+    from scrapgpulibrary_b200 import synth
+    out = {}
+    L = capi.lib()
+    cases = [("q6_k", 33, 4096, 4096, 12), ("q6_k", 33, 4096, 12288, 5), ("q6_k", 33, 12288, 4096, 5), ("q4_0", 16, 4096, 4096, 16), ("q8_0", 17, 4096, 4096, 10),
+             ("q6_k_head", 33, 4096, 151936, 1)]
+    for name, dtype, k, n, copies in cases:
+        base = synth.quantized_matrix(dtype, 40 + dtype + n % 97, min(n, 16384), k)
+        if n > base.shape[0]:
+            base = np.tile(base, (-(-n // base.shape[0]), 1))[:n]
+        staging = capi.Buffer(base.nbytes)
+        mats = []
+        for c in range(copies):
+            staging.upload(stream, np.roll(base, c * 17, axis=0) if c else base)
+            dst = capi.Buffer(base.nbytes)
+            capi.check(L.sm100_pack_device(stream.handle, dtype, k, n, staging.at(), dst.at()), "pack_device")
+            stream.sync()
+            mats.append(dst)
+        staging.free()
+        x = capi.Buffer(4 * k)
+        x.upload(stream, np.random.default_rng(k).standard_normal(k).astype(np.float32))
+        y = capi.Buffer(4 * n)
+        with capi.Graph(stream) as g:
+            for m in mats:
+                capi.mul_mat(stream, dtype, 1, m, k, n, x, 1, y)
+        for _ in range(3):
+            g.launch()
+        e0, e1 = capi.Event(), capi.Event()
+        e0.record(stream)
+        for _ in range(reps):
+            g.launch()
+        e1.record(stream)
+        e1.sync()
+        ms = e0.elapsed_ms(e1) / (reps * copies)
+        g.destroy()
+        key = f"{name}_k{k}_n{n}_m1_gbps"
+        out[key] = round(algorithmic_bytes(dtype, k, n) / (ms * 1e-3) / 1e9, 1)
+        for b in mats + [x, y]:
+            b.free()
     return out
 
 

@@ -20,6 +20,7 @@
 
 namespace sm100 {
 
+int matvec_b32_imma_tiles(cudaStream_t s, int dtype, const void * w, int64_t k, int64_t n, const float * x, float * y, bool * handled);
 int matvec_q4k_imma_tiles(cudaStream_t s, const void * w, int64_t k, int64_t n, const float * x, int64_t ldx, int64_t m, float * y, int64_t ldy,
                           bool * handled);
 int matvec_q4k_tiles(cudaStream_t s, const void * w, int64_t k, int64_t n, const float * x, int64_t ldx, int64_t m, float * y, int64_t ldy,
@@ -495,6 +496,18 @@ int matvec(cudaStream_t s, int dtype, int layout, const void * w, int64_t w_row_
             const int64_t full = (n / 16) * 16;
             if (full < n) return launch_rows<UnitQ4K, true>(s, w, 0, k, n, x, ldx, m, y, ldy, full);
             return ST_OK;
+        }
+    }
+    static const int use_b32 = env_int("SM100_B32_IMMA", 1);
+    if (use_b32 && layout == LAYOUT_PACKED && (dtype == DT_Q4_0 || dtype == DT_Q8_0) && x_aligned && m == 1) {
+        bool handled = false;
+        const int st = matvec_b32_imma_tiles(s, dtype, w, k, n, x, y, &handled);
+        if (st != ST_OK) return st;
+        if (handled) {
+            const int64_t full = (n / 16) * 16;
+            if (full == n) return ST_OK;
+            return dtype == DT_Q4_0 ? launch_rows<UnitQ40, true>(s, w, 0, k, n, x, ldx, m, y, ldy, full)
+                                    : launch_rows<UnitQ80, true>(s, w, 0, k, n, x, ldx, m, y, ldy, full);
         }
     }
     static const int use_mma = env_int("SM100_Q4K_MMA", 1);

@@ -69,13 +69,11 @@ __device__ __forceinline__ void imma_16832(int (&c)[4], uint32_t a0, uint32_t a1
 // One row's share of a block for lane t: header words -> d, dmin and the scale field of sub-blocks 2t, 2t+1;
 // clo / chi = (H, L) integer dot products of the low / high nibble sub-block (chi carries a factor 16).
 // sq = (s_2t, sum_x_2t, s_2t+1, sum_x_2t+1).
-__device__ __forceinline__ float iq_row_term(const uint4 & h, int t, int clo_h, int clo_l, int chi_h, int chi_l, const float4 & sq) {
-    const __half2 dd = *reinterpret_cast<const __half2 *>(&h.x);
-    const float2 df = __half22float2(dd);   // d, dmin
-    // the 24-bit field t starts at bit 24 t of the 96-bit string (h.y, h.z, h.w)
-    const uint32_t lo = t < 2 ? h.y : (t == 2 ? h.z : h.w);
-    const uint32_t hi = t == 1 ? h.z : h.w;
-    const uint32_t f = __funnelshift_r(lo, hi, (24 * t) & 31);
+struct IqHdr { uint32_t dd, f0, f1; };   // (d, dmin) halves; the two words around the lane's scale field
+
+__device__ __forceinline__ float iq_row_term(const IqHdr & h, uint32_t shift, int clo_h, int clo_l, int chi_h, int chi_l, const float4 & sq) {
+    const float2 df = __half22float2(*reinterpret_cast<const __half2 *>(&h.dd));   // d, dmin
+    const uint32_t f = __funnelshift_r(h.f0, h.f1, shift);
     const int sc0 = (int) (f & 63u), m0 = (int) ((f >> 6) & 63u), sc1 = (int) ((f >> 12) & 63u), m1 = (int) ((f >> 18) & 63u);
     const int v0 = clo_h * 256 + clo_l;          // exact: |v0| < 2^24
     const int v1 = (chi_h * 256 + chi_l) >> 4;   // exact: every term is a multiple of 16
@@ -116,6 +114,11 @@ __device__ __forceinline__ void iq_cp_async16(uint32_t dst, const void * src) {
 __device__ __forceinline__ void iq_cp_async_arrive(uint32_t bar) {
     asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
 }
+__device__ __forceinline__ uint32_t iq_lds32(uint32_t addr) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
+}
 __device__ __forceinline__ uint4 iq_lds128(uint32_t addr) {
     uint4 v;
     asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
@@ -146,7 +149,8 @@ __device__ int g_iq_fault;
 // The first R chunks are requested before griddepcontrol.wait: weights do not depend on the predecessor kernel.
 // NB = 256-weight blocks per chunk: 2 with one CTA per SM, or 1 with two CTAs per SM (more warps to hide latencies,
 // and one CTA's barriers overlap the other's arithmetic).
-template <int M, int NB>
+// FULL: K is a whole number of chunks (no block-range checks in the loops).
+template <int M, int NB, bool FULL>
 __global__ void __launch_bounds__(IQ_THREADS, NB == 1 ? 2 : 1) matvec_q4k_imma(IqArgs p) {
     constexpr int IQ_TILES = 4 * NB;                    // pair tiles (64 weights each) per chunk
     constexpr uint32_t IQ_SLOT_BYTES = IQ_TILES * 512;  // weight tiles of one chunk
@@ -176,22 +180,25 @@ __global__ void __launch_bounds__(IQ_THREADS, NB == 1 ? 2 : 1) matvec_q4k_imma(I
     }
     __syncwarp();
 
-    // requests the chunk (rt, chunk) into slot s
+    // requests the chunk (rt, chunk) into slot s.  Per-lane constants keep the address work to a few operations.
+    const uint32_t rt_tile_bytes = (uint32_t) p.pairs * 512u;         // tiles of one row tile
+    const uint32_t rt_hdr_bytes = (uint32_t) p.blocks * 256u;         // headers of one row tile (16 rows)
+    const uint32_t lane_hdr_off = (uint32_t) (lane & 15) * (uint32_t) p.blocks * 16u + (uint32_t) (lane >> 4) * 16u;
     auto request = [&](int rt_global, int chunk, int s) {
-        const int tiles = p.pairs - chunk * IQ_TILES < IQ_TILES ? p.pairs - chunk * IQ_TILES : IQ_TILES;
         int ti, rt;
         iq_locate(p, rt_global, ti, rt);
         const uint8_t * wbase = p.w[ti];
+        const uint32_t bar = bar0 + 8 * s;
         if (lane == 0) {
+            const int tiles = FULL ? IQ_TILES : (p.pairs - chunk * IQ_TILES < IQ_TILES ? p.pairs - chunk * IQ_TILES : IQ_TILES);
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // earlier reads of the slot precede the copy's writes
-            iq_bar_expect_tx(bar0 + 8 * s, (uint32_t) tiles * 512);
-            iq_bulk_g2s(ring0 + s * IQ_SLOT_BYTES, wbase + ((int64_t) rt * p.pairs + (int64_t) chunk * IQ_TILES) * 512, (uint32_t) tiles * 512,
-                        bar0 + 8 * s);
+            iq_bar_expect_tx(bar, (uint32_t) tiles * 512);
+            iq_bulk_g2s(ring0 + s * IQ_SLOT_BYTES, wbase + (uint64_t) rt * rt_tile_bytes + (uint32_t) chunk * IQ_SLOT_BYTES, (uint32_t) tiles * 512, bar);
         }
-        const int blk = NB * chunk + (lane >> 4);
-        if (lane < 16 * NB && blk < p.blocks)
-            iq_cp_async16(hdr0 + s * IQ_HDR_BYTES + lane * 16, wbase + p.h_off[ti] + (((int64_t) rt * 16 + (lane & 15)) * p.blocks + blk) * 16);
-        iq_cp_async_arrive(bar0 + 8 * s);
+        if (lane < 16 * NB && (FULL || NB * chunk + (lane >> 4) < p.blocks))
+            iq_cp_async16(hdr0 + s * IQ_HDR_BYTES + lane * 16,
+                          wbase + p.h_off[ti] + (uint64_t) rt * rt_hdr_bytes + lane_hdr_off + (uint32_t) chunk * (NB * 16u));
+        iq_cp_async_arrive(bar);
     };
 
     // issue cursor: runs R chunks ahead of the consume cursor over the same sequence
@@ -223,17 +230,14 @@ __global__ void __launch_bounds__(IQ_THREADS, NB == 1 ? 2 : 1) matvec_q4k_imma(I
             sum += __shfl_xor_sync(0xffffffffu, sum, o);
         }
         const bool some = amax > 1e-30f;   // below that the block counts as zero
-        const float inv = some ? 32512.0f / amax : 0.0f;
+        const float inv = some ? __fdividef(32512.0f, amax) : 0.0f;
         const float s = some ? amax * (1.0f / 32512.0f) : 0.0f;
-        const int xi[4] = {__float2int_rn(v.x * inv), __float2int_rn(v.y * inv), __float2int_rn(v.z * inv), __float2int_rn(v.w * inv)};
-        uint32_t hp = 0, lp = 0;
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-            const int lo = ((xi[e] + 128) & 255) - 128;
-            const int hi = (xi[e] - lo) >> 8;
-            hp |= ((uint32_t) hi & 255u) << (8 * e);
-            lp |= ((uint32_t) lo & 255u) << (8 * e);
-        }
+        // 16-bit integer = 256 h + l with h, l signed bytes: h = (x + 128) >> 8, l = x - 256 h
+        const int x0 = __float2int_rn(v.x * inv), x1 = __float2int_rn(v.y * inv), x2 = __float2int_rn(v.z * inv), x3 = __float2int_rn(v.w * inv);
+        const int h0 = (x0 + 128) >> 8, h1 = (x1 + 128) >> 8, h2 = (x2 + 128) >> 8, h3 = (x3 + 128) >> 8;
+        const uint32_t hp = __byte_perm(__byte_perm((uint32_t) h0, (uint32_t) h1, 0x0040), __byte_perm((uint32_t) h2, (uint32_t) h3, 0x0040), 0x5410);
+        // the low bytes of x are the bytes of l (x - 256 h keeps the low byte)
+        const uint32_t lp = __byte_perm(__byte_perm((uint32_t) x0, (uint32_t) x1, 0x0040), __byte_perm((uint32_t) x2, (uint32_t) x3, 0x0040), 0x5410);
         // word of the pair: plane * 16 + t * 4 + (high sub-block ? 2 : 0) + (k >= 16 ? 1 : 0)
         uint32_t * dst = xq + ((size_t) m * p.pairs + (sb >> 1)) * 32 + (q & 3) * 4 + (sb & 1) * 2 + (q >> 2);
         dst[0] = hp;
@@ -249,6 +253,8 @@ __global__ void __launch_bounds__(IQ_THREADS, NB == 1 ? 2 : 1) matvec_q4k_imma(I
     const uint32_t zero_addr = xq0 + xq_bytes;
     const uint32_t xq_live = xq0 + (uint32_t) (g >> 1) * 128 + (g & 1) * 64 + t * 16;   // + m * pairs * 128 + blk * 512
     const int live_pair = g >> 1;
+    // the 24-bit scale field of lane t starts at byte 4 + 3 t of a 16-byte header
+    const uint32_t fld_off = (uint32_t) (4 + 3 * t) & ~3u, fld_shift = ((uint32_t) (4 + 3 * t) & 3u) * 8u;
     const uint32_t xs0 = iq_smem_addr(xs2) + t * 16;
     float * my_red = red + group * (IQ_WARPS * 64);
     const int gtid = tid - group * (IQ_WARPS * 32);
@@ -275,11 +281,11 @@ __global__ void __launch_bounds__(IQ_THREADS, NB == 1 ? 2 : 1) matvec_q4k_imma(I
                 }
             }
             const uint32_t tiles_lane = ring0 + cslot * IQ_SLOT_BYTES + lane * 16;
-            const uint32_t hdr_lane = hdr0 + cslot * IQ_HDR_BYTES + g * 16;
+            const uint32_t hdr_lane = hdr0 + cslot * IQ_HDR_BYTES + g * 16;   // row g of the chunk's first block
 #pragma unroll
             for (int b2 = 0; b2 < NB; ++b2) {
                 const int blk = chunk * NB + b2;
-                if (blk < p.blocks) {
+                if (FULL || blk < p.blocks) {
                     int clo[M][4], chi[M][4];
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
@@ -296,13 +302,16 @@ __global__ void __launch_bounds__(IQ_THREADS, NB == 1 ? 2 : 1) matvec_q4k_imma(I
                             }
                         }
                     }
-                    const uint4 h0 = iq_lds128(hdr_lane + b2 * 256), h1 = iq_lds128(hdr_lane + b2 * 256 + 128);
+                    // per row: the (d, dmin) word and the two words that hold this lane's 24-bit scale field
+                    const uint32_t ha = hdr_lane + b2 * 256, hb = ha + 128;
+                    const IqHdr h0 = {iq_lds32(ha), iq_lds32(ha + fld_off), iq_lds32(ha + fld_off + 4)};
+                    const IqHdr h1 = {iq_lds32(hb), iq_lds32(hb + fld_off), iq_lds32(hb + fld_off + 4)};
 #pragma unroll
                     for (int m = 0; m < M; ++m) {
                         const uint4 sqb = iq_lds128(xs0 + (uint32_t) (m * p.pairs + blk * 4) * 16);
                         const float4 sq = make_float4(__uint_as_float(sqb.x), __uint_as_float(sqb.y), __uint_as_float(sqb.z), __uint_as_float(sqb.w));
-                        acc0[m] += iq_row_term(h0, t, clo[m][0], clo[m][1], chi[m][0], chi[m][1], sq);
-                        acc1[m] += iq_row_term(h1, t, clo[m][2], clo[m][3], chi[m][2], chi[m][3], sq);
+                        acc0[m] += iq_row_term(h0, fld_shift, clo[m][0], clo[m][1], chi[m][0], chi[m][1], sq);
+                        acc1[m] += iq_row_term(h1, fld_shift, clo[m][2], clo[m][3], chi[m][2], chi[m][3], sq);
                     }
                 }
             }
@@ -360,13 +369,18 @@ size_t iq_smem_bytes(int pairs, int m, int ring, int nb) {
            (size_t) IQ_WARPS * IQ_GROUPS * ring * nb * (256 + 2048);
 }
 
-template <int M, int NB>
-int launch_iq(cudaStream_t s, const IqArgs & a, size_t smem, int grid) {
+template <int M, int NB, bool FULL>
+int launch_iq_full(cudaStream_t s, const IqArgs & a, size_t smem, int grid) {
     // always the device maximum: a smaller value set by a later launch would undercut kernel nodes already
     // recorded in a graph when a tool re-launches them
     if (smem > 48 * 1024)
-        SM100_CUDA(cudaFuncSetAttribute(matvec_q4k_imma<M, NB>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
-    return launch(matvec_q4k_imma<M, NB>, dim3((unsigned) grid), dim3(IQ_THREADS), smem, s, a);
+        SM100_CUDA(cudaFuncSetAttribute(matvec_q4k_imma<M, NB, FULL>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+    return launch(matvec_q4k_imma<M, NB, FULL>, dim3((unsigned) grid), dim3(IQ_THREADS), smem, s, a);
+}
+
+template <int M, int NB>
+int launch_iq(cudaStream_t s, const IqArgs & a, size_t smem, int grid) {
+    return a.blocks % NB == 0 ? launch_iq_full<M, NB, true>(s, a, smem, grid) : launch_iq_full<M, NB, false>(s, a, smem, grid);
 }
 
 std::atomic<bool> g_iq_launched{false};
