@@ -240,6 +240,14 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         except Exception as e:  # the headline line must survive a failure of the secondary measurement
             decode = {"error": f"{type(e).__name__}: {e}"[:300]}
 
+    # ---- the vocabulary head sharded by rows over the ranks, logits all-gathered (N > 1) ----
+    head = None
+    if dist is not None and not args.quick:
+        try:
+            head = sharded_head(capi, rank, world, local_rank, dist)
+        except Exception as e:
+            head = {"error": f"{type(e).__name__}: {e}"[:300]}
+
     out = None
     if rank == 0:
         peak, peak_src = measured_peak_gbs()
@@ -309,7 +317,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
             "config": {"workload": f"Q4_K matvec sweep, M=1, Qwen3-8B projection shapes (K,N) in {SHAPES} x {layers} layers per GPU",
                        "launches_per_step": per_step, "bytes_per_step_per_gpu": int(step_bytes), "weights_layout": "backend-packed planes",
                        "l2": "inputs larger than L2 (pool %.2f GB per GPU, L2 126 MB)" % (step_bytes / 1e9), "timing": "CUDA events on the launching stream, one graph replay per step",
-                       "setup_s": round(setup_s, 1), "detail": detail, "decode": decode},
+                       "setup_s": round(setup_s, 1), "detail": detail, "decode": decode, "head_sharded": head},
             "gpu_launches": int(launches_timed),
             "e2e": {"value": round(world * step_bytes / (e2e_ms * 1e-3) / 1e9, 1), "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "ms_per_step": round(e2e_ms, 4), "note": "host activations in / host results out per matvec, weights resident"},
@@ -324,6 +332,58 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     if dist is not None:
         dist.barrier()
     return out
+
+
+def sharded_head(capi, rank: int, world: int, local_rank: int, dist, reps: int = 50):
+    """Q6_K output head, K = 4096, N = 151936 rows split evenly over the ranks (151936 / P is a multiple of the
+    16-row tile for P = 2, 4, 8), each rank's slice of the logits all-gathered by NCCL.  One CUDA graph holds `reps`
+    rounds of matvec + all-gather; the time is the maximum over the ranks."""
+    import torch
+    from scrapgpulibrary_b200 import synth
+    k, n = 4096, 151936
+    n_local = n // world
+    assert n_local * world == n and n_local % 16 == 0
+    L = capi.lib()
+    dev = torch.device("cuda", local_rank)
+    ts = torch.cuda.Stream(device=dev)
+    handle = C.c_void_p(ts.cuda_stream)
+    base = synth.quantized_matrix(33, 99 + rank, 16384, k)
+    nat = np.tile(base, (-(-n_local // base.shape[0]), 1))[:n_local]
+    natural = torch.from_numpy(np.ascontiguousarray(nat)).to(dev)
+    packed = torch.empty(natural.numel(), dtype=torch.uint8, device=dev)
+    x = torch.randn(k, device=dev, dtype=torch.float32)
+    y_local = torch.empty(n_local, device=dev, dtype=torch.float32)
+    y_all = torch.empty(n, device=dev, dtype=torch.float32)
+    with torch.cuda.stream(ts):
+        capi.check(L.sm100_pack_device(handle, 33, k, n_local, C.c_void_p(natural.data_ptr()), C.c_void_p(packed.data_ptr())), "pack_device")
+
+        def round_():
+            capi.check(L.sm100_mul_mat(handle, 33, 1, C.c_void_p(packed.data_ptr()), 0, k, n_local, C.c_void_p(x.data_ptr()), k, 1,
+                                       C.c_void_p(y_local.data_ptr()), n_local), "mul_mat")
+            dist.all_gather_into_tensor(y_all, y_local)
+        round_()
+    torch.cuda.synchronize(dev)
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g, stream=ts):
+        for _ in range(reps):
+            round_()
+    torch.cuda.synchronize(dev)
+    with torch.cuda.stream(ts):
+        g.replay()
+    torch.cuda.synchronize(dev)
+    dist.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with torch.cuda.stream(ts):
+        e0.record()
+        g.replay()
+        e1.record()
+    torch.cuda.synchronize(dev)
+    t = torch.tensor([e0.elapsed_time(e1) / reps], device=dev, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+    total = algorithmic_bytes(33, k, n)
+    return {"ranks": world, "rows_per_rank": n_local, "us_per_round": round(ms * 1e3, 1), "gbps_aggregate": round(total / (ms * 1e-3) / 1e9, 1),
+            "collective": "NCCL all_gather_into_tensor of 151936 f32 logits"}
 
 
 def other_formats(capi, stream, reps: int = 20):

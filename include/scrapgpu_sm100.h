@@ -111,6 +111,21 @@ SM100_API int sm100_mul_mat_multi(sm100_stream_t s, int count, const int * dtype
                                   const void * const * ws, int64_t k, const int64_t * ns, const float * x,
                                   float * const * ys);
 
+/* MUL_MAT_MULTI with the producer of the activation column folded into the same launch (one f32 column).
+ *   SM100_PROLOGUE_SWIGLU    x = swiglu(a, b) = (a / (1 + expf(-a))) * b                 (src/core/ref/ops.cpp:383-425)
+ *   SM100_PROLOGUE_RMS_NORM  s = a (+ b when b != NULL), x = rms_norm(s, eps) * norm_w   (RMS_NORM_MUL / ADD_RMS_NORM_MUL,
+ *                            include/scrapgpu/op.h:43-44, src/core/ref/ops.cpp:466-519); s is written to sum_out and
+ *                            x to x_out when those are non-NULL; they must not alias a or b
+ * Same values as the separate ops followed by sm100_mul_mat_multi.  Served for packed Q4_K tensors whose row counts
+ * are multiples of 16 (K a multiple of 256, at most 8192 for the norm); otherwise UNSUPPORTED (status 1) and the
+ * caller runs the separate ops. */
+#define SM100_PROLOGUE_SWIGLU 1
+#define SM100_PROLOGUE_RMS_NORM 2
+SM100_API int sm100_mul_mat_fused(sm100_stream_t s, int prologue, const float * a, const float * b, const float * norm_w,
+                                  float eps, float * sum_out, float * x_out, int count, const int * dtypes,
+                                  const int * layouts, const void * const * ws, int64_t k, const int64_t * ns,
+                                  float * const * ys);
+
 /* ---- bit-exact dequantization: GET_ROWS over a quantized / F32 / F16 table
  *      (src/core/ref/ops.cpp:690-722, quant.cpp:30-108); ids are I32 on the device; table_row_stride is the
  *      byte stride of natural-layout rows (0 = dense) ---- */

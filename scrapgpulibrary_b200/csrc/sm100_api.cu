@@ -8,7 +8,7 @@ namespace sm100 {
 int matvec(cudaStream_t s, int dtype, int layout, const void * w, int64_t w_row_stride, int64_t k, int64_t n, const float * x,
            int64_t ldx, int64_t m, float * y, int64_t ldy);
 int matvec_q4k_imma_multi(cudaStream_t s, int count, const void * const * ws, const int64_t * ns, int64_t k, const float * x, int64_t ldx,
-                          int64_t m, float * const * ys, const int64_t * ldys, bool * handled);
+                          int64_t m, float * const * ys, const int64_t * ldys, bool * handled, const Q4KPrologue * pro);
 int gemm_tc_mul_mat(cudaStream_t s, int dtype, int layout, const void * w, int64_t w_row_stride, int64_t k, int64_t n, const float * x,
                     int64_t ldx, int64_t m, float * y, int64_t ldy, bool * handled);
 }
@@ -58,7 +58,7 @@ int sm100_mul_mat_multi(sm100_stream_t s, int count, const int * dtypes, const i
     }
     if (grouped >= 2 && x != nullptr && k > 0) {
         bool handled = false;
-        const int st = matvec_q4k_imma_multi((cudaStream_t) s, grouped, gw, gn, k, x, k, 1, gy, gld, &handled);
+        const int st = matvec_q4k_imma_multi((cudaStream_t) s, grouped, gw, gn, k, x, k, 1, gy, gld, &handled, nullptr);
         if (st != ST_OK) return st;
         if (!handled) in_group[0] = in_group[1] = in_group[2] = false;
     } else {
@@ -69,6 +69,32 @@ int sm100_mul_mat_multi(sm100_stream_t s, int count, const int * dtypes, const i
         const int st = matvec((cudaStream_t) s, dtypes[i], layouts[i], ws[i], 0, k, ns[i], x, k, 1, ys[i], ns[i]);
         if (st != ST_OK) return st;
     }
+    return ST_OK;
+}
+
+int sm100_mul_mat_fused(sm100_stream_t s, int prologue, const float * a, const float * b, const float * norm_w, float eps, float * sum_out,
+                        float * x_out, int count, const int * dtypes, const int * layouts, const void * const * ws, int64_t k, const int64_t * ns,
+                        float * const * ys) {
+    if (count < 1 || count > 3 || dtypes == nullptr || layouts == nullptr || ws == nullptr || ns == nullptr || ys == nullptr || a == nullptr)
+        return fail(ST_INVALID, "mul_mat_fused: 1..3 weight tensors with their dtypes, layouts and outputs, and the prologue input, are required");
+    if (prologue != SM100_PROLOGUE_SWIGLU && prologue != SM100_PROLOGUE_RMS_NORM) return fail(ST_INVALID, "mul_mat_fused: unknown prologue %d", prologue);
+    if (k <= 0) return fail(ST_INVALID, "mul_mat_fused: K must be positive");
+    int64_t ld[3];
+    for (int i = 0; i < count; ++i) {
+        if (ws[i] == nullptr || ys[i] == nullptr || ns[i] <= 0) return fail(ST_INVALID, "mul_mat_fused: null tensor or empty shape");
+        if (dtypes[i] != DT_Q4_K || layouts[i] != LAYOUT_PACKED || ns[i] % 16 != 0)
+            return fail(ST_UNSUPPORTED, "mul_mat_fused: every weight tensor must be packed Q4_K with a multiple of 16 rows; run the separate ops");
+        ld[i] = ns[i];
+    }
+    if ((sum_out != nullptr && (sum_out == a || sum_out == b)) || (x_out != nullptr && (x_out == a || x_out == b)))
+        return fail(ST_INVALID, "mul_mat_fused: sum_out and x_out must not alias the inputs (every CTA reads them while CTA 0 writes)");
+    Q4KPrologue pro = {};
+    pro.mode = prologue;
+    pro.a = a; pro.b = b; pro.norm_w = norm_w; pro.sum_out = sum_out; pro.x_out = x_out; pro.eps = eps;
+    bool handled = false;
+    const int st = matvec_q4k_imma_multi((cudaStream_t) s, count, ws, ns, k, a, k, 1, ys, ld, &handled, &pro);
+    if (st != ST_OK) return st;
+    if (!handled) return fail(ST_UNSUPPORTED, "mul_mat_fused: this shape is not served by the fused kernel; run the separate ops");
     return ST_OK;
 }
 

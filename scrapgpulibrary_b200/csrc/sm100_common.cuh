@@ -52,6 +52,14 @@ inline int block_bytes(int dtype) {
 
 inline bool is_quant(int dtype) { return block_elems(dtype) > 1; }
 
+// producer of a matvec's activation column folded into the matvec (sm100_mul_mat_fused)
+struct Q4KPrologue {
+    int mode;             // 0 none, 1 x = swiglu(a, b), 2 s = a (+ b), x = rms_norm(s) * norm_w
+    const float * a; const float * b; const float * norm_w;
+    float * sum_out; float * x_out;   // mode 2: s and x are also written here when set (must not alias a / b)
+    float eps;
+};
+
 int sm_count();          // SMs of the current device (cached per device)
 bool pdl_enabled();
 void count_launch();

@@ -45,6 +45,12 @@ struct IqArgs {
     int tile_end[IQ_MAX_TENSORS];        // row tiles of tensors 0..i together (INT32_MAX for unused slots)
     const float * x;     // [K, M], column stride ldx floats
     int64_t ldx;
+    // producer of the activation column folded in (M = 1): 0 none; 1 x = swiglu(pa, pb); 2 s = pa (+ pb),
+    // x = rms_norm(s) * pw, with s and x also written out (by CTA 0) when the pointers are set
+    int prologue;
+    const float * pa; const float * pb; const float * pw;
+    float * sum_out; float * x_out;
+    float eps;
     int n_tiles;         // full 16-row tiles of all tensors
     int pairs;           // K / 64
     int blocks;          // K / 256
@@ -218,10 +224,8 @@ __global__ void __launch_bounds__(IQ_THREADS, NB == 1 ? 2 : 1) matvec_q4k_imma(I
     // a sub-block sit in 8 consecutive lanes.
     const int items = p.pairs * 16;
     if (tid < 4) xq[xq_bytes / 4 + tid] = 0u;
-    for (int it0 = tid; it0 < M * items; it0 += IQ_THREADS) {
-        const int m = it0 / items, it = it0 - m * items;
+    auto quantize_item = [&](const float4 v, int m, int it) {
         const int sb = it >> 3, q = it & 7;
-        const float4 v = __ldcg(reinterpret_cast<const float4 *>(p.x + (int64_t) m * p.ldx + (int64_t) it * 4));   // coherent: the producer may still be running when this kernel starts
         float amax = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
         float sum = (v.x + v.y) + (v.z + v.w);
 #pragma unroll
@@ -243,6 +247,66 @@ __global__ void __launch_bounds__(IQ_THREADS, NB == 1 ? 2 : 1) matvec_q4k_imma(I
         dst[0] = hp;
         dst[16] = lp;
         if (q == 0) xs2[(size_t) m * nsb_of(p) + sb] = make_float2(s, sum);
+    };
+    if (M > 1 || p.prologue == 0) {
+        for (int it0 = tid; it0 < M * items; it0 += IQ_THREADS) {
+            const int m = it0 / items, it = it0 - m * items;
+            // coherent load: the producer may still be running when this kernel starts
+            quantize_item(__ldcg(reinterpret_cast<const float4 *>(p.x + (int64_t) m * p.ldx + (int64_t) it * 4)), m, it);
+        }
+    } else if (p.prologue == 1) {
+        // SwiGLU (src/core/ref/ops.cpp:383-425): (a / (1 + expf(-a))) * b, the arithmetic of swiglu_kernel
+        for (int it = tid; it < items; it += IQ_THREADS) {
+            const float4 a = __ldcg(reinterpret_cast<const float4 *>(p.pa) + it), b = __ldcg(reinterpret_cast<const float4 *>(p.pb) + it);
+            float4 v;
+            v.x = __fmul_rn(__fdiv_rn(a.x, __fadd_rn(1.0f, expf(-a.x))), b.x);
+            v.y = __fmul_rn(__fdiv_rn(a.y, __fadd_rn(1.0f, expf(-a.y))), b.y);
+            v.z = __fmul_rn(__fdiv_rn(a.z, __fadd_rn(1.0f, expf(-a.z))), b.z);
+            v.w = __fmul_rn(__fdiv_rn(a.w, __fadd_rn(1.0f, expf(-a.w))), b.w);
+            quantize_item(v, 0, it);
+        }
+    } else {
+        // (ADD_)RMS_NORM_MUL (src/core/ref/ops.cpp:466-519): every CTA normalises the whole row itself (it reads
+        // it anyway); the row stays in registers between the two passes (the host bounds K for that)
+        constexpr int MAXI = 4;
+        float4 v[MAXI];
+        double sq = 0.0;
+#pragma unroll
+        for (int i = 0; i < MAXI; ++i) {
+            const int it = tid + i * IQ_THREADS;
+            v[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (it < items) {
+                v[i] = __ldcg(reinterpret_cast<const float4 *>(p.pa) + it);
+                if (p.pb != nullptr) {
+                    const float4 b = __ldcg(reinterpret_cast<const float4 *>(p.pb) + it);
+                    v[i] = make_float4(__fadd_rn(v[i].x, b.x), __fadd_rn(v[i].y, b.y), __fadd_rn(v[i].z, b.z), __fadd_rn(v[i].w, b.w));
+                }
+                if (p.sum_out != nullptr && blockIdx.x == 0) reinterpret_cast<float4 *>(p.sum_out)[it] = v[i];
+                sq += ((double) v[i].x * (double) v[i].x + (double) v[i].y * (double) v[i].y) +
+                      ((double) v[i].z * (double) v[i].z + (double) v[i].w * (double) v[i].w);
+            }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+        double * dred = reinterpret_cast<double *>(red);   // 16 doubles: the partial-output area is free before the first round
+        if (lane == 0) dred[wid] = sq;
+        __syncthreads();
+        double tot = 0.0;
+#pragma unroll
+        for (int w = 0; w < IQ_WARPS * IQ_GROUPS; ++w) tot += dred[w];
+        const float scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn((float) (tot / (double) (items * 4)), p.eps)));
+#pragma unroll
+        for (int i = 0; i < MAXI; ++i) {
+            const int it = tid + i * IQ_THREADS;
+            if (it < items) {   // warp-uniform: items is a multiple of 64
+                const float4 w4 = __ldg(reinterpret_cast<const float4 *>(p.pw) + it);
+                const float4 r = make_float4(__fmul_rn(__fmul_rn(v[i].x, scale), w4.x), __fmul_rn(__fmul_rn(v[i].y, scale), w4.y),
+                                             __fmul_rn(__fmul_rn(v[i].z, scale), w4.z), __fmul_rn(__fmul_rn(v[i].w, scale), w4.w));
+                if (p.x_out != nullptr && blockIdx.x == 0) reinterpret_cast<float4 *>(p.x_out)[it] = r;
+                quantize_item(r, 0, it);
+            }
+        }
+        __syncthreads();   // dred is part of `red`: everyone has read it before the rounds write there
     }
     __syncthreads();
     pdl_launch_dependents();
@@ -402,8 +466,16 @@ int iq_poll_fault() {
 // Q4_K packed matvec (1 or 2 activation columns) over the full 16-row tiles of up to three tensors that share
 // the activations; *handled = false when the shapes are left to the caller's other kernels.
 int matvec_q4k_imma_multi(cudaStream_t s, int count, const void * const * ws, const int64_t * ns, int64_t k, const float * x, int64_t ldx,
-                          int64_t m, float * const * ys, const int64_t * ldys, bool * handled) {
+                          int64_t m, float * const * ys, const int64_t * ldys, bool * handled, const Q4KPrologue * pro) {
     *handled = false;
+    if (pro != nullptr && pro->mode != 0) {
+        if (m != 1 || pro->a == nullptr) return ST_OK;
+        const uintptr_t al = (uintptr_t) pro->a | (uintptr_t) pro->b | (uintptr_t) pro->norm_w | (uintptr_t) pro->sum_out | (uintptr_t) pro->x_out;
+        if ((al & 15) != 0) return ST_OK;
+        if (pro->mode == 1 && pro->b == nullptr) return ST_OK;
+        if (pro->mode == 2 && (pro->norm_w == nullptr || k > 4 * 4 * IQ_THREADS)) return ST_OK;   // the row must fit the registers of one CTA
+        x = pro->a;   // alignment checks below
+    }
     if (count < 1 || count > IQ_MAX_TENSORS || m < 1 || m > 2 || k % 256 != 0 || k / 64 > 4096) return ST_OK;
     if (((uintptr_t) x & 15) != 0 || (m > 1 && (ldx & 3) != 0)) return ST_OK;
     int64_t tiles = 0;
@@ -438,6 +510,10 @@ int matvec_q4k_imma_multi(cudaStream_t s, int count, const void * const * ws, co
     }
     a.x = x;
     a.ldx = ldx;
+    if (pro != nullptr && pro->mode != 0) {
+        a.prologue = pro->mode;
+        a.pa = pro->a; a.pb = pro->b; a.pw = pro->norm_w; a.sum_out = pro->sum_out; a.x_out = pro->x_out; a.eps = pro->eps;
+    }
     a.n_tiles = (int) tiles;
     a.pairs = pairs;
     a.blocks = (int) (k / 256);
@@ -456,7 +532,7 @@ int matvec_q4k_imma_multi(cudaStream_t s, int count, const void * const * ws, co
 
 int matvec_q4k_imma_tiles(cudaStream_t s, const void * w, int64_t k, int64_t n, const float * x, int64_t ldx, int64_t m, float * y, int64_t ldy,
                           bool * handled) {
-    return matvec_q4k_imma_multi(s, 1, &w, &n, k, x, ldx, m, &y, &ldy, handled);
+    return matvec_q4k_imma_multi(s, 1, &w, &n, k, x, ldx, m, &y, &ldy, handled, nullptr);
 }
 
 }  // namespace sm100

@@ -70,7 +70,7 @@ class Weight:
 
 class DecodeModel:
     def __init__(self, cfg: DecodeConfig, rank: int = 0, world: int = 1, device_index: int = 0, seed: int = 0x5CA9,
-                 weights: dict | None = None, allreduce=None):
+                 weights: dict | None = None, allreduce=None, fuse: bool = True):
         """weights: optional dict name -> (dtype, natural uint8 [N_global, row_bytes], K_global) with GLOBAL matrices
         (sharded here); otherwise seeded synthetic shards are generated per rank.  allreduce / allgather: callables
         on torch tensors (default: torch.distributed when world > 1)."""
@@ -83,6 +83,7 @@ class DecodeModel:
         self.tstream = torch.cuda.Stream(self.device)
         self.stream = C.c_void_p(self.tstream.cuda_stream)
         self.allreduce = allreduce
+        self.fuse = fuse   # fold RMS norm / SwiGLU into the Q4_K projections that consume them (one launch each)
         c = cfg
         self.hq, self.hkv = c.heads // world, c.kv_heads // world
         self.q_dim, self.kv_dim, self.ffn = self.hq * c.head_dim, self.hkv * c.head_dim, c.ffn // world
@@ -118,6 +119,7 @@ class DecodeModel:
             self.token = torch.zeros(1, dtype=torch.int32, device=self.device)
             self.pos = torch.full((1,), c.start_pos, dtype=torch.int32, device=self.device)
             self.x = torch.zeros(c.hidden, **f32)          # residual stream
+            self.x2 = torch.zeros(c.hidden, **f32)         # its alternate buffer (fused launches do not update in place)
             self.xn = torch.zeros(c.hidden, **f32)         # normalised
             self.q = torch.zeros(self.q_dim, **f32)
             self.k = torch.zeros(self.kv_dim, **f32)
@@ -208,6 +210,20 @@ class DecodeModel:
         ns = (C.c_int64 * n)(*[w.n for w in ws])
         capi.check(self.L.sm100_mul_mat_multi(self.stream, n, dts, lays, wp, k, ns, _dev(x), yp), "mul_mat_multi")
 
+    def _mm_fused(self, prologue: int, a, b, norm_w, sum_out, x_out, ws, ys):
+        """MUL_MAT_MULTI with the producer of the activation column (1 = SwiGLU(a, b), 2 = (ADD_)RMS_NORM_MUL) in the
+        same launch; packed Q4_K tensors only."""
+        n = len(ws)
+        k = ws[0].k
+        dts = (C.c_int * n)(*[w.dtype for w in ws])
+        lays = (C.c_int * n)(*([1] * n))
+        wp = (C.c_void_p * n)(*[w.data.data_ptr() for w in ws])
+        yp = (C.c_void_p * n)(*[y.data_ptr() for y in ys])
+        ns = (C.c_int64 * n)(*[w.n for w in ws])
+        opt = lambda t: _dev(t) if t is not None else None
+        capi.check(self.L.sm100_mul_mat_fused(self.stream, prologue, _dev(a), opt(b), opt(norm_w), self.cfg.eps, opt(sum_out), opt(x_out), n,
+                                              dts, lays, wp, k, ns, yp), "mul_mat_fused")
+
     def _reduce(self, t: torch.Tensor):
         if self.world > 1:
             if self.allreduce is not None:
@@ -221,12 +237,29 @@ class DecodeModel:
         chk = capi.check
         chk(L.sm100_get_rows(s, self.embed.dtype, 1, _dev(self.embed.data), 0, c.hidden, c.vocab, _dev(self.token), 1, _dev(self.x), c.hidden), "get_rows")
         scale = float(1.0 / np.sqrt(c.head_dim))
+        # the residual stream alternates between two buffers: the fused launches read the old one in every CTA
+        # while one CTA writes the updated one
+        x_cur, x_alt = self.x, self.x2
         for i, lw in enumerate(self.layers):
-            if i == 0:
-                chk(L.sm100_rms_norm(s, _dev(self.x), None, _dev(lw["attn_norm"]), None, _dev(self.xn), c.hidden, 1, c.eps), "rms_norm")
-            else:   # residual add of the previous layer's FFN output fused with this norm
-                chk(L.sm100_rms_norm(s, _dev(self.x), _dev(self.proj), _dev(lw["attn_norm"]), _dev(self.x), _dev(self.xn), c.hidden, 1, c.eps), "add_rms_norm")
-            self._mm_multi([lw["wq"], lw["wk"], lw["wv"]], self.xn, [self.q, self.k, self.v])
+            add = self.proj if i > 0 else None     # the previous layer's FFN output joins the residual here
+            qkv = [lw["wq"], lw["wk"], lw["wv"]]
+            q4 = [w for w in qkv if w.dtype == Q4_K]
+            if self.fuse and len(q4) >= 2:
+                # ADD_RMS_NORM_MUL folded into the Q4_K projections; a Q6_K value projection reads the normalised row
+                outs = {id(lw["wq"]): self.q, id(lw["wk"]): self.k, id(lw["wv"]): self.v}
+                need_xn = len(q4) < 3
+                self._mm_fused(2, x_cur, add, lw["attn_norm"], x_alt if add is not None else None, self.xn if need_xn else None,
+                               q4, [outs[id(w)] for w in q4])
+                if add is not None:
+                    x_cur, x_alt = x_alt, x_cur
+                if need_xn:
+                    self._mm(lw["wv"], self.xn, self.v)
+            else:
+                if add is None:
+                    chk(L.sm100_rms_norm(s, _dev(x_cur), None, _dev(lw["attn_norm"]), None, _dev(self.xn), c.hidden, 1, c.eps), "rms_norm")
+                else:
+                    chk(L.sm100_rms_norm(s, _dev(x_cur), _dev(add), _dev(lw["attn_norm"]), _dev(x_cur), _dev(self.xn), c.hidden, 1, c.eps), "add_rms_norm")
+                self._mm_multi(qkv, self.xn, [self.q, self.k, self.v])
             chk(L.sm100_head_post(s, _dev(self.q), _dev(self.k), _dev(self.v), _dev(lw["q_norm"]) if c.qk_norm else None,
                                   _dev(lw["k_norm"]) if c.qk_norm else None, _dev(self.pos), _dev(self.rope), 0, c.n_ctx, _dev(lw["k_cache"]),
                                   _dev(lw["v_cache"]), c.head_dim, self.hq, self.hkv, c.n_ctx, c.eps, c.rope_base, 1), "head_post")
@@ -234,12 +267,20 @@ class DecodeModel:
                                   self.hq, self.hkv, 1, 0, _dev(self.pos), scale), "attention")
             self._mm(lw["wo"], self.att, self.proj)
             self._reduce(self.proj)
-            chk(L.sm100_rms_norm(s, _dev(self.x), _dev(self.proj), _dev(lw["ffn_norm"]), _dev(self.x), _dev(self.xn), c.hidden, 1, c.eps), "add_rms_norm")
-            self._mm_multi([lw["wgate"], lw["wup"]], self.xn, [self.gate, self.up])
-            chk(L.sm100_swiglu(s, _dev(self.gate), _dev(self.up), _dev(self.act), self.ffn), "swiglu")
-            self._mm(lw["wdown"], self.act, self.proj)
+            if self.fuse:
+                self._mm_fused(2, x_cur, self.proj, lw["ffn_norm"], x_alt, None, [lw["wgate"], lw["wup"]], [self.gate, self.up])
+                x_cur, x_alt = x_alt, x_cur
+            else:
+                chk(L.sm100_rms_norm(s, _dev(x_cur), _dev(self.proj), _dev(lw["ffn_norm"]), _dev(x_cur), _dev(self.xn), c.hidden, 1, c.eps), "add_rms_norm")
+                self._mm_multi([lw["wgate"], lw["wup"]], self.xn, [self.gate, self.up])
+            if self.fuse and lw["wdown"].dtype == Q4_K:
+                self._mm_fused(1, self.gate, self.up, None, None, None, [lw["wdown"]], [self.proj])
+            else:
+                chk(L.sm100_swiglu(s, _dev(self.gate), _dev(self.up), _dev(self.act), self.ffn), "swiglu")
+                self._mm(lw["wdown"], self.act, self.proj)
             self._reduce(self.proj)
-        chk(L.sm100_rms_norm(s, _dev(self.x), _dev(self.proj), _dev(self.out_norm), _dev(self.x), _dev(self.xn), c.hidden, 1, c.eps), "out_norm")
+        # (the next token starts by overwriting self.x with its embedding, so it does not matter where the stream ended)
+        chk(L.sm100_rms_norm(s, _dev(x_cur), _dev(self.proj), _dev(self.out_norm), _dev(x_cur), _dev(self.xn), c.hidden, 1, c.eps), "out_norm")
         if self.head is not None:
             self._mm(self.head, self.xn, self.logits)
             chk(L.sm100_argmax(s, _dev(self.logits), self.vocab_n, _dev(self.best)), "argmax")

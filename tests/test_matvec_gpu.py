@@ -92,3 +92,69 @@ def test_matvec_argument_errors(sm100, stream):
         sm100.mul_mat(stream, U.Q4_K, U.PACKED, 0, 256, 4, buf, 1, buf)  # null weights
     assert e.value.status == 2
     buf.free()
+
+
+def _fused(sm100, stream, prologue, a, b, norm_w, wqs, k, want_sum, want_x):
+    """Runs sm100_mul_mat_fused over packed Q4_K tensors; returns the outputs and the optional side outputs."""
+    import ctypes as C
+    n = len(wqs)
+    bufs = [U.to_device(sm100, stream, sm100.pack(U.Q4_K, k, w)) for w in wqs]
+    ab = U.to_device(sm100, stream, a)
+    bb = U.to_device(sm100, stream, b) if b is not None else None
+    wb = U.to_device(sm100, stream, norm_w) if norm_w is not None else None
+    sb = sm100.Buffer(4 * k) if want_sum else None
+    xb = sm100.Buffer(4 * k) if want_x else None
+    ys = [U.guarded_output(sm100, stream, w.shape[0]) for w in wqs]
+    dts = (C.c_int * n)(*([U.Q4_K] * n))
+    lays = (C.c_int * n)(*([1] * n))
+    wp = (C.c_void_p * n)(*[bf.ptr for bf in bufs])
+    yp = (C.c_void_p * n)(*[p for _, p in ys])
+    ns = (C.c_int64 * n)(*[w.shape[0] for w in wqs])
+    sm100.check(sm100.lib().sm100_mul_mat_fused(stream.handle, prologue, ab.at(), bb.at() if bb else None, wb.at() if wb else None, 1e-6,
+                                                sb.at() if sb else None, xb.at() if xb else None, n, dts, lays, wp, k, ns, yp), "mul_mat_fused")
+    stream.sync()
+    outs = [U.read_guarded(sm100, stream, yb, w.shape[0]).copy() for (yb, _), w in zip(ys, wqs)]
+    s_out = sb.download(stream, np.float32, k) if sb else None
+    x_out = xb.download(stream, np.float32, k) if xb else None
+    return outs, s_out, x_out
+
+
+def test_mul_mat_fused_prologues(sm100, stream):
+    """RMS norm (with and without the residual add) and SwiGLU folded into the Q4_K projections: outputs against the
+    oracle's separate ops, the residual sum bit-exact, the normalised row within one ulp."""
+    k = 4096
+    rng = np.random.default_rng(3)
+    wqs = [U.quantize(U.Q4_K, U.seeded_weights(300 + i, n, k)) for i, n in enumerate((4096, 1024, 1024))]
+    a = (rng.standard_normal(k) * 4).astype(np.float32)
+    b = rng.standard_normal(k).astype(np.float32)
+    g = rng.standard_normal(k).astype(np.float32)
+    for add in (b, None):
+        if add is not None:
+            want_s, want_x = sgref.rms_norm(a[None], g, add=add[None])
+        else:
+            want_s, want_x = None, sgref.rms_norm(a[None], g)
+        outs, s_out, x_out = _fused(sm100, stream, 2, a, add, g, wqs, k, add is not None, True)
+        if add is not None:
+            assert np.array_equal(s_out, want_s[0])
+        assert np.max(np.abs(x_out.view(np.int32) - want_x[0].view(np.int32))) <= 1
+        for w, y in zip(wqs, outs):
+            assert sgref.nmse(y, sgref.mul_mat(U.Q4_K, w, k, want_x)[0]) <= TOL
+    # SwiGLU in front of a down projection: K = 12288
+    k2 = 12288
+    wd = U.quantize(U.Q4_K, U.seeded_weights(400, 512, k2))
+    ga = rng.standard_normal(k2).astype(np.float32)
+    up = rng.standard_normal(k2).astype(np.float32)
+    outs, _, _ = _fused(sm100, stream, 1, ga, up, None, [wd], k2, False, False)
+    act = sgref.swiglu(ga, up)
+    assert sgref.nmse(outs[0], sgref.mul_mat(U.Q4_K, wd, k2, act[None])[0]) <= TOL
+
+
+def test_mul_mat_fused_refuses_what_it_does_not_serve(sm100, stream):
+    import ctypes as C
+    k, n = 256, 24   # 24 rows: not whole 16-row tiles
+    w = U.to_device(sm100, stream, sm100.pack(U.Q4_K, k, U.quantize(U.Q4_K, U.seeded_weights(1, n, k))))
+    a = U.to_device(sm100, stream, np.ones(k, np.float32))
+    y = sm100.Buffer(4 * n)
+    st = sm100.lib().sm100_mul_mat_fused(stream.handle, 2, a.at(), None, a.at(), 1e-6, None, None, 1, (C.c_int * 1)(U.Q4_K), (C.c_int * 1)(1),
+                                         (C.c_void_p * 1)(w.ptr), k, (C.c_int64 * 1)(n), (C.c_void_p * 1)(y.ptr))
+    assert st == 1   # UNSUPPORTED: the caller runs the separate ops
