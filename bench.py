@@ -472,7 +472,13 @@ def run_decode(args, rank: int, world: int, local_rank: int, dist, stream_sync):
     from scrapgpulibrary_b200.decode import DecodeConfig, DecodeModel
     cfg = DecodeConfig()
     steps = args.decode_steps
-    model = DecodeModel(cfg, rank=rank, world=world, device_index=local_rank, seed=0x5CA9)
+    allreduce, exchange = None, "none"
+    if world > 1:
+        exchange = os.environ.get("SM100_TP_EXCHANGE", "peer")
+        if exchange == "peer":   # the library's one-shot all-reduce over peer-mapped memory; "nccl" = torch.distributed
+            from scrapgpulibrary_b200.collective import PeerAllReduce
+            allreduce = PeerAllReduce(rank, world, local_rank, cfg.hidden, dist)
+    model = DecodeModel(cfg, rank=rank, world=world, device_index=local_rank, seed=0x5CA9, allreduce=allreduce)
     model.reset(token=1234, prefill_seed=7)
     model.capture()
     model.reset(token=1234, prefill_seed=None)
@@ -499,7 +505,8 @@ def run_decode(args, rank: int, world: int, local_rank: int, dist, stream_sync):
     mid_pos = cfg.start_pos + steps // 2
     bytes_tok = model.bytes_per_token(mid_pos)      # this rank's share
     tok_s = steps / (ms * 1e-3)
-    return {"tok_s": round(tok_s, 1), "ms_per_token": round(ms / steps, 4), "steps": steps, "tp": world,
+    return {"tok_s": round(tok_s, 1), "ms_per_token": round(ms / steps, 4), "steps": steps, "tp": world, "all_reduce": exchange,
+            "all_reduce_fault": allreduce.fault() if allreduce is not None else 0,
             "bytes_per_token_per_gpu": int(bytes_tok), "hbm_gbps_per_gpu": round(bytes_tok * tok_s / 1e9, 1),
             "hbm_frac_of_measured": round(bytes_tok * tok_s / 1e9 / peak, 4),
             "model": "Qwen3-8B shape, random Q4_K_M-style weights (Q6_K for attn_v / ffn_down in the more-bits layers and the head)",

@@ -65,6 +65,26 @@ SM100_API int sm100_memset(sm100_stream_t s, void * dst, int byte, size_t n, int
 SM100_API int sm100_memcpy_peer(sm100_stream_t dst_stream, int dst_device, void * dst, sm100_stream_t src_stream,
                                 int src_device, const void * src, size_t n);
 
+/* ---- tensor-parallel exchange over peer-mapped memory (one process per GPU) ----
+ * The reference moves tensors between devices through a host bounce (src/core/transport.cpp:53-146) and has no
+ * collective; the tensor-parallel decode needs an all-reduce of the hidden vector after the row-parallel projections.
+ * Each rank allocates one area of sm100_allreduce_area_bytes() with sm100_malloc, zero-fills it, exports it
+ * (sm100_ipc_export), and opens the other ranks' handles (sm100_ipc_open); `areas` lists all ranks' areas as seen from
+ * this process (entry `rank` = the local pointer).  sm100_allreduce_sum is one single-CTA kernel: stores to every
+ * peer, a system-scope flag, a bounded wait for the peers' flags, and the sum in rank order (same bits on every rank).
+ * Every rank must call it the same number of times.  A wait that runs out sets a fault (sm100_allreduce_fault != 0)
+ * and the kernel returns; it never spins without bound. */
+typedef void * sm100_allreduce_t;
+SM100_API size_t sm100_ipc_handle_bytes(void);
+SM100_API int sm100_ipc_export(void * device_ptr, void * handle_out);
+SM100_API int sm100_ipc_open(const void * handle, void ** device_ptr_out);
+SM100_API int sm100_ipc_close(void * device_ptr);
+SM100_API size_t sm100_allreduce_area_bytes(int world, int capacity_floats);
+SM100_API int sm100_allreduce_create(int rank, int world, int capacity_floats, void * const * areas, sm100_allreduce_t * out);
+SM100_API int sm100_allreduce_sum(sm100_allreduce_t ctx, sm100_stream_t s, float * x, int n);
+SM100_API int sm100_allreduce_fault(sm100_allreduce_t ctx, int * fault_out);
+SM100_API int sm100_allreduce_destroy(sm100_allreduce_t ctx);
+
 /* ---- timing and replay: the plan seat of the reference (src/core/registry.cpp:200-220, "selection
  *      happens once at plan build") becomes a captured CUDA graph ---- */
 SM100_API int sm100_event_create(sm100_event_t * out);

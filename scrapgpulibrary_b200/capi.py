@@ -63,6 +63,16 @@ def lib() -> C.CDLL:
         L.sm100_unpack_device.argtypes = [vp, i32, i64, i64, vp, vp]
         L.sm100_mul_mat.argtypes = [vp, i32, i32, vp, i64, i64, i64, vp, i64, i64, vp, i64]
         L.sm100_head_post.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, vp, vp, i64, i64, i64, i64, C.c_float, C.c_float, i32]
+        L.sm100_ipc_handle_bytes.restype = sz
+        L.sm100_ipc_export.argtypes = [vp, vp]
+        L.sm100_ipc_open.argtypes = [vp, pv]
+        L.sm100_ipc_close.argtypes = [vp]
+        L.sm100_allreduce_area_bytes.restype = sz
+        L.sm100_allreduce_area_bytes.argtypes = [i32, i32]
+        L.sm100_allreduce_create.argtypes = [i32, i32, i32, pv, pv]
+        L.sm100_allreduce_sum.argtypes = [vp, vp, vp, i32]
+        L.sm100_allreduce_fault.argtypes = [vp, C.POINTER(i32)]
+        L.sm100_allreduce_destroy.argtypes = [vp]
         L.sm100_mul_mat_fused.argtypes = [vp, i32, vp, vp, vp, C.c_float, vp, vp, i32, C.POINTER(i32), C.POINTER(i32), pv, i64, C.POINTER(i64), pv]
         L.sm100_mul_mat_multi.argtypes = [vp, i32, C.POINTER(i32), C.POINTER(i32), pv, i64, C.POINTER(i64), vp, pv]
         L.sm100_get_rows.argtypes = [vp, i32, i32, vp, i64, i64, i64, vp, i64, vp, i64]

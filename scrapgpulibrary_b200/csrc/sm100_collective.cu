@@ -1,0 +1,176 @@
+// One-shot all-reduce (sum) of a short f32 vector over the GPUs of one node, through peer-mapped memory.
+//
+// The tensor-parallel decode needs two all-reduces of the hidden vector (16 KiB) per layer.  At that size a
+// collective is pure latency, so it is one kernel of one CTA per GPU instead of a library call: every rank stores
+// its vector into its slot of EVERY rank's receive area (plain 16-byte stores over NVLink), fences, raises a flag
+// next to it, waits - with a bound - until all ranks' flags for this step have arrived in its own memory, and adds
+// the slots in rank order (the same order everywhere: every rank gets the same bits).  No multicast, no loads from
+// peer memory, no library kernel on peer pointers.
+//
+// Two receive areas alternate by step: a rank can only be one step ahead of the slowest one (it needs that rank's
+// flag to finish a step), and a rank raises its flag for step s + 1 only after it has finished reading step s.
+//
+// This replaces the host-bounce copy the reference uses between devices (src/core/transport.cpp:53-146) on the
+// tensor-parallel path; the reference itself has no collective.
+#include "sm100_common.cuh"
+
+#include <cstring>
+
+namespace sm100 {
+
+namespace {
+
+constexpr int AR_MAX_RANKS = 8;
+constexpr int AR_THREADS = 1024;
+constexpr uint32_t AR_WAIT_LIMIT = 1u << 22;   // polls (each with a short sleep) before a rank gives up: ~1 s
+
+struct ArArgs {
+    float * recv[AR_MAX_RANKS];       // every rank's receive area [2][world][capacity] (entry `rank` is the local one)
+    uint32_t * flags[AR_MAX_RANKS];   // every rank's flags [2][world]
+    uint32_t * counter;               // local: calls so far
+    int * fault;                      // local: set when a wait ran out
+    float * x;                        // in / out
+    int n, capacity, rank, world;
+};
+
+__device__ __forceinline__ void st_release_sys(uint32_t * p, uint32_t v) { asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory"); }
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t * p) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+__global__ void __launch_bounds__(AR_THREADS, 1) allreduce_kernel(ArArgs a) {
+    pdl_wait();
+    __shared__ uint32_t s_step;
+    const int tid = threadIdx.x;
+    if (tid == 0) {
+        const uint32_t step = *a.counter + 1u;
+        *a.counter = step;
+        s_step = step;
+    }
+    __syncthreads();
+    const uint32_t step = s_step;
+    const int buf = (int) (step & 1u);
+    const int n4 = a.n >> 2;
+    // 1. my vector into my slot of every rank's receive area
+    const float4 * src = reinterpret_cast<const float4 *>(a.x);
+    for (int i = tid; i < n4; i += AR_THREADS) {
+        const float4 v = src[i];
+        for (int p = 0; p < a.world; ++p)
+            reinterpret_cast<float4 *>(a.recv[p] + ((size_t) buf * a.world + a.rank) * a.capacity)[i] = v;
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (tid < a.world) st_release_sys(a.flags[tid] + buf * a.world + a.rank, step);
+    // 2. all ranks' flags for this step, bounded
+    if (tid < a.world) {
+        const uint32_t * f = a.flags[a.rank] + buf * a.world + tid;
+        bool ok = false;
+        for (uint32_t i = 0; i < AR_WAIT_LIMIT; ++i) {
+            if (ld_acquire_sys(f) == step) { ok = true; break; }
+            __nanosleep(100);
+        }
+        if (!ok) atomicExch(a.fault, 1 + tid);
+    }
+    __syncthreads();
+    pdl_launch_dependents();
+    // 3. sum of the slots in rank order
+    const float * mine = a.recv[a.rank] + (size_t) buf * a.world * a.capacity;
+    float4 * dst = reinterpret_cast<float4 *>(a.x);
+    for (int i = tid; i < n4; i += AR_THREADS) {
+        float4 acc = __ldcg(reinterpret_cast<const float4 *>(mine) + i);
+        for (int r = 1; r < a.world; ++r) {
+            const float4 v = __ldcg(reinterpret_cast<const float4 *>(mine + (size_t) r * a.capacity) + i);
+            acc.x = __fadd_rn(acc.x, v.x); acc.y = __fadd_rn(acc.y, v.y); acc.z = __fadd_rn(acc.z, v.z); acc.w = __fadd_rn(acc.w, v.w);
+        }
+        dst[i] = acc;
+    }
+}
+
+struct ArContext {
+    ArArgs args;
+    int device;
+};
+
+}  // namespace
+
+}  // namespace sm100
+
+using namespace sm100;
+
+extern "C" {
+
+size_t sm100_ipc_handle_bytes(void) { return sizeof(cudaIpcMemHandle_t); }
+
+int sm100_ipc_export(void * device_ptr, void * handle_out) {
+    if (device_ptr == nullptr || handle_out == nullptr) return fail(ST_INVALID, "ipc_export: null pointer");
+    cudaIpcMemHandle_t h;
+    SM100_CUDA(cudaIpcGetMemHandle(&h, device_ptr));
+    memcpy(handle_out, &h, sizeof(h));
+    return ST_OK;
+}
+
+int sm100_ipc_open(const void * handle, void ** device_ptr_out) {
+    if (handle == nullptr || device_ptr_out == nullptr) return fail(ST_INVALID, "ipc_open: null pointer");
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle, sizeof(h));
+    SM100_CUDA(cudaIpcOpenMemHandle(device_ptr_out, h, cudaIpcMemLazyEnablePeerAccess));
+    return ST_OK;
+}
+
+int sm100_ipc_close(void * device_ptr) {
+    if (device_ptr == nullptr) return ST_OK;
+    SM100_CUDA(cudaIpcCloseMemHandle(device_ptr));
+    return ST_OK;
+}
+
+size_t sm100_allreduce_area_bytes(int world, int capacity) {
+    return (size_t) 2 * world * capacity * sizeof(float) + 256 /* flags [2][world] */ + 256 /* counter, fault */;
+}
+
+int sm100_allreduce_create(int rank, int world, int capacity, void * const * areas, sm100_allreduce_t * out) {
+    if (out == nullptr || areas == nullptr) return fail(ST_INVALID, "allreduce_create: null pointer");
+    if (world < 1 || world > AR_MAX_RANKS || rank < 0 || rank >= world) return fail(ST_INVALID, "allreduce_create: 1..8 ranks");
+    if (capacity <= 0 || capacity % 4 != 0) return fail(ST_INVALID, "allreduce_create: the capacity must be a positive multiple of 4 floats");
+    ArContext * c = new ArContext();
+    SM100_CUDA(cudaGetDevice(&c->device));
+    const size_t data = (size_t) 2 * world * capacity * sizeof(float);
+    for (int p = 0; p < world; ++p) {
+        if (areas[p] == nullptr) { delete c; return fail(ST_INVALID, "allreduce_create: area %d is null", p); }
+        c->args.recv[p] = (float *) areas[p];
+        c->args.flags[p] = (uint32_t *) ((uint8_t *) areas[p] + data);
+    }
+    c->args.counter = (uint32_t *) ((uint8_t *) areas[rank] + data + 256);
+    c->args.fault = (int *) ((uint8_t *) areas[rank] + data + 256 + 64);
+    c->args.capacity = capacity;
+    c->args.rank = rank;
+    c->args.world = world;
+    *out = c;
+    return ST_OK;
+}
+
+int sm100_allreduce_sum(sm100_allreduce_t ctx, sm100_stream_t s, float * x, int n) {
+    ArContext * c = (ArContext *) ctx;
+    if (c == nullptr || x == nullptr) return fail(ST_INVALID, "allreduce_sum: null pointer");
+    if (n <= 0 || n % 4 != 0 || n > c->args.capacity || ((uintptr_t) x & 15) != 0)
+        return fail(ST_INVALID, "allreduce_sum: n must be a positive multiple of 4 within the capacity, x 16-byte aligned");
+    ArArgs a = c->args;
+    a.x = x;
+    a.n = n;
+    return launch(allreduce_kernel, dim3(1), dim3(AR_THREADS), 0, (cudaStream_t) s, a);
+}
+
+int sm100_allreduce_fault(sm100_allreduce_t ctx, int * fault_out) {
+    ArContext * c = (ArContext *) ctx;
+    if (c == nullptr || fault_out == nullptr) return fail(ST_INVALID, "allreduce_fault: null pointer");
+    SM100_CUDA(cudaMemcpy(fault_out, c->args.fault, sizeof(int), cudaMemcpyDeviceToHost));
+    return ST_OK;
+}
+
+int sm100_allreduce_destroy(sm100_allreduce_t ctx) {
+    delete (ArContext *) ctx;
+    return ST_OK;
+}
+
+}  // extern "C"

@@ -1,4 +1,5 @@
-"""Tensor-parallel decode on 2 GPUs (one process per GPU, NCCL): greedy tokens identical to the CPU oracle's and to
+"""Tensor-parallel decode on 2 GPUs (one process per GPU; all-reduce by NCCL, or by the library's own one-shot kernel
+over peer-mapped memory): greedy tokens identical to the CPU oracle's and to
 the single-GPU run, eager and under CUDA-graph replay.  Needs two GPUs; on a single-GPU box the test is skipped."""
 import json
 import os
@@ -14,7 +15,8 @@ pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def test_tp2_decode_tokens_match_oracle(sm100, tmp_path):
+@pytest.mark.parametrize("exchange", ["nccl", "peer"])
+def test_tp2_decode_tokens_match_oracle(sm100, tmp_path, exchange):
     if sm100.device_count() < 2:
         pytest.skip("needs 2 GPUs")
     from scrapgpulibrary_b200.decode import DecodeConfig
@@ -28,10 +30,10 @@ def test_tp2_decode_tokens_match_oracle(sm100, tmp_path):
     out = tmp_path / "tokens.json"
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
     r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
-                        "--master-port", "29731", os.path.join(ROOT, "tests", "tp_decode_worker.py"), str(out), str(steps)],
+                        "--master-port", "29731" if exchange == "nccl" else "29733", os.path.join(ROOT, "tests", "tp_decode_worker.py"), str(out), str(steps), exchange],
                        capture_output=True, text=True, timeout=600, env=env)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-4000:]
     got = json.loads(out.read_text())
-    assert got["world"] == 2
+    assert got["world"] == 2 and got["fault"] == 0
     assert got["eager"] == want.tolist()
     assert got["replay"] == want.tolist()

@@ -17,6 +17,7 @@ from scrapgpulibrary_b200.decode import DecodeConfig, DecodeModel  # noqa: E402
 
 def main():
     out_path, steps = sys.argv[1], int(sys.argv[2])
+    exchange = sys.argv[3] if len(sys.argv) > 3 else "nccl"
     rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
     torch.cuda.set_device(local)
     dist.init_process_group("nccl", device_id=torch.device("cuda", local))
@@ -25,7 +26,11 @@ def main():
     rng = np.random.default_rng(11)
     kp = [rng.standard_normal((cfg.kv_heads, cfg.start_pos, cfg.head_dim)).astype(np.float32) for _ in range(cfg.layers)]
     vp = [rng.standard_normal((cfg.kv_heads, cfg.start_pos, cfg.head_dim)).astype(np.float32) for _ in range(cfg.layers)]
-    model = DecodeModel(cfg, rank=rank, world=world, device_index=local, weights=weights)
+    allreduce = None
+    if exchange == "peer":   # the library's one-shot all-reduce over peer-mapped memory instead of NCCL
+        from scrapgpulibrary_b200.collective import PeerAllReduce
+        allreduce = PeerAllReduce(rank, world, local, cfg.hidden, dist)
+    model = DecodeModel(cfg, rank=rank, world=world, device_index=local, weights=weights, allreduce=allreduce)
 
     def load_prefill():
         model.reset(123)
@@ -46,7 +51,7 @@ def main():
     replay = model.tokens(steps).tolist()
     if rank == 0:
         with open(out_path, "w") as f:
-            json.dump({"eager": eager, "replay": replay, "world": world}, f)
+            json.dump({"eager": eager, "replay": replay, "world": world, "fault": allreduce.fault() if allreduce is not None else 0}, f)
     dist.barrier()
     torch.cuda.synchronize()
     # no destroy_process_group(): it was seen to block for minutes here while captured graphs hold the communicator
