@@ -447,16 +447,29 @@ scrapgpu_status supports(const scrapgpu_op_desc * desc, const char ** reason) {
                        ? SCRAPGPU_STATUS_OK : bad("GET_ROWS: dst must be [ne00, ids] over the slices of src0", reason);
         }
 
-        case SCRAPGPU_OP_SET_ROWS: {
-            if (desc->input_count != 2) return bad("SET_ROWS takes two inputs", reason);
+        case SCRAPGPU_OP_SET_ROWS:
+        case SCRAPGPU_OP_SET_ROWS_PAIR: {
+            // SET_ROWS_PAIR = two SET_ROWS in one op: inputs [src0_a, ids_a, src0_b, ids_b], outputs [dst_a, dst_b]
+            // (include/scrapgpu/op.h:45, src/core/op.cpp:208-210, src/backends/opencl11/api.cpp:454-458)
+            const bool pair = enum_bits(desc->op) == (uint32_t) SCRAPGPU_OP_SET_ROWS_PAIR;
+            if (!pair && desc->input_count != 2) return bad("SET_ROWS takes two inputs", reason);
+            if (pair && (desc->input_count != 4 || desc->output_count != 2)) return bad("SET_ROWS_PAIR takes four inputs and two outputs", reason);
             const auto okdt = [](const scrapgpu_tensor_desc & t) { return t.dtype == SCRAPGPU_DTYPE_F32 || t.dtype == SCRAPGPU_DTYPE_F16; };
-            if (!okdt(s0) || !okdt(dd)) return unsupported("SET_ROWS expects F32/F16 values and destination", reason);
-            if (s1.dtype != SCRAPGPU_DTYPE_I32 && s1.dtype != SCRAPGPU_DTYPE_I64) return unsupported("SET_ROWS indices must be I32 or I64", reason);
-            const scrapgpu_status st = require_rows(s0, "SET_ROWS needs contiguous rows (nb0 == element size)", reason);
-            if (st != SCRAPGPU_STATUS_OK) return st;
-            return ne(s0, 0) == ne(dd, 0) && ne(s0, 2) == ne(dd, 2) && ne(s0, 3) == ne(dd, 3) && ne(dd, 1) >= 1 && ne(s1, 0) >= ne(s0, 1) &&
-                           ne(s0, 2) % ne(s1, 1) == 0 && ne(s0, 3) % ne(s1, 2) == 0
-                       ? SCRAPGPU_STATUS_OK : bad("SET_ROWS: dst must match src0 except along dim 1 and the index tensor must cover its rows", reason);
+            const auto one = [&](const scrapgpu_tensor_desc & src, const scrapgpu_tensor_desc & ids, const scrapgpu_tensor_desc & dst) -> scrapgpu_status {
+                if (!okdt(src) || !okdt(dst)) return unsupported("SET_ROWS expects F32/F16 values and destination", reason);
+                if (ids.dtype != SCRAPGPU_DTYPE_I32 && ids.dtype != SCRAPGPU_DTYPE_I64) return unsupported("SET_ROWS indices must be I32 or I64", reason);
+                const scrapgpu_status st = require_rows(src, "SET_ROWS needs contiguous rows (nb0 == element size)", reason);
+                if (st != SCRAPGPU_STATUS_OK) return st;
+                return ne(src, 0) == ne(dst, 0) && ne(src, 2) == ne(dst, 2) && ne(src, 3) == ne(dst, 3) && ne(dst, 1) >= 1 && ne(ids, 0) >= ne(src, 1) &&
+                               ne(src, 2) % ne(ids, 1) == 0 && ne(src, 3) % ne(ids, 2) == 0
+                           ? SCRAPGPU_STATUS_OK : bad("SET_ROWS: dst must match src0 except along dim 1 and the index tensor must cover its rows", reason);
+            };
+            const scrapgpu_status first = one(s0, s1, dd);
+            if (first != SCRAPGPU_STATUS_OK || !pair) return first;
+            const auto s3 = load_desc(desc->inputs[3]);
+            const auto o1 = load_desc(desc->outputs[1]);
+            if (s0.dtype != s2.dtype || dd.dtype != o1.dtype) return unsupported("SET_ROWS_PAIR needs two SET_ROWS with the same dtypes", reason);
+            return one(s2, s3, o1);
         }
 
         case SCRAPGPU_OP_CPY: case SCRAPGPU_OP_DUP: case SCRAPGPU_OP_CONT: {
@@ -756,6 +769,15 @@ scrapgpu_status execute(Stream * s, const scrapgpu_op_desc * desc) {
         case SCRAPGPU_OP_SET_ROWS: {
             const sm100_view src = view_of(in[0]), ids = view_of(in[1]), dst = view_of(out[0]);
             return from_sm100(sm100_set_rows_view(s->cuda, &src, in[0].d.dtype, &ids, in[1].d.dtype == SCRAPGPU_DTYPE_I64, &dst, out[0].d.dtype));
+        }
+        case SCRAPGPU_OP_SET_ROWS_PAIR: {
+            for (int i = 0; i < 2; ++i) {
+                const sm100_view src = view_of(in[2 * i]), ids = view_of(in[2 * i + 1]), dst = view_of(out[i]);
+                const scrapgpu_status st = from_sm100(
+                    sm100_set_rows_view(s->cuda, &src, in[2 * i].d.dtype, &ids, in[2 * i + 1].d.dtype == SCRAPGPU_DTYPE_I64, &dst, out[i].d.dtype));
+                if (st != SCRAPGPU_STATUS_OK) return st;
+            }
+            return SCRAPGPU_STATUS_OK;
         }
         case SCRAPGPU_OP_CPY: case SCRAPGPU_OP_DUP: case SCRAPGPU_OP_CONT: {
             const sm100_view src = view_of(in[0]), dst = view_of(out[0]);
@@ -1123,6 +1145,7 @@ const char * op_name(int op) {
         case SCRAPGPU_OP_RMS_NORM_MUL: return "RMS_NORM_MUL";
         case SCRAPGPU_OP_ADD_RMS_NORM_MUL: return "ADD_RMS_NORM_MUL";
         case SCRAPGPU_OP_MUL_MAT_MULTI: return "MUL_MAT_MULTI";
+        case SCRAPGPU_OP_SET_ROWS_PAIR: return "SET_ROWS_PAIR";
         default: return "OP";
     }
 }

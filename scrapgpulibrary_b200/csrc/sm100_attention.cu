@@ -297,55 +297,97 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_fast_kernel(AttnArgs a) {
     }
     const float4 * kbase = reinterpret_cast<const float4 *>(a.k + (hk * a.nk + k0) * D) + lane;
     const float4 * vbase = reinterpret_cast<const float4 *>(a.v + (hk * a.nk + k0) * D) + lane;
-    for (int kk = warp; kk < count; kk += 2 * NW) {
-        // two keys per trip: four independent row requests in flight
-        const bool second = kk + NW < count;
-        float4 kv[2][D4], vv[2][D4];
+    // A warp takes NKB consecutive keys per trip: their K and V rows are requested together, the G x NKB partial
+    // dot products are reduced over the lanes with a halving exchange (NV values cost NV - 1 + log2(32 / NV)
+    // shuffles instead of 5 NV) and handed to all lanes through the warp's own shared-memory slot.
+    constexpr int NKB = D4 == 1 ? 4 : 2;
+    constexpr int NV = G * NKB;
+    float * my_scores = smem + warp * G * (D + 2);   // first NV floats of the area this warp fills after the loop
+    for (int kb = warp * NKB; kb < count; kb += NW * NKB) {
+        float4 kv[NKB][D4], vv[NKB][D4];
 #pragma unroll
-        for (int i = 0; i < D4; ++i) {
-            kv[0][i] = kbase[(int64_t) kk * (D / 4) + 32 * i];
-            vv[0][i] = vbase[(int64_t) kk * (D / 4) + 32 * i];
-            kv[1][i] = second ? kbase[(int64_t) (kk + NW) * (D / 4) + 32 * i] : make_float4(0.f, 0.f, 0.f, 0.f);
-            vv[1][i] = second ? vbase[(int64_t) (kk + NW) * (D / 4) + 32 * i] : make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int j = 0; j < NKB; ++j) {
+            const bool in = kb + j < count;
+#pragma unroll
+            for (int i = 0; i < D4; ++i) {
+                kv[j][i] = in ? kbase[(int64_t) (kb + j) * (D / 4) + 32 * i] : make_float4(0.f, 0.f, 0.f, 0.f);
+                vv[j][i] = in ? vbase[(int64_t) (kb + j) * (D / 4) + 32 * i] : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
         }
+        float part[NV];
 #pragma unroll
-        for (int u = 0; u < 2; ++u) {
-            if (u == 1 && !second) break;
-            const int key = kk + u * NW;
+        for (int g = 0; g < G; ++g)
 #pragma unroll
-            for (int g = 0; g < G; ++g) {
+            for (int j = 0; j < NKB; ++j) {
                 float sc = 0.f;
 #pragma unroll
                 for (int i = 0; i < D4; ++i)
-                    sc += (kv[u][i].x * qr[g][i].x + kv[u][i].y * qr[g][i].y) + (kv[u][i].z * qr[g][i].z + kv[u][i].w * qr[g][i].w);
+                    sc += (kv[j][i].x * qr[g][i].x + kv[j][i].y * qr[g][i].y) + (kv[j][i].z * qr[g][i].z + kv[j][i].w * qr[g][i].w);
+                part[g * NKB + j] = sc;
+            }
+        // halving exchange: after the step with offset o a lane keeps the half selected by its bit o
+        int n = NV;
 #pragma unroll
-                for (int sh = 16; sh > 0; sh >>= 1) sc += __shfl_xor_sync(0xffffffffu, sc, sh);
-                sc *= a.scale;
-                if (a.mask != nullptr) {
-                    const int64_t mh = a.mask_heads == 1 ? 0 : hk * G + g;
-                    sc += a.mask[(mh * a.nq + q) * a.nk + k0 + key];
-                }
-                if (sc > m[g]) {   // warp-uniform: every lane holds the same score
-                    const float corr = m[g] == -INFINITY ? 0.f : expf(m[g] - sc);
-                    l[g] *= corr;
+        for (int off = 16; off > 0; off >>= 1) {
+            if (n > 1) {
+                const bool upper = (lane & off) != 0;
 #pragma unroll
-                    for (int i = 0; i < D4; ++i) {
-                        o[g][i].x *= corr; o[g][i].y *= corr; o[g][i].z *= corr; o[g][i].w *= corr;
+                for (int i = 0; i < NV / 2; ++i) {
+                    if (i < n / 2) {
+                        const float keep = upper ? part[i + n / 2] : part[i];
+                        const float give = upper ? part[i] : part[i + n / 2];
+                        part[i] = keep + __shfl_xor_sync(0xffffffffu, give, off);
                     }
-                    m[g] = sc;
                 }
-                const float pr = sc == -INFINITY ? 0.f : expf(sc - m[g]);
-                l[g] += pr;
+                n >>= 1;
+            } else {
+                part[0] += __shfl_xor_sync(0xffffffffu, part[0], off);
+            }
+        }
+        // this lane holds the complete sum of value index (lane * NV) / 32
+        __syncwarp();
+        my_scores[(lane * NV) >> 5] = part[0];
+        __syncwarp();
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+            float sc[NKB];
+            float mx = m[g];
+#pragma unroll
+            for (int j = 0; j < NKB; ++j) {
+                sc[j] = my_scores[g * NKB + j] * a.scale;
+                if (a.mask != nullptr && kb + j < count) {
+                    const int64_t mh = a.mask_heads == 1 ? 0 : hk * G + g;
+                    sc[j] += a.mask[(mh * a.nq + q) * a.nk + k0 + kb + j];
+                }
+                if (kb + j >= count) sc[j] = -INFINITY;
+                mx = fmaxf(mx, sc[j]);
+            }
+            if (mx != -INFINITY) {   // warp-uniform: every lane holds the same scores
+                const float corr = m[g] == -INFINITY ? 0.f : expf(m[g] - mx);
+                float pr[NKB], psum = 0.f;
+#pragma unroll
+                for (int j = 0; j < NKB; ++j) {
+                    pr[j] = expf(sc[j] - mx);   // exp(-inf) = 0 for hidden keys
+                    psum += pr[j];
+                }
+                l[g] = fmaf(l[g], corr, psum);
+                m[g] = mx;
 #pragma unroll
                 for (int i = 0; i < D4; ++i) {
-                    o[g][i].x = fmaf(pr, vv[u][i].x, o[g][i].x);
-                    o[g][i].y = fmaf(pr, vv[u][i].y, o[g][i].y);
-                    o[g][i].z = fmaf(pr, vv[u][i].z, o[g][i].z);
-                    o[g][i].w = fmaf(pr, vv[u][i].w, o[g][i].w);
+                    float4 acc = make_float4(o[g][i].x * corr, o[g][i].y * corr, o[g][i].z * corr, o[g][i].w * corr);
+#pragma unroll
+                    for (int j = 0; j < NKB; ++j) {
+                        acc.x = fmaf(pr[j], vv[j][i].x, acc.x);
+                        acc.y = fmaf(pr[j], vv[j][i].y, acc.y);
+                        acc.z = fmaf(pr[j], vv[j][i].z, acc.z);
+                        acc.w = fmaf(pr[j], vv[j][i].w, acc.w);
+                    }
+                    o[g][i] = acc;
                 }
             }
         }
     }
+    __syncwarp();
     // warps -> shared memory
 #pragma unroll
     for (int g = 0; g < G; ++g) {

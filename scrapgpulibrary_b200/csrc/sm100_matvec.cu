@@ -20,6 +20,7 @@
 
 namespace sm100 {
 
+int matvec_q6k_imma_tiles(cudaStream_t s, const void * w, int64_t k, int64_t n, const float * x, float * y, bool * handled);
 int matvec_b32_imma_tiles(cudaStream_t s, int dtype, const void * w, int64_t k, int64_t n, const float * x, float * y, bool * handled);
 int matvec_q4k_imma_tiles(cudaStream_t s, const void * w, int64_t k, int64_t n, const float * x, int64_t ldx, int64_t m, float * y, int64_t ldy,
                           bool * handled);
@@ -508,6 +509,16 @@ int matvec(cudaStream_t s, int dtype, int layout, const void * w, int64_t w_row_
             if (full == n) return ST_OK;
             return dtype == DT_Q4_0 ? launch_rows<UnitQ40, true>(s, w, 0, k, n, x, ldx, m, y, ldy, full)
                                     : launch_rows<UnitQ80, true>(s, w, 0, k, n, x, ldx, m, y, ldy, full);
+        }
+    }
+    static const int use_q6k = env_int("SM100_Q6K_IMMA", 1);
+    if (use_q6k && layout == LAYOUT_PACKED && dtype == DT_Q6_K && x_aligned && m == 1) {
+        bool handled = false;
+        const int st = matvec_q6k_imma_tiles(s, w, k, n, x, y, &handled);
+        if (st != ST_OK) return st;
+        if (handled) {
+            const int64_t full = (n / 16) * 16;
+            return full == n ? ST_OK : launch_rows<UnitQ6K, true>(s, w, 0, k, n, x, ldx, m, y, ldy, full);
         }
     }
     static const int use_mma = env_int("SM100_Q4K_MMA", 1);

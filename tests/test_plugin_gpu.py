@@ -456,3 +456,33 @@ def test_unmodified_reference_example_runs_on_cuda_sm100():
     assert "(b200)" in r.stdout, r.stdout
     m = re.search(r"NMSE ([0-9.e+-]+)", r.stdout)
     assert m and float(m.group(1)) <= 1e-6, r.stdout
+
+
+def test_set_rows_pair_matches_two_set_rows(both):
+    """SET_ROWS_PAIR (K and V rows of one token into their caches in one op) against two plain SET_ROWS on the CPU
+    backend, which does not implement the fused op (src/core/ref/ops.cpp:1428-1429; ops_tests.cpp:765-776 compares
+    the same way)."""
+    cpu, gpu = both
+    ks, vs = rnd(31, 8, 1, 128), rnd(32, 8, 1, 128)
+    ids = np.array([9], np.int32)
+    want = []
+    for src in (ks, vs):
+        cache = cpu.tensor(abi.F32, [128, 16, 8])
+        refapi.check(refapi.lib().scrapgpu_buffer_fill(cpu.stream, cache.buf, 0, cache.nbytes, 0, 1), "fill")
+        cpu.execute(abi.OP_SET_ROWS, [cpu.tensor(abi.F32, [128, 1, 8]).upload(src), cpu.tensor(abi.I32, [1]).upload(ids)], [cache], abi.SetRowsParams())
+        want.append(cache.download(np.float32, 128 * 16 * 8))
+    caches = [gpu.tensor(abi.F32, [128, 16, 8]) for _ in range(2)]
+    for c in caches:
+        refapi.check(refapi.lib().scrapgpu_buffer_fill(gpu.stream, c.buf, 0, c.nbytes, 0, 1), "fill")
+    ins = [gpu.tensor(abi.F32, [128, 1, 8]).upload(ks), gpu.tensor(abi.I32, [1]).upload(ids),
+           gpu.tensor(abi.F32, [128, 1, 8]).upload(vs), gpu.tensor(abi.I32, [1]).upload(ids)]
+    st, why = gpu.supported(abi.OP_SET_ROWS_PAIR, ins, caches)
+    assert st == abi.OK, why
+    gpu.execute(abi.OP_SET_ROWS_PAIR, ins, caches)
+    gpu.sync()
+    for c, w_ in zip(caches, want):
+        assert np.array_equal(c.download(np.float32, 128 * 16 * 8), w_)
+    # mixed destination dtypes are refused with a reason
+    bad = [gpu.tensor(abi.F32, [128, 16, 8]), gpu.tensor(abi.F16, [128, 16, 8])]
+    st, why = gpu.supported(abi.OP_SET_ROWS_PAIR, ins, bad)
+    assert st in (abi.UNSUPPORTED, abi.INVALID_ARGUMENT) and why
