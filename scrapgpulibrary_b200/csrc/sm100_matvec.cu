@@ -512,7 +512,9 @@ int matvec(cudaStream_t s, int dtype, int layout, const void * w, int64_t w_row_
         }
     }
     static const int use_q6k = env_int("SM100_Q6K_IMMA", 1);
-    if (use_q6k && layout == LAYOUT_PACKED && dtype == DT_Q6_K && x_aligned && m == 1) {
+    // measured: the tensor-core kernel wins on small tensors (4096 x 4096: 1.7 vs 1.25 TB/s), the streaming kernel on
+    // large ones (vocabulary head: 4.1 vs 2.1 TB/s), where its lower instruction count per byte pays
+    if (use_q6k && layout == LAYOUT_PACKED && dtype == DT_Q6_K && x_aligned && m == 1 && (use_q6k > 1 || n * k <= (int64_t) 20 << 20)) {
         bool handled = false;
         const int st = matvec_q6k_imma_tiles(s, w, k, n, x, y, &handled);
         if (st != ST_OK) return st;

@@ -64,10 +64,6 @@ __device__ __forceinline__ void bq_load(BqBlock<Q8> & b, const uint8_t * p) {
     }
 }
 
-struct BqStage {
-    uint32_t d;   // f16 scales of rows g (low half) and g + 8 (high half) for this lane's block
-};
-
 // Shared memory of one CTA:
 //   xq   [K/32][2 planes][32 B]   quantized activations, natural order inside a block; 64 zero bytes follow
 //   xs   [K/32] float2            (s_b, 8 * sum of the block's integers as float - Q4_0's offset term)
@@ -105,23 +101,36 @@ __global__ void __launch_bounds__(BQ_THREADS, 1) matvec_b32_imma(BqArgs p) {
     // activations -> 16-bit integers per 32-element block.  One item = 4 consecutive elements; the 8 items of a
     // block sit in 8 consecutive lanes.
     if (tid < 16) xq[p.blocks * 16 + tid] = 0u;
-    for (int it = tid; it < p.blocks * 8; it += BQ_THREADS) {
-        const int sb = it >> 3, q = it & 7;
-        const float4 v = __ldcg(reinterpret_cast<const float4 *>(p.x) + it);   // coherent: the producer may still be running when this kernel starts
-        float amax = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
+    // all loads of a batch are issued before the first one is used: one L2 latency per batch, not per trip
+    constexpr int BATCH = 6;
+    for (int base = 0; base < p.blocks * 8; base += BATCH * BQ_THREADS) {
+        float4 xv[BATCH];
 #pragma unroll
-        for (int o = 1; o < 8; o <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-        const bool some = amax > 1e-30f;   // below that the block counts as zero
-        const float inv = some ? __fdividef(32512.0f, amax) : 0.0f;
-        const int x0 = __float2int_rn(v.x * inv), x1 = __float2int_rn(v.y * inv), x2 = __float2int_rn(v.z * inv), x3 = __float2int_rn(v.w * inv);
-        int isum = (x0 + x1) + (x2 + x3);
+        for (int i = 0; i < BATCH; ++i) {
+            const int it = base + i * BQ_THREADS + tid;
+            if (it < p.blocks * 8) xv[i] = __ldcg(reinterpret_cast<const float4 *>(p.x) + it);   // coherent: the producer may still be running when this kernel starts
+        }
 #pragma unroll
-        for (int o = 1; o < 8; o <<= 1) isum += __shfl_xor_sync(0xffffffffu, isum, o);
-        // 16-bit integer = 256 h + l with h, l signed bytes: h = (x + 128) >> 8, l = low byte of x
-        const int h0 = (x0 + 128) >> 8, h1 = (x1 + 128) >> 8, h2 = (x2 + 128) >> 8, h3 = (x3 + 128) >> 8;
-        xq[sb * 16 + q] = __byte_perm(__byte_perm((uint32_t) h0, (uint32_t) h1, 0x0040), __byte_perm((uint32_t) h2, (uint32_t) h3, 0x0040), 0x5410);
-        xq[sb * 16 + 8 + q] = __byte_perm(__byte_perm((uint32_t) x0, (uint32_t) x1, 0x0040), __byte_perm((uint32_t) x2, (uint32_t) x3, 0x0040), 0x5410);
-        if (q == 0) xs[sb] = make_float2(some ? amax * (1.0f / 32512.0f) : 0.0f, 8.0f * (float) isum);
+        for (int i = 0; i < BATCH; ++i) {
+            const int it = base + i * BQ_THREADS + tid;
+            if (it >= p.blocks * 8) continue;   // warp-uniform: the item count is a multiple of 32
+            const float4 v = xv[i];
+            const int sb = it >> 3, q = it & 7;
+            float amax = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
+#pragma unroll
+            for (int o = 1; o < 8; o <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+            const bool some = amax > 1e-30f;   // below that the block counts as zero
+            const float inv = some ? __fdividef(32512.0f, amax) : 0.0f;
+            const int x0 = __float2int_rn(v.x * inv), x1 = __float2int_rn(v.y * inv), x2 = __float2int_rn(v.z * inv), x3 = __float2int_rn(v.w * inv);
+            int isum = (x0 + x1) + (x2 + x3);
+#pragma unroll
+            for (int o = 1; o < 8; o <<= 1) isum += __shfl_xor_sync(0xffffffffu, isum, o);
+            // 16-bit integer = 256 h + l with h, l signed bytes: h = (x + 128) >> 8, l = low byte of x
+            const int h0 = (x0 + 128) >> 8, h1 = (x1 + 128) >> 8, h2 = (x2 + 128) >> 8, h3 = (x3 + 128) >> 8;
+            xq[sb * 16 + q] = __byte_perm(__byte_perm((uint32_t) h0, (uint32_t) h1, 0x0040), __byte_perm((uint32_t) h2, (uint32_t) h3, 0x0040), 0x5410);
+            xq[sb * 16 + 8 + q] = __byte_perm(__byte_perm((uint32_t) x0, (uint32_t) x1, 0x0040), __byte_perm((uint32_t) x2, (uint32_t) x3, 0x0040), 0x5410);
+            if (q == 0) xs[sb] = make_float2(some ? amax * (1.0f / 32512.0f) : 0.0f, 8.0f * (float) isum);
+        }
     }
     __syncthreads();
     pdl_launch_dependents();

@@ -249,21 +249,54 @@ __global__ void __launch_bounds__(IQ_THREADS, NB == 1 ? 2 : 1) matvec_q4k_imma(I
         if (q == 0) xs2[(size_t) m * nsb_of(p) + sb] = make_float2(s, sum);
     };
     if (M > 1 || p.prologue == 0) {
-        for (int it0 = tid; it0 < M * items; it0 += IQ_THREADS) {
-            const int m = it0 / items, it = it0 - m * items;
-            // coherent load: the producer may still be running when this kernel starts
-            quantize_item(__ldcg(reinterpret_cast<const float4 *>(p.x + (int64_t) m * p.ldx + (int64_t) it * 4)), m, it);
+        // all loads of a batch are issued before the first one is used: the row comes from L2 with one latency,
+        // not one per loop trip (coherent loads: the producer may still be running when this kernel starts)
+        constexpr int BATCH = 6;
+        for (int base = 0; base < M * items; base += BATCH * IQ_THREADS) {
+            float4 xv[BATCH];
+#pragma unroll
+            for (int i = 0; i < BATCH; ++i) {
+                const int it0 = base + i * IQ_THREADS + tid;
+                if (it0 < M * items) {
+                    const int m = it0 / items, it = it0 - m * items;
+                    xv[i] = __ldcg(reinterpret_cast<const float4 *>(p.x + (int64_t) m * p.ldx + (int64_t) it * 4));
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < BATCH; ++i) {
+                const int it0 = base + i * IQ_THREADS + tid;
+                if (it0 < M * items) {   // warp-uniform: the item count is a multiple of 64
+                    const int m = it0 / items, it = it0 - m * items;
+                    quantize_item(xv[i], m, it);
+                }
+            }
         }
     } else if (p.prologue == 1) {
         // SwiGLU (src/core/ref/ops.cpp:383-425): (a / (1 + expf(-a))) * b, the arithmetic of swiglu_kernel
-        for (int it = tid; it < items; it += IQ_THREADS) {
-            const float4 a = __ldcg(reinterpret_cast<const float4 *>(p.pa) + it), b = __ldcg(reinterpret_cast<const float4 *>(p.pb) + it);
-            float4 v;
-            v.x = __fmul_rn(__fdiv_rn(a.x, __fadd_rn(1.0f, expf(-a.x))), b.x);
-            v.y = __fmul_rn(__fdiv_rn(a.y, __fadd_rn(1.0f, expf(-a.y))), b.y);
-            v.z = __fmul_rn(__fdiv_rn(a.z, __fadd_rn(1.0f, expf(-a.z))), b.z);
-            v.w = __fmul_rn(__fdiv_rn(a.w, __fadd_rn(1.0f, expf(-a.w))), b.w);
-            quantize_item(v, 0, it);
+        constexpr int BATCH = 3;
+        for (int base = 0; base < items; base += BATCH * IQ_THREADS) {
+            float4 av[BATCH], bv[BATCH];
+#pragma unroll
+            for (int i = 0; i < BATCH; ++i) {
+                const int it = base + i * IQ_THREADS + tid;
+                if (it < items) {
+                    av[i] = __ldcg(reinterpret_cast<const float4 *>(p.pa) + it);
+                    bv[i] = __ldcg(reinterpret_cast<const float4 *>(p.pb) + it);
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < BATCH; ++i) {
+                const int it = base + i * IQ_THREADS + tid;
+                if (it < items) {
+                    const float4 a = av[i], b = bv[i];
+                    float4 v;
+                    v.x = __fmul_rn(__fdiv_rn(a.x, __fadd_rn(1.0f, expf(-a.x))), b.x);
+                    v.y = __fmul_rn(__fdiv_rn(a.y, __fadd_rn(1.0f, expf(-a.y))), b.y);
+                    v.z = __fmul_rn(__fdiv_rn(a.z, __fadd_rn(1.0f, expf(-a.z))), b.z);
+                    v.w = __fmul_rn(__fdiv_rn(a.w, __fadd_rn(1.0f, expf(-a.w))), b.w);
+                    quantize_item(v, 0, it);
+                }
+            }
         }
     } else {
         // (ADD_)RMS_NORM_MUL (src/core/ref/ops.cpp:466-519): every CTA normalises the whole row itself (it reads

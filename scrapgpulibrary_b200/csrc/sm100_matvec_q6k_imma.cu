@@ -89,23 +89,36 @@ __global__ void __launch_bounds__(SQ_THREADS, 1) matvec_q6k_imma(SqArgs p) {
     // activations -> 16-bit integers per 16-element group.  One item = 4 consecutive elements; the 4 items of a
     // group sit in 4 consecutive lanes.
     if (tid < 8) xq[ngroups * 8 + tid] = 0u;
-    for (int it = tid; it < ngroups * 4; it += SQ_THREADS) {
-        const int grp = it >> 2, q = it & 3;
-        const float4 v = __ldcg(reinterpret_cast<const float4 *>(p.x) + it);   // coherent: the producer may still be running when this kernel starts
-        float amax = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
-        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-        const bool some = amax > 1e-30f;   // below that the group counts as zero
-        const float inv = some ? __fdividef(32512.0f, amax) : 0.0f;
-        const int x0 = __float2int_rn(v.x * inv), x1 = __float2int_rn(v.y * inv), x2 = __float2int_rn(v.z * inv), x3 = __float2int_rn(v.w * inv);
-        int isum = (x0 + x1) + (x2 + x3);
-        isum += __shfl_xor_sync(0xffffffffu, isum, 1);
-        isum += __shfl_xor_sync(0xffffffffu, isum, 2);
-        // 16-bit integer = 256 h + l with h, l signed bytes: h = (x + 128) >> 8, l = low byte of x
-        const int h0 = (x0 + 128) >> 8, h1 = (x1 + 128) >> 8, h2 = (x2 + 128) >> 8, h3 = (x3 + 128) >> 8;
-        xq[grp * 8 + q] = __byte_perm(__byte_perm((uint32_t) h0, (uint32_t) h1, 0x0040), __byte_perm((uint32_t) h2, (uint32_t) h3, 0x0040), 0x5410);
-        xq[grp * 8 + 4 + q] = __byte_perm(__byte_perm((uint32_t) x0, (uint32_t) x1, 0x0040), __byte_perm((uint32_t) x2, (uint32_t) x3, 0x0040), 0x5410);
-        if (q == 0) xs[grp] = make_float2(some ? amax * (1.0f / 32512.0f) : 0.0f, __int_as_float(32 * isum));
+    // all loads of a batch are issued before the first one is used: one L2 latency per batch, not per trip
+    constexpr int BATCH = 6;
+    for (int base = 0; base < ngroups * 4; base += BATCH * SQ_THREADS) {
+        float4 xv[BATCH];
+#pragma unroll
+        for (int i = 0; i < BATCH; ++i) {
+            const int it = base + i * SQ_THREADS + tid;
+            if (it < ngroups * 4) xv[i] = __ldcg(reinterpret_cast<const float4 *>(p.x) + it);   // coherent: the producer may still be running when this kernel starts
+        }
+#pragma unroll
+        for (int i = 0; i < BATCH; ++i) {
+            const int it = base + i * SQ_THREADS + tid;
+            if (it >= ngroups * 4) continue;   // warp-uniform: the item count is a multiple of 32
+            const float4 v = xv[i];
+            const int grp = it >> 2, q = it & 3;
+            float amax = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
+            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+            const bool some = amax > 1e-30f;   // below that the group counts as zero
+            const float inv = some ? __fdividef(32512.0f, amax) : 0.0f;
+            const int x0 = __float2int_rn(v.x * inv), x1 = __float2int_rn(v.y * inv), x2 = __float2int_rn(v.z * inv), x3 = __float2int_rn(v.w * inv);
+            int isum = (x0 + x1) + (x2 + x3);
+            isum += __shfl_xor_sync(0xffffffffu, isum, 1);
+            isum += __shfl_xor_sync(0xffffffffu, isum, 2);
+            // 16-bit integer = 256 h + l with h, l signed bytes: h = (x + 128) >> 8, l = low byte of x
+            const int h0 = (x0 + 128) >> 8, h1 = (x1 + 128) >> 8, h2 = (x2 + 128) >> 8, h3 = (x3 + 128) >> 8;
+            xq[grp * 8 + q] = __byte_perm(__byte_perm((uint32_t) h0, (uint32_t) h1, 0x0040), __byte_perm((uint32_t) h2, (uint32_t) h3, 0x0040), 0x5410);
+            xq[grp * 8 + 4 + q] = __byte_perm(__byte_perm((uint32_t) x0, (uint32_t) x1, 0x0040), __byte_perm((uint32_t) x2, (uint32_t) x3, 0x0040), 0x5410);
+            if (q == 0) xs[grp] = make_float2(some ? amax * (1.0f / 32512.0f) : 0.0f, __int_as_float(32 * isum));
+        }
     }
     __syncthreads();
     pdl_launch_dependents();
