@@ -121,7 +121,9 @@ __global__ void __launch_bounds__(BQ_THREADS, 1) matvec_b32_imma(BqArgs p) {
             for (int o = 1; o < 8; o <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
             const bool some = amax > 1e-30f;   // below that the block counts as zero
             const float inv = some ? __fdividef(32512.0f, amax) : 0.0f;
-            const int x0 = __float2int_rn(v.x * inv), x1 = __float2int_rn(v.y * inv), x2 = __float2int_rn(v.z * inv), x3 = __float2int_rn(v.w * inv);
+            // round to nearest (even) without the conversion unit: 1.5 * 2^23 + x keeps the integer in the mantissa (|x| <= 32512)
+        const int x0 = __float_as_int(fmaf(v.x, inv, 12582912.0f)) - 0x4B400000, x1 = __float_as_int(fmaf(v.y, inv, 12582912.0f)) - 0x4B400000,
+                  x2 = __float_as_int(fmaf(v.z, inv, 12582912.0f)) - 0x4B400000, x3 = __float_as_int(fmaf(v.w, inv, 12582912.0f)) - 0x4B400000;
             int isum = (x0 + x1) + (x2 + x3);
 #pragma unroll
             for (int o = 1; o < 8; o <<= 1) isum += __shfl_xor_sync(0xffffffffu, isum, o);

@@ -140,6 +140,12 @@ __device__ __forceinline__ void imma_16832_zero(int (&c)[4], uint32_t a0, uint32
 constexpr uint32_t IQ_WAIT_LIMIT = 1u << 22;         // polls of one barrier before the warp gives up
 
 __device__ int g_iq_fault;
+#ifdef IQ_TIMING
+__device__ unsigned long long g_iq_t[8];   // development: cycles of CTA 0 per phase, summed over launches; [7] = launches
+#define IQ_T(i) if (blockIdx.x == 0 && threadIdx.x == 0) { const long long now_ = clock64(); atomicAdd(&g_iq_t[i], (unsigned long long) (now_ - t_prev_)); t_prev_ = now_; }
+#else
+#define IQ_T(i)
+#endif
 
 // Shared memory of one CTA:
 //   xq    [M][K/64][128 B]    quantized activations in B-fragment order: per pair [plane h, l][t][low sub-block b0, b1,
@@ -176,6 +182,10 @@ __global__ void __launch_bounds__(IQ_THREADS, NB == 1 ? 2 : 1) matvec_q4k_imma(I
     const int group = wid / IQ_WARPS, warp = wid % IQ_WARPS;
     const int g = lane >> 2, t = lane & 3;
     const int rt_step = gridDim.x * IQ_GROUPS;
+#ifdef IQ_TIMING
+    long long t_prev_ = clock64();
+    if (blockIdx.x == 0 && threadIdx.x == 0) atomicAdd(&g_iq_t[7], 1ull);
+#endif
     const uint32_t bar0 = iq_smem_addr(bars + wid * R);
     const uint32_t hdr0 = iq_smem_addr(hdr) + (uint32_t) wid * R * IQ_HDR_BYTES;
     const uint32_t ring0 = iq_smem_addr(ring) + (uint32_t) wid * R * IQ_SLOT_BYTES;
@@ -218,7 +228,9 @@ __global__ void __launch_bounds__(IQ_THREADS, NB == 1 ? 2 : 1) matvec_q4k_imma(I
         }
     }
 
+    IQ_T(0)   // set-up and first requests
     pdl_wait();
+    IQ_T(1)   // waiting for the predecessor
 
     // activations -> 16-bit integers per 32-element sub-block.  One item = 4 consecutive elements; the 8 items of
     // a sub-block sit in 8 consecutive lanes.
@@ -237,7 +249,9 @@ __global__ void __launch_bounds__(IQ_THREADS, NB == 1 ? 2 : 1) matvec_q4k_imma(I
         const float inv = some ? __fdividef(32512.0f, amax) : 0.0f;
         const float s = some ? amax * (1.0f / 32512.0f) : 0.0f;
         // 16-bit integer = 256 h + l with h, l signed bytes: h = (x + 128) >> 8, l = x - 256 h
-        const int x0 = __float2int_rn(v.x * inv), x1 = __float2int_rn(v.y * inv), x2 = __float2int_rn(v.z * inv), x3 = __float2int_rn(v.w * inv);
+        // round to nearest (even) without the conversion unit: 1.5 * 2^23 + x keeps the integer in the mantissa (|x| <= 32512)
+        const int x0 = __float_as_int(fmaf(v.x, inv, 12582912.0f)) - 0x4B400000, x1 = __float_as_int(fmaf(v.y, inv, 12582912.0f)) - 0x4B400000,
+                  x2 = __float_as_int(fmaf(v.z, inv, 12582912.0f)) - 0x4B400000, x3 = __float_as_int(fmaf(v.w, inv, 12582912.0f)) - 0x4B400000;
         const int h0 = (x0 + 128) >> 8, h1 = (x1 + 128) >> 8, h2 = (x2 + 128) >> 8, h3 = (x3 + 128) >> 8;
         const uint32_t hp = __byte_perm(__byte_perm((uint32_t) h0, (uint32_t) h1, 0x0040), __byte_perm((uint32_t) h2, (uint32_t) h3, 0x0040), 0x5410);
         // the low bytes of x are the bytes of l (x - 256 h keeps the low byte)
@@ -342,6 +356,7 @@ __global__ void __launch_bounds__(IQ_THREADS, NB == 1 ? 2 : 1) matvec_q4k_imma(I
         __syncthreads();   // dred is part of `red`: everyone has read it before the rounds write there
     }
     __syncthreads();
+    IQ_T(2)   // activation quantization
     pdl_launch_dependents();
 
     // per-lane views.  Pair j of a block feeds B columns 2j (h plane) and 2j+1 (l plane): lane (g, t) supplies
@@ -421,6 +436,7 @@ __global__ void __launch_bounds__(IQ_THREADS, NB == 1 ? 2 : 1) matvec_q4k_imma(I
             }
             if (++cslot == R) { cslot = 0; cphase ^= 1u; }
         }
+        IQ_T(3)   // chunks of this round (waits included)
         // sum over the four lanes of a row (each held other sub-blocks), then over the warps (each held other chunks)
 #pragma unroll
         for (int m = 0; m < M; ++m) {
@@ -450,6 +466,7 @@ __global__ void __launch_bounds__(IQ_THREADS, NB == 1 ? 2 : 1) matvec_q4k_imma(I
             }
         }
         __syncthreads();
+        IQ_T(4)   // reduction and store of this round
         rt += rt_step;
         chunk = warp;
     }
@@ -483,6 +500,14 @@ int launch_iq(cudaStream_t s, const IqArgs & a, size_t smem, int grid) {
 std::atomic<bool> g_iq_launched{false};
 
 }  // namespace
+
+#ifdef IQ_TIMING
+extern "C" __attribute__((visibility("default"))) int sm100_debug_iq_timing(unsigned long long * out, int reset) {
+    if (cudaMemcpyFromSymbol(out, g_iq_t, sizeof(unsigned long long) * 8) != cudaSuccess) return 4;
+    if (reset) { unsigned long long z[8] = {}; cudaMemcpyToSymbol(g_iq_t, z, sizeof(z)); }
+    return 0;
+}
+#endif
 
 // Reads and clears the kernel's fault flag on the current device (set when a warp gave up waiting for a copy);
 // called after a stream synchronisation.

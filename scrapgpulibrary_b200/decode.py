@@ -18,6 +18,7 @@ stream, graph capture and the NCCL process group; every kernel on the path is th
 from __future__ import annotations
 
 import ctypes as C
+import os
 import zlib
 from dataclasses import dataclass
 
@@ -84,6 +85,7 @@ class DecodeModel:
         self.stream = C.c_void_p(self.tstream.cuda_stream)
         self.allreduce = allreduce
         self.fuse = fuse   # fold RMS norm / SwiGLU into the Q4_K projections that consume them (one launch each)
+        self.fuse_swiglu = fuse and os.environ.get("SM100_FUSE_SWIGLU", "1") != "0"
         c = cfg
         self.hq, self.hkv = c.heads // world, c.kv_heads // world
         self.q_dim, self.kv_dim, self.ffn = self.hq * c.head_dim, self.hkv * c.head_dim, c.ffn // world
@@ -273,7 +275,7 @@ class DecodeModel:
             else:
                 chk(L.sm100_rms_norm(s, _dev(x_cur), _dev(self.proj), _dev(lw["ffn_norm"]), _dev(x_cur), _dev(self.xn), c.hidden, 1, c.eps), "add_rms_norm")
                 self._mm_multi([lw["wgate"], lw["wup"]], self.xn, [self.gate, self.up])
-            if self.fuse and lw["wdown"].dtype == Q4_K:
+            if self.fuse_swiglu and lw["wdown"].dtype == Q4_K:
                 self._mm_fused(1, self.gate, self.up, None, None, None, [lw["wdown"]], [self.proj])
             else:
                 chk(L.sm100_swiglu(s, _dev(self.gate), _dev(self.up), _dev(self.act), self.ffn), "swiglu")
