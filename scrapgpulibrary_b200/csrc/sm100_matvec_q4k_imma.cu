@@ -162,7 +162,10 @@ __device__ unsigned long long g_iq_t[8];   // development: cycles of CTA 0 per p
 // NB = 256-weight blocks per chunk: 2 with one CTA per SM, or 1 with two CTAs per SM (more warps to hide latencies,
 // and one CTA's barriers overlap the other's arithmetic).
 // FULL: K is a whole number of chunks (no block-range checks in the loops).
-template <int M, int NB, bool FULL>
+// CL = 2: the kernel runs in clusters of two CTAs (the two SMs of a TPC) that quantize half of the activation column
+// each and store the result into both CTAs' shared memory (distributed shared memory), which halves the fixed
+// cost every CTA pays before its first MMA.
+template <int M, int NB, bool FULL, int CL>
 __global__ void __launch_bounds__(IQ_THREADS, NB == 1 ? 2 : 1) matvec_q4k_imma(IqArgs p) {
     constexpr int IQ_TILES = 4 * NB;                    // pair tiles (64 weights each) per chunk
     constexpr uint32_t IQ_SLOT_BYTES = IQ_TILES * 512;  // weight tiles of one chunk
@@ -236,6 +239,20 @@ __global__ void __launch_bounds__(IQ_THREADS, NB == 1 ? 2 : 1) matvec_q4k_imma(I
     // a sub-block sit in 8 consecutive lanes.
     const int items = p.pairs * 16;
     if (tid < 4) xq[xq_bytes / 4 + tid] = 0u;
+    // cluster peer's view of this CTA's shared-memory offsets (CL = 2 and a prologue that can be split)
+    uint32_t cta_rank = 0;
+    bool share = false;
+    uint32_t peer_xq = 0, peer_xs = 0;
+    if (CL == 2) {
+        asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(cta_rank));
+        share = M == 1;
+        const uint32_t peer = cta_rank ^ 1u;
+        asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(peer_xq) : "r"(iq_smem_addr(xq)), "r"(peer));
+        asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(peer_xs) : "r"(iq_smem_addr(xs2)), "r"(peer));
+    }
+    // with sharing, this CTA takes every other group of 32 items (4 sub-blocks): local item li -> item it
+    const int my_items = share ? items / 2 : items;
+    auto item_of = [&](int li) { return share ? (((li >> 5) * 2 + (int) cta_rank) << 5) + (li & 31) : li; };
     auto quantize_item = [&](const float4 v, int m, int it) {
         const int sb = it >> 3, q = it & 7;
         float amax = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
@@ -257,30 +274,37 @@ __global__ void __launch_bounds__(IQ_THREADS, NB == 1 ? 2 : 1) matvec_q4k_imma(I
         // the low bytes of x are the bytes of l (x - 256 h keeps the low byte)
         const uint32_t lp = __byte_perm(__byte_perm((uint32_t) x0, (uint32_t) x1, 0x0040), __byte_perm((uint32_t) x2, (uint32_t) x3, 0x0040), 0x5410);
         // word of the pair: plane * 16 + t * 4 + (high sub-block ? 2 : 0) + (k >= 16 ? 1 : 0)
-        uint32_t * dst = xq + ((size_t) m * p.pairs + (sb >> 1)) * 32 + (q & 3) * 4 + (sb & 1) * 2 + (q >> 2);
-        dst[0] = hp;
-        dst[16] = lp;
+        const uint32_t word = (uint32_t) (((size_t) m * p.pairs + (sb >> 1)) * 32 + (q & 3) * 4 + (sb & 1) * 2 + (q >> 2));
+        xq[word] = hp;
+        xq[word + 16] = lp;
         if (q == 0) xs2[(size_t) m * nsb_of(p) + sb] = make_float2(s, sum);
+        if (CL == 2 && share) {
+            asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(peer_xq + word * 4u), "r"(hp) : "memory");
+            asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(peer_xq + (word + 16u) * 4u), "r"(lp) : "memory");
+            if (q == 0)
+                asm volatile("st.shared::cluster.v2.f32 [%0], {%1, %2};" ::"r"(peer_xs + (uint32_t) ((size_t) m * nsb_of(p) + sb) * 8u), "f"(s), "f"(sum)
+                             : "memory");
+        }
     };
     if (M > 1 || p.prologue == 0) {
         // all loads of a batch are issued before the first one is used: the row comes from L2 with one latency,
         // not one per loop trip (coherent loads: the producer may still be running when this kernel starts)
         constexpr int BATCH = 6;
-        for (int base = 0; base < M * items; base += BATCH * IQ_THREADS) {
+        for (int base = 0; base < M * my_items; base += BATCH * IQ_THREADS) {
             float4 xv[BATCH];
 #pragma unroll
             for (int i = 0; i < BATCH; ++i) {
                 const int it0 = base + i * IQ_THREADS + tid;
-                if (it0 < M * items) {
-                    const int m = it0 / items, it = it0 - m * items;
+                if (it0 < M * my_items) {
+                    const int m = it0 / my_items, it = item_of(it0 - m * my_items);
                     xv[i] = __ldcg(reinterpret_cast<const float4 *>(p.x + (int64_t) m * p.ldx + (int64_t) it * 4));
                 }
             }
 #pragma unroll
             for (int i = 0; i < BATCH; ++i) {
                 const int it0 = base + i * IQ_THREADS + tid;
-                if (it0 < M * items) {   // warp-uniform: the item count is a multiple of 64
-                    const int m = it0 / items, it = it0 - m * items;
+                if (it0 < M * my_items) {   // warp-uniform: the item counts are multiples of 32
+                    const int m = it0 / my_items, it = item_of(it0 - m * my_items);
                     quantize_item(xv[i], m, it);
                 }
             }
@@ -288,20 +312,21 @@ __global__ void __launch_bounds__(IQ_THREADS, NB == 1 ? 2 : 1) matvec_q4k_imma(I
     } else if (p.prologue == 1) {
         // SwiGLU (src/core/ref/ops.cpp:383-425): (a / (1 + expf(-a))) * b, the arithmetic of swiglu_kernel
         constexpr int BATCH = 3;
-        for (int base = 0; base < items; base += BATCH * IQ_THREADS) {
+        for (int base = 0; base < my_items; base += BATCH * IQ_THREADS) {
             float4 av[BATCH], bv[BATCH];
 #pragma unroll
             for (int i = 0; i < BATCH; ++i) {
-                const int it = base + i * IQ_THREADS + tid;
-                if (it < items) {
-                    av[i] = __ldcg(reinterpret_cast<const float4 *>(p.pa) + it);
-                    bv[i] = __ldcg(reinterpret_cast<const float4 *>(p.pb) + it);
+                const int li = base + i * IQ_THREADS + tid;
+                if (li < my_items) {
+                    av[i] = __ldcg(reinterpret_cast<const float4 *>(p.pa) + item_of(li));
+                    bv[i] = __ldcg(reinterpret_cast<const float4 *>(p.pb) + item_of(li));
                 }
             }
 #pragma unroll
             for (int i = 0; i < BATCH; ++i) {
-                const int it = base + i * IQ_THREADS + tid;
-                if (it < items) {
+                const int li = base + i * IQ_THREADS + tid;
+                const int it = item_of(li);
+                if (li < my_items) {
                     const float4 a = av[i], b = bv[i];
                     float4 v;
                     v.x = __fmul_rn(__fdiv_rn(a.x, __fadd_rn(1.0f, expf(-a.x))), b.x);
@@ -313,49 +338,70 @@ __global__ void __launch_bounds__(IQ_THREADS, NB == 1 ? 2 : 1) matvec_q4k_imma(I
             }
         }
     } else {
-        // (ADD_)RMS_NORM_MUL (src/core/ref/ops.cpp:466-519): every CTA normalises the whole row itself (it reads
-        // it anyway); the row stays in registers between the two passes (the host bounds K for that)
+        // (ADD_)RMS_NORM_MUL (src/core/ref/ops.cpp:466-519): every CTA (or pair of CTAs) normalises the row itself
+        // (it reads it anyway); the row stays in registers between the two passes (the host bounds K for that)
         constexpr int MAXI = 4;
         float4 v[MAXI];
         double sq = 0.0;
+        const bool writer = CL == 2 && share ? blockIdx.x < 2 : blockIdx.x == 0;   // who stores the side outputs
 #pragma unroll
         for (int i = 0; i < MAXI; ++i) {
-            const int it = tid + i * IQ_THREADS;
+            const int li = tid + i * IQ_THREADS;
+            const int it = item_of(li);
             v[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (it < items) {
+            if (li < my_items) {
                 v[i] = __ldcg(reinterpret_cast<const float4 *>(p.pa) + it);
                 if (p.pb != nullptr) {
                     const float4 b = __ldcg(reinterpret_cast<const float4 *>(p.pb) + it);
                     v[i] = make_float4(__fadd_rn(v[i].x, b.x), __fadd_rn(v[i].y, b.y), __fadd_rn(v[i].z, b.z), __fadd_rn(v[i].w, b.w));
                 }
-                if (p.sum_out != nullptr && blockIdx.x == 0) reinterpret_cast<float4 *>(p.sum_out)[it] = v[i];
+                if (p.sum_out != nullptr && writer) reinterpret_cast<float4 *>(p.sum_out)[it] = v[i];
                 sq += ((double) v[i].x * (double) v[i].x + (double) v[i].y * (double) v[i].y) +
                       ((double) v[i].z * (double) v[i].z + (double) v[i].w * (double) v[i].w);
             }
         }
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
-        double * dred = reinterpret_cast<double *>(red);   // 16 doubles: the partial-output area is free before the first round
+        double * dred = reinterpret_cast<double *>(red);   // 16 + 2 doubles: the partial-output area is free before the first round
         if (lane == 0) dred[wid] = sq;
         __syncthreads();
         double tot = 0.0;
 #pragma unroll
         for (int w = 0; w < IQ_WARPS * IQ_GROUPS; ++w) tot += dred[w];
+        if (CL == 2 && share) {
+            // the two CTAs exchange their halves of the sum of squares and add them in rank order (same bits in both)
+            if (tid == 0) {
+                dred[16 + cta_rank] = tot;
+                uint32_t peer_slot;
+                asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(peer_slot) : "r"(iq_smem_addr(dred + 16 + cta_rank)), "r"(cta_rank ^ 1u));
+                asm volatile("st.shared::cluster.f64 [%0], %1;" ::"r"(peer_slot), "d"(tot) : "memory");
+            }
+            asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+            asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+            tot = dred[16] + dred[17];
+        }
         const float scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn((float) (tot / (double) (items * 4)), p.eps)));
 #pragma unroll
         for (int i = 0; i < MAXI; ++i) {
-            const int it = tid + i * IQ_THREADS;
-            if (it < items) {   // warp-uniform: items is a multiple of 64
+            const int li = tid + i * IQ_THREADS;
+            const int it = item_of(li);
+            if (li < my_items) {   // warp-uniform: the item counts are multiples of 32
                 const float4 w4 = __ldg(reinterpret_cast<const float4 *>(p.pw) + it);
                 const float4 r = make_float4(__fmul_rn(__fmul_rn(v[i].x, scale), w4.x), __fmul_rn(__fmul_rn(v[i].y, scale), w4.y),
                                              __fmul_rn(__fmul_rn(v[i].z, scale), w4.z), __fmul_rn(__fmul_rn(v[i].w, scale), w4.w));
-                if (p.x_out != nullptr && blockIdx.x == 0) reinterpret_cast<float4 *>(p.x_out)[it] = r;
+                if (p.x_out != nullptr && writer) reinterpret_cast<float4 *>(p.x_out)[it] = r;
                 quantize_item(r, 0, it);
             }
         }
         __syncthreads();   // dred is part of `red`: everyone has read it before the rounds write there
     }
-    __syncthreads();
+    if (CL == 2) {
+        // both CTAs' halves are in place (release / acquire at cluster scope; also a barrier for this CTA's threads)
+        asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+        asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+    } else {
+        __syncthreads();
+    }
     IQ_T(2)   // activation quantization
     pdl_launch_dependents();
 
@@ -487,9 +533,18 @@ template <int M, int NB, bool FULL>
 int launch_iq_full(cudaStream_t s, const IqArgs & a, size_t smem, int grid) {
     // always the device maximum: a smaller value set by a later launch would undercut kernel nodes already
     // recorded in a graph when a tool re-launches them
+    static const int use_cluster = [] { const char * e = getenv("SM100_Q4K_CLUSTER"); return e != nullptr ? atoi(e) : 1; }();
+    // measured: the pair pays off from K = 8192 on (K = 12288: 6440 -> 5270 cycles before the first MMA); below that the
+    // cluster barrier and the remote stores cost more than the half row they save (K = 4096: 2240 -> 2850)
+    if (use_cluster && M == 1 && NB == 2 && (use_cluster > 1 || a.pairs >= 128)) {
+        if (smem > 48 * 1024)
+            SM100_CUDA(cudaFuncSetAttribute(matvec_q4k_imma<M, NB, FULL, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+        const int even = (grid + 1) & ~1;   // an extra CTA finds no row tile but still takes its half of the quantization
+        return launch_cluster(matvec_q4k_imma<M, NB, FULL, 2>, dim3((unsigned) even), dim3(IQ_THREADS), smem, s, 2u, a);
+    }
     if (smem > 48 * 1024)
-        SM100_CUDA(cudaFuncSetAttribute(matvec_q4k_imma<M, NB, FULL>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
-    return launch(matvec_q4k_imma<M, NB, FULL>, dim3((unsigned) grid), dim3(IQ_THREADS), smem, s, a);
+        SM100_CUDA(cudaFuncSetAttribute(matvec_q4k_imma<M, NB, FULL, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+    return launch(matvec_q4k_imma<M, NB, FULL, 1>, dim3((unsigned) grid), dim3(IQ_THREADS), smem, s, a);
 }
 
 template <int M, int NB>
