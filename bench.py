@@ -182,6 +182,9 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         return cnt
 
     def timed_graph(m: int, only_shape, steps: int, warmup: int):
+        if m > 2:   # the multi-column path keeps quantized activations in library scratch: create it outside the capture
+            enqueue_step(m, only_shape if only_shape is not None else 0)
+            stream.sync()
         launches0 = L.sm100_launch_count()
         with capi.Graph(stream) as g:
             matvecs = enqueue_step(m, only_shape)

@@ -22,6 +22,8 @@ namespace sm100 {
 
 int matvec_q6k_imma_tiles(cudaStream_t s, const void * w, int64_t k, int64_t n, const float * x, float * y, bool * handled);
 int matvec_b32_imma_tiles(cudaStream_t s, int dtype, const void * w, int64_t k, int64_t n, const float * x, float * y, bool * handled);
+int matvec_q4k_imma_cols_tiles(cudaStream_t s, const void * w, int64_t k, int64_t n, const float * x, int64_t ldx, int64_t m, float * y, int64_t ldy,
+                               bool * handled);
 int matvec_q4k_imma_tiles(cudaStream_t s, const void * w, int64_t k, int64_t n, const float * x, int64_t ldx, int64_t m, float * y, int64_t ldy,
                           bool * handled);
 int matvec_q4k_tiles(cudaStream_t s, const void * w, int64_t k, int64_t n, const float * x, int64_t ldx, int64_t m, float * y, int64_t ldy,
@@ -521,6 +523,29 @@ int matvec(cudaStream_t s, int dtype, int layout, const void * w, int64_t w_row_
         if (handled) {
             const int64_t full = (n / 16) * 16;
             return full == n ? ST_OK : launch_rows<UnitQ6K, true>(s, w, 0, k, n, x, ldx, m, y, ldy, full);
+        }
+    }
+    if (use_imma && layout == LAYOUT_PACKED && dtype == DT_Q4_K && x_aligned && m >= 3) {
+        // integer tensor-core kernel with the tokens in the B columns; when 8 columns do not fit shared memory, two passes of 4
+        bool handled = false;
+        int st = matvec_q4k_imma_cols_tiles(s, w, k, n, x, ldx, m, y, ldy, &handled);
+        if (st != ST_OK) return st;
+        if (!handled && m > 4) {
+            st = matvec_q4k_imma_cols_tiles(s, w, k, n, x, ldx, 4, y, ldy, &handled);
+            if (st != ST_OK) return st;
+            if (handled) {
+                bool second = false;
+                const int64_t rest = m - 4;
+                if (rest >= 3) st = matvec_q4k_imma_cols_tiles(s, w, k, n, x + 4 * ldx, ldx, rest, y + 4 * ldy, ldy, &second);
+                else st = matvec_q4k_imma_tiles(s, w, k, n, x + 4 * ldx, ldx, rest, y + 4 * ldy, ldy, &second);
+                if (st != ST_OK) return st;
+                if (!second) return fail(ST_BACKEND, "mul_mat: the Q4_K column kernel accepted the first pass but not the second");
+            }
+        }
+        if (handled) {
+            const int64_t full = (n / 16) * 16;
+            if (full < n) return launch_rows<UnitQ4K, true>(s, w, 0, k, n, x, ldx, m, y, ldy, full);
+            return ST_OK;
         }
     }
     static const int use_mma = env_int("SM100_Q4K_MMA", 1);

@@ -27,6 +27,8 @@
 
 namespace sm100 {
 
+int device_scratch(int slot, size_t bytes, void ** out);
+
 namespace {
 
 constexpr int IQ_WARPS = 8;    // warps that share one row tile (they split K)
@@ -524,6 +526,216 @@ __global__ void __launch_bounds__(IQ_THREADS, NB == 1 ? 2 : 1) matvec_q4k_imma(I
     }
 }
 
+// ---------------------------------------------------------------------------------------------------------
+// 3..8 activation columns: "tokens in columns".  The B operand's eight columns are the (h, l) planes of four
+// tokens, so every lane supplies data and one MMA serves four tokens; each MMA covers one sub-block, whose scale is
+// applied right away (lane (g, t) owns token t of the column group for rows g and g + 8 - no reduction inside the
+// warp).  MG = column groups (1: up to 4 tokens, 2: up to 8).  One-block chunks keep the ring small next to the
+// quantized activations of all tokens.
+// ---------------------------------------------------------------------------------------------------------
+// Quantizes the activation columns once for the whole launch that follows: the image has the shared-memory layout
+// of matvec_q4k_imma_cols (per token and pair the B-fragment words, then (s, sum x) per sub-block), so that kernel
+// fetches it with one bulk copy instead of having every CTA redo the work for every token.
+__global__ void __launch_bounds__(256) q4k_quantize_cols(const float * x, int64_t ldx, int m_tokens, int mt, int pairs, uint32_t * img) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int items = pairs * 16;
+    float2 * xs2 = reinterpret_cast<float2 *>(img + (size_t) mt * pairs * 32);
+    for (int it0 = blockIdx.x * blockDim.x + threadIdx.x; it0 < mt * items; it0 += gridDim.x * blockDim.x) {   // whole warps: items is a multiple of 64
+        const int m = it0 / items, it = it0 - m * items;
+        const int sb = it >> 3, q = it & 7;
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (m < m_tokens) v = __ldcg(reinterpret_cast<const float4 *>(x + (int64_t) m * ldx + (int64_t) it * 4));
+        float amax = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
+        float sum = (v.x + v.y) + (v.z + v.w);
+#pragma unroll
+        for (int o = 1; o < 8; o <<= 1) {
+            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+            sum += __shfl_xor_sync(0xffffffffu, sum, o);
+        }
+        const bool some = amax > 1e-30f;
+        const float inv = some ? __fdividef(32512.0f, amax) : 0.0f;
+        const int x0 = __float_as_int(fmaf(v.x, inv, 12582912.0f)) - 0x4B400000, x1 = __float_as_int(fmaf(v.y, inv, 12582912.0f)) - 0x4B400000,
+                  x2 = __float_as_int(fmaf(v.z, inv, 12582912.0f)) - 0x4B400000, x3 = __float_as_int(fmaf(v.w, inv, 12582912.0f)) - 0x4B400000;
+        const int h0 = (x0 + 128) >> 8, h1 = (x1 + 128) >> 8, h2 = (x2 + 128) >> 8, h3 = (x3 + 128) >> 8;
+        const uint32_t hp = __byte_perm(__byte_perm((uint32_t) h0, (uint32_t) h1, 0x0040), __byte_perm((uint32_t) h2, (uint32_t) h3, 0x0040), 0x5410);
+        const uint32_t lp = __byte_perm(__byte_perm((uint32_t) x0, (uint32_t) x1, 0x0040), __byte_perm((uint32_t) x2, (uint32_t) x3, 0x0040), 0x5410);
+        // per pair [plane][t][low sub-block b0, b1, high sub-block b0, b1]
+        const size_t word = ((size_t) m * pairs + (sb >> 1)) * 32 + (q & 3) * 4 + (sb & 1) * 2 + (q >> 2);
+        img[word] = hp;
+        img[word + 16] = lp;
+        if (q == 0) xs2[(size_t) m * pairs * 2 + sb] = make_float2(some ? amax * (1.0f / 32512.0f) : 0.0f, sum);
+    }
+}
+
+template <int MG>
+__global__ void __launch_bounds__(IQ_THREADS, 1) matvec_q4k_imma_cols(IqArgs p, int m_tokens, const uint32_t * img) {
+    constexpr int MT = 4 * MG;                          // token slots
+    constexpr uint32_t SLOT_BYTES = 4 * 512;            // weight tiles of one block
+    constexpr uint32_t HDR_BYTES = 256;                 // its 16 block headers
+    extern __shared__ __align__(128) uint8_t smem[];
+    const int R = p.ring;
+    const uint32_t xq_bytes = (uint32_t) MT * p.pairs * 128;
+    uint32_t * xq = reinterpret_cast<uint32_t *>(smem);
+    float2 * xs2 = reinterpret_cast<float2 *>(smem + xq_bytes);
+    float * red = reinterpret_cast<float *>(smem + xq_bytes + (uint32_t) MT * p.pairs * 16);   // [warp][16 rows][8 tokens]
+    float2 * scs = reinterpret_cast<float2 *>(red + IQ_WARPS * IQ_GROUPS * 128);               // [warp][16 rows][8 sub-blocks] (d sc, dmin m)
+    uint64_t * bars = reinterpret_cast<uint64_t *>(scs + IQ_WARPS * IQ_GROUPS * 128);   // [warp][R], then one for the activation image
+    uint8_t * hdr = reinterpret_cast<uint8_t *>(bars + IQ_WARPS * IQ_GROUPS * R + 1);
+    hdr += (128 - (iq_smem_addr(hdr) & 127)) & 127;
+    uint8_t * ring = hdr + (uint32_t) IQ_WARPS * IQ_GROUPS * R * HDR_BYTES;
+    const uint32_t img_bar = iq_smem_addr(bars + IQ_WARPS * IQ_GROUPS * R);
+
+    const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
+    const int group = wid / IQ_WARPS, warp = wid % IQ_WARPS;
+    const int g = lane >> 2, t = lane & 3;
+    const int rt_step = gridDim.x * IQ_GROUPS;
+    const uint32_t bar0 = iq_smem_addr(bars + wid * R);
+    const uint32_t hdr0 = iq_smem_addr(hdr) + (uint32_t) wid * R * HDR_BYTES;
+    const uint32_t ring0 = iq_smem_addr(ring) + (uint32_t) wid * R * SLOT_BYTES;
+
+    if (lane == 0) {
+        for (int s = 0; s < R; ++s) iq_bar_init(bar0 + 8 * s, 33);   // lane 0's expect_tx + 32 header arrivals
+        if (tid == 0) iq_bar_init(img_bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();   // the image barrier is polled by every thread
+
+    const uint32_t rt_tile_bytes = (uint32_t) p.pairs * 512u, rt_hdr_bytes = (uint32_t) p.blocks * 256u;
+    const uint32_t lane_hdr_off = (uint32_t) (lane & 15) * (uint32_t) p.blocks * 16u;
+    auto request = [&](int rt, int blk, int s) {
+        const uint32_t bar = bar0 + 8 * s;
+        if (lane == 0) {
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            iq_bar_expect_tx(bar, SLOT_BYTES);
+            iq_bulk_g2s(ring0 + s * SLOT_BYTES, p.w[0] + (uint64_t) rt * rt_tile_bytes + (uint32_t) blk * SLOT_BYTES, SLOT_BYTES, bar);
+        }
+        if (lane < 16) iq_cp_async16(hdr0 + s * HDR_BYTES + lane * 16, p.w[0] + p.h_off[0] + (uint64_t) rt * rt_hdr_bytes + lane_hdr_off + (uint32_t) blk * 16u);
+        iq_cp_async_arrive(bar);
+    };
+    int irt = blockIdx.x * IQ_GROUPS + group, iblk = warp, islot = 0;
+    for (int i = 0; i < R; ++i) {
+        if (irt < p.n_tiles && iblk < p.blocks) {
+            request(irt, iblk, islot);
+            if (++islot == R) islot = 0;
+            iblk += IQ_WARPS;
+            if (iblk >= p.blocks) { iblk = warp; irt += rt_step; }
+        }
+    }
+
+    pdl_wait();
+
+    // the quantized activation columns (made by q4k_quantize_cols, the predecessor on the stream): one bulk copy
+    if (tid == 0) {
+        const uint32_t bytes = xq_bytes + (uint32_t) MT * p.pairs * 16;
+        iq_bar_expect_tx(img_bar, bytes);
+        iq_bulk_g2s(iq_smem_addr(xq), img, bytes, img_bar);
+    }
+    {
+        bool ok = iq_bar_try_wait(img_bar, 0u);
+        for (uint32_t i = 0; !ok && i < IQ_WAIT_LIMIT; ++i) ok = iq_bar_try_wait(img_bar, 0u);
+        if (!ok) atomicExch(&g_iq_fault, 2);
+    }
+    pdl_launch_dependents();
+
+    // lane (g, t) supplies B column g = plane (g & 1) of token (g >> 1) of each column group, and owns token t
+    const uint32_t xq0 = iq_smem_addr(xq);
+    const uint32_t xs0 = iq_smem_addr(xs2);
+    float2 * my_sc = scs + wid * 128;
+    float * my_red = red + group * (IQ_WARPS * 128);
+    const int gtid = tid - group * (IQ_WARPS * 32);
+
+    int rt = blockIdx.x * IQ_GROUPS + group, blk = warp, cslot = 0;
+    uint32_t cphase = 0;
+    bool alive = true;
+    for (int round = blockIdx.x * IQ_GROUPS; round < p.n_tiles; round += rt_step) {
+        float acc0[MG], acc1[MG];   // rows g and g + 8, token t of each column group
+#pragma unroll
+        for (int cg = 0; cg < MG; ++cg) acc0[cg] = acc1[cg] = 0.f;
+        for (; alive && rt < p.n_tiles && blk < p.blocks; blk += IQ_WARPS) {
+            {
+                const uint32_t bar = bar0 + 8 * cslot;
+                bool ok = iq_bar_try_wait(bar, cphase);
+                for (uint32_t i = 0; !ok && i < IQ_WAIT_LIMIT; ++i) ok = iq_bar_try_wait(bar, cphase);
+                if (!__all_sync(0xffffffffu, ok)) {
+                    if (lane == 0) atomicExch(&g_iq_fault, 1);
+                    alive = false;
+                    break;
+                }
+            }
+            // decode the block's 16 headers for the warp: lane -> (row lane & 15, sub-blocks 4 (lane >> 4) .. + 3)
+            {
+                const uint4 h = iq_lds128(hdr0 + cslot * HDR_BYTES + (lane & 15) * 16);
+                const float2 df = __half22float2(*reinterpret_cast<const __half2 *>(&h.x));
+                const uint32_t f0 = lane < 16 ? h.y : __funnelshift_r(h.z, h.w, 16);            // field 0 or 2
+                const uint32_t f1 = lane < 16 ? __funnelshift_r(h.y, h.z, 24) : h.w >> 8;         // field 1 or 3
+                float2 * dst = my_sc + (lane & 15) * 8 + (lane >> 4) * 4;
+                dst[0] = make_float2(df.x * (float) (f0 & 63u), df.y * (float) ((f0 >> 6) & 63u));
+                dst[1] = make_float2(df.x * (float) ((f0 >> 12) & 63u), df.y * (float) ((f0 >> 18) & 63u));
+                dst[2] = make_float2(df.x * (float) (f1 & 63u), df.y * (float) ((f1 >> 6) & 63u));
+                dst[3] = make_float2(df.x * (float) ((f1 >> 12) & 63u), df.y * (float) ((f1 >> 18) & 63u));
+            }
+            __syncwarp();
+            const uint32_t tiles_lane = ring0 + cslot * SLOT_BYTES + lane * 16;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const uint4 wt = iq_lds128(tiles_lane + j * 512);   // x, y: row g k-halves 0, 1; z, w: row g + 8
+                const float2 s_lo0 = my_sc[g * 8 + 2 * j], s_hi0 = my_sc[g * 8 + 2 * j + 1];             // row g: (d sc, dmin m)
+                const float2 s_lo1 = my_sc[(g + 8) * 8 + 2 * j], s_hi1 = my_sc[(g + 8) * 8 + 2 * j + 1];   // row g + 8
+#pragma unroll
+                for (int cg = 0; cg < MG; ++cg) {
+                    const uint32_t tok_b = (uint32_t) (cg * 4 + (g >> 1)), tok_c = (uint32_t) (cg * 4 + t);
+                    const uint4 bf = iq_lds128(xq0 + (tok_b * p.pairs + (uint32_t) (blk * 4 + j)) * 128u + (uint32_t) (g & 1) * 64u + (uint32_t) t * 16u);
+                    int clo[4], chi[4];
+                    imma_16832_zero(clo, wt.x & 0x0F0F0F0Fu, wt.z & 0x0F0F0F0Fu, wt.y & 0x0F0F0F0Fu, wt.w & 0x0F0F0F0Fu, bf.x, bf.y);
+                    imma_16832_zero(chi, wt.x & 0xF0F0F0F0u, wt.z & 0xF0F0F0F0u, wt.y & 0xF0F0F0F0u, wt.w & 0xF0F0F0F0u, bf.z, bf.w);
+                    // (s, sum x) of the pair's two sub-blocks for the token this lane owns
+                    const uint4 sqb = iq_lds128(xs0 + (tok_c * p.pairs + (uint32_t) (blk * 4 + j)) * 16u);
+                    const float s_l = __uint_as_float(sqb.x), x_l = __uint_as_float(sqb.y), s_h = __uint_as_float(sqb.z), x_h = __uint_as_float(sqb.w);
+                    const float vl0 = (float) (clo[0] * 256 + clo[1]), vl1 = (float) (clo[2] * 256 + clo[3]);
+                    const float vh0 = (float) ((chi[0] * 256 + chi[1]) >> 4), vh1 = (float) ((chi[2] * 256 + chi[3]) >> 4);
+                    acc0[cg] += (s_lo0.x * s_l) * vl0 - s_lo0.y * x_l + (s_hi0.x * s_h) * vh0 - s_hi0.y * x_h;
+                    acc1[cg] += (s_lo1.x * s_l) * vl1 - s_lo1.y * x_l + (s_hi1.x * s_h) * vh1 - s_hi1.y * x_h;
+                }
+            }
+            __syncwarp();
+            if (irt < p.n_tiles && iblk < p.blocks) {
+                request(irt, iblk, cslot);
+                iblk += IQ_WARPS;
+                if (iblk >= p.blocks) { iblk = warp; irt += rt_step; }
+            }
+            if (++cslot == R) { cslot = 0; cphase ^= 1u; }
+        }
+#pragma unroll
+        for (int cg = 0; cg < MG; ++cg) {
+            my_red[(warp * 16 + g) * 8 + cg * 4 + t] = acc0[cg];
+            my_red[(warp * 16 + g + 8) * 8 + cg * 4 + t] = acc1[cg];
+        }
+        __syncthreads();
+        if (gtid < 128 && rt < p.n_tiles) {
+            const int row = gtid >> 3, col = gtid & 7;
+            if (col < m_tokens && col < MT) {
+                float v = 0.f;
+#pragma unroll
+                for (int w = 0; w < IQ_WARPS; ++w) v += my_red[(w * 16 + row) * 8 + col];
+                p.y[0][(int64_t) col * p.ldy[0] + (int64_t) rt * 16 + row] = v;
+            }
+        }
+        __syncthreads();
+        rt += rt_step;
+        blk = warp;
+    }
+    if (!alive) {
+        for (int s = 0; s < R; ++s)
+            for (uint32_t i = 0; i < IQ_WAIT_LIMIT && !iq_bar_try_wait(bar0 + 8 * s, cphase); ++i) {}
+    }
+}
+
+size_t iq_cols_smem_bytes(int pairs, int mt, int ring) {
+    return (size_t) mt * pairs * (128 + 16) + (size_t) IQ_WARPS * IQ_GROUPS * 128 * 4 + (size_t) IQ_WARPS * IQ_GROUPS * 128 * 8 +
+           (size_t) IQ_WARPS * IQ_GROUPS * ring * 8 + 8 + 128 + (size_t) IQ_WARPS * IQ_GROUPS * ring * (256 + 2048);
+}
+
 size_t iq_smem_bytes(int pairs, int m, int ring, int nb) {
     return (size_t) m * pairs * (128 + 16) + 16 + (size_t) IQ_WARPS * IQ_GROUPS * 64 * 4 + (size_t) IQ_WARPS * IQ_GROUPS * ring * 8 + 128 +
            (size_t) IQ_WARPS * IQ_GROUPS * ring * nb * (256 + 2048);
@@ -639,6 +851,56 @@ int matvec_q4k_imma_multi(cudaStream_t s, int count, const void * const * ws, co
     int st;
     if (nb == 1) st = m == 1 ? launch_iq<1, 1>(s, a, smem, (int) grid) : launch_iq<2, 1>(s, a, smem, (int) grid);
     else st = m == 1 ? launch_iq<1, 2>(s, a, smem, (int) grid) : launch_iq<2, 2>(s, a, smem, (int) grid);
+    *handled = st == ST_OK;
+    return st;
+}
+
+// 3..8 activation columns of one packed Q4_K tensor over its full 16-row tiles; *handled = false when the shape
+// (or the shared memory the quantized columns need) is left to the caller's other kernels.
+int matvec_q4k_imma_cols_tiles(cudaStream_t s, const void * w, int64_t k, int64_t n, const float * x, int64_t ldx, int64_t m, float * y, int64_t ldy,
+                               bool * handled) {
+    *handled = false;
+    const int64_t tiles = n / 16;
+    if (tiles == 0 || m < 3 || m > 8 || k % 256 != 0 || k / 64 > 4096 || tiles > INT32_MAX / 2) return ST_OK;
+    if (((uintptr_t) w & 15) != 0 || ((uintptr_t) x & 15) != 0 || (ldx & 3) != 0) return ST_OK;
+    const int pairs = (int) (k / 64);
+    const int mg = m > 4 ? 2 : 1;
+    int ring = 4;
+    while (ring >= 2 && iq_cols_smem_bytes(pairs, 4 * mg, ring) > (size_t) 227 * 1024) --ring;
+    if (ring < 2) return ST_OK;
+    const size_t smem = iq_cols_smem_bytes(pairs, 4 * mg, ring);
+    IqArgs a = {};
+    a.w[0] = (const uint8_t *) w;
+    a.h_off[0] = n * (k / 256) * 128;
+    a.y[0] = y;
+    a.ldy[0] = ldy;
+    a.tile_end[0] = (int) tiles;
+    a.tile_end[1] = a.tile_end[2] = INT32_MAX;
+    a.x = x;
+    a.ldx = ldx;
+    a.n_tiles = (int) tiles;
+    a.pairs = pairs;
+    a.blocks = (int) (k / 256);
+    a.chunks = a.blocks;
+    a.ring = ring;
+    int64_t grid = sm_count();
+    const int64_t rounds = (tiles + IQ_GROUPS - 1) / IQ_GROUPS;
+    if (grid > rounds) grid = rounds;
+    g_iq_launched.store(true, std::memory_order_relaxed);
+    const int mt = 4 * mg;
+    void * img = nullptr;
+    int st = device_scratch(2, (size_t) mt * pairs * 144, &img);
+    if (st != ST_OK) return st;
+    const int q_items = mt * pairs * 16;
+    st = launch(q4k_quantize_cols, dim3((unsigned) ((q_items + 255) / 256)), dim3(256), 0, s, x, ldx, (int) m, mt, pairs, (uint32_t *) img);
+    if (st != ST_OK) return st;
+    if (mg == 1) {
+        SM100_CUDA(cudaFuncSetAttribute(matvec_q4k_imma_cols<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+        st = launch(matvec_q4k_imma_cols<1>, dim3((unsigned) grid), dim3(IQ_THREADS), smem, s, a, (int) m, (const uint32_t *) img);
+    } else {
+        SM100_CUDA(cudaFuncSetAttribute(matvec_q4k_imma_cols<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+        st = launch(matvec_q4k_imma_cols<2>, dim3((unsigned) grid), dim3(IQ_THREADS), smem, s, a, (int) m, (const uint32_t *) img);
+    }
     *handled = st == ST_OK;
     return st;
 }

@@ -48,11 +48,11 @@ int sm_count() {
 }
 
 // Per-device scratch owned by the library, one buffer per slot (0 = attention partials, 1 = GEMM
-// activations), grown on demand and never shrunk.  Calls that use the same slot must be ordered on one
+// activations, 2 = quantized activation columns of the multi-column matvec), grown on demand and never shrunk.  Calls that use the same slot must be ordered on one
 // stream; growing frees the old buffer, which waits for the device to go idle.
 int device_scratch(int slot, size_t bytes, void ** out) {
-    constexpr int SLOTS = 2;
-    struct Entry { void * ptr[SLOTS] = {nullptr, nullptr}; size_t size[SLOTS] = {0, 0}; };
+    constexpr int SLOTS = 3;
+    struct Entry { void * ptr[SLOTS] = {nullptr, nullptr, nullptr}; size_t size[SLOTS] = {0, 0, 0}; };
     static std::mutex mu;
     static std::vector<Entry> table;
     if (slot < 0 || slot >= SLOTS) return fail(ST_INVALID, "device_scratch: bad slot");
@@ -66,7 +66,13 @@ int device_scratch(int slot, size_t bytes, void ** out) {
         e.ptr[slot] = nullptr;
         e.size[slot] = 0;
         const size_t want = bytes < (size_t) (8u << 20) ? (size_t) (8u << 20) : bytes;
-        SM100_CUDA(cudaMalloc(&e.ptr[slot], want));
+        const cudaError_t me = cudaMalloc(&e.ptr[slot], want);
+        if (me == cudaErrorStreamCaptureUnsupported || me == cudaErrorStreamCaptureInvalidated) {
+            (void) cudaGetLastError();
+            return fail(ST_BACKEND, "the library's scratch buffer for this op does not exist yet (or is too small) and cannot be allocated while a "
+                                    "stream is capturing: issue the same call once outside the capture first");
+        }
+        if (me != cudaSuccess) return cuda_fail(me, "cudaMalloc(scratch)");
         SM100_CUDA(cudaMemset(e.ptr[slot], 0, want));   // the attention kernels keep counters in it that start at zero
         e.size[slot] = want;
     }
