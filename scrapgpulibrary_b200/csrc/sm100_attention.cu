@@ -32,8 +32,12 @@ struct AttnArgs {
 };
 
 // scratch layout per (q, h, split): [m, l, o[dv]]
+// A split's partial of one (query, head) is [m, l, unused, unused, o[dv]]: the accumulator starts 16 bytes in, so
+// that it can be moved as float4 when dv is a multiple of 4.
+constexpr int ATT_HDR = 4;
+
 __device__ __forceinline__ int64_t scratch_index(const AttnArgs & a, int64_t q, int64_t h, int split) {
-    return ((q * a.hq + h) * a.splits + split) * (a.dv + 2);
+    return ((q * a.hq + h) * a.splits + split) * (a.dv + ATT_HDR);
 }
 
 __device__ __forceinline__ int64_t visible_keys(const AttnArgs & a, int64_t q) {
@@ -144,10 +148,10 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_partial_kernel(AttnArgs a) {
                 for (int g = 0; g < group; ++g) sred[g * a.dv + dvi] = o[g];
             __syncthreads();
             if (active && half == 0)
-                for (int g = 0; g < group; ++g) a.scratch[scratch_index(a, q, hk * group + g, split) + 2 + dvi] = o[g] + sred[g * a.dv + dvi];
+                for (int g = 0; g < group; ++g) a.scratch[scratch_index(a, q, hk * group + g, split) + ATT_HDR + dvi] = o[g] + sred[g * a.dv + dvi];
             __syncthreads();
         } else if (active) {
-            for (int g = 0; g < group; ++g) a.scratch[scratch_index(a, q, hk * group + g, split) + 2 + dvi] = o[g];
+            for (int g = 0; g < group; ++g) a.scratch[scratch_index(a, q, hk * group + g, split) + ATT_HDR + dvi] = o[g];
         }
     }
 }
@@ -160,7 +164,7 @@ constexpr int ATT_MAX_SPLITS = 1024;
 
 __device__ __forceinline__ void attn_merge_head(const AttnArgs & a, int64_t q, int64_t h, float * s_w, float (*s_red)[32]) {
     const float * base = a.scratch + scratch_index(a, q, h, 0);
-    const int64_t stride = a.dv + 2;
+    const int64_t stride = a.dv + ATT_HDR;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
     __syncthreads();   // s_w / s_red may still be read from a previous head
     float m = -INFINITY;
@@ -193,7 +197,7 @@ __device__ __forceinline__ void attn_merge_head(const AttnArgs & a, int64_t q, i
         if (m != -INFINITY) {
             // unconditional loads (every split wrote its accumulator, zeros if it had no key): they pipeline
 #pragma unroll 8
-            for (int s = 0; s < a.splits; ++s) o = fmaf(__ldcg(base + s * stride + 2 + dvi), s_w[s], o);
+            for (int s = 0; s < a.splits; ++s) o = fmaf(__ldcg(base + s * stride + ATT_HDR + dvi), s_w[s], o);
             o = o / l;
         }
         a.out[(h * a.nq + q) * a.dv + dvi] = o;
@@ -201,46 +205,99 @@ __device__ __forceinline__ void attn_merge_head(const AttnArgs & a, int64_t q, i
 }
 
 // The same merge for the G heads of a KV group at once, by the CTA that delivered the group's last partial
-// (splits <= ATT_FUSED_SPLITS): warp g reduces head g's (m, l) over the splits, then the threads cover (head, dv).
+// (splits <= ATT_FUSED_SPLITS, dv = 128 D4).  It is one round trip to L2 deep: every thread first requests its
+// share of the accumulators (a float4 column of one head, a 1/P share of the splits, up to ATT_MERGE_BATCH loads in
+// flight), then warp g turns head g's (m, l) pairs - one float2 load per split - into the weights exp(m_s - m) in
+// shared memory, and only then are the requested accumulators weighted and summed.
 constexpr int ATT_FUSED_SPLITS = 128;
+constexpr int ATT_MERGE_BATCH = 20;
 
-template <int G>
-__device__ __forceinline__ void attn_merge_group(const AttnArgs & a, int64_t q, int64_t hk, float * s_w, float * s_l) {
+template <int G, int D4>
+__device__ __forceinline__ void attn_merge_group(const AttnArgs & a, int64_t q, int64_t hk, float * s_w, float * s_l, float4 * s_part) {
+    constexpr int COLS = 32 * D4;                      // float4 columns per head
+    constexpr int ITEMS = G * COLS;
+    constexpr int P = ITEMS >= ATT_THREADS ? 1 : ATT_THREADS / ITEMS;   // threads per column, each with a share of the splits
+    constexpr int ROUNDS = (ITEMS + ATT_THREADS - 1) / ATT_THREADS;
+    constexpr int ACTIVE = ITEMS < ATT_THREADS ? ITEMS : ATT_THREADS;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int64_t stride = a.dv + 2;
+    const int64_t stride = a.dv + ATT_HDR;
+    const int64_t st4 = stride / 4;
+    const float * gbase = a.scratch + scratch_index(a, q, hk * G, 0);   // head g of the group: + g * splits * stride
+    const int item = tid % ACTIVE, part = tid / ACTIVE;
+    const int per = (a.splits + P - 1) / P;
+    const int s_begin = part * per;
+    const int s_end = s_begin + per < a.splits ? s_begin + per : a.splits;
+    const float4 * col0 = reinterpret_cast<const float4 *>(gbase + (int64_t) (item / COLS) * a.splits * stride + ATT_HDR) + item % COLS;
+    float4 pre[ATT_MERGE_BATCH];
+#pragma unroll
+    for (int i = 0; i < ATT_MERGE_BATCH; ++i)
+        pre[i] = s_begin + i < s_end ? __ldcg(col0 + (int64_t) (s_begin + i) * st4) : make_float4(0.f, 0.f, 0.f, 0.f);
+
     if (warp < G) {
-        const float * base = a.scratch + scratch_index(a, q, hk * G + warp, 0);
+        const float * base = gbase + (int64_t) warp * a.splits * stride;
+        float2 ml[ATT_FUSED_SPLITS / 32];
         float m = -INFINITY;
-        for (int s = lane; s < a.splits; s += 32) {
-            const float ms = __ldcg(base + s * stride);
-            s_w[warp * ATT_FUSED_SPLITS + s] = ms;
-            m = fmaxf(m, ms);
+#pragma unroll
+        for (int i = 0; i < ATT_FUSED_SPLITS / 32; ++i) {
+            const int sp = lane + 32 * i;
+            ml[i] = sp < a.splits ? __ldcg(reinterpret_cast<const float2 *>(base + (int64_t) sp * stride)) : make_float2(-INFINITY, 0.f);
+            m = fmaxf(m, ml[i].x);
         }
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+        for (int off = 16; off > 0; off >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, off));
         float l = 0.f;
-        for (int s = lane; s < a.splits; s += 32) {
-            const float ms = s_w[warp * ATT_FUSED_SPLITS + s];
-            const float e = ms != -INFINITY ? expf(ms - m) : 0.f;
-            s_w[warp * ATT_FUSED_SPLITS + s] = e;
-            l = fmaf(__ldcg(base + s * stride + 1), e, l);
+#pragma unroll
+        for (int i = 0; i < ATT_FUSED_SPLITS / 32; ++i) {
+            const int sp = lane + 32 * i;
+            const float e = ml[i].x != -INFINITY ? expf(ml[i].x - m) : 0.f;
+            if (sp < a.splits) s_w[warp * ATT_FUSED_SPLITS + sp] = e;
+            l = fmaf(ml[i].y, e, l);
         }
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) l += __shfl_xor_sync(0xffffffffu, l, o);
+        for (int off = 16; off > 0; off >>= 1) l += __shfl_xor_sync(0xffffffffu, l, off);
         if (lane == 0) s_l[warp] = m == -INFINITY ? 0.f : l;   // 0: no visible key at all
     }
     __syncthreads();
-    for (int item = tid; item < G * (int) a.dv; item += blockDim.x) {
-        const int g = item / (int) a.dv, dvi = item - g * (int) a.dv;
-        const float * base = a.scratch + scratch_index(a, q, hk * G + g, 0) + 2 + dvi;
-        const float l = s_l[g];
-        float o = 0.f;
-        if (l != 0.f) {
-#pragma unroll 8
-            for (int s = 0; s < a.splits; ++s) o = fmaf(__ldcg(base + s * stride), s_w[g * ATT_FUSED_SPLITS + s], o);
-            o = o / l;
+#pragma unroll
+    for (int r = 0; r < ROUNDS; ++r) {
+        const int it = item + r * ATT_THREADS;     // ROUNDS > 1 only with P == 1
+        const int g = it / COLS, c = it % COLS;
+        const float * w = s_w + g * ATT_FUSED_SPLITS;
+        const float4 * col = reinterpret_cast<const float4 *>(gbase + (int64_t) g * a.splits * stride + ATT_HDR) + c;
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        int sp = s_begin;
+        if (r == 0) {
+#pragma unroll
+            for (int i = 0; i < ATT_MERGE_BATCH; ++i) {
+                const float ws = s_begin + i < s_end ? w[s_begin + i] : 0.f;
+                acc.x = fmaf(pre[i].x, ws, acc.x); acc.y = fmaf(pre[i].y, ws, acc.y);
+                acc.z = fmaf(pre[i].z, ws, acc.z); acc.w = fmaf(pre[i].w, ws, acc.w);
+            }
+            sp = s_begin + ATT_MERGE_BATCH;
         }
-        a.out[((hk * G + g) * a.nq + q) * a.dv + dvi] = o;
+#pragma unroll 8
+        for (; sp < s_end; ++sp) {
+            const float4 v = __ldcg(col + (int64_t) sp * st4);
+            const float ws = w[sp];
+            acc.x = fmaf(v.x, ws, acc.x); acc.y = fmaf(v.y, ws, acc.y);
+            acc.z = fmaf(v.z, ws, acc.z); acc.w = fmaf(v.w, ws, acc.w);
+        }
+        if (P > 1) {
+            if (part > 0) s_part[(part - 1) * ITEMS + item] = acc;
+            __syncthreads();
+            if (part == 0) {
+#pragma unroll
+                for (int pp = 1; pp < P; ++pp) {
+                    const float4 v = s_part[(pp - 1) * ITEMS + item];
+                    acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+                }
+            }
+        }
+        if (part == 0) {
+            const float l = s_l[g];
+            reinterpret_cast<float4 *>(a.out + ((hk * G + g) * a.nq + q) * a.dv)[c] =
+                l != 0.f ? make_float4(acc.x / l, acc.y / l, acc.z / l, acc.w / l) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
     }
 }
 
@@ -259,12 +316,25 @@ __global__ void attn_combine_kernel(AttnArgs a) {
 // the three phases of the generic kernel.  The 8 warps are merged through shared memory into the split's partial;
 // the CTA that delivers the last partial of a (query, KV head) merges the splits right away (counter in global
 // memory, reset for the next call), so no second launch is needed.
+#ifdef SM100_ATTN_TIMING
+__device__ unsigned long long g_att_t[8];   // development builds: cycles per phase summed over CTAs; [6] CTAs, [7] merging CTAs
+#define ATT_T(i) if (threadIdx.x == 0) { const long long now_ = clock64(); atomicAdd(&g_att_t[i], (unsigned long long) (now_ - t_prev_)); t_prev_ = now_; }
+#else
+#define ATT_T(i)
+#endif
+
 template <int G, int D4>
 __global__ void __launch_bounds__(ATT_THREADS) attn_fast_kernel(AttnArgs a) {
+#ifdef SM100_ATTN_TIMING
+    long long t_prev_ = clock64();
+    if (threadIdx.x == 0) atomicAdd(&g_att_t[6], 1ull);
+#endif
     pdl_wait();
     pdl_launch_dependents();
+    ATT_T(0)
     constexpr int D = 128 * D4;
-    extern __shared__ float smem[];   // [8 warps][G][D + 2]
+    extern __shared__ __align__(16) float smem[];   // [8 warps][G][ATT_HDR + D]
+    constexpr int SROW = ATT_HDR + D;
     __shared__ float s_w[ATT_MAX_SPLITS];
     __shared__ float s_red[2][32];
     __shared__ int s_last;
@@ -302,7 +372,7 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_fast_kernel(AttnArgs a) {
     // shuffles instead of 5 NV) and handed to all lanes through the warp's own shared-memory slot.
     constexpr int NKB = D4 == 1 ? 4 : 2;
     constexpr int NV = G * NKB;
-    float * my_scores = smem + warp * G * (D + 2);   // first NV floats of the area this warp fills after the loop
+    float * my_scores = smem + warp * G * SROW;   // first NV floats of the area this warp fills after the loop
     for (int kb = warp * NKB; kb < count; kb += NW * NKB) {
         float4 kv[NKB][D4], vv[NKB][D4];
 #pragma unroll
@@ -388,52 +458,82 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_fast_kernel(AttnArgs a) {
         }
     }
     __syncwarp();
-    // warps -> shared memory
+    ATT_T(1)
+    // warps -> shared memory: per (warp, head) [m, l, -, -, o[D]]
 #pragma unroll
     for (int g = 0; g < G; ++g) {
-        float * dst = smem + (warp * G + g) * (D + 2);
+        float * dst = smem + (warp * G + g) * SROW;
         if (lane == 0) {
             dst[0] = m[g];
             dst[1] = l[g];
         }
 #pragma unroll
-        for (int i = 0; i < D4; ++i) {
-            const int e = (lane + 32 * i) * 4;
-            dst[2 + e] = o[g][i].x; dst[3 + e] = o[g][i].y; dst[4 + e] = o[g][i].z; dst[5 + e] = o[g][i].w;
-        }
+        for (int i = 0; i < D4; ++i) reinterpret_cast<float4 *>(dst + ATT_HDR)[lane + 32 * i] = o[g][i];
     }
     __syncthreads();
-    // merge the warps into the split's partial [m, l, o[D]] per head
-    for (int item = tid; item < G * D; item += ATT_THREADS) {
-        const int g = item / D, e = item - g * D;
+    // weight of each warp's partial within the split, exp(m_w - max_w m_w), computed once per (head, warp)
+    float * s_f = s_w;
+    if (tid < G * NW) {
+        const int g = tid / NW, w = tid % NW;
         float mm = -INFINITY;
 #pragma unroll
-        for (int w = 0; w < NW; ++w) mm = fmaxf(mm, smem[(w * G + g) * (D + 2)]);
-        float ll = 0.f, oo = 0.f;
+        for (int w2 = 0; w2 < NW; ++w2) mm = fmaxf(mm, smem[(w2 * G + g) * SROW]);
+        const float mw = smem[(w * G + g) * SROW];
+        s_f[tid] = mw == -INFINITY ? 0.f : expf(mw - mm);
+    }
+    __syncthreads();
+    // merge the warps into the split's partial per head, a float4 column per thread
+    for (int item = tid; item < G * (D / 4); item += ATT_THREADS) {
+        const int g = item / (D / 4), c = item - g * (D / 4);
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
         for (int w = 0; w < NW; ++w) {
-            const float * src = smem + (w * G + g) * (D + 2);
-            const float f = src[0] == -INFINITY ? 0.f : expf(src[0] - mm);
-            ll = fmaf(src[1], f, ll);
-            oo = fmaf(src[2 + e], f, oo);
+            const float f = s_f[g * NW + w];
+            const float4 v = reinterpret_cast<const float4 *>(smem + (w * G + g) * SROW + ATT_HDR)[c];
+            acc.x = fmaf(v.x, f, acc.x); acc.y = fmaf(v.y, f, acc.y);
+            acc.z = fmaf(v.z, f, acc.z); acc.w = fmaf(v.w, f, acc.w);
         }
         float * dst = a.scratch + scratch_index(a, q, hk * G + g, split);
-        if (e == 0) {
-            dst[0] = mm;
-            dst[1] = ll;
+        if (c == 0) {
+            float mm = -INFINITY, ll = 0.f;
+#pragma unroll
+            for (int w = 0; w < NW; ++w) {
+                mm = fmaxf(mm, smem[(w * G + g) * SROW]);
+                ll = fmaf(smem[(w * G + g) * SROW + 1], s_f[g * NW + w], ll);
+            }
+            *reinterpret_cast<float2 *>(dst) = make_float2(mm, ll);
         }
-        dst[2 + e] = oo;
+        reinterpret_cast<float4 *>(dst + ATT_HDR)[c] = acc;
     }
     if (a.counters == nullptr) return;   // the caller merges with a second launch
-    __threadfence();
+    ATT_T(2)
+    // the CTA's partial is complete once all its threads passed the barrier; thread 0 publishes it (the fence is
+    // cumulative over what the barrier ordered before it) and takes a ticket
     __syncthreads();
-    if (tid == 0) s_last = atomicAdd(a.counters + q * a.hkv + hk, 1) == a.splits - 1 ? 1 : 0;
+    if (tid == 0) {
+        __threadfence();
+        const int last = atomicAdd(a.counters + q * a.hkv + hk, 1) == a.splits - 1 ? 1 : 0;
+        if (last) __threadfence();
+        s_last = last;
+    }
     __syncthreads();
+    ATT_T(3)
     if (s_last == 0) return;
-    __threadfence();
-    attn_merge_group<G>(a, q, hk, s_w, &s_red[0][0]);
+    attn_merge_group<G, D4>(a, q, hk, s_w, &s_red[0][0], reinterpret_cast<float4 *>(smem));
     if (tid == 0) a.counters[q * a.hkv + hk] = 0;
+    ATT_T(4)
+#ifdef SM100_ATTN_TIMING
+    if (threadIdx.x == 0) atomicAdd(&g_att_t[7], 1ull);
+#endif
 }
+
+#ifdef SM100_ATTN_TIMING
+extern "C" __attribute__((visibility("default"))) int sm100_debug_attn_timing(unsigned long long * out, int reset) {
+    if (cudaMemcpyFromSymbol(out, g_att_t, sizeof(unsigned long long) * 8) != cudaSuccess) return 4;
+    if (reset) { unsigned long long z[8] = {}; cudaMemcpyToSymbol(g_att_t, z, sizeof(z)); }
+    return 0;
+}
+#endif
 
 int device_scratch(int slot, size_t bytes, void ** out);
 
@@ -448,7 +548,7 @@ constexpr int ATT_COUNTER_SLOTS = 16384;   // ints at the start of the scratch: 
 
 template <int G, int D4>
 static int launch_fast(cudaStream_t s, const AttnArgs & a) {
-    const size_t smem = (size_t) (ATT_THREADS / 32) * G * (128 * D4 + 2) * sizeof(float);
+    const size_t smem = (size_t) (ATT_THREADS / 32) * G * (128 * D4 + ATT_HDR) * sizeof(float);
     if (smem > 48 * 1024) SM100_CUDA(cudaFuncSetAttribute(attn_fast_kernel<G, D4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024));
     return launch(attn_fast_kernel<G, D4>, dim3((unsigned) a.splits, (unsigned) a.hkv, (unsigned) a.nq), dim3(ATT_THREADS), smem, s, a);
 }
@@ -459,7 +559,7 @@ int attention_launch(cudaStream_t s, AttnArgs a, float * scratch) {
     a.counters = nullptr;
     a.scratch = scratch + ATT_COUNTER_SLOTS;
     static const int use_fast = [] { const char * e = getenv("SM100_ATTN_FAST"); return e != nullptr ? atoi(e) : 1; }();
-    const bool aligned = (((uintptr_t) a.q | (uintptr_t) a.k | (uintptr_t) a.v) & 15) == 0;
+    const bool aligned = (((uintptr_t) a.q | (uintptr_t) a.k | (uintptr_t) a.v | (uintptr_t) a.out | (uintptr_t) scratch) & 15) == 0;
     if (use_fast && a.d == a.dv && (a.d == 128 || a.d == 256) && aligned && (group == 1 || group == 2 || group == 4 || group == 8)) {
         const bool fused = a.nq * a.hkv <= ATT_COUNTER_SLOTS && a.splits <= ATT_FUSED_SPLITS;
         if (fused) a.counters = reinterpret_cast<int *>(scratch);
@@ -500,7 +600,7 @@ int attention_check(const AttnArgs & a) {
 }
 
 size_t attention_scratch_bytes(const AttnArgs & a) {
-    return ((size_t) ATT_COUNTER_SLOTS + (size_t) a.nq * a.hq * a.splits * (a.dv + 2)) * sizeof(float);
+    return ((size_t) ATT_COUNTER_SLOTS + (size_t) a.nq * a.hq * a.splits * (a.dv + ATT_HDR)) * sizeof(float);
 }
 
 void attention_plan(AttnArgs & a) {

@@ -44,13 +44,31 @@ constexpr int TM = 128;            // weight rows per CTA = rows of one tcgen05.
 // by the polling producers (each of its instructions took 50-80 cycles to issue).
 constexpr int WARP_MMA = 0;        // owns TMEM and issues the MMAs
 constexpr int WARP_BULK = 1;       // issues the bulk copies of the activation stages
-constexpr int FIRST_PRODUCER = 2;  // warps 2-17 dequantize, then run the epilogue
-constexpr int PRODUCER_WARPS = 16; // 512 threads = 512 (row, 32-weight block) tasks: one chunk of 128 K, or two of 64
+constexpr int FIRST_PRODUCER = 2;  // warps 2.. dequantize; the first 16 of them then run the epilogue
+// Producer warps: 8 warps = 256 (row, 32-weight block) tasks = one 64-wide chunk of the 128 rows, so 24 warps are three
+// groups that take the chunks in turn.  A producer's instruction stream is a dependent chain (~7 cycles per
+// instruction), so the third group buys throughput that the issue slots still have.
+constexpr int PRODUCER_WARPS = 24;
+constexpr int EPILOGUE_WARPS = 16;
 constexpr int GEMM_THREADS = 32 * (FIRST_PRODUCER + PRODUCER_WARPS);
 constexpr float W_PRESCALE = 256.0f;  // applied to quantized weights before they are rounded to f16
 constexpr uint32_t WAIT_LIMIT = 1u << 21;  // polls of one mbarrier wait before the CTA gives up (~1 s)
 
 __device__ int g_gemm_fault;  // 0, or 1 + the wait site that gave up
+#ifdef SM100_GEMM_TIMING
+// development builds only: cycle counters of CTA 0 (see sm100_debug_gemm_timing)
+__device__ unsigned long long g_gemm_timing[16];
+__device__ long long g_gemm_trace[6][64];   // CTA 0, chunk c < 64: [0] bulk saw empty, [1] producer saw empty, [2] producer arrived, [3] MMA saw full, [4] MMA committed, [5] kernel start
+#define GT_TRACE(i, c) do { if (blockIdx.x == 0 && lane == 0 && (c) < 64) g_gemm_trace[i][c] = clock64(); } while (0)
+#define GT_DECL(v) long long v = 0
+#define GT_NOW() clock64()
+#define GT_PUT(i, v) do { if (blockIdx.x == 0 && lane == 0) atomicAdd(&g_gemm_timing[i], (unsigned long long) (v)); } while (0)
+#else
+#define GT_DECL(v)
+#define GT_NOW() 0
+#define GT_PUT(i, v)
+#define GT_TRACE(i, c)
+#endif
 
 
 // ---------------------------------------------------------------------------------------------
@@ -120,20 +138,50 @@ __device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t cols) {
 __host__ __device__ constexpr uint32_t instr_desc_f16(int m, int n) {
     return (1u << 4) | ((uint32_t) (n >> 3) << 17) | ((uint32_t) (m >> 4) << 24);
 }
-// D[tmem] (+)= A . B^T; both descriptors share their high word (same 8-row-group stride and version)
+// D[tmem] (+)= A . B^T; both descriptors share their high word (same 8-row-group stride and version).
+// Executed by a whole (converged) warp: one elected lane issues.  Keeping the warp converged around the issue lets the
+// operands live in uniform registers - issued from inside a divergent `if (lane == 0)` each MMA cost ~86 cycles.
 __device__ __forceinline__ void mma_f16(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t desc_hi, uint32_t idesc, uint32_t accumulate) {
     asm volatile(
-        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+        "{\n\t.reg .pred p, e;\n\t.reg .b64 da, db;\n\t"
+        "elect.sync _|e, 0xffffffff;\n\t"
         "setp.ne.b32 p, %5, 0;\n\t"
         "mov.b64 da, {%1, %3};\n\t"
         "mov.b64 db, {%2, %3};\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p;\n\t}" ::"r"(d_tmem),
+        "@e tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p;\n\t}" ::"r"(d_tmem),
         "r"(a_lo), "r"(b_lo), "r"(desc_hi), "r"(idesc), "r"(accumulate)
         : "memory");
 }
-// arrives on `bar` when every MMA this thread issued so far has finished reading shared memory and writing TMEM
+// The same with the A operand in tensor memory: lane = row, 32-bit column j of the 8 columns at `a_tmem` = the row's
+// K elements 2j (low half) and 2j + 1.
+__device__ __forceinline__ void mma_f16_ta(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t desc_hi, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p, e;\n\t.reg .b64 db;\n\t"
+        "elect.sync _|e, 0xffffffff;\n\t"
+        "setp.ne.b32 p, %5, 0;\n\t"
+        "mov.b64 db, {%2, %3};\n\t"
+        "@e tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t}" ::"r"(d_tmem),
+        "r"(a_tmem), "r"(b_lo), "r"(desc_hi), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// 16 consecutive 32-bit columns of this thread's own TMEM lane (lane = base lane of the warp's quarter + lane id)
+__device__ __forceinline__ void tmem_st16(uint32_t addr, const uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};" ::"r"(addr),
+        "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]),
+        "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// arrives on `bar` when every MMA issued so far by the elected lane has finished reading shared memory and writing
+// TMEM (whole converged warp, like mma_f16: elect.sync picks the same lane)
 __device__ __forceinline__ void mma_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+    asm volatile(
+        "{\n\t.reg .pred e;\n\t"
+        "elect.sync _|e, 0xffffffff;\n\t"
+        "@e tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}" ::"r"(bar)
+        : "memory");
 }
 // 32 lanes x 16 consecutive f32 columns of the accumulator: thread i of the warp receives lane (base lane + i)
 __device__ __forceinline__ void tmem_ld16(uint32_t addr, uint32_t (&r)[16]) {
@@ -321,14 +369,20 @@ struct SrcTraits<SrcQ4K> {
 // ---------------------------------------------------------------------------------------------
 // Shared memory of one CTA
 // ---------------------------------------------------------------------------------------------
-template <int TN, int KC, int STAGES>
+template <int TN, int KC, int STAGES, int RT, bool ATM>
 struct GemmSmem {
-    static constexpr int A_BYTES = TM * KC * 2;
+    static constexpr int A_BYTES = TM * KC * 2;   // one row tile of a stage
     static constexpr int B_BYTES = TN * KC * 2;
-    uint8_t a[STAGES][A_BYTES];  // [k / 8][row][8 halves]
+    // Weight stages: in tensor memory (ATM) as many as the columns left by the accumulators hold, at most 8;
+    // in shared memory as many as activation stages.  The two rings have their own barriers: the activation copies
+    // are the long-latency side (~2 us under load) and want every byte of shared memory in flight.
+    static constexpr int SA = !ATM ? STAGES : (512 - RT * TN) / (RT * (KC / 2)) < 8 ? (512 - RT * TN) / (RT * (KC / 2)) : 8;
+    uint8_t a[SA][ATM ? 16 : RT * A_BYTES];  // [row tile][k / 8][row][8 halves]; unused when A lives in tensor memory
     uint8_t b[STAGES][B_BYTES];  // [k / 8][token][8 halves]
-    uint64_t full[STAGES];       // -> MMA: one arrival per producer warp of the stage's group, plus the bulk copy's bytes
-    uint64_t empty[STAGES];      // MMA commit -> producers and the bulk warp
+    uint64_t full_a[SA];         // producers -> MMA: one arrival per producer warp and row tile
+    uint64_t empty_a[SA];        // MMA commit -> producers
+    uint64_t full_b[STAGES];     // bulk copy -> MMA: the issuing lane's expect_tx arrival + the bytes
+    uint64_t empty_b[STAGES];    // MMA commit -> bulk warp
     uint64_t accum;              // last commit -> epilogue
     uint32_t tmem_base;
     int abort_flag;
@@ -347,32 +401,54 @@ struct GemmArgs {
     int m_tiles;
 };
 
-template <typename S, int TN, int KC, int STAGES>
+// RT row tiles of 128 weight rows per CTA (RT accumulators of TN columns in TMEM) share one activation stage: the
+// activation bytes a CTA pulls from L2 per multiply-add halve with RT = 2, and that traffic is what bounds the kernel.
+//
+// ATM: the dequantized weights go to tensor memory instead of shared memory (tcgen05.st by the producers, A operand
+// of the MMA read from TMEM).  Shared memory then carries only the activation stages: its data pipe - 128 bytes per
+// cycle, shared by the producers' stores, the bulk copies and the MMA's operand reads - is what bounds the
+// shared-memory variant (a 128 x 128 x 64 chunk moves 64 KB through it = 512 cycles, against 256 cycles of MMA).
+// TMEM columns: RT accumulators of TN, then per stage and row tile KC / 2 columns of A (two f16 per column).
+template <typename S, int TN, int KC, int STAGES, int RT, bool ATM>
 __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc(const GemmArgs g) {
     // a chunk of KC weights per row is 4 KC tasks; the 512 producer threads form 512 / (4 KC) groups that
     // take the chunks in turn
     constexpr int GROUPS = PRODUCER_WARPS * 32 / (4 * KC);
     constexpr int GROUP_WARPS = PRODUCER_WARPS / GROUPS;
-    static_assert(GROUPS >= 1 && STAGES % GROUPS == 0, "each producer group owns every GROUPS-th stage");
+    static_assert(GROUPS >= 1 && GROUPS * 4 * KC == PRODUCER_WARPS * 32, "whole producer groups of one chunk's tasks each");
     extern __shared__ __align__(128) uint8_t smem_raw[];
-    using Smem = GemmSmem<TN, KC, STAGES>;
+    using Smem = GemmSmem<TN, KC, STAGES, RT, ATM>;
+    constexpr int ACC_COLS = RT * TN;
+    constexpr int A_COLS = KC / 2;                                   // per stage and row tile
+    constexpr int SA = Smem::SA;
+    static_assert(SA >= 2, "at least two weight stages");
+    constexpr int USED_COLS = ACC_COLS + (ATM ? SA * RT * A_COLS : 0);
+    constexpr int TMEM_COLS = USED_COLS <= 32 ? 32 : USED_COLS <= 64 ? 64 : USED_COLS <= 128 ? 128 : USED_COLS <= 256 ? 256 : 512;
+    static_assert(USED_COLS <= 512, "accumulators and weight stages exceed the tensor memory");
     Smem & sm = *reinterpret_cast<Smem *>(smem_raw);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int mt = blockIdx.x % g.m_tiles, nt = blockIdx.x / g.m_tiles;
-    const int n0 = nt * TM, m0 = mt * TN;
+    const int n0 = nt * (TM * RT), m0 = mt * TN;
     volatile int * abort_flag = &sm.abort_flag;
+#ifdef SM100_GEMM_TIMING
+    const long long gt_start = clock64();
+#endif
 
     if (threadIdx.x == 0) {
+        for (int s = 0; s < SA; ++s) {
+            mbar_init(smem_addr(&sm.full_a[s]), RT * GROUP_WARPS);
+            mbar_init(smem_addr(&sm.empty_a[s]), 1);
+        }
         for (int s = 0; s < STAGES; ++s) {
-            mbar_init(smem_addr(&sm.full[s]), GROUP_WARPS + 1);  // the group's warps + the bulk copy's expect_tx
-            mbar_init(smem_addr(&sm.empty[s]), 1);
+            mbar_init(smem_addr(&sm.full_b[s]), 1);
+            mbar_init(smem_addr(&sm.empty_b[s]), 1);
         }
         mbar_init(smem_addr(&sm.accum), 1);
         sm.abort_flag = 0;
         fence_barrier_init();
     }
     if (warp == WARP_MMA) {
-        tmem_alloc(smem_addr(&sm.tmem_base), TN);
+        tmem_alloc(smem_addr(&sm.tmem_base), TMEM_COLS);
         tmem_relinquish();
     }
     tc_fence_before();
@@ -380,11 +456,18 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc(const GemmArgs g) {
     tc_fence_after();
     const uint32_t tmem = *(volatile uint32_t *) &sm.tmem_base;
     // barrier addresses advance by 8 bytes per stage, operand stages by their byte size
-    const uint32_t full0 = smem_addr(&sm.full[0]), empty0 = smem_addr(&sm.empty[0]);
+    const uint32_t full_a0 = smem_addr(&sm.full_a[0]), empty_a0 = smem_addr(&sm.empty_a[0]);
+    const uint32_t full_b0 = smem_addr(&sm.full_b[0]), empty_b0 = smem_addr(&sm.empty_b[0]);
     const uint32_t a_smem = smem_addr(sm.a[0]), b_smem = smem_addr(sm.b[0]);
 
-    // everything above overlaps the tail of the previous kernel; the activations it wrote are read below
-    pdl_wait();
+    // Everything above, and the weight side below, overlaps the activation preparation that precedes this kernel
+    // in the stream: only the bulk-copy warp (prepared activations) and the epilogue (token factors, output) wait
+    // for it.  That kernel itself starts only after everything before it has completed, so nothing older is in flight.
+#ifdef SM100_GEMM_TIMING
+    const long long gt_go = clock64();
+    if (warp == FIRST_PRODUCER) { GT_PUT(0, gt_go - gt_start); GT_PUT(1, 1); if (blockIdx.x == 0 && lane == 0) g_gemm_trace[5][0] = gt_start; }
+    long long gt_wait = 0, gt_t;
+#endif
 
     if (warp >= FIRST_PRODUCER) {
         // ---- A operand.  A task is (row, 32-weight block), one per thread of a producer group; with 64-wide
@@ -399,94 +482,135 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc(const GemmArgs g) {
         const int pw = warp - FIRST_PRODUCER;
         const int group = pw / GROUP_WARPS;
         const int gw = pw % GROUP_WARPS;
-        const int row_in = 16 * (gw & 7) + (lane & 7) + 8 * (lane >> 4);
-        const int blk = ((lane >> 3) & 1) + 2 * (gw >> 3);
-        const int64_t row = n0 + row_in;
-        const bool row_ok = row < g.n;
+        // ATM: a thread may only write its warp's quarter of the TMEM lanes (32 (warp % 4) ..), so a warp takes 32
+        // consecutive rows of one block; the group's eight consecutive warps cover the four quarters for both blocks
+        const int row_in = ATM ? 32 * (warp & 3) + lane : 16 * (gw & 7) + (lane & 7) + 8 * (lane >> 4);
+        const int blk = ATM ? gw >> 2 : ((lane >> 3) & 1) + 2 * (gw >> 3);
+        // The work unit is (chunk, row tile): unit u = chunk * RT + row tile, and group g takes the units g, g + GROUPS, ...
+        // Rows past the tensor and blocks past K are clamped to the last valid ones instead of zero-filled: such rows
+        // are never stored, and the activation image is zero where K is padded (the weights read there are finite).
+        const int units = g.nchunks * RT;
+        const int kb_last = g.kblocks - 1;
         const uint32_t dst0 = a_smem + (blk * 4) * (TM * 16) + row_in * 16;
+        auto unit_row = [&](int u) -> int64_t {
+            const int64_t row = (int64_t) n0 + (u % RT) * TM + row_in;
+            return row < g.n ? row : (int64_t) g.n - 1;
+        };
+        auto unit_kb = [&](int u) -> int {
+            const int kb = (u / RT) * BLOCKS + blk;
+            return kb < kb_last ? kb : kb_last;
+        };
         typename S::Regs ring[DEPTH];
 #pragma unroll
         for (int d = 0; d < DEPTH; ++d) {
-            const int kb = (GROUPS * d + group) * BLOCKS + blk;
-            if (row_ok && kb < g.kblocks) S::load(ring[d], g.w, row, kb);
+            const int u = group + GROUPS * d;
+            S::load(ring[d], g.w, unit_row(u), unit_kb(u));
         }
         bool alive = true;
-        int s = group;  // this group's stage: advances by GROUPS, wraps at STAGES
-        uint32_t phase = 0;
-        for (int c0 = group; c0 < g.nchunks && alive; c0 += GROUPS * DEPTH) {
+        for (int u0 = group; u0 < units && alive; u0 += GROUPS * DEPTH) {
 #pragma unroll
             for (int d = 0; d < DEPTH; ++d) {
-                const int c = c0 + GROUPS * d;
-                if (c >= g.nchunks) break;
-                const int kb = c * BLOCKS + blk;
+                const int u = u0 + GROUPS * d;
+                if (u >= units) break;
+                const int c = u / RT, rt = u % RT;
                 uint32_t out[16];
-                if (row_ok && kb < g.kblocks) {
-                    SrcTraits<S>::convert(ring[d], kb, out);
-                } else {
-#pragma unroll
-                    for (int i = 0; i < 16; ++i) out[i] = 0u;
-                }
-                const int kb_next = kb + GROUPS * DEPTH * BLOCKS;
-                if (row_ok && kb_next < g.kblocks) S::load(ring[d], g.w, row, kb_next);
+                SrcTraits<S>::convert(ring[d], unit_kb(u), out);
+                const int u_next = u + GROUPS * DEPTH;   // past the end: a clamped, unused load
+                S::load(ring[d], g.w, unit_row(u_next), unit_kb(u_next));
                 // the stage is free once the MMAs of the chunk that used it last have retired
-                bool ok = mbar_try_wait(empty0 + 8 * s, phase ^ 1u);
-                if (!ok) ok = mbar_wait(empty0 + 8 * s, phase ^ 1u, abort_flag, 0);
+                const int s = c % SA;
+                const uint32_t phase = (uint32_t) (c / SA) & 1u;
+#ifdef SM100_GEMM_TIMING
+                gt_t = clock64();
+#endif
+                bool ok = mbar_try_wait(empty_a0 + 8 * s, phase ^ 1u);
+                if (!ok) ok = mbar_wait(empty_a0 + 8 * s, phase ^ 1u, abort_flag, 0);
                 if (!__all_sync(0xffffffffu, ok)) { alive = false; break; }
-                const uint32_t dst = dst0 + s * Smem::A_BYTES;
+#ifdef SM100_GEMM_TIMING
+                gt_wait += clock64() - gt_t;
+                if (gw == 0 && rt == 0) GT_TRACE(1, c);
+#endif
+                if (ATM) {
+                    tc_fence_after();   // the stage's previous MMAs (observed through the barrier) precede these stores
+                    tmem_st16(tmem + ((uint32_t) (32 * (warp & 3)) << 16) + (uint32_t) (ACC_COLS + (s * RT + rt) * A_COLS + blk * 16), out);
+                    tmem_st_wait();
+                    tc_fence_before();   // the stores are ordered before the MMA that the arrival releases
+                } else {
+                    const uint32_t dst = dst0 + (s * RT + rt) * Smem::A_BYTES;
 #pragma unroll
-                for (int j = 0; j < 4; ++j)
-                    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst + j * (TM * 16)), "r"(out[4 * j]), "r"(out[4 * j + 1]),
-                                 "r"(out[4 * j + 2]), "r"(out[4 * j + 3])
-                                 : "memory");
-                fence_proxy_async();  // generic-proxy stores -> visible to the tensor core's async proxy
+                    for (int j = 0; j < 4; ++j)
+                        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst + j * (TM * 16)), "r"(out[4 * j]), "r"(out[4 * j + 1]),
+                                     "r"(out[4 * j + 2]), "r"(out[4 * j + 3])
+                                     : "memory");
+                    fence_proxy_async();  // generic-proxy stores -> visible to the tensor core's async proxy
+                }
                 __syncwarp();
-                if (lane == 0) mbar_arrive(full0 + 8 * s);
-                s += GROUPS;
-                if (s >= STAGES) { s -= STAGES; phase ^= 1u; }
+                if (lane == 0) mbar_arrive(full_a0 + 8 * s);
+#ifdef SM100_GEMM_TIMING
+                if (gw == 0 && rt == 0) GT_TRACE(2, c);
+#endif
             }
         }
         pdl_launch_dependents();
+#ifdef SM100_GEMM_TIMING
+        if (warp == FIRST_PRODUCER) { GT_PUT(2, clock64() - gt_go); GT_PUT(3, gt_wait); }
+        gt_t = clock64();
+#endif
 
         // ---- epilogue: a warp may read the TMEM lanes 32 (warp % 4) ..; four consecutive producer warps cover
         // the four lane quarters, and each such set takes a quarter of the columns ----
+        pdl_wait();
         bool acc_ok = alive;
         if (acc_ok) {
             acc_ok = mbar_try_wait(smem_addr(&sm.accum), 0u);
             if (!acc_ok) acc_ok = mbar_wait(smem_addr(&sm.accum), 0u, abort_flag, 1);
         }
-        if (__all_sync(0xffffffffu, acc_ok)) {
+        if (__all_sync(0xffffffffu, acc_ok) && pw < EPILOGUE_WARPS) {
             tc_fence_after();
             const int lane_base = 32 * (warp & 3);
             const int col_base = (pw >> 2) * (TN / 4);
-            const int64_t n_out = n0 + lane_base + lane;
 #pragma unroll 1
-            for (int cc = 0; cc < TN / 4; cc += 16) {
-                uint32_t r[16];
-                tmem_ld16(tmem + ((uint32_t) lane_base << 16) + (uint32_t) (col_base + cc), r);
-                tmem_ld_wait();
+            for (int rt = 0; rt < RT; ++rt) {
+                const int64_t n_out = (int64_t) n0 + rt * TM + lane_base + lane;
+#pragma unroll 1
+                for (int cc = 0; cc < TN / 4; cc += 16) {
+                    uint32_t r[16];
+                    tmem_ld16(tmem + ((uint32_t) lane_base << 16) + (uint32_t) (rt * TN + col_base + cc), r);
+                    // the token factors are fetched before any store: a load after a store to memory that may alias
+                    // is not moved up by the compiler, and 16 dependent trips to L2 per pass cost ~5 us per CTA
+                    float f[16];
 #pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                    const int tok = m0 + col_base + cc + j;
-                    if (tok < g.m && n_out < g.n) g.y[(int64_t) tok * g.ldy + n_out] = __uint_as_float(r[j]) * (__ldcg(g.tokscale + tok) * g.out_scale);
+                    for (int j = 0; j < 16; ++j) f[j] = __ldcg(g.tokscale + m0 + col_base + cc + j) * g.out_scale;   // allocated for whole tiles
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        const int tok = m0 + col_base + cc + j;
+                        if (tok < g.m && n_out < g.n) g.y[(int64_t) tok * g.ldy + n_out] = __uint_as_float(r[j]) * f[j];
+                    }
                 }
             }
         }
+#ifdef SM100_GEMM_TIMING
+        if (warp == FIRST_PRODUCER) { GT_PUT(4, clock64() - gt_t); GT_PUT(5, clock64() - gt_start); }
+#endif
     } else if (warp == WARP_BULK) {
         // ---- B operand: one bulk copy per stage, issued as soon as the stage is free ----
         if (lane == 0) {
+            pdl_wait();
             const uint8_t * src = reinterpret_cast<const uint8_t *>(g.xh) + (int64_t) mt * g.nchunks * Smem::B_BYTES;
             int issued = 0, s = 0;
             uint32_t phase = 0;
             for (int c = 0; c < g.nchunks; ++c) {
-                if (!mbar_try_wait(empty0 + 8 * s, phase ^ 1u) && !mbar_wait(empty0 + 8 * s, phase ^ 1u, abort_flag, 2)) break;
-                mbar_expect_tx(full0 + 8 * s, Smem::B_BYTES);
-                bulk_g2s(b_smem + s * Smem::B_BYTES, src + (int64_t) c * Smem::B_BYTES, Smem::B_BYTES, full0 + 8 * s);
+                if (!mbar_try_wait(empty_b0 + 8 * s, phase ^ 1u) && !mbar_wait(empty_b0 + 8 * s, phase ^ 1u, abort_flag, 2)) break;
+                GT_TRACE(0, c);
+                mbar_expect_tx(full_b0 + 8 * s, Smem::B_BYTES);
+                bulk_g2s(b_smem + s * Smem::B_BYTES, src + (int64_t) c * Smem::B_BYTES, Smem::B_BYTES, full_b0 + 8 * s);
                 issued = c + 1;
                 if (++s == STAGES) { s = 0; phase ^= 1u; }
             }
             // copies still in flight must land before the CTA's shared memory goes away
             for (int c = issued > STAGES ? issued - STAGES : 0; c < issued; ++c) {
-                const uint32_t bar = full0 + 8 * (c % STAGES);
+                const uint32_t bar = full_b0 + 8 * (c % STAGES);
                 for (uint32_t i = 0; i < WAIT_LIMIT && !mbar_try_wait(bar, (uint32_t) (c / STAGES) & 1u); ++i) __nanosleep(64);
             }
         }
@@ -500,31 +624,54 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc(const GemmArgs g) {
         const uint32_t a_lo0 = (a_smem >> 4) | ((uint32_t) (TM * 16) >> 4) << 16;  // start address | bytes between K halves
         const uint32_t b_lo0 = (b_smem >> 4) | ((uint32_t) (TN * 16) >> 4) << 16;
         bool alive = true;
-        int s = 0;
-        uint32_t phase = 0, accumulate = 0;
+        int sa = 0, sb = 0;                       // stage of the weight ring and of the activation ring
+        uint32_t pa = 0, pb = 0, accumulate = 0;
         for (int c = 0; c < g.nchunks; ++c) {
-            bool ok = mbar_try_wait(full0 + 8 * s, phase);
-            if (!ok) ok = mbar_wait(full0 + 8 * s, phase, abort_flag, 3, false);
+#ifdef SM100_GEMM_TIMING
+            gt_t = clock64();
+#endif
+            bool ok = mbar_try_wait(full_b0 + 8 * sb, pb);
+            if (!ok) ok = mbar_wait(full_b0 + 8 * sb, pb, abort_flag, 3, false);
+            if (ok) {
+                ok = mbar_try_wait(full_a0 + 8 * sa, pa);
+                if (!ok) ok = mbar_wait(full_a0 + 8 * sa, pa, abort_flag, 4, false);
+            }
             if (!__all_sync(0xffffffffu, ok)) { alive = false; break; }
+#ifdef SM100_GEMM_TIMING
+            gt_wait += clock64() - gt_t;
+            GT_TRACE(3, c);
+#endif
             tc_fence_after();
-            if (lane == 0) {
-                const uint32_t a_lo = a_lo0 + s * (Smem::A_BYTES >> 4), b_lo = b_lo0 + s * (Smem::B_BYTES >> 4);
+            {
+                const uint32_t a_lo = ATM ? 0u : a_lo0 + sa * (RT * Smem::A_BYTES >> 4), b_lo = b_lo0 + sb * (Smem::B_BYTES >> 4);
 #pragma unroll
-                for (int ks = 0; ks < KC / 16; ++ks) {
-                    mma_f16(tmem, a_lo + ks * (2 * TM * 16 >> 4), b_lo + ks * (2 * TN * 16 >> 4), DESC_HI, IDESC, accumulate);
-                    accumulate = 1u;
+                for (int rt = 0; rt < RT; ++rt) {
+#pragma unroll
+                    for (int ks = 0; ks < KC / 16; ++ks) {
+                        if (ATM)
+                            mma_f16_ta(tmem + rt * TN, tmem + ACC_COLS + (sa * RT + rt) * A_COLS + ks * 8, b_lo + ks * (2 * TN * 16 >> 4), DESC_HI,
+                                       IDESC, ks == 0 ? accumulate : 1u);
+                        else
+                            mma_f16(tmem + rt * TN, a_lo + rt * (Smem::A_BYTES >> 4) + ks * (2 * TM * 16 >> 4), b_lo + ks * (2 * TN * 16 >> 4),
+                                    DESC_HI, IDESC, ks == 0 ? accumulate : 1u);
+                    }
                 }
-                mma_commit(empty0 + 8 * s);
+                accumulate = 1u;
+                mma_commit(empty_a0 + 8 * sa);   // each commit covers every MMA issued so far
+                mma_commit(empty_b0 + 8 * sb);
+                GT_TRACE(4, c);
             }
-            __syncwarp();
-            if (++s == STAGES) { s = 0; phase ^= 1u; }
+            if (++sa == SA) { sa = 0; pa ^= 1u; }
+            if (++sb == STAGES) { sb = 0; pb ^= 1u; }
         }
-        if (lane == 0) {
-            // the accumulator is complete (or abandoned) once everything issued so far has retired
-            mma_commit(smem_addr(&sm.accum));
-            if (!alive) {
-                for (uint32_t i = 0; i < WAIT_LIMIT && !mbar_try_wait(smem_addr(&sm.accum), 0u); ++i) __nanosleep(64);
-            }
+        __syncwarp();
+#ifdef SM100_GEMM_TIMING
+        GT_PUT(6, clock64() - gt_go); GT_PUT(7, gt_wait); GT_PUT(8, g.nchunks);
+#endif
+        // the accumulator is complete (or abandoned) once everything issued so far has retired
+        mma_commit(smem_addr(&sm.accum));
+        if (!alive && lane == 0) {
+            for (uint32_t i = 0; i < WAIT_LIMIT && !mbar_try_wait(smem_addr(&sm.accum), 0u); ++i) __nanosleep(64);
         }
         __syncwarp();
     }
@@ -533,73 +680,92 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc(const GemmArgs g) {
     __syncthreads();
     if (warp == WARP_MMA) {
         tc_fence_after();
-        tmem_dealloc(tmem, TN);
+        tmem_dealloc(tmem, TMEM_COLS);
     }
 }
 
 // ---------------------------------------------------------------------------------------------
 // Activation preparation: f32 [M, K] (column stride ldx) -> normalised f16 stage images + token factors
 // ---------------------------------------------------------------------------------------------
+// A CTA takes `toks` consecutive tokens (a power of two, 1..8) with 256 / toks threads each and keeps their rows in
+// registers (up to PREP_MAX_V float4 per thread, all requested at once): one trip to memory gives both the
+// token's largest magnitude and, after the scale is known, the f16 image.  Rows too long for the registers
+// (K > 32768 / toks at toks = 1) take the two-pass path: the same loop twice.
+constexpr int PREP_MAX_V = 32;
+
 template <int TN, int KC>
-__global__ void __launch_bounds__(256) gemm_prep_x(const float * x, int64_t ldx, int m, int k, int nchunks, int kslices, float * tokscale,
+__global__ void __launch_bounds__(256) gemm_prep_x(const float * x, int64_t ldx, int m, int k, int nchunks, int toks, float * tokscale,
                                                    __half * xh) {
     pdl_wait();
-    __shared__ float s_scale[8];
-    const int group = blockIdx.x / kslices, slice = blockIdx.x % kslices;
+    pdl_launch_dependents();
+    __shared__ float s_amax[8];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    {
-        const int tok = group * 8 + warp;
-        float amax = 0.0f;
-        if (tok < m) {
-            const float4 * row = reinterpret_cast<const float4 *>(x + (int64_t) tok * ldx);
-            for (int i = lane; i < k / 4; i += 32) {
-                const float4 v = __ldcg(row + i);
-                amax = fmaxf(amax, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
-            }
+    const int tpt = 256 / toks;                  // threads per token: 32, 64, 128 or 256
+    const int tok = blockIdx.x * toks + threadIdx.x / tpt;
+    const int r = threadIdx.x % tpt;
+    const int kpad4 = nchunks * (KC / 4);        // float4 per token in the image (K padded to whole chunks)
+    const int k4 = k / 4;
+    const bool in_regs = kpad4 <= PREP_MAX_V * tpt;
+    const float4 * row = reinterpret_cast<const float4 *>(x + (int64_t) tok * ldx);
+    const bool tok_ok = tok < m;
+    float4 v[PREP_MAX_V];
+    float amax = 0.0f;
+    if (in_regs) {
+#pragma unroll
+        for (int i = 0; i < PREP_MAX_V; ++i) {
+            const int idx = r + i * tpt;
+            v[i] = tok_ok && idx < k4 ? __ldcg(row + idx) : make_float4(0.f, 0.f, 0.f, 0.f);
         }
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-        int sh = 0;
-        if (amax > 0.0f && amax <= 3.0e38f) {
-            sh = 13 - ilogbf(amax);
-            sh = sh > 100 ? 100 : sh < -100 ? -100 : sh;
-        }
-        if (lane == 0) {
-            s_scale[warp] = ldexpf(1.0f, sh);
-            if (slice == 0) tokscale[tok] = ldexpf(1.0f, -sh);
+        for (int i = 0; i < PREP_MAX_V; ++i)
+            amax = fmaxf(amax, fmaxf(fmaxf(fabsf(v[i].x), fabsf(v[i].y)), fmaxf(fabsf(v[i].z), fabsf(v[i].w))));
+    } else if (tok_ok) {
+#pragma unroll 8
+        for (int idx = r; idx < k4; idx += tpt) {
+            const float4 t = __ldcg(row + idx);
+            amax = fmaxf(amax, fmaxf(fmaxf(fabsf(t.x), fabsf(t.y)), fmaxf(fabsf(t.z), fabsf(t.w))));
         }
     }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    if (lane == 0) s_amax[warp] = amax;
     __syncthreads();
-    pdl_launch_dependents();
-    const int t = threadIdx.x & 7;
-    const int tok = group * 8 + t;
-    const float scale = s_scale[t];
-    constexpr int UPC = KC / 8;       // 8-element K units per chunk
-    const int units = nchunks * UPC;  // per token, K padded to whole chunks
-    const int per_slice = (units + kslices - 1) / kslices;
-    const int u_end = (slice + 1) * per_slice < units ? (slice + 1) * per_slice : units;
+    const int wpt = tpt / 32, w0 = (threadIdx.x / tpt) * wpt;   // the token's warps
+    amax = 0.0f;
+    for (int w = 0; w < wpt; ++w) amax = fmaxf(amax, s_amax[w0 + w]);
+    int sh = 0;
+    if (amax > 0.0f && amax <= 3.0e38f) {
+        sh = 13 - ilogbf(amax);
+        sh = sh > 100 ? 100 : sh < -100 ? -100 : sh;
+    }
+    const float scale = ldexpf(1.0f, sh);
+    if (r == 0) tokscale[tok] = ldexpf(1.0f, -sh);
+    // image: [token tile][chunk][k / 8][token in tile][8 halves]; a float4 is half of one 16-byte unit
     const int mt = tok / TN, tt = tok % TN;
-    for (int u = slice * per_slice + (threadIdx.x >> 3); u < u_end; u += 32) {
-        const int k0 = u * 8;
-        float4 a = make_float4(0.f, 0.f, 0.f, 0.f), b = a;
-        if (tok < m && k0 < k) {
-            const float4 * p = reinterpret_cast<const float4 *>(x + (int64_t) tok * ldx + k0);
-            a = __ldcg(p);
-            b = __ldcg(p + 1);
+    __half * img = xh + (int64_t) mt * nchunks * (TN * KC) + tt * 8;
+    auto put = [&](int idx, const float4 & t) {
+        const int kk = idx * 4, c = kk / KC, u = (kk % KC) >> 3;
+        const __half2 h0 = __floats2half2_rn(t.x * scale, t.y * scale), h1 = __floats2half2_rn(t.z * scale, t.w * scale);
+        *reinterpret_cast<uint2 *>(img + (int64_t) c * (TN * KC) + u * (TN * 8) + (kk & 4)) = make_uint2(h2_bits(h0), h2_bits(h1));
+    };
+    if (in_regs) {
+#pragma unroll
+        for (int i = 0; i < PREP_MAX_V; ++i) {
+            const int idx = r + i * tpt;
+            if (idx < kpad4) put(idx, v[i]);
         }
-        const __half2 h0 = __floats2half2_rn(a.x * scale, a.y * scale), h1 = __floats2half2_rn(a.z * scale, a.w * scale);
-        const __half2 h2 = __floats2half2_rn(b.x * scale, b.y * scale), h3 = __floats2half2_rn(b.z * scale, b.w * scale);
-        __half * dst = xh + ((int64_t) mt * nchunks + u / UPC) * (TN * KC) + (u % UPC) * (TN * 8) + tt * 8;
-        *reinterpret_cast<uint4 *>(dst) = make_uint4(h2_bits(h0), h2_bits(h1), h2_bits(h2), h2_bits(h3));
+    } else {
+#pragma unroll 8
+        for (int idx = r; idx < kpad4; idx += tpt) put(idx, tok_ok && idx < k4 ? __ldcg(row + idx) : make_float4(0.f, 0.f, 0.f, 0.f));
     }
 }
 
 std::atomic<bool> g_gemm_launched{false};
 
-template <typename S, int TN, int KC, int STAGES>
+template <typename S, int TN, int KC, int STAGES, int RT, bool ATM>
 int launch_gemm(cudaStream_t s, GemmArgs g, int n_tiles) {
     g.out_scale = 1.0f / S::PRESCALE;
-    using Smem = GemmSmem<TN, KC, STAGES>;
+    using Smem = GemmSmem<TN, KC, STAGES, RT, ATM>;
     static std::mutex mu;
     static std::vector<char> configured;
     int dev = 0;
@@ -608,30 +774,31 @@ int launch_gemm(cudaStream_t s, GemmArgs g, int n_tiles) {
         std::lock_guard<std::mutex> lock(mu);
         if ((int) configured.size() <= dev) configured.resize(dev + 1, 0);
         if (!configured[dev]) {
-            SM100_CUDA(cudaFuncSetAttribute(gemm_tc<S, TN, KC, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) sizeof(Smem)));
+            SM100_CUDA(cudaFuncSetAttribute(gemm_tc<S, TN, KC, STAGES, RT, ATM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) sizeof(Smem)));
             configured[dev] = 1;
         }
     }
     g_gemm_launched.store(true, std::memory_order_relaxed);
-    return launch(gemm_tc<S, TN, KC, STAGES>, dim3((unsigned) (n_tiles * g.m_tiles)), dim3(GEMM_THREADS), sizeof(Smem), s, g);
+    return launch(gemm_tc<S, TN, KC, STAGES, RT, ATM>, dim3((unsigned) (n_tiles * g.m_tiles)), dim3(GEMM_THREADS), sizeof(Smem), s, g);
 }
 
-template <int TN, int KC, int STAGES>
+template <int TN, int KC, int STAGES, int RT, bool ATM>
 int launch_gemm_dtype(cudaStream_t s, int dtype, int layout, const GemmArgs & g, int n_tiles) {
     const bool packed = layout == LAYOUT_PACKED;
     switch (dtype) {
         case DT_Q8_0:
-            return packed ? launch_gemm<SrcQ80<true>, TN, KC, STAGES>(s, g, n_tiles) : launch_gemm<SrcQ80<false>, TN, KC, STAGES>(s, g, n_tiles);
+            return packed ? launch_gemm<SrcQ80<true>, TN, KC, STAGES, RT, ATM>(s, g, n_tiles) : launch_gemm<SrcQ80<false>, TN, KC, STAGES, RT, ATM>(s, g, n_tiles);
         case DT_Q4_0:
-            return packed ? launch_gemm<SrcQ40<true>, TN, KC, STAGES>(s, g, n_tiles) : launch_gemm<SrcQ40<false>, TN, KC, STAGES>(s, g, n_tiles);
-        case DT_Q4_K: return launch_gemm<SrcQ4K, TN, KC, STAGES>(s, g, n_tiles);
-        case DT_F16: return launch_gemm<SrcF16, TN, KC, STAGES>(s, g, n_tiles);
+            return packed ? launch_gemm<SrcQ40<true>, TN, KC, STAGES, RT, ATM>(s, g, n_tiles) : launch_gemm<SrcQ40<false>, TN, KC, STAGES, RT, ATM>(s, g, n_tiles);
+        case DT_Q4_K: return launch_gemm<SrcQ4K, TN, KC, STAGES, RT, ATM>(s, g, n_tiles);
+        case DT_F16: return launch_gemm<SrcF16, TN, KC, STAGES, RT, ATM>(s, g, n_tiles);
     }
     return fail(ST_UNSUPPORTED, "gemm: no tensor-core source for dtype %d", dtype);
 }
 
-template <int TN, int KC, int STAGES>
-int gemm_passes(cudaStream_t s, int dtype, int layout, GemmArgs g, const float * x, int64_t ldx, int64_t m, int64_t k, float * y, int n_tiles) {
+template <int TN, int KC, int STAGES, int RT, bool ATM>
+int gemm_passes(cudaStream_t s, int dtype, int layout, GemmArgs g, const float * x, int64_t ldx, int64_t m, int64_t k, float * y) {
+    const int n_tiles = (g.n + TM * RT - 1) / (TM * RT);
     g.nchunks = (int) ((k + KC - 1) / KC);
     // tokens per pass: the prepared activations of one pass stay below 64 MiB
     int64_t pass = ((int64_t) 64 << 20) / ((int64_t) g.nchunks * KC * 2) / TN * TN;
@@ -647,19 +814,18 @@ int gemm_passes(cudaStream_t s, int dtype, int layout, GemmArgs g, const float *
         if (st != ST_OK) return st;
         float * tokscale = (float *) ws;
         __half * xh = (__half *) ((uint8_t *) ws + scale_bytes);
-        const int groups = (int) (mpad / 8);
-        int kslices = (2 * sm_count() + groups - 1) / groups;
-        if (kslices < 1) kslices = 1;
-        if (kslices > g.nchunks) kslices = g.nchunks;
-        st = launch(gemm_prep_x<TN, KC>, dim3((unsigned) (groups * kslices)), dim3(256), 0, s, x + c0 * ldx, ldx, (int) mm, (int) k, g.nchunks,
-                    kslices, tokscale, xh);
+        // tokens per CTA: as many (up to 8) as keep a token's share of the row within the registers of its threads
+        int toks = 8;
+        while (toks > 1 && (int64_t) g.nchunks * (KC / 4) > (int64_t) PREP_MAX_V * (256 / toks)) toks >>= 1;
+        st = launch(gemm_prep_x<TN, KC>, dim3((unsigned) (mpad / toks)), dim3(256), 0, s, x + c0 * ldx, ldx, (int) mm, (int) k, g.nchunks,
+                    toks, tokscale, xh);
         if (st != ST_OK) return st;
         g.xh = xh;
         g.tokscale = tokscale;
         g.y = y + c0 * g.ldy;
         g.m = (int) mm;
         g.m_tiles = m_tiles;
-        st = launch_gemm_dtype<TN, KC, STAGES>(s, dtype, layout, g, n_tiles);
+        st = launch_gemm_dtype<TN, KC, STAGES, RT, ATM>(s, dtype, layout, g, n_tiles);
         if (st != ST_OK) return st;
     }
     return ST_OK;
@@ -669,6 +835,20 @@ int gemm_passes(cudaStream_t s, int dtype, int layout, GemmArgs g, const float *
 
 // Reads and clears the fault flag of the tensor-core GEMM on the current device; called after a stream
 // synchronisation.  Costs nothing until a GEMM has been launched.
+#ifdef SM100_GEMM_TIMING
+extern "C" __attribute__((visibility("default"))) int sm100_debug_gemm_trace(long long * out) {
+    return cudaMemcpyFromSymbol(out, g_gemm_trace, sizeof(long long) * 6 * 64) != cudaSuccess ? 1 : 0;
+}
+extern "C" __attribute__((visibility("default"))) int sm100_debug_gemm_timing(unsigned long long * out, int reset) {
+    if (cudaMemcpyFromSymbol(out, g_gemm_timing, sizeof(unsigned long long) * 16) != cudaSuccess) return 1;
+    if (reset) {
+        unsigned long long z[16] = {};
+        if (cudaMemcpyToSymbol(g_gemm_timing, z, sizeof(z)) != cudaSuccess) return 1;
+    }
+    return 0;
+}
+#endif
+
 int gemm_poll_fault() {
     if (!g_gemm_launched.exchange(false, std::memory_order_relaxed)) return ST_OK;
     int v = 0;
@@ -701,13 +881,31 @@ int gemm_tc_mul_mat(cudaStream_t s, int dtype, int layout, const void * w, int64
     g.n = (int) n;
     g.kblocks = (int) (k / 32);
     g.ldy = ldy;
-    // 256-token tiles halve the dequantization work and the weight traffic per output, but a CTA then owns
-    // all of an SM: worth it once there are enough tiles to fill the machine
+    // Tile choice.  The kernel is bound by what a CTA pulls from L2 per multiply-add, so larger tiles are faster as
+    // long as there are enough of them for the SMs: 256 weight rows x 256 tokens (two accumulators of 256 columns)
+    // when that still occupies most SMs, else 128 x 256 when it fills them, else 128 x 128.
     static const int forced_tn = [] { const char * e = getenv("SM100_GEMM_TN"); return e != nullptr ? atoi(e) : 0; }();
-    const int64_t tiles256 = (int64_t) n_tiles * ((m + 255) / 256);
-    const bool wide = forced_tn != 0 ? forced_tn == 256 : tiles256 >= (int64_t) sm_count();
-    const int st = wide ? gemm_passes<256, 64, 4>(s, dtype, layout, g, x, ldx, m, k, y, n_tiles)
-                        : gemm_passes<128, 64, 6>(s, dtype, layout, g, x, ldx, m, k, y, n_tiles);
+    static const int forced_rt = [] { const char * e = getenv("SM100_GEMM_RT"); return e != nullptr ? atoi(e) : 0; }();
+    const int64_t mt256 = (m + 255) / 256;
+    const int64_t tiles_1_256 = (int64_t) n_tiles * mt256;
+    const int64_t tiles_2_256 = (int64_t) ((n + 2 * TM - 1) / (2 * TM)) * mt256;
+    int tn = tiles_1_256 >= (int64_t) sm_count() ? 256 : 128;
+    int rt = 1;
+    if (tiles_2_256 * 5 >= (int64_t) sm_count() * 3) { tn = 256; rt = 2; }
+    if (forced_tn == 128 || forced_tn == 256) tn = forced_tn;
+    if (forced_rt == 1 || forced_rt == 2) rt = forced_rt;
+    // weights through tensor memory (default) or through shared memory
+    static const int use_atm = [] { const char * e = getenv("SM100_GEMM_TMEM_A"); return e != nullptr ? atoi(e) : 1; }();
+    int st;
+    if (use_atm) {
+        if (rt == 2) tn = 128;   // two accumulators of 256 columns leave no tensor memory for the weight stages
+        if (rt == 2) st = gemm_passes<128, 64, 12, 2, true>(s, dtype, layout, g, x, ldx, m, k, y);
+        else st = tn == 256 ? gemm_passes<256, 64, 6, 1, true>(s, dtype, layout, g, x, ldx, m, k, y) : gemm_passes<128, 64, 12, 1, true>(s, dtype, layout, g, x, ldx, m, k, y);
+    } else if (rt == 2) {
+        st = tn == 256 ? gemm_passes<256, 64, 3, 2, false>(s, dtype, layout, g, x, ldx, m, k, y) : gemm_passes<128, 64, 4, 2, false>(s, dtype, layout, g, x, ldx, m, k, y);
+    } else {
+        st = tn == 256 ? gemm_passes<256, 64, 4, 1, false>(s, dtype, layout, g, x, ldx, m, k, y) : gemm_passes<128, 64, 6, 1, false>(s, dtype, layout, g, x, ldx, m, k, y);
+    }
     if (st != ST_OK) return st;
     *handled = true;
     return ST_OK;

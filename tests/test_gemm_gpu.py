@@ -95,3 +95,22 @@ def test_gemm_q8_0_prefill_shapes(sm100, stream, n):
     gs = U.device_mul_mat(sm100, stream, U.Q8_0, U.PACKED, wq, k, s)
     assert sgref.nmse(gs[:40], got[:40] + got[40:80]) <= TOL
     assert sgref.nmse(gs[40:], got[:40]) <= 1e-12
+
+
+@pytest.mark.parametrize("tn,rt,tmem_a", [(128, 1, 1), (256, 1, 1), (128, 2, 1), (128, 1, 0), (256, 1, 0), (128, 2, 0), (256, 2, 0)],
+                         ids=lambda v: str(v))
+def test_gemm_forced_tiles(sm100, tn, rt, tmem_a):
+    """Every variant of the kernel (tokens per tile x row tiles per CTA x weights staged in tensor or shared memory)
+    on ragged shapes: the variant is chosen from the problem size, so small problems reach the others only when a
+    child process pins them."""
+    import json
+    import os
+    import subprocess
+    import sys
+    env = dict(os.environ, SM100_GEMM_TN=str(tn), SM100_GEMM_RT=str(rt), SM100_GEMM_TMEM_A=str(tmem_a))
+    worker = os.path.join(os.path.dirname(os.path.abspath(__file__)), "gemm_tiles_worker.py")
+    r = subprocess.run([sys.executable, worker], env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    res = json.loads(r.stdout.strip().splitlines()[-1])
+    assert res["cases"] == 6
+    assert res["worst"] <= TOL, res
