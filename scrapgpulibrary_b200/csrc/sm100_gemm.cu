@@ -14,13 +14,16 @@
 //                   one contiguous block of 8-token x 16-byte core matrices.  A consumer CTA then fetches a
 //                   whole B stage with one bulk copy (cp.async.bulk, completion on an mbarrier).
 //
-//  2. gemm_tc       one CTA per 128 weight rows x TN tokens.  Warps 0-7 dequantize the weights of the
-//                   CTA's rows chunk by chunk into f16 core matrices in shared memory (the A operand;
-//                   weights are multiplied by 256 to keep small scales out of the f16 subnormals), warp 8
-//                   issues the bulk copies of the B operand, one thread of warp 9 issues tcgen05.mma
-//                   (kind::f16, 128 x TN x 16 per instruction) into a TMEM accumulator of TN columns and
-//                   commits each stage back to the producers.  When the last commit lands, warps 0-7
-//                   read the accumulator with tcgen05.ld, undo the two scalings and store y.
+//  2. gemm_tc       one CTA per 128 weight rows x TN tokens (TN = 128 or 256).  Warp 0 owns the tensor memory
+//                   and issues tcgen05.mma (kind::f16, 128 x TN x 16 per instruction, f32 accumulator of TN
+//                   TMEM columns), warp 1 issues the bulk copies of the B stages, warps 2-25 dequantize the
+//                   CTA's weight rows chunk by chunk to f16 (weights are multiplied by 256 to keep small
+//                   scales out of the f16 subnormals) - by default straight into tensor memory with
+//                   tcgen05.st, from where the MMA reads its A operand, so that shared memory carries the
+//                   activations only; optionally into shared-memory core matrices.  Weight stages and
+//                   activation stages are two rings with their own full/empty mbarriers; tcgen05.commit
+//                   hands both back.  When the last commit lands, warps 2-17 read the accumulator with
+//                   tcgen05.ld, undo the two scalings and store y.
 //
 // f16 operands with f32 accumulation: each product carries two roundings of 2^-11 relative size, which
 // puts the NMSE near 2e-7.  Every wait on an mbarrier is bounded; a CTA that gives up raises a fault flag
@@ -881,26 +884,22 @@ int gemm_tc_mul_mat(cudaStream_t s, int dtype, int layout, const void * w, int64
     g.n = (int) n;
     g.kblocks = (int) (k / 32);
     g.ldy = ldy;
-    // Tile choice.  The kernel is bound by what a CTA pulls from L2 per multiply-add, so larger tiles are faster as
-    // long as there are enough of them for the SMs: 256 weight rows x 256 tokens (two accumulators of 256 columns)
-    // when that still occupies most SMs, else 128 x 256 when it fills them, else 128 x 128.
+    // Tile choice.  128 weight rows x 256 tokens per CTA once such tiles fill the SMs: per multiply-add it pulls 20 %
+    // fewer bytes into the SM than 128 x 128, and the kernel is bound by what an SM can take in (activation stages by
+    // bulk copy + quantized weights by loads, ~50 bytes per cycle measured).  Two row tiles per CTA (256 x 128) pull
+    // less still but are bound by the dequantizing warps instead; they stay selectable for experiments.
     static const int forced_tn = [] { const char * e = getenv("SM100_GEMM_TN"); return e != nullptr ? atoi(e) : 0; }();
     static const int forced_rt = [] { const char * e = getenv("SM100_GEMM_RT"); return e != nullptr ? atoi(e) : 0; }();
-    const int64_t mt256 = (m + 255) / 256;
-    const int64_t tiles_1_256 = (int64_t) n_tiles * mt256;
-    const int64_t tiles_2_256 = (int64_t) ((n + 2 * TM - 1) / (2 * TM)) * mt256;
-    int tn = tiles_1_256 >= (int64_t) sm_count() ? 256 : 128;
-    int rt = 1;
-    if (tiles_2_256 * 5 >= (int64_t) sm_count() * 3) { tn = 256; rt = 2; }
-    if (forced_tn == 128 || forced_tn == 256) tn = forced_tn;
-    if (forced_rt == 1 || forced_rt == 2) rt = forced_rt;
-    // weights through tensor memory (default) or through shared memory
+    // weights staged in tensor memory (default) or in shared memory
     static const int use_atm = [] { const char * e = getenv("SM100_GEMM_TMEM_A"); return e != nullptr ? atoi(e) : 1; }();
+    int tn = (int64_t) n_tiles * ((m + 255) / 256) >= (int64_t) sm_count() ? 256 : 128;
+    if (forced_tn == 128 || forced_tn == 256) tn = forced_tn;
+    const int rt = forced_rt == 2 ? 2 : 1;
     int st;
     if (use_atm) {
-        if (rt == 2) tn = 128;   // two accumulators of 256 columns leave no tensor memory for the weight stages
-        if (rt == 2) st = gemm_passes<128, 64, 12, 2, true>(s, dtype, layout, g, x, ldx, m, k, y);
-        else st = tn == 256 ? gemm_passes<256, 64, 6, 1, true>(s, dtype, layout, g, x, ldx, m, k, y) : gemm_passes<128, 64, 12, 1, true>(s, dtype, layout, g, x, ldx, m, k, y);
+        // more activation stages than these in flight slow the weight loads down by more than they hide
+        if (rt == 2) st = gemm_passes<128, 64, 8, 2, true>(s, dtype, layout, g, x, ldx, m, k, y);   // 2 x 128 accumulator columns + 4 weight stages
+        else st = tn == 256 ? gemm_passes<256, 64, 6, 1, true>(s, dtype, layout, g, x, ldx, m, k, y) : gemm_passes<128, 64, 8, 1, true>(s, dtype, layout, g, x, ldx, m, k, y);
     } else if (rt == 2) {
         st = tn == 256 ? gemm_passes<256, 64, 3, 2, false>(s, dtype, layout, g, x, ldx, m, k, y) : gemm_passes<128, 64, 4, 2, false>(s, dtype, layout, g, x, ldx, m, k, y);
     } else {
