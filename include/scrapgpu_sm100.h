@@ -201,13 +201,26 @@ SM100_API int sm100_attention(sm100_stream_t s, const float * q, const float * k
                               int64_t mask_heads, float * out, int64_t d, int64_t dv, int64_t nq, int64_t nk, int64_t hq,
                               int64_t hkv, int causal, int64_t offset, const int32_t * positions, float scale);
 
+/* sm100_attention over a KV cache, with one promise from the caller that lets the key/value rows be requested while the
+ * launch that precedes this call in the stream is still finishing: of each query's visible keys only the last
+ * fresh_keys (>= 0) may be written by that preceding launch; every earlier K/V row, and positions[0], were written
+ * by work that completed before the preceding launch began to run.  (Every kernel of this library, and any kernel
+ * launched without programmatic dependent launch, begins only after its own predecessors have completed, so "the
+ * launch before" is the only one that can still be running.)  In a decode step the promise holds with
+ * fresh_keys = 1: the launch before the attention stores the new token's K and V (SET_ROWS / SET_ROWS_PAIR,
+ * include/scrapgpu/op.h:43-47), all older rows date from earlier tokens.  Same values as sm100_attention; with the
+ * promise broken the result is undefined.  This entry has no counterpart in the reference. */
+SM100_API int sm100_attention_kvcache(sm100_stream_t s, const float * q, const float * k, const float * v, const float * mask,
+                                      int64_t mask_heads, float * out, int64_t d, int64_t dv, int64_t nq, int64_t nk,
+                                      int64_t hq, int64_t hkv, int causal, int64_t offset, const int32_t * positions,
+                                      float scale, int fresh_keys);
 
 /* sm100_attention for callers that cannot allocate device memory at call time (a host whose HBM is fully claimed
  * by its own pools, a latency-critical thread that must stay off the driver's allocator, an externally enforced
  * memory budget).  Same arguments and values as sm100_attention; the split-key partials go to a fixed 4 MiB array
  * inside the library image (every GPU that loads the library holds it until exit) instead of a scratch buffer
  * allocated on demand.  Shapes whose partials exceed sm100_attention_static_capacity() bytes
- * (nq * hq * splits * (dv + 2) floats) are refused with UNSUPPORTED.  The first call on a device looks the array's
+ * (nq * hq * splits * (dv + 4) floats) are refused with UNSUPPORTED.  The first call on a device looks the array's
  * address up: make it before any stream capture.  All calls on one device share the array, so calls that overlap
  * on the GPU race.  This entry has no counterpart in the reference. */
 SM100_API int sm100_attention_static(sm100_stream_t s, const float * q, const float * k, const float * v, const float * mask,

@@ -28,6 +28,10 @@ struct AttnArgs {
     int64_t d, dv, nq, nk, hq, hkv, offset;
     int64_t mask_heads;
     int splits, chunk, causal;
+    // KV-cache calls: the last `fresh_keys` visible keys of a query may have been written by the kernel that precedes
+    // this one in the stream, every earlier key (and `positions`) is older than that kernel, so those rows can be
+    // requested before the dependency wait.  -1: no such promise, everything is read after the wait.
+    int fresh_keys;
     float scale;
 };
 
@@ -329,9 +333,6 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_fast_kernel(AttnArgs a) {
     long long t_prev_ = clock64();
     if (threadIdx.x == 0) atomicAdd(&g_att_t[6], 1ull);
 #endif
-    pdl_wait();
-    pdl_launch_dependents();
-    ATT_T(0)
     constexpr int D = 128 * D4;
     extern __shared__ __align__(16) float smem[];   // [8 warps][G][ATT_HDR + D]
     constexpr int SROW = ATT_HDR + D;
@@ -342,6 +343,14 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_fast_kernel(AttnArgs a) {
     const int64_t hk = blockIdx.y, q = blockIdx.z;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     constexpr int NW = ATT_THREADS / 32;
+    // A warp takes NKB consecutive keys per trip: their K and V rows are requested together, the G x NKB partial
+    // dot products are reduced over the lanes with a halving exchange (NV values cost NV - 1 + log2(32 / NV)
+    // shuffles instead of 5 NV) and handed to all lanes through the warp's own shared-memory slot.
+    constexpr int NKB = D4 == 1 ? 4 : 2;
+    constexpr int NV = G * NKB;
+
+    const bool early = a.fresh_keys >= 0;   // warp-uniform: see AttnArgs
+    if (!early) pdl_wait();
 
     // the visible keys (known only on the device when the offset comes from `positions`) are spread evenly over the splits
     const int64_t n_vis = visible_keys(a, q);
@@ -349,6 +358,38 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_fast_kernel(AttnArgs a) {
     const int64_t k0 = (int64_t) split * chunk;
     const int64_t k1 = k0 + chunk < n_vis ? k0 + chunk : n_vis;
     const int count = k1 > k0 ? (int) (k1 - k0) : 0;
+    const float4 * kbase = reinterpret_cast<const float4 *>(a.k + (hk * a.nk + k0) * D) + lane;
+    const float4 * vbase = reinterpret_cast<const float4 *>(a.v + (hk * a.nk + k0) * D) + lane;
+
+    float4 kv[NKB][D4], vv[NKB][D4];
+    int kb = warp * NKB;
+    if (early) {
+        // the first trip's stable rows are on their way while the preceding kernel finishes
+        const int64_t stable = n_vis - a.fresh_keys - k0;   // keys of this split below this index are stable
+#pragma unroll
+        for (int j = 0; j < NKB; ++j) {
+            const bool in = kb + j < count && kb + j < stable;
+#pragma unroll
+            for (int i = 0; i < D4; ++i) {
+                kv[j][i] = in ? kbase[(int64_t) (kb + j) * (D / 4) + 32 * i] : make_float4(0.f, 0.f, 0.f, 0.f);
+                vv[j][i] = in ? vbase[(int64_t) (kb + j) * (D / 4) + 32 * i] : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+        }
+        pdl_wait();
+#pragma unroll
+        for (int j = 0; j < NKB; ++j) {
+            const bool in = kb + j < count && kb + j >= stable;
+            if (in) {
+#pragma unroll
+                for (int i = 0; i < D4; ++i) {
+                    kv[j][i] = kbase[(int64_t) (kb + j) * (D / 4) + 32 * i];
+                    vv[j][i] = vbase[(int64_t) (kb + j) * (D / 4) + 32 * i];
+                }
+            }
+        }
+    }
+    pdl_launch_dependents();
+    ATT_T(0)
 
     float4 qr[G][D4];
 #pragma unroll
@@ -365,25 +406,21 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_fast_kernel(AttnArgs a) {
 #pragma unroll
         for (int i = 0; i < D4; ++i) o[g][i] = make_float4(0.f, 0.f, 0.f, 0.f);
     }
-    const float4 * kbase = reinterpret_cast<const float4 *>(a.k + (hk * a.nk + k0) * D) + lane;
-    const float4 * vbase = reinterpret_cast<const float4 *>(a.v + (hk * a.nk + k0) * D) + lane;
-    // A warp takes NKB consecutive keys per trip: their K and V rows are requested together, the G x NKB partial
-    // dot products are reduced over the lanes with a halving exchange (NV values cost NV - 1 + log2(32 / NV)
-    // shuffles instead of 5 NV) and handed to all lanes through the warp's own shared-memory slot.
-    constexpr int NKB = D4 == 1 ? 4 : 2;
-    constexpr int NV = G * NKB;
     float * my_scores = smem + warp * G * SROW;   // first NV floats of the area this warp fills after the loop
-    for (int kb = warp * NKB; kb < count; kb += NW * NKB) {
-        float4 kv[NKB][D4], vv[NKB][D4];
+    bool have = early;   // the first trip's rows are already requested
+    for (; kb < count; kb += NW * NKB) {
+        if (!have) {
 #pragma unroll
-        for (int j = 0; j < NKB; ++j) {
-            const bool in = kb + j < count;
+            for (int j = 0; j < NKB; ++j) {
+                const bool in = kb + j < count;
 #pragma unroll
-            for (int i = 0; i < D4; ++i) {
-                kv[j][i] = in ? kbase[(int64_t) (kb + j) * (D / 4) + 32 * i] : make_float4(0.f, 0.f, 0.f, 0.f);
-                vv[j][i] = in ? vbase[(int64_t) (kb + j) * (D / 4) + 32 * i] : make_float4(0.f, 0.f, 0.f, 0.f);
+                for (int i = 0; i < D4; ++i) {
+                    kv[j][i] = in ? kbase[(int64_t) (kb + j) * (D / 4) + 32 * i] : make_float4(0.f, 0.f, 0.f, 0.f);
+                    vv[j][i] = in ? vbase[(int64_t) (kb + j) * (D / 4) + 32 * i] : make_float4(0.f, 0.f, 0.f, 0.f);
+                }
             }
         }
+        have = false;
         float part[NV];
 #pragma unroll
         for (int g = 0; g < G; ++g)
@@ -619,14 +656,15 @@ void attention_plan(AttnArgs & a) {
 
 using namespace sm100;
 
-extern "C" int sm100_attention(sm100_stream_t s, const float * q, const float * k, const float * v, const float * mask, int64_t mask_heads,
-                               float * out, int64_t d, int64_t dv, int64_t nq, int64_t nk, int64_t hq, int64_t hkv, int causal,
-                               int64_t offset, const int32_t * positions, float scale) {
+static int attention_entry(sm100_stream_t s, const float * q, const float * k, const float * v, const float * mask, int64_t mask_heads,
+                           float * out, int64_t d, int64_t dv, int64_t nq, int64_t nk, int64_t hq, int64_t hkv, int causal, int64_t offset,
+                           const int32_t * positions, float scale, int fresh_keys) {
     AttnArgs a = {};
     a.q = q; a.k = k; a.v = v; a.mask = mask; a.out = out; a.positions = positions;
     a.d = d; a.dv = dv; a.nq = nq; a.nk = nk; a.hq = hq; a.hkv = hkv; a.offset = offset;
     a.mask_heads = mask_heads <= 1 ? 1 : mask_heads;
     a.causal = causal; a.scale = scale;
+    a.fresh_keys = fresh_keys;
     const int st = attention_check(a);
     if (st != ST_OK) return st;
     attention_plan(a);
@@ -635,6 +673,20 @@ extern "C" int sm100_attention(sm100_stream_t s, const float * q, const float * 
     if (sw != ST_OK) return sw;
     return attention_launch((cudaStream_t) s, a, ws);
 }
+
+extern "C" int sm100_attention(sm100_stream_t s, const float * q, const float * k, const float * v, const float * mask, int64_t mask_heads,
+                               float * out, int64_t d, int64_t dv, int64_t nq, int64_t nk, int64_t hq, int64_t hkv, int causal,
+                               int64_t offset, const int32_t * positions, float scale) {
+    return attention_entry(s, q, k, v, mask, mask_heads, out, d, dv, nq, nk, hq, hkv, causal, offset, positions, scale, -1);
+}
+
+extern "C" int sm100_attention_kvcache(sm100_stream_t s, const float * q, const float * k, const float * v, const float * mask,
+                                       int64_t mask_heads, float * out, int64_t d, int64_t dv, int64_t nq, int64_t nk, int64_t hq, int64_t hkv,
+                                       int causal, int64_t offset, const int32_t * positions, float scale, int fresh_keys) {
+    if (fresh_keys < 0) return sm100::fail(sm100::ST_INVALID, "attention (KV cache): fresh_keys must not be negative");
+    return attention_entry(s, q, k, v, mask, mask_heads, out, d, dv, nq, nk, hq, hkv, causal, offset, positions, scale, fresh_keys);
+}
+
 
 
 // ---------------------------------------------------------------------------------------------------------
@@ -686,6 +738,7 @@ extern "C" int sm100_attention_static(sm100_stream_t s, const float * q, const f
     a.d = d; a.dv = dv; a.nq = nq; a.nk = nk; a.hq = hq; a.hkv = hkv; a.offset = offset;
     a.mask_heads = mask_heads <= 1 ? 1 : mask_heads;
     a.causal = causal; a.scale = scale;
+    a.fresh_keys = -1;
     const int st = attention_check(a);
     if (st != ST_OK) return st;
     attention_plan(a);

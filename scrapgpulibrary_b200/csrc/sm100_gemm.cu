@@ -554,6 +554,9 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc(const GemmArgs g) {
 #endif
             }
         }
+        // the dependency wait (long satisfied: the activations have been flowing) comes before the successor is
+        // released, as in every kernel of this library: a successor's early section then overlaps this kernel only
+        pdl_wait();
         pdl_launch_dependents();
 #ifdef SM100_GEMM_TIMING
         if (warp == FIRST_PRODUCER) { GT_PUT(2, clock64() - gt_go); GT_PUT(3, gt_wait); }
@@ -562,7 +565,6 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc(const GemmArgs g) {
 
         // ---- epilogue: a warp may read the TMEM lanes 32 (warp % 4) ..; four consecutive producer warps cover
         // the four lane quarters, and each such set takes a quarter of the columns ----
-        pdl_wait();
         bool acc_ok = alive;
         if (acc_ok) {
             acc_ok = mbar_try_wait(smem_addr(&sm.accum), 0u);

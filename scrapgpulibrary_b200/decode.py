@@ -265,8 +265,9 @@ class DecodeModel:
             chk(L.sm100_head_post(s, _dev(self.q), _dev(self.k), _dev(self.v), _dev(lw["q_norm"]) if c.qk_norm else None,
                                   _dev(lw["k_norm"]) if c.qk_norm else None, _dev(self.pos), _dev(self.rope), 0, c.n_ctx, _dev(lw["k_cache"]),
                                   _dev(lw["v_cache"]), c.head_dim, self.hq, self.hkv, c.n_ctx, c.eps, c.rope_base, 1), "head_post")
-            chk(L.sm100_attention(s, _dev(self.q), _dev(lw["k_cache"]), _dev(lw["v_cache"]), None, 1, _dev(self.att), c.head_dim, c.head_dim, 1, c.n_ctx,
-                                  self.hq, self.hkv, 1, 0, _dev(self.pos), scale), "attention")
+            # only the row that head_post has just stored is newer than the preceding kernel: the older rows are requested early
+            chk(L.sm100_attention_kvcache(s, _dev(self.q), _dev(lw["k_cache"]), _dev(lw["v_cache"]), None, 1, _dev(self.att), c.head_dim, c.head_dim,
+                                          1, c.n_ctx, self.hq, self.hkv, 1, 0, _dev(self.pos), scale, 1), "attention")
             self._mm(lw["wo"], self.att, self.proj)
             self._reduce(self.proj)
             if self.fuse:

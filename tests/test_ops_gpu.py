@@ -300,3 +300,46 @@ def test_attention_single_pass_kernel(sm100, stream, hq, hkv, d, nk, nq):
     mask[0, :, nk // 3:] = -np.inf
     got = run_attention(sm100, stream, q, k, v, False, 0, s, mask=mask, mask_heads=1)
     assert sgref.nmse(got, sgref.attention(q, k[:, :nk // 3], v[:, :nk // 3], False, 0, s)) <= TOL
+
+
+def test_attention_kvcache_entry(sm100, stream):
+    """The KV-cache entry requests the older rows before its dependency wait.  Each round first stores the new
+    token's K and V rows with SET_ROWS (the launch right before the attention, as in a decode step), then attends
+    with fresh_keys = 1; the values must be those of the plain entry and of the oracle, round after round (a
+    stale row would show as the previous round's values)."""
+    hq, hkv, d, n_ctx = 32, 8, 128, 1152
+    lib = sm100.lib()
+    rng = np.random.default_rng(21)
+    start = 1024
+    k = np.zeros((hkv, n_ctx, d), np.float32)
+    v = np.zeros((hkv, n_ctx, d), np.float32)
+    k[:, :start] = rng.standard_normal((hkv, start, d))
+    v[:, :start] = rng.standard_normal((hkv, start, d))
+    kb, vb = U.to_device(sm100, stream, k), U.to_device(sm100, stream, v)
+    ob = sm100.Buffer(hq * d * 4)
+    scale = float(1.0 / np.sqrt(d))
+    for t in range(6):
+        pos = start + t
+        q = rng.standard_normal((hq, 1, d)).astype(np.float32)
+        k_new = (10.0 * rng.standard_normal((hkv, 1, d))).astype(np.float32)   # large: the new key dominates the softmax
+        v_new = rng.standard_normal((hkv, 1, d)).astype(np.float32)
+        k[:, pos], v[:, pos] = k_new[:, 0], v_new[:, 0]
+        qb, knb, vnb = (U.to_device(sm100, stream, a) for a in (q, k_new, v_new))
+        pb = U.to_device(sm100, stream, np.array([pos], np.int32))
+        stream.sync()
+        sm100.check(lib.sm100_set_rows(stream.handle, knb.at(), pb.at(), kb.at(), d, 1, hkv, n_ctx), "set_rows k")
+        sm100.check(lib.sm100_set_rows(stream.handle, vnb.at(), pb.at(), vb.at(), d, 1, hkv, n_ctx), "set_rows v")
+        sm100.check(lib.sm100_attention_kvcache(stream.handle, qb.at(), kb.at(), vb.at(), None, 1, ob.at(), d, d, 1, n_ctx, hq, hkv, 1, 0, pb.at(),
+                                                scale, 1), "attention_kvcache")   # one fresh key: its V row comes from the launch right before
+        stream.sync()
+        got = ob.download(stream, np.float32, hq * d).reshape(hq, 1, d)
+        want = sgref.attention(q, k, v, True, pos, scale)
+        assert sgref.nmse(got, want) <= TOL, t
+        plain = run_attention(sm100, stream, q, k, v, True, pos, scale)
+        assert np.array_equal(got, plain), t
+        for b in (qb, knb, vnb, pb):
+            b.free()
+    st = lib.sm100_attention_kvcache(stream.handle, ob.at(), kb.at(), vb.at(), None, 1, ob.at(), d, d, 1, n_ctx, hq, hkv, 1, 0, None, scale, -1)
+    assert st == 2
+    for b in (kb, vb, ob):
+        b.free()
