@@ -90,6 +90,9 @@ SM100_API int sm100_allreduce_destroy(sm100_allreduce_t ctx);
 SM100_API int sm100_event_create(sm100_event_t * out);
 SM100_API int sm100_event_destroy(sm100_event_t e);
 SM100_API int sm100_event_record(sm100_event_t e, sm100_stream_t s);
+/* work enqueued on s after this call starts only when the work recorded in e has completed (the backend's streams
+ * are in-order, include/scrapgpu/stream.h:10-12; this is the edge between two of them: copies on one, kernels on another) */
+SM100_API int sm100_stream_wait_event(sm100_stream_t s, sm100_event_t e);
 SM100_API int sm100_event_sync(sm100_event_t e);
 SM100_API int sm100_event_elapsed_ms(sm100_event_t start, sm100_event_t stop, float * ms);
 SM100_API int sm100_graph_begin(sm100_stream_t s);

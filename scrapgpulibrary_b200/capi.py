@@ -47,6 +47,7 @@ def lib() -> C.CDLL:
         L.sm100_event_create.argtypes = [pv]
         L.sm100_event_destroy.argtypes = [vp]
         L.sm100_event_record.argtypes = [vp, vp]
+        L.sm100_stream_wait_event.argtypes = [vp, vp]
         L.sm100_event_sync.argtypes = [vp]
         L.sm100_event_elapsed_ms.argtypes = [vp, vp, C.POINTER(C.c_float)]
         L.sm100_graph_begin.argtypes = [vp]
@@ -125,6 +126,10 @@ class Stream:
 
     def sync(self) -> None:
         check(lib().sm100_stream_sync(self.handle), "stream_sync")
+
+    def wait(self, event: "Event") -> None:
+        """Later work on this stream starts only after the work recorded in `event` (on another stream) is done."""
+        check(lib().sm100_stream_wait_event(self.handle, event.handle), "stream_wait_event")
 
     def close(self) -> None:
         if self.handle:

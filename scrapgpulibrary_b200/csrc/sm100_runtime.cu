@@ -244,6 +244,11 @@ int sm100_event_record(sm100_event_t e, sm100_stream_t s) {
     return ST_OK;
 }
 
+int sm100_stream_wait_event(sm100_stream_t s, sm100_event_t e) {
+    SM100_CUDA(cudaStreamWaitEvent((cudaStream_t) s, (cudaEvent_t) e, 0));
+    return ST_OK;
+}
+
 int sm100_event_sync(sm100_event_t e) {
     SM100_CUDA(cudaEventSynchronize((cudaEvent_t) e));
     return ST_OK;
