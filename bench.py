@@ -11,9 +11,9 @@ metric = algorithmic GB/s = sum over launches of (N*K*0.5625 + 4*K + 4*N) bytes 
   value      launches replayed from one CUDA graph, inputs resident in HBM, CUDA-event timing on the
              launching stream
   e2e        the same pass driven call by call with HOST activations: per matvec a pinned host->device copy
-             of x, the kernel, a device->host copy of y - the copies on two streams of their own beside the
-             kernels' stream, tied by events - and a sync per step (weights stay resident, as they do after
-             scrapgpu_tensor_upload in the reference's usage)
+             of x, the kernel, a device->host copy of y (sm100_hostpipe_mul_mat: the copies on two streams
+             of their own beside the kernels' stream, tied by events) and a sync per step (weights stay
+             resident, as they do after scrapgpu_tensor_upload in the reference's usage)
   roofline   achieved = algorithmic bytes per launch / mean launch duration (the same CUDA-event region),
              peak = measured HBM copy bandwidth of MEASURED_PEAKS.json (burst figure; fallback 6650 GB/s)
   cpu_baseline  the unmodified reference's CPU MUL_MAT (oracle/_ref, built from the reference's own sources) on
@@ -291,43 +291,30 @@ def run_ours(args, rank: int, world: int, local_rank: int):
             capi.check(L.sm100_host_alloc(4 * n, C.byref(p)), "host_alloc")
             hy[n] = p
 
-        # Three in-order streams: the copy of matvec i + 1's activations and the read-back of matvec i - 1's result
-        # run beside matvec i's kernel.  Every matvec of a step has its own device buffers, so the only edges are
-        # copy-in -> kernel -> copy-out (events); the step ends when the last result is on the host.
-        s_in, s_out = capi.Stream(), capi.Stream()
-        xd = [capi.Buffer(4 * pool[s]["k"]) for s, _ in order]
-        yd = [capi.Buffer(4 * pool[s]["n"]) for s, _ in order]
-        ev_in = [capi.Event() for _ in order]
-        ev_mm = [capi.Event() for _ in order]
+        # sm100_hostpipe_mul_mat: one call per matvec; inside it the copy of the activations, the kernel and the
+        # read-back of the result go to three in-order streams tied by events, so the copy of matvec i + 1 and the
+        # read-back of matvec i - 1 run beside matvec i's kernel.  A step ends when the last result is on the host.
+        pipe = capi.HostPipe(8, 4 * 12288, 4 * 12288)
+        s_first, s_last = pipe.stream(0), pipe.stream(2)
 
         def e2e_step():
-            for i, (s, layer) in enumerate(order):
+            for s, layer in order:
                 p = pool[s]
                 k, n = p["k"], p["n"]
-                L.sm100_memcpy_h2d(s_in.handle, xd[i].at(), hx[k], 4 * k, 0)
-                ev_in[i].record(s_in)
-                stream.wait(ev_in[i])
-                capi.mul_mat(stream, dtype, 1, p["mats"][layer], k, n, xd[i], 1, yd[i])
-                ev_mm[i].record(stream)
-                s_out.wait(ev_mm[i])
-                L.sm100_memcpy_d2h(s_out.handle, hy[n], yd[i].at(), 4 * n, 0)
-            s_out.sync()
-            stream.sync()   # reports a kernel fault, if any
+                pipe.mul_mat(dtype, 1, p["mats"][layer], k, n, hx[k], 1, hy[n])
+            pipe.sync()
 
         for _ in range(max(3, args.warmup)):
             e2e_step()
         e2e_steps = max(3, args.steps // 2)
         e0, e1 = capi.Event(), capi.Event()
-        e0.record(s_in)
+        e0.record(s_first)
         for _ in range(e2e_steps):
             e2e_step()
-        e1.record(s_out)
+        e1.record(s_last)
         e1.sync()
         e2e_ms = e0.elapsed_ms(e1) / e2e_steps
-        for b in xd + yd:
-            b.free()
-        s_in.close()
-        s_out.close()
+        pipe.close()
         h2d = sum(4 * pool[s]["k"] for s, _ in order)
         d2h = sum(4 * pool[s]["n"] for s, _ in order)
 
@@ -342,7 +329,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
                        "setup_s": round(setup_s, 1), "detail": detail, "decode": decode, "head_sharded": head},
             "gpu_launches": int(launches_timed),
             "e2e": {"value": round(world * step_bytes / (e2e_ms * 1e-3) / 1e9, 1), "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                    "ms_per_step": round(e2e_ms, 4), "note": "host activations in / host results out per matvec (copies on their own streams beside the kernels), weights resident"},
+                    "ms_per_step": round(e2e_ms, 4), "note": "host activations in / host results out per matvec through sm100_hostpipe_mul_mat (copies on their own streams beside the kernels), weights resident"},
             "roofline": {"bound": "hbm", "kernel": "matvec_q4k_imma<1,2,true,1>", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
                          "frac": round(achieved / peak, 4), "peak_source": peak_src, "bytes_per_launch": round(per_launch_bytes, 1),
                          "us_per_launch": round(per_launch_us, 3),

@@ -128,6 +128,22 @@ SM100_API int sm100_pack_device_range(sm100_stream_t s, int dtype, int64_t k, in
  *      dequantize-and-dot matvec; larger m takes the tensor-core GEMM. ---- */
 SM100_API int sm100_mul_mat(sm100_stream_t s, int dtype, int layout, const void * w, int64_t w_row_stride, int64_t k,
                             int64_t n, const float * x, int64_t ldx, int64_t m, float * y, int64_t ldy);
+/* MUL_MAT with activations and results in HOST memory, one call per product and no host synchronisation in between:
+ * what a caller of the reference does with scrapgpu_tensor_upload -> op_execute -> scrapgpu_tensor_download
+ * (include/scrapgpu/tensor.h:45-53), as a pipeline.  A pipe owns three in-order streams and `depth` slots of device
+ * staging (max_x_bytes of activations, max_y_bytes of results each): the copy of the next product's activations and
+ * the read-back of the previous product's result run beside the current product's kernel.  host_x [k * m] and
+ * host_y [n * m] are dense f32 (column stride k and n); they must stay untouched until sm100_hostpipe_sync returns,
+ * and should be pinned (sm100_host_alloc) so that the copies overlap.  w is a device pointer as for sm100_mul_mat.
+ * sm100_hostpipe_stream hands out the pipe's streams (0 copy-in, 1 kernels, 2 read-back), e.g. to time a region with
+ * events.  One pipe is used from one thread at a time.  These entries have no counterpart in the reference. */
+typedef struct sm100_hostpipe_s * sm100_hostpipe_t;
+SM100_API int sm100_hostpipe_create(int device, int depth, size_t max_x_bytes, size_t max_y_bytes, sm100_hostpipe_t * out);
+SM100_API int sm100_hostpipe_destroy(sm100_hostpipe_t pipe);
+SM100_API int sm100_hostpipe_stream(sm100_hostpipe_t pipe, int which, sm100_stream_t * out);
+SM100_API int sm100_hostpipe_mul_mat(sm100_hostpipe_t pipe, int dtype, int layout, const void * w, int64_t w_row_stride,
+                                     int64_t k, int64_t n, const float * host_x, int64_t m, float * host_y);
+SM100_API int sm100_hostpipe_sync(sm100_hostpipe_t pipe);
 /* MUL_MAT_MULTI (include/scrapgpu/op.h:46, src/backends/opencl11/kernels/mul_mv_multi.cl:46-104):
  * up to 3 weight tensors sharing one activation column, one launch */
 SM100_API int sm100_mul_mat_multi(sm100_stream_t s, int count, const int * dtypes, const int * layouts,

@@ -63,6 +63,11 @@ def lib() -> C.CDLL:
         L.sm100_pack_device.argtypes = [vp, i32, i64, i64, vp, vp]
         L.sm100_unpack_device.argtypes = [vp, i32, i64, i64, vp, vp]
         L.sm100_mul_mat.argtypes = [vp, i32, i32, vp, i64, i64, i64, vp, i64, i64, vp, i64]
+        L.sm100_hostpipe_create.argtypes = [i32, i32, sz, sz, pv]
+        L.sm100_hostpipe_destroy.argtypes = [vp]
+        L.sm100_hostpipe_stream.argtypes = [vp, i32, pv]
+        L.sm100_hostpipe_mul_mat.argtypes = [vp, i32, i32, vp, i64, i64, i64, vp, i64, vp]
+        L.sm100_hostpipe_sync.argtypes = [vp]
         L.sm100_head_post.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, vp, vp, i64, i64, i64, i64, C.c_float, C.c_float, i32]
         L.sm100_ipc_handle_bytes.restype = sz
         L.sm100_ipc_export.argtypes = [vp, vp]
@@ -134,6 +139,36 @@ class Stream:
     def close(self) -> None:
         if self.handle:
             lib().sm100_stream_destroy(self.device, self.handle)
+            self.handle = None
+
+
+class HostPipe:
+    """MUL_MAT with host activations in and host results out, one call per product (sm100_hostpipe_*): copies and
+    kernels on three streams of the pipe's own.  Host pointers are raw addresses of pinned memory."""
+
+    def __init__(self, depth: int, max_x_bytes: int, max_y_bytes: int, device: int | None = None):
+        self.device = _DEFAULT_DEVICE if device is None else device
+        h = C.c_void_p()
+        check(lib().sm100_hostpipe_create(self.device, depth, max_x_bytes, max_y_bytes, C.byref(h)), "hostpipe_create")
+        self.handle = h
+
+    def stream(self, which: int) -> "Stream":
+        """0: copy-in, 1: kernels, 2: read-back.  A view: closing it is not the caller's business."""
+        h = C.c_void_p()
+        check(lib().sm100_hostpipe_stream(self.handle, which, C.byref(h)), "hostpipe_stream")
+        s = Stream.__new__(Stream)
+        s.device, s.handle = self.device, h
+        return s
+
+    def mul_mat(self, dtype: int, layout: int, w: "Buffer", k: int, n: int, host_x, m: int, host_y) -> None:
+        check(lib().sm100_hostpipe_mul_mat(self.handle, dtype, layout, w.at(), 0, k, n, host_x, m, host_y), "hostpipe_mul_mat")
+
+    def sync(self) -> None:
+        check(lib().sm100_hostpipe_sync(self.handle), "hostpipe_sync")
+
+    def close(self) -> None:
+        if self.handle:
+            lib().sm100_hostpipe_destroy(self.handle)
             self.handle = None
 
 

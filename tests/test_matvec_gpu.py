@@ -158,3 +158,41 @@ def test_mul_mat_fused_refuses_what_it_does_not_serve(sm100, stream):
     st = sm100.lib().sm100_mul_mat_fused(stream.handle, 2, a.at(), None, a.at(), 1e-6, None, None, 1, (C.c_int * 1)(U.Q4_K), (C.c_int * 1)(1),
                                          (C.c_void_p * 1)(w.ptr), k, (C.c_int64 * 1)(n), (C.c_void_p * 1)(y.ptr))
     assert st == 1   # UNSUPPORTED: the caller runs the separate ops
+
+
+def test_hostpipe_mul_mat_matches_device_path(sm100, stream):
+    """Host activations in, host results out, several products in flight over fewer slots than calls: every result
+    equals the device-resident call bit for bit (same kernels), for matvec and for a small batch."""
+    import ctypes as C
+    lib = sm100.lib()
+    k, n = 1024, 272
+    wq = U.quantize(U.Q4_K, U.seeded_weights(91, n, k))
+    wb = U.to_device(sm100, stream, sm100.pack(U.Q4_K, k, wq))
+    stream.sync()
+    calls = [(1, 3), (1, 4), (2, 5), (1, 6), (4, 7), (1, 8), (1, 9)]   # (m, seed)
+    pipe = sm100.HostPipe(3, 4 * k * 4, 4 * n * 4)
+    host = []
+    for m, seed in calls:
+        px, py = C.c_void_p(), C.c_void_p()
+        sm100.check(lib.sm100_host_alloc(4 * k * m, C.byref(px)), "host_alloc")
+        sm100.check(lib.sm100_host_alloc(4 * n * m, C.byref(py)), "host_alloc")
+        x = U.seeded_acts(seed, m, k)
+        C.memmove(px, x.ctypes.data, x.nbytes)
+        C.memset(py, 0xFF, 4 * n * m)
+        host.append((m, x, px, py))
+    for m, x, px, py in host:
+        pipe.mul_mat(U.Q4_K, U.PACKED, wb, k, n, px, m, py)
+    pipe.sync()
+    for m, x, px, py in host:
+        got = np.ctypeslib.as_array(C.cast(py, C.POINTER(C.c_float)), shape=(m * n,)).reshape(m, n).copy()
+        want = U.device_mul_mat(sm100, stream, U.Q4_K, U.PACKED, wq, k, x)
+        assert np.array_equal(got, want), m
+        assert sgref.nmse(got, sgref.mul_mat(U.Q4_K, wq, k, x)) <= 1e-6
+    # a product larger than the pipe's staging is refused, not truncated
+    st = lib.sm100_hostpipe_mul_mat(pipe.handle, U.Q4_K, U.PACKED, wb.at(), 0, k, n, host[0][2], 8, host[0][3])
+    assert st == 2
+    pipe.close()
+    for _, _, px, py in host:
+        lib.sm100_host_free(px)
+        lib.sm100_host_free(py)
+    wb.free()
