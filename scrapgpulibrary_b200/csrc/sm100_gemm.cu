@@ -16,14 +16,15 @@
 //
 //  2. gemm_tc       one CTA per 128 weight rows x TN tokens (TN = 128 or 256).  Warp 0 owns the tensor memory
 //                   and issues tcgen05.mma (kind::f16, 128 x TN x 16 per instruction, f32 accumulator of TN
-//                   TMEM columns), warp 1 issues the bulk copies of the B stages, warps 2-25 dequantize the
-//                   CTA's weight rows chunk by chunk to f16 (weights are multiplied by 256 to keep small
-//                   scales out of the f16 subnormals) - by default straight into tensor memory with
-//                   tcgen05.st, from where the MMA reads its A operand, so that shared memory carries the
-//                   activations only; optionally into shared-memory core matrices.  Weight stages and
-//                   activation stages are two rings with their own full/empty mbarriers; tcgen05.commit
-//                   hands both back.  When the last commit lands, warps 2-17 read the accumulator with
-//                   tcgen05.ld, undo the two scalings and store y.
+//                   TMEM columns), warps 1-3 issue the bulk copies of the B stages in turn (a warp gets one
+//                   bulk copy through per ~530 cycles), warps 4-27 dequantize the CTA's weight rows chunk by
+//                   chunk to f16 (weights are multiplied by 256 to keep small scales out of the f16
+//                   subnormals) - by default straight into tensor memory with tcgen05.st, from where the MMA
+//                   reads its A operand, so that shared memory carries the activations only; optionally
+//                   into shared-memory core matrices.  Weight stages and activation stages are two rings
+//                   with their own full/empty mbarriers; tcgen05.commit hands both back.  When the last
+//                   commit lands, warps 4-19 read the accumulator with tcgen05.ld, undo the two scalings
+//                   and store y.
 //
 // f16 operands with f32 accumulation: each product carries two roundings of 2^-11 relative size, which
 // puts the NMSE near 2e-7.  Every wait on an mbarrier is bounded; a CTA that gives up raises a fault flag
@@ -43,11 +44,12 @@ int device_scratch(int slot, size_t bytes, void ** out);
 namespace {
 
 constexpr int TM = 128;            // weight rows per CTA = rows of one tcgen05.mma = TMEM lanes
-// Warp roles.  The MMA warp is warp 0: the scheduler favours older warps, and a young MMA warp was starved
-// by the polling producers (each of its instructions took 50-80 cycles to issue).
+// Warp roles.  The MMA warp is warp 0: as a young warp it was starved by the polling producers (each of its
+// instructions took 50-80 cycles to issue).
 constexpr int WARP_MMA = 0;        // owns TMEM and issues the MMAs
-constexpr int WARP_BULK = 1;       // issues the bulk copies of the activation stages
-constexpr int FIRST_PRODUCER = 2;  // warps 2.. dequantize; the first 16 of them then run the epilogue
+constexpr int WARP_BULK = 1;       // warps 1-3 issue the bulk copies of the activation stages, a chunk each in turn
+constexpr int BULK_WARPS = 3;
+constexpr int FIRST_PRODUCER = 4;  // warps 4.. dequantize; the first 16 of them then run the epilogue
 // Producer warps: 8 warps = 256 (row, 32-weight block) tasks = one 64-wide chunk of the 128 rows, so 24 warps are three
 // groups that take the chunks in turn.  A producer's instruction stream is a dependent chain (~7 cycles per
 // instruction), so the third group buys throughput that the issue slots still have.
@@ -93,6 +95,18 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
         "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// non-blocking look at a barrier phase
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(ok)
         : "r"(bar), "r"(parity)
@@ -165,6 +179,39 @@ __device__ __forceinline__ void mma_f16_ta(uint32_t d_tmem, uint32_t a_tmem, uin
         "mov.b64 db, {%2, %3};\n\t"
         "@e tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t}" ::"r"(d_tmem),
         "r"(a_tmem), "r"(b_lo), "r"(desc_hi), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// The four MMAs of a 64-wide chunk (A in tensor memory) as one block of instructions: the issuing lane is given as a
+// flag, the descriptors and addresses of the K steps are derived inside.  `b_desc` is the whole 64-bit descriptor
+// of the first K step, `b_step` what a K step adds to it.
+__device__ __forceinline__ void mma4_f16_ta(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint64_t b_step, uint32_t idesc, uint32_t accumulate,
+                                            uint32_t issuer) {
+    asm volatile(
+        "{\n\t.reg .pred pi, pacc, pone;\n\t.reg .b64 d1, d2, d3;\n\t.reg .b32 a1, a2, a3;\n\t"
+        "elect.sync _|pi, 0xffffffff;\n\t"
+        "setp.ne.b32 pacc, %5, 0;\n\t"
+        "setp.eq.b32 pone, %6, %6;\n\t"
+        "add.u64 d1, %2, %3;\n\t"
+        "add.u64 d2, d1, %3;\n\t"
+        "add.u64 d3, d2, %3;\n\t"
+        "add.u32 a1, %1, 8;\n\t"
+        "add.u32 a2, %1, 16;\n\t"
+        "add.u32 a3, %1, 24;\n\t"
+        "@pi tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %4, pacc;\n\t"
+        "@pi tcgen05.mma.cta_group::1.kind::f16 [%0], [a1], d1, %4, pone;\n\t"
+        "@pi tcgen05.mma.cta_group::1.kind::f16 [%0], [a2], d2, %4, pone;\n\t"
+        "@pi tcgen05.mma.cta_group::1.kind::f16 [%0], [a3], d3, %4, pone;\n\t}" ::"r"(d_tmem),
+        "r"(a_tmem), "l"(b_desc), "l"(b_step), "r"(idesc), "r"(accumulate), "r"(issuer)
+        : "memory");
+}
+// two commits (weight stage, activation stage) by the issuing lane
+__device__ __forceinline__ void mma_commit2(uint32_t bar_a, uint32_t bar_b, uint32_t issuer) {
+    asm volatile(
+        "{\n\t.reg .pred pi;\n\t"
+        "elect.sync _|pi, 0xffffffff;\n\t"
+        "@pi tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t"
+        "@pi tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%1];\n\t}" ::"r"(bar_a),
+        "r"(bar_b), "r"(issuer)
         : "memory");
 }
 // 16 consecutive 32-bit columns of this thread's own TMEM lane (lane = base lane of the warp's quarter + lane id)
@@ -531,7 +578,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc(const GemmArgs g) {
                 if (!__all_sync(0xffffffffu, ok)) { alive = false; break; }
 #ifdef SM100_GEMM_TIMING
                 gt_wait += clock64() - gt_t;
-                if (gw == 0 && rt == 0) GT_TRACE(1, c);
+                (void) 0;
 #endif
                 if (ATM) {
                     tc_fence_after();   // the stage's previous MMAs (observed through the barrier) precede these stores
@@ -598,25 +645,31 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc(const GemmArgs g) {
 #ifdef SM100_GEMM_TIMING
         if (warp == FIRST_PRODUCER) { GT_PUT(4, clock64() - gt_t); GT_PUT(5, clock64() - gt_start); }
 #endif
-    } else if (warp == WARP_BULK) {
-        // ---- B operand: one bulk copy per stage, issued as soon as the stage is free ----
+    } else if (warp >= WARP_BULK) {
+        // ---- B operand: one bulk copy per stage, issued as soon as the stage is free.  A warp gets one bulk copy
+        // through per ~530 cycles whatever its size (measured: 16 KB copies from one thread 31 B/cycle, from four
+        // warps 113 B/cycle), so the chunks go round BULK_WARPS issuing warps. ----
         if (lane == 0) {
             pdl_wait();
             const uint8_t * src = reinterpret_cast<const uint8_t *>(g.xh) + (int64_t) mt * g.nchunks * Smem::B_BYTES;
-            int issued = 0, s = 0;
-            uint32_t phase = 0;
-            for (int c = 0; c < g.nchunks; ++c) {
+            int last = -1;
+            for (int c = warp - WARP_BULK; c < g.nchunks; c += BULK_WARPS) {
+                const int s = c % STAGES;
+                const uint32_t phase = (uint32_t) (c / STAGES) & 1u;
                 if (!mbar_try_wait(empty_b0 + 8 * s, phase ^ 1u) && !mbar_wait(empty_b0 + 8 * s, phase ^ 1u, abort_flag, 2)) break;
-                GT_TRACE(0, c);
+                if (warp == WARP_BULK) GT_TRACE(0, c);
                 mbar_expect_tx(full_b0 + 8 * s, Smem::B_BYTES);
                 bulk_g2s(b_smem + s * Smem::B_BYTES, src + (int64_t) c * Smem::B_BYTES, Smem::B_BYTES, full_b0 + 8 * s);
-                issued = c + 1;
-                if (++s == STAGES) { s = 0; phase ^= 1u; }
+                last = c;
             }
-            // copies still in flight must land before the CTA's shared memory goes away
-            for (int c = issued > STAGES ? issued - STAGES : 0; c < issued; ++c) {
-                const uint32_t bar = full_b0 + 8 * (c % STAGES);
-                for (uint32_t i = 0; i < WAIT_LIMIT && !mbar_try_wait(bar, (uint32_t) (c / STAGES) & 1u); ++i) __nanosleep(64);
+            // Every copy has landed once the MMA warp has passed its stage's barrier, which it does for every chunk
+            // before the CTA ends.  Only a CTA that is giving up can have copies in flight when it leaves: wait,
+            // briefly, for this warp's last ones so that they do not land in freed shared memory.
+            if (*abort_flag != 0) {
+                for (int c = last; c >= 0 && c > last - STAGES; c -= BULK_WARPS) {
+                    const uint32_t bar = full_b0 + 8 * (c % STAGES);
+                    for (uint32_t i = 0; i < (1u << 14) && !mbar_try_wait(bar, (uint32_t) (c / STAGES) & 1u); ++i) __nanosleep(64);
+                }
             }
         }
         __syncwarp();
@@ -629,45 +682,71 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc(const GemmArgs g) {
         const uint32_t a_lo0 = (a_smem >> 4) | ((uint32_t) (TM * 16) >> 4) << 16;  // start address | bytes between K halves
         const uint32_t b_lo0 = (b_smem >> 4) | ((uint32_t) (TN * 16) >> 4) << 16;
         bool alive = true;
+        const uint32_t issuer = lane == 0 ? 1u : 0u;   // the lane that issues the MMAs and the commits (always the same one)
         int sa = 0, sb = 0;                       // stage of the weight ring and of the activation ring
         uint32_t pa = 0, pb = 0, accumulate = 0;
+        // Both rings run several stages ahead, so the barriers of a chunk are almost always complete when this warp
+        // gets to it - but asking costs a round trip (~250 cycles per barrier for this lone warp, two thirds of
+        // the loop).  The look at chunk c + 1's barriers is therefore issued before chunk c's MMAs and its answer
+        // used an iteration later; only a "not yet" takes the waiting path.
+        uint32_t ready = (mbar_test_wait(full_b0, 0u) ? 1u : 0u) & (mbar_test_wait(full_a0, 0u) ? 1u : 0u);
         for (int c = 0; c < g.nchunks; ++c) {
 #ifdef SM100_GEMM_TIMING
             gt_t = clock64();
 #endif
-            bool ok = mbar_try_wait(full_b0 + 8 * sb, pb);
-            if (!ok) ok = mbar_wait(full_b0 + 8 * sb, pb, abort_flag, 3, false);
-            if (ok) {
-                ok = mbar_try_wait(full_a0 + 8 * sa, pa);
-                if (!ok) ok = mbar_wait(full_a0 + 8 * sa, pa, abort_flag, 4, false);
+            if (ready == 0u) {
+                bool ok = mbar_try_wait(full_b0 + 8 * sb, pb);
+                if (!ok) ok = mbar_wait(full_b0 + 8 * sb, pb, abort_flag, 3, false);
+                if (ok) {
+                    ok = mbar_try_wait(full_a0 + 8 * sa, pa);
+                    if (!ok) ok = mbar_wait(full_a0 + 8 * sa, pa, abort_flag, 4, false);
+                }
+                if (!__all_sync(0xffffffffu, ok)) { alive = false; break; }
+            } else {
+                GT_PUT(9, 1);    // development builds: chunks that were ready when looked at an iteration early
             }
-            if (!__all_sync(0xffffffffu, ok)) { alive = false; break; }
 #ifdef SM100_GEMM_TIMING
             gt_wait += clock64() - gt_t;
             GT_TRACE(3, c);
 #endif
             tc_fence_after();
+            // next chunk's stages
+            int sa_n = sa + 1, sb_n = sb + 1;
+            uint32_t pa_n = pa, pb_n = pb;
+            if (sa_n == SA) { sa_n = 0; pa_n ^= 1u; }
+            if (sb_n == STAGES) { sb_n = 0; pb_n ^= 1u; }
+            const uint32_t rb = mbar_test_wait(full_b0 + 8 * sb_n, pb_n) ? 1u : 0u;   // read after this chunk's MMAs are issued
+            const uint32_t ra = mbar_test_wait(full_a0 + 8 * sa_n, pa_n) ? 1u : 0u;
             {
                 const uint32_t a_lo = ATM ? 0u : a_lo0 + sa * (RT * Smem::A_BYTES >> 4), b_lo = b_lo0 + sb * (Smem::B_BYTES >> 4);
+                if (ATM && KC == 64) {
+                    const uint64_t b_desc = ((uint64_t) DESC_HI << 32) | b_lo;
 #pragma unroll
-                for (int rt = 0; rt < RT; ++rt) {
+                    for (int rt = 0; rt < RT; ++rt)
+                        mma4_f16_ta(tmem + rt * TN, tmem + ACC_COLS + (sa * RT + rt) * A_COLS, b_desc, (uint64_t) (2 * TN * 16 >> 4), IDESC, accumulate, issuer);
+                    accumulate = 1u;
+                    mma_commit2(empty_a0 + 8 * sa, empty_b0 + 8 * sb, issuer);   // each commit covers every MMA issued so far
+                } else {
 #pragma unroll
-                    for (int ks = 0; ks < KC / 16; ++ks) {
-                        if (ATM)
-                            mma_f16_ta(tmem + rt * TN, tmem + ACC_COLS + (sa * RT + rt) * A_COLS + ks * 8, b_lo + ks * (2 * TN * 16 >> 4), DESC_HI,
-                                       IDESC, ks == 0 ? accumulate : 1u);
-                        else
-                            mma_f16(tmem + rt * TN, a_lo + rt * (Smem::A_BYTES >> 4) + ks * (2 * TM * 16 >> 4), b_lo + ks * (2 * TN * 16 >> 4),
-                                    DESC_HI, IDESC, ks == 0 ? accumulate : 1u);
+                    for (int rt = 0; rt < RT; ++rt) {
+#pragma unroll
+                        for (int ks = 0; ks < KC / 16; ++ks) {
+                            if (ATM)
+                                mma_f16_ta(tmem + rt * TN, tmem + ACC_COLS + (sa * RT + rt) * A_COLS + ks * 8, b_lo + ks * (2 * TN * 16 >> 4), DESC_HI,
+                                           IDESC, ks == 0 ? accumulate : 1u);
+                            else
+                                mma_f16(tmem + rt * TN, a_lo + rt * (Smem::A_BYTES >> 4) + ks * (2 * TM * 16 >> 4), b_lo + ks * (2 * TN * 16 >> 4),
+                                        DESC_HI, IDESC, ks == 0 ? accumulate : 1u);
+                        }
                     }
+                    accumulate = 1u;
+                    mma_commit(empty_a0 + 8 * sa);   // each commit covers every MMA issued so far
+                    mma_commit(empty_b0 + 8 * sb);
                 }
-                accumulate = 1u;
-                mma_commit(empty_a0 + 8 * sa);   // each commit covers every MMA issued so far
-                mma_commit(empty_b0 + 8 * sb);
                 GT_TRACE(4, c);
             }
-            if (++sa == SA) { sa = 0; pa ^= 1u; }
-            if (++sb == STAGES) { sb = 0; pb ^= 1u; }
+            ready = c + 1 < g.nchunks ? (ra & rb) : 1u;
+            sa = sa_n; pa = pa_n; sb = sb_n; pb = pb_n;
         }
         __syncwarp();
 #ifdef SM100_GEMM_TIMING
