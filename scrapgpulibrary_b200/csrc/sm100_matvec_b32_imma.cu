@@ -64,40 +64,8 @@ __device__ __forceinline__ void bq_load(BqBlock<Q8> & b, const uint8_t * p) {
     }
 }
 
-// Shared memory of one CTA:
-//   xq   [K/32][2 planes][32 B]   quantized activations, natural order inside a block; 64 zero bytes follow
-//   xs   [K/32] float2            (s_b, 8 * sum of the block's integers as float - Q4_0's offset term)
-//   red  [warp][16 rows] float    partial outputs of the warps of one row tile
-template <bool Q8>
-__global__ void __launch_bounds__(BQ_THREADS, 1) matvec_b32_imma(BqArgs p) {
-    extern __shared__ __align__(16) uint8_t smem[];
-    uint32_t * xq = reinterpret_cast<uint32_t *>(smem);
-    float2 * xs = reinterpret_cast<float2 *>(smem + (size_t) p.blocks * 64 + 64);
-    float * red = reinterpret_cast<float *>(xs + p.blocks);
-    constexpr int BB = Q8 ? 32 : 16;   // quant bytes per block
-
-    const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
-    const int group = wid / BQ_WARPS, warp = wid % BQ_WARPS;
-    const int g = lane >> 2, t = lane & 3;
-    const int rt_step = gridDim.x * BQ_GROUPS;
-    const uint32_t row_bytes = (uint32_t) p.blocks * BB;
-
-    // first quad of weights: independent of the predecessor kernel
-    BqBlock<Q8> cur0, cur1, nxt0, nxt1;   // rows g and g + 8
-    uint32_t cur_d = 0, nxt_d = 0;
-    int rt = blockIdx.x * BQ_GROUPS + group, quad = warp;
-    auto load = [&](int rt_, int quad_, BqBlock<Q8> & b0, BqBlock<Q8> & b1, uint32_t & dd) {
-        const int blk = quad_ * 4 + t;
-        const uint8_t * q0 = p.w + ((int64_t) rt_ * 16 + g) * row_bytes + (uint32_t) blk * BB;
-        bq_load<Q8>(b0, q0);
-        bq_load<Q8>(b1, q0 + 8 * (int64_t) row_bytes);
-        const unsigned short * dp = reinterpret_cast<const unsigned short *>(p.w + p.d_off) + ((int64_t) rt_ * 16 + g) * p.blocks + blk;
-        dd = (uint32_t) __ldg(dp) | (uint32_t) __ldg(dp + 8 * (int64_t) p.blocks) << 16;
-    };
-    if (rt < p.n_tiles && quad < p.quads) load(rt, quad, cur0, cur1, cur_d);
-
-    pdl_wait();
-
+// activations -> 16-bit integers per 32-element block (shared by the kernels below); the caller synchronises the CTA
+__device__ __forceinline__ void bq_quantize_x(const BqArgs & p, uint32_t * xq, float2 * xs, int tid) {
     // activations -> 16-bit integers per 32-element block.  One item = 4 consecutive elements; the 8 items of a
     // block sit in 8 consecutive lanes.
     if (tid < 16) xq[p.blocks * 16 + tid] = 0u;
@@ -134,6 +102,43 @@ __global__ void __launch_bounds__(BQ_THREADS, 1) matvec_b32_imma(BqArgs p) {
             if (q == 0) xs[sb] = make_float2(some ? amax * (1.0f / 32512.0f) : 0.0f, 8.0f * (float) isum);
         }
     }
+}
+
+// Shared memory of one CTA:
+//   xq   [K/32][2 planes][32 B]   quantized activations, natural order inside a block; 64 zero bytes follow
+//   xs   [K/32] float2            (s_b, 8 * sum of the block's integers as float - Q4_0's offset term)
+//   red  [warp][16 rows] float    partial outputs of the warps of one row tile
+template <bool Q8>
+__global__ void __launch_bounds__(BQ_THREADS, 1) matvec_b32_imma(BqArgs p) {
+    extern __shared__ __align__(16) uint8_t smem[];
+    uint32_t * xq = reinterpret_cast<uint32_t *>(smem);
+    float2 * xs = reinterpret_cast<float2 *>(smem + (size_t) p.blocks * 64 + 64);
+    float * red = reinterpret_cast<float *>(xs + p.blocks);
+    constexpr int BB = Q8 ? 32 : 16;   // quant bytes per block
+
+    const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
+    const int group = wid / BQ_WARPS, warp = wid % BQ_WARPS;
+    const int g = lane >> 2, t = lane & 3;
+    const int rt_step = gridDim.x * BQ_GROUPS;
+    const uint32_t row_bytes = (uint32_t) p.blocks * BB;
+
+    // first quad of weights: independent of the predecessor kernel
+    BqBlock<Q8> cur0, cur1, nxt0, nxt1;   // rows g and g + 8
+    uint32_t cur_d = 0, nxt_d = 0;
+    int rt = blockIdx.x * BQ_GROUPS + group, quad = warp;
+    auto load = [&](int rt_, int quad_, BqBlock<Q8> & b0, BqBlock<Q8> & b1, uint32_t & dd) {
+        const int blk = quad_ * 4 + t;
+        const uint8_t * q0 = p.w + ((int64_t) rt_ * 16 + g) * row_bytes + (uint32_t) blk * BB;
+        bq_load<Q8>(b0, q0);
+        bq_load<Q8>(b1, q0 + 8 * (int64_t) row_bytes);
+        const unsigned short * dp = reinterpret_cast<const unsigned short *>(p.w + p.d_off) + ((int64_t) rt_ * 16 + g) * p.blocks + blk;
+        dd = (uint32_t) __ldg(dp) | (uint32_t) __ldg(dp + 8 * (int64_t) p.blocks) << 16;
+    };
+    if (rt < p.n_tiles && quad < p.quads) load(rt, quad, cur0, cur1, cur_d);
+
+    pdl_wait();
+
+    bq_quantize_x(p, xq, xs, tid);
     __syncthreads();
     pdl_launch_dependents();
 
@@ -196,10 +201,120 @@ __global__ void __launch_bounds__(BQ_THREADS, 1) matvec_b32_imma(BqArgs p) {
     }
 }
 
+// The same product with BQ_DEPTH steps (16 rows x 4 blocks each) of a warp in flight in registers instead of two: a
+// slot is refilled as soon as its step has been multiplied, and the first BQ_DEPTH steps are requested before the
+// dependency wait.  With two steps a CTA has 16 KB (Q4_0) on its way, which is half of what the HBM latency asks for.
+// Needs a whole number of BQ_DEPTH-step batches per warp and row tile: K a multiple of 128 * BQ_WARPS * BQ_DEPTH.
+constexpr int BQ_DEPTH = 4;
+
+template <bool Q8>
+__global__ void __launch_bounds__(BQ_THREADS, 1) matvec_b32_imma_deep(BqArgs p) {
+    extern __shared__ __align__(16) uint8_t smem[];
+    uint32_t * xq = reinterpret_cast<uint32_t *>(smem);
+    float2 * xs = reinterpret_cast<float2 *>(smem + (size_t) p.blocks * 64 + 64);
+    float * red = reinterpret_cast<float *>(xs + p.blocks);
+    constexpr int BB = Q8 ? 32 : 16;   // quant bytes per block
+
+    const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
+    const int group = wid / BQ_WARPS, warp = wid % BQ_WARPS;
+    const int g = lane >> 2, t = lane & 3;
+    const int rt_step = gridDim.x * BQ_GROUPS;
+    const uint32_t row_bytes = (uint32_t) p.blocks * BB;
+
+    BqBlock<Q8> s0[BQ_DEPTH], s1[BQ_DEPTH];   // rows g and g + 8 of the steps in flight
+    uint32_t sd[BQ_DEPTH];
+    auto load = [&](int rt_, int quad_, BqBlock<Q8> & b0, BqBlock<Q8> & b1, uint32_t & dd) {
+        const int blk = quad_ * 4 + t;
+        const uint8_t * q0 = p.w + ((int64_t) rt_ * 16 + g) * row_bytes + (uint32_t) blk * BB;
+        bq_load<Q8>(b0, q0);
+        bq_load<Q8>(b1, q0 + 8 * (int64_t) row_bytes);
+        const unsigned short * dp = reinterpret_cast<const unsigned short *>(p.w + p.d_off) + ((int64_t) rt_ * 16 + g) * p.blocks + blk;
+        dd = (uint32_t) __ldg(dp) | (uint32_t) __ldg(dp + 8 * (int64_t) p.blocks) << 16;
+    };
+    // load cursor: runs BQ_DEPTH steps ahead of the multiply over the same (row tile, quad) sequence
+    int lrt = blockIdx.x * BQ_GROUPS + group, lquad = warp;
+    auto advance = [&]() {
+        lquad += BQ_WARPS;
+        if (lquad >= p.quads) { lquad = warp; lrt += rt_step; }
+    };
+#pragma unroll
+    for (int i = 0; i < BQ_DEPTH; ++i) {
+        if (lrt < p.n_tiles) load(lrt, lquad, s0[i], s1[i], sd[i]);
+        advance();
+    }
+
+    pdl_wait();
+    bq_quantize_x(p, xq, xs, tid);
+    __syncthreads();
+    pdl_launch_dependents();
+
+    const bool live = t == (g >> 1);
+    const uint4 * xq_lane = reinterpret_cast<const uint4 *>(xq) + (live ? (t * 4 + (g & 1) * 2) : p.blocks * 4);
+    const uint32_t xq_step = live ? 16u : 0u;
+    float * my_red = red + group * (BQ_WARPS * 16);
+    const int gtid = tid - group * (BQ_WARPS * 32);
+
+    int rt = blockIdx.x * BQ_GROUPS + group;
+    for (int round = blockIdx.x * BQ_GROUPS; round < p.n_tiles; round += rt_step) {
+        float acc0 = 0.f, acc1 = 0.f;
+        if (rt < p.n_tiles) {
+            for (int quad = warp; quad < p.quads; quad += BQ_WARPS * BQ_DEPTH) {
+#pragma unroll
+                for (int i = 0; i < BQ_DEPTH; ++i) {
+                    const int q = quad + i * BQ_WARPS;
+                    const uint4 bx0 = xq_lane[(uint32_t) q * xq_step], bx1 = xq_lane[(uint32_t) q * xq_step + 1];
+                    const uint32_t blo[4] = {bx0.x, bx0.y, bx0.z, bx0.w}, bhi[4] = {bx1.x, bx1.y, bx1.z, bx1.w};
+                    int c[4] = {0, 0, 0, 0};
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        if (Q8) {
+                            bq_imma_s8(c, s0[i].w[j], s1[i].w[j], s0[i].w[4 + j], s1[i].w[4 + j], blo[j], bhi[j]);
+                        } else {
+                            bq_imma_u8(c, s0[i].w[j] & 0x0F0F0F0Fu, s1[i].w[j] & 0x0F0F0F0Fu, (s0[i].w[j] >> 4) & 0x0F0F0F0Fu,
+                                       (s1[i].w[j] >> 4) & 0x0F0F0F0Fu, blo[j], bhi[j]);
+                        }
+                    }
+                    const float2 sq = xs[q * 4 + t];
+                    const float2 dd = __half22float2(*reinterpret_cast<const __half2 *>(&sd[i]));
+                    float v0 = (float) (c[0] * 256 + c[1]), v1 = (float) (c[2] * 256 + c[3]);
+                    if (!Q8) { v0 -= sq.y; v1 -= sq.y; }
+                    acc0 = fmaf(dd.x * sq.x, v0, acc0);
+                    acc1 = fmaf(dd.y * sq.x, v1, acc1);
+                    // the slot is free: its step BQ_DEPTH ahead goes in
+                    if (lrt < p.n_tiles) load(lrt, lquad, s0[i], s1[i], sd[i]);
+                    advance();
+                }
+            }
+        }
+        acc0 += __shfl_xor_sync(0xffffffffu, acc0, 1);
+        acc0 += __shfl_xor_sync(0xffffffffu, acc0, 2);
+        acc1 += __shfl_xor_sync(0xffffffffu, acc1, 1);
+        acc1 += __shfl_xor_sync(0xffffffffu, acc1, 2);
+        if (t == 0) {
+            my_red[warp * 16 + g] = acc0;
+            my_red[warp * 16 + g + 8] = acc1;
+        }
+        __syncthreads();
+        if (gtid < 16 && rt < p.n_tiles) {
+            float v = 0.f;
+#pragma unroll
+            for (int w = 0; w < BQ_WARPS; ++w) v += my_red[w * 16 + gtid];
+            p.y[(int64_t) rt * 16 + gtid] = v;
+        }
+        __syncthreads();
+        rt += rt_step;
+    }
+}
+
 size_t bq_smem_bytes(int blocks) { return (size_t) blocks * 64 + 64 + (size_t) blocks * 8 + (size_t) BQ_WARPS * BQ_GROUPS * 16 * 4; }
 
 template <bool Q8>
 int launch_bq(cudaStream_t s, const BqArgs & a, size_t smem, int grid) {
+    static const int deep_ok = [] { const char * e = getenv("SM100_B32_DEEP"); return e != nullptr ? atoi(e) : 1; }();
+    if (deep_ok && a.quads % (BQ_WARPS * BQ_DEPTH) == 0) {
+        if (smem > 48 * 1024) SM100_CUDA(cudaFuncSetAttribute(matvec_b32_imma_deep<Q8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+        return launch(matvec_b32_imma_deep<Q8>, dim3((unsigned) grid), dim3(BQ_THREADS), smem, s, a);
+    }
     if (smem > 48 * 1024) SM100_CUDA(cudaFuncSetAttribute(matvec_b32_imma<Q8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
     return launch(matvec_b32_imma<Q8>, dim3((unsigned) grid), dim3(BQ_THREADS), smem, s, a);
 }

@@ -60,8 +60,9 @@ def test_k_order_cancellation(sm100, stream):
 
 
 @pytest.mark.parametrize("dtype,k,n", [(U.Q4_0, 4096, 4096), (U.Q4_K, 4096, 12288), (U.Q4_K, 12288, 4096),
-                                       (U.Q6_K, 4096, 4096), (U.Q8_0, 4096, 4096)],
-                         ids=["q4_0_4096x4096", "q4_k_4096x12288", "q4_k_12288x4096", "q6_k_4096x4096", "q8_0_4096x4096"])
+                                       (U.Q6_K, 4096, 4096), (U.Q8_0, 4096, 4096), (U.Q4_0, 4096, 9744), (U.Q8_0, 8192, 4800)],
+                         ids=["q4_0_4096x4096", "q4_k_4096x12288", "q4_k_12288x4096", "q6_k_4096x4096", "q8_0_4096x4096",
+                              "q4_0_4096x9744_three_rounds", "q8_0_8192x4800_two_rounds"])
 def test_matvec_benchmark_shapes(sm100, stream, dtype, k, n):
     """The benchmark's shapes: full comparison with the oracle at M = 1 and 8, plus linearity
     W(a + b) = Wa + Wb as a size-independent property."""
