@@ -514,9 +514,11 @@ int matvec(cudaStream_t s, int dtype, int layout, const void * w, int64_t w_row_
         }
     }
     static const int use_q6k = env_int("SM100_Q6K_IMMA", 1);
-    // measured: the tensor-core kernel wins on small tensors (4096 x 4096: 1.7 vs 1.25 TB/s), the streaming kernel on
-    // large ones (vocabulary head: 4.1 vs 2.1 TB/s), where its lower instruction count per byte pays
-    if (use_q6k && layout == LAYOUT_PACKED && dtype == DT_Q6_K && x_aligned && m == 1 && (use_q6k > 1 || n * k <= (int64_t) 20 << 20)) {
+    // measured: the tensor-core kernel wins on small tensors and on short rows (4096 x 4096: 1.9 vs 1.25 TB/s,
+    // 4096 x 12288: 2.45 vs 2.29), the streaming kernel on long rows and large tensors (12288 x 4096: 2.98 vs 2.35,
+    // vocabulary head: 4.1 vs 3.1 TB/s), where its lower instruction count per byte pays
+    const int64_t q6k_limit = k <= 4096 ? (int64_t) 64 << 20 : (int64_t) 20 << 20;
+    if (use_q6k && layout == LAYOUT_PACKED && dtype == DT_Q6_K && x_aligned && m == 1 && (use_q6k > 1 || n * k <= q6k_limit)) {
         bool handled = false;
         const int st = matvec_q6k_imma_tiles(s, w, k, n, x, y, &handled);
         if (st != ST_OK) return st;

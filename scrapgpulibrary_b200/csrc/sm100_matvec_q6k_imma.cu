@@ -47,6 +47,46 @@ struct SqPiece {
     uint32_t sc, d;   // the unit's four group scales; the block's f16 d
 };
 
+// activations -> 16-bit integers per 16-element group (shared by the kernels below); the caller synchronises the CTA
+__device__ __forceinline__ void sq_quantize_x(const SqArgs & p, uint32_t * xq, float2 * xs, int ngroups, int tid) {
+    // activations -> 16-bit integers per 16-element group.  One item = 4 consecutive elements; the 4 items of a
+    // group sit in 4 consecutive lanes.
+    if (tid < 8) xq[ngroups * 8 + tid] = 0u;
+    // all loads of a batch are issued before the first one is used: one L2 latency per batch, not per trip
+    constexpr int BATCH = 6;
+    for (int base = 0; base < ngroups * 4; base += BATCH * SQ_THREADS) {
+        float4 xv[BATCH];
+#pragma unroll
+        for (int i = 0; i < BATCH; ++i) {
+            const int it = base + i * SQ_THREADS + tid;
+            if (it < ngroups * 4) xv[i] = __ldcg(reinterpret_cast<const float4 *>(p.x) + it);   // coherent: the producer may still be running when this kernel starts
+        }
+#pragma unroll
+        for (int i = 0; i < BATCH; ++i) {
+            const int it = base + i * SQ_THREADS + tid;
+            if (it >= ngroups * 4) continue;   // warp-uniform: the item count is a multiple of 32
+            const float4 v = xv[i];
+            const int grp = it >> 2, q = it & 3;
+            float amax = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
+            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+            const bool some = amax > 1e-30f;   // below that the group counts as zero
+            const float inv = some ? __fdividef(32512.0f, amax) : 0.0f;
+            // round to nearest (even) without the conversion unit: 1.5 * 2^23 + x keeps the integer in the mantissa (|x| <= 32512)
+        const int x0 = __float_as_int(fmaf(v.x, inv, 12582912.0f)) - 0x4B400000, x1 = __float_as_int(fmaf(v.y, inv, 12582912.0f)) - 0x4B400000,
+                  x2 = __float_as_int(fmaf(v.z, inv, 12582912.0f)) - 0x4B400000, x3 = __float_as_int(fmaf(v.w, inv, 12582912.0f)) - 0x4B400000;
+            int isum = (x0 + x1) + (x2 + x3);
+            isum += __shfl_xor_sync(0xffffffffu, isum, 1);
+            isum += __shfl_xor_sync(0xffffffffu, isum, 2);
+            // 16-bit integer = 256 h + l with h, l signed bytes: h = (x + 128) >> 8, l = low byte of x
+            const int h0 = (x0 + 128) >> 8, h1 = (x1 + 128) >> 8, h2 = (x2 + 128) >> 8, h3 = (x3 + 128) >> 8;
+            xq[grp * 8 + q] = __byte_perm(__byte_perm((uint32_t) h0, (uint32_t) h1, 0x0040), __byte_perm((uint32_t) h2, (uint32_t) h3, 0x0040), 0x5410);
+            xq[grp * 8 + 4 + q] = __byte_perm(__byte_perm((uint32_t) x0, (uint32_t) x1, 0x0040), __byte_perm((uint32_t) x2, (uint32_t) x3, 0x0040), 0x5410);
+            if (q == 0) xs[grp] = make_float2(some ? amax * (1.0f / 32512.0f) : 0.0f, __int_as_float(32 * isum));
+        }
+    }
+}
+
 // Shared memory of one CTA:
 //   xq   [K/16][2 planes][16 B]   quantized activations, natural order inside a group; 32 zero bytes follow
 //   xs   [K/16] (float s, int 32 * sum of the group's integers)
@@ -86,42 +126,7 @@ __global__ void __launch_bounds__(SQ_THREADS, 1) matvec_q6k_imma(SqArgs p) {
 
     pdl_wait();
 
-    // activations -> 16-bit integers per 16-element group.  One item = 4 consecutive elements; the 4 items of a
-    // group sit in 4 consecutive lanes.
-    if (tid < 8) xq[ngroups * 8 + tid] = 0u;
-    // all loads of a batch are issued before the first one is used: one L2 latency per batch, not per trip
-    constexpr int BATCH = 6;
-    for (int base = 0; base < ngroups * 4; base += BATCH * SQ_THREADS) {
-        float4 xv[BATCH];
-#pragma unroll
-        for (int i = 0; i < BATCH; ++i) {
-            const int it = base + i * SQ_THREADS + tid;
-            if (it < ngroups * 4) xv[i] = __ldcg(reinterpret_cast<const float4 *>(p.x) + it);   // coherent: the producer may still be running when this kernel starts
-        }
-#pragma unroll
-        for (int i = 0; i < BATCH; ++i) {
-            const int it = base + i * SQ_THREADS + tid;
-            if (it >= ngroups * 4) continue;   // warp-uniform: the item count is a multiple of 32
-            const float4 v = xv[i];
-            const int grp = it >> 2, q = it & 3;
-            float amax = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
-            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-            const bool some = amax > 1e-30f;   // below that the group counts as zero
-            const float inv = some ? __fdividef(32512.0f, amax) : 0.0f;
-            // round to nearest (even) without the conversion unit: 1.5 * 2^23 + x keeps the integer in the mantissa (|x| <= 32512)
-        const int x0 = __float_as_int(fmaf(v.x, inv, 12582912.0f)) - 0x4B400000, x1 = __float_as_int(fmaf(v.y, inv, 12582912.0f)) - 0x4B400000,
-                  x2 = __float_as_int(fmaf(v.z, inv, 12582912.0f)) - 0x4B400000, x3 = __float_as_int(fmaf(v.w, inv, 12582912.0f)) - 0x4B400000;
-            int isum = (x0 + x1) + (x2 + x3);
-            isum += __shfl_xor_sync(0xffffffffu, isum, 1);
-            isum += __shfl_xor_sync(0xffffffffu, isum, 2);
-            // 16-bit integer = 256 h + l with h, l signed bytes: h = (x + 128) >> 8, l = low byte of x
-            const int h0 = (x0 + 128) >> 8, h1 = (x1 + 128) >> 8, h2 = (x2 + 128) >> 8, h3 = (x3 + 128) >> 8;
-            xq[grp * 8 + q] = __byte_perm(__byte_perm((uint32_t) h0, (uint32_t) h1, 0x0040), __byte_perm((uint32_t) h2, (uint32_t) h3, 0x0040), 0x5410);
-            xq[grp * 8 + 4 + q] = __byte_perm(__byte_perm((uint32_t) x0, (uint32_t) x1, 0x0040), __byte_perm((uint32_t) x2, (uint32_t) x3, 0x0040), 0x5410);
-            if (q == 0) xs[grp] = make_float2(some ? amax * (1.0f / 32512.0f) : 0.0f, __int_as_float(32 * isum));
-        }
-    }
+    sq_quantize_x(p, xq, xs, ngroups, tid);
     __syncthreads();
     pdl_launch_dependents();
 
@@ -191,6 +196,128 @@ __global__ void __launch_bounds__(SQ_THREADS, 1) matvec_q6k_imma(SqArgs p) {
     }
 }
 
+// The same product with SQ_DEPTH steps (16 rows x one 64-weight unit each) of a warp in flight in registers instead of
+// two, the first SQ_DEPTH requested before the dependency wait.  Needs whole batches: every warp's unit range a
+// multiple of SQ_DEPTH long.
+constexpr int SQ_DEPTH = 4;
+
+__global__ void __launch_bounds__(SQ_THREADS, 1) matvec_q6k_imma_deep(SqArgs p) {
+    extern __shared__ __align__(16) uint8_t smem[];
+    const int ngroups = p.units * 4;
+    uint32_t * xq = reinterpret_cast<uint32_t *>(smem);
+    float2 * xs = reinterpret_cast<float2 *>(smem + (size_t) ngroups * 32 + 32);
+    float * red = reinterpret_cast<float *>(xs + ngroups);
+
+    const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
+    const int group = wid / SQ_WARPS, warp = wid % SQ_WARPS;
+    const int g = lane >> 2, t = lane & 3;
+    const int rt_step = gridDim.x * SQ_GROUPS;
+    const int u_begin = warp * p.units_per_warp;
+    const int u_end = u_begin + p.units_per_warp < p.units ? u_begin + p.units_per_warp : p.units;
+    const uint32_t nib_shift = (uint32_t) (t >> 1) * 4u, hb_shift = (uint32_t) t * 2u, sc_shift = 24u - 8u * (uint32_t) t;
+
+    auto load = [&](int rt_, int unit, SqPiece & p0, SqPiece & p1) {
+        const int64_t blk0 = ((int64_t) rt_ * 16 + g) * p.blocks + (unit >> 2);   // block of row g
+        const int64_t blk1 = blk0 + 8 * (int64_t) p.blocks;                        // block of row g + 8
+        const int u = unit & 3;
+        p0.nib = ldg_stream(p.w + blk0 * 128 + u * 32 + (t & 1) * 16);
+        p1.nib = ldg_stream(p.w + blk1 * 128 + u * 32 + (t & 1) * 16);
+        p0.hb = __ldg(reinterpret_cast<const uint4 *>(p.w + p.x_off + blk0 * 64 + u * 16));
+        p1.hb = __ldg(reinterpret_cast<const uint4 *>(p.w + p.x_off + blk1 * 64 + u * 16));
+        p0.sc = __ldg(reinterpret_cast<const uint32_t *>(p.w + p.s_off + blk0 * 16 + u * 4));
+        p1.sc = __ldg(reinterpret_cast<const uint32_t *>(p.w + p.s_off + blk1 * 16 + u * 4));
+        p0.d = __ldg(reinterpret_cast<const unsigned short *>(p.w + p.d_off) + blk0);
+        p1.d = __ldg(reinterpret_cast<const unsigned short *>(p.w + p.d_off) + blk1);
+    };
+
+    SqPiece slot0[SQ_DEPTH], slot1[SQ_DEPTH];   // rows g and g + 8 of the steps in flight
+    int rt = blockIdx.x * SQ_GROUPS + group;
+    // load cursor: runs SQ_DEPTH steps ahead of the multiply over the same (row tile, unit) sequence
+    int lrt = rt, lunit = u_begin;
+    auto advance = [&]() {
+        if (++lunit >= u_end) { lunit = u_begin; lrt += rt_step; }
+    };
+#pragma unroll
+    for (int i = 0; i < SQ_DEPTH; ++i) {
+        if (lrt < p.n_tiles) load(lrt, lunit, slot0[i], slot1[i]);
+        advance();
+    }
+
+    pdl_wait();
+
+    sq_quantize_x(p, xq, xs, ngroups, tid);
+    __syncthreads();
+    pdl_launch_dependents();
+
+    // B operand: lane (g, t) supplies column g; it is group t's plane (g & 1) when t == g / 2 and zero otherwise
+    const bool live = t == (g >> 1);
+    const uint32_t xq0 = (uint32_t) __cvta_generic_to_shared(xq);
+    const uint32_t zero_addr = xq0 + (uint32_t) ngroups * 32u;
+    const uint32_t lane_off = (uint32_t) t * 64u + (uint32_t) (g & 1) * 16u;   // group +2t of the unit, plane g & 1
+    float * my_red = red + group * (SQ_WARPS * 16);
+    const int gtid = tid - group * (SQ_WARPS * 32);
+
+    // every group runs the same number of rounds so that the CTA-wide barriers match
+    for (int round = blockIdx.x * SQ_GROUPS; round < p.n_tiles; round += rt_step) {
+        float acc0 = 0.f, acc1 = 0.f;   // rows g and g + 8, this lane's groups
+        for (int ub = u_begin; rt < p.n_tiles && ub < u_end; ub += SQ_DEPTH) {
+#pragma unroll
+          for (int si = 0; si < SQ_DEPTH; ++si) {
+            const int unit = ub + si;
+            const SqPiece & cur0 = slot0[si];
+            const SqPiece & cur1 = slot1[si];
+            const float d0 = __half2float(__ushort_as_half((unsigned short) cur0.d)), d1 = __half2float(__ushort_as_half((unsigned short) cur1.d));
+            // group index of (block, unit, t): 16 block + 8 (unit / 2) + (unit & 1) + 2 t
+            const int u = unit & 3;
+            const uint32_t grp0 = (uint32_t) (unit >> 2) * 16u + (uint32_t) (u >> 1) * 8u + (uint32_t) (u & 1);
+            uint4 bx = make_uint4(0u, 0u, 0u, 0u);
+            {
+                const uint32_t addr = live ? xq0 + grp0 * 32u + lane_off : zero_addr;
+                asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(bx.x), "=r"(bx.y), "=r"(bx.z), "=r"(bx.w) : "r"(addr));
+            }
+            const uint32_t n0[4] = {cur0.nib.x, cur0.nib.y, cur0.nib.z, cur0.nib.w}, n1[4] = {cur1.nib.x, cur1.nib.y, cur1.nib.z, cur1.nib.w};
+            const uint32_t h0[4] = {cur0.hb.x, cur0.hb.y, cur0.hb.z, cur0.hb.w}, h1[4] = {cur1.hb.x, cur1.hb.y, cur1.hb.z, cur1.hb.w};
+            uint32_t q0[4], q1[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                q0[i] = ((n0[i] >> nib_shift) & 0x0F0F0F0Fu) | (((h0[i] >> hb_shift) & 0x03030303u) << 4);
+                q1[i] = ((n1[i] >> nib_shift) & 0x0F0F0F0Fu) | (((h1[i] >> hb_shift) & 0x03030303u) << 4);
+            }
+            int c[4] = {0, 0, 0, 0};
+            sq_imma(c, q0[0], q1[0], q0[1], q1[1], bx.x, bx.y);
+            sq_imma(c, q0[2], q1[2], q0[3], q1[3], bx.z, bx.w);
+            // columns 2t, 2t + 1 of this lane: (H, L) of group t
+            const float2 sq = xs[grp0 + 2 * t];
+            const int sx32 = __float_as_int(sq.y);
+            const int s0 = ((int) (cur0.sc << sc_shift)) >> 24, s1 = ((int) (cur1.sc << sc_shift)) >> 24;   // signed byte t
+            const float v0 = (float) (c[0] * 256 + c[1] - sx32), v1 = (float) (c[2] * 256 + c[3] - sx32);
+            acc0 = fmaf(d0 * (float) s0 * sq.x, v0, acc0);
+            acc1 = fmaf(d1 * (float) s1 * sq.x, v1, acc1);
+            // the slot is free: its step SQ_DEPTH ahead goes in
+            if (lrt < p.n_tiles) load(lrt, lunit, slot0[si], slot1[si]);
+            advance();
+          }
+        }
+        acc0 += __shfl_xor_sync(0xffffffffu, acc0, 1);
+        acc0 += __shfl_xor_sync(0xffffffffu, acc0, 2);
+        acc1 += __shfl_xor_sync(0xffffffffu, acc1, 1);
+        acc1 += __shfl_xor_sync(0xffffffffu, acc1, 2);
+        if (t == 0) {
+            my_red[warp * 16 + g] = acc0;
+            my_red[warp * 16 + g + 8] = acc1;
+        }
+        __syncthreads();
+        if (gtid < 16 && rt < p.n_tiles) {
+            float v = 0.f;
+#pragma unroll
+            for (int w = 0; w < SQ_WARPS; ++w) v += my_red[w * 16 + gtid];
+            p.y[(int64_t) rt * 16 + gtid] = v;
+        }
+        __syncthreads();
+        rt += rt_step;
+    }
+}
+
 size_t sq_smem_bytes(int units) { return (size_t) units * 4 * 32 + 32 + (size_t) units * 4 * 8 + (size_t) SQ_WARPS * SQ_GROUPS * 16 * 4; }
 
 }  // namespace
@@ -220,8 +347,15 @@ int matvec_q6k_imma_tiles(cudaStream_t s, const void * w, int64_t k, int64_t n, 
     int64_t grid = sm_count();
     const int64_t rounds = (tiles + SQ_GROUPS - 1) / SQ_GROUPS;
     if (grid > rounds) grid = rounds;
-    if (smem > 48 * 1024) SM100_CUDA(cudaFuncSetAttribute(matvec_q6k_imma, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
-    const int st = launch(matvec_q6k_imma, dim3((unsigned) grid), dim3(SQ_THREADS), smem, s, a);
+    static const int deep_ok = [] { const char * e = getenv("SM100_Q6K_DEEP"); return e != nullptr ? atoi(e) : 1; }();
+    int st;
+    if (deep_ok && units % SQ_WARPS == 0 && a.units_per_warp % SQ_DEPTH == 0) {
+        if (smem > 48 * 1024) SM100_CUDA(cudaFuncSetAttribute(matvec_q6k_imma_deep, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+        st = launch(matvec_q6k_imma_deep, dim3((unsigned) grid), dim3(SQ_THREADS), smem, s, a);
+    } else {
+        if (smem > 48 * 1024) SM100_CUDA(cudaFuncSetAttribute(matvec_q6k_imma, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+        st = launch(matvec_q6k_imma, dim3((unsigned) grid), dim3(SQ_THREADS), smem, s, a);
+    }
     *handled = st == ST_OK;
     return st;
 }
