@@ -143,6 +143,17 @@ SM100_API int sm100_hostpipe_destroy(sm100_hostpipe_t pipe);
 SM100_API int sm100_hostpipe_stream(sm100_hostpipe_t pipe, int which, sm100_stream_t * out);
 SM100_API int sm100_hostpipe_mul_mat(sm100_hostpipe_t pipe, int dtype, int layout, const void * w, int64_t w_row_stride,
                                      int64_t k, int64_t n, const float * host_x, int64_t m, float * host_y);
+/* the same for a list of products (a plan's worth, include/scrapgpu/backend.h:29-57 plan_execute): one call enqueues
+ * them all in order; returns at the first failing item */
+typedef struct sm100_hostpipe_item {
+    int dtype, layout;
+    const void * w;          /* device */
+    int64_t w_row_stride, k, n;
+    const float * host_x;
+    int64_t m;
+    float * host_y;
+} sm100_hostpipe_item;
+SM100_API int sm100_hostpipe_mul_mat_many(sm100_hostpipe_t pipe, int count, const sm100_hostpipe_item * items);
 SM100_API int sm100_hostpipe_sync(sm100_hostpipe_t pipe);
 /* MUL_MAT_MULTI (include/scrapgpu/op.h:46, src/backends/opencl11/kernels/mul_mv_multi.cl:46-104):
  * up to 3 weight tensors sharing one activation column, one launch */

@@ -67,6 +67,7 @@ def lib() -> C.CDLL:
         L.sm100_hostpipe_destroy.argtypes = [vp]
         L.sm100_hostpipe_stream.argtypes = [vp, i32, pv]
         L.sm100_hostpipe_mul_mat.argtypes = [vp, i32, i32, vp, i64, i64, i64, vp, i64, vp]
+        L.sm100_hostpipe_mul_mat_many.argtypes = [vp, i32, vp]
         L.sm100_hostpipe_sync.argtypes = [vp]
         L.sm100_head_post.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, vp, vp, i64, i64, i64, i64, C.c_float, C.c_float, i32]
         L.sm100_ipc_handle_bytes.restype = sz
@@ -142,6 +143,12 @@ class Stream:
             self.handle = None
 
 
+class HostPipeItem(C.Structure):
+    """sm100_hostpipe_item"""
+    _fields_ = [("dtype", C.c_int), ("layout", C.c_int), ("w", C.c_void_p), ("w_row_stride", C.c_int64), ("k", C.c_int64), ("n", C.c_int64),
+                ("host_x", C.c_void_p), ("m", C.c_int64), ("host_y", C.c_void_p)]
+
+
 class HostPipe:
     """MUL_MAT with host activations in and host results out, one call per product (sm100_hostpipe_*): copies and
     kernels on three streams of the pipe's own.  Host pointers are raw addresses of pinned memory."""
@@ -162,6 +169,10 @@ class HostPipe:
 
     def mul_mat(self, dtype: int, layout: int, w: "Buffer", k: int, n: int, host_x, m: int, host_y) -> None:
         check(lib().sm100_hostpipe_mul_mat(self.handle, dtype, layout, w.at(), 0, k, n, host_x, m, host_y), "hostpipe_mul_mat")
+
+    def mul_mat_many(self, items, count: int) -> None:
+        """items: a ctypes array of HostPipeItem"""
+        check(lib().sm100_hostpipe_mul_mat_many(self.handle, count, C.cast(items, C.c_void_p)), "hostpipe_mul_mat_many")
 
     def sync(self) -> None:
         check(lib().sm100_hostpipe_sync(self.handle), "hostpipe_sync")

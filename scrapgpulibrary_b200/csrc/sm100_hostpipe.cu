@@ -127,6 +127,16 @@ extern "C" int sm100_hostpipe_mul_mat(sm100_hostpipe_t pipe, int dtype, int layo
     return ST_OK;
 }
 
+extern "C" int sm100_hostpipe_mul_mat_many(sm100_hostpipe_t pipe, int count, const sm100_hostpipe_item * items) {
+    if (count < 0 || (count > 0 && items == nullptr)) return fail(ST_INVALID, "hostpipe_mul_mat_many: bad item list");
+    for (int i = 0; i < count; ++i) {
+        const sm100_hostpipe_item & it = items[i];
+        const int st = sm100_hostpipe_mul_mat(pipe, it.dtype, it.layout, it.w, it.w_row_stride, it.k, it.n, it.host_x, it.m, it.host_y);
+        if (st != ST_OK) return st;
+    }
+    return ST_OK;
+}
+
 extern "C" int sm100_hostpipe_sync(sm100_hostpipe_t pipe) {
     HostPipe * p = reinterpret_cast<HostPipe *>(pipe);
     if (p == nullptr) return fail(ST_INVALID, "hostpipe_sync: null pipe");

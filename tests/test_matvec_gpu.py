@@ -189,6 +189,16 @@ def test_hostpipe_mul_mat_matches_device_path(sm100, stream):
         want = U.device_mul_mat(sm100, stream, U.Q4_K, U.PACKED, wq, k, x)
         assert np.array_equal(got, want), m
         assert sgref.nmse(got, sgref.mul_mat(U.Q4_K, wq, k, x)) <= 1e-6
+    # the same products as one list
+    items = (sm100.HostPipeItem * len(host))()
+    for i, (m, x, px, py) in enumerate(host):
+        C.memset(py, 0xFF, 4 * n * m)
+        items[i] = sm100.HostPipeItem(U.Q4_K, U.PACKED, wb.ptr, 0, k, n, px.value, m, py.value)
+    pipe.mul_mat_many(items, len(host))
+    pipe.sync()
+    for m, x, px, py in host:
+        got = np.ctypeslib.as_array(C.cast(py, C.POINTER(C.c_float)), shape=(m * n,)).reshape(m, n).copy()
+        assert sgref.nmse(got, sgref.mul_mat(U.Q4_K, wq, k, x)) <= 1e-6
     # a product larger than the pipe's staging is refused, not truncated
     st = lib.sm100_hostpipe_mul_mat(pipe.handle, U.Q4_K, U.PACKED, wb.at(), 0, k, n, host[0][2], 8, host[0][3])
     assert st == 2
