@@ -46,11 +46,27 @@ Q4_0, Q8_0, Q4_K, Q6_K = 16, 17, 32, 33
 BPW = {Q4_0: 0.5625, Q8_0: 1.0625, Q4_K: 0.5625, Q6_K: 0.8203125}
 SHAPES = [(4096, 4096), (4096, 12288), (12288, 4096)]  # (K, N)
 METRIC = "q4_k_matvec_algorithmic_gbps"
+# what the timed kernel computes in (not a precision claim: results are within NMSE 1e-6 of the f32 reference, measured ~5e-9)
+ARITHMETIC = "u8 weights x s16 activations (two s8 planes, one f32 scale per 32) -> s32 on mma.sync; f32 block scales and accumulation"
 
 
 def algorithmic_bytes(dtype: int, k: int, n: int, m: int = 1) -> float:
     """Bytes a MUL_MAT must move: packed weights once, activations in, results out."""
     return n * k * BPW[dtype] + 4.0 * k * m + 4.0 * n * m
+
+
+def profiled_traffic(kernel_prefix: str):
+    """DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) of the dominant kernel from the ncu capture
+    summarised under profiles/: profiles/roofline_traffic.json names the kernel it was taken from, so a figure that
+    belongs to another kernel is not reported."""
+    p = os.path.join(ROOT, "profiles", "roofline_traffic.json")
+    try:
+        rec = json.load(open(p))
+        if str(rec.get("kernel", "")).startswith(kernel_prefix):
+            return int(rec["dram_bytes_per_launch"]), rec.get("source")
+    except Exception:
+        pass
+    return None, None
 
 
 def measured_peak_gbs():
@@ -60,7 +76,7 @@ def measured_peak_gbs():
             return float(json.load(open(p))["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
         except Exception:
             pass
-    return 6650.0, "fallback (6.65 TB/s, earlier measurement on this pool)"
+    return 6650.0, "fallback (6.65 TB/s, a B200 HBM3e copy bandwidth measured earlier; MEASURED_PEAKS.json absent)"
 
 
 class ClockSampler:
@@ -225,6 +241,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     if rank == 0:
         sampler.start()
     ms, per_step = timed_graph(1, None, args.steps, args.warmup)
+    headline_kernel = (L.sm100_matvec_last_kernel() or b"").decode()   # the kernel family that served the timed launches
     barrier()
     clocks = sampler.stop() if rank == 0 else {}
     if dist is not None:
@@ -321,9 +338,11 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         d2h = sum(4 * pool[s]["n"] for s, _ in order)
 
         cpu = cpu_baseline(pool, threads=1, repeats=5)
+        kernel_name = (L.sm100_matvec_last_kernel() or b"").decode() if headline_kernel is None else headline_kernel
+        traffic, traffic_src = profiled_traffic(kernel_name)
         out = {
             "metric": METRIC, "value": round(value, 1), "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-            "ms_per_step": round(ms_per_step, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+            "ms_per_step": round(ms_per_step, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": ARITHMETIC,
             "data": "synthetic: seeded N(0, 0.02) weights in Q4_K blocks, N(0, 1) activations",
             "config": {"workload": f"Q4_K matvec sweep, M=1, Qwen3-8B projection shapes (K,N) in {SHAPES} x {layers} layers per GPU",
                        "launches_per_step": per_step, "bytes_per_step_per_gpu": int(step_bytes), "weights_layout": "backend-packed planes",
@@ -332,11 +351,11 @@ def run_ours(args, rank: int, world: int, local_rank: int):
             "gpu_launches": int(launches_timed),
             "e2e": {"value": round(world * step_bytes / (e2e_ms * 1e-3) / 1e9, 1), "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "ms_per_step": round(e2e_ms, 4), "note": "host activations in / host results out per matvec through sm100_hostpipe_mul_mat_many (one list per step; copies on their own streams beside the kernels), weights resident"},
-            "roofline": {"bound": "hbm", "kernel": "matvec_q4k_imma<1,2,true,1>", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
+            "roofline": {"bound": "hbm", "kernel": kernel_name, "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
                          "frac": round(achieved / peak, 4), "peak_source": peak_src, "bytes_per_launch": round(per_launch_bytes, 1),
                          "us_per_launch": round(per_launch_us, 3),
-                         # dram__bytes_read + write per launch, mean of the three shapes of one ncu capture (profiles/matvec_q4k_imma_q4k_sweep.md)
-                         "traffic": 22109867},
+                         # dram__bytes_read + write per launch, mean over the three shapes of one ncu capture of this kernel
+                         "traffic": traffic, "traffic_source": traffic_src},
             "cpu_baseline": cpu,
             "clocks": clocks,
         }
@@ -476,7 +495,7 @@ def prefill_gemm(capi, stream, reps: int = 20):
 
 
 def run_decode(args, rank: int, world: int, local_rank: int, dist, stream_sync):
-    """Qwen3-8B-shaped layer-stack decode (BASELINE config 5): 36 layers, hidden 4096, 32/8 heads of 128, FFN 12288,
+    """Qwen3-8B-shaped layer-stack decode: 36 layers, hidden 4096, 32/8 heads of 128, FFN 12288,
     vocab 151936, random Q4_K_M-style weights, f32 KV cache pre-filled to position 1024, batch 1, greedy; one CUDA
     graph per token, tensor-parallel over `world` ranks with NCCL all-reduces.  Returns tok/s and the roofline view."""
     import torch
@@ -568,7 +587,7 @@ def run_reference(args, rank: int, world: int):
     value = res["value"]
     return {"impl": "reference", "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": steps, "warmup": args.warmup,
             "ms_per_step": round(total / (value * 1e9) * 1e3, 3), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": "f32", "data": "synthetic: seeded N(0, 0.02) weights in Q4_K blocks, N(0, 1) activations",
+            "dtype": "f32 (SSE2 scalar / panel code of the reference's CPU backend)", "data": "synthetic: seeded N(0, 0.02) weights in Q4_K blocks, N(0, 1) activations",
             "config": {"workload": f"Q4_K matvec sweep, M=1, Qwen3-8B projection shapes (K,N) in {SHAPES}; each step = one layer (bounded sample of the sweep)"},
             "cpu_baseline": {**res, "cores": threads}, "gpu_launches": 0,
             "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}, "wall_s_per_step": round(elapsed, 3)}
@@ -600,8 +619,8 @@ def main():
         print(json.dumps(out), flush=True)
     if world > 1:
         # Leave without tearing the NCCL communicator down: destroy_process_group() was seen to block for minutes
-        # on this pool while captured CUDA graphs still reference the communicator.  All ranks have passed the
-        # final barrier, nothing is in flight.
+        # while captured CUDA graphs still reference the communicator.  All ranks have passed the final barrier,
+        # nothing is in flight.
         sys.stdout.flush()
         sys.stderr.flush()
         os._exit(0)

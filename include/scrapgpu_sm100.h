@@ -99,6 +99,13 @@ SM100_API int sm100_graph_begin(sm100_stream_t s);
 SM100_API int sm100_graph_end(sm100_stream_t s, sm100_graph_t * out);
 SM100_API int sm100_graph_launch(sm100_graph_t g, sm100_stream_t s);
 SM100_API int sm100_graph_destroy(sm100_graph_t g);
+/* Library-owned scratch (slot 0 attention partials, 1 GEMM activation image, 2 quantized columns of the 3..8-column
+ * matvec) is allocated on first use and only ever grows: a block that was handed out is never freed or moved, so CUDA
+ * graphs captured earlier stay valid when a later, larger call makes the library allocate a bigger block.  Allocation
+ * is impossible during stream capture; a caller that captures reserves the largest size it will need beforehand, either
+ * by issuing the call once outside the capture or with sm100_scratch_reserve on the device in question.  No
+ * counterpart in the reference (its backends allocate per call: src/core/attention.cpp:576). */
+SM100_API int sm100_scratch_reserve(int slot, size_t bytes);
 /* number of kernels of this library launched (or captured) by the calling process so far */
 SM100_API uint64_t sm100_launch_count(void);
 /* 1: launch kernels with programmatic dependent launch so that a kernel's weight prefetch overlaps
@@ -128,6 +135,11 @@ SM100_API int sm100_pack_device_range(sm100_stream_t s, int dtype, int64_t k, in
  *      dequantize-and-dot matvec; larger m takes the tensor-core GEMM. ---- */
 SM100_API int sm100_mul_mat(sm100_stream_t s, int dtype, int layout, const void * w, int64_t w_row_stride, int64_t k,
                             int64_t n, const float * x, int64_t ldx, int64_t m, float * y, int64_t ldy);
+/* Name of the kernel family that served the calling thread's last sm100_mul_mat with m <= 8 ("matvec_q4k_imma",
+ * "matvec_wide", "matvec_rows", ...; "+rows" when leftover rows took the row kernel).  The reference reports its kernel
+ * choice per op key in its profile table (src/backends/opencl11/executor.h:41-112); here the parity tests use it to
+ * prove that every branch of the dispatcher is exercised. */
+SM100_API const char * sm100_matvec_last_kernel(void);
 /* MUL_MAT with activations and results in HOST memory, one call per product and no host synchronisation in between:
  * what a caller of the reference does with scrapgpu_tensor_upload -> op_execute -> scrapgpu_tensor_download
  * (include/scrapgpu/tensor.h:45-53), as a pipeline.  A pipe owns three in-order streams and `depth` slots of device
@@ -249,15 +261,23 @@ SM100_API int sm100_attention_kvcache(sm100_stream_t s, const float * q, const f
  * by its own pools, a latency-critical thread that must stay off the driver's allocator, an externally enforced
  * memory budget).  Same arguments and values as sm100_attention; the split-key partials go to a fixed 4 MiB array
  * inside the library image (every GPU that loads the library holds it until exit) instead of a scratch buffer
- * allocated on demand.  Shapes whose partials exceed sm100_attention_static_capacity() bytes
- * (nq * hq * splits * (dv + 4) floats) are refused with UNSUPPORTED.  The first call on a device looks the array's
- * address up: make it before any stream capture.  All calls on one device share the array, so calls that overlap
- * on the GPU race.  This entry has no counterpart in the reference. */
+ * allocated on demand.  sm100_attention_static_capacity() is the array's size; its first 64 KiB hold the ticket
+ * counters of the single-launch merge, so shapes whose partials (nq * hq * splits * (dv + 4) floats) exceed the
+ * capacity minus 64 KiB are refused with UNSUPPORTED.  The first call on a device looks the array's address up:
+ * make it before any stream capture.  All calls on one device share the array and it keeps the last call's
+ * contents: every call first clears the counters it will use (a memset on the caller's stream, no allocation), the
+ * partials need no clearing; calls that overlap on the GPU race, and a raced call's result is undefined (later,
+ * non-overlapping calls are correct again because of the clearing).  This entry has no counterpart in the reference. */
 SM100_API int sm100_attention_static(sm100_stream_t s, const float * q, const float * k, const float * v, const float * mask,
                                      int64_t mask_heads, float * out, int64_t d, int64_t dv, int64_t nq, int64_t nk,
                                      int64_t hq, int64_t hkv, int causal, int64_t offset, const int32_t * positions,
                                      float scale);
 SM100_API size_t sm100_attention_static_capacity(void);
+/* Does, for the current device, the one-time address look-up that the first sm100_attention_static call on a device
+ * would otherwise do, so that a caller can get it out of the way explicitly before it starts a stream capture; allocates
+ * nothing.  device_address_out (may be NULL) receives the array's device address, for diagnostics only: the contents
+ * belong to the library.  No counterpart in the reference. */
+SM100_API int sm100_attention_static_prepare(void ** device_address_out);
 
 /* ---- the same ops over strided views (arbitrary nb[1..3], broadcast operands, transposed CPY sources): what
  *      op_execute needs to honour every descriptor the reference's CPU backend accepts
@@ -278,6 +298,11 @@ SM100_API int sm100_cpy(sm100_stream_t s, const sm100_view * src, int src_dtype,
 SM100_API int sm100_set_rows_view(sm100_stream_t s, const sm100_view * src, int src_dtype, const sm100_view * ids, int ids_are_i64,
                                   const sm100_view * dst, int dst_dtype);                   /* ops.cpp:724-762 */
 SM100_API int sm100_top1_view(sm100_stream_t s, const sm100_view * x, const sm100_view * out);   /* ops.cpp:1189-1228, k = 1 */
+/* CONT_MUL_MAT (include/scrapgpu/op.h:47; inputs [a, x] per src/backends/opencl11/api.cpp:11-12; OpenCL kernels
+ * attn.cl:123-237): `a` is the transposed F16 (or F32) view a CONT would have copied -- its dim 1 is the contiguous
+ * one -- and dst[i1, 0, i2, i3] = sum_i0 a[i0, i1, i2 / r2, i3 / r3] * x[i0, 0, i2, i3], the values of CONT followed
+ * by MUL_MAT (src/core/ref/ops.cpp:764-800, 891-984) without the copy */
+SM100_API int sm100_cont_mul_mat(sm100_stream_t s, const sm100_view * a, int a_dtype, const sm100_view * x, const sm100_view * y);
 
 #ifdef __cplusplus
 }

@@ -38,6 +38,18 @@ def build_example() -> bool:
     return os.path.exists(EXAMPLE)
 
 
+OPS_TESTS = os.path.join(_HERE, "_ref", "ops_tests")
+ATTENTION_TESTS = os.path.join(_HERE, "_ref", "attention_tests")
+
+
+def build_device_tests() -> bool:
+    """The reference's own device test programs (tests/ops/ops_tests.cpp, tests/attention/attention_tests.cpp),
+    compiled unchanged and linked against the plugin; True if both binaries exist afterwards."""
+    if os.path.isfile(os.path.join(REFERENCE_DIR, "tests", "ops", "ops_tests.cpp")):
+        subprocess.run(["make", "-C", _HERE, "device_tests", f"REF={REFERENCE_DIR}"], check=True, capture_output=True)
+    return os.path.exists(OPS_TESTS) and os.path.exists(ATTENTION_TESTS)
+
+
 def available() -> bool:
     return os.path.exists(SO)
 

@@ -499,6 +499,19 @@ scrapgpu_status supports(const scrapgpu_op_desc * desc, const char ** reason) {
             return SCRAPGPU_STATUS_OK;
         }
 
+        case SCRAPGPU_OP_CONT_MUL_MAT: {
+            // inputs [a, x], output [dst]: `a` is the transposed view a CONT would have copied (dim 1 contiguous), x one
+            // F32 column per (i2, i3) (src/backends/opencl11/api.cpp:260-300 states the OpenCL backend's conditions)
+            if (desc->input_count != 2) return bad("CONT_MUL_MAT takes two inputs", reason);
+            if ((s0.dtype != SCRAPGPU_DTYPE_F16 && !f32(s0)) || !f32(s1) || !f32(dd)) return unsupported("CONT_MUL_MAT needs an F16 or F32 view, an F32 vector and an F32 dst", reason);
+            if (s0.nb[1] != type_size(s0.dtype)) return unsupported("CONT_MUL_MAT src0 must be a transposed view (dim 1 contiguous)", reason);
+            if (ne(s1, 1) != 1 || s1.nb[0] != 4 || dd.nb[0] != 4 || ne(s0, 0) != ne(s1, 0) || ne(s1, 2) % ne(s0, 2) != 0 || ne(s1, 3) % ne(s0, 3) != 0)
+                return unsupported("CONT_MUL_MAT needs a single F32 column x with x.ne[0] == a.ne[0] and x.ne[2], x.ne[3] multiples of a's", reason);
+            if (ne(dd, 0) != ne(s0, 1) || ne(dd, 1) != 1 || ne(dd, 2) != ne(s1, 2) || ne(dd, 3) != ne(s1, 3)) return bad("CONT_MUL_MAT dst must be [a.ne1, 1, x.ne2, x.ne3]", reason);
+            if (ne(s1, 2) * ne(s1, 3) > 65535) return unsupported("CONT_MUL_MAT: too many (dim 2, dim 3) slices", reason);
+            return SCRAPGPU_STATUS_OK;
+        }
+
         case SCRAPGPU_OP_ARGSORT:
             return unsupported("ARGSORT is not implemented on cuda_sm100 (TOP_K with k = 1 is)", reason);
         case SCRAPGPU_OP_TOP_K: {
@@ -807,6 +820,10 @@ scrapgpu_status execute(Stream * s, const scrapgpu_op_desc * desc) {
                 if (st != SCRAPGPU_STATUS_OK) return st;
             }
             return SCRAPGPU_STATUS_OK;
+        }
+        case SCRAPGPU_OP_CONT_MUL_MAT: {
+            const sm100_view a = view_of(in[0]), x = view_of(in[1]), y = view_of(out[0]);
+            return from_sm100(sm100_cont_mul_mat(s->cuda, &a, in[0].d.dtype, &x, &y));
         }
         case SCRAPGPU_OP_TOP_K: {
             const sm100_view x = view_of(in[0]), o = view_of(out[0]);
@@ -1146,6 +1163,7 @@ const char * op_name(int op) {
         case SCRAPGPU_OP_ADD_RMS_NORM_MUL: return "ADD_RMS_NORM_MUL";
         case SCRAPGPU_OP_MUL_MAT_MULTI: return "MUL_MAT_MULTI";
         case SCRAPGPU_OP_SET_ROWS_PAIR: return "SET_ROWS_PAIR";
+        case SCRAPGPU_OP_CONT_MUL_MAT: return "CONT_MUL_MAT";
         default: return "OP";
     }
 }

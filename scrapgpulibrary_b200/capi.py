@@ -95,6 +95,9 @@ def lib() -> C.CDLL:
         L.sm100_attention_static.argtypes = L.sm100_attention.argtypes
         L.sm100_attention_kvcache.argtypes = L.sm100_attention.argtypes + [i32]
         L.sm100_attention_static_capacity.restype = C.c_size_t
+        L.sm100_attention_static_prepare.argtypes = [pv]
+        L.sm100_matvec_last_kernel.restype = C.c_char_p
+        L.sm100_cont_mul_mat.argtypes = [vp, vp, i32, vp, vp]
         _LIB = L
     return _LIB
 

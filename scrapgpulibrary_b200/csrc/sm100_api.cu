@@ -9,6 +9,7 @@ int matvec(cudaStream_t s, int dtype, int layout, const void * w, int64_t w_row_
            int64_t ldx, int64_t m, float * y, int64_t ldy);
 int matvec_q4k_imma_multi(cudaStream_t s, int count, const void * const * ws, const int64_t * ns, int64_t k, const float * x, int64_t ldx,
                           int64_t m, float * const * ys, const int64_t * ldys, bool * handled, const Q4KPrologue * pro);
+const char * matvec_last_kernel();
 int gemm_tc_mul_mat(cudaStream_t s, int dtype, int layout, const void * w, int64_t w_row_stride, int64_t k, int64_t n, const float * x,
                     int64_t ldx, int64_t m, float * y, int64_t ldy, bool * handled);
 }
@@ -16,6 +17,8 @@ int gemm_tc_mul_mat(cudaStream_t s, int dtype, int layout, const void * w, int64
 using namespace sm100;
 
 extern "C" {
+
+const char * sm100_matvec_last_kernel(void) { return matvec_last_kernel(); }
 
 int sm100_mul_mat(sm100_stream_t s, int dtype, int layout, const void * w, int64_t w_row_stride, int64_t k, int64_t n, const float * x,
                   int64_t ldx, int64_t m, float * y, int64_t ldy) {

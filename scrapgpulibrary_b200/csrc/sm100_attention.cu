@@ -320,19 +320,9 @@ __global__ void attn_combine_kernel(AttnArgs a) {
 // the three phases of the generic kernel.  The 8 warps are merged through shared memory into the split's partial;
 // the CTA that delivers the last partial of a (query, KV head) merges the splits right away (counter in global
 // memory, reset for the next call), so no second launch is needed.
-#ifdef SM100_ATTN_TIMING
-__device__ unsigned long long g_att_t[8];   // development builds: cycles per phase summed over CTAs; [6] CTAs, [7] merging CTAs
-#define ATT_T(i) if (threadIdx.x == 0) { const long long now_ = clock64(); atomicAdd(&g_att_t[i], (unsigned long long) (now_ - t_prev_)); t_prev_ = now_; }
-#else
-#define ATT_T(i)
-#endif
 
 template <int G, int D4>
 __global__ void __launch_bounds__(ATT_THREADS) attn_fast_kernel(AttnArgs a) {
-#ifdef SM100_ATTN_TIMING
-    long long t_prev_ = clock64();
-    if (threadIdx.x == 0) atomicAdd(&g_att_t[6], 1ull);
-#endif
     constexpr int D = 128 * D4;
     extern __shared__ __align__(16) float smem[];   // [8 warps][G][ATT_HDR + D]
     constexpr int SROW = ATT_HDR + D;
@@ -389,7 +379,6 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_fast_kernel(AttnArgs a) {
         }
     }
     pdl_launch_dependents();
-    ATT_T(0)
 
     float4 qr[G][D4];
 #pragma unroll
@@ -495,7 +484,6 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_fast_kernel(AttnArgs a) {
         }
     }
     __syncwarp();
-    ATT_T(1)
     // warps -> shared memory: per (warp, head) [m, l, -, -, o[D]]
 #pragma unroll
     for (int g = 0; g < G; ++g) {
@@ -543,7 +531,6 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_fast_kernel(AttnArgs a) {
         reinterpret_cast<float4 *>(dst + ATT_HDR)[c] = acc;
     }
     if (a.counters == nullptr) return;   // the caller merges with a second launch
-    ATT_T(2)
     // the CTA's partial is complete once all its threads passed the barrier; thread 0 publishes it (the fence is
     // cumulative over what the barrier ordered before it) and takes a ticket
     __syncthreads();
@@ -554,23 +541,11 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_fast_kernel(AttnArgs a) {
         s_last = last;
     }
     __syncthreads();
-    ATT_T(3)
     if (s_last == 0) return;
     attn_merge_group<G, D4>(a, q, hk, s_w, &s_red[0][0], reinterpret_cast<float4 *>(smem));
     if (tid == 0) a.counters[q * a.hkv + hk] = 0;
-    ATT_T(4)
-#ifdef SM100_ATTN_TIMING
-    if (threadIdx.x == 0) atomicAdd(&g_att_t[7], 1ull);
-#endif
 }
 
-#ifdef SM100_ATTN_TIMING
-extern "C" __attribute__((visibility("default"))) int sm100_debug_attn_timing(unsigned long long * out, int reset) {
-    if (cudaMemcpyFromSymbol(out, g_att_t, sizeof(unsigned long long) * 8) != cudaSuccess) return 4;
-    if (reset) { unsigned long long z[8] = {}; cudaMemcpyToSymbol(g_att_t, z, sizeof(z)); }
-    return 0;
-}
-#endif
 
 int device_scratch(int slot, size_t bytes, void ** out);
 
@@ -700,8 +675,16 @@ extern "C" int sm100_attention_kvcache(sm100_stream_t s, const float * q, const 
 // In host code the name of a __device__ array is only a stand-in symbol, not a device address, so the address is
 // looked up with cudaGetSymbolAddress once per device (with that device current) and cached; the FIRST call on a
 // device does this look-up, so make that first call outside of any stream capture.  All calls on a device share
-// the one array: two calls whose kernels overlap on the GPU (different streams) race on it.  Nothing in it has to
-// start at zero -- every entry the merge kernel reads is written by the partial kernel of the same call.
+// the one array: two calls whose kernels overlap on the GPU (different streams) race on it.
+//
+// What must start at zero: the first ATT_COUNTER_SLOTS ints of the array are the ticket counters of the single-launch
+// merge, one per (query, KV head): the CTA that draws the last ticket merges the splits and puts the counter back
+// to zero.  A call that raced with another one, or a launch that ended between drawing and resetting, would leave
+// a counter non-zero and every later call on that device would merge too early or never.  So this entry does not
+// rely on what the previous call left behind: it clears the counters it is going to use with a memset on the
+// caller's stream in front of the launch (a memset node, no allocation).  The partials behind the counters need no
+// clearing: every entry the merge reads is written by the same call first.  The counters take 64 KiB of the array;
+// the partials of one call may use the remaining 4 MiB - 64 KiB.
 // ---------------------------------------------------------------------------------------------------------
 namespace sm100 {
 
@@ -749,7 +732,17 @@ extern "C" int sm100_attention_static(sm100_stream_t s, const float * q, const f
     float * ws = nullptr;
     const int sw = static_scratch(&ws);
     if (sw != ST_OK) return sw;
+    const size_t used_counters = (size_t) a.nq * a.hkv < (size_t) ATT_COUNTER_SLOTS ? (size_t) a.nq * a.hkv : (size_t) ATT_COUNTER_SLOTS;
+    SM100_CUDA(cudaMemsetAsync(ws, 0, used_counters * sizeof(int), (cudaStream_t) s));   // see above: never trust the last call's counters
     return attention_launch((cudaStream_t) s, a, ws);
 }
 
 extern "C" size_t sm100_attention_static_capacity(void) { return sm100::ATT_STATIC_FLOATS * sizeof(float); }
+
+extern "C" int sm100_attention_static_prepare(void ** device_address_out) {
+    float * ws = nullptr;
+    const int sw = sm100::static_scratch(&ws);
+    if (sw != sm100::ST_OK) return sw;
+    if (device_address_out != nullptr) *device_address_out = ws;
+    return sm100::ST_OK;
+}

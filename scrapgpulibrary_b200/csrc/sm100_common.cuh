@@ -4,6 +4,7 @@
 #include <cuda_runtime.h>
 #include <cuda_fp16.h>
 
+#include <atomic>
 #include <cstdarg>
 #include <cstdint>
 #include <cstdio>
@@ -61,6 +62,11 @@ struct Q4KPrologue {
 };
 
 int sm_count();          // SMs of the current device (cached per device)
+int current_device();    // ordinal of the current device (0 when it cannot be read)
+
+// One "a kernel with bounded waits was launched" mark per device: the kernel's fault word is a __device__ variable,
+// i.e. one copy per device, and it is read back after a stream synchronisation only on devices that launched one.
+constexpr int MAX_DEVICES = 64;
 bool pdl_enabled();
 void count_launch();
 
@@ -113,6 +119,29 @@ int launch_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
     if (e != cudaSuccess) return cuda_fail(e, "kernel launch (cluster)");
     count_launch();
     return ST_OK;
+}
+
+// ---- activations as 16-bit integers (the integer tensor-core matvecs) ----
+// A group of activations (16 or 32 of them) becomes integers in [-32512, 32512] with one f32 scale: x ~ s * q.
+// The largest magnitude of the group is found on the BIT PATTERNS of |x| (for non-negative floats the integer
+// order is the float order), because that order also ranks +inf and every NaN above all finite values, whereas
+// fmaxf() drops NaNs: a group that holds a NaN or an infinity gets s = NaN and q = 0, so every output that
+// reads the group becomes NaN, as the reference's f32 dot product would make it non-finite
+// (src/core/ref/ops.cpp:968-980).  Groups below 1e-30 count as zero (their products are below 1e-28 of a weight).
+__device__ __forceinline__ uint32_t act_abs_bits(const float4 & v) {
+    const uint32_t a = __float_as_uint(v.x) & 0x7fffffffu, b = __float_as_uint(v.y) & 0x7fffffffu;
+    const uint32_t c = __float_as_uint(v.z) & 0x7fffffffu, d = __float_as_uint(v.w) & 0x7fffffffu;
+    return max(max(a, b), max(c, d));
+}
+// inv: multiplier that maps the group's values to the integer range (0 for an empty or poisoned group);
+// s: the scale that maps the integers back
+__device__ __forceinline__ void act_group_scale(uint32_t amax_bits, float & inv, float & s) {
+    const float amax = __uint_as_float(amax_bits);
+    const bool finite = amax_bits < 0x7f800000u;
+    const bool some = finite && amax > 1e-30f;
+    inv = some ? __fdiv_rn(32512.0f, amax) : 0.0f;   // IEEE division: the fast one returns 0 for amax above 2^126
+    s = some ? amax * (1.0f / 32512.0f) : 0.0f;
+    if (!finite) s = __uint_as_float(0x7fc00000u);
 }
 
 // device side of programmatic dependent launch

@@ -60,20 +60,6 @@ constexpr float W_PRESCALE = 256.0f;  // applied to quantized weights before the
 constexpr uint32_t WAIT_LIMIT = 1u << 21;  // polls of one mbarrier wait before the CTA gives up (~1 s)
 
 __device__ int g_gemm_fault;  // 0, or 1 + the wait site that gave up
-#ifdef SM100_GEMM_TIMING
-// development builds only: cycle counters of CTA 0 (see sm100_debug_gemm_timing)
-__device__ unsigned long long g_gemm_timing[16];
-__device__ long long g_gemm_trace[6][64];   // CTA 0, chunk c < 64: [0] bulk saw empty, [1] producer saw empty, [2] producer arrived, [3] MMA saw full, [4] MMA committed, [5] kernel start
-#define GT_TRACE(i, c) do { if (blockIdx.x == 0 && lane == 0 && (c) < 64) g_gemm_trace[i][c] = clock64(); } while (0)
-#define GT_DECL(v) long long v = 0
-#define GT_NOW() clock64()
-#define GT_PUT(i, v) do { if (blockIdx.x == 0 && lane == 0) atomicAdd(&g_gemm_timing[i], (unsigned long long) (v)); } while (0)
-#else
-#define GT_DECL(v)
-#define GT_NOW() 0
-#define GT_PUT(i, v)
-#define GT_TRACE(i, c)
-#endif
 
 
 // ---------------------------------------------------------------------------------------------
@@ -480,9 +466,6 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc(const GemmArgs g) {
     const int mt = blockIdx.x % g.m_tiles, nt = blockIdx.x / g.m_tiles;
     const int n0 = nt * (TM * RT), m0 = mt * TN;
     volatile int * abort_flag = &sm.abort_flag;
-#ifdef SM100_GEMM_TIMING
-    const long long gt_start = clock64();
-#endif
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < SA; ++s) {
@@ -513,11 +496,6 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc(const GemmArgs g) {
     // Everything above, and the weight side below, overlaps the activation preparation that precedes this kernel
     // in the stream: only the bulk-copy warp (prepared activations) and the epilogue (token factors, output) wait
     // for it.  That kernel itself starts only after everything before it has completed, so nothing older is in flight.
-#ifdef SM100_GEMM_TIMING
-    const long long gt_go = clock64();
-    if (warp == FIRST_PRODUCER) { GT_PUT(0, gt_go - gt_start); GT_PUT(1, 1); if (blockIdx.x == 0 && lane == 0) g_gemm_trace[5][0] = gt_start; }
-    long long gt_wait = 0, gt_t;
-#endif
 
     if (warp >= FIRST_PRODUCER) {
         // ---- A operand.  A task is (row, 32-weight block), one per thread of a producer group; with 64-wide
@@ -570,16 +548,9 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc(const GemmArgs g) {
                 // the stage is free once the MMAs of the chunk that used it last have retired
                 const int s = c % SA;
                 const uint32_t phase = (uint32_t) (c / SA) & 1u;
-#ifdef SM100_GEMM_TIMING
-                gt_t = clock64();
-#endif
                 bool ok = mbar_try_wait(empty_a0 + 8 * s, phase ^ 1u);
                 if (!ok) ok = mbar_wait(empty_a0 + 8 * s, phase ^ 1u, abort_flag, 0);
                 if (!__all_sync(0xffffffffu, ok)) { alive = false; break; }
-#ifdef SM100_GEMM_TIMING
-                gt_wait += clock64() - gt_t;
-                (void) 0;
-#endif
                 if (ATM) {
                     tc_fence_after();   // the stage's previous MMAs (observed through the barrier) precede these stores
                     tmem_st16(tmem + ((uint32_t) (32 * (warp & 3)) << 16) + (uint32_t) (ACC_COLS + (s * RT + rt) * A_COLS + blk * 16), out);
@@ -596,19 +567,12 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc(const GemmArgs g) {
                 }
                 __syncwarp();
                 if (lane == 0) mbar_arrive(full_a0 + 8 * s);
-#ifdef SM100_GEMM_TIMING
-                if (gw == 0 && rt == 0) GT_TRACE(2, c);
-#endif
             }
         }
         // the dependency wait (long satisfied: the activations have been flowing) comes before the successor is
         // released, as in every kernel of this library: a successor's early section then overlaps this kernel only
         pdl_wait();
         pdl_launch_dependents();
-#ifdef SM100_GEMM_TIMING
-        if (warp == FIRST_PRODUCER) { GT_PUT(2, clock64() - gt_go); GT_PUT(3, gt_wait); }
-        gt_t = clock64();
-#endif
 
         // ---- epilogue: a warp may read the TMEM lanes 32 (warp % 4) ..; four consecutive producer warps cover
         // the four lane quarters, and each such set takes a quarter of the columns ----
@@ -642,9 +606,6 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc(const GemmArgs g) {
                 }
             }
         }
-#ifdef SM100_GEMM_TIMING
-        if (warp == FIRST_PRODUCER) { GT_PUT(4, clock64() - gt_t); GT_PUT(5, clock64() - gt_start); }
-#endif
     } else if (warp >= WARP_BULK) {
         // ---- B operand: one bulk copy per stage, issued as soon as the stage is free.  A warp gets one bulk copy
         // through per ~530 cycles whatever its size (measured: 16 KB copies from one thread 31 B/cycle, from four
@@ -657,7 +618,6 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc(const GemmArgs g) {
                 const int s = c % STAGES;
                 const uint32_t phase = (uint32_t) (c / STAGES) & 1u;
                 if (!mbar_try_wait(empty_b0 + 8 * s, phase ^ 1u) && !mbar_wait(empty_b0 + 8 * s, phase ^ 1u, abort_flag, 2)) break;
-                if (warp == WARP_BULK) GT_TRACE(0, c);
                 mbar_expect_tx(full_b0 + 8 * s, Smem::B_BYTES);
                 bulk_g2s(b_smem + s * Smem::B_BYTES, src + (int64_t) c * Smem::B_BYTES, Smem::B_BYTES, full_b0 + 8 * s);
                 last = c;
@@ -691,9 +651,6 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc(const GemmArgs g) {
         // used an iteration later; only a "not yet" takes the waiting path.
         uint32_t ready = (mbar_test_wait(full_b0, 0u) ? 1u : 0u) & (mbar_test_wait(full_a0, 0u) ? 1u : 0u);
         for (int c = 0; c < g.nchunks; ++c) {
-#ifdef SM100_GEMM_TIMING
-            gt_t = clock64();
-#endif
             if (ready == 0u) {
                 bool ok = mbar_try_wait(full_b0 + 8 * sb, pb);
                 if (!ok) ok = mbar_wait(full_b0 + 8 * sb, pb, abort_flag, 3, false);
@@ -702,13 +659,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc(const GemmArgs g) {
                     if (!ok) ok = mbar_wait(full_a0 + 8 * sa, pa, abort_flag, 4, false);
                 }
                 if (!__all_sync(0xffffffffu, ok)) { alive = false; break; }
-            } else {
-                GT_PUT(9, 1);    // development builds: chunks that were ready when looked at an iteration early
             }
-#ifdef SM100_GEMM_TIMING
-            gt_wait += clock64() - gt_t;
-            GT_TRACE(3, c);
-#endif
             tc_fence_after();
             // next chunk's stages
             int sa_n = sa + 1, sb_n = sb + 1;
@@ -743,15 +694,11 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc(const GemmArgs g) {
                     mma_commit(empty_a0 + 8 * sa);   // each commit covers every MMA issued so far
                     mma_commit(empty_b0 + 8 * sb);
                 }
-                GT_TRACE(4, c);
             }
             ready = c + 1 < g.nchunks ? (ra & rb) : 1u;
             sa = sa_n; pa = pa_n; sb = sb_n; pb = pb_n;
         }
         __syncwarp();
-#ifdef SM100_GEMM_TIMING
-        GT_PUT(6, clock64() - gt_go); GT_PUT(7, gt_wait); GT_PUT(8, g.nchunks);
-#endif
         // the accumulator is complete (or abandoned) once everything issued so far has retired
         mma_commit(smem_addr(&sm.accum));
         if (!alive && lane == 0) {
@@ -844,7 +791,7 @@ __global__ void __launch_bounds__(256) gemm_prep_x(const float * x, int64_t ldx,
     }
 }
 
-std::atomic<bool> g_gemm_launched{false};
+std::atomic<bool> g_gemm_launched[MAX_DEVICES];   // per device, see sm100_common.cuh
 
 template <typename S, int TN, int KC, int STAGES, int RT, bool ATM>
 int launch_gemm(cudaStream_t s, GemmArgs g, int n_tiles) {
@@ -862,7 +809,7 @@ int launch_gemm(cudaStream_t s, GemmArgs g, int n_tiles) {
             configured[dev] = 1;
         }
     }
-    g_gemm_launched.store(true, std::memory_order_relaxed);
+    g_gemm_launched[current_device()].store(true, std::memory_order_relaxed);
     return launch(gemm_tc<S, TN, KC, STAGES, RT, ATM>, dim3((unsigned) (n_tiles * g.m_tiles)), dim3(GEMM_THREADS), sizeof(Smem), s, g);
 }
 
@@ -919,22 +866,9 @@ int gemm_passes(cudaStream_t s, int dtype, int layout, GemmArgs g, const float *
 
 // Reads and clears the fault flag of the tensor-core GEMM on the current device; called after a stream
 // synchronisation.  Costs nothing until a GEMM has been launched.
-#ifdef SM100_GEMM_TIMING
-extern "C" __attribute__((visibility("default"))) int sm100_debug_gemm_trace(long long * out) {
-    return cudaMemcpyFromSymbol(out, g_gemm_trace, sizeof(long long) * 6 * 64) != cudaSuccess ? 1 : 0;
-}
-extern "C" __attribute__((visibility("default"))) int sm100_debug_gemm_timing(unsigned long long * out, int reset) {
-    if (cudaMemcpyFromSymbol(out, g_gemm_timing, sizeof(unsigned long long) * 16) != cudaSuccess) return 1;
-    if (reset) {
-        unsigned long long z[16] = {};
-        if (cudaMemcpyToSymbol(g_gemm_timing, z, sizeof(z)) != cudaSuccess) return 1;
-    }
-    return 0;
-}
-#endif
 
 int gemm_poll_fault() {
-    if (!g_gemm_launched.exchange(false, std::memory_order_relaxed)) return ST_OK;
+    if (!g_gemm_launched[current_device()].exchange(false, std::memory_order_relaxed)) return ST_OK;
     int v = 0;
     SM100_CUDA(cudaMemcpyFromSymbol(&v, g_gemm_fault, sizeof(v)));
     if (v == 0) return ST_OK;

@@ -387,6 +387,15 @@ __global__ void matvec_scalar(const uint8_t * __restrict__ w, int64_t w_row_stri
 
 // ---- host dispatch ------------------------------------------------------------------------------------
 
+// name of the kernel family the last matvec() call of this thread was served by (tests pin every dispatch branch by it)
+static thread_local const char * t_last_kernel = "";
+static int took(const char * name, int st) {
+    t_last_kernel = name;
+    return st;
+}
+const char * matvec_last_kernel() { return t_last_kernel; }
+
+
 template <class U>
 static int launch_stream(cudaStream_t s, const void * w, int64_t k, int64_t n, const float * x, float * y) {
     const int upr = (int) (k / U::WEIGHTS);
@@ -467,10 +476,10 @@ static int matvec_dispatch(cudaStream_t s, int layout, const void * w, int64_t w
                            int64_t ldx, int64_t m, float * y, int64_t ldy) {
     const int upr = (int) (k / U::WEIGHTS);
     if (layout == LAYOUT_PACKED) {
-        if (m == 1 && upr % 32 == 0 && upr <= U::MAX_THREADS) return launch_stream<U>(s, w, k, n, x, y);
-        return launch_rows<U, true>(s, w, 0, k, n, x, ldx, m, y, ldy);
+        if (m == 1 && upr % 32 == 0 && upr <= U::MAX_THREADS) return took("matvec_stream", launch_stream<U>(s, w, k, n, x, y));
+        return took("matvec_rows", launch_rows<U, true>(s, w, 0, k, n, x, ldx, m, y, ldy));
     }
-    return launch_rows<U, false>(s, w, w_row_stride, k, n, x, ldx, m, y, ldy);
+    return took("matvec_rows_natural", launch_rows<U, false>(s, w, w_row_stride, k, n, x, ldx, m, y, ldy));
 }
 
 // Decode matvec entry used by sm100_mul_mat for m <= 8.  w_row_stride (bytes) only matters for the
@@ -497,8 +506,8 @@ int matvec(cudaStream_t s, int dtype, int layout, const void * w, int64_t w_row_
         if (st != ST_OK) return st;
         if (handled) {
             const int64_t full = (n / 16) * 16;
-            if (full < n) return launch_rows<UnitQ4K, true>(s, w, 0, k, n, x, ldx, m, y, ldy, full);
-            return ST_OK;
+            if (full < n) return took("matvec_q4k_imma+rows", launch_rows<UnitQ4K, true>(s, w, 0, k, n, x, ldx, m, y, ldy, full));
+            return took("matvec_q4k_imma", ST_OK);
         }
     }
     static const int use_b32 = env_int("SM100_B32_IMMA", 1);
@@ -508,9 +517,9 @@ int matvec(cudaStream_t s, int dtype, int layout, const void * w, int64_t w_row_
         if (st != ST_OK) return st;
         if (handled) {
             const int64_t full = (n / 16) * 16;
-            if (full == n) return ST_OK;
-            return dtype == DT_Q4_0 ? launch_rows<UnitQ40, true>(s, w, 0, k, n, x, ldx, m, y, ldy, full)
-                                    : launch_rows<UnitQ80, true>(s, w, 0, k, n, x, ldx, m, y, ldy, full);
+            if (full == n) return took("matvec_b32_imma", ST_OK);
+            return took("matvec_b32_imma+rows", dtype == DT_Q4_0 ? launch_rows<UnitQ40, true>(s, w, 0, k, n, x, ldx, m, y, ldy, full)
+                                                                 : launch_rows<UnitQ80, true>(s, w, 0, k, n, x, ldx, m, y, ldy, full));
         }
     }
     static const int use_q6k = env_int("SM100_Q6K_IMMA", 1);
@@ -524,7 +533,7 @@ int matvec(cudaStream_t s, int dtype, int layout, const void * w, int64_t w_row_
         if (st != ST_OK) return st;
         if (handled) {
             const int64_t full = (n / 16) * 16;
-            return full == n ? ST_OK : launch_rows<UnitQ6K, true>(s, w, 0, k, n, x, ldx, m, y, ldy, full);
+            return full == n ? took("matvec_q6k_imma", ST_OK) : took("matvec_q6k_imma+rows", launch_rows<UnitQ6K, true>(s, w, 0, k, n, x, ldx, m, y, ldy, full));
         }
     }
     if (use_imma && layout == LAYOUT_PACKED && dtype == DT_Q4_K && x_aligned && m >= 3) {
@@ -546,8 +555,8 @@ int matvec(cudaStream_t s, int dtype, int layout, const void * w, int64_t w_row_
         }
         if (handled) {
             const int64_t full = (n / 16) * 16;
-            if (full < n) return launch_rows<UnitQ4K, true>(s, w, 0, k, n, x, ldx, m, y, ldy, full);
-            return ST_OK;
+            if (full < n) return took("matvec_q4k_imma_cols+rows", launch_rows<UnitQ4K, true>(s, w, 0, k, n, x, ldx, m, y, ldy, full));
+            return took("matvec_q4k_imma_cols", ST_OK);
         }
     }
     static const int use_mma = env_int("SM100_Q4K_MMA", 1);
@@ -568,16 +577,16 @@ int matvec(cudaStream_t s, int dtype, int layout, const void * w, int64_t w_row_
         }
         if (all) {
             const int64_t full = (n / 16) * 16;
-            if (full < n) return launch_rows<UnitQ4K, true>(s, w, 0, k, n, x, ldx, m, y, ldy, full);
-            return ST_OK;
+            if (full < n) return took("matvec_q4k_mma+rows", launch_rows<UnitQ4K, true>(s, w, 0, k, n, x, ldx, m, y, ldy, full));
+            return took("matvec_q4k_mma", ST_OK);
         }
     }
     static const int use_wide = env_int("SM100_MV_WIDE", 1);
     if (use_wide && layout == LAYOUT_PACKED) {
         switch (dtype) {
-            case DT_Q6_K: if (wide_ok<WideQ6K>(k, m)) return launch_wide<WideQ6K>(s, w, k, n, x, y); break;
-            case DT_Q4_0: if (wide_ok<WideQ40>(k, m)) return launch_wide<WideQ40>(s, w, k, n, x, y); break;
-            case DT_Q8_0: if (wide_ok<WideQ80>(k, m)) return launch_wide<WideQ80>(s, w, k, n, x, y); break;
+            case DT_Q6_K: if (wide_ok<WideQ6K>(k, m)) return took("matvec_wide", launch_wide<WideQ6K>(s, w, k, n, x, y)); break;
+            case DT_Q4_0: if (wide_ok<WideQ40>(k, m)) return took("matvec_wide", launch_wide<WideQ40>(s, w, k, n, x, y)); break;
+            case DT_Q8_0: if (wide_ok<WideQ80>(k, m)) return took("matvec_wide", launch_wide<WideQ80>(s, w, k, n, x, y)); break;
         }
     }
     switch (dtype) {
@@ -590,13 +599,14 @@ int matvec(cudaStream_t s, int dtype, int layout, const void * w, int64_t w_row_
             const int per = dtype == DT_F32 ? 4 : 8;
             const bool w_aligned = true;  // ld_u128_any handles any alignment
             if (x_aligned && w_aligned && k % per == 0) {
-                if (dtype == DT_F32) return launch_rows<UnitF32, false>(s, w, w_row_stride, k, n, x, ldx, m, y, ldy);
-                return launch_rows<UnitF16, false>(s, w, w_row_stride, k, n, x, ldx, m, y, ldy);
+                if (dtype == DT_F32) return took("matvec_rows_f32", launch_rows<UnitF32, false>(s, w, w_row_stride, k, n, x, ldx, m, y, ldy));
+                return took("matvec_rows_f16", launch_rows<UnitF16, false>(s, w, w_row_stride, k, n, x, ldx, m, y, ldy));
             }
             const int threads = 256, warps = 8;
             int64_t grid = (n + warps - 1) / warps;
             const int64_t cap = (int64_t) sm_count() * 8;
             if (grid > cap) grid = cap;
+            t_last_kernel = "matvec_scalar";
             if (dtype == DT_F32)
                 return launch(matvec_scalar<DT_F32>, dim3((unsigned) grid), dim3(threads), 0, s, (const uint8_t *) w, w_row_stride, x, ldx, y, ldy, (int) n, (int) k, (int) m);
             return launch(matvec_scalar<DT_F16>, dim3((unsigned) grid), dim3(threads), 0, s, (const uint8_t *) w, w_row_stride, x, ldx, y, ldy, (int) n, (int) k, (int) m);

@@ -84,11 +84,11 @@ __device__ __forceinline__ void bq_quantize_x(const BqArgs & p, uint32_t * xq, f
             if (it >= p.blocks * 8) continue;   // warp-uniform: the item count is a multiple of 32
             const float4 v = xv[i];
             const int sb = it >> 3, q = it & 7;
-            float amax = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
+            uint32_t amax_bits = act_abs_bits(v);
 #pragma unroll
-            for (int o = 1; o < 8; o <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-            const bool some = amax > 1e-30f;   // below that the block counts as zero
-            const float inv = some ? __fdividef(32512.0f, amax) : 0.0f;
+            for (int o = 1; o < 8; o <<= 1) amax_bits = max(amax_bits, __shfl_xor_sync(0xffffffffu, amax_bits, o));
+            float inv, s;
+            act_group_scale(amax_bits, inv, s);
             // round to nearest (even) without the conversion unit: 1.5 * 2^23 + x keeps the integer in the mantissa (|x| <= 32512)
         const int x0 = __float_as_int(fmaf(v.x, inv, 12582912.0f)) - 0x4B400000, x1 = __float_as_int(fmaf(v.y, inv, 12582912.0f)) - 0x4B400000,
                   x2 = __float_as_int(fmaf(v.z, inv, 12582912.0f)) - 0x4B400000, x3 = __float_as_int(fmaf(v.w, inv, 12582912.0f)) - 0x4B400000;
@@ -99,7 +99,7 @@ __device__ __forceinline__ void bq_quantize_x(const BqArgs & p, uint32_t * xq, f
             const int h0 = (x0 + 128) >> 8, h1 = (x1 + 128) >> 8, h2 = (x2 + 128) >> 8, h3 = (x3 + 128) >> 8;
             xq[sb * 16 + q] = __byte_perm(__byte_perm((uint32_t) h0, (uint32_t) h1, 0x0040), __byte_perm((uint32_t) h2, (uint32_t) h3, 0x0040), 0x5410);
             xq[sb * 16 + 8 + q] = __byte_perm(__byte_perm((uint32_t) x0, (uint32_t) x1, 0x0040), __byte_perm((uint32_t) x2, (uint32_t) x3, 0x0040), 0x5410);
-            if (q == 0) xs[sb] = make_float2(some ? amax * (1.0f / 32512.0f) : 0.0f, 8.0f * (float) isum);
+            if (q == 0) xs[sb] = make_float2(s, 8.0f * (float) isum);
         }
     }
 }

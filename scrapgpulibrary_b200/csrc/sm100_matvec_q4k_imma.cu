@@ -142,12 +142,6 @@ __device__ __forceinline__ void imma_16832_zero(int (&c)[4], uint32_t a0, uint32
 constexpr uint32_t IQ_WAIT_LIMIT = 1u << 22;         // polls of one barrier before the warp gives up
 
 __device__ int g_iq_fault;
-#ifdef IQ_TIMING
-__device__ unsigned long long g_iq_t[8];   // development: cycles of CTA 0 per phase, summed over launches; [7] = launches
-#define IQ_T(i) if (blockIdx.x == 0 && threadIdx.x == 0) { const long long now_ = clock64(); atomicAdd(&g_iq_t[i], (unsigned long long) (now_ - t_prev_)); t_prev_ = now_; }
-#else
-#define IQ_T(i)
-#endif
 
 // Shared memory of one CTA:
 //   xq    [M][K/64][128 B]    quantized activations in B-fragment order: per pair [plane h, l][t][low sub-block b0, b1,
@@ -187,10 +181,6 @@ __global__ void __launch_bounds__(IQ_THREADS, NB == 1 ? 2 : 1) matvec_q4k_imma(I
     const int group = wid / IQ_WARPS, warp = wid % IQ_WARPS;
     const int g = lane >> 2, t = lane & 3;
     const int rt_step = gridDim.x * IQ_GROUPS;
-#ifdef IQ_TIMING
-    long long t_prev_ = clock64();
-    if (blockIdx.x == 0 && threadIdx.x == 0) atomicAdd(&g_iq_t[7], 1ull);
-#endif
     const uint32_t bar0 = iq_smem_addr(bars + wid * R);
     const uint32_t hdr0 = iq_smem_addr(hdr) + (uint32_t) wid * R * IQ_HDR_BYTES;
     const uint32_t ring0 = iq_smem_addr(ring) + (uint32_t) wid * R * IQ_SLOT_BYTES;
@@ -233,9 +223,7 @@ __global__ void __launch_bounds__(IQ_THREADS, NB == 1 ? 2 : 1) matvec_q4k_imma(I
         }
     }
 
-    IQ_T(0)   // set-up and first requests
     pdl_wait();
-    IQ_T(1)   // waiting for the predecessor
 
     // activations -> 16-bit integers per 32-element sub-block.  One item = 4 consecutive elements; the 8 items of
     // a sub-block sit in 8 consecutive lanes.
@@ -257,16 +245,15 @@ __global__ void __launch_bounds__(IQ_THREADS, NB == 1 ? 2 : 1) matvec_q4k_imma(I
     auto item_of = [&](int li) { return share ? (((li >> 5) * 2 + (int) cta_rank) << 5) + (li & 31) : li; };
     auto quantize_item = [&](const float4 v, int m, int it) {
         const int sb = it >> 3, q = it & 7;
-        float amax = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
+        uint32_t amax_bits = act_abs_bits(v);
         float sum = (v.x + v.y) + (v.z + v.w);
 #pragma unroll
         for (int o = 1; o < 8; o <<= 1) {
-            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+            amax_bits = max(amax_bits, __shfl_xor_sync(0xffffffffu, amax_bits, o));
             sum += __shfl_xor_sync(0xffffffffu, sum, o);
         }
-        const bool some = amax > 1e-30f;   // below that the block counts as zero
-        const float inv = some ? __fdividef(32512.0f, amax) : 0.0f;
-        const float s = some ? amax * (1.0f / 32512.0f) : 0.0f;
+        float inv, s;
+        act_group_scale(amax_bits, inv, s);
         // 16-bit integer = 256 h + l with h, l signed bytes: h = (x + 128) >> 8, l = x - 256 h
         // round to nearest (even) without the conversion unit: 1.5 * 2^23 + x keeps the integer in the mantissa (|x| <= 32512)
         const int x0 = __float_as_int(fmaf(v.x, inv, 12582912.0f)) - 0x4B400000, x1 = __float_as_int(fmaf(v.y, inv, 12582912.0f)) - 0x4B400000,
@@ -404,7 +391,6 @@ __global__ void __launch_bounds__(IQ_THREADS, NB == 1 ? 2 : 1) matvec_q4k_imma(I
     } else {
         __syncthreads();
     }
-    IQ_T(2)   // activation quantization
     pdl_launch_dependents();
 
     // per-lane views.  Pair j of a block feeds B columns 2j (h plane) and 2j+1 (l plane): lane (g, t) supplies
@@ -484,7 +470,6 @@ __global__ void __launch_bounds__(IQ_THREADS, NB == 1 ? 2 : 1) matvec_q4k_imma(I
             }
             if (++cslot == R) { cslot = 0; cphase ^= 1u; }
         }
-        IQ_T(3)   // chunks of this round (waits included)
         // sum over the four lanes of a row (each held other sub-blocks), then over the warps (each held other chunks)
 #pragma unroll
         for (int m = 0; m < M; ++m) {
@@ -514,7 +499,6 @@ __global__ void __launch_bounds__(IQ_THREADS, NB == 1 ? 2 : 1) matvec_q4k_imma(I
             }
         }
         __syncthreads();
-        IQ_T(4)   // reduction and store of this round
         rt += rt_step;
         chunk = warp;
     }
@@ -546,15 +530,15 @@ __global__ void __launch_bounds__(256) q4k_quantize_cols(const float * x, int64_
         const int sb = it >> 3, q = it & 7;
         float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
         if (m < m_tokens) v = __ldcg(reinterpret_cast<const float4 *>(x + (int64_t) m * ldx + (int64_t) it * 4));
-        float amax = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
+        uint32_t amax_bits = act_abs_bits(v);
         float sum = (v.x + v.y) + (v.z + v.w);
 #pragma unroll
         for (int o = 1; o < 8; o <<= 1) {
-            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+            amax_bits = max(amax_bits, __shfl_xor_sync(0xffffffffu, amax_bits, o));
             sum += __shfl_xor_sync(0xffffffffu, sum, o);
         }
-        const bool some = amax > 1e-30f;
-        const float inv = some ? __fdividef(32512.0f, amax) : 0.0f;
+        float inv, s;
+        act_group_scale(amax_bits, inv, s);
         const int x0 = __float_as_int(fmaf(v.x, inv, 12582912.0f)) - 0x4B400000, x1 = __float_as_int(fmaf(v.y, inv, 12582912.0f)) - 0x4B400000,
                   x2 = __float_as_int(fmaf(v.z, inv, 12582912.0f)) - 0x4B400000, x3 = __float_as_int(fmaf(v.w, inv, 12582912.0f)) - 0x4B400000;
         const int h0 = (x0 + 128) >> 8, h1 = (x1 + 128) >> 8, h2 = (x2 + 128) >> 8, h3 = (x3 + 128) >> 8;
@@ -564,7 +548,7 @@ __global__ void __launch_bounds__(256) q4k_quantize_cols(const float * x, int64_
         const size_t word = ((size_t) m * pairs + (sb >> 1)) * 32 + (q & 3) * 4 + (sb & 1) * 2 + (q >> 2);
         img[word] = hp;
         img[word + 16] = lp;
-        if (q == 0) xs2[(size_t) m * pairs * 2 + sb] = make_float2(some ? amax * (1.0f / 32512.0f) : 0.0f, sum);
+        if (q == 0) xs2[(size_t) m * pairs * 2 + sb] = make_float2(s, sum);
     }
 }
 
@@ -764,22 +748,15 @@ int launch_iq(cudaStream_t s, const IqArgs & a, size_t smem, int grid) {
     return a.blocks % NB == 0 ? launch_iq_full<M, NB, true>(s, a, smem, grid) : launch_iq_full<M, NB, false>(s, a, smem, grid);
 }
 
-std::atomic<bool> g_iq_launched{false};
+std::atomic<bool> g_iq_launched[MAX_DEVICES];   // per device, see sm100_common.cuh
 
 }  // namespace
 
-#ifdef IQ_TIMING
-extern "C" __attribute__((visibility("default"))) int sm100_debug_iq_timing(unsigned long long * out, int reset) {
-    if (cudaMemcpyFromSymbol(out, g_iq_t, sizeof(unsigned long long) * 8) != cudaSuccess) return 4;
-    if (reset) { unsigned long long z[8] = {}; cudaMemcpyToSymbol(g_iq_t, z, sizeof(z)); }
-    return 0;
-}
-#endif
 
 // Reads and clears the kernel's fault flag on the current device (set when a warp gave up waiting for a copy);
 // called after a stream synchronisation.
 int iq_poll_fault() {
-    if (!g_iq_launched.exchange(false, std::memory_order_relaxed)) return ST_OK;
+    if (!g_iq_launched[current_device()].exchange(false, std::memory_order_relaxed)) return ST_OK;
     int v = 0;
     SM100_CUDA(cudaMemcpyFromSymbol(&v, g_iq_fault, sizeof(v)));
     if (v == 0) return ST_OK;
@@ -847,7 +824,7 @@ int matvec_q4k_imma_multi(cudaStream_t s, int count, const void * const * ws, co
     int64_t grid = (int64_t) sm_count() * (nb == 1 ? 2 : 1);   // resident CTAs: each quantizes the activations once
     const int64_t rounds = (tiles + IQ_GROUPS - 1) / IQ_GROUPS;
     if (grid > rounds) grid = rounds;
-    g_iq_launched.store(true, std::memory_order_relaxed);
+    g_iq_launched[current_device()].store(true, std::memory_order_relaxed);
     int st;
     if (nb == 1) st = m == 1 ? launch_iq<1, 1>(s, a, smem, (int) grid) : launch_iq<2, 1>(s, a, smem, (int) grid);
     else st = m == 1 ? launch_iq<1, 2>(s, a, smem, (int) grid) : launch_iq<2, 2>(s, a, smem, (int) grid);
@@ -886,7 +863,7 @@ int matvec_q4k_imma_cols_tiles(cudaStream_t s, const void * w, int64_t k, int64_
     int64_t grid = sm_count();
     const int64_t rounds = (tiles + IQ_GROUPS - 1) / IQ_GROUPS;
     if (grid > rounds) grid = rounds;
-    g_iq_launched.store(true, std::memory_order_relaxed);
+    g_iq_launched[current_device()].store(true, std::memory_order_relaxed);
     const int mt = 4 * mg;
     void * img = nullptr;
     int st = device_scratch(2, (size_t) mt * pairs * 144, &img);

@@ -67,11 +67,11 @@ __device__ __forceinline__ void sq_quantize_x(const SqArgs & p, uint32_t * xq, f
             if (it >= ngroups * 4) continue;   // warp-uniform: the item count is a multiple of 32
             const float4 v = xv[i];
             const int grp = it >> 2, q = it & 3;
-            float amax = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
-            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-            const bool some = amax > 1e-30f;   // below that the group counts as zero
-            const float inv = some ? __fdividef(32512.0f, amax) : 0.0f;
+            uint32_t amax_bits = act_abs_bits(v);
+            amax_bits = max(amax_bits, __shfl_xor_sync(0xffffffffu, amax_bits, 1));
+            amax_bits = max(amax_bits, __shfl_xor_sync(0xffffffffu, amax_bits, 2));
+            float inv, s;
+            act_group_scale(amax_bits, inv, s);
             // round to nearest (even) without the conversion unit: 1.5 * 2^23 + x keeps the integer in the mantissa (|x| <= 32512)
         const int x0 = __float_as_int(fmaf(v.x, inv, 12582912.0f)) - 0x4B400000, x1 = __float_as_int(fmaf(v.y, inv, 12582912.0f)) - 0x4B400000,
                   x2 = __float_as_int(fmaf(v.z, inv, 12582912.0f)) - 0x4B400000, x3 = __float_as_int(fmaf(v.w, inv, 12582912.0f)) - 0x4B400000;
@@ -82,7 +82,7 @@ __device__ __forceinline__ void sq_quantize_x(const SqArgs & p, uint32_t * xq, f
             const int h0 = (x0 + 128) >> 8, h1 = (x1 + 128) >> 8, h2 = (x2 + 128) >> 8, h3 = (x3 + 128) >> 8;
             xq[grp * 8 + q] = __byte_perm(__byte_perm((uint32_t) h0, (uint32_t) h1, 0x0040), __byte_perm((uint32_t) h2, (uint32_t) h3, 0x0040), 0x5410);
             xq[grp * 8 + 4 + q] = __byte_perm(__byte_perm((uint32_t) x0, (uint32_t) x1, 0x0040), __byte_perm((uint32_t) x2, (uint32_t) x3, 0x0040), 0x5410);
-            if (q == 0) xs[grp] = make_float2(some ? amax * (1.0f / 32512.0f) : 0.0f, __int_as_float(32 * isum));
+            if (q == 0) xs[grp] = make_float2(s, __int_as_float(32 * isum));
         }
     }
 }

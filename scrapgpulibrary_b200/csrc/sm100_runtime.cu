@@ -32,6 +32,12 @@ int cuda_fail(cudaError_t e, const char * what) {
 bool pdl_enabled() { return g_pdl.load(std::memory_order_relaxed) != 0; }
 void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
 
+int current_device() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) { (void) cudaGetLastError(); return 0; }
+    return dev < 0 || dev >= MAX_DEVICES ? 0 : dev;
+}
+
 int sm_count() {
     static std::mutex mu;
     static std::vector<int> cache;
@@ -48,11 +54,16 @@ int sm_count() {
 }
 
 // Per-device scratch owned by the library, one buffer per slot (0 = attention partials, 1 = GEMM
-// activations, 2 = quantized activation columns of the multi-column matvec), grown on demand and never shrunk.  Calls that use the same slot must be ordered on one
-// stream; growing frees the old buffer, which waits for the device to go idle.
+// activations, 2 = quantized activation columns of the multi-column matvec), grown on demand.  A buffer that was
+// handed out once is NEVER freed or moved: a CUDA graph captured earlier has its address baked into its kernel
+// nodes and may be replayed at any time.  Growing therefore allocates a second, larger block (at least twice the
+// old size, so the blocks left behind add up to less than the live one) and later calls use that; replays of older
+// graphs keep working on the block they were captured with.  Calls that use the same slot must be ordered on one
+// stream.  Allocation cannot happen while a stream is capturing: the first call of a shape (or sm100_scratch_reserve)
+// has to come before the capture.
 int device_scratch(int slot, size_t bytes, void ** out) {
     constexpr int SLOTS = 3;
-    struct Entry { void * ptr[SLOTS] = {nullptr, nullptr, nullptr}; size_t size[SLOTS] = {0, 0, 0}; };
+    struct Entry { void * ptr[SLOTS] = {nullptr, nullptr, nullptr}; size_t size[SLOTS] = {0, 0, 0}; std::vector<void *> retired; };
     static std::mutex mu;
     static std::vector<Entry> table;
     if (slot < 0 || slot >= SLOTS) return fail(ST_INVALID, "device_scratch: bad slot");
@@ -62,18 +73,19 @@ int device_scratch(int slot, size_t bytes, void ** out) {
     if ((int) table.size() <= dev) table.resize(dev + 1);
     Entry & e = table[dev];
     if (e.size[slot] < bytes) {
-        if (e.ptr[slot] != nullptr) SM100_CUDA(cudaFree(e.ptr[slot]));
-        e.ptr[slot] = nullptr;
-        e.size[slot] = 0;
-        const size_t want = bytes < (size_t) (8u << 20) ? (size_t) (8u << 20) : bytes;
-        const cudaError_t me = cudaMalloc(&e.ptr[slot], want);
+        size_t want = bytes < (size_t) (8u << 20) ? (size_t) (8u << 20) : bytes;
+        if (want < 2 * e.size[slot]) want = 2 * e.size[slot];
+        void * fresh = nullptr;
+        const cudaError_t me = cudaMalloc(&fresh, want);
         if (me == cudaErrorStreamCaptureUnsupported || me == cudaErrorStreamCaptureInvalidated) {
             (void) cudaGetLastError();
             return fail(ST_BACKEND, "the library's scratch buffer for this op does not exist yet (or is too small) and cannot be allocated while a "
                                     "stream is capturing: issue the same call once outside the capture first");
         }
         if (me != cudaSuccess) return cuda_fail(me, "cudaMalloc(scratch)");
-        SM100_CUDA(cudaMemset(e.ptr[slot], 0, want));   // the attention kernels keep counters in it that start at zero
+        SM100_CUDA(cudaMemset(fresh, 0, want));   // the attention kernels keep counters in it that start at zero
+        if (e.ptr[slot] != nullptr) e.retired.push_back(e.ptr[slot]);   // stays allocated: earlier graphs may still name it
+        e.ptr[slot] = fresh;
         e.size[slot] = want;
     }
     *out = e.ptr[slot];
@@ -82,6 +94,24 @@ int device_scratch(int slot, size_t bytes, void ** out) {
 
 int gemm_poll_fault();
 int iq_poll_fault();
+
+// Waits for the stream, then reads the fault words of the kernels with bounded waits on the STREAM's device (they are
+// per-device variables; the current device may be another one in a process that drives several GPUs).
+static int sync_and_poll(cudaStream_t st) {
+    SM100_CUDA(cudaStreamSynchronize(st));
+    int cur = 0, dev = 0;
+    SM100_CUDA(cudaGetDevice(&cur));
+    dev = cur;
+    if (st != nullptr && cudaStreamGetDevice(st, &dev) != cudaSuccess) {
+        (void) cudaGetLastError();
+        dev = cur;
+    }
+    if (dev != cur) SM100_CUDA(cudaSetDevice(dev));
+    int r = gemm_poll_fault();
+    if (r == ST_OK) r = iq_poll_fault();
+    if (dev != cur) (void) cudaSetDevice(cur);
+    return r;
+}
 
 }  // namespace sm100
 
@@ -163,11 +193,7 @@ int sm100_stream_destroy(int device, sm100_stream_t stream) {
     return ST_OK;
 }
 
-int sm100_stream_sync(sm100_stream_t stream) {
-    SM100_CUDA(cudaStreamSynchronize((cudaStream_t) stream));
-    const int st = gemm_poll_fault();
-    return st != ST_OK ? st : iq_poll_fault();
-}
+int sm100_stream_sync(sm100_stream_t stream) { return sync_and_poll((cudaStream_t) stream); }
 
 int sm100_memcpy_h2d(sm100_stream_t s, void * dst, const void * src, size_t n, int blocking) {
     if (n == 0) return ST_OK;
@@ -179,7 +205,9 @@ int sm100_memcpy_h2d(sm100_stream_t s, void * dst, const void * src, size_t n, i
 int sm100_memcpy_d2h(sm100_stream_t s, void * dst, const void * src, size_t n, int blocking) {
     if (n == 0) return ST_OK;
     SM100_CUDA(cudaMemcpyAsync(dst, src, n, cudaMemcpyDeviceToHost, (cudaStream_t) s));
-    if (blocking) SM100_CUDA(cudaStreamSynchronize((cudaStream_t) s));
+    // a blocking read makes results visible like a stream_sync does (include/scrapgpu/op.h:190-194), so a kernel that
+    // gave up on a bounded wait is reported here too instead of handing out an incomplete result with status OK
+    if (blocking) return sync_and_poll((cudaStream_t) s);
     return ST_OK;
 }
 
@@ -287,6 +315,11 @@ int sm100_graph_destroy(sm100_graph_t g) {
 }
 
 uint64_t sm100_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
+int sm100_scratch_reserve(int slot, size_t bytes) {
+    void * p = nullptr;
+    return device_scratch(slot, bytes, &p);
+}
 
 int sm100_set_pdl(int enabled) {
     g_pdl.store(enabled ? 1 : 0, std::memory_order_relaxed);

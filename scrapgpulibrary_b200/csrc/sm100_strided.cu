@@ -312,6 +312,37 @@ __global__ void __launch_bounds__(1024) top1_view_kernel(V4 x, V4 out) {
     }
 }
 
+// CONT_MUL_MAT (include/scrapgpu/op.h:47; input order src/backends/opencl11/api.cpp:11-12; reference kernels
+// attn.cl:123-237): dst[i1, 0, i2, i3] = sum_i0 a[i0, i1, i2 / r2, i3 / r3] * x[i0, 0, i2, i3] where `a` is the
+// transposed view a CONT would have copied first (its dim 1 is the contiguous one: the P.V product of attention over
+// a V cache stored [head][position][dim] or [position][head][dim]).  A CTA takes 32 consecutive i1 (the 32 lanes of
+// a warp read 32 consecutive elements of `a`) and splits i0 over its 8 warps; f32 accumulation.
+__global__ void __launch_bounds__(256) cont_mul_mat_kernel(V4 a, int a_f16, V4 x, V4 y, int64_t r2, int64_t r3) {
+    pdl_wait();
+    pdl_launch_dependents();
+    __shared__ float red[8][33];
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+    const int64_t i1 = (int64_t) blockIdx.x * 32 + tx;
+    const int64_t i2 = blockIdx.y % x.ne[2], i3 = blockIdx.y / x.ne[2];
+    float acc = 0.f;
+    if (i1 < a.ne[1]) {
+        const char * ap = a.p + i1 * a.nb[1] + (i2 / r2) * a.nb[2] + (i3 / r3) * a.nb[3];
+        const char * xp = x.p + i2 * x.nb[2] + i3 * x.nb[3];
+        for (int64_t i0 = ty; i0 < a.ne[0]; i0 += 8) {
+            const float av = a_f16 ? __half2float(*(const __half *) (ap + i0 * a.nb[0])) : *(const float *) (ap + i0 * a.nb[0]);
+            acc = fmaf(av, *(const float *) (xp + i0 * x.nb[0]), acc);
+        }
+    }
+    red[ty][tx] = acc;
+    __syncthreads();
+    if (ty == 0 && i1 < a.ne[1]) {
+        float v = 0.f;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) v += red[w][tx];
+        *(float *) (y.p + i1 * y.nb[0] + i2 * y.nb[2] + i3 * y.nb[3]) = v;
+    }
+}
+
 static unsigned grid_cap(int64_t n, int threads) {
     int64_t g = (n + threads - 1) / threads;
     const int64_t cap = (int64_t) sm_count() * 16;
@@ -404,6 +435,19 @@ int sm100_top1_view(sm100_stream_t s, const sm100_view * x, const sm100_view * o
     const int64_t rows = vx.ne[1] * vx.ne[2] * vx.ne[3];
     if (rows > INT32_MAX) return fail(ST_UNSUPPORTED, "top_k: too many rows");
     return launch(top1_view_kernel, dim3((unsigned) rows), dim3(1024), 0, (cudaStream_t) s, vx, vo);
+}
+
+int sm100_cont_mul_mat(sm100_stream_t s, const sm100_view * a, int a_dtype, const sm100_view * x, const sm100_view * y) {
+    if (a == nullptr || x == nullptr || y == nullptr || a->data == nullptr || x->data == nullptr || y->data == nullptr) return fail(ST_INVALID, "cont_mul_mat: null view");
+    if (a_dtype != DT_F16 && a_dtype != DT_F32) return fail(ST_UNSUPPORTED, "cont_mul_mat: the transposed view must be F16 or F32");
+    const V4 va = load_view(a), vx = load_view(x), vy = load_view(y);
+    if (vx.ne[1] != 1 || vx.ne[0] != va.ne[0] || vx.ne[2] % va.ne[2] != 0 || vx.ne[3] % va.ne[3] != 0)
+        return fail(ST_INVALID, "cont_mul_mat: x must be one column [a.ne0, 1, n2, n3] with n2, n3 multiples of a's");
+    if (vy.ne[0] != va.ne[1] || vy.ne[1] != 1 || vy.ne[2] != vx.ne[2] || vy.ne[3] != vx.ne[3]) return fail(ST_INVALID, "cont_mul_mat: dst must be [a.ne1, 1, x.ne2, x.ne3]");
+    const int64_t outer = vx.ne[2] * vx.ne[3], tiles = (va.ne[1] + 31) / 32;
+    if (outer > 65535 || tiles > INT32_MAX) return fail(ST_UNSUPPORTED, "cont_mul_mat: too many slices");
+    return launch(cont_mul_mat_kernel, dim3((unsigned) tiles, (unsigned) outer), dim3(256), 0, (cudaStream_t) s, va, a_dtype == DT_F16 ? 1 : 0, vx, vy,
+                  vx.ne[2] / va.ne[2], vx.ne[3] / va.ne[3]);
 }
 
 }  // extern "C"

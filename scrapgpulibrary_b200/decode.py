@@ -53,6 +53,70 @@ class DecodeConfig:
         return layer < n // 8 or layer >= 7 * n // 8 or (layer - n // 8) % 3 == 2
 
 
+class SyntheticWeights:
+    """A seeded synthetic model of a DecodeConfig's shapes, defined GLOBALLY (unsharded) and independent of rank
+    and world size, so that every tensor-parallel layout shards the same model and the CPU oracle can run it too.
+
+    Behaves like the `weights` mapping of DecodeModel / oracle.decode_ref: name -> (dtype, natural blocks [N, row_bytes],
+    K) for matrices, name -> float32 vector for norm gains.  Real GGUF files are not available offline; generating
+    8 G distinct weights per rank would take minutes, so a matrix is built from one base matrix per (dtype, shape) --
+    valid blocks of seeded N(0, 0.02) weights (synth.py) -- whose rows are rotated by a per-name amount; where a matrix
+    has more rows than its base (embedding, vocabulary head), each repetition of the base gets its own low bits in the
+    blocks' f16 scale, so no two rows of the matrix are equal (equal rows would tie in the greedy arg-max)."""
+
+    BASE_ROWS = 16384
+
+    def __init__(self, cfg: DecodeConfig, seed: int = 0x5CA9):
+        self.cfg, self.seed = cfg, seed
+        self._base = {}
+        c = cfg
+        self.shapes = {"embed": (Q4_K, c.vocab, c.hidden), "head": (Q6_K, c.vocab, c.hidden)}
+        rng = np.random.default_rng(seed + 17)
+        self.vectors = {}
+        for i in range(c.layers):
+            vdt = Q6_K if c.more_bits(i) else Q4_K
+            for nm, n in (("attn_norm", c.hidden), ("ffn_norm", c.hidden), ("q_norm", c.head_dim), ("k_norm", c.head_dim)):
+                self.vectors[f"l{i}.{nm}"] = (1.0 + 0.1 * rng.standard_normal(n)).astype(np.float32)
+            self.shapes[f"l{i}.wq"] = (Q4_K, c.heads * c.head_dim, c.hidden)
+            self.shapes[f"l{i}.wk"] = (Q4_K, c.kv_heads * c.head_dim, c.hidden)
+            self.shapes[f"l{i}.wv"] = (vdt, c.kv_heads * c.head_dim, c.hidden)
+            self.shapes[f"l{i}.wo"] = (Q4_K, c.hidden, c.heads * c.head_dim)
+            self.shapes[f"l{i}.wgate"] = (Q4_K, c.ffn, c.hidden)
+            self.shapes[f"l{i}.wup"] = (Q4_K, c.ffn, c.hidden)
+            self.shapes[f"l{i}.wdown"] = (vdt, c.hidden, c.ffn)
+        self.vectors["out_norm"] = (1.0 + 0.1 * rng.standard_normal(c.hidden)).astype(np.float32)
+
+    def __contains__(self, name) -> bool:
+        return name in self.shapes or name in self.vectors
+
+    def _base_matrix(self, dtype: int, n: int, k: int) -> np.ndarray:
+        key = (dtype, min(n, self.BASE_ROWS), k)
+        if key not in self._base:
+            self._base[key] = synth.quantized_matrix(dtype, (self.seed * 31 + dtype * 7 + key[1] * 3 + k) % (1 << 31), key[1], k)
+        return self._base[key]
+
+    def rows(self, name: str, lo: int, count: int) -> np.ndarray:
+        """Rows [lo, lo + count) of the global matrix `name` (natural blocks)."""
+        dtype, n, k = self.shapes[name]
+        base = self._base_matrix(dtype, n, k)
+        rot = (zlib.crc32(name.encode()) % 977) * 3
+        src = (np.arange(lo, lo + count, dtype=np.int64) - rot) % n      # row of the unrotated tiling
+        out = base[src % base.shape[0]]                                    # a copy (fancy indexing)
+        if n > base.shape[0]:
+            be, bb = tp.BLOCK[dtype]
+            d_at = 0 if dtype == Q4_K else bb - 2                          # byte offset of the block's f16 scale d
+            blocks = out.reshape(count, k // be, bb)
+            rep = (src // base.shape[0]).astype(np.uint8)                  # < 16 for every shape in use
+            blocks[:, :, d_at] = (blocks[:, :, d_at] & 0xF0) | rep[:, None]
+        return out
+
+    def __getitem__(self, name):
+        if name in self.vectors:
+            return self.vectors[name]
+        dtype, n, k = self.shapes[name]
+        return dtype, self.rows(name, 0, n), k
+
+
 def _dev(t: torch.Tensor) -> C.c_void_p:
     return C.c_void_p(t.data_ptr())
 
@@ -72,9 +136,12 @@ class Weight:
 class DecodeModel:
     def __init__(self, cfg: DecodeConfig, rank: int = 0, world: int = 1, device_index: int = 0, seed: int = 0x5CA9,
                  weights: dict | None = None, allreduce=None, fuse: bool = True):
-        """weights: optional dict name -> (dtype, natural uint8 [N_global, row_bytes], K_global) with GLOBAL matrices
-        (sharded here); otherwise seeded synthetic shards are generated per rank.  allreduce / allgather: callables
-        on torch tensors (default: torch.distributed when world > 1)."""
+        """weights: mapping name -> (dtype, natural uint8 [N_global, row_bytes], K_global) with GLOBAL matrices (sharded
+        here) and name -> f32 vector for the norm gains; default: SyntheticWeights(cfg, seed), the same global model
+        for every rank and world size.  allreduce: callable on a torch tensor (default: torch.distributed when
+        world > 1)."""
+        if weights is None:
+            weights = SyntheticWeights(cfg, seed)
         assert cfg.heads % cfg.kv_heads == 0 and cfg.kv_heads % world == 0 and cfg.ffn % (256 * world) == 0
         self.cfg, self.rank, self.world = cfg, rank, world
         self.device = torch.device("cuda", device_index)
@@ -91,7 +158,6 @@ class DecodeModel:
         self.q_dim, self.kv_dim, self.ffn = self.hq * c.head_dim, self.hkv * c.head_dim, c.ffn // world
         self.vocab_lo, self.vocab_n = tp.vocab_shard(c.vocab, rank, world)
         self.weight_bytes = 0
-        self._base = {}
         f32 = dict(dtype=torch.float32, device=self.device)
         with torch.cuda.stream(self.tstream):
             self.embed = self._weight("embed", Q4_K, c.vocab, c.hidden, weights, seed, shard=None)
@@ -166,7 +232,17 @@ class DecodeModel:
 
     def _weight(self, name, dtype, n_global, k_global, weights, seed, shard):
         """shard: None (replicated), ("rows", n_local[, lo]) or ("cols", k_local)."""
-        if weights is not None and name in weights:
+        if isinstance(weights, SyntheticWeights):
+            dt, n_all, kg = weights.shapes[name]
+            assert dt == dtype and kg == k_global and n_all == n_global
+            if shard is not None and shard[0] == "rows":
+                lo = shard[2] if len(shard) > 2 else self.rank * shard[1]
+                loc, k = weights.rows(name, lo, shard[1]), k_global      # only this rank's rows are materialised
+            elif shard is None:
+                loc, k = weights.rows(name, 0, n_global), k_global
+            else:
+                loc, k = tp.shard_cols(weights.rows(name, 0, n_global), dtype, k_global, self.rank, shard[1]), shard[1]
+        else:
             dt, nat, kg = weights[name]
             assert dt == dtype and kg == k_global
             nat = np.asarray(nat)
@@ -177,19 +253,6 @@ class DecodeModel:
                 loc, k = tp.shard_rows(nat, lo, shard[1]), k_global
             else:
                 loc, k = tp.shard_cols(nat, dtype, k_global, self.rank, shard[1]), shard[1]
-        else:
-            if shard is None:
-                n, k = n_global, k_global
-            elif shard[0] == "rows":
-                n, k = shard[1], k_global
-            else:
-                n, k = n_global, shard[1]
-            key = (dtype, n, k)
-            if key not in self._base:      # one synthetic matrix per (dtype, shape); layers use row rotations of it
-                self._base[key] = synth.quantized_matrix(dtype, seed * 31 + self.rank + len(self._base), min(n, 16384), k)
-            base = self._base[key]
-            reps = -(-n // base.shape[0])
-            loc = np.roll(np.tile(base, (reps, 1))[:n], (zlib.crc32(name.encode()) % 977) * 3, axis=0) if n > 0 else base[:0]
         if loc.shape[0] == 0:
             return None
         w = Weight(self, dtype, loc, k)

@@ -47,3 +47,26 @@ def test_decode_matches_oracle_tokens_and_logits(sm100):
     load_prefill()
     model.run(steps)
     assert np.array_equal(model.tokens(steps), want_tokens)
+
+
+def test_full_shape_decode_tokens_match_oracle(sm100):
+    """The benchmark's decode configuration at full shape (36 layers, hidden 4096, 32 / 8 heads of 128, FFN 12288,
+    vocabulary 151936, KV cache pre-filled to 1024): the first greedy tokens of the GPU stack, eager and under graph
+    replay, equal the CPU oracle's on the same rank-independent synthetic model.  The oracle's tokens are the
+    committed list tests/golden/decode_qwen3_8b_shape.json (generator: tests/golden/make_decode_golden.py; one token
+    costs the oracle seconds on all host cores)."""
+    import json
+    import os
+    from scrapgpulibrary_b200.decode import DecodeConfig, DecodeModel
+    gold = json.load(open(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "decode_qwen3_8b_shape.json")))
+    want = gold["tokens"]
+    assert len(want) >= 4
+    model = DecodeModel(DecodeConfig(), seed=gold["seed"])
+    model.reset(token=gold["first_token"], prefill_seed=gold["prefill_seed"])
+    model.run(len(want))
+    assert model.tokens(len(want)).tolist() == want
+    model.reset(token=gold["first_token"], prefill_seed=gold["prefill_seed"])
+    model.capture()     # runs one eager token, then records the step
+    model.reset(token=gold["first_token"], prefill_seed=gold["prefill_seed"])
+    model.run(len(want))
+    assert model.tokens(len(want)).tolist() == want

@@ -37,3 +37,22 @@ def test_tp2_decode_tokens_match_oracle(sm100, tmp_path, exchange):
     assert got["world"] == 2 and got["fault"] == 0
     assert got["eager"] == want.tolist()
     assert got["replay"] == want.tolist()
+
+
+def test_tp2_full_shape_tokens_match_oracle(sm100, tmp_path):
+    """The benchmark's full decode configuration split over 2 GPUs (own peer all-reduce): the same greedy tokens as
+    the CPU oracle's committed list, i.e. as the single-GPU run of test_decode_gpu.py -- one global model, sharded."""
+    if sm100.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    gold = json.load(open(os.path.join(ROOT, "tests", "golden", "decode_qwen3_8b_shape.json")))
+    steps = len(gold["tokens"])
+    out = tmp_path / "tokens_full.json"
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+                        "--master-port", "29735", os.path.join(ROOT, "tests", "tp_decode_worker.py"), str(out), str(steps), "peer", "full"],
+                       capture_output=True, text=True, timeout=1200, env=env)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-4000:]
+    got = json.loads(out.read_text())
+    assert got["world"] == 2 and got["fault"] == 0
+    assert got["eager"] == gold["tokens"]
+    assert got["replay"] == gold["tokens"]

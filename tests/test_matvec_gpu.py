@@ -81,6 +81,130 @@ def test_matvec_benchmark_shapes(sm100, stream, dtype, k, n):
     assert sgref.nmse(gnat, want[:1]) <= TOL
 
 
+# ---- every branch of the dispatcher, every benchmark shape, hostile activations -------------------------------------
+
+def _kernel(sm100):
+    return (sm100.lib().sm100_matvec_last_kernel() or b"").decode()
+
+
+# environment that switches kernel families off -> the "dtype:kernel" names that must then have served some case
+FORCED = [
+    ({}, ["q4_k:matvec_q4k_imma", "q4_k:matvec_q4k_imma+rows", "q6_k:matvec_q6k_imma", "q4_0:matvec_b32_imma", "q8_0:matvec_b32_imma"]),
+    ({"SM100_Q6K_IMMA": "0", "SM100_B32_IMMA": "0"}, ["q6_k:matvec_wide", "q4_0:matvec_wide", "q8_0:matvec_wide", "q6_k:matvec_rows"]),
+    ({"SM100_Q4K_IMMA": "0"}, ["q4_k:matvec_q4k_mma", "q4_k:matvec_q4k_mma+rows"]),
+    ({"SM100_Q4K_IMMA": "0", "SM100_Q4K_MMA": "0", "SM100_Q6K_IMMA": "0", "SM100_B32_IMMA": "0", "SM100_MV_WIDE": "0"},
+     ["q4_k:matvec_stream", "q6_k:matvec_stream", "q4_0:matvec_stream", "q8_0:matvec_stream", "q4_k:matvec_rows", "q8_0:matvec_rows"]),
+]
+
+
+@pytest.mark.parametrize("env,expected", FORCED, ids=["default", "no_q6k_b32_imma", "no_q4k_imma", "cuda_core_only"])
+def test_matvec_forced_branches(env, expected):
+    """Each kernel family of the dispatcher (sm100_matvec.cu) is reached by name and agrees with the oracle: the
+    families behind the default one serve the shapes the default declines, so they are tested by switching the
+    families in front of them off in a child process (the switches are read once per process)."""
+    import json
+    import os
+    import subprocess
+    import sys
+    worker = os.path.join(os.path.dirname(os.path.abspath(__file__)), "matvec_branch_worker.py")
+    r = subprocess.run([sys.executable, worker], capture_output=True, text=True, timeout=900, env=dict(os.environ, **env))
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    out = json.loads(r.stdout.strip().splitlines()[-1])
+    assert out["worst"] <= TOL, out
+    for name in expected:
+        assert name in out["kernels"], (name, out["kernels"])
+
+
+@pytest.mark.parametrize("dtype,k,n", [(U.Q6_K, 4096, 12288), (U.Q6_K, 12288, 4096), (U.Q4_K, 4096, 4096), (U.Q4_K, 4096, 12288), (U.Q4_K, 12288, 4096)],
+                         ids=["q6_k_4096x12288", "q6_k_12288x4096", "q4_k_4096x4096", "q4_k_4096x12288", "q4_k_12288x4096"])
+def test_matvec_sweep_shapes_every_batch(sm100, stream, dtype, k, n):
+    """The Q4_K / Q6_K projection shapes of the benchmark sweep at full size for every batch it names (M = 1, 2, 4, 8;
+    each M is a kernel or a template of its own), every column on its own against the oracle."""
+    wq = U.quantize(dtype, U.seeded_weights(77 + dtype + n, n, k))
+    x = U.seeded_acts(5 + k, 8, k)
+    want = sgref.mul_mat(dtype, wq, k, x)
+    served = {}
+    for m in (1, 2, 4, 8):
+        got = U.device_mul_mat(sm100, stream, dtype, U.PACKED, wq, k, x[:m])
+        served[m] = _kernel(sm100)
+        assert np.isfinite(got).all()
+        for c in range(m):
+            e = sgref.nmse(got[c], want[c])
+            assert e <= TOL, f"{U.NAMES[dtype]} K={k} N={n} M={m} column {c} ({served[m]}): NMSE {e:.3e}"
+    print(U.NAMES[dtype], k, n, served)
+
+
+def test_matvec_vocabulary_head(sm100, stream):
+    """The Q6_K output head of the decode stack, K = 4096, N = 151936 (510 MB), M = 1: every row against the oracle,
+    and the first and the last 16-row tile on their own."""
+    from scrapgpulibrary_b200 import synth
+    k, n = 4096, 151936
+    wq = synth.quantized_matrix(U.Q6_K, 1234, n, k)   # valid Q6_K blocks of seeded N(0, 0.02) weights (min/max rule)
+    x = U.seeded_acts(31, 1, k)
+    want = sgref.mul_mat(U.Q6_K, wq, k, x)
+    got = U.device_mul_mat(sm100, stream, U.Q6_K, U.PACKED, wq, k, x)
+    name = _kernel(sm100)
+    assert np.isfinite(got).all()
+    assert sgref.nmse(got, want) <= TOL, name
+    for lo, hi in ((0, 16), (n - 16, n), (n // 2, n // 2 + 512)):
+        assert sgref.nmse(got[0, lo:hi], want[0, lo:hi]) <= TOL, (name, lo)
+    assert int(np.argmax(got[0])) == int(np.argmax(want[0]))
+    print("head served by", name)
+
+
+def _quantization_bound(dtype, wq, k, x, group):
+    """Largest error the 16-bit activation image can cause per output row: every group of `group` activations is
+    rounded to multiples of amax / 32512, i.e. off by at most amax / 65024 per element (groups below 1e-30 count as
+    zero), times the row's weight magnitudes; plus the f32 accumulation of |w x|."""
+    w = np.abs(sgref.dequantize(dtype, wq, k).astype(np.float64))
+    ax = np.abs(x.astype(np.float64)).reshape(-1, group)
+    amax = ax.max(axis=1)
+    per_elem = np.repeat(np.where(amax > 1e-30, amax / 65024.0, amax), group)
+    return w @ per_elem + 4e-6 * (w @ np.abs(x.astype(np.float64))) + 1e-30
+
+
+@pytest.mark.parametrize("dtype,group", [(U.Q4_K, 32), (U.Q6_K, 16), (U.Q4_0, 32), (U.Q8_0, 32)], ids=lambda v: U.NAMES.get(v, str(v)))
+def test_matvec_hostile_activations(sm100, stream, dtype, group):
+    """Activations the integer kernels could get wrong: one 1e7 outlier inside a block of ordinary values, an
+    all-zero block beside it, a block at 1e-30, a block of alternating huge values that cancel.  Checked per
+    output row against a bound derived from the activation format, not only as an NMSE."""
+    k, n = 4096, 272
+    wq = U.quantize(dtype, U.seeded_weights(600 + dtype, n, k))
+    x = U.seeded_acts(8, 1, k)
+    x[0, 5] = 1e7
+    x[0, 32:64] = 0.0
+    x[0, 64:96] *= 1e-30
+    x[0, 96:128] = np.where(np.arange(32) % 2 == 0, 3e6, -3e6).astype(np.float32)
+    x[0, 4000:4032] *= 1e-12
+    want = sgref.mul_mat(dtype, wq, k, x).astype(np.float64)
+    got = U.device_mul_mat(sm100, stream, dtype, U.PACKED, wq, k, x).astype(np.float64)
+    name = _kernel(sm100)
+    assert np.isfinite(got).all(), name
+    bound = _quantization_bound(dtype, wq, k, x[0], group)
+    excess = np.abs(got[0] - want[0]) / bound
+    assert excess.max() <= 1.05, f"{name}: row {int(excess.argmax())} is {excess.max():.2f}x the format's error bound"
+    assert sgref.nmse(got, want) <= TOL
+
+
+@pytest.mark.parametrize("dtype", U.QUANT, ids=lambda d: U.NAMES[d])
+@pytest.mark.parametrize("m", [1, 4], ids=["m1", "m4"])
+def test_matvec_nan_and_inf_propagate(sm100, stream, dtype, m):
+    """A NaN or an infinity among the activations makes every output of that column non-finite in the reference
+    (f32 dot product, src/core/ref/ops.cpp:968-980); the device must not hand out finite numbers instead.  The other
+    columns stay exact."""
+    k, n = 4096, 48
+    wq = U.quantize(dtype, U.seeded_weights(700 + dtype, n, k))
+    for bad in (np.nan, np.inf, -np.inf):
+        x = U.seeded_acts(9, m, k)
+        x[0, 1234] = bad
+        want = sgref.mul_mat(dtype, wq, k, x)
+        got = U.device_mul_mat(sm100, stream, dtype, U.PACKED, wq, k, x)
+        assert not np.isfinite(want[0]).any()
+        assert not np.isfinite(got[0]).any(), (_kernel(sm100), bad)
+        if m > 1:
+            assert sgref.nmse(got[1:], want[1:]) <= TOL
+
+
 def test_matvec_argument_errors(sm100, stream):
     buf = sm100.Buffer(1 << 16)
     with pytest.raises(sm100.Sm100Error) as e:

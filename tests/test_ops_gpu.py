@@ -226,6 +226,49 @@ def test_attention_masks(sm100, stream):
     assert np.all(got[:, 1] == 0.0)
 
 
+def test_attention_graph_survives_scratch_growth(sm100, stream):
+    """A captured graph names the library's scratch block by address.  A later, larger call makes the library
+    allocate a bigger block; the earlier block must stay valid (it is never freed or moved), so a replay of the
+    graph afterwards still gives the right result."""
+    import ctypes as C
+    lib = sm100.lib()
+    hq, hkv, d, nk = 32, 8, 128, 1152
+    rng = np.random.default_rng(12)
+    q = rng.standard_normal((hq, 1, d)).astype(np.float32)
+    k = rng.standard_normal((hkv, nk, d)).astype(np.float32)
+    v = rng.standard_normal((hkv, nk, d)).astype(np.float32)
+    scale = float(1.0 / np.sqrt(d))
+    want = sgref.attention(q, k, v, True, 1100, scale)
+    qb, kb, vb = (U.to_device(sm100, stream, a) for a in (q, k, v))
+    ob, optr = U.guarded_output(sm100, stream, hq * d)
+
+    def enqueue():
+        sm100.check(lib.sm100_attention(stream.handle, qb.at(), kb.at(), vb.at(), None, 1, C.c_void_p(optr), d, d, 1, nk, hq, hkv, 1, 1100, None, scale), "attention")
+    enqueue()              # outside the capture: the scratch block comes into being
+    stream.sync()
+    with sm100.Graph(stream) as g:
+        enqueue()
+    g.launch()
+    stream.sync()
+    assert sgref.nmse(U.read_guarded(sm100, stream, ob, hq * d).reshape(hq, 1, d), want) <= TOL
+    # a prefill-sized call: 640 queries x 32 heads x (128 + 4) floats per split is beyond the 8 MiB the first block has
+    nq2 = 640
+    q2 = rng.standard_normal((hq, nq2, d)).astype(np.float32)
+    got2 = run_attention(sm100, stream, q2, k[:, :256], v[:, :256], True, 0, scale)
+    assert sgref.nmse(got2, sgref.attention(q2, k[:, :256], v[:, :256], True, 0, scale)) <= TOL
+    # dirty everything the allocator could have recycled, then replay the old graph
+    junk = [sm100.Buffer(8 << 20) for _ in range(4)]
+    for j in junk:
+        sm100.check(lib.sm100_memset(stream.handle, j.at(), 0x7F, 8 << 20, 1), "memset")
+    sm100.check(lib.sm100_memset(stream.handle, C.c_void_p(optr), 0, 4 * hq * d, 1), "memset")
+    g.launch()
+    stream.sync()
+    assert sgref.nmse(U.read_guarded(sm100, stream, ob, hq * d).reshape(hq, 1, d), want) <= TOL
+    g.destroy()
+    for b in junk + [qb, kb, vb, ob]:
+        b.free()
+
+
 def test_attention_argument_errors(sm100, stream):
     b = sm100.Buffer(1 << 16)
     lib = sm100.lib()

@@ -1,0 +1,55 @@
+"""The reference's OWN device test programs, compiled byte-for-byte unchanged, run against the cuda_sm100 plugin.
+
+tests/ops/ops_tests.cpp of the reference runs every op its backend reports as supported on the device and compares it
+with scrapgpu_ref_execute (NMSE 1e-7, 1e-6 for quantized MUL_MAT, exact for GET_ROWS / SET_ROWS / CPY:
+ops_tests.cpp:411-412,725,588-603); tests/attention/attention_tests.cpp checks the core's SDPA composition on the
+device against a double-precision oracle (3e-4 absolute, attention_tests.cpp:40).  Both select their GPU backend by
+the literal name "opencl11" under -DSCRAPGPU_*_TEST_WITH_OPENCL11 (ops_tests.cpp:1222-1236,
+attention_tests.cpp:433-459); oracle/Makefile (`device_tests`) compiles them where they lie and links the one-function
+shim backend/opencl11_register_shim.c, so that name registers cuda_sm100.  The programs print PASS / SKIP per case and
+exit 0 only if nothing failed; SKIP lines are ops this backend reports UNSUPPORTED (outside the decode hot path)."""
+import os
+import re
+import subprocess
+
+import pytest
+
+from oracle import refapi
+
+pytestmark = pytest.mark.gpu
+
+# ops of the decode hot path: none of their cases may be skipped
+HOT_PATH = ("ADD", "GLU", "RMS_NORM", "RMS_NORM_MUL", "ADD_RMS_NORM_MUL", "SOFT_MAX", "ROPE", "GET_ROWS", "SET_ROWS", "CPY", "MUL_MAT",
+            "MUL_MAT_MULTI", "CONT_MUL_MAT")
+
+
+def run(binary):
+    if not os.path.exists(binary):
+        pytest.fail(f"{binary} is missing on the GPU box: run `make -C oracle device_tests` where the reference is checked out")
+    env = dict(os.environ, SCRAPGPU_TEST_BACKEND="opencl11")
+    r = subprocess.run([binary], capture_output=True, text=True, timeout=600, env=env)
+    print(r.stdout)
+    print(r.stderr)
+    assert r.returncode == 0, f"exit {r.returncode} (77 = no device)\n" + r.stdout[-4000:] + r.stderr[-2000:]
+    return r.stdout
+
+
+def test_reference_ops_tests_pass_on_cuda_sm100():
+    out = run(refapi.OPS_TESTS)
+    assert "(NVIDIA, b200)" in out, out[:400]
+    assert "FAIL" not in out
+    m = re.search(r"(\d+) op runs, (\d+) skipped", out)
+    assert m, out[-400:]
+    runs, skipped = int(m.group(1)), int(m.group(2))
+    assert runs >= 100, out[-400:]
+    skipped_names = [ln.split()[1] for ln in out.splitlines() if ln.startswith("SKIP ")]
+    for name in skipped_names:
+        assert name not in HOT_PATH, f"a decode hot-path op was skipped as unsupported: {name}\n" + "\n".join(ln for ln in out.splitlines() if ln.startswith("SKIP "))
+    assert "PASS  CONT_MUL_MAT" in out and "CONT_MUL_MAT V n_kv=520" in out
+    print(f"ops_tests: {runs} op runs, {skipped} skipped: {sorted(set(skipped_names))}")
+
+
+def test_reference_attention_tests_pass_on_cuda_sm100():
+    out = run(refapi.ATTENTION_TESTS)
+    assert "(cuda_sm100)" in out, out[:400]
+    assert "4 attention runs" in out, out[-400:]

@@ -51,6 +51,27 @@ def test_static_scratch_attention_matches_regular_entry(sm100, stream):
             assert sgref.nmse(got, sgref.attention(q, k, v, causal, off, scale)) <= TOL
 
 
+def test_static_scratch_survives_dirty_ticket_counters(sm100, stream):
+    """The first 64 KiB of the built-in array are the ticket counters of the single-launch merge.  A call that raced
+    with another one could leave them non-zero; the entry clears the ones it uses before every launch, so a later call
+    must be right whatever they hold.  Here they are overwritten with ones on purpose."""
+    lib = sm100.lib()
+    p = C.c_void_p()
+    sm100.check(lib.sm100_attention_static_prepare(C.byref(p)), "static_prepare")
+    assert p.value
+    rng = np.random.default_rng(22)
+    hq, hkv, d, nk, nq, off = 32, 8, 128, 1152, 1, 1100
+    q = rng.standard_normal((hq, nq, d)).astype(np.float32)
+    k = rng.standard_normal((hkv, nk, d)).astype(np.float32)
+    v = rng.standard_normal((hkv, nk, d)).astype(np.float32)
+    scale = float(1.0 / np.sqrt(d))
+    want = sgref.attention(q, k, v, True, off, scale)
+    for rep in range(2):
+        sm100.check(lib.sm100_memset(stream.handle, p, 1, 64 << 10, 1), "memset")
+        got = call(sm100, stream, lib.sm100_attention_static, q, k, v, True, off, scale)
+        assert sgref.nmse(got, want) <= TOL, rep
+
+
 def test_static_scratch_refuses_oversized_shapes(sm100, stream):
     lib = sm100.lib()
     b = sm100.Buffer(1 << 16)
