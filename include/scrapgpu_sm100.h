@@ -292,6 +292,14 @@ SM100_API int sm100_rope_view(sm100_stream_t s, const sm100_view * x, const int3
                               int32_t table_first_position, int32_t table_positions, const float * freq_factors,
                               const sm100_view * y, int n_dims, int neox, float freq_base, float freq_scale,
                               float attn_factor);                                           /* ops.cpp:530-634 */
+/* the same for F16 tensors (x and y share the dtype, ops.cpp:531-533): dtype is 0 (F32) or 1 (F16) */
+SM100_API int sm100_rope_view_dt(sm100_stream_t s, int dtype, const sm100_view * x, const int32_t * positions, const float * table,
+                                 int32_t table_first_position, int32_t table_positions, const float * freq_factors,
+                                 const sm100_view * y, int n_dims, int neox, float freq_base, float freq_scale, float attn_factor);
+/* SCALE / CLAMP / SQR / SQRT / UNARY over F32 views of one shape (ops.cpp:314-381).  code: 0 SCALE y = x * p0 + p1,
+ * 1 CLAMP to [p0, p1], 2 SQR, 3 SQRT, 10 + scrapgpu_unary_kind (include/scrapgpu/op.h:50-57: SILU, RELU, NEG, ABS,
+ * SIGMOID, TANH) */
+SM100_API int sm100_unary(sm100_stream_t s, int code, float p0, float p1, const sm100_view * x, const sm100_view * y);
 SM100_API int sm100_soft_max_view(sm100_stream_t s, const sm100_view * x, const sm100_view * mask, int mask_is_f16,
                                   const sm100_view * y, float scale);                       /* ops.cpp:636-684 */
 SM100_API int sm100_cpy(sm100_stream_t s, const sm100_view * src, int src_dtype, const sm100_view * dst, int dst_dtype); /* ops.cpp:764-800 */

@@ -376,6 +376,13 @@ scrapgpu_status supports(const scrapgpu_op_desc * desc, const char ** reason) {
             for (int i = 0; i < 4; ++i) if (ne(s1, i) > ne(dd, i)) return bad("binary op: src1 cannot be larger than dst", reason);
             return SCRAPGPU_STATUS_OK;
 
+        case SCRAPGPU_OP_SCALE: case SCRAPGPU_OP_CLAMP: case SCRAPGPU_OP_SQR: case SCRAPGPU_OP_SQRT: case SCRAPGPU_OP_UNARY:
+            if (!f32(s0) || !f32(dd)) return unsupported("unary-like ops expect F32 tensors", reason);
+            if (!same_shape(s0, dd)) return bad("unary-like op: src0 must have the shape of dst", reason);
+            if (desc->op == SCRAPGPU_OP_UNARY && enum_bits(load_params<scrapgpu_unary_params>(desc).kind) > (uint32_t) SCRAPGPU_UNARY_TANH)
+                return unsupported("unary kind is not implemented", reason);
+            return SCRAPGPU_STATUS_OK;
+
         case SCRAPGPU_OP_GLU: {
             const auto p = load_params<scrapgpu_glu_params>(desc);
             const bool split = desc->input_count == 2;
@@ -410,13 +417,13 @@ scrapgpu_status supports(const scrapgpu_op_desc * desc, const char ** reason) {
             const auto p = load_params<scrapgpu_rope_params>(desc);
             if (enum_bits(p.mode) > (uint32_t) SCRAPGPU_ROPE_MODE_NEOX) return unsupported("unknown ROPE mode", reason);
             if (desc->input_count < 2) return bad("ROPE needs the positions tensor as inputs[1]", reason);
-            if (!f32(s0) || !f32(dd)) return unsupported("ROPE is implemented for F32 tensors on cuda_sm100", reason);
+            if ((!f32(s0) && s0.dtype != SCRAPGPU_DTYPE_F16) || dd.dtype != s0.dtype) return unsupported("ROPE expects F32 or F16 tensors of the same dtype", reason);
             if (s1.dtype != SCRAPGPU_DTYPE_I32) return unsupported("ROPE positions must be I32", reason);
             if (p.n_offs != nullptr) return unsupported("ROPE n_offs is not supported", reason);
             if (p.freq_factors != nullptr && desc->input_count != 3) return unsupported("ROPE params->freq_factors must be NULL or describe inputs[2]", reason);
             if (p.ext_factor != 0.0f) return unsupported("ROPE with yarn extrapolation (ext_factor != 0) is not implemented on cuda_sm100", reason);
             if (!same_shape(s0, dd)) return bad("ROPE: src0 must have the shape of dst", reason);
-            if (s0.nb[0] != 4 || dd.nb[0] != 4) return unsupported("ROPE needs contiguous rows (nb0 == element size)", reason);
+            if (s0.nb[0] != type_size(s0.dtype) || dd.nb[0] != type_size(dd.dtype)) return unsupported("ROPE needs contiguous rows (nb0 == element size)", reason);
             if (p.n_dims <= 0 || p.n_dims % 2 != 0 || p.n_dims > s0.ne[0] || s0.ne[0] % 2 != 0) return bad("ROPE: n_dims must be a positive even number not above ne0 (ne0 even)", reason);
             if (ne(s1, 0) < ne(dd, 2)) return bad("ROPE: not enough positions for the sequence dimension", reason);
             if (s1.nb[0] != 4) return unsupported("ROPE positions must be contiguous", reason);
@@ -566,6 +573,7 @@ bool same_view(const Ref & a, const Ref & b) {
 bool in_place_ok(scrapgpu_op op) {
     switch (op) {
         case SCRAPGPU_OP_ADD: case SCRAPGPU_OP_SUB: case SCRAPGPU_OP_MUL: case SCRAPGPU_OP_DIV: case SCRAPGPU_OP_GLU:
+        case SCRAPGPU_OP_SCALE: case SCRAPGPU_OP_CLAMP: case SCRAPGPU_OP_SQR: case SCRAPGPU_OP_SQRT: case SCRAPGPU_OP_UNARY:
         case SCRAPGPU_OP_RMS_NORM: case SCRAPGPU_OP_SOFT_MAX: case SCRAPGPU_OP_RMS_NORM_MUL: case SCRAPGPU_OP_ADD_RMS_NORM_MUL:
         case SCRAPGPU_OP_CPY: case SCRAPGPU_OP_DUP: case SCRAPGPU_OP_CONT:
             return true;
@@ -718,6 +726,17 @@ scrapgpu_status execute(Stream * s, const scrapgpu_op_desc * desc) {
             const sm100_view a = view_of(in[0]), b = view_of(in[1]), y = view_of(out[0]);
             return from_sm100(sm100_binary(s->cuda, (int) desc->op - (int) SCRAPGPU_OP_ADD, &a, &b, &y));
         }
+        case SCRAPGPU_OP_SCALE: case SCRAPGPU_OP_CLAMP: case SCRAPGPU_OP_SQR: case SCRAPGPU_OP_SQRT: case SCRAPGPU_OP_UNARY: {
+            const sm100_view x = view_of(in[0]), y = view_of(out[0]);
+            int code = 0;
+            float p0 = 0.f, p1 = 0.f;
+            if (desc->op == SCRAPGPU_OP_SCALE) { const auto p = load_params<scrapgpu_scale_params>(desc); code = 0; p0 = p.scale; p1 = p.bias; }
+            else if (desc->op == SCRAPGPU_OP_CLAMP) { const auto p = load_params<scrapgpu_clamp_params>(desc); code = 1; p0 = p.min_value; p1 = p.max_value; }
+            else if (desc->op == SCRAPGPU_OP_SQR) code = 2;
+            else if (desc->op == SCRAPGPU_OP_SQRT) code = 3;
+            else code = 10 + (int) enum_bits(load_params<scrapgpu_unary_params>(desc).kind);
+            return from_sm100(sm100_unary(s->cuda, code, p0, p1, &x, &y));
+        }
         case SCRAPGPU_OP_GLU: {
             const auto p = load_params<scrapgpu_glu_params>(desc);
             const sm100_view x = view_of(in[0]), y = view_of(out[0]);
@@ -751,8 +770,8 @@ scrapgpu_status execute(Stream * s, const scrapgpu_op_desc * desc) {
                 if (st != SCRAPGPU_STATUS_OK) return st;
             }
             const sm100_view x = view_of(in[0]), y = view_of(out[0]);
-            return from_sm100(sm100_rope_view(s->cuda, &x, (const int32_t *) in[1].base(), table, 0, count, ff, &y, p.n_dims,
-                                              p.mode == SCRAPGPU_ROPE_MODE_NEOX, p.freq_base, p.freq_scale, p.attn_factor));
+            return from_sm100(sm100_rope_view_dt(s->cuda, in[0].d.dtype, &x, (const int32_t *) in[1].base(), table, 0, count, ff, &y, p.n_dims,
+                                                 p.mode == SCRAPGPU_ROPE_MODE_NEOX, p.freq_base, p.freq_scale, p.attn_factor));
         }
         case SCRAPGPU_OP_SOFT_MAX: {
             const auto p = load_params<scrapgpu_soft_max_params>(desc);

@@ -10,6 +10,8 @@ int matvec(cudaStream_t s, int dtype, int layout, const void * w, int64_t w_row_
 int matvec_q4k_imma_multi(cudaStream_t s, int count, const void * const * ws, const int64_t * ns, int64_t k, const float * x, int64_t ldx,
                           int64_t m, float * const * ys, const int64_t * ldys, bool * handled, const Q4KPrologue * pro);
 const char * matvec_last_kernel();
+int matvec_q4k_ring_multi(cudaStream_t s, int count, const void * const * ws, const int64_t * ns, int64_t k, const float * x,
+                          float * const * ys, bool * handled, const Q4KPrologue * pro);
 int gemm_tc_mul_mat(cudaStream_t s, int dtype, int layout, const void * w, int64_t w_row_stride, int64_t k, int64_t n, const float * x,
                     int64_t ldx, int64_t m, float * y, int64_t ldy, bool * handled);
 }
@@ -61,7 +63,9 @@ int sm100_mul_mat_multi(sm100_stream_t s, int count, const int * dtypes, const i
     }
     if (grouped >= 2 && x != nullptr && k > 0) {
         bool handled = false;
-        const int st = matvec_q4k_imma_multi((cudaStream_t) s, grouped, gw, gn, k, x, k, 1, gy, gld, &handled, nullptr);
+        int st = matvec_q4k_ring_multi((cudaStream_t) s, grouped, gw, gn, k, x, gy, &handled, nullptr);
+        if (st != ST_OK) return st;
+        if (!handled) st = matvec_q4k_imma_multi((cudaStream_t) s, grouped, gw, gn, k, x, k, 1, gy, gld, &handled, nullptr);
         if (st != ST_OK) return st;
         if (!handled) in_group[0] = in_group[1] = in_group[2] = false;
     } else {
@@ -95,7 +99,9 @@ int sm100_mul_mat_fused(sm100_stream_t s, int prologue, const float * a, const f
     pro.mode = prologue;
     pro.a = a; pro.b = b; pro.norm_w = norm_w; pro.sum_out = sum_out; pro.x_out = x_out; pro.eps = eps;
     bool handled = false;
-    const int st = matvec_q4k_imma_multi((cudaStream_t) s, count, ws, ns, k, a, k, 1, ys, ld, &handled, &pro);
+    int st = matvec_q4k_ring_multi((cudaStream_t) s, count, ws, ns, k, a, ys, &handled, &pro);
+    if (st != ST_OK) return st;
+    if (!handled) st = matvec_q4k_imma_multi((cudaStream_t) s, count, ws, ns, k, a, k, 1, ys, ld, &handled, &pro);
     if (st != ST_OK) return st;
     if (!handled) return fail(ST_UNSUPPORTED, "mul_mat_fused: this shape is not served by the fused kernel; run the separate ops");
     return ST_OK;

@@ -29,6 +29,8 @@ int matvec_q4k_imma_tiles(cudaStream_t s, const void * w, int64_t k, int64_t n, 
 int matvec_q4k_tiles(cudaStream_t s, const void * w, int64_t k, int64_t n, const float * x, int64_t ldx, int64_t m, float * y, int64_t ldy,
                      bool * handled);
 int q4k_pass_width(int64_t k, int64_t m);
+int matvec_q4k_ring_multi(cudaStream_t s, int count, const void * const * ws, const int64_t * ns, int64_t k, const float * x,
+                          float * const * ys, bool * handled, const Q4KPrologue * pro);
 
 // ---- natural-layout loading: assemble the packed-unit registers from GGUF blocks -----------------
 
@@ -499,6 +501,17 @@ int matvec(cudaStream_t s, int dtype, int layout, const void * w, int64_t w_row_
     if (layout != LAYOUT_PACKED && layout != LAYOUT_NATURAL) return fail(ST_INVALID, "mul_mat: unknown layout %d", layout);
     if (is_quant(dtype) && !x_aligned) return fail(ST_UNSUPPORTED, "mul_mat: activations must be 16-byte aligned (columns too)");
     static const int use_imma = env_int("SM100_Q4K_IMMA", 1);
+    if (use_imma && layout == LAYOUT_PACKED && dtype == DT_Q4_K && x_aligned && m == 1) {
+        // the ring kernel (consecutive launches overlap); leftover rows take the row kernel
+        bool handled = false;
+        const int st = matvec_q4k_ring_multi(s, 1, &w, &n, k, x, &y, &handled, nullptr);
+        if (st != ST_OK) return st;
+        if (handled) {
+            const int64_t full = (n / 16) * 16;
+            if (full < n) return took("matvec_q4k_ring+rows", launch_rows<UnitQ4K, true>(s, w, 0, k, n, x, ldx, m, y, ldy, full));
+            return took("matvec_q4k_ring", ST_OK);
+        }
+    }
     if (use_imma && layout == LAYOUT_PACKED && dtype == DT_Q4_K && x_aligned && m <= 2) {
         // integer tensor-core kernel over the full 16-row tiles; leftover rows take the row kernel
         bool handled = false;

@@ -94,6 +94,7 @@ int device_scratch(int slot, size_t bytes, void ** out) {
 
 int gemm_poll_fault();
 int iq_poll_fault();
+int ring_poll_fault();
 
 // Waits for the stream, then reads the fault words of the kernels with bounded waits on the STREAM's device (they are
 // per-device variables; the current device may be another one in a process that drives several GPUs).
@@ -109,6 +110,7 @@ static int sync_and_poll(cudaStream_t st) {
     if (dev != cur) SM100_CUDA(cudaSetDevice(dev));
     int r = gemm_poll_fault();
     if (r == ST_OK) r = iq_poll_fault();
+    if (r == ST_OK) r = ring_poll_fault();
     if (dev != cur) (void) cudaSetDevice(cur);
     return r;
 }

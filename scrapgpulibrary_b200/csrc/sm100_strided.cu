@@ -124,11 +124,35 @@ __global__ void __launch_bounds__(256) rms_norm_view_kernel(V4 x, V4 add, int ha
     }
 }
 
+__device__ __forceinline__ float load_as_float(const char * p, int dtype) {
+    if (dtype == DT_F32) return *(const float *) p;
+    if (dtype == DT_F16) return __half2float(*(const __half *) p);
+    return __uint_as_float((uint32_t) (*(const unsigned short *) p) << 16);  // BF16
+}
+
+__device__ __forceinline__ void store_from_float(char * p, int dtype, float v) {
+    if (dtype == DT_F32) {
+        *(float *) p = v;
+    } else if (dtype == DT_F16) {
+        *(__half *) p = __float2half_rn(v);
+    } else {
+        // BF16, round to nearest even, NaN kept (ops.cpp:41-52)
+        uint32_t bits = __float_as_uint(v);
+        if ((bits & 0x7fffffffu) > 0x7f800000u) {
+            *(unsigned short *) p = (unsigned short) ((bits >> 16) | 0x0040u);
+        } else {
+            bits += 0x7fffu + ((bits >> 16) & 1u);
+            *(unsigned short *) p = (unsigned short) (bits >> 16);
+        }
+    }
+}
+
 // ROPE (ops.cpp:530-634) over a view [ne0, heads, tokens, batch]; optional frequency factors; yarn is left to
 // the caller to reject
 __global__ void rope_view_kernel(V4 x, const int32_t * positions, const float * table, int32_t table_first,
                                  int32_t table_n, const float * freq_factors, V4 y, int n_dims, int neox, float theta_scale,
-                                 float freq_scale, float attn_factor, int64_t total) {
+                                 float freq_scale, float attn_factor, int64_t total, int dtype) {
+    const int64_t es = dtype == DT_F16 ? 2 : 4;   // x and y share the dtype (ops.cpp:531-533)
     pdl_wait();
     pdl_launch_dependents();
     const int64_t hp = x.ne[0] / 2;
@@ -158,13 +182,13 @@ __global__ void rope_view_kernel(V4 x, const int32_t * positions, const float * 
                 sn = __fmul_rn(sinf(th), attn_factor);
             }
             const int64_t e0 = neox ? j : 2 * j, e1 = neox ? j + n_dims / 2 : 2 * j + 1;
-            const float x0 = *(const float *) (xr + e0 * 4), x1 = *(const float *) (xr + e1 * 4);
-            *(float *) (yr + e0 * 4) = __fsub_rn(__fmul_rn(x0, cs), __fmul_rn(x1, sn));
-            *(float *) (yr + e1 * 4) = __fadd_rn(__fmul_rn(x0, sn), __fmul_rn(x1, cs));
+            const float x0 = load_as_float(xr + e0 * es, dtype), x1 = load_as_float(xr + e1 * es, dtype);
+            store_from_float(yr + e0 * es, dtype, __fsub_rn(__fmul_rn(x0, cs), __fmul_rn(x1, sn)));
+            store_from_float(yr + e1 * es, dtype, __fadd_rn(__fmul_rn(x0, sn), __fmul_rn(x1, cs)));
         } else {
             const int64_t e = 2 * (j - n_dims / 2) + n_dims;
-            *(float *) (yr + e * 4) = *(const float *) (xr + e * 4);
-            *(float *) (yr + (e + 1) * 4) = *(const float *) (xr + (e + 1) * 4);
+            store_from_float(yr + e * es, dtype, load_as_float(xr + e * es, dtype));
+            store_from_float(yr + (e + 1) * es, dtype, load_as_float(xr + (e + 1) * es, dtype));
         }
     }
 }
@@ -221,26 +245,30 @@ __global__ void __launch_bounds__(256) soft_max_view_kernel(V4 x, V4 mask, int h
     }
 }
 
-__device__ __forceinline__ float load_as_float(const char * p, int dtype) {
-    if (dtype == DT_F32) return *(const float *) p;
-    if (dtype == DT_F16) return __half2float(*(const __half *) p);
-    return __uint_as_float((uint32_t) (*(const unsigned short *) p) << 16);  // BF16
-}
-
-__device__ __forceinline__ void store_from_float(char * p, int dtype, float v) {
-    if (dtype == DT_F32) {
-        *(float *) p = v;
-    } else if (dtype == DT_F16) {
-        *(__half *) p = __float2half_rn(v);
-    } else {
-        // BF16, round to nearest even, NaN kept (ops.cpp:41-52)
-        uint32_t bits = __float_as_uint(v);
-        if ((bits & 0x7fffffffu) > 0x7f800000u) {
-            *(unsigned short *) p = (unsigned short) ((bits >> 16) | 0x0040u);
-        } else {
-            bits += 0x7fffu + ((bits >> 16) & 1u);
-            *(unsigned short *) p = (unsigned short) (bits >> 16);
+// SCALE / CLAMP / SQR / SQRT / UNARY (ops.cpp:314-381): y = f(x) element by element over F32 views of one shape.
+// code: 0 SCALE (x * p0 + p1, two roundings as the reference's unfused expression), 1 CLAMP to [p0, p1], 2 SQR, 3 SQRT,
+// 10.. = 10 + scrapgpu_unary_kind (SILU, RELU, NEG, ABS, SIGMOID, TANH)
+__global__ void unary_kernel(int code, float p0, float p1, V4 x, V4 y, int64_t total) {
+    pdl_wait();
+    pdl_launch_dependents();
+    for (int64_t idx = blockIdx.x * (int64_t) blockDim.x + threadIdx.x; idx < total; idx += (int64_t) gridDim.x * blockDim.x) {
+        int64_t i0, i1, i2, i3;
+        unflatten(idx, y.ne, i0, i1, i2, i3);
+        const float v = *(const float *) (x.p + off4(x, i0, i1, i2, i3));
+        float r;
+        switch (code) {
+            case 0: r = __fadd_rn(__fmul_rn(v, p0), p1); break;
+            case 1: r = fminf(fmaxf(v, p0), p1); break;
+            case 2: r = __fmul_rn(v, v); break;
+            case 3: r = __fsqrt_rn(v); break;
+            case 10: r = __fdiv_rn(v, __fadd_rn(1.0f, expf(-v))); break;
+            case 11: r = fmaxf(v, 0.0f); break;
+            case 12: r = -v; break;
+            case 13: r = fabsf(v); break;
+            case 14: r = __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-v))); break;
+            default: r = tanhf(v); break;
         }
+        *(float *) (y.p + off4(y, i0, i1, i2, i3)) = r;
     }
 }
 
@@ -386,17 +414,35 @@ int sm100_rms_norm_view(sm100_stream_t s, const sm100_view * x, const sm100_view
                   sum_out != nullptr ? 1 : 0, vy, eps);
 }
 
+int sm100_unary(sm100_stream_t s, int code, float p0, float p1, const sm100_view * x, const sm100_view * y) {
+    if (x == nullptr || y == nullptr || x->data == nullptr || y->data == nullptr) return fail(ST_INVALID, "unary: null view");
+    if (!((code >= 0 && code <= 3) || (code >= 10 && code <= 15))) return fail(ST_UNSUPPORTED, "unary: unknown function code %d", code);
+    const V4 vx = load_view(x), vy = load_view(y);
+    const int64_t total = count(vy);
+    if (total != count(vx)) return fail(ST_INVALID, "unary: src0 must have the shape of dst");
+    return launch(unary_kernel, dim3(grid_cap(total, 256)), dim3(256), 0, (cudaStream_t) s, code, p0, p1, vx, vy, total);
+}
+
 int sm100_rope_view(sm100_stream_t s, const sm100_view * x, const int32_t * positions, const float * table, int32_t table_first_position,
                     int32_t table_positions, const float * freq_factors, const sm100_view * y, int n_dims, int neox, float freq_base,
                     float freq_scale, float attn_factor) {
+    return sm100_rope_view_dt(s, DT_F32, x, positions, table, table_first_position, table_positions, freq_factors, y, n_dims, neox, freq_base,
+                              freq_scale, attn_factor);
+}
+
+int sm100_rope_view_dt(sm100_stream_t s, int dtype, const sm100_view * x, const int32_t * positions, const float * table,
+                       int32_t table_first_position, int32_t table_positions, const float * freq_factors, const sm100_view * y, int n_dims,
+                       int neox, float freq_base, float freq_scale, float attn_factor) {
+    if (dtype != DT_F32 && dtype != DT_F16) return fail(ST_UNSUPPORTED, "rope: F32 or F16 tensors");
     if (x == nullptr || y == nullptr || positions == nullptr || x->data == nullptr || y->data == nullptr) return fail(ST_INVALID, "rope: null view");
     const V4 vx = load_view(x), vy = load_view(y);
     if (n_dims <= 0 || n_dims % 2 != 0 || n_dims > vx.ne[0] || vx.ne[0] % 2 != 0) return fail(ST_INVALID, "rope: n_dims must be a positive even number not above ne0 (ne0 even)");
-    if (vx.nb[0] != 4 || vy.nb[0] != 4) return fail(ST_UNSUPPORTED, "rope: rows must be contiguous F32");
+    const int64_t es = dtype == DT_F16 ? 2 : 4;
+    if (vx.nb[0] != es || vy.nb[0] != es) return fail(ST_UNSUPPORTED, "rope: rows must be contiguous");
     const float theta_scale = powf(freq_base, -2.0f / (float) n_dims);
     const int64_t total = (vx.ne[0] / 2) * vx.ne[1] * vx.ne[2] * vx.ne[3];
     return launch(rope_view_kernel, dim3(grid_cap(total, 256)), dim3(256), 0, (cudaStream_t) s, vx, positions, table, table_first_position,
-                  table_positions, freq_factors, vy, n_dims, neox, theta_scale, freq_scale, attn_factor, total);
+                  table_positions, freq_factors, vy, n_dims, neox, theta_scale, freq_scale, attn_factor, total, dtype);
 }
 
 int sm100_soft_max_view(sm100_stream_t s, const sm100_view * x, const sm100_view * mask, int mask_is_f16, const sm100_view * y, float scale) {

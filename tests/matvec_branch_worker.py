@@ -1,5 +1,5 @@
 """Worker of tests/test_matvec_gpu.py::test_matvec_forced_branches: the decode matvec with its dispatcher pinned by the
-environment of this process (SM100_Q4K_IMMA, SM100_Q4K_MMA, SM100_B32_IMMA, SM100_Q6K_IMMA, SM100_MV_WIDE = 0 switch the
+environment of this process (SM100_Q4K_RING, SM100_Q4K_IMMA, SM100_Q4K_MMA, SM100_B32_IMMA, SM100_Q6K_IMMA, SM100_MV_WIDE = 0 switch the
 respective kernel family off, so the next one in the chain serves the call), checked against the CPU oracle on ragged
 and benchmark-like shapes.  The library reports the kernel family that served each call
 (sm100_matvec_last_kernel); the worker prints one JSON line {"worst": NMSE, "kernels": {name: calls}}."""
@@ -18,6 +18,7 @@ from tests import util as U  # noqa: E402
 
 # (dtype, K, N, M): whole tiles and leftover rows, short and long rows, one and several columns
 CASES = [(U.Q4_K, 4096, 272, 1), (U.Q4_K, 4096, 264, 2), (U.Q4_K, 2048, 40, 4), (U.Q4_K, 12288, 48, 1), (U.Q4_K, 512, 33, 8),
+         (U.Q4_K, 1024, 40, 1), (U.Q4_K, 4096, 64, 2), (U.Q4_K, 6144, 4112, 1), (U.Q4_K, 768, 9616, 1), (U.Q4_K, 16384, 32, 1), (U.Q4_K, 4096, 24016, 1),
          (U.Q6_K, 4096, 272, 1), (U.Q6_K, 2048, 40, 1), (U.Q6_K, 12288, 528, 1), (U.Q6_K, 4096, 64, 4), (U.Q6_K, 768, 24, 1),
          (U.Q4_0, 4096, 272, 1), (U.Q4_0, 2048, 33, 1), (U.Q4_0, 4096, 64, 3), (U.Q4_0, 96, 24, 1),
          (U.Q8_0, 4096, 272, 1), (U.Q8_0, 1024, 40, 1), (U.Q8_0, 4096, 64, 8), (U.Q8_0, 160, 17, 1)]

@@ -89,15 +89,17 @@ def _kernel(sm100):
 
 # environment that switches kernel families off -> the "dtype:kernel" names that must then have served some case
 FORCED = [
-    ({}, ["q4_k:matvec_q4k_imma", "q4_k:matvec_q4k_imma+rows", "q6_k:matvec_q6k_imma", "q4_0:matvec_b32_imma", "q8_0:matvec_b32_imma"]),
+    ({}, ["q4_k:matvec_q4k_ring", "q4_k:matvec_q4k_ring+rows", "q4_k:matvec_q4k_imma", "q4_k:matvec_q4k_imma+rows", "q4_k:matvec_q4k_imma_cols+rows",
+          "q6_k:matvec_q6k_imma", "q4_0:matvec_b32_imma", "q8_0:matvec_b32_imma"]),
+    ({"SM100_Q4K_RING": "0"}, ["q4_k:matvec_q4k_imma", "q4_k:matvec_q4k_imma+rows"]),
     ({"SM100_Q6K_IMMA": "0", "SM100_B32_IMMA": "0"}, ["q6_k:matvec_wide", "q4_0:matvec_wide", "q8_0:matvec_wide", "q6_k:matvec_rows"]),
-    ({"SM100_Q4K_IMMA": "0"}, ["q4_k:matvec_q4k_mma", "q4_k:matvec_q4k_mma+rows"]),
+    ({"SM100_Q4K_IMMA": "0"}, ["q4_k:matvec_q4k_mma", "q4_k:matvec_q4k_mma+rows"]),   # (switches the ring kernel off too: same arithmetic family)
     ({"SM100_Q4K_IMMA": "0", "SM100_Q4K_MMA": "0", "SM100_Q6K_IMMA": "0", "SM100_B32_IMMA": "0", "SM100_MV_WIDE": "0"},
      ["q4_k:matvec_stream", "q6_k:matvec_stream", "q4_0:matvec_stream", "q8_0:matvec_stream", "q4_k:matvec_rows", "q8_0:matvec_rows"]),
 ]
 
 
-@pytest.mark.parametrize("env,expected", FORCED, ids=["default", "no_q6k_b32_imma", "no_q4k_imma", "cuda_core_only"])
+@pytest.mark.parametrize("env,expected", FORCED, ids=["default", "no_q4k_ring", "no_q6k_b32_imma", "no_q4k_imma", "cuda_core_only"])
 def test_matvec_forced_branches(env, expected):
     """Each kernel family of the dispatcher (sm100_matvec.cu) is reached by name and agrees with the oracle: the
     families behind the default one serve the shapes the default declines, so they are tested by switching the
