@@ -10,10 +10,12 @@ metric = algorithmic GB/s = sum over launches of (N*K*0.5625 + 4*K + 4*N) bytes 
 
   value      launches replayed from one CUDA graph, inputs resident in HBM, CUDA-event timing on the
              launching stream
-  e2e        the same pass driven call by call with HOST activations: per matvec a pinned host->device copy
-             of x, the kernel, a device->host copy of y (sm100_hostpipe_mul_mat: the copies on two streams
-             of their own beside the kernels' stream, tied by events) and a sync per step (weights stay
-             resident, as they do after scrapgpu_tensor_upload in the reference's usage)
+  e2e        the same pass through the backend plugin's vtable (what scrapgpu_buffer_write / scrapgpu_plan_execute /
+             scrapgpu_buffer_read / scrapgpu_stream_sync of the reference's C API forward to) with HOST activations:
+             per step a non-blocking write of every matvec's x from pinned host memory, one plan_execute of the
+             step's MUL_MAT nodes, a non-blocking read of every y into pinned host memory, one sync (weights stay
+             resident, as they do after scrapgpu_tensor_upload in the reference's usage); timed on the host clock
+             around steps that each end in a sync
   roofline   achieved = algorithmic bytes per launch / mean launch duration (the same CUDA-event region),
              peak = measured HBM copy bandwidth of MEASURED_PEAKS.json (burst figure; fallback 6650 GB/s)
   cpu_baseline  the unmodified reference's CPU MUL_MAT (oracle/_ref, built from the reference's own sources) on
@@ -296,44 +298,8 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         # ---- prefill GEMM (tensor cores): Q8_0, M = 512 tokens, K = 4096, N in {4096, 12288} ----
         detail.update(prefill_gemm(capi, stream))
 
-        # ---- e2e: host activations in, host results out, call by call ----
-        hx, hy = {}, {}
-        for k in (4096, 12288):
-            p = C.c_void_p()
-            capi.check(L.sm100_host_alloc(4 * k, C.byref(p)), "host_alloc")
-            C.memmove(p, rng.standard_normal(k).astype(np.float32).ctypes.data, 4 * k)
-            hx[k] = p
-        for n in (4096, 12288):
-            p = C.c_void_p()
-            capi.check(L.sm100_host_alloc(4 * n, C.byref(p)), "host_alloc")
-            hy[n] = p
-
-        # sm100_hostpipe_mul_mat: one call per matvec; inside it the copy of the activations, the kernel and the
-        # read-back of the result go to three in-order streams tied by events, so the copy of matvec i + 1 and the
-        # read-back of matvec i - 1 run beside matvec i's kernel.  A step ends when the last result is on the host.
-        pipe = capi.HostPipe(8, 4 * 12288, 4 * 12288)
-        s_first, s_last = pipe.stream(0), pipe.stream(2)
-
-        items = (capi.HostPipeItem * len(order))()
-        for i, (s, layer) in enumerate(order):
-            p = pool[s]
-            items[i] = capi.HostPipeItem(dtype, 1, p["mats"][layer].ptr, 0, p["k"], p["n"], hx[p["k"]].value, 1, hy[p["n"]].value)
-
-        def e2e_step():
-            pipe.mul_mat_many(items, len(order))   # the step's products as one list: same copies and kernels per product
-            pipe.sync()
-
-        for _ in range(max(3, args.warmup)):
-            e2e_step()
-        e2e_steps = max(3, args.steps // 2)
-        e0, e1 = capi.Event(), capi.Event()
-        e0.record(s_first)
-        for _ in range(e2e_steps):
-            e2e_step()
-        e1.record(s_last)
-        e1.sync()
-        e2e_ms = e0.elapsed_ms(e1) / e2e_steps
-        pipe.close()
+        # ---- e2e: host activations in, host results out, through the backend plugin's vtable ----
+        e2e = e2e_through_plugin(capi, stream, pool, order, dtype, local_rank, rng, max(3, args.warmup), max(3, args.steps // 2))
         h2d = sum(4 * pool[s]["k"] for s, _ in order)
         d2h = sum(4 * pool[s]["n"] for s, _ in order)
 
@@ -349,8 +315,14 @@ def run_ours(args, rank: int, world: int, local_rank: int):
                        "l2": "inputs larger than L2 (pool %.2f GB per GPU, L2 126 MB)" % (step_bytes / 1e9), "timing": "CUDA events on the launching stream, one graph replay per step",
                        "setup_s": round(setup_s, 1), "detail": detail, "decode": decode, "head_sharded": head},
             "gpu_launches": int(launches_timed),
-            "e2e": {"value": round(world * step_bytes / (e2e_ms * 1e-3) / 1e9, 1), "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                    "ms_per_step": round(e2e_ms, 4), "note": "host activations in / host results out per matvec through sm100_hostpipe_mul_mat_many (one list per step; copies on their own streams beside the kernels), weights resident"},
+            "e2e": {"value": round(world * step_bytes / (e2e["ms_per_step"] * 1e-3) / 1e9, 1), "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "ms_per_step": round(e2e["ms_per_step"], 4), "per_op_ms_per_step": round(e2e["per_op_ms_per_step"], 4),
+                    "per_op_value": round(world * step_bytes / (e2e["per_op_ms_per_step"] * 1e-3) / 1e9, 1), "results_checked": e2e["checked"],
+                    "note": "through the cuda_sm100 backend vtable (the calls behind scrapgpu_buffer_write / scrapgpu_plan_execute / scrapgpu_buffer_read / "
+                            "scrapgpu_stream_sync): per step one non-blocking buffer_write of every matvec's activations from pinned host memory, one "
+                            "plan_execute of the step's MUL_MAT nodes, one non-blocking buffer_read of every result into pinned host memory, one stream_sync; "
+                            "weights resident (uploaded once with tensor_upload, packed layout).  per_op_*: the same with one op_execute per matvec instead "
+                            "of the plan"},
             "roofline": {"bound": "hbm", "kernel": kernel_name, "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
                          "frac": round(achieved / peak, 4), "peak_source": peak_src, "bytes_per_launch": round(per_launch_bytes, 1),
                          "us_per_launch": round(per_launch_us, 3),
@@ -362,6 +334,121 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     if dist is not None:
         dist.barrier()
     return out
+
+
+def e2e_through_plugin(capi, stream, pool, order, dtype, device_index, rng, warmup, steps):
+    """The sweep as a caller of the reference library drives it: device buffers, uploads, ops and read-backs all go
+    through the backend vtable of the cuda_sm100 plugin (include/scrapgpu/backend.h:29-57 of the reference; the
+    reference's core forwards scrapgpu_buffer_write / scrapgpu_plan_execute / ... to exactly these slots).  The
+    plugin's weights are separate buffers of its own (tensor_upload with the packed-layout tag, the way
+    examples/standalone_matmul.c:126-130 uploads)."""
+    import ctypes as C
+    from scrapgpulibrary_b200 import _build, abi
+    if not os.path.exists(_build.PLUGIN_SO):
+        raise FileNotFoundError(f"{_build.PLUGIN_SO} is missing: the end-to-end leg needs the backend plugin")
+    P = C.CDLL(_build.PLUGIN_SO, mode=C.RTLD_GLOBAL)
+    P.scrapgpu_cuda_sm100_vtable.restype = C.POINTER(abi.Vtable)
+    vt = P.scrapgpu_cuda_sm100_vtable().contents
+    L = capi.lib()
+
+    def ok(st, what):
+        if st != 0:
+            raise RuntimeError(f"{what}: status {st}: {(L.sm100_last_error() or b'').decode()}")
+
+    dev, st_ = C.c_void_p(), C.c_void_p()
+    ok(vt.get_device(None, device_index, C.byref(dev)), "get_device")
+    ok(vt.stream_create(dev, C.byref(st_)), "stream_create")
+
+    def alloc(nbytes):
+        b = C.c_void_p()
+        ok(vt.buffer_alloc(dev, nbytes, C.byref(b)), "buffer_alloc")
+        return b
+
+    def pinned(nbytes):
+        p = C.c_void_p()
+        capi.check(L.sm100_host_alloc(nbytes, C.byref(p)), "host_alloc")
+        return p
+
+    # weights: natural bytes up, packed on the way (layout tag 1)
+    wdesc = {}
+    for s, (k, n) in enumerate(SHAPES):
+        base = pool[s]["natural"]
+        for layer in sorted({l for ss, l in order if ss == s}):
+            buf = alloc(base.nbytes)
+            d = abi.tensor_desc(dtype, [k, n], buffer=buf.value, layout=abi.LAYOUT_R32)
+            rot = np.ascontiguousarray(np.roll(base, layer * 17, axis=0) if layer else base)
+            ok(vt.tensor_upload(st_, C.byref(d), rot.ctypes.data_as(C.c_void_p), rot.nbytes), "tensor_upload")
+            wdesc[(s, layer)] = d
+    ops, hx, hy, xbuf, ybuf = [], [], [], [], []
+    for s, layer in order:
+        k, n = SHAPES[s]
+        xb, yb = alloc(4 * k), alloc(4 * n)
+        xbuf.append(xb)
+        ybuf.append(yb)
+        px, py = pinned(4 * k), pinned(4 * n)
+        C.memmove(px, rng.standard_normal(k).astype(np.float32).ctypes.data, 4 * k)
+        hx.append(px)
+        hy.append(py)
+        ops.append(abi.Op(abi.OP_MUL_MAT, [wdesc[(s, layer)], abi.tensor_desc(abi.F32, [k], buffer=xb.value)], [abi.tensor_desc(abi.F32, [n], buffer=yb.value)],
+                          abi.MulMatParams(0, 0)))
+    nodes = (abi.PlanNode * len(ops))()
+    for i, o in enumerate(ops):
+        nodes[i].struct_size = C.sizeof(abi.PlanNode)
+        nodes[i].op = o.desc
+        nodes[i].output_use_count = 0
+    pd = abi.PlanDesc(C.sizeof(abi.PlanDesc), nodes, len(ops))
+    plan = C.c_void_p()
+    ok(vt.plan_build(dev, C.byref(pd), C.byref(plan)), "plan_build")
+    sizes = [(4 * SHAPES[s][0], 4 * SHAPES[s][1]) for s, _ in order]
+
+    def step(per_op):
+        if per_op:
+            for i, o in enumerate(ops):
+                ok(vt.buffer_write(st_, xbuf[i], 0, hx[i], sizes[i][0], 0), "buffer_write")
+                ok(vt.op_execute(st_, o.ptr()), "op_execute")
+                ok(vt.buffer_read(st_, ybuf[i], 0, hy[i], sizes[i][1], 0), "buffer_read")
+        else:
+            for i in range(len(ops)):
+                ok(vt.buffer_write(st_, xbuf[i], 0, hx[i], sizes[i][0], 0), "buffer_write")
+            ok(vt.plan_execute(st_, plan), "plan_execute")
+            for i in range(len(ops)):
+                ok(vt.buffer_read(st_, ybuf[i], 0, hy[i], sizes[i][1], 0), "buffer_read")
+        ok(vt.stream_sync(st_), "stream_sync")
+
+    def timed(per_op):
+        for _ in range(warmup):
+            step(per_op)
+        t0 = time.perf_counter()      # every step ends with a stream_sync: host time brackets the device work
+        for _ in range(steps):
+            step(per_op)
+        return (time.perf_counter() - t0) * 1e3 / steps
+
+    plan_ms = timed(False)
+    per_op_ms = timed(True)
+    # the results that arrived on the host are the device path's (same kernels): compare one product per shape
+    checked = 0
+    for s in range(len(SHAPES)):
+        i = next(j for j, (ss, _) in enumerate(order) if ss == s)
+        k, n = SHAPES[s]
+        got = np.ctypeslib.as_array(C.cast(hy[i], C.POINTER(C.c_float)), shape=(n,)).copy()
+        xh = np.ctypeslib.as_array(C.cast(hx[i], C.POINTER(C.c_float)), shape=(k,)).copy()
+        xd, yd = capi.Buffer(4 * k), capi.Buffer(4 * n)
+        xd.upload(stream, xh)
+        capi.mul_mat(stream, dtype, 1, pool[s]["mats"][order[i][1]], k, n, xd, 1, yd)
+        stream.sync()
+        want = yd.download(stream, np.float32, n)
+        if not np.array_equal(got, want):
+            raise RuntimeError(f"end-to-end result of shape {SHAPES[s]} differs from the device-resident call")
+        checked += 1
+        xd.free()
+        yd.free()
+    ok(vt.plan_free(plan), "plan_free")
+    for b in xbuf + ybuf + [C.c_void_p(d.buffer) for d in wdesc.values()]:
+        vt.buffer_free(b)
+    for p in hx + hy:
+        L.sm100_host_free(p)
+    vt.stream_free(st_)
+    return {"ms_per_step": plan_ms, "per_op_ms_per_step": per_op_ms, "checked": checked}
 
 
 def sharded_head(capi, rank: int, world: int, local_rank: int, dist, reps: int = 50):

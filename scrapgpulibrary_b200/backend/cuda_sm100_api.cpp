@@ -82,13 +82,56 @@ struct PlanNode {
     scrapgpu_op_desc desc;
     std::vector<scrapgpu_tensor_desc> inputs, outputs;
     std::vector<uint8_t> params;
+    uint32_t use_count = 0;   // consumers of the node's result as the caller counted them (backend.h:10-14); 0 = not stated
+    // the pointers inside desc refer to this object's own vectors: keep them right when the object is copied or moved
+    void rebind() {
+        desc.struct_size = sizeof(desc);
+        desc.inputs = inputs.data();
+        desc.input_count = inputs.size();
+        desc.outputs = outputs.data();
+        desc.output_count = outputs.size();
+        desc.params = params.empty() ? nullptr : params.data();
+        desc.params_size = params.size();
+    }
+    PlanNode() { desc = {}; }
+    PlanNode(const PlanNode & o) : desc(o.desc), inputs(o.inputs), outputs(o.outputs), params(o.params), use_count(o.use_count) { rebind(); }
+    PlanNode & operator=(const PlanNode & o) {
+        if (this != &o) { desc = o.desc; inputs = o.inputs; outputs = o.outputs; params = o.params; use_count = o.use_count; rebind(); }
+        return *this;
+    }
+};
+
+// One sm100_mul_mat_fused launch standing for a normalisation or activation node and the MUL_MAT(s) that consume it
+struct FusedCall {
+    int prologue = 0;   // SM100_PROLOGUE_RMS_NORM or SM100_PROLOGUE_SWIGLU
+    scrapgpu_tensor_desc a = {}, b = {}, norm_w = {}, sum_out = {}, x_out = {};
+    bool has_b = false, has_sum = false, has_x = false;
+    float eps = 0.0f;
+    std::vector<scrapgpu_tensor_desc> w, y;
+};
+
+// What plan_execute runs in place of a group of consecutive nodes of the caller's list
+struct PlanStep {
+    std::vector<size_t> nodes;   // the caller's nodes this step stands for, in order
+    int lowered = -1;            // a public fused op (Plan::lowered) that replaces them, or -1
+    int fused = -1;              // a FusedCall (Plan::fused) that replaces them, or -1
+    bool declined = false;       // the replacement was answered UNSUPPORTED when first run: the caller's nodes run instead
 };
 
 struct Plan {
     scrapgpu_object_header hdr;
     Device * dev = nullptr;
-    std::vector<PlanNode> nodes;
+    std::vector<PlanNode> nodes;       // deep copy of the caller's list
+    std::vector<PlanNode> lowered;     // fused ops found at build time
+    std::vector<FusedCall> fused;
+    std::vector<PlanStep> steps;
     std::vector<Buffer *> pinned;
+    // replay: the steps are recorded once into a CUDA graph (the second execution; the first one runs them one by one
+    // and lets the library create whatever scratch and tables they need), later executions launch the graph
+    uint64_t executions = 0;
+    sm100_graph_t graph = nullptr;
+    bool graph_refused = false;
+    size_t launches_per_execution = 0;
 };
 
 extern const scrapgpu_backend_vtable g_vtable;
@@ -997,10 +1040,11 @@ scrapgpu_status v_buffer_write(scrapgpu_stream_t * stream, scrapgpu_buffer_t * b
         const scrapgpu_status st = io_check(stream, buffer, offset, size, "write exceeds the buffer", io);
         if (st != SCRAPGPU_STATUS_OK || size == 0) return st;
         if (data == nullptr) return invalid("data is null");
-        // the host pointer may be pageable and reused by the caller right away: a non-blocking write still
-        // has to have consumed it, so pageable sources are copied synchronously by the runtime either way
-        (void) blocking;
-        return enqueue_result(io.s, from_sm100(sm100_memcpy_h2d(io.s->cuda, static_cast<char *>(io.b->ptr) + offset, data, size, 1)));
+        // blocking = 0 enqueues the copy (in stream order) and returns.  From page-locked host memory the copy engine
+        // reads `data` later, so the caller keeps it untouched until the next stream_sync, as with a non-blocking
+        // clEnqueueWriteBuffer of the OpenCL backend; a pageable source is staged by the CUDA runtime before the call
+        // returns, so it may be reused at once.
+        return enqueue_result(io.s, from_sm100(sm100_memcpy_h2d(io.s->cuda, static_cast<char *>(io.b->ptr) + offset, data, size, blocking != 0)));
     });
 }
 
@@ -1010,8 +1054,9 @@ scrapgpu_status v_buffer_read(scrapgpu_stream_t * stream, scrapgpu_buffer_t * bu
         const scrapgpu_status st = io_check(stream, buffer, offset, size, "read exceeds the buffer", io);
         if (st != SCRAPGPU_STATUS_OK || size == 0) return st;
         if (data == nullptr) return invalid("data is null");
-        (void) blocking;  // the caller may read `data` as soon as the call returns
-        return enqueue_result(io.s, from_sm100(sm100_memcpy_d2h(io.s->cuda, data, static_cast<char *>(io.b->ptr) + offset, size, 1)));
+        // blocking = 0: `data` holds the bytes after the next stream_sync (page-locked destination; the CUDA runtime
+        // completes a copy into pageable memory before it returns)
+        return enqueue_result(io.s, from_sm100(sm100_memcpy_d2h(io.s->cuda, data, static_cast<char *>(io.b->ptr) + offset, size, blocking != 0)));
     });
 }
 
@@ -1187,6 +1232,251 @@ const char * op_name(int op) {
     }
 }
 
+// ---------------------------------------------------------------------------------------------------------
+// plans: "selection happens once at plan build, launches are cheap afterwards" (docs/API_CONTRACT.md:79-92 of the
+// reference).  plan_build copies the caller's nodes, then looks at neighbouring nodes the way the reference's ggml
+// adapter does per graph (adapters/ggml/ggml-cl11.cpp:904-1031): RMS_NORM + MUL, ADD + RMS_NORM + MUL, MUL_MATs that
+// share src1, pairs of SET_ROWS become the public fused ops (include/scrapgpu/op.h:43-46); on top of that a
+// normalisation or a split SwiGLU whose row feeds packed Q4_K MUL_MATs goes into the matvec launch itself
+// (sm100_mul_mat_fused).  An intermediate result is left unwritten only when the caller's output_use_count
+// (include/scrapgpu/backend.h:10-14) says that the next node is its single consumer.  plan_execute runs the steps
+// one by one the first time and replays a captured CUDA graph from the third time on.
+// ---------------------------------------------------------------------------------------------------------
+
+bool same_tensor(const scrapgpu_tensor_desc & a, const scrapgpu_tensor_desc & b) {
+    if (a.buffer != b.buffer || a.offset != b.offset || a.dtype != b.dtype || a.layout != b.layout) return false;
+    for (int i = 0; i < 4; ++i) if (ne(a, i) != ne(b, i) || (ne(a, i) > 1 && a.nb[i] != b.nb[i])) return false;
+    return a.nb[0] == b.nb[0];
+}
+
+bool single_row(const scrapgpu_tensor_desc & t) { return f32(t) && t.nb[0] == 4 && ne(t, 1) * ne(t, 2) * ne(t, 3) == 1; }
+
+bool descs_overlap(const scrapgpu_tensor_desc & a, const scrapgpu_tensor_desc & b) {
+    if (a.buffer != b.buffer) return false;
+    const uint64_t a0 = a.offset, a1 = a0 + span_bytes(a), b0 = b.offset, b1 = b0 + span_bytes(b);
+    return a0 < b1 && b0 < a1;
+}
+
+PlanNode make_node(scrapgpu_op op, std::vector<scrapgpu_tensor_desc> in, std::vector<scrapgpu_tensor_desc> out, const void * params, size_t params_size,
+                   uint32_t use_count) {
+    PlanNode n;
+    n.desc.op = op;
+    n.inputs = std::move(in);
+    n.outputs = std::move(out);
+    if (params != nullptr && params_size > 0) n.params.assign(static_cast<const uint8_t *>(params), static_cast<const uint8_t *>(params) + params_size);
+    n.use_count = use_count;
+    n.rebind();
+    return n;
+}
+
+bool packed_q4k_weight(const scrapgpu_tensor_desc & w) {
+    return w.dtype == kQ4_K && w.layout == SCRAPGPU_LAYOUT_R32 && ne(w, 2) * ne(w, 3) == 1 && ne(w, 1) % 16 == 0 && ne(w, 0) % 256 == 0;
+}
+
+// an item of the working list while lowering: a node (the caller's or a fused one) and the caller's nodes it covers
+struct LowerItem {
+    PlanNode node;
+    std::vector<size_t> covers;
+    bool synthetic = false;     // built here (the caller's nodes stay available as the fallback)
+    bool y_count_known = false; // use_count is the consumer count of the row a following MUL_MAT would read
+};
+
+void lower_plan(Plan & plan) {
+    std::vector<LowerItem> items;
+    for (size_t i = 0; i < plan.nodes.size(); ++i) {
+        LowerItem it;
+        it.node = plan.nodes[i];
+        it.covers = {i};
+        const auto op = plan.nodes[i].desc.op;
+        it.y_count_known = op == SCRAPGPU_OP_RMS_NORM_MUL || op == SCRAPGPU_OP_MUL || op == SCRAPGPU_OP_GLU || op == SCRAPGPU_OP_RMS_NORM;
+        items.push_back(std::move(it));
+    }
+    auto accepted = [](PlanNode & n) {
+        const char * why = nullptr;
+        return supports(&n.desc, &why) == SCRAPGPU_STATUS_OK;
+    };
+    auto merge = [&](size_t at, size_t count, PlanNode node, bool y_known) {
+        LowerItem m;
+        m.node = std::move(node);
+        for (size_t k = 0; k < count; ++k) m.covers.insert(m.covers.end(), items[at + k].covers.begin(), items[at + k].covers.end());
+        m.synthetic = true;
+        m.y_count_known = y_known;
+        items.erase(items.begin() + (long) at, items.begin() + (long) (at + count));
+        items.insert(items.begin() + (long) at, std::move(m));
+    };
+
+    // 1. RMS_NORM -> MUL by a weight row  =>  RMS_NORM_MUL (the normalised, unweighted row is not written: one consumer only)
+    for (size_t i = 0; i + 1 < items.size(); ++i) {
+        const PlanNode & a = items[i].node, & b = items[i + 1].node;
+        if (a.desc.op != SCRAPGPU_OP_RMS_NORM || b.desc.op != SCRAPGPU_OP_MUL || a.use_count != 1 || b.inputs.size() != 2) continue;
+        const scrapgpu_tensor_desc & t = a.outputs[0];
+        int wi = -1;
+        if (same_tensor(b.inputs[0], t)) wi = 1;
+        else if (same_tensor(b.inputs[1], t) && same_shape(b.inputs[1], b.outputs[0])) wi = 0;
+        if (wi < 0) continue;
+        const scrapgpu_tensor_desc & w = b.inputs[wi];
+        if (!f32(w) || w.nb[0] != 4 || ne(w, 0) != ne(t, 0) || ne(w, 1) * ne(w, 2) * ne(w, 3) != 1) continue;
+        PlanNode n = make_node(SCRAPGPU_OP_RMS_NORM_MUL, {a.inputs[0], w}, {b.outputs[0]}, a.desc.params, a.desc.params_size, b.use_count);
+        if (!accepted(n)) continue;
+        merge(i, 2, std::move(n), true);
+    }
+    // 2. ADD -> RMS_NORM_MUL on one row  =>  ADD_RMS_NORM_MUL (the sum is still written: it is the new residual)
+    for (size_t i = 0; i + 1 < items.size(); ++i) {
+        const PlanNode & a = items[i].node, & b = items[i + 1].node;
+        if (a.desc.op != SCRAPGPU_OP_ADD || b.desc.op != SCRAPGPU_OP_RMS_NORM_MUL || a.inputs.size() != 2) continue;
+        if (!same_tensor(b.inputs[0], a.outputs[0]) || !single_row(a.outputs[0]) || !same_shape(a.inputs[0], a.inputs[1])) continue;
+        PlanNode n = make_node(SCRAPGPU_OP_ADD_RMS_NORM_MUL, {a.inputs[0], a.inputs[1], b.inputs[1]}, {a.outputs[0], b.outputs[0]}, b.desc.params,
+                               b.desc.params_size, b.use_count);
+        if (!accepted(n)) continue;
+        merge(i, 2, std::move(n), items[i + 1].y_count_known);
+    }
+    // 3. neighbouring MUL_MATs over the same single activation column  =>  MUL_MAT_MULTI (2 or 3 of them)
+    for (size_t i = 0; i + 1 < items.size(); ++i) {
+        if (items[i].node.desc.op != SCRAPGPU_OP_MUL_MAT) continue;
+        const scrapgpu_tensor_desc & x = items[i].node.inputs[1];
+        if (ne(x, 1) * ne(x, 2) * ne(x, 3) != 1) continue;
+        size_t run = 1;
+        while (run < 3 && i + run < items.size() && items[i + run].node.desc.op == SCRAPGPU_OP_MUL_MAT && same_tensor(items[i + run].node.inputs[1], x)) ++run;
+        if (run < 2) continue;
+        // no member may write what a later member reads (they run as one launch)
+        bool independent = true;
+        for (size_t k = 0; k < run && independent; ++k)
+            for (size_t m = 0; m < run; ++m)
+                if (descs_overlap(items[i + k].node.outputs[0], x) || (m != k && descs_overlap(items[i + k].node.outputs[0], items[i + m].node.inputs[0]))) independent = false;
+        if (!independent) continue;
+        std::vector<scrapgpu_tensor_desc> in, out;
+        for (size_t k = 0; k < run; ++k) { in.push_back(items[i + k].node.inputs[0]); out.push_back(items[i + k].node.outputs[0]); }
+        in.push_back(x);
+        PlanNode n = make_node(SCRAPGPU_OP_MUL_MAT_MULTI, std::move(in), std::move(out), nullptr, 0, 0);
+        if (!accepted(n)) continue;
+        merge(i, run, std::move(n), false);
+    }
+    // 4. two neighbouring SET_ROWS (the K and the V row of a token)  =>  SET_ROWS_PAIR
+    for (size_t i = 0; i + 1 < items.size(); ++i) {
+        const PlanNode & a = items[i].node, & b = items[i + 1].node;
+        if (a.desc.op != SCRAPGPU_OP_SET_ROWS || b.desc.op != SCRAPGPU_OP_SET_ROWS) continue;
+        if (descs_overlap(a.outputs[0], b.inputs[0]) || descs_overlap(a.outputs[0], b.inputs[1]) || descs_overlap(a.outputs[0], b.outputs[0])) continue;
+        PlanNode n = make_node(SCRAPGPU_OP_SET_ROWS_PAIR, {a.inputs[0], a.inputs[1], b.inputs[0], b.inputs[1]}, {a.outputs[0], b.outputs[0]}, a.desc.params,
+                               a.desc.params_size, 0);
+        if (!accepted(n)) continue;
+        merge(i, 2, std::move(n), false);
+    }
+
+    // 5. steps: a normalisation / split SwiGLU followed by the packed Q4_K MUL_MAT(s) that read its row goes into one launch
+    for (size_t i = 0; i < items.size(); ++i) {
+        PlanStep step;
+        step.nodes = items[i].covers;
+        const PlanNode & a = items[i].node;
+        bool fused_away = false;
+        if (i + 1 < items.size()) {
+            const PlanNode & b = items[i + 1].node;
+            const bool mm = b.desc.op == SCRAPGPU_OP_MUL_MAT || b.desc.op == SCRAPGPU_OP_MUL_MAT_MULTI;
+            const size_t nw = mm ? b.outputs.size() : 0;
+            const scrapgpu_tensor_desc * x = mm ? &b.inputs[nw] : nullptr;
+            bool weights_ok = mm;
+            for (size_t k = 0; k < nw && weights_ok; ++k) weights_ok = packed_q4k_weight(b.inputs[k]) && dense_rows(b.outputs[k]);
+            FusedCall f;
+            bool ok = false;
+            if (weights_ok && (a.desc.op == SCRAPGPU_OP_RMS_NORM_MUL || a.desc.op == SCRAPGPU_OP_ADD_RMS_NORM_MUL)) {
+                const bool add = a.desc.op == SCRAPGPU_OP_ADD_RMS_NORM_MUL;
+                const scrapgpu_tensor_desc & y = a.outputs[add ? 1 : 0];
+                if (same_tensor(*x, y) && single_row(y) && ne(y, 0) <= 8192 && single_row(a.inputs[0])) {
+                    f.prologue = SM100_PROLOGUE_RMS_NORM;
+                    f.a = a.inputs[0];
+                    f.has_b = add;
+                    if (add) f.b = a.inputs[1];
+                    f.norm_w = a.inputs[add ? 2 : 1];
+                    f.has_sum = add;
+                    if (add) f.sum_out = a.outputs[0];
+                    f.eps = load_params<scrapgpu_rms_norm_params>(&a.desc).eps;
+                    // the normalised row itself is written unless the caller said that these MUL_MATs are its only reader
+                    f.has_x = !(items[i].y_count_known && a.use_count == (uint32_t) nw);
+                    f.x_out = y;
+                    ok = !descs_overlap(y, f.a) && (!add || (!descs_overlap(y, f.b) && !descs_overlap(f.sum_out, f.a) && !descs_overlap(f.sum_out, f.b)));
+                }
+            } else if (weights_ok && nw == 1 && a.desc.op == SCRAPGPU_OP_GLU && a.inputs.size() == 2 && a.use_count == 1) {
+                const auto gp = load_params<scrapgpu_glu_params>(&a.desc);
+                if (gp.kind == SCRAPGPU_GLU_SWIGLU && same_tensor(*x, a.outputs[0]) && single_row(a.outputs[0]) && single_row(a.inputs[0]) && single_row(a.inputs[1])) {
+                    f.prologue = SM100_PROLOGUE_SWIGLU;
+                    f.a = a.inputs[0];
+                    f.b = a.inputs[1];
+                    f.has_b = true;
+                    ok = true;
+                }
+            }
+            if (ok) {
+                for (size_t k = 0; k < nw; ++k) {
+                    f.w.push_back(b.inputs[k]);
+                    f.y.push_back(b.outputs[k]);
+                    if (descs_overlap(b.outputs[k], f.a) || (f.has_b && descs_overlap(b.outputs[k], f.b))) ok = false;
+                }
+            }
+            if (ok) {
+                step.nodes.insert(step.nodes.end(), items[i + 1].covers.begin(), items[i + 1].covers.end());
+                step.fused = (int) plan.fused.size();
+                plan.fused.push_back(std::move(f));
+                fused_away = true;
+            }
+        }
+        if (!fused_away && items[i].synthetic) {
+            step.lowered = (int) plan.lowered.size();
+            plan.lowered.push_back(items[i].node);
+        }
+        plan.steps.push_back(std::move(step));
+        if (fused_away) ++i;
+    }
+}
+
+scrapgpu_status run_fused(Stream * s, const FusedCall & f) {
+    Ref a, b, nw, so, xo;
+    scrapgpu_status st = resolve(s, f.a, a);
+    if (st == SCRAPGPU_STATUS_OK && f.has_b) st = resolve(s, f.b, b);
+    if (st == SCRAPGPU_STATUS_OK && f.prologue == SM100_PROLOGUE_RMS_NORM) st = resolve(s, f.norm_w, nw);
+    if (st == SCRAPGPU_STATUS_OK && f.has_sum) st = resolve(s, f.sum_out, so);
+    if (st == SCRAPGPU_STATUS_OK && f.has_x) st = resolve(s, f.x_out, xo);
+    if (st != SCRAPGPU_STATUS_OK) return st;
+    const size_t n = f.w.size();
+    int dtypes[3], layouts[3];
+    const void * ws[3];
+    int64_t ns[3];
+    float * ys[3];
+    for (size_t i = 0; i < n; ++i) {
+        Ref w, y;
+        if ((st = resolve(s, f.w[i], w)) != SCRAPGPU_STATUS_OK || (st = resolve(s, f.y[i], y)) != SCRAPGPU_STATUS_OK) return st;
+        dtypes[i] = w.d.dtype;
+        layouts[i] = 1;
+        ws[i] = w.base();
+        ns[i] = ne(w.d, 1);
+        ys[i] = (float *) y.base();
+    }
+    if ((st = from_sm100(sm100_set_device(s->dev->ordinal))) != SCRAPGPU_STATUS_OK) return st;
+    return from_sm100(sm100_mul_mat_fused(s->cuda, f.prologue, (const float *) a.base(), f.has_b ? (const float *) b.base() : nullptr,
+                                          f.prologue == SM100_PROLOGUE_RMS_NORM ? (const float *) nw.base() : nullptr, f.eps,
+                                          f.has_sum ? (float *) so.base() : nullptr, f.has_x ? (float *) xo.base() : nullptr, (int) n, dtypes, layouts, ws,
+                                          ne(f.a, 0), ns, ys));
+}
+
+// runs the plan's steps in order on the stream (directly, or into a capture)
+scrapgpu_status run_steps(Stream * s, Plan * plan) {
+    for (PlanStep & step : plan->steps) {
+        scrapgpu_status st = SCRAPGPU_STATUS_UNSUPPORTED;
+        if (!step.declined && step.fused >= 0) st = run_fused(s, plan->fused[(size_t) step.fused]);
+        else if (!step.declined && step.lowered >= 0) st = execute(s, &plan->lowered[(size_t) step.lowered].desc);
+        if ((step.fused >= 0 || step.lowered >= 0) && !step.declined) {
+            if (st == SCRAPGPU_STATUS_OK) continue;
+            // refused before anything was launched (a shape the fused kernel does not serve, an aliasing the fused form
+            // cannot honour): the caller's own nodes, each of which was accepted at build time, run from now on
+            if (st != SCRAPGPU_STATUS_UNSUPPORTED && st != SCRAPGPU_STATUS_INVALID_ARGUMENT) return enqueue_result(s, st);
+            step.declined = true;
+        }
+        for (size_t i : step.nodes) {
+            st = enqueue_result(s, execute(s, &plan->nodes[i].desc));
+            if (st != SCRAPGPU_STATUS_OK) return st;
+        }
+    }
+    return SCRAPGPU_STATUS_OK;
+}
+
 scrapgpu_status v_plan_build(scrapgpu_device_t * device, const scrapgpu_plan_desc * desc, scrapgpu_plan_t ** out_plan) {
     return guard([&]() -> scrapgpu_status {
         Device * d = as_device(device);
@@ -1211,16 +1501,14 @@ scrapgpu_status v_plan_build(scrapgpu_device_t * device, const scrapgpu_plan_des
             }
             PlanNode & n = plan->nodes[i];
             n.desc = src.op;
-            n.desc.struct_size = sizeof(n.desc);
             for (size_t j = 0; j < src.op.input_count; ++j) n.inputs.push_back(load_desc(src.op.inputs[j]));
             for (size_t j = 0; j < src.op.output_count; ++j) n.outputs.push_back(load_desc(src.op.outputs[j]));
             if (src.op.params != nullptr && src.op.params_size > 0) {
                 const uint8_t * p = static_cast<const uint8_t *>(src.op.params);
                 n.params.assign(p, p + src.op.params_size);
             }
-            n.desc.inputs = n.inputs.data();
-            n.desc.outputs = n.outputs.data();
-            n.desc.params = n.params.empty() ? nullptr : n.params.data();
+            n.use_count = src.struct_size >= offsetof(scrapgpu_plan_node, output_use_count) + sizeof(src.output_use_count) ? src.output_use_count : 0;
+            n.rebind();
             // descriptor pointers inside the params must point at the plan's own copies
             if (src.op.op == SCRAPGPU_OP_ROPE && n.params.size() >= sizeof(scrapgpu_rope_params)) {
                 auto * p = reinterpret_cast<scrapgpu_rope_params *>(n.params.data());
@@ -1233,6 +1521,16 @@ scrapgpu_status v_plan_build(scrapgpu_device_t * device, const scrapgpu_plan_des
             }
             for (const auto & t : n.inputs) if (Buffer * rb = as_buffer(t.buffer)) plan->pinned.push_back(rb);
             for (const auto & t : n.outputs) if (Buffer * rb = as_buffer(t.buffer)) plan->pinned.push_back(rb);
+        }
+        static const bool fuse = [] { const char * e = std::getenv("SCRAPGPU_SM100_PLAN_FUSION"); return e == nullptr || std::atoi(e) != 0; }();
+        if (fuse) {
+            lower_plan(*plan);
+        } else {
+            for (size_t i = 0; i < plan->nodes.size(); ++i) {
+                PlanStep st;
+                st.nodes = {i};
+                plan->steps.push_back(std::move(st));
+            }
         }
         {
             std::lock_guard<std::mutex> lock(g_pin_mutex);
@@ -1249,11 +1547,35 @@ scrapgpu_status v_plan_execute(scrapgpu_stream_t * stream, scrapgpu_plan_t * pla
         Plan * plan = as_plan(plan_);
         if (s == nullptr || plan == nullptr) return invalid("stream or plan is not a cuda_sm100 object");
         if (plan->dev != s->dev) return invalid("plan and stream belong to different devices");
-        for (auto & node : plan->nodes) {
-            const scrapgpu_status st = enqueue_result(s, execute(s, &node.desc));
-            if (st != SCRAPGPU_STATUS_OK) return st;
+        static const bool graphs = [] { const char * e = std::getenv("SCRAPGPU_SM100_PLAN_GRAPH"); return e == nullptr || std::atoi(e) != 0; }();
+        const uint64_t run = plan->executions++;
+        scrapgpu_status st = from_sm100(sm100_set_device(s->dev->ordinal));
+        if (st != SCRAPGPU_STATUS_OK) return st;
+        if (plan->graph != nullptr) return enqueue_result(s, from_sm100(sm100_graph_launch(plan->graph, s->cuda)));
+        // first execution: step by step (scratch buffers, ROPE tables and fused-or-not decisions settle here);
+        // second: the same steps recorded into a graph, which is then launched; a plan of one launch gains nothing
+        if (!graphs || plan->graph_refused || run == 0 || plan->launches_per_execution < 2) {
+            const uint64_t before = sm100_launch_count();
+            st = run_steps(s, plan);
+            plan->launches_per_execution = (size_t) (sm100_launch_count() - before);
+            return st;
         }
-        return SCRAPGPU_STATUS_OK;
+        st = from_sm100(sm100_graph_begin(s->cuda));
+        if (st != SCRAPGPU_STATUS_OK) {   // e.g. the caller is capturing this stream itself: just enqueue
+            plan->graph_refused = true;
+            return run_steps(s, plan);
+        }
+        const scrapgpu_status recorded = run_steps(s, plan);
+        sm100_graph_t g = nullptr;
+        const scrapgpu_status ended = from_sm100(sm100_graph_end(s->cuda, &g));
+        if (recorded != SCRAPGPU_STATUS_OK || ended != SCRAPGPU_STATUS_OK) {
+            if (g != nullptr) sm100_graph_destroy(g);
+            plan->graph_refused = true;   // nothing was executed by the failed recording: run the steps directly
+            s->sticky = SCRAPGPU_STATUS_OK;
+            return run_steps(s, plan);
+        }
+        plan->graph = g;
+        return enqueue_result(s, from_sm100(sm100_graph_launch(plan->graph, s->cuda)));
     });
 }
 
@@ -1268,6 +1590,7 @@ scrapgpu_status v_plan_free(scrapgpu_plan_t * plan_) {
                 if (it != g_pins.end() && --it->second == 0) g_pins.erase(it);
             }
         }
+        if (plan->graph != nullptr) sm100_graph_destroy(plan->graph);
         plan->hdr.backend = nullptr;
         delete plan;
         return SCRAPGPU_STATUS_OK;
