@@ -12,8 +12,9 @@ metric = algorithmic GB/s = sum over launches of (N*K*0.5625 + 4*K + 4*N) bytes 
              launching stream
   e2e        the same pass through the backend plugin's vtable (what scrapgpu_buffer_write / scrapgpu_plan_execute /
              scrapgpu_buffer_read / scrapgpu_stream_sync of the reference's C API forward to) with HOST activations:
-             per step a non-blocking write of every matvec's x from pinned host memory, one plan_execute of the
-             step's MUL_MAT nodes, a non-blocking read of every y into pinned host memory, one sync (weights stay
+             per step one non-blocking write of the arena that holds every matvec's x from pinned host memory, one
+             plan_execute of the step's MUL_MAT nodes, one non-blocking read of the results arena into pinned host
+             memory, one sync (weights stay
              resident, as they do after scrapgpu_tensor_upload in the reference's usage); timed on the host clock
              around steps that each end in a sync
   roofline   achieved = algorithmic bytes per launch / mean launch duration (the same CUDA-event region),
@@ -319,10 +320,10 @@ def run_ours(args, rank: int, world: int, local_rank: int):
                     "ms_per_step": round(e2e["ms_per_step"], 4), "per_op_ms_per_step": round(e2e["per_op_ms_per_step"], 4),
                     "per_op_value": round(world * step_bytes / (e2e["per_op_ms_per_step"] * 1e-3) / 1e9, 1), "results_checked": e2e["checked"],
                     "note": "through the cuda_sm100 backend vtable (the calls behind scrapgpu_buffer_write / scrapgpu_plan_execute / scrapgpu_buffer_read / "
-                            "scrapgpu_stream_sync): per step one non-blocking buffer_write of every matvec's activations from pinned host memory, one "
-                            "plan_execute of the step's MUL_MAT nodes, one non-blocking buffer_read of every result into pinned host memory, one stream_sync; "
-                            "weights resident (uploaded once with tensor_upload, packed layout).  per_op_*: the same with one op_execute per matvec instead "
-                            "of the plan"},
+                            "scrapgpu_stream_sync): per step ONE non-blocking buffer_write of the step's activations (an arena holding every matvec's x) from "
+                            "pinned host memory, one plan_execute of the step's MUL_MAT nodes, ONE non-blocking buffer_read of the results arena into pinned "
+                            "host memory, one stream_sync; weights resident (uploaded once with tensor_upload, packed layout).  per_op_*: one buffer_write, "
+                            "one op_execute and one buffer_read per matvec instead (324 vtable calls and 216 small copies per step)"},
             "roofline": {"bound": "hbm", "kernel": kernel_name, "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
                          "frac": round(achieved / peak, 4), "peak_source": peak_src, "bytes_per_launch": round(per_launch_bytes, 1),
                          "us_per_launch": round(per_launch_us, 3),
@@ -379,18 +380,22 @@ def e2e_through_plugin(capi, stream, pool, order, dtype, device_index, rng, warm
             rot = np.ascontiguousarray(np.roll(base, layer * 17, axis=0) if layer else base)
             ok(vt.tensor_upload(st_, C.byref(d), rot.ctypes.data_as(C.c_void_p), rot.nbytes), "tensor_upload")
             wdesc[(s, layer)] = d
-    ops, hx, hy, xbuf, ybuf = [], [], [], [], []
-    for s, layer in order:
+    # one activation arena and one result arena on the device, mirrored by two pinned host arenas: a step's inputs
+    # go up with ONE buffer_write and its results come back with ONE buffer_read (tensor i lives at its offset)
+    xoff, yoff, xo, yo = [], [], 0, 0
+    for s, _ in order:
+        xoff.append(xo)
+        yoff.append(yo)
+        xo += 4 * SHAPES[s][0]
+        yo += 4 * SHAPES[s][1]
+    xarena, yarena = alloc(xo), alloc(yo)
+    hx, hy = pinned(xo), pinned(yo)
+    C.memmove(hx, rng.standard_normal(xo // 4).astype(np.float32).ctypes.data, xo)
+    ops = []
+    for i, (s, layer) in enumerate(order):
         k, n = SHAPES[s]
-        xb, yb = alloc(4 * k), alloc(4 * n)
-        xbuf.append(xb)
-        ybuf.append(yb)
-        px, py = pinned(4 * k), pinned(4 * n)
-        C.memmove(px, rng.standard_normal(k).astype(np.float32).ctypes.data, 4 * k)
-        hx.append(px)
-        hy.append(py)
-        ops.append(abi.Op(abi.OP_MUL_MAT, [wdesc[(s, layer)], abi.tensor_desc(abi.F32, [k], buffer=xb.value)], [abi.tensor_desc(abi.F32, [n], buffer=yb.value)],
-                          abi.MulMatParams(0, 0)))
+        ops.append(abi.Op(abi.OP_MUL_MAT, [wdesc[(s, layer)], abi.tensor_desc(abi.F32, [k], buffer=xarena.value, offset=xoff[i])],
+                          [abi.tensor_desc(abi.F32, [n], buffer=yarena.value, offset=yoff[i])], abi.MulMatParams(0, 0)))
     nodes = (abi.PlanNode * len(ops))()
     for i, o in enumerate(ops):
         nodes[i].struct_size = C.sizeof(abi.PlanNode)
@@ -400,19 +405,19 @@ def e2e_through_plugin(capi, stream, pool, order, dtype, device_index, rng, warm
     plan = C.c_void_p()
     ok(vt.plan_build(dev, C.byref(pd), C.byref(plan)), "plan_build")
     sizes = [(4 * SHAPES[s][0], 4 * SHAPES[s][1]) for s, _ in order]
+    hxi = [C.c_void_p(hx.value + o) for o in xoff]
+    hyi = [C.c_void_p(hy.value + o) for o in yoff]
 
     def step(per_op):
-        if per_op:
+        if per_op:     # one write, one op_execute and one read per matvec
             for i, o in enumerate(ops):
-                ok(vt.buffer_write(st_, xbuf[i], 0, hx[i], sizes[i][0], 0), "buffer_write")
+                ok(vt.buffer_write(st_, xarena, xoff[i], hxi[i], sizes[i][0], 0), "buffer_write")
                 ok(vt.op_execute(st_, o.ptr()), "op_execute")
-                ok(vt.buffer_read(st_, ybuf[i], 0, hy[i], sizes[i][1], 0), "buffer_read")
+                ok(vt.buffer_read(st_, yarena, yoff[i], hyi[i], sizes[i][1], 0), "buffer_read")
         else:
-            for i in range(len(ops)):
-                ok(vt.buffer_write(st_, xbuf[i], 0, hx[i], sizes[i][0], 0), "buffer_write")
+            ok(vt.buffer_write(st_, xarena, 0, hx, xo, 0), "buffer_write")
             ok(vt.plan_execute(st_, plan), "plan_execute")
-            for i in range(len(ops)):
-                ok(vt.buffer_read(st_, ybuf[i], 0, hy[i], sizes[i][1], 0), "buffer_read")
+            ok(vt.buffer_read(st_, yarena, 0, hy, yo, 0), "buffer_read")
         ok(vt.stream_sync(st_), "stream_sync")
 
     def timed(per_op):
@@ -430,8 +435,8 @@ def e2e_through_plugin(capi, stream, pool, order, dtype, device_index, rng, warm
     for s in range(len(SHAPES)):
         i = next(j for j, (ss, _) in enumerate(order) if ss == s)
         k, n = SHAPES[s]
-        got = np.ctypeslib.as_array(C.cast(hy[i], C.POINTER(C.c_float)), shape=(n,)).copy()
-        xh = np.ctypeslib.as_array(C.cast(hx[i], C.POINTER(C.c_float)), shape=(k,)).copy()
+        got = np.ctypeslib.as_array(C.cast(hyi[i], C.POINTER(C.c_float)), shape=(n,)).copy()
+        xh = np.ctypeslib.as_array(C.cast(hxi[i], C.POINTER(C.c_float)), shape=(k,)).copy()
         xd, yd = capi.Buffer(4 * k), capi.Buffer(4 * n)
         xd.upload(stream, xh)
         capi.mul_mat(stream, dtype, 1, pool[s]["mats"][order[i][1]], k, n, xd, 1, yd)
@@ -443,9 +448,9 @@ def e2e_through_plugin(capi, stream, pool, order, dtype, device_index, rng, warm
         xd.free()
         yd.free()
     ok(vt.plan_free(plan), "plan_free")
-    for b in xbuf + ybuf + [C.c_void_p(d.buffer) for d in wdesc.values()]:
+    for b in [xarena, yarena] + [C.c_void_p(d.buffer) for d in wdesc.values()]:
         vt.buffer_free(b)
-    for p in hx + hy:
+    for p in (hx, hy):
         L.sm100_host_free(p)
     vt.stream_free(st_)
     return {"ms_per_step": plan_ms, "per_op_ms_per_step": per_op_ms, "checked": checked}

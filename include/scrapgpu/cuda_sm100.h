@@ -40,6 +40,49 @@ SCRAPGPU_API scrapgpu_status scrapgpu_cuda_sm100_attention_at(scrapgpu_device_t 
                                                              const scrapgpu_attention_params * params,
                                                              const scrapgpu_tensor_desc * position);
 
+/* ---- multi-GPU transport -----------------------------------------------------------------------------------------
+ * The core moves a tensor between two devices through a host staging buffer: a blocking read on the source stream,
+ * then a blocking write on the destination stream (src/core/transport.cpp:128-145, contract
+ * include/scrapgpu/tensor.h:55-67).  Between two cuda_sm100 devices the bytes can go GPU to GPU over NVLink instead. */
+
+/* scrapgpu_tensor_copy for two cuda_sm100 tensors: same contract (contiguous tensors of one dtype and shape, natural
+ * layout only, the copy happens after the work already enqueued on src_stream and before work enqueued later on
+ * dst_stream), but asynchronous and without the host bounce: an event on src_stream, a wait on dst_stream, one
+ * peer copy.  Works for the same device too. */
+SCRAPGPU_API scrapgpu_status scrapgpu_cuda_sm100_tensor_copy(scrapgpu_stream_t * src_stream, const scrapgpu_tensor_desc * src,
+                                                            scrapgpu_stream_t * dst_stream, const scrapgpu_tensor_desc * dst);
+
+/* A group of cuda_sm100 devices that run one model tensor-parallel from ONE process (one stream per device, each
+ * driven by the calling thread as the contract asks, docs/API_CONTRACT.md:59).  Creating the group enables peer access
+ * between all pairs and sets up the receive areas of the one-shot all-reduce (up to 8 devices, max_elements floats). */
+typedef struct scrapgpu_cuda_sm100_group scrapgpu_cuda_sm100_group_t;
+SCRAPGPU_API scrapgpu_status scrapgpu_cuda_sm100_group_create(scrapgpu_device_t * const * devices, size_t count, size_t max_elements,
+                                                             scrapgpu_cuda_sm100_group_t ** out_group);
+SCRAPGPU_API scrapgpu_status scrapgpu_cuda_sm100_group_free(scrapgpu_cuda_sm100_group_t * group);
+/* In-place sum over the group: tensors[i] (F32, contiguous, the same length on every device, a multiple of 4 elements,
+ * 16-byte aligned) lives on device i and is updated on streams[i]; every device ends up with the same bits (the
+ * partial vectors are added in device order).  One kernel per device; a device that waits longer than about a second
+ * for a peer gives up and the next scrapgpu_cuda_sm100_group_status reports BACKEND_ERROR. */
+SCRAPGPU_API scrapgpu_status scrapgpu_cuda_sm100_group_all_reduce(scrapgpu_cuda_sm100_group_t * group, scrapgpu_stream_t * const * streams,
+                                                                 const scrapgpu_tensor_desc * tensors);
+SCRAPGPU_API scrapgpu_status scrapgpu_cuda_sm100_group_status(scrapgpu_cuda_sm100_group_t * group);
+
+/* Shard arithmetic for tensor parallelism, on descriptors only (no device needed).  `full` describes a natural-layout
+ * 2-D weight [K, N] (N rows of K elements); out_view receives the view of rank `rank` of `world`:
+ *   split_dim 1 (column-parallel: Q, K, V, gate, up, vocabulary head): rows [rank * ceil(N / world), ...), the last
+ *               rank may get fewer rows (or none: ne[1] = 0);
+ *   split_dim 0 (row-parallel: o, down): elements [rank * K / world, (rank + 1) * K / world) of every row; K / world
+ *               must be a whole number of quantization blocks.  The view keeps the row stride of the full tensor.
+ * The view shares `full`'s buffer field and has offset advanced accordingly, so it describes the shard inside a host
+ * image of the full tensor just as well as inside a device buffer. */
+SCRAPGPU_API scrapgpu_status scrapgpu_cuda_sm100_shard(const scrapgpu_tensor_desc * full, int split_dim, size_t rank, size_t world,
+                                                      scrapgpu_tensor_desc * out_view);
+/* Uploads the (possibly strided) view `src_view` of a natural-layout host image starting at `host_base` (the byte the
+ * view's offset counts from) into the contiguous device tensor `dst` of the same dtype and shape; dst may carry the
+ * packed-layout tag.  This is tensor_upload for a shard cut out of the full tensor's host image. */
+SCRAPGPU_API scrapgpu_status scrapgpu_cuda_sm100_upload_view(scrapgpu_stream_t * stream, const scrapgpu_tensor_desc * dst, const void * host_base,
+                                                            const scrapgpu_tensor_desc * src_view);
+
 /* Kernels launched by this process through the backend so far (per-process counter for profiling). */
 SCRAPGPU_API uint64_t scrapgpu_cuda_sm100_launch_count(void);
 

@@ -65,7 +65,12 @@ SM100_API int sm100_memset(sm100_stream_t s, void * dst, int byte, size_t n, int
 SM100_API int sm100_memcpy_peer(sm100_stream_t dst_stream, int dst_device, void * dst, sm100_stream_t src_stream,
                                 int src_device, const void * src, size_t n);
 
-/* ---- tensor-parallel exchange over peer-mapped memory (one process per GPU) ----
+/* lets kernels and copies running on `device` address memory allocated on `peer` (both in this process); UNSUPPORTED
+ * when the two GPUs have no peer path.  Needed once per ordered pair before sm100_allreduce_* is used with areas that
+ * live in the same process (ranks in separate processes map each other's areas with sm100_ipc_open instead). */
+SM100_API int sm100_peer_access(int device, int peer);
+
+/* ---- tensor-parallel exchange over peer-mapped memory (one process per GPU, or one process driving several) ----
  * The reference moves tensors between devices through a host bounce (src/core/transport.cpp:53-146) and has no
  * collective; the tensor-parallel decode needs an all-reduce of the hidden vector after the row-parallel projections.
  * Each rank allocates one area of sm100_allreduce_area_bytes() with sm100_malloc, zero-fills it, exports it

@@ -1686,6 +1686,103 @@ scrapgpu_status attention(scrapgpu_device_t * device, scrapgpu_stream_t * stream
     return SCRAPGPU_STATUS_OK;
 }
 
+
+// ---------------------------------------------------------------------------------------------------------
+// multi-GPU transport and the tensor-parallel device group
+// ---------------------------------------------------------------------------------------------------------
+
+struct Group {
+    std::vector<Device *> devices;
+    std::vector<void *> areas;              // receive area of every device (sm100_allreduce_area_bytes each)
+    std::vector<sm100_allreduce_t> ranks;   // the all-reduce context of every device
+    size_t capacity = 0;
+};
+
+std::mutex g_group_mutex;
+std::vector<Group *> g_groups;
+
+Group * as_group(scrapgpu_cuda_sm100_group_t * g) {
+    std::lock_guard<std::mutex> lock(g_group_mutex);
+    for (Group * known : g_groups) if ((void *) known == (void *) g) return known;
+    return nullptr;
+}
+
+void destroy_group(Group * g) {
+    for (size_t i = 0; i < g->ranks.size(); ++i) if (g->ranks[i] != nullptr) sm100_allreduce_destroy(g->ranks[i]);
+    for (size_t i = 0; i < g->areas.size(); ++i) if (g->areas[i] != nullptr) sm100_free(g->devices[i]->ordinal, g->areas[i]);
+    delete g;
+}
+
+scrapgpu_status tensor_copy(scrapgpu_stream_t * src_stream, const scrapgpu_tensor_desc * src, scrapgpu_stream_t * dst_stream, const scrapgpu_tensor_desc * dst) {
+    Stream * ss = as_stream(src_stream);
+    Stream * ds = as_stream(dst_stream);
+    if (ss == nullptr || ds == nullptr || src == nullptr || dst == nullptr) return invalid("src_stream, dst_stream, src or dst is null or not a cuda_sm100 object");
+    if (src->struct_size < sizeof(scrapgpu_tensor_desc) || dst->struct_size < sizeof(scrapgpu_tensor_desc)) return invalid("tensor desc is too small");
+    const scrapgpu_tensor_desc s = load_desc(*src), d = load_desc(*dst);
+    if (type_size(s.dtype) == 0) return unsupported("unknown tensor dtype");
+    if (s.dtype != d.dtype) return unsupported("src and dst dtypes differ");
+    for (int i = 0; i < 4; ++i) {
+        if (s.ne[i] != d.ne[i]) return unsupported("src and dst shapes differ");
+        if (s.ne[i] < 0) return invalid("negative tensor dim");
+    }
+    if (s.layout == SCRAPGPU_LAYOUT_R32 || d.layout == SCRAPGPU_LAYOUT_R32)
+        return unsupported("backend-packed tensors are not allowed: move them through the host with tensor_download / tensor_upload");
+    if (!contiguous(s) || !contiguous(d)) return unsupported("tensor is not contiguous; use buffer_read / buffer_write for raw strided transfers");
+    Ref rs, rd;
+    scrapgpu_status st = resolve(ss, s, rs);
+    if (st == SCRAPGPU_STATUS_OK) st = resolve(ds, d, rd);
+    if (st != SCRAPGPU_STATUS_OK) return st;
+    const uint64_t bytes = span_bytes(s);
+    if (bytes == 0) return SCRAPGPU_STATUS_OK;
+    if (ss->dev == ds->dev && overlap(rs, rd)) return invalid("src and dst overlap");
+    return enqueue_result(ds, from_sm100(sm100_memcpy_peer(ds->cuda, ds->dev->ordinal, rd.base(), ss->cuda, ss->dev->ordinal, rs.base(), (size_t) bytes)));
+}
+
+scrapgpu_status shard(const scrapgpu_tensor_desc * full_, int split_dim, size_t rank, size_t world, scrapgpu_tensor_desc * out) {
+    if (full_ == nullptr || out == nullptr || full_->struct_size < sizeof(scrapgpu_tensor_desc)) return invalid("tensor desc is null or too small");
+    if (world == 0 || rank >= world) return invalid("rank must be below world");
+    const scrapgpu_tensor_desc full = load_desc(*full_);
+    const size_t bs = block_size(full.dtype), ts = type_size(full.dtype);
+    if (bs == 0) return unsupported("unknown tensor dtype");
+    if (full.layout != SCRAPGPU_LAYOUT_NATURAL) return unsupported("shards are cut from the natural layout (pack the shard, not the full tensor)");
+    if (ne(full, 2) * ne(full, 3) != 1) return unsupported("a 2-D weight tensor is expected");
+    if (full.nb[0] != ts) return unsupported("rows must be contiguous");
+    scrapgpu_tensor_desc v = full;
+    if (split_dim == 1) {
+        const int64_t n = ne(full, 1), per = (n + (int64_t) world - 1) / (int64_t) world;
+        const int64_t lo = std::min<int64_t>(n, (int64_t) rank * per), cnt = std::max<int64_t>(0, std::min<int64_t>(n, lo + per) - lo);
+        v.ne[1] = cnt;
+        v.offset = full.offset + (uint64_t) lo * full.nb[1];
+    } else if (split_dim == 0) {
+        const int64_t k = ne(full, 0);
+        if (k % (int64_t) world != 0 || (k / (int64_t) world) % (int64_t) bs != 0) return unsupported("K / world must be a whole number of quantization blocks");
+        const int64_t kl = k / (int64_t) world;
+        v.ne[0] = kl;
+        v.offset = full.offset + (uint64_t) rank * (uint64_t) (kl / (int64_t) bs) * ts;
+    } else {
+        return invalid("split_dim must be 0 (K) or 1 (rows)");
+    }
+    *out = v;
+    return SCRAPGPU_STATUS_OK;
+}
+
+scrapgpu_status upload_view(scrapgpu_stream_t * stream, const scrapgpu_tensor_desc * dst_, const void * host_base, const scrapgpu_tensor_desc * view_) {
+    Stream * s = as_stream(stream);
+    if (s == nullptr || dst_ == nullptr || view_ == nullptr || host_base == nullptr) return invalid("stream, dst, host_base or src_view is null");
+    if (dst_->struct_size < sizeof(scrapgpu_tensor_desc) || view_->struct_size < sizeof(scrapgpu_tensor_desc)) return invalid("tensor desc is too small");
+    const scrapgpu_tensor_desc d = load_desc(*dst_), v = load_desc(*view_);
+    const size_t bs = block_size(v.dtype), ts = type_size(v.dtype);
+    if (bs == 0 || v.dtype != d.dtype) return unsupported("dtypes differ or are unknown");
+    for (int i = 0; i < 4; ++i) if (ne(v, i) != ne(d, i)) return unsupported("src view and dst shapes differ");
+    if (v.nb[0] != ts || ne(v, 0) % (int64_t) bs != 0 || ne(v, 2) * ne(v, 3) != 1) return unsupported("the view must be 2-D with contiguous rows of whole blocks");
+    const size_t row = (size_t) (ne(v, 0) / (int64_t) bs) * ts;
+    const size_t rows = (size_t) ne(v, 1);
+    std::vector<uint8_t> staging(row * rows);
+    const uint8_t * base = static_cast<const uint8_t *>(host_base) + v.offset;
+    for (size_t r = 0; r < rows; ++r) std::memcpy(staging.data() + r * row, base + r * v.nb[1], row);
+    return transfer(stream, &d, staging.data(), staging.size(), true);
+}
+
 }  // namespace
 
 extern "C" {
@@ -1718,6 +1815,127 @@ SCRAPGPU_API scrapgpu_status scrapgpu_cuda_sm100_attention_at(scrapgpu_device_t 
     return guard([&]() -> scrapgpu_status {
         if (position == nullptr) return invalid("position tensor is null");
         return attention(device, stream, params, position);
+    });
+}
+
+SCRAPGPU_API scrapgpu_status scrapgpu_cuda_sm100_tensor_copy(scrapgpu_stream_t * src_stream, const scrapgpu_tensor_desc * src, scrapgpu_stream_t * dst_stream,
+                                                            const scrapgpu_tensor_desc * dst) {
+    return guard([&]() -> scrapgpu_status { return tensor_copy(src_stream, src, dst_stream, dst); });
+}
+
+SCRAPGPU_API scrapgpu_status scrapgpu_cuda_sm100_shard(const scrapgpu_tensor_desc * full, int split_dim, size_t rank, size_t world, scrapgpu_tensor_desc * out_view) {
+    return guard([&]() -> scrapgpu_status { return shard(full, split_dim, rank, world, out_view); });
+}
+
+SCRAPGPU_API scrapgpu_status scrapgpu_cuda_sm100_upload_view(scrapgpu_stream_t * stream, const scrapgpu_tensor_desc * dst, const void * host_base,
+                                                            const scrapgpu_tensor_desc * src_view) {
+    return guard([&]() -> scrapgpu_status { return upload_view(stream, dst, host_base, src_view); });
+}
+
+SCRAPGPU_API scrapgpu_status scrapgpu_cuda_sm100_group_create(scrapgpu_device_t * const * devices, size_t count, size_t max_elements,
+                                                             scrapgpu_cuda_sm100_group_t ** out_group) {
+    return guard([&]() -> scrapgpu_status {
+        if (devices == nullptr || out_group == nullptr) return invalid("devices or out_group is null");
+        *out_group = nullptr;
+        if (count < 1 || count > 8) return unsupported("a group has 1 to 8 devices");
+        if (max_elements == 0 || max_elements % 4 != 0 || max_elements > (size_t) 1 << 24) return invalid("max_elements must be a positive multiple of 4 (at most 2^24)");
+        auto g = std::make_unique<Group>();
+        for (size_t i = 0; i < count; ++i) {
+            Device * d = as_device(devices[i]);
+            if (d == nullptr) return invalid("not a cuda_sm100 device");
+            for (Device * seen : g->devices) if (seen == d) return invalid("a device appears twice in the group");
+            g->devices.push_back(d);
+        }
+        g->capacity = max_elements;
+        scrapgpu_status st = SCRAPGPU_STATUS_OK;
+        for (size_t i = 0; i < count && st == SCRAPGPU_STATUS_OK; ++i)
+            for (size_t j = 0; j < count && st == SCRAPGPU_STATUS_OK; ++j)
+                if (i != j) st = from_sm100(sm100_peer_access(g->devices[i]->ordinal, g->devices[j]->ordinal));
+        const size_t area_bytes = sm100_allreduce_area_bytes((int) count, (int) max_elements);
+        g->areas.assign(count, nullptr);
+        g->ranks.assign(count, nullptr);
+        for (size_t i = 0; i < count && st == SCRAPGPU_STATUS_OK; ++i) {
+            st = from_sm100(sm100_malloc(g->devices[i]->ordinal, area_bytes, &g->areas[i]));
+            if (st == SCRAPGPU_STATUS_OK) st = from_sm100(sm100_memset(nullptr, g->areas[i], 0, area_bytes, 1));
+        }
+        for (size_t i = 0; i < count && st == SCRAPGPU_STATUS_OK; ++i) {
+            st = from_sm100(sm100_set_device(g->devices[i]->ordinal));
+            if (st == SCRAPGPU_STATUS_OK) st = from_sm100(sm100_allreduce_create((int) i, (int) count, (int) max_elements, g->areas.data(), &g->ranks[i]));
+        }
+        if (st != SCRAPGPU_STATUS_OK) {
+            destroy_group(g.release());
+            return st;
+        }
+        Group * raw = g.release();
+        {
+            std::lock_guard<std::mutex> lock(g_group_mutex);
+            g_groups.push_back(raw);
+        }
+        *out_group = reinterpret_cast<scrapgpu_cuda_sm100_group_t *>(raw);
+        return SCRAPGPU_STATUS_OK;
+    });
+}
+
+SCRAPGPU_API scrapgpu_status scrapgpu_cuda_sm100_group_free(scrapgpu_cuda_sm100_group_t * group) {
+    return guard([&]() -> scrapgpu_status {
+        Group * g = as_group(group);
+        if (g == nullptr) return invalid("not a cuda_sm100 device group");
+        {
+            std::lock_guard<std::mutex> lock(g_group_mutex);
+            g_groups.erase(std::find(g_groups.begin(), g_groups.end(), g));
+        }
+        destroy_group(g);
+        return SCRAPGPU_STATUS_OK;
+    });
+}
+
+SCRAPGPU_API scrapgpu_status scrapgpu_cuda_sm100_group_all_reduce(scrapgpu_cuda_sm100_group_t * group, scrapgpu_stream_t * const * streams,
+                                                                 const scrapgpu_tensor_desc * tensors) {
+    return guard([&]() -> scrapgpu_status {
+        Group * g = as_group(group);
+        if (g == nullptr || streams == nullptr || tensors == nullptr) return invalid("group, streams or tensors is null");
+        const size_t n = g->devices.size();
+        std::vector<Ref> refs(n);
+        std::vector<Stream *> ss(n);
+        int64_t count = 0;
+        for (size_t i = 0; i < n; ++i) {
+            ss[i] = as_stream(streams[i]);
+            if (ss[i] == nullptr || ss[i]->dev != g->devices[i]) return invalid("streams[i] must be a stream of the group's device i");
+            if (tensors[i].struct_size < sizeof(scrapgpu_tensor_desc)) return invalid("tensor desc is too small");
+            const scrapgpu_status st = resolve(ss[i], tensors[i], refs[i]);
+            if (st != SCRAPGPU_STATUS_OK) return st;
+            int64_t elems = 0;
+            if (!f32(refs[i].d) || !contiguous(refs[i].d) || !elements(refs[i].d, elems)) return unsupported("all-reduce tensors must be contiguous F32");
+            if (i == 0) count = elems;
+            if (elems != count) return invalid("all-reduce tensors must have the same length on every device");
+            if (((uintptr_t) refs[i].base() & 15) != 0) return unsupported("all-reduce tensors must be 16-byte aligned");
+        }
+        if (count <= 0 || count % 4 != 0 || (size_t) count > g->capacity) return invalid("the tensor length must be a positive multiple of 4 within the group's max_elements");
+        if (n == 1) return SCRAPGPU_STATUS_OK;   // the sum over one device is the tensor itself
+        for (size_t i = 0; i < n; ++i) {
+            scrapgpu_status st = from_sm100(sm100_set_device(g->devices[i]->ordinal));
+            if (st == SCRAPGPU_STATUS_OK) st = from_sm100(sm100_allreduce_sum(g->ranks[i], ss[i]->cuda, (float *) refs[i].base(), (int) count));
+            if (st != SCRAPGPU_STATUS_OK) return enqueue_result(ss[i], st);
+        }
+        return SCRAPGPU_STATUS_OK;
+    });
+}
+
+SCRAPGPU_API scrapgpu_status scrapgpu_cuda_sm100_group_status(scrapgpu_cuda_sm100_group_t * group) {
+    return guard([&]() -> scrapgpu_status {
+        Group * g = as_group(group);
+        if (g == nullptr) return invalid("not a cuda_sm100 device group");
+        for (size_t i = 0; i < g->ranks.size(); ++i) {
+            int fault = 0;
+            scrapgpu_status st = from_sm100(sm100_set_device(g->devices[i]->ordinal));
+            if (st == SCRAPGPU_STATUS_OK) st = from_sm100(sm100_allreduce_fault(g->ranks[i], &fault));
+            if (st != SCRAPGPU_STATUS_OK) return st;
+            if (fault != 0) {
+                set_error("a device of the group gave up waiting for a peer during an all-reduce; the reduced tensors are incomplete");
+                return SCRAPGPU_STATUS_BACKEND_ERROR;
+            }
+        }
+        return SCRAPGPU_STATUS_OK;
     });
 }
 

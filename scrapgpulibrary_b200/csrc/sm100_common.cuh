@@ -139,7 +139,9 @@ __device__ __forceinline__ void act_group_scale(uint32_t amax_bits, float & inv,
     const float amax = __uint_as_float(amax_bits);
     const bool finite = amax_bits < 0x7f800000u;
     const bool some = finite && amax > 1e-30f;
-    inv = some ? __fdiv_rn(32512.0f, amax) : 0.0f;   // IEEE division: the fast one returns 0 for amax above 2^126
+    // the fast division is exact enough here (the integer range keeps 255 counts of head room) but returns 0 for a
+    // divisor above 2^126: such groups are scaled down first
+    inv = !some ? 0.0f : (amax > 1e30f ? __fdividef(32512.0f * 0x1p-40f, amax * 0x1p-40f) : __fdividef(32512.0f, amax));
     s = some ? amax * (1.0f / 32512.0f) : 0.0f;
     if (!finite) s = __uint_as_float(0x7fc00000u);
 }

@@ -4,12 +4,20 @@
 // from the HBM roofline is not its streaming rate but what happens around it: the ramp of a fresh launch, the
 // activation hand-over from the previous op, the tail.  This kernel is organised around that:
 //
-//  * it needs at most half of an SM (512 threads, <= 64 registers per thread, about 100 KB of shared memory), so the
+//  * it needs at most half of an SM (512 threads, <= 64 registers per thread, about 82 KB of shared memory), so the
 //    CTAs of the NEXT launch on the stream become resident beside the running ones as soon as this launch has allowed
-//    it - which it does in its first instructions (griddepcontrol.launch_dependents).  A resident successor requests
-//    its first weights (up to 72 KB per SM: 10.9 MB over the GPU, more than a whole 4096 x 4096 matrix) with bulk
-//    copies into its shared-memory ring and only then waits for its predecessor (griddepcontrol.wait): HBM streams the
-//    successor's weights while the predecessor computes and drains;
+//    it - which it does in its first instructions (griddepcontrol.launch_dependents).  A resident successor copies
+//    its first weights into its shared-memory ring (72 KB per SM: 10.9 MB over the GPU, more than a whole
+//    4096 x 4096 matrix) and only then waits for its predecessor (griddepcontrol.wait): HBM streams the successor's
+//    first weights while the predecessor computes and drains.  (Asking for the REST of the successor's weights to be
+//    brought into L2 at the same moment was measured too - per-lane prefetch.global.L2 as well as
+//    cp.async.bulk.prefetch.L2 - and made the sweep 4 % slower: the predecessor's loop already runs at the rate HBM
+//    delivers, so the early requests only take bandwidth from it.);
+//  * the ring is fed by per-lane 16-byte asynchronous copies (cp.async), not by bulk copies: a lane copies exactly
+//    the 16 bytes of each tile that it will read back (the packed layout is in MMA-fragment order), so a slot needs no
+//    barrier and no proxy fence - the lane waits for its own copy group - and issuing a refill costs four
+//    instructions.  (Measured with a bulk copy per 2 KB unit: issuing one stalls the warp for about 0.4 us, which
+//    made the loop latency-bound at 0.95 us per unit whatever the memory system delivered.);
 //  * nothing in the main loop is CTA-wide.  A warp owns a fixed K range (whole 256-weight blocks), quantizes exactly
 //    the activations of that range into REGISTERS in the B-fragment order of mma.m16n8k32 (no shared-memory image of
 //    x, no barrier between quantization and the first MMA), and walks over the CTA's row tiles with its own ring
@@ -22,7 +30,6 @@
 // mul_mv_multi.cl:46-104) for packed tensors, M = 1, K up to 48 blocks per group of warps.
 #include "sm100_quant_units.cuh"
 
-#include <atomic>
 #include <cstdlib>
 
 namespace sm100 {
@@ -31,12 +38,11 @@ namespace {
 
 constexpr int RG_WARPS = 16;
 constexpr int RG_THREADS = RG_WARPS * 32;
-constexpr int RG_SLOTS = 2;                       // ring slots per warp
+constexpr int RG_MAX_SLOTS = 3;                   // ring slots per warp: 3 where two CTAs of that size fit an SM, else 2
 constexpr uint32_t RG_TILE_BYTES = 2048;          // 16 rows x 256 weights
 constexpr uint32_t RG_HDR_BYTES = 256;            // their 16 block headers
-constexpr int RG_WINDOW = 8;                      // rounds whose partial sums are kept before the CTA adds them up
+constexpr int RG_WINDOW = 4;                      // rounds whose partial sums are kept before the CTA adds them up
 constexpr int RG_MAX_TENSORS = 3;
-constexpr uint32_t RG_WAIT_LIMIT = 1u << 22;      // polls of one barrier before the warp gives up
 
 struct RingArgs {
     const uint8_t * w[RG_MAX_TENSORS];   // packed tensor bases
@@ -51,40 +57,17 @@ struct RingArgs {
     int blocks;         // K / 256
     int wpt;            // warps that share one row tile (they split K); a power of two <= 16
     int groups;         // row tiles a CTA works on at a time = 16 / wpt
+    int slots;          // ring slots per warp (2 or 3)
 };
 
-__device__ int g_ring_fault;
-
 __device__ __forceinline__ uint32_t rg_smem(const void * p) { return (uint32_t) __cvta_generic_to_shared(p); }
-__device__ __forceinline__ void rg_bar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void rg_bar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool rg_bar_try_wait(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-// global -> shared bulk copy (the TMA unit, untiled form); addresses and size are multiples of 16
-__device__ __forceinline__ void rg_bulk_g2s(uint32_t dst, const void * src, uint32_t bytes, uint32_t bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(src),
-                 "r"(bytes), "r"(bar)
-                 : "memory");
-}
+// per-thread 16-byte asynchronous copy global -> shared (L2 only), and the grouping of such copies
 __device__ __forceinline__ void rg_cp_async16(uint32_t dst, const void * src) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
 }
-__device__ __forceinline__ void rg_cp_async_arrive(uint32_t bar) {
-    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
-}
+__device__ __forceinline__ void rg_cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void rg_cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 __device__ __forceinline__ uint32_t rg_lds32(uint32_t addr) {
     uint32_t v;
     asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
@@ -128,44 +111,68 @@ struct RgBlockX {
     float s0, x0, s1, x1;   // (scale, sum of activations) of sub-blocks 2t and 2t+1: what this lane's C columns need
 };
 
-__device__ __forceinline__ void rg_quantize(const float4 va, const float4 vb, int lane, RgBlockX & o) {
+// Quantizes the NB blocks of a warp side by side, stage by stage, so that the shuffle and conversion latencies of the
+// blocks overlap (one block after the other the chains are serial: 0.55 us per block was measured).
+template <int NBW>
+__device__ __forceinline__ void rg_quantize(const float4 (&va)[NBW], const float4 (&vb)[NBW], int nb, int lane, RgBlockX (&o)[NBW]) {
     const int g = lane >> 2, t = lane & 3;
-    float amax = rg_absmax_nan(rg_absmax_nan(rg_absmax_nan(va.x, va.y), rg_absmax_nan(va.z, va.w)),
-                               rg_absmax_nan(rg_absmax_nan(vb.x, vb.y), rg_absmax_nan(vb.z, vb.w)));
-    float sum = ((va.x + va.y) + (va.z + va.w)) + ((vb.x + vb.y) + (vb.z + vb.w));
-    amax = rg_absmax_nan(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-    sum += __shfl_xor_sync(0xffffffffu, sum, 1);
-    amax = rg_absmax_nan(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-    sum += __shfl_xor_sync(0xffffffffu, sum, 2);
-    float inv, s;
-    act_group_scale(__float_as_uint(amax), inv, s);
+    float amax[NBW], sum[NBW], inv[NBW], s[NBW];
+#pragma unroll
+    for (int i = 0; i < NBW; ++i) {
+        if (i < nb) {
+            amax[i] = rg_absmax_nan(rg_absmax_nan(rg_absmax_nan(va[i].x, va[i].y), rg_absmax_nan(va[i].z, va[i].w)),
+                                    rg_absmax_nan(rg_absmax_nan(vb[i].x, vb[i].y), rg_absmax_nan(vb[i].z, vb[i].w)));
+            sum[i] = ((va[i].x + va[i].y) + (va[i].z + va[i].w)) + ((vb[i].x + vb[i].y) + (vb[i].z + vb[i].w));
+        }
+    }
+#pragma unroll
+    for (int o2 = 1; o2 <= 2; o2 <<= 1) {
+#pragma unroll
+        for (int i = 0; i < NBW; ++i) {
+            if (i < nb) {
+                amax[i] = rg_absmax_nan(amax[i], __shfl_xor_sync(0xffffffffu, amax[i], o2));
+                sum[i] += __shfl_xor_sync(0xffffffffu, sum[i], o2);
+            }
+        }
+    }
     // round to nearest even without the conversion unit: 1.5 * 2^23 + v keeps the integer in the mantissa (|v| <= 32512),
     // integer = bits - 0x4B400000.  16-bit integer = 256 h + l with h, l signed bytes: h = (integer + 128) >> 8, l = its
     // low byte, which is also the low byte of `bits`.
-    const int q0 = __float_as_int(fmaf(va.x, inv, 12582912.0f)), q1 = __float_as_int(fmaf(va.y, inv, 12582912.0f)),
-              q2 = __float_as_int(fmaf(va.z, inv, 12582912.0f)), q3 = __float_as_int(fmaf(va.w, inv, 12582912.0f)),
-              q4 = __float_as_int(fmaf(vb.x, inv, 12582912.0f)), q5 = __float_as_int(fmaf(vb.y, inv, 12582912.0f)),
-              q6 = __float_as_int(fmaf(vb.z, inv, 12582912.0f)), q7 = __float_as_int(fmaf(vb.w, inv, 12582912.0f));
     constexpr int HB = 128 - 0x4B400000;
-    const uint32_t h0 = __byte_perm(__byte_perm((uint32_t) ((q0 + HB) >> 8), (uint32_t) ((q1 + HB) >> 8), 0x0040),
-                                    __byte_perm((uint32_t) ((q2 + HB) >> 8), (uint32_t) ((q3 + HB) >> 8), 0x0040), 0x5410);
-    const uint32_t h1 = __byte_perm(__byte_perm((uint32_t) ((q4 + HB) >> 8), (uint32_t) ((q5 + HB) >> 8), 0x0040),
-                                    __byte_perm((uint32_t) ((q6 + HB) >> 8), (uint32_t) ((q7 + HB) >> 8), 0x0040), 0x5410);
-    const uint32_t l0 = __byte_perm(__byte_perm((uint32_t) q0, (uint32_t) q1, 0x0040), __byte_perm((uint32_t) q2, (uint32_t) q3, 0x0040), 0x5410);
-    const uint32_t l1 = __byte_perm(__byte_perm((uint32_t) q4, (uint32_t) q5, 0x0040), __byte_perm((uint32_t) q6, (uint32_t) q7, 0x0040), 0x5410);
-    // an even g holds the pair's low sub-block and supplies the h plane; an odd g the high sub-block and the l plane
-    const bool odd = (g & 1) != 0;
-    const uint32_t r0 = __shfl_xor_sync(0xffffffffu, odd ? h0 : l0, 4);
-    const uint32_t r1 = __shfl_xor_sync(0xffffffffu, odd ? h1 : l1, 4);
-    o.lo0 = odd ? r0 : h0;
-    o.lo1 = odd ? r1 : h1;
-    o.hi0 = odd ? l0 : r0;
-    o.hi1 = odd ? l1 : r1;
-    // C column pair of lane t = sub-blocks 2t (low nibbles of pair t) and 2t + 1: their scales sit in quads 2t, 2t + 1
-    o.s0 = __shfl_sync(0xffffffffu, s, 8 * t);
-    o.x0 = __shfl_sync(0xffffffffu, sum, 8 * t);
-    o.s1 = __shfl_sync(0xffffffffu, s, 8 * t + 4);
-    o.x1 = __shfl_sync(0xffffffffu, sum, 8 * t + 4);
+    const bool odd = (g & 1) != 0;   // an even g holds the pair's low sub-block and supplies the h plane; an odd g the high sub-block and the l plane
+    uint32_t h0[NBW], h1[NBW], l0[NBW], l1[NBW];
+#pragma unroll
+    for (int i = 0; i < NBW; ++i) {
+        if (i < nb) {
+            act_group_scale(__float_as_uint(amax[i]), inv[i], s[i]);
+            const int q0 = __float_as_int(fmaf(va[i].x, inv[i], 12582912.0f)), q1 = __float_as_int(fmaf(va[i].y, inv[i], 12582912.0f)),
+                      q2 = __float_as_int(fmaf(va[i].z, inv[i], 12582912.0f)), q3 = __float_as_int(fmaf(va[i].w, inv[i], 12582912.0f)),
+                      q4 = __float_as_int(fmaf(vb[i].x, inv[i], 12582912.0f)), q5 = __float_as_int(fmaf(vb[i].y, inv[i], 12582912.0f)),
+                      q6 = __float_as_int(fmaf(vb[i].z, inv[i], 12582912.0f)), q7 = __float_as_int(fmaf(vb[i].w, inv[i], 12582912.0f));
+            h0[i] = __byte_perm(__byte_perm((uint32_t) ((q0 + HB) >> 8), (uint32_t) ((q1 + HB) >> 8), 0x0040),
+                                __byte_perm((uint32_t) ((q2 + HB) >> 8), (uint32_t) ((q3 + HB) >> 8), 0x0040), 0x5410);
+            h1[i] = __byte_perm(__byte_perm((uint32_t) ((q4 + HB) >> 8), (uint32_t) ((q5 + HB) >> 8), 0x0040),
+                                __byte_perm((uint32_t) ((q6 + HB) >> 8), (uint32_t) ((q7 + HB) >> 8), 0x0040), 0x5410);
+            l0[i] = __byte_perm(__byte_perm((uint32_t) q0, (uint32_t) q1, 0x0040), __byte_perm((uint32_t) q2, (uint32_t) q3, 0x0040), 0x5410);
+            l1[i] = __byte_perm(__byte_perm((uint32_t) q4, (uint32_t) q5, 0x0040), __byte_perm((uint32_t) q6, (uint32_t) q7, 0x0040), 0x5410);
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < NBW; ++i) {
+        if (i < nb) {
+            const uint32_t r0 = __shfl_xor_sync(0xffffffffu, odd ? h0[i] : l0[i], 4);
+            const uint32_t r1 = __shfl_xor_sync(0xffffffffu, odd ? h1[i] : l1[i], 4);
+            o[i].lo0 = odd ? r0 : h0[i];
+            o[i].lo1 = odd ? r1 : h1[i];
+            o[i].hi0 = odd ? l0[i] : r0;
+            o[i].hi1 = odd ? l1[i] : r1;
+            // C column pair of lane t = sub-blocks 2t (low nibbles of pair t) and 2t + 1: their scales sit in quads 2t, 2t + 1
+            o[i].s0 = __shfl_sync(0xffffffffu, s[i], 8 * t);
+            o[i].x0 = __shfl_sync(0xffffffffu, sum[i], 8 * t);
+            o[i].s1 = __shfl_sync(0xffffffffu, s[i], 8 * t + 4);
+            o[i].x1 = __shfl_sync(0xffffffffu, sum[i], 8 * t + 4);
+        }
+    }
 }
 
 // one row's share of a block for lane t (see iq_row_term of sm100_matvec_q4k_imma.cu)
@@ -175,28 +182,26 @@ __device__ __forceinline__ float rg_row_term(uint32_t dd, uint32_t f0, uint32_t 
     const uint32_t f = __funnelshift_r(f0, f1, shift);
     const int sc0 = (int) (f & 63u), m0 = (int) ((f >> 6) & 63u), sc1 = (int) ((f >> 12) & 63u), m1 = (int) ((f >> 18) & 63u);
     const int v0 = clo_h * 256 + clo_l;          // exact: |v0| < 2^24
-    const int v1 = (chi_h * 256 + chi_l) >> 4;   // exact: every term carries the factor 16 of the high nibble
+    const int v1 = (chi_h * 256 + chi_l) >> 4;   // exact: every term carries the factor 16 of the high nibble (kept out of v1 * sc1: |.| < 2^31)
     const float dot = fmaf((float) (v1 * sc1), b.s1, (float) (v0 * sc0) * b.s0);
     const float mins = fmaf((float) m1, b.x1, (float) m0 * b.x0);
     return fmaf(df.x, dot, -df.y * mins);
 }
 
 // Shared memory of one CTA:
-//   bars  [warp][RG_SLOTS] mbarrier
 //   red   [RG_WINDOW][warp][16 rows] float     partial sums of the warps, one window of rounds
-//   hdr   [warp][RG_SLOTS][16 rows] uint4      block headers of the units in flight (128-byte aligned)
-//   ring  [warp][RG_SLOTS][4 tiles][512 B]     weight tiles of the units in flight
+//   hdr   [warp][slots][16 rows] uint4         block headers of the units in flight
+//   ring  [warp][slots][4 tiles][512 B]        weight tiles of the units in flight (each lane's 16 bytes are its own)
 //   row   [K] float                            PRO == 2 only: the residual row before normalisation
 // NBW: 256-weight blocks of K per warp (compile time: their activations live in registers).
 // PRO: 0 x is given; 1 x = swiglu(pa, pb); 2 s = pa (+ pb), x = rms_norm(s) * pw (s, x written out by CTA 0 when asked).
 template <int NBW, int PRO>
 __global__ void __launch_bounds__(RG_THREADS, 2) matvec_q4k_ring(RingArgs p) {
     extern __shared__ __align__(128) uint8_t smem[];
-    uint64_t * bars = reinterpret_cast<uint64_t *>(smem);
-    float * red = reinterpret_cast<float *>(smem + RG_WARPS * RG_SLOTS * 8);
-    uint8_t * hdr = smem + RG_WARPS * RG_SLOTS * 8 + RG_WINDOW * RG_WARPS * 16 * 4;
-    uint8_t * ring = hdr + RG_WARPS * RG_SLOTS * RG_HDR_BYTES;
-    float * row = reinterpret_cast<float *>(ring + RG_WARPS * RG_SLOTS * RG_TILE_BYTES);
+    float * red = reinterpret_cast<float *>(smem);
+    uint8_t * hdr = smem + RG_WINDOW * RG_WARPS * 16 * 4;
+    uint8_t * ring = hdr + RG_WARPS * p.slots * RG_HDR_BYTES;
+    float * row = reinterpret_cast<float *>(ring + RG_WARPS * p.slots * RG_TILE_BYTES);
 
     // the successor on the stream may become resident (and prefetch) from now on; it still waits for this grid's
     // completion before it reads anything this grid writes
@@ -212,39 +217,41 @@ __global__ void __launch_bounds__(RG_THREADS, 2) matvec_q4k_ring(RingArgs p) {
     const int rounds = tile0 < p.n_tiles ? (p.n_tiles - tile0 + tile_step - 1) / tile_step : 0;   // row tiles of this warp's group
     const int units = rounds * nb;
 
-    const uint32_t bar0 = rg_smem(bars + wid * RG_SLOTS);
-    const uint32_t hdr0 = rg_smem(hdr) + (uint32_t) wid * RG_SLOTS * RG_HDR_BYTES;
-    const uint32_t ring0 = rg_smem(ring) + (uint32_t) wid * RG_SLOTS * RG_TILE_BYTES;
-    if (lane == 0) {
-#pragma unroll
-        for (int s = 0; s < RG_SLOTS; ++s) rg_bar_init(bar0 + 8 * s, 33);   // lane 0's expect_tx + 32 header-copy arrivals
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    }
-    __syncwarp();
+    const uint32_t hdr0 = rg_smem(hdr) + (uint32_t) (wid * p.slots) * RG_HDR_BYTES;
+    const uint32_t ring0 = rg_smem(ring) + (uint32_t) (wid * p.slots) * RG_TILE_BYTES + (uint32_t) lane * 16u;   // this lane's 16 bytes of tile 0, slot 0
 
-    // unit u of this warp = (round u / nb, block kw + wpt * (u % nb)); requests it into slot u % RG_SLOTS
+    // Unit u of this warp = (round u / nb, block kw + wpt * (u % nb)), kept in slot u % slots.  The request cursor
+    // walks the units in that order; the addresses of a round (tensor, row tile) are worked out once per round.
     const uint32_t tile_bytes_per_rt = (uint32_t) p.blocks * RG_TILE_BYTES;
     const uint32_t hdr_bytes_per_rt = (uint32_t) p.blocks * 256u;
-    auto request = [&](int u) {
-        const int r = u / nb, i = u - r * nb;
-        const int blk = kw + p.wpt * i;
+    const uint32_t blk_tile_step = (uint32_t) p.wpt * RG_TILE_BYTES, blk_hdr_step = (uint32_t) p.wpt * 16u;
+    int issued = 0, rq_r = 0, rq_i = 0;
+    uint32_t rq_slot = 0;
+    const uint8_t * rq_tiles = nullptr;   // tiles of (round rq_r, this warp's first block)
+    const uint8_t * rq_hdrs = nullptr;    // header of (round rq_r, row lane & 15, this warp's first block)
+    auto rq_round = [&]() {
         int ti, rt;
-        rg_locate(p, tile0 + r * tile_step, ti, rt);
+        rg_locate(p, tile0 + rq_r * tile_step, ti, rt);
         const uint8_t * wbase = p.w[ti];
-        const int s = u % RG_SLOTS;
-        const uint32_t bar = bar0 + 8 * s;
-        if (lane == 0) {
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // earlier reads of the slot precede the copy's writes
-            rg_bar_expect_tx(bar, RG_TILE_BYTES);
-            rg_bulk_g2s(ring0 + s * RG_TILE_BYTES, wbase + (uint64_t) rt * tile_bytes_per_rt + (uint32_t) blk * RG_TILE_BYTES, RG_TILE_BYTES, bar);
-        }
-        if (lane < 16)
-            rg_cp_async16(hdr0 + s * RG_HDR_BYTES + lane * 16,
-                          wbase + p.h_off[ti] + (uint64_t) rt * hdr_bytes_per_rt + (uint32_t) (lane * p.blocks + blk) * 16u);
-        rg_cp_async_arrive(bar);
+        rq_tiles = wbase + (uint64_t) rt * tile_bytes_per_rt + (uint32_t) kw * RG_TILE_BYTES;
+        rq_hdrs = wbase + p.h_off[ti] + (uint64_t) rt * hdr_bytes_per_rt + (uint32_t) ((lane & 15) * p.blocks + kw) * 16u;
     };
-    int issued = 0;
-    for (; issued < RG_SLOTS && issued < units; ++issued) request(issued);
+    auto request = [&]() {   // copies the unit under the cursor into the next slot (one copy group per unit) and advances the cursor
+        const uint32_t s = rq_slot;
+        rq_slot = rq_slot + 1 == (uint32_t) p.slots ? 0u : rq_slot + 1;
+        const uint8_t * src = rq_tiles + (uint32_t) rq_i * blk_tile_step + (uint32_t) lane * 16u;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) rg_cp_async16(ring0 + s * RG_TILE_BYTES + j * 512, src + j * 512);
+        if (lane < 16) rg_cp_async16(hdr0 + s * RG_HDR_BYTES + lane * 16, rq_hdrs + (uint32_t) rq_i * blk_hdr_step);
+        rg_cp_async_commit();
+        ++issued;
+        if (++rq_i == nb) {
+            rq_i = 0;
+            if (++rq_r < rounds) rq_round();
+        }
+    };
+    if (units > 0) rq_round();
+    while (issued < p.slots && issued < units) request();
 
     pdl_wait();   // everything below may depend on the predecessor's output
 
@@ -275,23 +282,25 @@ __global__ void __launch_bounds__(RG_THREADS, 2) matvec_q4k_ring(RingArgs p) {
         for (int w = 0; w < RG_WARPS; ++w) tot += dred[w];
         const float scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn((float) (tot / (double) (items * 4)), p.eps)));
         __syncthreads();   // dred is part of `red`
+        float4 va[NBW], vb[NBW];
 #pragma unroll
         for (int i = 0; i < NBW; ++i) {
             if (i < nb) {
                 const int e0 = (kw + p.wpt * i) * 256 + g * 32 + 4 * t;   // element index of the lane's first float4
-                float4 va = *reinterpret_cast<const float4 *>(row + e0), vb = *reinterpret_cast<const float4 *>(row + e0 + 16);
+                va[i] = *reinterpret_cast<const float4 *>(row + e0);
+                vb[i] = *reinterpret_cast<const float4 *>(row + e0 + 16);
                 const float4 wa = __ldg(reinterpret_cast<const float4 *>(p.pw + e0)), wb = __ldg(reinterpret_cast<const float4 *>(p.pw + e0 + 16));
-                va = make_float4(__fmul_rn(__fmul_rn(va.x, scale), wa.x), __fmul_rn(__fmul_rn(va.y, scale), wa.y),
-                                 __fmul_rn(__fmul_rn(va.z, scale), wa.z), __fmul_rn(__fmul_rn(va.w, scale), wa.w));
-                vb = make_float4(__fmul_rn(__fmul_rn(vb.x, scale), wb.x), __fmul_rn(__fmul_rn(vb.y, scale), wb.y),
-                                 __fmul_rn(__fmul_rn(vb.z, scale), wb.z), __fmul_rn(__fmul_rn(vb.w, scale), wb.w));
+                va[i] = make_float4(__fmul_rn(__fmul_rn(va[i].x, scale), wa.x), __fmul_rn(__fmul_rn(va[i].y, scale), wa.y),
+                                    __fmul_rn(__fmul_rn(va[i].z, scale), wa.z), __fmul_rn(__fmul_rn(va[i].w, scale), wa.w));
+                vb[i] = make_float4(__fmul_rn(__fmul_rn(vb[i].x, scale), wb.x), __fmul_rn(__fmul_rn(vb[i].y, scale), wb.y),
+                                    __fmul_rn(__fmul_rn(vb[i].z, scale), wb.z), __fmul_rn(__fmul_rn(vb[i].w, scale), wb.w));
                 if (p.x_out != nullptr && blockIdx.x == 0 && group == 0) {
-                    *reinterpret_cast<float4 *>(p.x_out + e0) = va;
-                    *reinterpret_cast<float4 *>(p.x_out + e0 + 16) = vb;
+                    *reinterpret_cast<float4 *>(p.x_out + e0) = va[i];
+                    *reinterpret_cast<float4 *>(p.x_out + e0 + 16) = vb[i];
                 }
-                rg_quantize(va, vb, lane, bx[i]);
             }
         }
+        rg_quantize<NBW>(va, vb, nb, lane, bx);
     } else {
         float4 va[NBW], vb[NBW], ga[NBW], gb[NBW];
 #pragma unroll
@@ -324,35 +333,36 @@ __global__ void __launch_bounds__(RG_THREADS, 2) matvec_q4k_ring(RingArgs p) {
                                         __fmul_rn(__fdiv_rn(vb[i].z, __fadd_rn(1.0f, expf(-vb[i].z))), gb[i].z),
                                         __fmul_rn(__fdiv_rn(vb[i].w, __fadd_rn(1.0f, expf(-vb[i].w))), gb[i].w));
                 }
-                rg_quantize(va[i], vb[i], lane, bx[i]);
             }
         }
+        rg_quantize<NBW>(va, vb, nb, lane, bx);
     }
 
     // ---- main loop: this warp's units, round by round ----
     const int live_pair = g >> 1;
     // the 24-bit scale field of lane t starts at byte 4 + 3 t of a 16-byte header
     const uint32_t fld_off = (uint32_t) (4 + 3 * t) & ~3u, fld_shift = ((uint32_t) (4 + 3 * t) & 3u) * 8u;
-    bool alive = true;
     int u = 0;
+    uint32_t cs = 0;   // slot of unit u
     // rounds of group 0, the most any group of this CTA has: the window loop and its barriers are CTA-uniform
     const int cta_rounds = (p.n_tiles - (int) blockIdx.x * p.groups + tile_step - 1) / tile_step;
     for (int base = 0; base < cta_rounds; base += RG_WINDOW) {
         const int wend = base + RG_WINDOW < rounds ? base + RG_WINDOW : rounds;
-        for (int r = base; r < wend && alive; ++r) {
+        for (int r = base; r < wend; ++r) {
             float acc0 = 0.f, acc1 = 0.f;   // rows g and g + 8 of the tile
 #pragma unroll
             for (int i = 0; i < NBW; ++i) {
-                if (i < nb && alive) {
-                    const int s = u % RG_SLOTS;
-                    const uint32_t bar = bar0 + 8 * s, parity = (uint32_t) (u / RG_SLOTS) & 1u;
-                    bool ok = rg_bar_try_wait(bar, parity);
-                    for (uint32_t n = 0; !ok && n < RG_WAIT_LIMIT; ++n) ok = rg_bar_try_wait(bar, parity);
-                    if (!__all_sync(0xffffffffu, ok)) {   // a copy that never lands must not hang the GPU
-                        if (lane == 0) atomicExch(&g_ring_fault, 1);
-                        alive = false;
-                    } else {
-                        const uint32_t tiles_lane = ring0 + s * RG_TILE_BYTES + lane * 16;
+                if (i < nb) {
+                    const uint32_t s = cs;
+                    cs = cs + 1 == (uint32_t) p.slots ? 0u : cs + 1;
+                    // unit u's copy group is the oldest one outstanding; those of the units requested after it may still be in flight
+                    const int younger = issued - u - 1;
+                    if (younger >= 2) rg_cp_async_wait<2>();
+                    else if (younger == 1) rg_cp_async_wait<1>();
+                    else rg_cp_async_wait<0>();
+                    __syncwarp();   // the headers were copied by lanes 0..15 for the whole warp
+                    {
+                        const uint32_t tiles_lane = ring0 + s * RG_TILE_BYTES;
                         int clo[4], chi[4];
 #pragma unroll
                         for (int j = 0; j < 4; ++j) {
@@ -374,7 +384,7 @@ __global__ void __launch_bounds__(RG_THREADS, 2) matvec_q4k_ring(RingArgs p) {
                         acc1 += rg_row_term(db, fb0, fb1, fld_shift, clo[2], clo[3], chi[2], chi[3], bx[i]);
                         // the slot's contents sit in registers that the MMAs have read: refill it
                         __syncwarp();
-                        if (issued < units) { request(issued); ++issued; }
+                        if (issued < units) request();
                         ++u;
                     }
                 }
@@ -406,30 +416,19 @@ __global__ void __launch_bounds__(RG_THREADS, 2) matvec_q4k_ring(RingArgs p) {
                 p.y[ti][(int64_t) lrt * 16 + rw] = v;
             }
         }
-        __syncthreads();
-    }
-
-    // copies that were requested but never consumed (only after a fault) must land before the CTA's memory goes away
-    if (!alive) {
-        for (int q = u; q < issued; ++q) {
-            const uint32_t bar = bar0 + 8 * (q % RG_SLOTS), parity = (uint32_t) (q / RG_SLOTS) & 1u;
-            for (uint32_t n = 0; n < RG_WAIT_LIMIT && !rg_bar_try_wait(bar, parity); ++n) {}
-        }
+        if (base + RG_WINDOW < cta_rounds) __syncthreads();   // the next window reuses `red`
     }
 }
 
-size_t ring_smem_bytes(int64_t k, int pro) {
-    return (size_t) RG_WARPS * RG_SLOTS * 8 + (size_t) RG_WINDOW * RG_WARPS * 16 * 4 + (size_t) RG_WARPS * RG_SLOTS * (RG_HDR_BYTES + RG_TILE_BYTES) +
-           (pro == 2 ? (size_t) k * 4 : 0);
+size_t ring_smem_bytes(int64_t k, int pro, int slots) {
+    return (size_t) RG_WINDOW * RG_WARPS * 16 * 4 + (size_t) RG_WARPS * slots * (RG_HDR_BYTES + RG_TILE_BYTES) + (pro == 2 ? (size_t) k * 4 : 0);
 }
-
-std::atomic<bool> g_ring_launched[MAX_DEVICES];
 
 template <int NBW>
 int launch_ring(cudaStream_t s, const RingArgs & a, int pro, size_t smem, int grid) {
 #define SM100_RING_CASE(P)                                                                                                             \
     case P:                                                                                                                            \
-        SM100_CUDA(cudaFuncSetAttribute(matvec_q4k_ring<NBW, P>, cudaFuncAttributeMaxDynamicSharedMemorySize, 112 * 1024));          \
+        SM100_CUDA(cudaFuncSetAttribute(matvec_q4k_ring<NBW, P>, cudaFuncAttributeMaxDynamicSharedMemorySize, 113 * 1024));          \
         return launch(matvec_q4k_ring<NBW, P>, dim3((unsigned) grid), dim3(RG_THREADS), smem, s, a);
     switch (pro) {
         SM100_RING_CASE(0)
@@ -441,16 +440,6 @@ int launch_ring(cudaStream_t s, const RingArgs & a, int pro, size_t smem, int gr
 }
 
 }  // namespace
-
-int ring_poll_fault() {
-    if (!g_ring_launched[current_device()].exchange(false, std::memory_order_relaxed)) return ST_OK;
-    int v = 0;
-    SM100_CUDA(cudaMemcpyFromSymbol(&v, g_ring_fault, sizeof(v)));
-    if (v == 0) return ST_OK;
-    const int zero = 0;
-    SM100_CUDA(cudaMemcpyToSymbol(g_ring_fault, &zero, sizeof(zero)));
-    return fail(ST_BACKEND, "mul_mat: the Q4_K ring matvec gave up waiting for a weight copy; its output is incomplete");
-}
 
 // Q4_K packed matvec, one activation column, over the full 16-row tiles of up to three tensors that share the
 // activations; *handled = false when the shapes are left to the caller's other kernels.
@@ -507,8 +496,9 @@ int matvec_q4k_ring_multi(cudaStream_t s, int count, const void * const * ws, co
     int64_t grid = sm_count();
     const int64_t rounds = (tiles + a.groups - 1) / a.groups;
     if (grid > rounds) grid = rounds;
-    const size_t smem = ring_smem_bytes(k, mode);
-    g_ring_launched[current_device()].store(true, std::memory_order_relaxed);
+    // two CTAs (this launch's and its successor's) have to fit one SM: 228 KB less 1 KB per CTA
+    a.slots = ring_smem_bytes(k, mode, RG_MAX_SLOTS) <= (size_t) 113 * 1024 ? RG_MAX_SLOTS : 2;
+    const size_t smem = ring_smem_bytes(k, mode, a.slots);
     int st;
     if (nbw == 1) st = launch_ring<1>(s, a, mode, smem, (int) grid);
     else if (nbw == 2) st = launch_ring<2>(s, a, mode, smem, (int) grid);

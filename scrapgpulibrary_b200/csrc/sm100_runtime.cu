@@ -94,7 +94,6 @@ int device_scratch(int slot, size_t bytes, void ** out) {
 
 int gemm_poll_fault();
 int iq_poll_fault();
-int ring_poll_fault();
 
 // Waits for the stream, then reads the fault words of the kernels with bounded waits on the STREAM's device (they are
 // per-device variables; the current device may be another one in a process that drives several GPUs).
@@ -110,7 +109,6 @@ static int sync_and_poll(cudaStream_t st) {
     if (dev != cur) SM100_CUDA(cudaSetDevice(dev));
     int r = gemm_poll_fault();
     if (r == ST_OK) r = iq_poll_fault();
-    if (r == ST_OK) r = ring_poll_fault();
     if (dev != cur) (void) cudaSetDevice(cur);
     return r;
 }
@@ -253,6 +251,24 @@ int sm100_memcpy_peer(sm100_stream_t dst_stream, int dst_device, void * dst, sm1
     if (e == cudaSuccess) e = cudaMemcpyPeerAsync(dst, dst_device, src, src_device, n, (cudaStream_t) dst_stream);
     cudaEventDestroy(ready);
     if (e != cudaSuccess) return cuda_fail(e, "sm100_memcpy_peer");
+    return ST_OK;
+}
+
+int sm100_peer_access(int device, int peer) {
+    if (device == peer) return ST_OK;
+    int can = 0;
+    SM100_CUDA(cudaDeviceCanAccessPeer(&can, device, peer));
+    if (!can) return fail(ST_UNSUPPORTED, "device %d cannot map the memory of device %d", device, peer);
+    int cur = 0;
+    SM100_CUDA(cudaGetDevice(&cur));
+    SM100_CUDA(cudaSetDevice(device));
+    const cudaError_t e = cudaDeviceEnablePeerAccess(peer, 0);
+    (void) cudaSetDevice(cur);
+    if (e == cudaErrorPeerAccessAlreadyEnabled) {
+        (void) cudaGetLastError();
+        return ST_OK;
+    }
+    if (e != cudaSuccess) return cuda_fail(e, "cudaDeviceEnablePeerAccess");
     return ST_OK;
 }
 
