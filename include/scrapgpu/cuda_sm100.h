@@ -86,6 +86,16 @@ SCRAPGPU_API scrapgpu_status scrapgpu_cuda_sm100_upload_view(scrapgpu_stream_t *
 /* Kernels launched by this process through the backend so far (per-process counter for profiling). */
 SCRAPGPU_API uint64_t scrapgpu_cuda_sm100_launch_count(void);
 
+/* The per-op-key timing table, the counterpart of the OpenCL backend's GGML_CL11_PROFILE table
+ * (src/backends/opencl11/executor.h:41-112; keys as adapters/ggml/ggml-cl11.cpp:1033-1049).  With the environment
+ * variable SCRAPGPU_SM100_PROFILE=1 every op executed on a stream (directly or as a plan step; plans then run step by
+ * step instead of replaying a graph, and every launch is fully serialized) is bracketed by two events; stream_sync
+ * adds the finished pairs to the stream's table, stream_free prints it to stderr.  This call writes the table collected
+ * so far ("<key> <calls> <ms> <us/call> <share> [weights GB/s]", slowest first) into out (NUL-terminated, truncated to
+ * capacity) and returns the size the whole text needs, 0 when the table is off or empty.
+ * SCRAPGPU_SM100_PROFILE_SHAPES=1 adds the shape of src0 to the keys. */
+SCRAPGPU_API size_t scrapgpu_cuda_sm100_profile_report(scrapgpu_stream_t * stream, char * out, size_t capacity);
+
 #ifdef __cplusplus
 }
 #endif

@@ -116,6 +116,15 @@ SM100_API uint64_t sm100_launch_count(void);
 /* 1: launch kernels with programmatic dependent launch so that a kernel's weight prefetch overlaps
  * the tail of its predecessor on the same stream (default 1) */
 SM100_API int sm100_set_pdl(int enabled);
+/* What a kernel of this library may touch before its dependency wait, i.e. while kernels enqueued earlier on the
+ * stream are still running: the WEIGHTS of the matvec / mul_mat / gemm entries (w, ws[i]) and nothing else.  Some
+ * kernels release their successor before their own dependency wait, so "earlier" can reach back over several launches, up
+ * to the last point of full serialization on the stream (a copy, an event wait, a graph launch, a synchronisation, a
+ * kernel launched under sm100_launch_serialized).  A caller whose weight operand was produced by a kernel since that
+ * point (a K cache used as the left operand, a weight converted on the device) brackets the call with
+ * sm100_launch_serialized(1) ... (0): launches of the calling thread in between start only after everything enqueued
+ * before them has completed.  sm100_pack_device needs no bracket: its kernel holds its successor back itself. */
+SM100_API int sm100_launch_serialized(int on);
 
 /* ---- weight packing: replaces the R32 repack of the OpenCL backend
  *      (src/backends/opencl11/r32.h:35-90, r32.cpp:19-86; geometry src/tensor/tensor.cpp:5-19).
@@ -248,15 +257,15 @@ SM100_API int sm100_attention(sm100_stream_t s, const float * q, const float * k
                               int64_t mask_heads, float * out, int64_t d, int64_t dv, int64_t nq, int64_t nk, int64_t hq,
                               int64_t hkv, int causal, int64_t offset, const int32_t * positions, float scale);
 
-/* sm100_attention over a KV cache, with one promise from the caller that lets the key/value rows be requested while the
- * launch that precedes this call in the stream is still finishing: of each query's visible keys only the last
- * fresh_keys (>= 0) may be written by that preceding launch; every earlier K/V row, and positions[0], were written
- * by work that completed before the preceding launch began to run.  (Every kernel of this library, and any kernel
- * launched without programmatic dependent launch, begins only after its own predecessors have completed, so "the
- * launch before" is the only one that can still be running.)  In a decode step the promise holds with
- * fresh_keys = 1: the launch before the attention stores the new token's K and V (SET_ROWS / SET_ROWS_PAIR,
- * include/scrapgpu/op.h:43-47), all older rows date from earlier tokens.  Same values as sm100_attention; with the
- * promise broken the result is undefined.  This entry has no counterpart in the reference. */
+/* sm100_attention over a KV cache, with one promise from the caller that lets the key/value rows be requested while
+ * launches that precede this call in the stream are still running: of each query's visible keys only the last
+ * fresh_keys (>= 0) may have been written since the stream's last point of full serialization (a copy, an event wait,
+ * a graph launch, a synchronisation, a kernel launched without programmatic dependent launch: see
+ * sm100_launch_serialized); every earlier K/V row, and positions[0], were written before that point.  In a decode
+ * step the promise holds with fresh_keys = 1: the step stores the new token's K and V (SET_ROWS / SET_ROWS_PAIR,
+ * include/scrapgpu/op.h:43-47) and all older rows date from earlier steps, which a graph launch or the host's read
+ * of the token separates from this one.  Same values as sm100_attention; with the promise broken the result is
+ * undefined.  This entry has no counterpart in the reference. */
 SM100_API int sm100_attention_kvcache(sm100_stream_t s, const float * q, const float * k, const float * v, const float * mask,
                                       int64_t mask_heads, float * out, int64_t d, int64_t dv, int64_t nq, int64_t nk,
                                       int64_t hq, int64_t hkv, int causal, int64_t offset, const int32_t * positions,

@@ -25,6 +25,7 @@
 #include <cstdlib>
 #include <cstring>
 #include <limits>
+#include <atomic>
 #include <map>
 #include <memory>
 #include <mutex>
@@ -63,17 +64,31 @@ struct Device {
     std::map<std::tuple<int, uint32_t, uint32_t, uint32_t>, std::pair<void *, int32_t>> rope_tables;
 };
 
+struct Stream;
+
 struct Buffer {
     scrapgpu_object_header hdr;
     Device * dev = nullptr;
     void * ptr = nullptr;
     size_t size = 0;
+    // the last kernel that wrote into the buffer: the stream it ran on and that stream's launch number (see fresh())
+    std::atomic<const Stream *> writer{nullptr};
+    std::atomic<uint64_t> written{0};
 };
 
 struct Stream {
     scrapgpu_object_header hdr;
     Device * dev = nullptr;
     sm100_stream_t cuda = nullptr;
+    uint64_t epoch = 0;     // ops enqueued so far
+    uint64_t settled = 0;   // ops up to this number have completed before anything enqueued from now on starts
+    // per-op-key timing table (SCRAPGPU_SM100_PROFILE=1), the counterpart of the OpenCL backend's GGML_CL11_PROFILE table
+    // (src/backends/opencl11/executor.h:41-112): a pair of events around every op, read back at stream_sync
+    struct ProfStat { std::string name; double ms = 0; size_t count = 0; double bytes = 0; };
+    struct ProfPending { sm100_event_t start, stop; int key; };
+    std::vector<ProfStat> prof_stats;
+    std::vector<ProfPending> prof_pending;
+    std::vector<sm100_event_t> prof_spare;
     scrapgpu_status sticky = SCRAPGPU_STATUS_OK;  // failure of enqueued work, reported at the next sync
     std::string sticky_message;
 };
@@ -737,7 +752,181 @@ scrapgpu_status run_mul_mat(Stream * s, const Ref & w, const Ref & x, const Ref 
     return SCRAPGPU_STATUS_OK;
 }
 
+// ---- profile table ----
+bool profiling() {
+    static const bool on = [] { const char * e = std::getenv("SCRAPGPU_SM100_PROFILE"); return e != nullptr && std::atoi(e) != 0; }();
+    return on;
+}
+
+const char * dtype_name(int dt) {
+    switch (dt) {
+        case SCRAPGPU_DTYPE_F32: return "f32";
+        case SCRAPGPU_DTYPE_F16: return "f16";
+        case SCRAPGPU_DTYPE_I32: return "i32";
+        case SCRAPGPU_DTYPE_I64: return "i64";
+        case SCRAPGPU_DTYPE_I16: return "i16";
+        case SCRAPGPU_DTYPE_BF16: return "bf16";
+        case SCRAPGPU_DTYPE_Q4_0: return "q4_0";
+        case SCRAPGPU_DTYPE_Q8_0: return "q8_0";
+        case SCRAPGPU_DTYPE_Q4_K: return "q4_K";
+        case SCRAPGPU_DTYPE_Q6_K: return "q6_K";
+        default: return "?";
+    }
+}
+
+const char * op_name(int op);
+
+// the key of an op in the table: the op, for MUL_MAT the weight type, matvec or matrix form and the column count, for
+// the row and copy ops the two types (the keys of adapters/ggml/ggml-cl11.cpp:1033-1049)
+std::string prof_key_name(const scrapgpu_op_desc * desc) {
+    std::string key = op_name(desc->op);
+    if (desc->input_count == 0 || desc->inputs == nullptr) return key;
+    const scrapgpu_tensor_desc a = load_desc(desc->inputs[0]);
+    if (desc->op == SCRAPGPU_OP_MUL_MAT && desc->input_count >= 2) {
+        const int64_t cols = ne(load_desc(desc->inputs[1]), 1);
+        key += std::string(" ") + dtype_name(a.dtype) + (a.layout == SCRAPGPU_LAYOUT_R32 ? " packed" : "") + (cols <= 8 ? " mv" : " mm") + " n=" + std::to_string(cols);
+    } else if (desc->op == SCRAPGPU_OP_MUL_MAT_MULTI) {
+        key += std::string(" ") + dtype_name(a.dtype) + " x" + std::to_string(desc->output_count);
+    } else if ((desc->op == SCRAPGPU_OP_GET_ROWS || desc->op == SCRAPGPU_OP_CPY || desc->op == SCRAPGPU_OP_SET_ROWS) && desc->output_count >= 1) {
+        key += std::string(" ") + dtype_name(a.dtype) + "->" + dtype_name(load_desc(desc->outputs[0]).dtype);
+    }
+    static const bool shapes = std::getenv("SCRAPGPU_SM100_PROFILE_SHAPES") != nullptr;
+    if (shapes) {
+        char buf[96];
+        std::snprintf(buf, sizeof(buf), " src0[%lld,%lld,%lld,%lld]", (long long) ne(a, 0), (long long) ne(a, 1), (long long) ne(a, 2), (long long) ne(a, 3));
+        key += buf;
+    }
+    return key;
+}
+
+double weight_bytes(const scrapgpu_tensor_desc & w) {
+    return (double) (ne(w, 0) / (int64_t) block_size(w.dtype)) * (double) type_size(w.dtype) * (double) (ne(w, 1) * ne(w, 2) * ne(w, 3));
+}
+
+// Brackets the launches of one op with two events while the table is on; the launches inside are fully serialized so
+// that the pair times this op alone (with programmatic dependent launch neighbouring kernels overlap).
+struct ProfScope {
+    Stream * s = nullptr;
+    sm100_event_t start = nullptr;
+    int key = -1;
+    ProfScope(Stream * stream, const std::string & name, double bytes) {
+        if (!profiling()) return;
+        s = stream;
+        for (size_t i = 0; i < s->prof_stats.size() && key < 0; ++i) if (s->prof_stats[i].name == name) key = (int) i;
+        if (key < 0) {
+            s->prof_stats.emplace_back();
+            s->prof_stats.back().name = name;
+            key = (int) s->prof_stats.size() - 1;
+        }
+        s->prof_stats[(size_t) key].count++;
+        s->prof_stats[(size_t) key].bytes += bytes;
+        start = event();
+        if (start != nullptr) sm100_event_record(start, s->cuda);
+        sm100_launch_serialized(1);
+    }
+    ~ProfScope() {
+        if (s == nullptr) return;
+        sm100_launch_serialized(0);
+        sm100_event_t stop = start != nullptr ? event() : nullptr;
+        if (stop == nullptr) {
+            if (start != nullptr) s->prof_spare.push_back(start);
+            return;
+        }
+        sm100_event_record(stop, s->cuda);
+        s->prof_pending.push_back({start, stop, key});
+    }
+    sm100_event_t event() {
+        if (!s->prof_spare.empty()) {
+            sm100_event_t e = s->prof_spare.back();
+            s->prof_spare.pop_back();
+            return e;
+        }
+        sm100_event_t e = nullptr;
+        return sm100_event_create(&e) == 0 ? e : nullptr;
+    }
+};
+
+// after a successful stream synchronisation: the finished pairs go into the table
+void prof_collect(Stream * s) {
+    for (const Stream::ProfPending & p : s->prof_pending) {
+        float ms = 0.0f;
+        if (sm100_event_elapsed_ms(p.start, p.stop, &ms) == 0 && p.key >= 0 && (size_t) p.key < s->prof_stats.size()) s->prof_stats[(size_t) p.key].ms += ms;
+        s->prof_spare.push_back(p.start);
+        s->prof_spare.push_back(p.stop);
+    }
+    s->prof_pending.clear();
+}
+
+// the table as text, slowest key first (the layout of cl11_prof_print, src/backends/opencl11/executor.h:87-106)
+std::string prof_report(Stream * s) {
+    std::vector<const Stream::ProfStat *> v;
+    double total = 0;
+    for (const Stream::ProfStat & st : s->prof_stats) {
+        v.push_back(&st);
+        total += st.ms;
+    }
+    std::sort(v.begin(), v.end(), [](const Stream::ProfStat * a, const Stream::ProfStat * b) { return a->ms > b->ms; });
+    char line[256];
+    std::snprintf(line, sizeof(line), "cuda_sm100 profile of %s: total kernel time %.3f ms\n", s->dev->name.c_str(), total);
+    std::string out = line;
+    for (const Stream::ProfStat * st : v) {
+        char gbs[64] = "";
+        if (st->bytes > 0 && st->ms > 0) std::snprintf(gbs, sizeof(gbs), "  weights %.2f GB/s", st->bytes / (st->ms * 1e6));
+        std::snprintf(line, sizeof(line), "  %-44s %6zu calls %10.3f ms %8.1f us/call %5.1f%%%s\n", st->name.c_str(), st->count, st->ms,
+                      st->ms * 1e3 / (double) std::max<size_t>(1, st->count), 100.0 * st->ms / std::max(1e-9, total), gbs);
+        out += line;
+    }
+    return out;
+}
+
+// The matvec and GEMM kernels request their weights before they wait for the kernels ahead of them on the stream
+// (sm100_launch_serialized in scrapgpu_sm100.h).  That is sound for weights that sit in memory since an upload, not for
+// a left operand some kernel has written since the stream last settled (the K cache of the core's attention
+// composition, a CPY into a weight): such a MUL_MAT is launched fully serialized.
+bool fresh(const Stream * s, const scrapgpu_tensor_desc & raw) {
+    const Buffer * b = as_buffer(load_desc(raw).buffer);
+    return b != nullptr && b->writer.load(std::memory_order_relaxed) == s && b->written.load(std::memory_order_relaxed) > s->settled;
+}
+void wrote(Stream * s, const scrapgpu_tensor_desc & raw) {
+    Buffer * b = as_buffer(load_desc(raw).buffer);
+    if (b == nullptr) return;
+    b->writer.store(s, std::memory_order_relaxed);
+    b->written.store(s->epoch, std::memory_order_relaxed);
+}
+struct Serialized {
+    bool on;
+    explicit Serialized(bool o) : on(o) { if (on) sm100_launch_serialized(1); }
+    ~Serialized() { if (on) sm100_launch_serialized(0); }
+};
+
+scrapgpu_status execute_op(Stream * s, const scrapgpu_op_desc * desc);
+
 scrapgpu_status execute(Stream * s, const scrapgpu_op_desc * desc) {
+    bool serial = false;
+    if (desc != nullptr && desc->inputs != nullptr) {
+        const size_t weights = desc->op == SCRAPGPU_OP_MUL_MAT || desc->op == SCRAPGPU_OP_CONT_MUL_MAT ? 1
+                               : desc->op == SCRAPGPU_OP_MUL_MAT_MULTI ? desc->output_count : 0;
+        for (size_t i = 0; i < weights && i < desc->input_count; ++i) serial = serial || fresh(s, desc->inputs[i]);
+    }
+    scrapgpu_status st;
+    if (profiling() && desc != nullptr) {
+        const bool mm = (desc->op == SCRAPGPU_OP_MUL_MAT || desc->op == SCRAPGPU_OP_MUL_MAT_MULTI) && desc->inputs != nullptr;
+        double bytes = 0;
+        for (size_t i = 0; mm && i < (desc->op == SCRAPGPU_OP_MUL_MAT ? 1 : desc->output_count) && i < desc->input_count; ++i) bytes += weight_bytes(load_desc(desc->inputs[i]));
+        ProfScope prof(s, prof_key_name(desc), bytes);
+        st = execute_op(s, desc);
+    } else {
+        Serialized scope(serial);
+        st = execute_op(s, desc);
+    }
+    if (st == SCRAPGPU_STATUS_OK && desc->outputs != nullptr) {
+        ++s->epoch;
+        for (size_t i = 0; i < desc->output_count; ++i) wrote(s, desc->outputs[i]);
+    }
+    return st;
+}
+
+scrapgpu_status execute_op(Stream * s, const scrapgpu_op_desc * desc) {
     const char * why = nullptr;
     scrapgpu_status st = supports(desc, &why);
     if (st != SCRAPGPU_STATUS_OK) return st;
@@ -1031,6 +1220,7 @@ scrapgpu_status io_check(scrapgpu_stream_t * stream, scrapgpu_buffer_t * buffer,
     if (io.s == nullptr || io.b == nullptr) return invalid("stream or buffer is not a cuda_sm100 object");
     if (io.b->dev != io.s->dev) return invalid("buffer and stream belong to different devices");
     if (size != 0 && (offset > (uint64_t) io.b->size || size > io.b->size - (size_t) offset)) return invalid(what);
+    io.s->settled = io.s->epoch;   // a copy or fill on the stream runs after all kernels before it and before all after it
     return from_sm100(sm100_set_device(io.s->dev->ordinal));
 }
 
@@ -1105,7 +1295,10 @@ scrapgpu_status v_stream_free(scrapgpu_stream_t * stream) {
     return guard([&]() -> scrapgpu_status {
         Stream * s = as_stream(stream);
         if (s == nullptr) return invalid("not a cuda_sm100 stream");
-        sm100_stream_sync(s->cuda);
+        if (sm100_stream_sync(s->cuda) == 0) prof_collect(s);
+        if (!s->prof_stats.empty()) std::fputs(prof_report(s).c_str(), stderr);
+        for (const Stream::ProfPending & p : s->prof_pending) { sm100_event_destroy(p.start); sm100_event_destroy(p.stop); }
+        for (sm100_event_t e : s->prof_spare) sm100_event_destroy(e);
         const scrapgpu_status st = from_sm100(sm100_stream_destroy(s->dev->ordinal, s->cuda));
         s->hdr.backend = nullptr;
         delete s;
@@ -1119,6 +1312,8 @@ scrapgpu_status v_stream_sync(scrapgpu_stream_t * stream) {
         if (s == nullptr) return invalid("not a cuda_sm100 stream");
         const scrapgpu_status st = from_sm100(sm100_stream_sync(s->cuda));
         if (st != SCRAPGPU_STATUS_OK) return st;
+        s->settled = s->epoch;
+        prof_collect(s);
         if (s->sticky != SCRAPGPU_STATUS_OK) {
             const scrapgpu_status sticky = s->sticky;
             set_error(s->sticky_message.empty() ? "an operation enqueued on this stream failed" : s->sticky_message.c_str());
@@ -1450,10 +1645,29 @@ scrapgpu_status run_fused(Stream * s, const FusedCall & f) {
         ys[i] = (float *) y.base();
     }
     if ((st = from_sm100(sm100_set_device(s->dev->ordinal))) != SCRAPGPU_STATUS_OK) return st;
-    return from_sm100(sm100_mul_mat_fused(s->cuda, f.prologue, (const float *) a.base(), f.has_b ? (const float *) b.base() : nullptr,
-                                          f.prologue == SM100_PROLOGUE_RMS_NORM ? (const float *) nw.base() : nullptr, f.eps,
-                                          f.has_sum ? (float *) so.base() : nullptr, f.has_x ? (float *) xo.base() : nullptr, (int) n, dtypes, layouts, ws,
-                                          ne(f.a, 0), ns, ys));
+    bool serial = false;
+    for (size_t i = 0; i < n; ++i) serial = serial || fresh(s, f.w[i]);
+    std::unique_ptr<ProfScope> prof;
+    if (profiling()) {
+        double bytes = 0;
+        for (size_t i = 0; i < n; ++i) bytes += weight_bytes(load_desc(f.w[i]));
+        prof.reset(new ProfScope(s, std::string(f.prologue == SM100_PROLOGUE_RMS_NORM ? "RMS_NORM_MUL" : "GLU") + " + MUL_MAT " + dtype_name(dtypes[0]) + " packed mv x" + std::to_string(n), bytes));
+    }
+    {
+        Serialized scope(serial);
+        st = from_sm100(sm100_mul_mat_fused(s->cuda, f.prologue, (const float *) a.base(), f.has_b ? (const float *) b.base() : nullptr,
+                                            f.prologue == SM100_PROLOGUE_RMS_NORM ? (const float *) nw.base() : nullptr, f.eps,
+                                            f.has_sum ? (float *) so.base() : nullptr, f.has_x ? (float *) xo.base() : nullptr, (int) n, dtypes, layouts,
+                                            ws, ne(f.a, 0), ns, ys));
+    }
+    prof.reset();
+    if (st == SCRAPGPU_STATUS_OK) {
+        ++s->epoch;
+        for (size_t i = 0; i < n; ++i) wrote(s, f.y[i]);
+        if (f.has_sum) wrote(s, f.sum_out);
+        if (f.has_x) wrote(s, f.x_out);
+    }
+    return st;
 }
 
 // runs the plan's steps in order on the stream (directly, or into a capture)
@@ -1551,10 +1765,15 @@ scrapgpu_status v_plan_execute(scrapgpu_stream_t * stream, scrapgpu_plan_t * pla
         const uint64_t run = plan->executions++;
         scrapgpu_status st = from_sm100(sm100_set_device(s->dev->ordinal));
         if (st != SCRAPGPU_STATUS_OK) return st;
-        if (plan->graph != nullptr) return enqueue_result(s, from_sm100(sm100_graph_launch(plan->graph, s->cuda)));
+        if (plan->graph != nullptr) {
+            // a graph launch starts after everything enqueued before it and ends before anything enqueued after it
+            st = enqueue_result(s, from_sm100(sm100_graph_launch(plan->graph, s->cuda)));
+            s->settled = ++s->epoch;
+            return st;
+        }
         // first execution: step by step (scratch buffers, ROPE tables and fused-or-not decisions settle here);
         // second: the same steps recorded into a graph, which is then launched; a plan of one launch gains nothing
-        if (!graphs || plan->graph_refused || run == 0 || plan->launches_per_execution < 2) {
+        if (!graphs || profiling() || plan->graph_refused || run == 0 || plan->launches_per_execution < 2) {
             const uint64_t before = sm100_launch_count();
             st = run_steps(s, plan);
             plan->launches_per_execution = (size_t) (sm100_launch_count() - before);
@@ -1575,7 +1794,9 @@ scrapgpu_status v_plan_execute(scrapgpu_stream_t * stream, scrapgpu_plan_t * pla
             return run_steps(s, plan);
         }
         plan->graph = g;
-        return enqueue_result(s, from_sm100(sm100_graph_launch(plan->graph, s->cuda)));
+        st = enqueue_result(s, from_sm100(sm100_graph_launch(plan->graph, s->cuda)));
+        s->settled = ++s->epoch;
+        return st;
     });
 }
 
@@ -1940,5 +2161,25 @@ SCRAPGPU_API scrapgpu_status scrapgpu_cuda_sm100_group_status(scrapgpu_cuda_sm10
 }
 
 SCRAPGPU_API uint64_t scrapgpu_cuda_sm100_launch_count(void) { return sm100_launch_count(); }
+
+SCRAPGPU_API size_t scrapgpu_cuda_sm100_profile_report(scrapgpu_stream_t * stream, char * out, size_t capacity) {
+    Stream * s = as_stream(stream);
+    if (s == nullptr || s->prof_stats.empty()) {
+        if (out != nullptr && capacity > 0) out[0] = 0;
+        return 0;
+    }
+    std::string text;
+    try {
+        text = prof_report(s);
+    } catch (...) {
+        return 0;
+    }
+    if (out != nullptr && capacity > 0) {
+        const size_t n = std::min(capacity - 1, text.size());
+        std::memcpy(out, text.data(), n);
+        out[n] = 0;
+    }
+    return text.size() + 1;
+}
 
 }  // extern "C"

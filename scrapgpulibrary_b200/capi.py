@@ -91,6 +91,7 @@ def lib() -> C.CDLL:
         L.sm100_add.argtypes = [vp, vp, vp, vp, i64]
         L.sm100_set_rows.argtypes = [vp, vp, vp, vp, i64, i64, i64, i64]
         L.sm100_argmax.argtypes = [vp, vp, i64, vp]
+        L.sm100_launch_serialized.argtypes = [i32]
         L.sm100_attention.argtypes = [vp, vp, vp, vp, vp, i64, vp, i64, i64, i64, i64, i64, i64, i32, i64, vp, C.c_float]
         L.sm100_attention_static.argtypes = L.sm100_attention.argtypes
         L.sm100_attention_kvcache.argtypes = L.sm100_attention.argtypes + [i32]

@@ -28,8 +28,8 @@ struct AttnArgs {
     int64_t d, dv, nq, nk, hq, hkv, offset;
     int64_t mask_heads;
     int splits, chunk, causal;
-    // KV-cache calls: the last `fresh_keys` visible keys of a query may have been written by the kernel that precedes
-    // this one in the stream, every earlier key (and `positions`) is older than that kernel, so those rows can be
+    // KV-cache calls: only the last `fresh_keys` visible keys of a query may have been written since the stream's last
+    // point of full serialization, every earlier key (and `positions`) is older than that, so those rows can be
     // requested before the dependency wait.  -1: no such promise, everything is read after the wait.
     int fresh_keys;
     float scale;

@@ -69,6 +69,15 @@ int current_device();    // ordinal of the current device (0 when it cannot be r
 constexpr int MAX_DEVICES = 64;
 bool pdl_enabled();
 void count_launch();
+// What the library launched last on a stream, as far as the dispatcher of the Q4_K matvec cares: TAIL_Q4K_MATVEC after
+// a single-tensor, single-column packed Q4_K matvec by matvec_q4k_imma, TAIL_Q4K_RING after one by matvec_q4k_ring
+// (both set by the host functions), TAIL_OTHER after any other launch or copy of this library (launch() and the copy
+// entries reset it).
+enum { TAIL_OTHER = 0, TAIL_Q4K_MATVEC = 1, TAIL_Q4K_RING = 2 };
+void stream_tail_set(cudaStream_t stream, int kind);
+int stream_tail(cudaStream_t stream);
+// launches of the calling thread without programmatic dependent launch while `on` (sm100_launch_serialized)
+void thread_serialized(bool on);
 
 // Launches `kernel` on `stream`; with programmatic dependent launch when enabled, so the kernel may
 // start (and prefetch) while its predecessor on the stream drains.  Kernels launched through this
@@ -89,6 +98,7 @@ int launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStr
     }
     cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
     if (e != cudaSuccess) return cuda_fail(e, "kernel launch");
+    stream_tail_set(stream, TAIL_OTHER);
     count_launch();
     return ST_OK;
 }
@@ -117,6 +127,7 @@ int launch_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
     cfg.numAttrs = n;
     cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
     if (e != cudaSuccess) return cuda_fail(e, "kernel launch (cluster)");
+    stream_tail_set(stream, TAIL_OTHER);
     count_launch();
     return ST_OK;
 }

@@ -502,7 +502,8 @@ int matvec(cudaStream_t s, int dtype, int layout, const void * w, int64_t w_row_
     if (is_quant(dtype) && !x_aligned) return fail(ST_UNSUPPORTED, "mul_mat: activations must be 16-byte aligned (columns too)");
     static const int use_imma = env_int("SM100_Q4K_IMMA", 1);
     if (use_imma && layout == LAYOUT_PACKED && dtype == DT_Q4_K && x_aligned && m == 1) {
-        // the ring kernel (consecutive launches overlap); leftover rows take the row kernel
+        // the ring kernel (consecutive launches overlap; it declines unless the stream's last launch was such a matvec);
+        // leftover rows take the row kernel
         bool handled = false;
         const int st = matvec_q4k_ring_multi(s, 1, &w, &n, k, x, &y, &handled, nullptr);
         if (st != ST_OK) return st;
@@ -520,6 +521,7 @@ int matvec(cudaStream_t s, int dtype, int layout, const void * w, int64_t w_row_
         if (handled) {
             const int64_t full = (n / 16) * 16;
             if (full < n) return took("matvec_q4k_imma+rows", launch_rows<UnitQ4K, true>(s, w, 0, k, n, x, ldx, m, y, ldy, full));
+            if (m == 1) stream_tail_set(s, TAIL_Q4K_MATVEC);   // a second plain Q4_K matvec right behind this one starts a run of the ring kernel
             return took("matvec_q4k_imma", ST_OK);
         }
     }
@@ -593,6 +595,18 @@ int matvec(cudaStream_t s, int dtype, int layout, const void * w, int64_t w_row_
             if (full < n) return took("matvec_q4k_mma+rows", launch_rows<UnitQ4K, true>(s, w, 0, k, n, x, ldx, m, y, ldy, full));
             return took("matvec_q4k_mma", ST_OK);
         }
+    }
+    // Q6_K / Q4_0 / Q8_0 with 2..8 columns: the single-column tensor-core and wide kernels have no multi-column form yet,
+    // and one launch of them per column (weights re-read per column, mostly from L2 for matrices below its size) is still
+    // 2-3 times faster than the one-warp-per-row kernel that serves every column in one pass (measured on the sweep
+    // shapes: Q6_K 4096 x 4096 at M = 2: 0.93 vs 0.35 TB/s of algorithmic bytes)
+    if (layout == LAYOUT_PACKED && m > 1 && (dtype == DT_Q6_K || dtype == DT_Q4_0 || dtype == DT_Q8_0) && x_aligned && n >= 16 &&
+        ((dtype == DT_Q6_K && k % 256 == 0) || (dtype != DT_Q6_K && k % 128 == 0))) {
+        for (int64_t c = 0; c < m; ++c) {
+            const int st = matvec(s, dtype, layout, w, w_row_stride, k, n, x + c * ldx, ldx, 1, y + c * ldy, ldy);
+            if (st != ST_OK) return st;
+        }
+        return took("matvec_per_column", ST_OK);
     }
     static const int use_wide = env_int("SM100_MV_WIDE", 1);
     if (use_wide && layout == LAYOUT_PACKED) {

@@ -38,10 +38,10 @@ namespace {
 
 constexpr int RG_WARPS = 16;
 constexpr int RG_THREADS = RG_WARPS * 32;
-constexpr int RG_MAX_SLOTS = 3;                   // ring slots per warp: 3 where two CTAs of that size fit an SM, else 2
+constexpr int RG_MAX_SLOTS = 2;                   // ring slots per warp (a third one was measured: the 4 KB it takes from the partial-sum window cost more than it gave)
 constexpr uint32_t RG_TILE_BYTES = 2048;          // 16 rows x 256 weights
 constexpr uint32_t RG_HDR_BYTES = 256;            // their 16 block headers
-constexpr int RG_WINDOW = 4;                      // rounds whose partial sums are kept before the CTA adds them up
+constexpr int RG_WINDOW = 8;                      // rounds whose partial sums are kept before the CTA adds them up
 constexpr int RG_MAX_TENSORS = 3;
 
 struct RingArgs {
@@ -446,8 +446,20 @@ int launch_ring(cudaStream_t s, const RingArgs & a, int pro, size_t smem, int gr
 int matvec_q4k_ring_multi(cudaStream_t s, int count, const void * const * ws, const int64_t * ns, int64_t k, const float * x,
                           float * const * ys, bool * handled, const Q4KPrologue * pro) {
     *handled = false;
+    // SM100_Q4K_RING: 0 never; 1 (default) in runs of plain matvecs: a single tensor without prologue whose predecessor
+    // on the stream is a matvec of the same kind; 2 wherever the shapes allow (tests).  The kernel pays off when launch
+    // N + 1 finds ONE free CTA slot on every SM beside launch N (back to back 4.0 / 7.0 / 8.2 us per launch on the three
+    // projection shapes against 4.4 / 7.9 / 8.6 of matvec_q4k_imma).  Behind a kernel of another kind its CTAs are placed
+    // as SMs drain, two on the first SMs that become free and none on others, and the skew is inherited by every later
+    // launch of the run (measured: 5.4 / 10.3 / 12.9 us per launch in a run started behind matvec_q4k_imma; a decode step
+    // that used this kernel for its fused projections lost a fifth of its speed).  So the first ring launch of a run is
+    // launched fully serialized - on an empty GPU the CTAs are dealt one per SM - and the later ones with programmatic
+    // dependent launch.
     static const int enabled = [] { const char * e = getenv("SM100_Q4K_RING"); return e != nullptr ? atoi(e) : 1; }();
     if (!enabled) return ST_OK;
+    const int tail = stream_tail(s);
+    if (enabled == 1 && (count != 1 || (pro != nullptr && pro->mode != 0) || tail == TAIL_OTHER)) return ST_OK;
+    const bool run_start = enabled == 1 && tail != TAIL_Q4K_RING;
     int mode = 0;
     if (pro != nullptr && pro->mode != 0) {
         mode = pro->mode;
@@ -500,10 +512,13 @@ int matvec_q4k_ring_multi(cudaStream_t s, int count, const void * const * ws, co
     a.slots = ring_smem_bytes(k, mode, RG_MAX_SLOTS) <= (size_t) 113 * 1024 ? RG_MAX_SLOTS : 2;
     const size_t smem = ring_smem_bytes(k, mode, a.slots);
     int st;
+    if (run_start) thread_serialized(true);
     if (nbw == 1) st = launch_ring<1>(s, a, mode, smem, (int) grid);
     else if (nbw == 2) st = launch_ring<2>(s, a, mode, smem, (int) grid);
     else st = launch_ring<3>(s, a, mode, smem, (int) grid);
+    if (run_start) thread_serialized(false);
     *handled = st == ST_OK;
+    if (st == ST_OK && count == 1 && mode == 0) stream_tail_set(s, TAIL_Q4K_RING);
     return st;
 }
 

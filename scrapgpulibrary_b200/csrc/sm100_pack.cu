@@ -121,8 +121,9 @@ __host__ __device__ inline void unpack_block(int dtype, const Planes & P, int64_
 
 // blocks [first, first + count): natural holds them contiguously starting at its byte 0
 __global__ void pack_kernel(int dtype, Planes P, int64_t first, int64_t count, int bb, const uint8_t * natural, uint8_t * packed, int to_packed) {
+    // never releases its successor early: what it writes are weights, which the matvec kernels request before their
+    // own dependency wait
     pdl_wait();
-    pdl_launch_dependents();
     for (int64_t i = blockIdx.x * (int64_t) blockDim.x + threadIdx.x; i < count; i += (int64_t) gridDim.x * blockDim.x) {
         if (to_packed) pack_block(dtype, P, first + i, natural + i * bb, packed);
         else unpack_block(dtype, P, first + i, packed, const_cast<uint8_t *>(natural) + i * bb);

@@ -29,7 +29,38 @@ int cuda_fail(cudaError_t e, const char * what) {
     return fail(st, "%s: %s (%s)", what, cudaGetErrorString(e), cudaGetErrorName(e));
 }
 
-bool pdl_enabled() { return g_pdl.load(std::memory_order_relaxed) != 0; }
+static thread_local int t_serialized = 0;
+
+static thread_local int t_serialized_inner = 0;   // the library's own bracket, independent of the caller's
+void thread_serialized(bool on) { t_serialized_inner = on ? 1 : 0; }
+
+// kind of the last launch per stream (stream handle + 8 with the kind in the low bits; the legacy stream 0 can so be
+// told from an empty slot); a handful of slots serves the few streams a process drives at a time, a lost entry only
+// costs speed
+static std::atomic<uintptr_t> g_tail[8];
+void stream_tail_set(cudaStream_t stream, int kind) {
+    const uintptr_t key = ((uintptr_t) stream + 8) & ~(uintptr_t) 7;
+    for (auto & slot : g_tail) {
+        if ((slot.load(std::memory_order_relaxed) & ~(uintptr_t) 7) != key) continue;
+        slot.store(kind == TAIL_OTHER ? 0 : key | (uintptr_t) kind, std::memory_order_relaxed);
+        return;
+    }
+    if (kind == TAIL_OTHER) return;
+    for (auto & slot : g_tail) {
+        uintptr_t empty = 0;
+        if (slot.compare_exchange_strong(empty, key | (uintptr_t) kind, std::memory_order_relaxed)) return;
+    }
+    g_tail[(key >> 6) % 8].store(key | (uintptr_t) kind, std::memory_order_relaxed);
+}
+int stream_tail(cudaStream_t stream) {
+    const uintptr_t key = ((uintptr_t) stream + 8) & ~(uintptr_t) 7;
+    for (auto & slot : g_tail) {
+        const uintptr_t v = slot.load(std::memory_order_relaxed);
+        if ((v & ~(uintptr_t) 7) == key) return (int) (v & 7);
+    }
+    return TAIL_OTHER;
+}
+bool pdl_enabled() { return t_serialized == 0 && t_serialized_inner == 0 && g_pdl.load(std::memory_order_relaxed) != 0; }
 void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
 
 int current_device() {
@@ -197,6 +228,7 @@ int sm100_stream_sync(sm100_stream_t stream) { return sync_and_poll((cudaStream_
 
 int sm100_memcpy_h2d(sm100_stream_t s, void * dst, const void * src, size_t n, int blocking) {
     if (n == 0) return ST_OK;
+    stream_tail_set((cudaStream_t) s, TAIL_OTHER);
     SM100_CUDA(cudaMemcpyAsync(dst, src, n, cudaMemcpyHostToDevice, (cudaStream_t) s));
     if (blocking) SM100_CUDA(cudaStreamSynchronize((cudaStream_t) s));
     return ST_OK;
@@ -204,6 +236,7 @@ int sm100_memcpy_h2d(sm100_stream_t s, void * dst, const void * src, size_t n, i
 
 int sm100_memcpy_d2h(sm100_stream_t s, void * dst, const void * src, size_t n, int blocking) {
     if (n == 0) return ST_OK;
+    stream_tail_set((cudaStream_t) s, TAIL_OTHER);
     SM100_CUDA(cudaMemcpyAsync(dst, src, n, cudaMemcpyDeviceToHost, (cudaStream_t) s));
     // a blocking read makes results visible like a stream_sync does (include/scrapgpu/op.h:190-194), so a kernel that
     // gave up on a bounded wait is reported here too instead of handing out an incomplete result with status OK
@@ -213,6 +246,7 @@ int sm100_memcpy_d2h(sm100_stream_t s, void * dst, const void * src, size_t n, i
 
 int sm100_memcpy_d2d(sm100_stream_t s, void * dst, const void * src, size_t n, int blocking) {
     if (n == 0) return ST_OK;
+    stream_tail_set((cudaStream_t) s, TAIL_OTHER);
     // overlapping ranges get memmove semantics through a stream-ordered temporary
     const char * a = (const char *) src;
     char * b = (char *) dst;
@@ -233,6 +267,7 @@ int sm100_memcpy_d2d(sm100_stream_t s, void * dst, const void * src, size_t n, i
 
 int sm100_memset(sm100_stream_t s, void * dst, int byte, size_t n, int blocking) {
     if (n == 0) return ST_OK;
+    stream_tail_set((cudaStream_t) s, TAIL_OTHER);
     SM100_CUDA(cudaMemsetAsync(dst, byte, n, (cudaStream_t) s));
     if (blocking) SM100_CUDA(cudaStreamSynchronize((cudaStream_t) s));
     return ST_OK;
@@ -323,6 +358,7 @@ int sm100_graph_end(sm100_stream_t s, sm100_graph_t * out) {
 }
 
 int sm100_graph_launch(sm100_graph_t g, sm100_stream_t s) {
+    stream_tail_set((cudaStream_t) s, TAIL_OTHER);
     SM100_CUDA(cudaGraphLaunch((cudaGraphExec_t) g, (cudaStream_t) s));
     return ST_OK;
 }
@@ -341,6 +377,11 @@ int sm100_scratch_reserve(int slot, size_t bytes) {
 
 int sm100_set_pdl(int enabled) {
     g_pdl.store(enabled ? 1 : 0, std::memory_order_relaxed);
+    return ST_OK;
+}
+
+int sm100_launch_serialized(int on) {
+    t_serialized = on ? 1 : 0;
     return ST_OK;
 }
 

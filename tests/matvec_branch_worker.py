@@ -19,9 +19,9 @@ from tests import util as U  # noqa: E402
 # (dtype, K, N, M): whole tiles and leftover rows, short and long rows, one and several columns
 CASES = [(U.Q4_K, 4096, 272, 1), (U.Q4_K, 4096, 264, 2), (U.Q4_K, 2048, 40, 4), (U.Q4_K, 12288, 48, 1), (U.Q4_K, 512, 33, 8),
          (U.Q4_K, 1024, 40, 1), (U.Q4_K, 4096, 64, 2), (U.Q4_K, 6144, 4112, 1), (U.Q4_K, 768, 9616, 1), (U.Q4_K, 16384, 32, 1), (U.Q4_K, 4096, 24016, 1),
-         (U.Q6_K, 4096, 272, 1), (U.Q6_K, 2048, 40, 1), (U.Q6_K, 12288, 528, 1), (U.Q6_K, 4096, 64, 4), (U.Q6_K, 768, 24, 1),
+         (U.Q6_K, 4096, 272, 1), (U.Q6_K, 2048, 40, 1), (U.Q6_K, 12288, 528, 1), (U.Q6_K, 4096, 64, 4), (U.Q6_K, 768, 24, 1), (U.Q6_K, 768, 8, 2),
          (U.Q4_0, 4096, 272, 1), (U.Q4_0, 2048, 33, 1), (U.Q4_0, 4096, 64, 3), (U.Q4_0, 96, 24, 1),
-         (U.Q8_0, 4096, 272, 1), (U.Q8_0, 1024, 40, 1), (U.Q8_0, 4096, 64, 8), (U.Q8_0, 160, 17, 1)]
+         (U.Q8_0, 4096, 272, 1), (U.Q8_0, 1024, 40, 1), (U.Q8_0, 4096, 64, 8), (U.Q8_0, 160, 17, 1), (U.Q8_0, 160, 17, 3)]
 
 
 def main():

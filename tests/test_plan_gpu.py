@@ -157,8 +157,14 @@ def test_plan_matches_node_by_node_execution_and_replays_as_a_graph(both):
         for name in glayer.outputs:
             assert np.array_equal(r[name].view(np.uint32), results[0][name].view(np.uint32)), f"{name}: graph replay differs from the first execution"
     first = results[0]
-    for name in ("x1", "x2", "kcache", "vcache"):    # adds and row scatters keep their arithmetic under fusion
+    for name in ("x1", "x2"):    # adds keep their arithmetic under fusion
         assert np.array_equal(first[name].view(np.uint32), per_op[name].view(np.uint32)), name
+    # the scattered rows are the k / v projections: node by node the second and third of three consecutive MUL_MATs are
+    # served by the ring kernel, in the plan all three by one fused launch of matvec_q4k_imma; the two add the same
+    # integer block sums in different orders, every other element of the caches must be untouched
+    for name in ("kcache", "vcache"):
+        assert sgref.nmse(first[name], per_op[name]) <= 1e-10, name
+        assert np.array_equal(first[name] == 0, per_op[name] == 0), name
     for name in glayer.outputs:
         assert sgref.nmse(first[name], per_op[name]) <= 1e-6, name
         assert sgref.nmse(first[name], want_cpu[name]) <= 1e-6, name

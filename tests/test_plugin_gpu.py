@@ -486,3 +486,54 @@ def test_set_rows_pair_matches_two_set_rows(both):
     bad = [gpu.tensor(abi.F32, [128, 16, 8]), gpu.tensor(abi.F16, [128, 16, 8])]
     st, why = gpu.supported(abi.OP_SET_ROWS_PAIR, ins, bad)
     assert st in (abi.UNSUPPORTED, abi.INVALID_ARGUMENT) and why
+
+
+@pytest.mark.parametrize("between", [0, 1, 3])
+def test_mul_mat_over_a_left_operand_written_just_before(both, between):
+    """MUL_MAT whose src0 was produced by a kernel enqueued right before it, with no synchronisation in between (the K
+    cache of the core's attention composition, src/core/attention.cpp:487-560: CPY then MUL_MAT).  The matvec kernels ask
+    for their weights before they wait for earlier kernels, so the backend has to notice that this operand is not an
+    upload that sits in memory and serialize the launch; `between` small kernels separate the producer and the matvec.
+    The producer is long (a 128 MB copy) and the destination starts as zeros, so a premature read shows."""
+    _, gpu = both
+    k, n = 4096, 8192
+    a = rnd(31, n, k)
+    x = rnd(32, k)
+    src = gpu.tensor(abi.F32, [k, n]).upload(a)
+    dst = gpu.tensor(abi.F32, [k, n]).upload(np.zeros(n * k, np.float32))
+    xt = gpu.tensor(abi.F32, [k]).upload(x)
+    tmp = gpu.tensor(abi.F32, [k]).upload(np.zeros(k, np.float32))
+    want, got = (gpu.tensor(abi.F32, [n]).upload(np.zeros(n, np.float32)) for _ in range(2))
+    gpu.execute(abi.OP_MUL_MAT, [src, xt], [want], abi.MulMatParams())
+    gpu.sync()
+    for trial in range(3):
+        dst.upload(np.zeros(n * k, np.float32))
+        gpu.sync()
+        gpu.execute(abi.OP_CPY, [src], [dst], abi.CpyParams())
+        for _ in range(between):
+            gpu.execute(abi.OP_ADD, [xt, xt], [tmp])
+        gpu.execute(abi.OP_MUL_MAT, [dst, xt], [got], abi.MulMatParams())
+        gpu.sync()
+        assert np.array_equal(got.download(np.float32, n), want.download(np.float32, n)), f"trial {trial}"
+    for t in (src, dst, xt, tmp, want, got):
+        t.free()
+
+
+def test_profile_table():
+    """SCRAPGPU_SM100_PROFILE=1: per-op-key event timings like the OpenCL backend's GGML_CL11_PROFILE table
+    (src/backends/opencl11/executor.h:41-112): keys carry op, weight type and mv/mm form, MUL_MAT rows report the
+    weight bandwidth, the table is also printed when the stream is freed."""
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, SCRAPGPU_SM100_PROFILE="1", PYTHONPATH=root)
+    r = subprocess.run([sys.executable, "-m", "tests.profile_worker"], cwd=root, env=env, capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stdout + r.stderr
+    lines = r.stdout.splitlines()
+    assert lines[0].startswith("cuda_sm100 profile of ") and "total kernel time" in lines[0]
+    mm = [l for l in lines if "MUL_MAT q4_K packed mv n=1" in l]
+    assert len(mm) == 1 and "     3 calls" in mm[0] and "weights" in mm[0] and "GB/s" in mm[0], r.stdout
+    add = [l for l in lines if l.strip().startswith("ADD")]
+    assert len(add) == 1 and "     1 calls" in add[0]
+    assert "RESULT_SUM True" in r.stdout
+    assert "cuda_sm100 profile of " in r.stderr          # printed at stream_free
