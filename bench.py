@@ -61,6 +61,10 @@ def algorithmic_bytes(dtype: int, k: int, n: int, m: int = 1) -> float:
     return n * k * BPW[dtype] + 4.0 * k * m + 4.0 * n * m
 
 
+# the all-reduce of a K-sharded product inside the matvec launch (sm100_mul_mat_allreduce); 0: matvec, then sm100_allreduce_sum
+FUSED_EXCHANGE = os.environ.get("SM100_TP_FUSED", "1") != "0"
+
+
 def profiled_traffic(kernel_prefix: str):
     """DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) of the dominant kernel from the ncu capture
     summarised under profiles/: profiles/roofline_traffic.json names the kernel it was taken from, so a figure that
@@ -220,6 +224,12 @@ def run_ours(args, rank: int, world: int, local_rank: int):
             if only_shape is not None and s != only_shape:
                 continue
             p = pool[s]
+            if p["split"] == "k" and m == 1 and FUSED_EXCHANGE:
+                # the K shards' partial sums are exchanged and added inside the matvec launch
+                capi.check(L.sm100_mul_mat_allreduce(allreduce.ctx, stream.handle, 0, C.c_void_p(xs[p["k"]].ptr), None, dtype, 1, C.c_void_p(p["mats"][layer].ptr),
+                                                     p["k"], p["n"], C.c_void_p(ys[p["n"]].ptr)), "mul_mat_allreduce")
+                cnt += 1
+                continue
             capi.mul_mat(stream, dtype, 1, p["mats"][layer], p["k"], p["n"], xs[p["k"]], m, ys[p["n"]])
             if p["split"] == "k":   # partial sums of the K shards -> the full result on every rank
                 capi.check(L.sm100_allreduce_sum(allreduce.ctx, stream.handle, C.c_void_p(ys[p["n"]].ptr), p["n"] * m), "allreduce_sum")
@@ -339,7 +349,8 @@ def run_ours(args, rank: int, world: int, local_rank: int):
             "data": "synthetic: seeded N(0, 0.02) weights in Q4_K blocks, N(0, 1) activations",
             "config": {"workload": f"Q4_K matvec sweep, M=1, Qwen3-8B projection shapes (K,N) in {SHAPES} x {layers} layers"
                                    + ("" if world == 1 else f", split over {world} GPUs: (K,N) {SHAPES[0]} and {SHAPES[1]} by weight rows, {SHAPES[2]} by K with an "
-                                      "all-reduce of the 4096-float partial results (own one-shot kernel over peer-mapped memory)"),
+                                      "all-reduce of the 4096-float partial results over peer-mapped memory ("
+                                      + ("inside the matvec launch" if FUSED_EXCHANGE else "own one-shot kernel after the matvec") + ")"),
                        "launches_per_step": per_step, "matvecs_per_step": matvecs_per_step, "bytes_per_step": int(step_bytes), "bytes_per_step_per_gpu": int(step_bytes / world),
                        "weights_layout": "backend-packed planes", "all_reduce_fault": allreduce.fault() if allreduce is not None else 0,
                        "l2": "inputs larger than L2 (pool %.2f GB per GPU, L2 126 MB)" % (step_bytes / world / 1e9), "timing": "CUDA events on the launching stream, one graph replay per step",

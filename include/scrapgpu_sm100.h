@@ -89,6 +89,19 @@ SM100_API int sm100_allreduce_create(int rank, int world, int capacity_floats, v
 SM100_API int sm100_allreduce_sum(sm100_allreduce_t ctx, sm100_stream_t s, float * x, int n);
 SM100_API int sm100_allreduce_fault(sm100_allreduce_t ctx, int * fault_out);
 SM100_API int sm100_allreduce_destroy(sm100_allreduce_t ctx);
+/* y[N] = sum over the ranks of W_r[K_r, N] . x_r[K_r]: the K-sharded ("row-parallel") product of tensor parallelism with
+ * its all-reduce, M = 1; every rank calls it with its own shard and ends up with the same bits in y.  prologue 0: a is x;
+ * SM100_PROLOGUE_SWIGLU: x = swiglu(a, b) (the down projection).  For packed Q4_K tensors with whole 16-row tiles the
+ * exchange is folded into the matvec launch: every CTA stores the partial sums of its row tiles into its slot of every
+ * rank's receive area (plain 8-byte peer stores: the value and the step number as its tag in one word, so neither a fence
+ * nor a flag is needed) and adds the slots in rank order, waiting for each value's tag - bounded, about a second, after
+ * which sm100_allreduce_fault reports it: the latency of one peer store at the end of the launch instead of a launch of
+ * its own between two dependency boundaries.  Other tensors
+ * run the matvec and sm100_allreduce_sum one after the other (same result contract).  All ranks must make the same
+ * sequence of calls with the same shapes.  Like sm100_allreduce_sum it stands where the reference bounces through the
+ * host (src/core/transport.cpp:53-146); the reference has no collective. */
+SM100_API int sm100_mul_mat_allreduce(sm100_allreduce_t ctx, sm100_stream_t s, int prologue, const float * a, const float * b, int dtype,
+                                      int layout, const void * w, int64_t k, int64_t n, float * y);
 
 /* ---- timing and replay: the plan seat of the reference (src/core/registry.cpp:200-220, "selection
  *      happens once at plan build") becomes a captured CUDA graph ---- */

@@ -54,6 +54,17 @@ def _run(cmd) -> None:
 def build_sm100(force: bool = False, verbose: bool = False) -> str:
     os.makedirs(LIBDIR, exist_ok=True)
     os.makedirs(OBJDIR, exist_ok=True)
+    # several ranks of one job may arrive here at once: one of them builds, the others wait and find the result current
+    import fcntl
+    with open(os.path.join(OBJDIR, ".lock"), "w") as lock:
+        fcntl.flock(lock, fcntl.LOCK_EX)
+        try:
+            return _build_sm100_locked(force, verbose)
+        finally:
+            fcntl.flock(lock, fcntl.LOCK_UN)
+
+
+def _build_sm100_locked(force: bool, verbose: bool) -> str:
     srcs = sorted(f for f in os.listdir(CSRC) if f.endswith(".cu"))
     headers = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".cuh", ".h"))]
     headers.append(os.path.join(INCLUDE, "scrapgpu_sm100.h"))
@@ -72,7 +83,9 @@ def build_sm100(force: bool = False, verbose: bool = False) -> str:
         with ThreadPoolExecutor(max_workers=min(8, len(jobs))) as ex:
             list(ex.map(_run, jobs))
     if force or jobs or _newer(SM100_SO, objs):
-        _run([nvcc, "-shared", "-o", SM100_SO] + objs)
+        tmp = SM100_SO + ".tmp.%d" % os.getpid()
+        _run([nvcc, "-shared", "-o", tmp] + objs)
+        os.replace(tmp, SM100_SO)   # readers never see a half-written library
     return SM100_SO
 
 

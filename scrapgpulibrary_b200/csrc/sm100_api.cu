@@ -10,8 +10,9 @@ int matvec(cudaStream_t s, int dtype, int layout, const void * w, int64_t w_row_
 int matvec_q4k_imma_multi(cudaStream_t s, int count, const void * const * ws, const int64_t * ns, int64_t k, const float * x, int64_t ldx,
                           int64_t m, float * const * ys, const int64_t * ldys, bool * handled, const Q4KPrologue * pro);
 const char * matvec_last_kernel();
+void matvec_note_kernel(const char * name);
 int matvec_q4k_ring_multi(cudaStream_t s, int count, const void * const * ws, const int64_t * ns, int64_t k, const float * x,
-                          float * const * ys, bool * handled, const Q4KPrologue * pro);
+                          float * const * ys, bool * handled, const Q4KPrologue * pro, const ArFuse * fuse);
 int gemm_tc_mul_mat(cudaStream_t s, int dtype, int layout, const void * w, int64_t w_row_stride, int64_t k, int64_t n, const float * x,
                     int64_t ldx, int64_t m, float * y, int64_t ldy, bool * handled);
 }
@@ -63,7 +64,7 @@ int sm100_mul_mat_multi(sm100_stream_t s, int count, const int * dtypes, const i
     }
     if (grouped >= 2 && x != nullptr && k > 0) {
         bool handled = false;
-        int st = matvec_q4k_ring_multi((cudaStream_t) s, grouped, gw, gn, k, x, gy, &handled, nullptr);
+        int st = matvec_q4k_ring_multi((cudaStream_t) s, grouped, gw, gn, k, x, gy, &handled, nullptr, nullptr);
         if (st != ST_OK) return st;
         if (!handled) st = matvec_q4k_imma_multi((cudaStream_t) s, grouped, gw, gn, k, x, k, 1, gy, gld, &handled, nullptr);
         if (st != ST_OK) return st;
@@ -99,12 +100,48 @@ int sm100_mul_mat_fused(sm100_stream_t s, int prologue, const float * a, const f
     pro.mode = prologue;
     pro.a = a; pro.b = b; pro.norm_w = norm_w; pro.sum_out = sum_out; pro.x_out = x_out; pro.eps = eps;
     bool handled = false;
-    int st = matvec_q4k_ring_multi((cudaStream_t) s, count, ws, ns, k, a, ys, &handled, &pro);
+    int st = matvec_q4k_ring_multi((cudaStream_t) s, count, ws, ns, k, a, ys, &handled, &pro, nullptr);
     if (st != ST_OK) return st;
     if (!handled) st = matvec_q4k_imma_multi((cudaStream_t) s, count, ws, ns, k, a, k, 1, ys, ld, &handled, &pro);
     if (st != ST_OK) return st;
     if (!handled) return fail(ST_UNSUPPORTED, "mul_mat_fused: this shape is not served by the fused kernel; run the separate ops");
     return ST_OK;
+}
+
+int sm100_mul_mat_allreduce(sm100_allreduce_t ctx, sm100_stream_t s, int prologue, const float * a, const float * b, int dtype, int layout,
+                            const void * w, int64_t k, int64_t n, float * y) {
+    if (ctx == nullptr || a == nullptr || w == nullptr || y == nullptr || k <= 0 || n <= 0) return fail(ST_INVALID, "mul_mat_allreduce: null pointer or empty shape");
+    if (prologue != 0 && prologue != SM100_PROLOGUE_SWIGLU) return fail(ST_INVALID, "mul_mat_allreduce: the prologue is 0 or SM100_PROLOGUE_SWIGLU");
+    if (prologue == SM100_PROLOGUE_SWIGLU && b == nullptr) return fail(ST_INVALID, "mul_mat_allreduce: SwiGLU needs both halves");
+    ArFuse fuse;
+    allreduce_fuse_args(ctx, &fuse);
+    if (n % 4 != 0 || n > fuse.capacity) return fail(ST_INVALID, "mul_mat_allreduce: N must be a multiple of 4 within the context's capacity");
+    if (dtype == DT_Q4_K && layout == LAYOUT_PACKED && fuse.world > 1) {
+        Q4KPrologue pro = {};
+        pro.mode = prologue;
+        pro.a = a; pro.b = b;
+        bool handled = false;
+        const int st = matvec_q4k_ring_multi((cudaStream_t) s, 1, &w, &n, k, a, &y, &handled, prologue != 0 ? &pro : nullptr, &fuse);
+        if (st != ST_OK) return st;
+        if (handled) {
+            matvec_note_kernel("matvec_q4k_ring+allreduce");
+            return ST_OK;
+        }
+    }
+    // the separate launches: (SwiGLU into library scratch,) the matvec, the one-shot all-reduce
+    int st;
+    if (prologue == SM100_PROLOGUE_SWIGLU) {
+        if (dtype == DT_Q4_K && layout == LAYOUT_PACKED && n % 16 == 0) {
+            const int dt = dtype, lay = layout;
+            st = sm100_mul_mat_fused(s, prologue, a, b, nullptr, 0.0f, nullptr, nullptr, 1, &dt, &lay, &w, k, &n, &y);
+        } else {
+            return fail(ST_UNSUPPORTED, "mul_mat_allreduce: the SwiGLU prologue is served for packed Q4_K tensors with a multiple of 16 rows; run the separate ops");
+        }
+    } else {
+        st = matvec((cudaStream_t) s, dtype, layout, w, 0, k, n, a, k, 1, y, n);
+    }
+    if (st != ST_OK) return st;
+    return fuse.world > 1 ? sm100_allreduce_sum(ctx, s, y, (int) n) : ST_OK;
 }
 
 }  // extern "C"

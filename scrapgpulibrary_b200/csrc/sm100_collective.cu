@@ -20,9 +20,7 @@ namespace sm100 {
 
 namespace {
 
-constexpr int AR_MAX_RANKS = 8;
 constexpr int AR_THREADS = 1024;
-constexpr uint32_t AR_WAIT_LIMIT = 1u << 22;   // polls (each with a short sleep) before a rank gives up: ~1 s
 
 struct ArArgs {
     float * recv[AR_MAX_RANKS];       // every rank's receive area [2][world][capacity] (entry `rank` is the local one)
@@ -90,10 +88,17 @@ __global__ void __launch_bounds__(AR_THREADS, 1) allreduce_kernel(ArArgs a) {
 
 struct ArContext {
     ArArgs args;
+    ArFuse fuse;
     int device;
 };
 
 }  // namespace
+
+bool allreduce_fuse_args(void * ctx, ArFuse * out) {
+    if (ctx == nullptr) return false;
+    *out = static_cast<ArContext *>(ctx)->fuse;
+    return true;
+}
 
 }  // namespace sm100
 
@@ -125,8 +130,11 @@ int sm100_ipc_close(void * device_ptr) {
     return ST_OK;
 }
 
+// area of one rank: [receive slots of sm100_allreduce_sum][its flags 256 B][counter, fault 256 B]
+//                   [receive slots of the fused matvec exchange: 8 bytes per value][its step counter and ticket 256 B]
 size_t sm100_allreduce_area_bytes(int world, int capacity) {
-    return (size_t) 2 * world * capacity * sizeof(float) + 256 /* flags [2][world] */ + 256 /* counter, fault */;
+    const size_t data = (size_t) 2 * world * capacity * sizeof(float);
+    return data + 256 + 256 + 2 * data + 256;
 }
 
 int sm100_allreduce_create(int rank, int world, int capacity, void * const * areas, sm100_allreduce_t * out) {
@@ -143,6 +151,14 @@ int sm100_allreduce_create(int rank, int world, int capacity, void * const * are
     }
     c->args.counter = (uint32_t *) ((uint8_t *) areas[rank] + data + 256);
     c->args.fault = (int *) ((uint8_t *) areas[rank] + data + 256 + 64);
+    const size_t fused = data + 512;
+    for (int p = 0; p < world; ++p) c->fuse.recv[p] = (uint2 *) ((uint8_t *) areas[p] + fused);
+    c->fuse.step = (uint32_t *) ((uint8_t *) areas[rank] + fused + 2 * data);
+    c->fuse.done = c->fuse.step + 16;
+    c->fuse.fault = c->args.fault;
+    c->fuse.capacity = capacity;
+    c->fuse.rank = rank;
+    c->fuse.world = world;
     c->args.capacity = capacity;
     c->args.rank = rank;
     c->args.world = world;

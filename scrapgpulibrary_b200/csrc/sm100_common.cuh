@@ -61,6 +61,21 @@ struct Q4KPrologue {
     float eps;
 };
 
+// All-reduce folded into the last phase of a K-sharded matvec: what the kernel needs of an all-reduce context
+// (sm100_collective.cu).  Every CTA stores the partial sums of its row tiles, each value in one 8-byte word with the step
+// number as its tag, into its slot of every rank's receive area, then adds the slots in rank order, waiting (bounded) for
+// each value's tag: the latency of one peer store, no fence, no flag (the scheme of NCCL's low-latency protocol).
+constexpr int AR_MAX_RANKS = 8;
+constexpr uint32_t AR_WAIT_LIMIT = 1u << 22;   // polls (each with a short sleep) before a rank gives up: ~1 s
+struct ArFuse {
+    uint2 * recv[AR_MAX_RANKS];       // every rank's receive area [2][world][capacity] of (value bits, step tag) (entry `rank` is the local one)
+    uint32_t * step;                  // local: fused launches completed so far (the tag of the next one is this + 1)
+    uint32_t * done;                  // local: CTAs of the running fused launch that have finished (the last one advances `step`)
+    int * fault;                      // local: set when a wait ran out
+    int rank, world, capacity;
+};
+bool allreduce_fuse_args(void * ctx, ArFuse * out);   // false when ctx is null
+
 int sm_count();          // SMs of the current device (cached per device)
 int current_device();    // ordinal of the current device (0 when it cannot be read)
 

@@ -30,7 +30,7 @@ int matvec_q4k_tiles(cudaStream_t s, const void * w, int64_t k, int64_t n, const
                      bool * handled);
 int q4k_pass_width(int64_t k, int64_t m);
 int matvec_q4k_ring_multi(cudaStream_t s, int count, const void * const * ws, const int64_t * ns, int64_t k, const float * x,
-                          float * const * ys, bool * handled, const Q4KPrologue * pro);
+                          float * const * ys, bool * handled, const Q4KPrologue * pro, const ArFuse * fuse);
 
 // ---- natural-layout loading: assemble the packed-unit registers from GGUF blocks -----------------
 
@@ -396,6 +396,7 @@ static int took(const char * name, int st) {
     return st;
 }
 const char * matvec_last_kernel() { return t_last_kernel; }
+void matvec_note_kernel(const char * name) { t_last_kernel = name; }
 
 
 template <class U>
@@ -505,7 +506,7 @@ int matvec(cudaStream_t s, int dtype, int layout, const void * w, int64_t w_row_
         // the ring kernel (consecutive launches overlap; it declines unless the stream's last launch was such a matvec);
         // leftover rows take the row kernel
         bool handled = false;
-        const int st = matvec_q4k_ring_multi(s, 1, &w, &n, k, x, &y, &handled, nullptr);
+        const int st = matvec_q4k_ring_multi(s, 1, &w, &n, k, x, &y, &handled, nullptr, nullptr);
         if (st != ST_OK) return st;
         if (handled) {
             const int64_t full = (n / 16) * 16;

@@ -68,6 +68,15 @@ __device__ __forceinline__ void rg_cp_async16(uint32_t dst, const void * src) {
 __device__ __forceinline__ void rg_cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void rg_cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+// a value and its step tag as ONE 8-byte access (single-copy atomic: the reader sees both words of a store or neither)
+__device__ __forceinline__ void rg_st_tagged(uint2 * p, float v, uint32_t tag) {
+    asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(__float_as_uint(v)), "r"(tag) : "memory");
+}
+__device__ __forceinline__ uint2 rg_ld_tagged(const uint2 * p) {
+    uint2 v;
+    asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
+    return v;
+}
 __device__ __forceinline__ uint32_t rg_lds32(uint32_t addr) {
     uint32_t v;
     asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
@@ -195,8 +204,10 @@ __device__ __forceinline__ float rg_row_term(uint32_t dd, uint32_t f0, uint32_t 
 //   row   [K] float                            PRO == 2 only: the residual row before normalisation
 // NBW: 256-weight blocks of K per warp (compile time: their activations live in registers).
 // PRO: 0 x is given; 1 x = swiglu(pa, pb); 2 s = pa (+ pb), x = rms_norm(s) * pw (s, x written out by CTA 0 when asked).
-template <int NBW, int PRO>
-__global__ void __launch_bounds__(RG_THREADS, 2) matvec_q4k_ring(RingArgs p) {
+// AR: the launch is one rank's K shard of a product (single tensor): the row tiles' partial sums go through the all-reduce
+//     exchange `f` (see ArFuse) instead of straight to y, and y receives the sum over the ranks.
+template <int NBW, int PRO, bool AR>
+__global__ void __launch_bounds__(RG_THREADS, 2) matvec_q4k_ring(RingArgs p, ArFuse f) {
     extern __shared__ __align__(128) uint8_t smem[];
     float * red = reinterpret_cast<float *>(smem);
     uint8_t * hdr = smem + RG_WINDOW * RG_WARPS * 16 * 4;
@@ -254,6 +265,12 @@ __global__ void __launch_bounds__(RG_THREADS, 2) matvec_q4k_ring(RingArgs p) {
     while (issued < p.slots && issued < units) request();
 
     pdl_wait();   // everything below may depend on the predecessor's output
+
+    // fused all-reduce: the number of this fused launch (every rank counts alike) tags its values and picks one of the
+    // two receive buffers; the last CTA to finish advances the counter, which the next fused launch reads after its own
+    // dependency wait, i.e. after this grid has completed
+    uint32_t ar_step = 0;
+    if constexpr (AR) ar_step = __ldcg(f.step) + 1u;
 
     // ---- activations of this warp's K range -> registers ----
     RgBlockX bx[NBW];
@@ -411,12 +428,49 @@ __global__ void __launch_bounds__(RG_THREADS, 2) matvec_q4k_ring(RingArgs p) {
                 const float * src = red + (r * RG_WARPS + gq * p.wpt) * 16 + rw;
                 float v = 0.f;
                 for (int w = 0; w < p.wpt; ++w) v += src[w * 16];
-                int ti, lrt;
-                rg_locate(p, tile, ti, lrt);
-                p.y[ti][(int64_t) lrt * 16 + rw] = v;
+                if constexpr (AR) {
+                    // my partial, tagged with the step, into my slot on every rank: one 8-byte store each (plain stores over
+                    // NVLink, the local slot included); the tag travels with the value, so no fence and no separate flag
+                    const size_t at = ((size_t) (ar_step & 1u) * f.world + f.rank) * f.capacity + (size_t) tile * 16 + rw;
+                    for (int r = 0; r < f.world; ++r) rg_st_tagged(f.recv[r] + at, v, ar_step);
+                } else {
+                    int ti, lrt;
+                    rg_locate(p, tile, ti, lrt);
+                    p.y[ti][(int64_t) lrt * 16 + rw] = v;
+                }
             }
         }
         if (base + RG_WINDOW < cta_rounds) __syncthreads();   // the next window reuses `red`
+    }
+    if constexpr (AR) {
+        // the sum of the ranks' partials for this CTA's row tiles, in rank order (the same bits on every rank).  A value
+        // is there when its tag equals this step; the wait for it is bounded (about a second), a give-up raises the fault
+        // word and the sum goes on with what is there
+        const uint2 * mine = f.recv[f.rank] + (size_t) (ar_step & 1u) * f.world * f.capacity;
+        for (int idx = tid; idx < cta_rounds * p.groups * 16; idx += RG_THREADS) {
+            const int r = idx / (p.groups * 16), rem = idx - r * (p.groups * 16);
+            const int tile = blockIdx.x * p.groups + (rem >> 4) + r * tile_step;
+            if (tile < p.n_tiles) {
+                const int64_t at = (int64_t) tile * 16 + (rem & 15);
+                float acc = 0.f;
+                for (int q = 0; q < f.world; ++q) {
+                    const uint2 * src = mine + (size_t) q * f.capacity + at;
+                    uint2 got = rg_ld_tagged(src);
+                    for (uint32_t spins = 0; got.y != ar_step && spins < AR_WAIT_LIMIT; ++spins) {
+                        if (spins > 32) __nanosleep(50);
+                        got = rg_ld_tagged(src);
+                    }
+                    if (got.y != ar_step) atomicExch(f.fault, 100 + q);
+                    acc = q == 0 ? __uint_as_float(got.x) : __fadd_rn(acc, __uint_as_float(got.x));
+                }
+                p.y[0][at] = acc;
+            }
+        }
+        __syncthreads();
+        if (tid == 0 && atomicAdd(f.done, 1u) == gridDim.x - 1) {
+            *f.done = 0u;
+            *f.step = ar_step;
+        }
     }
 }
 
@@ -425,16 +479,18 @@ size_t ring_smem_bytes(int64_t k, int pro, int slots) {
 }
 
 template <int NBW>
-int launch_ring(cudaStream_t s, const RingArgs & a, int pro, size_t smem, int grid) {
-#define SM100_RING_CASE(P)                                                                                                             \
-    case P:                                                                                                                            \
-        SM100_CUDA(cudaFuncSetAttribute(matvec_q4k_ring<NBW, P>, cudaFuncAttributeMaxDynamicSharedMemorySize, 113 * 1024));          \
-        return launch(matvec_q4k_ring<NBW, P>, dim3((unsigned) grid), dim3(RG_THREADS), smem, s, a);
-    switch (pro) {
-        SM100_RING_CASE(0)
-        SM100_RING_CASE(1)
-        SM100_RING_CASE(2)
+int launch_ring(cudaStream_t s, const RingArgs & a, int pro, size_t smem, int grid, const ArFuse * fuse) {
+    const ArFuse f = fuse != nullptr ? *fuse : ArFuse{};
+#define SM100_RING_CASE(P, A)                                                                                                          \
+    if (pro == P && (fuse != nullptr) == A) {                                                                                          \
+        SM100_CUDA(cudaFuncSetAttribute(matvec_q4k_ring<NBW, P, A>, cudaFuncAttributeMaxDynamicSharedMemorySize, 113 * 1024));       \
+        return launch(matvec_q4k_ring<NBW, P, A>, dim3((unsigned) grid), dim3(RG_THREADS), smem, s, a, f);                           \
     }
+    SM100_RING_CASE(0, false)
+    SM100_RING_CASE(1, false)
+    SM100_RING_CASE(2, false)
+    SM100_RING_CASE(0, true)
+    SM100_RING_CASE(1, true)
 #undef SM100_RING_CASE
     return fail(ST_INVALID, "matvec (Q4_K ring): unknown prologue");
 }
@@ -443,8 +499,9 @@ int launch_ring(cudaStream_t s, const RingArgs & a, int pro, size_t smem, int gr
 
 // Q4_K packed matvec, one activation column, over the full 16-row tiles of up to three tensors that share the
 // activations; *handled = false when the shapes are left to the caller's other kernels.
+// fuse (optional): the launch is this rank's K shard, y receives the sum over the ranks (single tensor, whole row tiles).
 int matvec_q4k_ring_multi(cudaStream_t s, int count, const void * const * ws, const int64_t * ns, int64_t k, const float * x,
-                          float * const * ys, bool * handled, const Q4KPrologue * pro) {
+                          float * const * ys, bool * handled, const Q4KPrologue * pro, const ArFuse * fuse) {
     *handled = false;
     // SM100_Q4K_RING: 0 never; 1 (default) in runs of plain matvecs: a single tensor without prologue whose predecessor
     // on the stream is a matvec of the same kind; 2 wherever the shapes allow (tests).  The kernel pays off when launch
@@ -458,8 +515,13 @@ int matvec_q4k_ring_multi(cudaStream_t s, int count, const void * const * ws, co
     static const int enabled = [] { const char * e = getenv("SM100_Q4K_RING"); return e != nullptr ? atoi(e) : 1; }();
     if (!enabled) return ST_OK;
     const int tail = stream_tail(s);
-    if (enabled == 1 && (count != 1 || (pro != nullptr && pro->mode != 0) || tail == TAIL_OTHER)) return ST_OK;
-    const bool run_start = enabled == 1 && tail != TAIL_Q4K_RING;
+    if (fuse != nullptr) {
+        // only this kernel has the fused exchange: taken whenever the shapes allow, with the same care at the start of a run
+        if (count != 1 || (pro != nullptr && pro->mode == 2) || ns[0] % 16 != 0 || ns[0] > fuse->capacity || fuse->world < 2 || fuse->world > AR_MAX_RANKS) return ST_OK;
+    } else if (enabled == 1 && (count != 1 || (pro != nullptr && pro->mode != 0) || tail == TAIL_OTHER)) {
+        return ST_OK;
+    }
+    const bool run_start = (enabled == 1 || fuse != nullptr) && tail != TAIL_Q4K_RING;
     int mode = 0;
     if (pro != nullptr && pro->mode != 0) {
         mode = pro->mode;
@@ -513,12 +575,12 @@ int matvec_q4k_ring_multi(cudaStream_t s, int count, const void * const * ws, co
     const size_t smem = ring_smem_bytes(k, mode, a.slots);
     int st;
     if (run_start) thread_serialized(true);
-    if (nbw == 1) st = launch_ring<1>(s, a, mode, smem, (int) grid);
-    else if (nbw == 2) st = launch_ring<2>(s, a, mode, smem, (int) grid);
-    else st = launch_ring<3>(s, a, mode, smem, (int) grid);
+    if (nbw == 1) st = launch_ring<1>(s, a, mode, smem, (int) grid, fuse);
+    else if (nbw == 2) st = launch_ring<2>(s, a, mode, smem, (int) grid, fuse);
+    else st = launch_ring<3>(s, a, mode, smem, (int) grid, fuse);
     if (run_start) thread_serialized(false);
     *handled = st == ST_OK;
-    if (st == ST_OK && count == 1 && mode == 0) stream_tail_set(s, TAIL_Q4K_RING);
+    if (st == ST_OK && count == 1 && (mode == 0 || fuse != nullptr)) stream_tail_set(s, TAIL_Q4K_RING);
     return st;
 }
 

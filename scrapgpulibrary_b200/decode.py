@@ -153,6 +153,8 @@ class DecodeModel:
         self.allreduce = allreduce
         self.fuse = fuse   # fold RMS norm / SwiGLU into the Q4_K projections that consume them (one launch each)
         self.fuse_swiglu = fuse and os.environ.get("SM100_FUSE_SWIGLU", "1") != "0"
+        # the all-reduce of the row-parallel projections inside their matvec launch (sm100_mul_mat_allreduce)
+        self.fuse_exchange = fuse and os.environ.get("SM100_TP_FUSED", "1") != "0"
         c = cfg
         self.hq, self.hkv = c.heads // world, c.kv_heads // world
         self.q_dim, self.kv_dim, self.ffn = self.hq * c.head_dim, self.hkv * c.head_dim, c.ffn // world
@@ -289,6 +291,16 @@ class DecodeModel:
         capi.check(self.L.sm100_mul_mat_fused(self.stream, prologue, _dev(a), opt(b), opt(norm_w), self.cfg.eps, opt(sum_out), opt(x_out), n,
                                               dts, lays, wp, k, ns, yp), "mul_mat_fused")
 
+    def _mm_reduce(self, w: Weight, prologue: int, a: torch.Tensor, b, y: torch.Tensor) -> bool:
+        """A row-parallel projection with its all-reduce in one launch (sm100_mul_mat_allreduce) where the exchange is the
+        library's own (PeerAllReduce) and the tensor is packed Q4_K; False: the caller runs the separate launches."""
+        ctx = getattr(self.allreduce, "ctx", None)
+        if self.world == 1 or ctx is None or not self.fuse_exchange or w.dtype != Q4_K or w.n % 16 != 0:
+            return False
+        capi.check(self.L.sm100_mul_mat_allreduce(ctx, self.stream, prologue, _dev(a), _dev(b) if b is not None else None, w.dtype, 1, _dev(w.data),
+                                                  w.k, w.n, _dev(y)), "mul_mat_allreduce")
+        return True
+
     def _reduce(self, t: torch.Tensor):
         if self.world > 1:
             if self.allreduce is not None:
@@ -331,20 +343,24 @@ class DecodeModel:
             # only the row that head_post has just stored is newer than the preceding kernel: the older rows are requested early
             chk(L.sm100_attention_kvcache(s, _dev(self.q), _dev(lw["k_cache"]), _dev(lw["v_cache"]), None, 1, _dev(self.att), c.head_dim, c.head_dim,
                                           1, c.n_ctx, self.hq, self.hkv, 1, 0, _dev(self.pos), scale, 1), "attention")
-            self._mm(lw["wo"], self.att, self.proj)
-            self._reduce(self.proj)
+            if not self._mm_reduce(lw["wo"], 0, self.att, None, self.proj):
+                self._mm(lw["wo"], self.att, self.proj)
+                self._reduce(self.proj)
             if self.fuse:
                 self._mm_fused(2, x_cur, self.proj, lw["ffn_norm"], x_alt, None, [lw["wgate"], lw["wup"]], [self.gate, self.up])
                 x_cur, x_alt = x_alt, x_cur
             else:
                 chk(L.sm100_rms_norm(s, _dev(x_cur), _dev(self.proj), _dev(lw["ffn_norm"]), _dev(x_cur), _dev(self.xn), c.hidden, 1, c.eps), "add_rms_norm")
                 self._mm_multi([lw["wgate"], lw["wup"]], self.xn, [self.gate, self.up])
-            if self.fuse_swiglu and lw["wdown"].dtype == Q4_K:
+            if self.fuse_swiglu and self._mm_reduce(lw["wdown"], 1, self.gate, self.up, self.proj):
+                pass
+            elif self.fuse_swiglu and lw["wdown"].dtype == Q4_K:
                 self._mm_fused(1, self.gate, self.up, None, None, None, [lw["wdown"]], [self.proj])
+                self._reduce(self.proj)
             else:
                 chk(L.sm100_swiglu(s, _dev(self.gate), _dev(self.up), _dev(self.act), self.ffn), "swiglu")
                 self._mm(lw["wdown"], self.act, self.proj)
-            self._reduce(self.proj)
+                self._reduce(self.proj)
         # (the next token starts by overwriting self.x with its embedding, so it does not matter where the stream ended)
         chk(L.sm100_rms_norm(s, _dev(x_cur), _dev(self.proj), _dev(self.out_norm), _dev(x_cur), _dev(self.xn), c.hidden, 1, c.eps), "out_norm")
         if self.head is not None:
