@@ -88,6 +88,8 @@ SM100_API size_t sm100_allreduce_area_bytes(int world, int capacity_floats);
 SM100_API int sm100_allreduce_create(int rank, int world, int capacity_floats, void * const * areas, sm100_allreduce_t * out);
 SM100_API int sm100_allreduce_sum(sm100_allreduce_t ctx, sm100_stream_t s, float * x, int n);
 SM100_API int sm100_allreduce_fault(sm100_allreduce_t ctx, int * fault_out);
+/* polls (each followed by a sleep of about 0.1 us) before a wait for a peer gives up; default 1 << 22, about a second */
+SM100_API int sm100_allreduce_set_wait_limit(sm100_allreduce_t ctx, uint32_t polls);
 SM100_API int sm100_allreduce_destroy(sm100_allreduce_t ctx);
 /* y[N] = sum over the ranks of W_r[K_r, N] . x_r[K_r]: the K-sharded ("row-parallel") product of tensor parallelism with
  * its all-reduce, M = 1; every rank calls it with its own shard and ends up with the same bits in y.  prologue 0: a is x;

@@ -40,6 +40,8 @@ def build_example() -> bool:
 
 OPS_TESTS = os.path.join(_HERE, "_ref", "ops_tests")
 ATTENTION_TESTS = os.path.join(_HERE, "_ref", "attention_tests")
+OPS_TESTS_REMOTE = os.path.join(_HERE, "_ref", "ops_tests_remote")
+DEVICE_SERVER = os.path.join(_HERE, "_ref", "scrapgpu-device-server")
 
 
 def build_device_tests() -> bool:
@@ -48,6 +50,14 @@ def build_device_tests() -> bool:
     if os.path.isfile(os.path.join(REFERENCE_DIR, "tests", "ops", "ops_tests.cpp")):
         subprocess.run(["make", "-C", _HERE, "device_tests", f"REF={REFERENCE_DIR}"], check=True, capture_output=True)
     return os.path.exists(OPS_TESTS) and os.path.exists(ATTENTION_TESTS)
+
+
+def build_remote_tests() -> bool:
+    """The reference's device server and its ops suite with the remote switch (src/backends/remote/server.cpp, client.cpp),
+    compiled unchanged against the plugin; True if both binaries exist afterwards."""
+    if os.path.isfile(os.path.join(REFERENCE_DIR, "src", "backends", "remote", "server.cpp")):
+        subprocess.run(["make", "-C", _HERE, "remote_tests", f"REF={REFERENCE_DIR}"], check=True, capture_output=True)
+    return os.path.exists(OPS_TESTS_REMOTE) and os.path.exists(DEVICE_SERVER)
 
 
 def available() -> bool:

@@ -29,6 +29,7 @@ struct ArArgs {
     int * fault;                      // local: set when a wait ran out
     float * x;                        // in / out
     int n, capacity, rank, world;
+    uint32_t wait_limit;              // polls before the wait for a peer gives up
 };
 
 __device__ __forceinline__ void st_release_sys(uint32_t * p, uint32_t v) { asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory"); }
@@ -65,7 +66,7 @@ __global__ void __launch_bounds__(AR_THREADS, 1) allreduce_kernel(ArArgs a) {
     if (tid < a.world) {
         const uint32_t * f = a.flags[a.rank] + buf * a.world + tid;
         bool ok = false;
-        for (uint32_t i = 0; i < AR_WAIT_LIMIT; ++i) {
+        for (uint32_t i = 0; i < a.wait_limit; ++i) {
             if (ld_acquire_sys(f) == step) { ok = true; break; }
             __nanosleep(100);
         }
@@ -155,6 +156,8 @@ int sm100_allreduce_create(int rank, int world, int capacity, void * const * are
     for (int p = 0; p < world; ++p) c->fuse.recv[p] = (uint2 *) ((uint8_t *) areas[p] + fused);
     c->fuse.step = (uint32_t *) ((uint8_t *) areas[rank] + fused + 2 * data);
     c->fuse.done = c->fuse.step + 16;
+    c->args.wait_limit = AR_WAIT_LIMIT;
+    c->fuse.wait_limit = AR_WAIT_LIMIT;
     c->fuse.fault = c->args.fault;
     c->fuse.capacity = capacity;
     c->fuse.rank = rank;
@@ -175,6 +178,14 @@ int sm100_allreduce_sum(sm100_allreduce_t ctx, sm100_stream_t s, float * x, int 
     a.x = x;
     a.n = n;
     return launch(allreduce_kernel, dim3(1), dim3(AR_THREADS), 0, (cudaStream_t) s, a);
+}
+
+int sm100_allreduce_set_wait_limit(sm100_allreduce_t ctx, uint32_t polls) {
+    ArContext * c = (ArContext *) ctx;
+    if (c == nullptr || polls == 0) return fail(ST_INVALID, "allreduce_set_wait_limit: null context or zero polls");
+    c->args.wait_limit = polls;
+    c->fuse.wait_limit = polls;
+    return ST_OK;
 }
 
 int sm100_allreduce_fault(sm100_allreduce_t ctx, int * fault_out) {

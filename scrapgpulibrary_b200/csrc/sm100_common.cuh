@@ -73,6 +73,7 @@ struct ArFuse {
     uint32_t * done;                  // local: CTAs of the running fused launch that have finished (the last one advances `step`)
     int * fault;                      // local: set when a wait ran out
     int rank, world, capacity;
+    uint32_t wait_limit;              // polls before a wait gives up (AR_WAIT_LIMIT unless the context was told otherwise)
 };
 bool allreduce_fuse_args(void * ctx, ArFuse * out);   // false when ctx is null
 

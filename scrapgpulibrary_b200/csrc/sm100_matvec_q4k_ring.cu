@@ -456,7 +456,7 @@ __global__ void __launch_bounds__(RG_THREADS, 2) matvec_q4k_ring(RingArgs p, ArF
                 for (int q = 0; q < f.world; ++q) {
                     const uint2 * src = mine + (size_t) q * f.capacity + at;
                     uint2 got = rg_ld_tagged(src);
-                    for (uint32_t spins = 0; got.y != ar_step && spins < AR_WAIT_LIMIT; ++spins) {
+                    for (uint32_t spins = 0; got.y != ar_step && spins < f.wait_limit; ++spins) {
                         if (spins > 32) __nanosleep(50);
                         got = rg_ld_tagged(src);
                     }

@@ -386,3 +386,36 @@ def test_attention_kvcache_entry(sm100, stream):
     assert st == 2
     for b in (kb, vb, ob):
         b.free()
+
+
+def test_allreduce_wait_is_bounded_and_reported(sm100, stream):
+    """A rank whose peer never arrives: the kernel's wait for the peer's flag is bounded, the kernel returns, the give-up is
+    reported through sm100_allreduce_fault and the device stays usable.  One GPU plays both ranks' memory (two areas on the
+    same device); only rank 0 calls, so the flag of rank 1 is one that nothing sets.  The wait limit is shortened for the
+    test (sm100_allreduce_set_wait_limit); the default is about a second."""
+    L = sm100.lib()
+    world, cap = 2, 1024
+    nbytes = int(L.sm100_allreduce_area_bytes(world, cap))
+    areas = [sm100.Buffer(nbytes) for _ in range(world)]
+    for a in areas:
+        a.fill(stream, 0)
+    stream.sync()
+    ptrs = (C.c_void_p * world)(*[a.ptr for a in areas])
+    ctx = C.c_void_p()
+    sm100.check(L.sm100_allreduce_create(0, world, cap, ptrs, C.byref(ctx)), "allreduce_create")
+    sm100.check(L.sm100_allreduce_set_wait_limit(ctx, 2000), "set_wait_limit")
+    x = np.arange(cap, dtype=np.float32)
+    xb = U.to_device(sm100, stream, x)
+    sm100.check(L.sm100_allreduce_sum(ctx, stream.handle, C.c_void_p(xb.ptr), cap), "allreduce_sum")
+    stream.sync()                                   # returns: the wait ran out instead of spinning
+    fault = C.c_int(0)
+    sm100.check(L.sm100_allreduce_fault(ctx, C.byref(fault)), "allreduce_fault")
+    assert fault.value != 0
+    # the context is intact: an ordinary kernel runs and gives the right answer
+    yb = sm100.Buffer(4 * cap)
+    sm100.check(L.sm100_add(stream.handle, C.c_void_p(xb.ptr), C.c_void_p(xb.ptr), C.c_void_p(yb.ptr), cap), "add")
+    stream.sync()
+    assert np.array_equal(yb.download(stream, np.float32, cap), 2 * xb.download(stream, np.float32, cap))
+    L.sm100_allreduce_destroy(ctx)
+    for b in areas + [xb, yb]:
+        b.free()

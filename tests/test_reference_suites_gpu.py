@@ -26,10 +26,10 @@ HOT_PATH = ("ADD", "SUB", "MUL", "DIV", "SCALE", "CLAMP", "SQR", "SQRT", "GLU", 
 OUTSIDE = ("MUL_MAT_ID", "ADD_ID", "SSM_CONV", "CONCAT", "PAD", "SUM_ROWS", "ARGSORT", "TOP_K", "tensor_copy")
 
 
-def run(binary):
+def run(binary, backend="opencl11"):
     if not os.path.exists(binary):
-        pytest.fail(f"{binary} is missing on the GPU box: run `make -C oracle device_tests` where the reference is checked out")
-    env = dict(os.environ, SCRAPGPU_TEST_BACKEND="opencl11")
+        pytest.fail(f"{binary} is missing on the GPU box: run `make -C oracle device_tests remote_tests` where the reference is checked out")
+    env = dict(os.environ, SCRAPGPU_TEST_BACKEND=backend)
     r = subprocess.run([binary], capture_output=True, text=True, timeout=600, env=env)
     print(r.stdout)
     print(r.stderr)
@@ -57,3 +57,21 @@ def test_reference_attention_tests_pass_on_cuda_sm100():
     out = run(refapi.ATTENTION_TESTS)
     assert "(cuda_sm100)" in out, out[:400]
     assert "4 attention runs" in out, out[-400:]
+
+
+def test_reference_ops_tests_pass_through_the_reference_device_server():
+    """The reference's scrapgpu-device-server (src/backends/remote/server.cpp) and the client side of its remote backend
+    (client.cpp), both compiled unchanged (`make -C oracle remote_tests`): the ops suite spawns the server, which registers
+    "opencl11" - answered by cuda_sm100 through the shim - and runs every case through the socket and shared-memory transport
+    (ops_tests.cpp:1249-1287).  The same pass / skip picture as in process."""
+    if not os.path.exists(refapi.DEVICE_SERVER):
+        pytest.fail(f"{refapi.DEVICE_SERVER} is missing on the GPU box: run `make -C oracle remote_tests` where the reference is checked out")
+    out = run(refapi.OPS_TESTS_REMOTE, backend="remote")
+    assert "FAIL" not in out
+    m = re.search(r"(\d+) op runs, (\d+) skipped", out)
+    assert m, out[-400:]
+    assert int(m.group(1)) >= 60, out[-400:]
+    skipped_names = [ln.split()[1].split("/")[0] for ln in out.splitlines() if ln.startswith("SKIP ")]
+    for name in skipped_names:
+        assert name not in HOT_PATH, f"a decode hot-path op was skipped through the device server: {name}"
+    print(f"ops_tests through scrapgpu-device-server: {m.group(1)} op runs, {m.group(2)} skipped")
