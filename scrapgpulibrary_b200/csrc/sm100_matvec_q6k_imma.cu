@@ -29,6 +29,7 @@ struct SqArgs {
     int64_t x_off, s_off, d_off;            // byte offsets of the bit-pair, scale and d planes (nibble plane at 0)
     const float * x;
     float * y;
+    int64_t ldx, ldy;   // floats between consecutive activation / result columns (multi-column kernel)
     int n_tiles;        // full 16-row tiles
     int blocks;         // K / 256
     int units;          // K / 64
@@ -48,7 +49,7 @@ struct SqPiece {
 };
 
 // activations -> 16-bit integers per 16-element group (shared by the kernels below); the caller synchronises the CTA
-__device__ __forceinline__ void sq_quantize_x(const SqArgs & p, uint32_t * xq, float2 * xs, int ngroups, int tid) {
+__device__ __forceinline__ void sq_quantize_x(const float * x, uint32_t * xq, float2 * xs, int ngroups, int tid) {
     // activations -> 16-bit integers per 16-element group.  One item = 4 consecutive elements; the 4 items of a
     // group sit in 4 consecutive lanes.
     if (tid < 8) xq[ngroups * 8 + tid] = 0u;
@@ -59,7 +60,7 @@ __device__ __forceinline__ void sq_quantize_x(const SqArgs & p, uint32_t * xq, f
 #pragma unroll
         for (int i = 0; i < BATCH; ++i) {
             const int it = base + i * SQ_THREADS + tid;
-            if (it < ngroups * 4) xv[i] = __ldcg(reinterpret_cast<const float4 *>(p.x) + it);   // coherent: the producer may still be running when this kernel starts
+            if (it < ngroups * 4) xv[i] = __ldcg(reinterpret_cast<const float4 *>(x) + it);   // coherent: the producer may still be running when this kernel starts
         }
 #pragma unroll
         for (int i = 0; i < BATCH; ++i) {
@@ -87,16 +88,21 @@ __device__ __forceinline__ void sq_quantize_x(const SqArgs & p, uint32_t * xq, f
     }
 }
 
-// Shared memory of one CTA:
+// Shared memory of one CTA, per activation column (M of them, one after the other):
 //   xq   [K/16][2 planes][16 B]   quantized activations, natural order inside a group; 32 zero bytes follow
 //   xs   [K/16] (float s, int 32 * sum of the group's integers)
-//   red  [warp][16 rows] float    partial outputs of the warps of one row tile
+// then
+//   red  [column][group][warp][16 rows] float    partial outputs of the warps of one row tile
+// M > 1: the weights of a step are assembled once and multiplied with every column in turn (two MMAs and the scale terms
+// per column), which is what makes a batch cheaper than one launch per column: the 6-bit assembly is the expensive part.
+template <int M>
 __global__ void __launch_bounds__(SQ_THREADS, 1) matvec_q6k_imma(SqArgs p) {
     extern __shared__ __align__(16) uint8_t smem[];
     const int ngroups = p.units * 4;
+    const uint32_t col_bytes = (uint32_t) ngroups * 40u + 32u;   // one column's xq, zero bytes and xs
     uint32_t * xq = reinterpret_cast<uint32_t *>(smem);
     float2 * xs = reinterpret_cast<float2 *>(smem + (size_t) ngroups * 32 + 32);
-    float * red = reinterpret_cast<float *>(xs + ngroups);
+    float * red = reinterpret_cast<float *>(smem + (size_t) M * col_bytes);
 
     const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
     const int group = wid / SQ_WARPS, warp = wid % SQ_WARPS;
@@ -126,7 +132,10 @@ __global__ void __launch_bounds__(SQ_THREADS, 1) matvec_q6k_imma(SqArgs p) {
 
     pdl_wait();
 
-    sq_quantize_x(p, xq, xs, ngroups, tid);
+#pragma unroll 1
+    for (int m = 0; m < M; ++m)
+        sq_quantize_x(p.x + m * p.ldx, reinterpret_cast<uint32_t *>(smem + (size_t) m * col_bytes),
+                      reinterpret_cast<float2 *>(smem + (size_t) m * col_bytes + (size_t) ngroups * 32 + 32), ngroups, tid);
     __syncthreads();
     pdl_launch_dependents();
 
@@ -135,12 +144,14 @@ __global__ void __launch_bounds__(SQ_THREADS, 1) matvec_q6k_imma(SqArgs p) {
     const uint32_t xq0 = (uint32_t) __cvta_generic_to_shared(xq);
     const uint32_t zero_addr = xq0 + (uint32_t) ngroups * 32u;
     const uint32_t lane_off = (uint32_t) t * 64u + (uint32_t) (g & 1) * 16u;   // group +2t of the unit, plane g & 1
-    float * my_red = red + group * (SQ_WARPS * 16);
+    float * my_red = red + group * (SQ_WARPS * 16);   // column m: + m * SQ_GROUPS * SQ_WARPS * 16
     const int gtid = tid - group * (SQ_WARPS * 32);
 
     // every group runs the same number of rounds so that the CTA-wide barriers match
     for (int round = blockIdx.x * SQ_GROUPS; round < p.n_tiles; round += rt_step) {
-        float acc0 = 0.f, acc1 = 0.f;   // rows g and g + 8, this lane's groups
+        float acc0[M], acc1[M];   // rows g and g + 8, this lane's groups, per column
+#pragma unroll
+        for (int m = 0; m < M; ++m) acc0[m] = acc1[m] = 0.f;
         for (; rt < p.n_tiles && unit < u_end; ++unit) {
             int nrt = rt, nunit = unit + 1;
             if (nunit >= u_end) { nrt = rt + rt_step; nunit = u_begin; }
@@ -149,11 +160,6 @@ __global__ void __launch_bounds__(SQ_THREADS, 1) matvec_q6k_imma(SqArgs p) {
             // group index of (block, unit, t): 16 block + 8 (unit / 2) + (unit & 1) + 2 t
             const int u = unit & 3;
             const uint32_t grp0 = (uint32_t) (unit >> 2) * 16u + (uint32_t) (u >> 1) * 8u + (uint32_t) (u & 1);
-            uint4 bx = make_uint4(0u, 0u, 0u, 0u);
-            {
-                const uint32_t addr = live ? xq0 + grp0 * 32u + lane_off : zero_addr;
-                asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(bx.x), "=r"(bx.y), "=r"(bx.z), "=r"(bx.w) : "r"(addr));
-            }
             const uint32_t n0[4] = {cur0.nib.x, cur0.nib.y, cur0.nib.z, cur0.nib.w}, n1[4] = {cur1.nib.x, cur1.nib.y, cur1.nib.z, cur1.nib.w};
             const uint32_t h0[4] = {cur0.hb.x, cur0.hb.y, cur0.hb.z, cur0.hb.w}, h1[4] = {cur1.hb.x, cur1.hb.y, cur1.hb.z, cur1.hb.w};
             uint32_t q0[4], q1[4];
@@ -162,33 +168,47 @@ __global__ void __launch_bounds__(SQ_THREADS, 1) matvec_q6k_imma(SqArgs p) {
                 q0[i] = ((n0[i] >> nib_shift) & 0x0F0F0F0Fu) | (((h0[i] >> hb_shift) & 0x03030303u) << 4);
                 q1[i] = ((n1[i] >> nib_shift) & 0x0F0F0F0Fu) | (((h1[i] >> hb_shift) & 0x03030303u) << 4);
             }
-            int c[4] = {0, 0, 0, 0};
-            sq_imma(c, q0[0], q1[0], q0[1], q1[1], bx.x, bx.y);
-            sq_imma(c, q0[2], q1[2], q0[3], q1[3], bx.z, bx.w);
-            // columns 2t, 2t + 1 of this lane: (H, L) of group t
-            const float2 sq = xs[grp0 + 2 * t];
-            const int sx32 = __float_as_int(sq.y);
             const int s0 = ((int) (cur0.sc << sc_shift)) >> 24, s1 = ((int) (cur1.sc << sc_shift)) >> 24;   // signed byte t
-            const float v0 = (float) (c[0] * 256 + c[1] - sx32), v1 = (float) (c[2] * 256 + c[3] - sx32);
-            acc0 = fmaf(d0 * (float) s0 * sq.x, v0, acc0);
-            acc1 = fmaf(d1 * (float) s1 * sq.x, v1, acc1);
+            const float ds0 = d0 * (float) s0, ds1 = d1 * (float) s1;
+#pragma unroll
+            for (int m = 0; m < M; ++m) {
+                uint4 bx = make_uint4(0u, 0u, 0u, 0u);
+                {
+                    const uint32_t addr = live ? xq0 + (uint32_t) m * col_bytes + grp0 * 32u + lane_off : zero_addr;
+                    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(bx.x), "=r"(bx.y), "=r"(bx.z), "=r"(bx.w) : "r"(addr));
+                }
+                int c[4] = {0, 0, 0, 0};
+                sq_imma(c, q0[0], q1[0], q0[1], q1[1], bx.x, bx.y);
+                sq_imma(c, q0[2], q1[2], q0[3], q1[3], bx.z, bx.w);
+                // columns 2t, 2t + 1 of this lane: (H, L) of group t
+                const float2 sq = *reinterpret_cast<const float2 *>(reinterpret_cast<const uint8_t *>(xs + grp0 + 2 * t) + (size_t) m * col_bytes);
+                const int sx32 = __float_as_int(sq.y);
+                const float v0 = (float) (c[0] * 256 + c[1] - sx32), v1 = (float) (c[2] * 256 + c[3] - sx32);
+                acc0[m] = fmaf(ds0 * sq.x, v0, acc0[m]);
+                acc1[m] = fmaf(ds1 * sq.x, v1, acc1[m]);
+            }
             cur0 = nxt0;
             cur1 = nxt1;
         }
-        acc0 += __shfl_xor_sync(0xffffffffu, acc0, 1);
-        acc0 += __shfl_xor_sync(0xffffffffu, acc0, 2);
-        acc1 += __shfl_xor_sync(0xffffffffu, acc1, 1);
-        acc1 += __shfl_xor_sync(0xffffffffu, acc1, 2);
-        if (t == 0) {
-            my_red[warp * 16 + g] = acc0;
-            my_red[warp * 16 + g + 8] = acc1;
+#pragma unroll
+        for (int m = 0; m < M; ++m) {
+            float a0 = acc0[m], a1 = acc1[m];
+            a0 += __shfl_xor_sync(0xffffffffu, a0, 1);
+            a0 += __shfl_xor_sync(0xffffffffu, a0, 2);
+            a1 += __shfl_xor_sync(0xffffffffu, a1, 1);
+            a1 += __shfl_xor_sync(0xffffffffu, a1, 2);
+            if (t == 0) {
+                my_red[m * (SQ_GROUPS * SQ_WARPS * 16) + warp * 16 + g] = a0;
+                my_red[m * (SQ_GROUPS * SQ_WARPS * 16) + warp * 16 + g + 8] = a1;
+            }
         }
         __syncthreads();
-        if (gtid < 16 && rt < p.n_tiles) {
+        if (gtid < 16 * M && rt < p.n_tiles) {
+            const int m = gtid >> 4, row = gtid & 15;
             float v = 0.f;
 #pragma unroll
-            for (int w = 0; w < SQ_WARPS; ++w) v += my_red[w * 16 + gtid];
-            p.y[(int64_t) rt * 16 + gtid] = v;
+            for (int w = 0; w < SQ_WARPS; ++w) v += my_red[m * (SQ_GROUPS * SQ_WARPS * 16) + w * 16 + row];
+            p.y[m * p.ldy + (int64_t) rt * 16 + row] = v;
         }
         __syncthreads();
         rt += rt_step;
@@ -245,7 +265,7 @@ __global__ void __launch_bounds__(SQ_THREADS, 1) matvec_q6k_imma_deep(SqArgs p) 
 
     pdl_wait();
 
-    sq_quantize_x(p, xq, xs, ngroups, tid);
+    sq_quantize_x(p.x, xq, xs, ngroups, tid);
     __syncthreads();
     pdl_launch_dependents();
 
@@ -318,7 +338,7 @@ __global__ void __launch_bounds__(SQ_THREADS, 1) matvec_q6k_imma_deep(SqArgs p) 
     }
 }
 
-size_t sq_smem_bytes(int units) { return (size_t) units * 4 * 32 + 32 + (size_t) units * 4 * 8 + (size_t) SQ_WARPS * SQ_GROUPS * 16 * 4; }
+size_t sq_smem_bytes(int units, int cols = 1) { return (size_t) cols * ((size_t) units * 4 * 40 + 32) + (size_t) cols * SQ_WARPS * SQ_GROUPS * 16 * 4; }
 
 }  // namespace
 
@@ -340,6 +360,8 @@ int matvec_q6k_imma_tiles(cudaStream_t s, const void * w, int64_t k, int64_t n, 
     a.d_off = P.off[3];
     a.x = x;
     a.y = y;
+    a.ldx = k;
+    a.ldy = n;
     a.n_tiles = (int) tiles;
     a.blocks = (int) (k / 256);
     a.units = units;
@@ -353,11 +375,61 @@ int matvec_q6k_imma_tiles(cudaStream_t s, const void * w, int64_t k, int64_t n, 
         if (smem > 48 * 1024) SM100_CUDA(cudaFuncSetAttribute(matvec_q6k_imma_deep, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
         st = launch(matvec_q6k_imma_deep, dim3((unsigned) grid), dim3(SQ_THREADS), smem, s, a);
     } else {
-        if (smem > 48 * 1024) SM100_CUDA(cudaFuncSetAttribute(matvec_q6k_imma, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
-        st = launch(matvec_q6k_imma, dim3((unsigned) grid), dim3(SQ_THREADS), smem, s, a);
+        if (smem > 48 * 1024) SM100_CUDA(cudaFuncSetAttribute(matvec_q6k_imma<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+        st = launch(matvec_q6k_imma<1>, dim3((unsigned) grid), dim3(SQ_THREADS), smem, s, a);
     }
     *handled = st == ST_OK;
     return st;
+}
+
+// The same for 2..8 activation columns: the columns are served in launches of 8, 4, 2 or 1 (as many as fit the shared
+// memory: a column of K = 12288 takes 30 KB), each launch assembling the weights once for all its columns.
+template <int M>
+static int launch_q6k_cols(cudaStream_t s, SqArgs a, int grid) {
+    const size_t smem = sq_smem_bytes(a.units, M);
+    if (smem > 48 * 1024) SM100_CUDA(cudaFuncSetAttribute(matvec_q6k_imma<M>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+    return launch(matvec_q6k_imma<M>, dim3((unsigned) grid), dim3(SQ_THREADS), smem, s, a);
+}
+
+int matvec_q6k_imma_cols(cudaStream_t s, const void * w, int64_t k, int64_t n, const float * x, int64_t ldx, int m, float * y, int64_t ldy, bool * handled) {
+    *handled = false;
+    const int64_t tiles = n / 16;
+    if (m < 2 || m > 8 || tiles == 0 || k % 256 != 0 || k > (int64_t) 1 << 18 || tiles > INT32_MAX / 2) return ST_OK;
+    if (((uintptr_t) w & 15) != 0 || ((uintptr_t) x & 15) != 0 || ldx % 4 != 0) return ST_OK;
+    const int units = (int) (k / 64);
+    if (sq_smem_bytes(units, 1) > (size_t) 227 * 1024) return ST_OK;
+    const Planes P = planes_for(DT_Q6_K, n, k);
+    SqArgs a;
+    a.w = (const uint8_t *) w;
+    a.x_off = P.off[1];
+    a.s_off = P.off[2];
+    a.d_off = P.off[3];
+    a.ldx = ldx;
+    a.ldy = ldy;
+    a.n_tiles = (int) tiles;
+    a.blocks = (int) (k / 256);
+    a.units = units;
+    a.units_per_warp = (units + SQ_WARPS - 1) / SQ_WARPS;
+    int64_t grid = sm_count();
+    const int64_t rounds = (tiles + SQ_GROUPS - 1) / SQ_GROUPS;
+    if (grid > rounds) grid = rounds;
+    for (int done = 0; done < m;) {
+        int take = 8;
+        while (take > m - done || sq_smem_bytes(units, take) > (size_t) 227 * 1024) take /= 2;
+        a.x = x + (int64_t) done * ldx;
+        a.y = y + (int64_t) done * ldy;
+        int st;
+        switch (take) {
+            case 8: st = launch_q6k_cols<8>(s, a, (int) grid); break;
+            case 4: st = launch_q6k_cols<4>(s, a, (int) grid); break;
+            case 2: st = launch_q6k_cols<2>(s, a, (int) grid); break;
+            default: st = launch_q6k_cols<1>(s, a, (int) grid); break;
+        }
+        if (st != ST_OK) return st;
+        done += take;
+    }
+    *handled = true;
+    return ST_OK;
 }
 
 }  // namespace sm100

@@ -90,11 +90,11 @@ def _kernel(sm100):
 # environment that switches kernel families off -> the "dtype:kernel" names that must then have served some case
 FORCED = [
     ({}, ["q4_k:matvec_q4k_imma", "q4_k:matvec_q4k_imma+rows", "q4_k:matvec_q4k_imma_cols+rows",
-          "q6_k:matvec_q6k_imma", "q4_0:matvec_b32_imma", "q8_0:matvec_b32_imma", "q6_k:matvec_per_column", "q4_0:matvec_per_column",
+          "q6_k:matvec_q6k_imma", "q4_0:matvec_b32_imma", "q8_0:matvec_b32_imma", "q6_k:matvec_q6k_imma_cols", "q4_0:matvec_per_column",
           "q6_k:matvec_rows", "q8_0:matvec_rows"]),
     ({"SM100_Q4K_RING": "2"}, ["q4_k:matvec_q4k_ring", "q4_k:matvec_q4k_ring+rows", "q4_k:matvec_q4k_imma"]),   # 2: the ring kernel wherever its shapes allow
     ({"SM100_Q4K_RING": "0"}, ["q4_k:matvec_q4k_imma", "q4_k:matvec_q4k_imma+rows"]),
-    ({"SM100_Q6K_IMMA": "0", "SM100_B32_IMMA": "0"}, ["q6_k:matvec_wide", "q4_0:matvec_wide", "q8_0:matvec_wide", "q6_k:matvec_rows"]),
+    ({"SM100_Q6K_IMMA": "0", "SM100_B32_IMMA": "0"}, ["q6_k:matvec_wide", "q4_0:matvec_wide", "q8_0:matvec_wide", "q6_k:matvec_rows", "q6_k:matvec_per_column"]),
     ({"SM100_Q4K_IMMA": "0"}, ["q4_k:matvec_q4k_mma", "q4_k:matvec_q4k_mma+rows"]),   # (switches the ring kernel off too: same arithmetic family)
     ({"SM100_Q4K_IMMA": "0", "SM100_Q4K_MMA": "0", "SM100_Q6K_IMMA": "0", "SM100_B32_IMMA": "0", "SM100_MV_WIDE": "0"},
      ["q4_k:matvec_stream", "q6_k:matvec_stream", "q4_0:matvec_stream", "q8_0:matvec_stream", "q4_k:matvec_rows", "q8_0:matvec_rows", "q8_0:matvec_per_column"]),
