@@ -65,6 +65,16 @@ SCRAPGPU_API scrapgpu_status scrapgpu_cuda_sm100_group_free(scrapgpu_cuda_sm100_
  * for a peer gives up and the next scrapgpu_cuda_sm100_group_status reports BACKEND_ERROR. */
 SCRAPGPU_API scrapgpu_status scrapgpu_cuda_sm100_group_all_reduce(scrapgpu_cuda_sm100_group_t * group, scrapgpu_stream_t * const * streams,
                                                                  const scrapgpu_tensor_desc * tensors);
+/* The row-parallel product of tensor parallelism with its all-reduce: outputs[i] (F32 [N], the same N everywhere) on every
+ * device receives the sum over the devices of weights[i] [K_i, N] . inputs[i] [K_i], the same bits everywhere.  weights[i] is
+ * device i's K shard (scrapgpu_cuda_sm100_shard with split_dim 0, uploaded with scrapgpu_cuda_sm100_upload_view).  For packed
+ * Q4_K shards with whole 16-row tiles the exchange happens inside the matvec launch of every device (peer stores tagged
+ * with the step number, bounded waits: see scrapgpu_cuda_sm100_group_status); other tensors run MUL_MAT and
+ * scrapgpu_cuda_sm100_group_all_reduce one after the other.  In the core's terms this is MUL_MAT on every device followed
+ * by the tensor copies and ADDs that src/core/transport.cpp:53-146 would bounce through the host. */
+SCRAPGPU_API scrapgpu_status scrapgpu_cuda_sm100_group_mul_mat_all_reduce(scrapgpu_cuda_sm100_group_t * group, scrapgpu_stream_t * const * streams,
+                                                                         const scrapgpu_tensor_desc * weights, const scrapgpu_tensor_desc * inputs,
+                                                                         const scrapgpu_tensor_desc * outputs);
 SCRAPGPU_API scrapgpu_status scrapgpu_cuda_sm100_group_status(scrapgpu_cuda_sm100_group_t * group);
 
 /* Shard arithmetic for tensor parallelism, on descriptors only (no device needed).  `full` describes a natural-layout

@@ -2142,6 +2142,53 @@ SCRAPGPU_API scrapgpu_status scrapgpu_cuda_sm100_group_all_reduce(scrapgpu_cuda_
     });
 }
 
+SCRAPGPU_API scrapgpu_status scrapgpu_cuda_sm100_group_mul_mat_all_reduce(scrapgpu_cuda_sm100_group_t * group, scrapgpu_stream_t * const * streams,
+                                                                         const scrapgpu_tensor_desc * weights, const scrapgpu_tensor_desc * inputs,
+                                                                         const scrapgpu_tensor_desc * outputs) {
+    return guard([&]() -> scrapgpu_status {
+        Group * g = as_group(group);
+        if (g == nullptr || streams == nullptr || weights == nullptr || inputs == nullptr || outputs == nullptr) return invalid("group, streams or tensors is null");
+        const size_t n = g->devices.size();
+        std::vector<Ref> w(n), x(n), y(n);
+        std::vector<Stream *> ss(n);
+        int64_t rows = 0;
+        for (size_t i = 0; i < n; ++i) {
+            ss[i] = as_stream(streams[i]);
+            if (ss[i] == nullptr || ss[i]->dev != g->devices[i]) return invalid("streams[i] must be a stream of the group's device i");
+            scrapgpu_status st = resolve(ss[i], weights[i], w[i]);
+            if (st == SCRAPGPU_STATUS_OK) st = resolve(ss[i], inputs[i], x[i]);
+            if (st == SCRAPGPU_STATUS_OK) st = resolve(ss[i], outputs[i], y[i]);
+            if (st != SCRAPGPU_STATUS_OK) return st;
+            int64_t xe = 0, ye = 0;
+            if (!f32(x[i].d) || !contiguous(x[i].d) || !elements(x[i].d, xe) || !f32(y[i].d) || !contiguous(y[i].d) || !elements(y[i].d, ye))
+                return unsupported("the activation and result vectors must be contiguous F32");
+            if (ne(w[i].d, 2) * ne(w[i].d, 3) != 1 || !is_quant(w[i].d.dtype)) return unsupported("the K shards must be 2-D quantized weight tensors");
+            if (xe != ne(w[i].d, 0) || ye != ne(w[i].d, 1)) return invalid("shapes: x has K_i elements, y has N, W_i is [K_i, N]");
+            if (i == 0) rows = ye;
+            if (ye != rows) return invalid("every device's shard must have the same number of rows");
+            if (w[i].d.layout != SCRAPGPU_LAYOUT_R32 && w[i].d.nb[1] != (uint64_t) (ne(w[i].d, 0) / (int64_t) block_size(w[i].d.dtype)) * type_size(w[i].d.dtype))
+                return unsupported("natural-layout shards must have contiguous rows");
+        }
+        if (rows <= 0 || rows % 4 != 0 || (size_t) rows > g->capacity) return invalid("N must be a positive multiple of 4 within the group's max_elements");
+        for (size_t i = 0; i < n; ++i) {
+            scrapgpu_status st = from_sm100(sm100_set_device(g->devices[i]->ordinal));
+            if (st != SCRAPGPU_STATUS_OK) return st;
+            Serialized scope(fresh(ss[i], weights[i]));
+            if (n == 1) {
+                st = from_sm100(sm100_mul_mat(ss[i]->cuda, w[i].d.dtype, w[i].d.layout == SCRAPGPU_LAYOUT_R32 ? 1 : 0, w[i].base(), 0, ne(w[i].d, 0), rows,
+                                              (const float *) x[i].base(), ne(w[i].d, 0), 1, (float *) y[i].base(), rows));
+            } else {
+                st = from_sm100(sm100_mul_mat_allreduce(g->ranks[i], ss[i]->cuda, 0, (const float *) x[i].base(), nullptr, w[i].d.dtype,
+                                                        w[i].d.layout == SCRAPGPU_LAYOUT_R32 ? 1 : 0, w[i].base(), ne(w[i].d, 0), rows, (float *) y[i].base()));
+            }
+            if (st != SCRAPGPU_STATUS_OK) return enqueue_result(ss[i], st);
+            ++ss[i]->epoch;
+            wrote(ss[i], outputs[i]);
+        }
+        return SCRAPGPU_STATUS_OK;
+    });
+}
+
 SCRAPGPU_API scrapgpu_status scrapgpu_cuda_sm100_group_status(scrapgpu_cuda_sm100_group_t * group) {
     return guard([&]() -> scrapgpu_status {
         Group * g = as_group(group);

@@ -124,3 +124,51 @@ def test_sharded_mul_mat_with_group_all_reduce(env):
             assert sgref.nmse(g, want) <= 1e-6
     assert P.scrapgpu_cuda_sm100_group_free(group) == abi.OK
     assert P.scrapgpu_cuda_sm100_group_free(group) == abi.INVALID_ARGUMENT
+
+
+@pytest.mark.parametrize("n", [256, 272])
+def test_group_mul_mat_all_reduce(env, n):
+    """scrapgpu_cuda_sm100_group_mul_mat_all_reduce: the K-sharded product and its all-reduce as one call.  N = 256 (whole
+    16-row tiles of packed Q4_K) takes the launch with the exchange inside on every device, N = 272 with a Q6_K weight the
+    separate launches; either way every device holds the full product, the same bits everywhere, NMSE 1e-6 of the oracle,
+    over several calls in a row.  With one device the call is a plain MUL_MAT."""
+    P, sessions = env
+    world = len(sessions)
+    dtype = abi.Q4_K if n == 256 else abi.Q6_K
+    udt = U.Q4_K if n == 256 else U.Q6_K
+    k = 2048
+    wq = U.quantize(udt, U.seeded_weights(27 + n, n, k))
+    image = np.ascontiguousarray(wq).ravel()
+    x = U.seeded_acts(28, 1, k)
+    want = sgref.mul_mat(udt, wq, k, x)[0]
+    full = abi.tensor_desc(dtype, [k, n])
+    devs = (C.c_void_p * world)(*[s.device.value for s in sessions])
+    group = C.c_void_p()
+    assert P.scrapgpu_cuda_sm100_group_create(devs, world, 4096, C.byref(group)) == abi.OK, refapi.last_error()
+    P.scrapgpu_cuda_sm100_group_mul_mat_all_reduce.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
+    ws, xs, ys = [], [], []
+    kl = k // world
+    for r, s in enumerate(sessions):
+        view = abi.TensorDesc()
+        assert P.scrapgpu_cuda_sm100_shard(C.byref(full), 0, r, world, C.byref(view)) == abi.OK
+        wt = s.tensor(dtype, [kl, n], layout=abi.LAYOUT_R32)
+        assert P.scrapgpu_cuda_sm100_upload_view(s.stream, C.byref(wt.desc), image.ctypes.data_as(C.c_void_p), C.byref(view)) == abi.OK, refapi.last_error()
+        ws.append(wt)
+        xs.append(s.tensor(abi.F32, [kl]).upload(x[0, r * kl:(r + 1) * kl]))
+        ys.append(s.tensor(abi.F32, [n]).upload(np.zeros(n, np.float32)))
+        s.sync()
+    streams = (C.c_void_p * world)(*[s.stream.value for s in sessions])
+    wd = (abi.TensorDesc * world)(*[t.desc for t in ws])
+    xd = (abi.TensorDesc * world)(*[t.desc for t in xs])
+    yd = (abi.TensorDesc * world)(*[t.desc for t in ys])
+    for rep in range(3):
+        assert P.scrapgpu_cuda_sm100_group_mul_mat_all_reduce(group, streams, wd, xd, yd) == abi.OK, refapi.last_error()
+    got = []
+    for s, t in zip(sessions, ys):
+        s.sync()
+        got.append(t.download(np.float32, n))
+    assert P.scrapgpu_cuda_sm100_group_status(group) == abi.OK
+    for g in got:
+        assert np.array_equal(g.view(np.uint32), got[0].view(np.uint32))
+        assert sgref.nmse(g, want) <= 1e-6
+    assert P.scrapgpu_cuda_sm100_group_free(group) == abi.OK
