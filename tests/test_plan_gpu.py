@@ -190,6 +190,9 @@ def test_plan_without_use_counts_keeps_every_intermediate(both):
         got = glayer.read(glayer.outputs + glayer.elidable)
         for name in glayer.outputs + glayer.elidable:
             assert sgref.nmse(got[name], per_op[name]) <= 1e-6, name
-        for name in ("t1", "x1", "x2", "act"):
+        for name in ("t1", "x1", "x2"):
             assert np.array_equal(got[name].view(np.uint32), per_op[name].view(np.uint32)), name
+        # (act = SwiGLU(gate, up): node by node `up` is the second of two consecutive MUL_MATs and comes from the ring
+        # kernel, in the plan gate and up are one fused launch of matvec_q4k_imma: same block sums, other order of addition)
+        assert sgref.nmse(got["act"], per_op["act"]) <= 1e-10
     refapi.check(L.scrapgpu_plan_free(plan), "plan_free")
