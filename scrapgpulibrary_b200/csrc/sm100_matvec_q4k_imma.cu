@@ -524,6 +524,8 @@ __global__ void __launch_bounds__(256) q4k_quantize_cols(const float * x, int64_
     pdl_wait();
     pdl_launch_dependents();
     const int items = pairs * 16;
+    // (scale, sum) pairs: one row of `pairs` 16-byte entries per token, padded by one entry so that the entries of the four
+    // tokens a warp reads together lie in different shared-memory banks
     float2 * xs2 = reinterpret_cast<float2 *>(img + (size_t) mt * pairs * 32);
     for (int it0 = blockIdx.x * blockDim.x + threadIdx.x; it0 < mt * items; it0 += gridDim.x * blockDim.x) {   // whole warps: items is a multiple of 64
         const int m = it0 / items, it = it0 - m * items;
@@ -548,9 +550,11 @@ __global__ void __launch_bounds__(256) q4k_quantize_cols(const float * x, int64_
         const size_t word = ((size_t) m * pairs + (sb >> 1)) * 32 + (q & 3) * 4 + (sb & 1) * 2 + (q >> 2);
         img[word] = hp;
         img[word + 16] = lp;
-        if (q == 0) xs2[(size_t) m * pairs * 2 + sb] = make_float2(s, sum);
+        if (q == 0) xs2[(size_t) m * (pairs + 1) * 2 + sb] = make_float2(s, sum);
     }
 }
+
+constexpr int IQ_SC_ROWS = 16 * 10;   // float2 entries of one warp's decoded scales: 16 rows of 8, padded to 10
 
 template <int MG>
 __global__ void __launch_bounds__(IQ_THREADS, 1) matvec_q4k_imma_cols(IqArgs p, int m_tokens, const uint32_t * img) {
@@ -562,9 +566,10 @@ __global__ void __launch_bounds__(IQ_THREADS, 1) matvec_q4k_imma_cols(IqArgs p, 
     const uint32_t xq_bytes = (uint32_t) MT * p.pairs * 128;
     uint32_t * xq = reinterpret_cast<uint32_t *>(smem);
     float2 * xs2 = reinterpret_cast<float2 *>(smem + xq_bytes);
-    float * red = reinterpret_cast<float *>(smem + xq_bytes + (uint32_t) MT * p.pairs * 16);   // [warp][16 rows][8 tokens]
-    float2 * scs = reinterpret_cast<float2 *>(red + IQ_WARPS * IQ_GROUPS * 128);               // [warp][16 rows][8 sub-blocks] (d sc, dmin m)
-    uint64_t * bars = reinterpret_cast<uint64_t *>(scs + IQ_WARPS * IQ_GROUPS * 128);   // [warp][R], then one for the activation image
+    float * red = reinterpret_cast<float *>(smem + xq_bytes + (uint32_t) MT * (p.pairs + 1) * 16);   // [warp][16 rows][8 tokens]
+    // [warp][16 rows][8 sub-blocks] (d sc, dmin m), rows 80 bytes apart: the eight rows a warp reads together cover all banks once
+    float2 * scs = reinterpret_cast<float2 *>(red + IQ_WARPS * IQ_GROUPS * 128);
+    uint64_t * bars = reinterpret_cast<uint64_t *>(scs + IQ_WARPS * IQ_GROUPS * IQ_SC_ROWS);   // [warp][R], then one for the activation image
     uint8_t * hdr = reinterpret_cast<uint8_t *>(bars + IQ_WARPS * IQ_GROUPS * R + 1);
     hdr += (128 - (iq_smem_addr(hdr) & 127)) & 127;
     uint8_t * ring = hdr + (uint32_t) IQ_WARPS * IQ_GROUPS * R * HDR_BYTES;
@@ -611,7 +616,7 @@ __global__ void __launch_bounds__(IQ_THREADS, 1) matvec_q4k_imma_cols(IqArgs p, 
 
     // the quantized activation columns (made by q4k_quantize_cols, the predecessor on the stream): one bulk copy
     if (tid == 0) {
-        const uint32_t bytes = xq_bytes + (uint32_t) MT * p.pairs * 16;
+        const uint32_t bytes = xq_bytes + (uint32_t) MT * (p.pairs + 1) * 16;
         iq_bar_expect_tx(img_bar, bytes);
         iq_bulk_g2s(iq_smem_addr(xq), img, bytes, img_bar);
     }
@@ -625,7 +630,7 @@ __global__ void __launch_bounds__(IQ_THREADS, 1) matvec_q4k_imma_cols(IqArgs p, 
     // lane (g, t) supplies B column g = plane (g & 1) of token (g >> 1) of each column group, and owns token t
     const uint32_t xq0 = iq_smem_addr(xq);
     const uint32_t xs0 = iq_smem_addr(xs2);
-    float2 * my_sc = scs + wid * 128;
+    float2 * my_sc = scs + wid * IQ_SC_ROWS;
     float * my_red = red + group * (IQ_WARPS * 128);
     const int gtid = tid - group * (IQ_WARPS * 32);
 
@@ -653,7 +658,7 @@ __global__ void __launch_bounds__(IQ_THREADS, 1) matvec_q4k_imma_cols(IqArgs p, 
                 const float2 df = __half22float2(*reinterpret_cast<const __half2 *>(&h.x));
                 const uint32_t f0 = lane < 16 ? h.y : __funnelshift_r(h.z, h.w, 16);            // field 0 or 2
                 const uint32_t f1 = lane < 16 ? __funnelshift_r(h.y, h.z, 24) : h.w >> 8;         // field 1 or 3
-                float2 * dst = my_sc + (lane & 15) * 8 + (lane >> 4) * 4;
+                float2 * dst = my_sc + (lane & 15) * 10 + (lane >> 4) * 4;
                 dst[0] = make_float2(df.x * (float) (f0 & 63u), df.y * (float) ((f0 >> 6) & 63u));
                 dst[1] = make_float2(df.x * (float) ((f0 >> 12) & 63u), df.y * (float) ((f0 >> 18) & 63u));
                 dst[2] = make_float2(df.x * (float) (f1 & 63u), df.y * (float) ((f1 >> 6) & 63u));
@@ -664,8 +669,10 @@ __global__ void __launch_bounds__(IQ_THREADS, 1) matvec_q4k_imma_cols(IqArgs p, 
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
                 const uint4 wt = iq_lds128(tiles_lane + j * 512);   // x, y: row g k-halves 0, 1; z, w: row g + 8
-                const float2 s_lo0 = my_sc[g * 8 + 2 * j], s_hi0 = my_sc[g * 8 + 2 * j + 1];             // row g: (d sc, dmin m)
-                const float2 s_lo1 = my_sc[(g + 8) * 8 + 2 * j], s_hi1 = my_sc[(g + 8) * 8 + 2 * j + 1];   // row g + 8
+                const float4 sc0 = *reinterpret_cast<const float4 *>(my_sc + g * 10 + 2 * j);         // row g: (d sc, dmin m) of the pair's two sub-blocks
+                const float4 sc1 = *reinterpret_cast<const float4 *>(my_sc + (g + 8) * 10 + 2 * j);   // row g + 8
+                const float2 s_lo0 = make_float2(sc0.x, sc0.y), s_hi0 = make_float2(sc0.z, sc0.w);
+                const float2 s_lo1 = make_float2(sc1.x, sc1.y), s_hi1 = make_float2(sc1.z, sc1.w);
 #pragma unroll
                 for (int cg = 0; cg < MG; ++cg) {
                     const uint32_t tok_b = (uint32_t) (cg * 4 + (g >> 1)), tok_c = (uint32_t) (cg * 4 + t);
@@ -674,7 +681,7 @@ __global__ void __launch_bounds__(IQ_THREADS, 1) matvec_q4k_imma_cols(IqArgs p, 
                     imma_16832_zero(clo, wt.x & 0x0F0F0F0Fu, wt.z & 0x0F0F0F0Fu, wt.y & 0x0F0F0F0Fu, wt.w & 0x0F0F0F0Fu, bf.x, bf.y);
                     imma_16832_zero(chi, wt.x & 0xF0F0F0F0u, wt.z & 0xF0F0F0F0u, wt.y & 0xF0F0F0F0u, wt.w & 0xF0F0F0F0u, bf.z, bf.w);
                     // (s, sum x) of the pair's two sub-blocks for the token this lane owns
-                    const uint4 sqb = iq_lds128(xs0 + (tok_c * p.pairs + (uint32_t) (blk * 4 + j)) * 16u);
+                    const uint4 sqb = iq_lds128(xs0 + (tok_c * (uint32_t) (p.pairs + 1) + (uint32_t) (blk * 4 + j)) * 16u);
                     const float s_l = __uint_as_float(sqb.x), x_l = __uint_as_float(sqb.y), s_h = __uint_as_float(sqb.z), x_h = __uint_as_float(sqb.w);
                     const float vl0 = (float) (clo[0] * 256 + clo[1]), vl1 = (float) (clo[2] * 256 + clo[3]);
                     const float vh0 = (float) ((chi[0] * 256 + chi[1]) >> 4), vh1 = (float) ((chi[2] * 256 + chi[3]) >> 4);
@@ -716,7 +723,7 @@ __global__ void __launch_bounds__(IQ_THREADS, 1) matvec_q4k_imma_cols(IqArgs p, 
 }
 
 size_t iq_cols_smem_bytes(int pairs, int mt, int ring) {
-    return (size_t) mt * pairs * (128 + 16) + (size_t) IQ_WARPS * IQ_GROUPS * 128 * 4 + (size_t) IQ_WARPS * IQ_GROUPS * 128 * 8 +
+    return (size_t) mt * (pairs * 128 + (pairs + 1) * 16) + (size_t) IQ_WARPS * IQ_GROUPS * 128 * 4 + (size_t) IQ_WARPS * IQ_GROUPS * IQ_SC_ROWS * 8 +
            (size_t) IQ_WARPS * IQ_GROUPS * ring * 8 + 8 + 128 + (size_t) IQ_WARPS * IQ_GROUPS * ring * (256 + 2048);
 }
 
@@ -866,7 +873,7 @@ int matvec_q4k_imma_cols_tiles(cudaStream_t s, const void * w, int64_t k, int64_
     g_iq_launched[current_device()].store(true, std::memory_order_relaxed);
     const int mt = 4 * mg;
     void * img = nullptr;
-    int st = device_scratch(2, (size_t) mt * pairs * 144, &img);
+    int st = device_scratch(2, (size_t) mt * (pairs * 128 + (pairs + 1) * 16), &img);
     if (st != ST_OK) return st;
     const int q_items = mt * pairs * 16;
     st = launch(q4k_quantize_cols, dim3((unsigned) ((q_items + 255) / 256)), dim3(256), 0, s, x, ldx, (int) m, mt, pairs, (uint32_t *) img);
