@@ -259,6 +259,20 @@ SM100_API int sm100_head_post(sm100_stream_t s, float * q, float * k, const floa
                               int64_t head_dim, int64_t q_heads, int64_t kv_heads, int64_t cache_rows, float eps,
                               float freq_base, int neox);
 
+/* sm100_head_post followed by sm100_attention_kvcache (one query, causal over the cache up to positions[0], fresh_keys 1) for
+ * one decode token - in ONE launch where the shapes allow (NEOX rotation, head_dim 128 or 256, 1 / 2 / 4 / 8 query heads per KV
+ * head, a cache short enough for the single-launch merge): every warp of the attention kernel normalises and rotates the
+ * query heads it uses, the CTA whose split ends at the newest position does the same for the new key, stores it and the new
+ * value into the caches and reads them back like any other row.  Other shapes run the two launches.  Same arguments as
+ * sm100_head_post plus the attention output [head_dim, q_heads] and the score scale; unlike sm100_head_post it leaves q and
+ * k_new as they were in the single-launch form (nothing else may rely on them being rotated in place).  Values: those of the
+ * two separate calls up to the order of the double-precision additions in the norms' sums of squares. */
+SM100_API int sm100_attention_decode(sm100_stream_t s, float * q, float * k_new, const float * v_new, const float * q_norm_w,
+                                     const float * k_norm_w, const int32_t * positions, const float * table,
+                                     int32_t table_first_position, int32_t table_positions, float * k_cache, float * v_cache,
+                                     float * out, int64_t head_dim, int64_t q_heads, int64_t kv_heads, int64_t cache_rows, float eps,
+                                     float freq_base, int neox, float scale);
+
 /* TOP_K with k = 1 (ops.cpp:1189-1228): index of the maximum, lowest index on ties */
 SM100_API int sm100_argmax(sm100_stream_t s, const float * x, int64_t n, int32_t * out);
 /* fused decode attention, the values of scrapgpu_scaled_dot_product_attention

@@ -70,6 +70,7 @@ def lib() -> C.CDLL:
         L.sm100_hostpipe_mul_mat_many.argtypes = [vp, i32, vp]
         L.sm100_hostpipe_sync.argtypes = [vp]
         L.sm100_head_post.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, vp, vp, i64, i64, i64, i64, C.c_float, C.c_float, i32]
+        L.sm100_attention_decode.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, vp, vp, vp, i64, i64, i64, i64, C.c_float, C.c_float, i32, C.c_float]
         L.sm100_ipc_handle_bytes.restype = sz
         L.sm100_ipc_export.argtypes = [vp, vp]
         L.sm100_ipc_open.argtypes = [vp, pv]

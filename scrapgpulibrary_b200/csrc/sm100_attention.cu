@@ -33,6 +33,14 @@ struct AttnArgs {
     // requested before the dependency wait.  -1: no such promise, everything is read after the wait.
     int fresh_keys;
     float scale;
+    // Decode step with the new token's head post-processing in the same launch (attn_fast_kernel<.., POST = true>): q is the
+    // RAW query projection; every warp applies the per-head RMS norm (when q_w is set) and the NEOX rotation to the query heads
+    // it uses, and the CTA whose split ends at the newest position does the same for the new key (k_new, k_w), stores it and
+    // the new value (v_new) into row positions[0] of the caches (k, v) and then reads them like any other row.
+    const float * k_new; const float * v_new; const float * q_w; const float * k_w;
+    const float * table;            // (cos, sin) per (position - table_first, pair), or null: computed from theta_scale
+    int64_t table_first; int table_n;
+    float eps, theta_scale;
 };
 
 // scratch layout per (q, h, split): [m, l, o[dv]]
@@ -321,7 +329,75 @@ __global__ void attn_combine_kernel(AttnArgs a) {
 // the CTA that delivers the last partial of a (query, KV head) merges the splits right away (counter in global
 // memory, reset for the next call), so no second launch is needed.
 
-template <int G, int D4>
+// RMS norm (optional) and NEOX rotation of one head of 128 D4 elements held by a warp as float4 per lane and 128-element
+// slab (elements 4 lane .. 4 lane + 3 of slab i), with the arithmetic of head_post_kernel (sm100_ops.cu): the values of
+// RMS_NORM_MUL (src/core/ref/ops.cpp:466-492) and ROPE (:530-634) for one token.  The rotation pairs element j with j + D/2:
+// for D = 128 that is the lane 16 away, for D = 256 the other slab of the same lane.
+template <int D4>
+__device__ __forceinline__ void post_head(const float * src, const float * w, const AttnArgs & a, int32_t pos, int lane, float4 (&out)[D4]) {
+    constexpr int D = 128 * D4, HP = D / 2;
+    float4 x[D4];
+    double sum = 0.0;
+#pragma unroll
+    for (int i = 0; i < D4; ++i) {
+        x[i] = __ldcg(reinterpret_cast<const float4 *>(src) + lane + 32 * i);
+        sum += ((double) x[i].x * (double) x[i].x + (double) x[i].y * (double) x[i].y) + ((double) x[i].z * (double) x[i].z + (double) x[i].w * (double) x[i].w);
+    }
+    if (w != nullptr) {
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+        const float scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn((float) (sum * (1.0 / (double) D)), a.eps)));   // D is a power of two: the same double as sum / D
+#pragma unroll
+        for (int i = 0; i < D4; ++i) {
+            const float4 g = __ldg(reinterpret_cast<const float4 *>(w) + lane + 32 * i);
+            x[i] = make_float4(__fmul_rn(__fmul_rn(x[i].x, scale), g.x), __fmul_rn(__fmul_rn(x[i].y, scale), g.y),
+                               __fmul_rn(__fmul_rn(x[i].z, scale), g.z), __fmul_rn(__fmul_rn(x[i].w, scale), g.w));
+        }
+    }
+    // pair index of this lane's component c: j0 + c
+    const int j0 = D4 == 1 ? 4 * (lane & 15) : 4 * lane;
+    const int64_t rel = (int64_t) pos - a.table_first;
+    const bool in_table = a.table != nullptr && rel >= 0 && rel < a.table_n;
+    float cs[4], sn[4];
+    if (in_table) {
+        const float4 t0 = __ldg(reinterpret_cast<const float4 *>(a.table + (rel * HP + j0) * 2));
+        const float4 t1 = __ldg(reinterpret_cast<const float4 *>(a.table + (rel * HP + j0) * 2) + 1);
+        cs[0] = t0.x; sn[0] = t0.y; cs[1] = t0.z; sn[1] = t0.w; cs[2] = t1.x; sn[2] = t1.y; cs[3] = t1.z; sn[3] = t1.w;
+    } else {
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            float theta = (float) pos;
+            for (int q = 0; q < j0 + c; ++q) theta = __fmul_rn(theta, a.theta_scale);
+            cs[c] = cosf(theta);
+            sn[c] = sinf(theta);
+        }
+    }
+    if (D4 == 1) {
+        const bool lower = lane < 16;
+        const float4 p = make_float4(__shfl_xor_sync(0xffffffffu, x[0].x, 16), __shfl_xor_sync(0xffffffffu, x[0].y, 16),
+                                     __shfl_xor_sync(0xffffffffu, x[0].z, 16), __shfl_xor_sync(0xffffffffu, x[0].w, 16));
+        const float mine[4] = {x[0].x, x[0].y, x[0].z, x[0].w}, other[4] = {p.x, p.y, p.z, p.w};
+        float y[4];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            const float v0 = lower ? mine[c] : other[c], v1 = lower ? other[c] : mine[c];
+            y[c] = lower ? __fsub_rn(__fmul_rn(v0, cs[c]), __fmul_rn(v1, sn[c])) : __fadd_rn(__fmul_rn(v0, sn[c]), __fmul_rn(v1, cs[c]));
+        }
+        out[0] = make_float4(y[0], y[1], y[2], y[3]);
+    } else {
+        const float v0[4] = {x[0].x, x[0].y, x[0].z, x[0].w}, v1[4] = {x[D4 - 1].x, x[D4 - 1].y, x[D4 - 1].z, x[D4 - 1].w};
+        float y0[4], y1[4];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            y0[c] = __fsub_rn(__fmul_rn(v0[c], cs[c]), __fmul_rn(v1[c], sn[c]));
+            y1[c] = __fadd_rn(__fmul_rn(v0[c], sn[c]), __fmul_rn(v1[c], cs[c]));
+        }
+        out[0] = make_float4(y0[0], y0[1], y0[2], y0[3]);
+        out[D4 - 1] = make_float4(y1[0], y1[1], y1[2], y1[3]);
+    }
+}
+
+template <int G, int D4, bool POST>
 __global__ void __launch_bounds__(ATT_THREADS) attn_fast_kernel(AttnArgs a) {
     constexpr int D = 128 * D4;
     extern __shared__ __align__(16) float smem[];   // [8 warps][G][ATT_HDR + D]
@@ -329,6 +405,7 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_fast_kernel(AttnArgs a) {
     __shared__ float s_w[ATT_MAX_SPLITS];
     __shared__ float s_red[2][32];
     __shared__ int s_last;
+    __shared__ float4 s_q[POST ? G * D4 * 32 : 1];   // POST: the group's query heads after norm and rotation
     const int split = blockIdx.x;
     const int64_t hk = blockIdx.y, q = blockIdx.z;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -366,14 +443,43 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_fast_kernel(AttnArgs a) {
             }
         }
         pdl_wait();
+        if constexpr (POST) {
+            // The new token's heads, once per CTA: warp t takes query head t of this KV head's group (normalised and rotated
+            // into shared memory, from where every warp fetches all G of them); in the CTA whose split ends at the newest
+            // position two more tasks make and store the new key and copy the new value into the caches (CTA-uniform
+            // condition), where the loop below finds them like any other row.
+            const int32_t pos = a.positions[0];
+            const bool owns_newest = n_vis > 0 && n_vis - 1 >= k0 && n_vis - 1 < k1 && pos >= 0 && pos < a.nk;
+            const int tasks = G + (owns_newest ? 2 : 0);
+            for (int task = warp; task < tasks; task += NW) {
+                if (task < G) {
+                    float4 qn[D4];
+                    post_head<D4>(a.q + (hk * G + task) * D, a.q_w, a, pos, lane, qn);
+#pragma unroll
+                    for (int i = 0; i < D4; ++i) s_q[(task * D4 + i) * 32 + lane] = qn[i];
+                } else if (task == G) {
+                    float4 kn[D4];
+                    post_head<D4>(a.k_new + hk * D, a.k_w, a, pos, lane, kn);
+                    float4 * dst = reinterpret_cast<float4 *>(const_cast<float *>(a.k) + (hk * a.nk + pos) * D);
+#pragma unroll
+                    for (int i = 0; i < D4; ++i) dst[lane + 32 * i] = kn[i];
+                } else {
+                    const float4 * src = reinterpret_cast<const float4 *>(a.v_new + hk * D);
+                    float4 * dst = reinterpret_cast<float4 *>(const_cast<float *>(a.v) + (hk * a.nk + pos) * D);
+#pragma unroll
+                    for (int i = 0; i < D4; ++i) dst[lane + 32 * i] = __ldcg(src + lane + 32 * i);
+                }
+            }
+            __syncthreads();
+        }
 #pragma unroll
         for (int j = 0; j < NKB; ++j) {
             const bool in = kb + j < count && kb + j >= stable;
             if (in) {
 #pragma unroll
                 for (int i = 0; i < D4; ++i) {
-                    kv[j][i] = kbase[(int64_t) (kb + j) * (D / 4) + 32 * i];
-                    vv[j][i] = vbase[(int64_t) (kb + j) * (D / 4) + 32 * i];
+                    kv[j][i] = POST ? __ldcg(kbase + (int64_t) (kb + j) * (D / 4) + 32 * i) : kbase[(int64_t) (kb + j) * (D / 4) + 32 * i];
+                    vv[j][i] = POST ? __ldcg(vbase + (int64_t) (kb + j) * (D / 4) + 32 * i) : vbase[(int64_t) (kb + j) * (D / 4) + 32 * i];
                 }
             }
         }
@@ -381,10 +487,17 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_fast_kernel(AttnArgs a) {
     pdl_launch_dependents();
 
     float4 qr[G][D4];
+    if constexpr (POST) {
 #pragma unroll
-    for (int g = 0; g < G; ++g)
+        for (int g = 0; g < G; ++g)
 #pragma unroll
-        for (int i = 0; i < D4; ++i) qr[g][i] = reinterpret_cast<const float4 *>(a.q + ((hk * G + g) * a.nq + q) * D)[lane + 32 * i];
+            for (int i = 0; i < D4; ++i) qr[g][i] = s_q[(g * D4 + i) * 32 + lane];
+    } else {
+#pragma unroll
+        for (int g = 0; g < G; ++g)
+#pragma unroll
+            for (int i = 0; i < D4; ++i) qr[g][i] = reinterpret_cast<const float4 *>(a.q + ((hk * G + g) * a.nq + q) * D)[lane + 32 * i];
+    }
 
     float m[G], l[G];
     float4 o[G][D4];
@@ -404,8 +517,9 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_fast_kernel(AttnArgs a) {
                 const bool in = kb + j < count;
 #pragma unroll
                 for (int i = 0; i < D4; ++i) {
-                    kv[j][i] = in ? kbase[(int64_t) (kb + j) * (D / 4) + 32 * i] : make_float4(0.f, 0.f, 0.f, 0.f);
-                    vv[j][i] = in ? vbase[(int64_t) (kb + j) * (D / 4) + 32 * i] : make_float4(0.f, 0.f, 0.f, 0.f);
+                    // (POST: the newest row was stored by this CTA a moment ago: read past L1)
+                    kv[j][i] = !in ? make_float4(0.f, 0.f, 0.f, 0.f) : POST ? __ldcg(kbase + (int64_t) (kb + j) * (D / 4) + 32 * i) : kbase[(int64_t) (kb + j) * (D / 4) + 32 * i];
+                    vv[j][i] = !in ? make_float4(0.f, 0.f, 0.f, 0.f) : POST ? __ldcg(vbase + (int64_t) (kb + j) * (D / 4) + 32 * i) : vbase[(int64_t) (kb + j) * (D / 4) + 32 * i];
                 }
             }
         }
@@ -561,8 +675,12 @@ constexpr int ATT_COUNTER_SLOTS = 16384;   // ints at the start of the scratch: 
 template <int G, int D4>
 static int launch_fast(cudaStream_t s, const AttnArgs & a) {
     const size_t smem = (size_t) (ATT_THREADS / 32) * G * (128 * D4 + ATT_HDR) * sizeof(float);
-    if (smem > 48 * 1024) SM100_CUDA(cudaFuncSetAttribute(attn_fast_kernel<G, D4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024));
-    return launch(attn_fast_kernel<G, D4>, dim3((unsigned) a.splits, (unsigned) a.hkv, (unsigned) a.nq), dim3(ATT_THREADS), smem, s, a);
+    if (a.k_new != nullptr) {
+        if (smem > 48 * 1024) SM100_CUDA(cudaFuncSetAttribute(attn_fast_kernel<G, D4, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024));
+        return launch(attn_fast_kernel<G, D4, true>, dim3((unsigned) a.splits, (unsigned) a.hkv, (unsigned) a.nq), dim3(ATT_THREADS), smem, s, a);
+    }
+    if (smem > 48 * 1024) SM100_CUDA(cudaFuncSetAttribute(attn_fast_kernel<G, D4, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024));
+    return launch(attn_fast_kernel<G, D4, false>, dim3((unsigned) a.splits, (unsigned) a.hkv, (unsigned) a.nq), dim3(ATT_THREADS), smem, s, a);
 }
 
 // `scratch` is the raw scratch area: counters first, partials behind them
@@ -663,6 +781,45 @@ extern "C" int sm100_attention_kvcache(sm100_stream_t s, const float * q, const 
 }
 
 
+
+extern "C" int sm100_attention_decode(sm100_stream_t s, float * q, float * k_new, const float * v_new, const float * q_norm_w, const float * k_norm_w,
+                                      const int32_t * positions, const float * table, int32_t table_first, int32_t table_n, float * k_cache,
+                                      float * v_cache, float * out, int64_t head_dim, int64_t q_heads, int64_t kv_heads, int64_t cache_rows, float eps,
+                                      float freq_base, int neox, float scale) {
+    using namespace sm100;
+    if (q == nullptr || k_new == nullptr || v_new == nullptr || positions == nullptr || k_cache == nullptr || v_cache == nullptr || out == nullptr)
+        return fail(ST_INVALID, "attention_decode: null pointer");
+    if (head_dim <= 0 || q_heads <= 0 || kv_heads <= 0 || cache_rows <= 0 || q_heads % kv_heads != 0) return fail(ST_INVALID, "attention_decode: bad shape");
+    const int64_t group = q_heads / kv_heads;
+    static const int fuse = [] { const char * e = getenv("SM100_ATTN_POST"); return e != nullptr ? atoi(e) : 1; }();
+    const bool aligned = (((uintptr_t) q | (uintptr_t) k_new | (uintptr_t) v_new | (uintptr_t) q_norm_w | (uintptr_t) k_norm_w | (uintptr_t) table |
+                           (uintptr_t) k_cache | (uintptr_t) v_cache | (uintptr_t) out) & 15) == 0;
+    if (fuse && neox && aligned && (head_dim == 128 || head_dim == 256) && (group == 1 || group == 2 || group == 4 || group == 8)) {
+        AttnArgs a = {};
+        a.q = q; a.k = k_cache; a.v = v_cache; a.out = out; a.positions = positions;
+        a.d = head_dim; a.dv = head_dim; a.nq = 1; a.nk = cache_rows; a.hq = q_heads; a.hkv = kv_heads; a.offset = 0;
+        a.mask_heads = 1;
+        a.causal = 1; a.scale = scale;
+        a.fresh_keys = 1;
+        a.k_new = k_new; a.v_new = v_new; a.q_w = q_norm_w; a.k_w = k_norm_w; a.table = table; a.table_first = table_first; a.table_n = (int) table_n;
+        a.eps = eps;
+        a.theta_scale = powf(freq_base, -2.0f / (float) head_dim);
+        int st = attention_check(a);
+        if (st != ST_OK) return st;
+        attention_plan(a);
+        if ((int64_t) a.nq * a.hkv <= ATT_COUNTER_SLOTS && a.splits <= ATT_FUSED_SPLITS) {   // the single-launch form of the fast kernel
+            float * ws = nullptr;
+            st = workspace(attention_scratch_bytes(a), &ws);
+            if (st != ST_OK) return st;
+            return attention_launch((cudaStream_t) s, a, ws);
+        }
+    }
+    // the separate launches
+    const int st = sm100_head_post(s, q, k_new, v_new, q_norm_w, k_norm_w, positions, table, table_first, table_n, k_cache, v_cache, head_dim, q_heads,
+                                   kv_heads, cache_rows, eps, freq_base, neox);
+    if (st != ST_OK) return st;
+    return sm100_attention_kvcache(s, q, k_cache, v_cache, nullptr, 1, out, head_dim, head_dim, 1, cache_rows, q_heads, kv_heads, 1, 0, positions, scale, 1);
+}
 
 // ---------------------------------------------------------------------------------------------------------
 // Attention without any allocation.

@@ -337,12 +337,11 @@ class DecodeModel:
                 else:
                     chk(L.sm100_rms_norm(s, _dev(x_cur), _dev(add), _dev(lw["attn_norm"]), _dev(x_cur), _dev(self.xn), c.hidden, 1, c.eps), "add_rms_norm")
                 self._mm_multi(qkv, self.xn, [self.q, self.k, self.v])
-            chk(L.sm100_head_post(s, _dev(self.q), _dev(self.k), _dev(self.v), _dev(lw["q_norm"]) if c.qk_norm else None,
-                                  _dev(lw["k_norm"]) if c.qk_norm else None, _dev(self.pos), _dev(self.rope), 0, c.n_ctx, _dev(lw["k_cache"]),
-                                  _dev(lw["v_cache"]), c.head_dim, self.hq, self.hkv, c.n_ctx, c.eps, c.rope_base, 1), "head_post")
-            # only the row that head_post has just stored is newer than the preceding kernel: the older rows are requested early
-            chk(L.sm100_attention_kvcache(s, _dev(self.q), _dev(lw["k_cache"]), _dev(lw["v_cache"]), None, 1, _dev(self.att), c.head_dim, c.head_dim,
-                                          1, c.n_ctx, self.hq, self.hkv, 1, 0, _dev(self.pos), scale, 1), "attention")
+            # per-head norm + rotation + KV store + attention over the cache: one launch (two where the shapes do not allow it)
+            chk(L.sm100_attention_decode(s, _dev(self.q), _dev(self.k), _dev(self.v), _dev(lw["q_norm"]) if c.qk_norm else None,
+                                         _dev(lw["k_norm"]) if c.qk_norm else None, _dev(self.pos), _dev(self.rope), 0, c.n_ctx, _dev(lw["k_cache"]),
+                                         _dev(lw["v_cache"]), _dev(self.att), c.head_dim, self.hq, self.hkv, c.n_ctx, c.eps, c.rope_base, 1, scale),
+                "attention_decode")
             if not self._mm_reduce(lw["wo"], 0, self.att, None, self.proj):
                 self._mm(lw["wo"], self.att, self.proj)
                 self._reduce(self.proj)

@@ -323,6 +323,60 @@ def test_head_post_matches_separate_reference_ops(sm100, stream, with_norm):
             b.free()
 
 
+@pytest.mark.parametrize("hq,hkv,d,rows,with_norm", [(32, 8, 128, 1200, True), (32, 8, 128, 96, False), (8, 4, 256, 300, True), (4, 4, 128, 64, True)],
+                         ids=lambda v: str(v))
+def test_attention_decode_one_launch(sm100, stream, hq, hkv, d, rows, with_norm):
+    """sm100_attention_decode (per-head norm + rotation of the new token's Q and K, K / V stored into the caches, attention
+    over the cache, in one launch) against sm100_head_post + sm100_attention_kvcache on the same inputs and against the
+    oracle's separate ops: caches equal (the new K row up to the order of additions in the norm's sum: NMSE 1e-12), outputs
+    within 1e-6, for positions inside and outside the rotation table, first and last row of the cache included."""
+    rng = np.random.default_rng(hq * 100 + rows)
+    L = sm100.lib()
+    qw = rng.standard_normal(d).astype(np.float32)
+    kw = rng.standard_normal(d).astype(np.float32)
+    first, count = 4, rows - 8
+    table = sgref.rope_table(np.arange(first, first + count), d, 1e6)
+    scale = float(1.0 / np.sqrt(d))
+    for pos in (0, first, rows // 2, rows - 5, rows - 1):
+        q = (rng.standard_normal((hq, d)) * 2).astype(np.float32)
+        k = (rng.standard_normal((hkv, d)) * 2).astype(np.float32)
+        v = rng.standard_normal((hkv, d)).astype(np.float32)
+        kc = rng.standard_normal((hkv, rows, d)).astype(np.float32)
+        vc = rng.standard_normal((hkv, rows, d)).astype(np.float32)
+        p = np.array([pos], np.int32)
+        res = []
+        for fused in (True, False):
+            b = {n: U.to_device(sm100, stream, a) for n, a in dict(q=q, k=k, v=v, kc=kc, vc=vc, qw=qw, kw=kw, t=table, p=p).items()}
+            ob, optr = U.guarded_output(sm100, stream, hq * d)
+            if fused:
+                sm100.check(L.sm100_attention_decode(stream.handle, b["q"].at(), b["k"].at(), b["v"].at(), b["qw"].at() if with_norm else None,
+                                                     b["kw"].at() if with_norm else None, b["p"].at(), b["t"].at(), first, count, b["kc"].at(),
+                                                     b["vc"].at(), C.c_void_p(optr), d, hq, hkv, rows, 1e-6, 1e6, 1, scale), "attention_decode")
+            else:
+                sm100.check(L.sm100_head_post(stream.handle, b["q"].at(), b["k"].at(), b["v"].at(), b["qw"].at() if with_norm else None,
+                                              b["kw"].at() if with_norm else None, b["p"].at(), b["t"].at(), first, count, b["kc"].at(), b["vc"].at(),
+                                              d, hq, hkv, rows, 1e-6, 1e6, 1), "head_post")
+                sm100.check(L.sm100_attention_kvcache(stream.handle, b["q"].at(), b["kc"].at(), b["vc"].at(), None, 1, C.c_void_p(optr), d, d, 1, rows,
+                                                      hq, hkv, 1, 0, b["p"].at(), scale, 1), "attention_kvcache")
+            stream.sync()
+            res.append((U.read_guarded(sm100, stream, ob, hq * d).reshape(hq, d).copy(),
+                        b["kc"].download(stream, np.float32, kc.size).reshape(kc.shape), b["vc"].download(stream, np.float32, vc.size).reshape(vc.shape)))
+            for x in list(b.values()) + [ob]:
+                x.free()
+        (o1, kc1, vc1), (o2, kc2, vc2) = res
+        assert np.array_equal(vc1, vc2)
+        other = np.ones(rows, bool)
+        other[pos] = False
+        assert np.array_equal(kc1[:, other], kc2[:, other]) and np.array_equal(kc1[:, other], kc[:, other])
+        assert sgref.nmse(kc1[:, pos], kc2[:, pos]) <= 1e-12
+        assert sgref.nmse(o1, o2) <= 1e-10, pos
+        # the oracle's separate ops
+        qn = sgref.rms_norm(q, qw) if with_norm else q
+        qr = sgref.rope(qn.reshape(1, hq, d), p, d, True, 1e6)[0]
+        want = sgref.attention(qr.reshape(hq, 1, d), kc2[:, :pos + 1], vc2[:, :pos + 1], False, 0, scale).reshape(hq, d)
+        assert sgref.nmse(o1, want) <= TOL, pos
+
+
 @pytest.mark.parametrize("hq,hkv,d,nk,nq", [(8, 8, 128, 300, 1), (8, 4, 128, 777, 2), (32, 8, 128, 1500, 1), (16, 2, 256, 130, 3), (4, 4, 256, 64, 1)],
                          ids=lambda v: str(v))
 def test_attention_single_pass_kernel(sm100, stream, hq, hkv, d, nk, nq):
