@@ -87,6 +87,12 @@ SM100_API int sm100_ipc_close(void * device_ptr);
 SM100_API size_t sm100_allreduce_area_bytes(int world, int capacity_floats);
 SM100_API int sm100_allreduce_create(int rank, int world, int capacity_floats, void * const * areas, sm100_allreduce_t * out);
 SM100_API int sm100_allreduce_sum(sm100_allreduce_t ctx, sm100_stream_t s, float * x, int n);
+/* Greedy token over a vocabulary head whose rows are sharded over the ranks: x holds this rank's n logits (n may be 0),
+ * index_offset the global index of x[0]; every rank receives in out[0] the global index of the largest logit of the whole
+ * row, lowest index on ties (TOP_K with k = 1, src/core/ref/ops.cpp:1189-1228).  One single-CTA kernel per rank: local
+ * arg-max, the (logit, index) candidates exchanged by tagged peer stores, bounded wait.  Every rank must call it the same
+ * number of times.  The reference would copy every shard's logits to one device through the host and sort there. */
+SM100_API int sm100_argmax_allreduce(sm100_allreduce_t ctx, sm100_stream_t s, const float * x, int64_t n, int64_t index_offset, int32_t * out);
 SM100_API int sm100_allreduce_fault(sm100_allreduce_t ctx, int * fault_out);
 /* polls (each followed by a sleep of about 0.1 us) before a wait for a peer gives up; default 1 << 22, about a second */
 SM100_API int sm100_allreduce_set_wait_limit(sm100_allreduce_t ctx, uint32_t polls);

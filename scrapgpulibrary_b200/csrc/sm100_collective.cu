@@ -87,9 +87,89 @@ __global__ void __launch_bounds__(AR_THREADS, 1) allreduce_kernel(ArArgs a) {
     }
 }
 
+// Greedy token over a row-sharded vocabulary head: every rank's best (logit, global index) goes to every rank as two
+// 8-byte words tagged with the call number (the scheme of the fused matvec exchange), and every rank picks the winner:
+// highest logit, lowest index on ties - the rule of TOP_K with k = 1 (src/core/ref/ops.cpp:1189-1228) over the whole row.
+struct AmArgs {
+    uint2 * slots[AR_MAX_RANKS];   // every rank's candidate slots [2][world][2 words] (entry `rank` is the local one)
+    uint32_t * step;               // local: calls completed so far
+    int * fault;
+    const float * x;               // this rank's logits (n of them, n may be 0)
+    int64_t n, index_offset;       // global index of x[0]
+    int32_t * out;                 // the winning global index
+    int rank, world;
+    uint32_t wait_limit;
+};
+
+__global__ void __launch_bounds__(1024) argmax_allreduce_kernel(AmArgs a) {
+    pdl_wait();
+    pdl_launch_dependents();
+    __shared__ float sv[32];
+    __shared__ int si[32];
+    float best = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int64_t i = threadIdx.x; i < a.n; i += blockDim.x) {
+        const float v = a.x[i];
+        if (v > best || bi == 0x7fffffff) { best = v; bi = (int) i; }   // increasing i: the first maximum wins
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+    }
+    if ((threadIdx.x & 31) == 0) { sv[threadIdx.x >> 5] = best; si[threadIdx.x >> 5] = bi; }
+    __syncthreads();
+    if (threadIdx.x >= 32) return;
+    const int nw = blockDim.x >> 5;
+    best = (int) threadIdx.x < nw ? sv[threadIdx.x] : -INFINITY;
+    bi = (int) threadIdx.x < nw ? si[threadIdx.x] : 0x7fffffff;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+    }
+    // every lane holds this rank's candidate; lane r hands it to rank r and then collects rank r's
+    const uint32_t step = *a.step + 1u;
+    const int lane = threadIdx.x;
+    const uint32_t gidx = bi == 0x7fffffff ? 0x7fffffffu : (uint32_t) (a.index_offset + bi);
+    if (lane < a.world) {
+        uint2 * dst = a.slots[lane] + ((size_t) (step & 1u) * a.world + a.rank) * 2;
+        asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(dst), "r"(__float_as_uint(best)), "r"(step) : "memory");
+        asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(dst + 1), "r"(gidx), "r"(step) : "memory");
+    }
+    float cv = -INFINITY;
+    uint32_t ci = 0x7fffffffu;
+    if (lane < a.world) {
+        const uint2 * src = a.slots[a.rank] + ((size_t) (step & 1u) * a.world + lane) * 2;
+        uint2 w0 = make_uint2(0u, 0u), w1 = make_uint2(0u, 0u);
+        bool ok = false;
+        for (uint32_t i = 0; i < a.wait_limit && !ok; ++i) {
+            asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(w0.x), "=r"(w0.y) : "l"(src) : "memory");
+            asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(w1.x), "=r"(w1.y) : "l"(src + 1) : "memory");
+            ok = w0.y == step && w1.y == step;
+            if (!ok && i > 32) __nanosleep(50);
+        }
+        if (!ok) atomicExch(a.fault, 200 + lane);
+        else { cv = __uint_as_float(w0.x); ci = w1.x; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, cv, o);
+        const uint32_t oi = __shfl_xor_sync(0xffffffffu, ci, o);
+        if (ov > cv || (ov == cv && oi < ci)) { cv = ov; ci = oi; }
+    }
+    if (lane == 0) {
+        a.out[0] = (int32_t) ci;
+        *a.step = step;
+    }
+}
+
 struct ArContext {
     ArArgs args;
     ArFuse fuse;
+    AmArgs argmax;
     int device;
 };
 
@@ -133,9 +213,10 @@ int sm100_ipc_close(void * device_ptr) {
 
 // area of one rank: [receive slots of sm100_allreduce_sum][its flags 256 B][counter, fault 256 B]
 //                   [receive slots of the fused matvec exchange: 8 bytes per value][its step counter and ticket 256 B]
+//                   [candidate slots and call counter of the greedy merge 512 B]
 size_t sm100_allreduce_area_bytes(int world, int capacity) {
     const size_t data = (size_t) 2 * world * capacity * sizeof(float);
-    return data + 256 + 256 + 2 * data + 256;
+    return data + 256 + 256 + 2 * data + 256 + 512 /* candidate slots of the greedy merge [2][8][2 words], its call counter */;
 }
 
 int sm100_allreduce_create(int rank, int world, int capacity, void * const * areas, sm100_allreduce_t * out) {
@@ -158,6 +239,13 @@ int sm100_allreduce_create(int rank, int world, int capacity, void * const * are
     c->fuse.done = c->fuse.step + 16;
     c->args.wait_limit = AR_WAIT_LIMIT;
     c->fuse.wait_limit = AR_WAIT_LIMIT;
+    const size_t merge = fused + 2 * data + 256;
+    for (int p = 0; p < world; ++p) c->argmax.slots[p] = (uint2 *) ((uint8_t *) areas[p] + merge);
+    c->argmax.step = (uint32_t *) ((uint8_t *) areas[rank] + merge + 256);
+    c->argmax.fault = c->args.fault;
+    c->argmax.rank = rank;
+    c->argmax.world = world;
+    c->argmax.wait_limit = AR_WAIT_LIMIT;
     c->fuse.fault = c->args.fault;
     c->fuse.capacity = capacity;
     c->fuse.rank = rank;
@@ -180,11 +268,24 @@ int sm100_allreduce_sum(sm100_allreduce_t ctx, sm100_stream_t s, float * x, int 
     return launch(allreduce_kernel, dim3(1), dim3(AR_THREADS), 0, (cudaStream_t) s, a);
 }
 
+int sm100_argmax_allreduce(sm100_allreduce_t ctx, sm100_stream_t s, const float * x, int64_t n, int64_t index_offset, int32_t * out) {
+    ArContext * c = (ArContext *) ctx;
+    if (c == nullptr || out == nullptr || n < 0 || (n > 0 && x == nullptr) || index_offset < 0 || index_offset + n > 0x7ffffffe)
+        return fail(ST_INVALID, "argmax_allreduce: null pointer or a shard outside the 31-bit index range");
+    AmArgs a = c->argmax;
+    a.x = x;
+    a.n = n;
+    a.index_offset = index_offset;
+    a.out = out;
+    return launch(argmax_allreduce_kernel, dim3(1), dim3(1024), 0, (cudaStream_t) s, a);
+}
+
 int sm100_allreduce_set_wait_limit(sm100_allreduce_t ctx, uint32_t polls) {
     ArContext * c = (ArContext *) ctx;
     if (c == nullptr || polls == 0) return fail(ST_INVALID, "allreduce_set_wait_limit: null context or zero polls");
     c->args.wait_limit = polls;
     c->fuse.wait_limit = polls;
+    c->argmax.wait_limit = polls;
     return ST_OK;
 }
 

@@ -362,19 +362,27 @@ class DecodeModel:
                 self._reduce(self.proj)
         # (the next token starts by overwriting self.x with its embedding, so it does not matter where the stream ended)
         chk(L.sm100_rms_norm(s, _dev(x_cur), _dev(self.proj), _dev(self.out_norm), _dev(x_cur), _dev(self.xn), c.hidden, 1, c.eps), "out_norm")
-        if self.head is not None:
-            self._mm(self.head, self.xn, self.logits)
-            chk(L.sm100_argmax(s, _dev(self.logits), self.vocab_n, _dev(self.best)), "argmax")
-        if self.world == 1:
-            self.token.copy_(self.best)
+        ctx = getattr(self.allreduce, "ctx", None)
+        if self.world > 1 and ctx is not None and self.fuse_exchange:
+            # row-sharded head: local arg-max and the exchange of the ranks' (logit, global index) candidates in one kernel
+            if self.head is not None:
+                self._mm(self.head, self.xn, self.logits)
+            chk(L.sm100_argmax_allreduce(ctx, s, _dev(self.logits) if self.head is not None else None, self.vocab_n if self.head is not None else 0,
+                                         self.vocab_lo, _dev(self.token)), "argmax_allreduce")
         else:
-            # (best logit, global index) per rank; highest logit wins, lowest index on ties
-            self.cand[0] = self.logits[self.best.long()][0] if self.head is not None else float("-inf")
-            self.cand[1] = (self.best + self.vocab_lo).float()[0]
-            torch.distributed.all_gather_into_tensor(self.cands.view(-1), self.cand)
-            top = self.cands[:, 0].max()
-            idx = torch.where(self.cands[:, 0] == top, self.cands[:, 1], torch.full_like(self.cands[:, 1], 3e9)).min()
-            self.token.copy_(idx.to(torch.int32).view(1))
+            if self.head is not None:
+                self._mm(self.head, self.xn, self.logits)
+                chk(L.sm100_argmax(s, _dev(self.logits), self.vocab_n, _dev(self.best)), "argmax")
+            if self.world == 1:
+                self.token.copy_(self.best)
+            else:
+                # (best logit, global index) per rank; highest logit wins, lowest index on ties
+                self.cand[0] = self.logits[self.best.long()][0] if self.head is not None else float("-inf")
+                self.cand[1] = (self.best + self.vocab_lo).float()[0]
+                torch.distributed.all_gather_into_tensor(self.cands.view(-1), self.cand)
+                top = self.cands[:, 0].max()
+                idx = torch.where(self.cands[:, 0] == top, self.cands[:, 1], torch.full_like(self.cands[:, 1], 3e9)).min()
+                self.token.copy_(idx.to(torch.int32).view(1))
         self.tokens_out.index_copy_(0, self.step_index, self.token)
         self.step_index.add_(1)
         self.pos.add_(1)

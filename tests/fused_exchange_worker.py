@@ -116,6 +116,28 @@ def main():
         for yb, _ in outs:
             worst = max(worst, float(sgref.nmse(U.read_guarded(capi, stream, yb, n).reshape(1, n), want.reshape(1, n))))
     report["interleaved_worst_nmse"] = worst
+    # greedy token over a row-sharded head: the global arg-max, lowest index on ties (also across ranks), an empty shard
+    L.sm100_argmax_allreduce.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_void_p]
+    rngm = np.random.default_rng(900)
+    total = 4099
+    ok_argmax = True
+    for trial in range(6):
+        row = rngm.standard_normal(total).astype(np.float32)
+        if trial == 1:                      # the same maximum on both ranks: the lower global index wins
+            row[[7, 3000]] = 9.0
+        if trial == 2:
+            row[[3000, 3500]] = 9.0
+        per = -(-total // world) if trial != 3 else total      # trial 3: everything on rank 0, the others hold no rows
+        lo = min(total, rank * per)
+        n_loc = max(0, min(total, lo + per) - lo)
+        xb_ = to_device(row[lo:lo + n_loc]) if n_loc else None
+        ob_ = to_device(np.full(1, -1, np.int32))
+        capi.check(L.sm100_argmax_allreduce(ar.ctx, stream.handle, C.c_void_p(xb_.ptr) if xb_ else None, n_loc, lo, C.c_void_p(ob_.ptr)), "argmax_allreduce")
+        stream.sync()
+        got_tok = int(ob_.download(stream, np.int32, 1)[0])
+        want_tok = int(np.flatnonzero(row == row.max())[0])
+        ok_argmax = ok_argmax and got_tok == want_tok
+    report["argmax_ok"] = bool(ok_argmax)
     report["fault"] = ar.fault()
     if rank == 0:
         with open(out_path, "w") as f:

@@ -16,7 +16,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
 def test_mul_mat_allreduce(sm100, tmp_path):
-    """sm100_mul_mat_allreduce on 2 GPUs: the K-sharded product with the exchange inside the matvec launch equals the CPU
+    """sm100_mul_mat_allreduce and sm100_argmax_allreduce on 2 GPUs: the K-sharded product with the exchange inside the matvec launch equals the CPU
     oracle's product over the full K (NMSE 1e-6), gives the same bits on both ranks, on repeated calls and under graph
     replay, never runs into its bounded wait; tensors the fused kernel does not serve take the separate launches."""
     if sm100.device_count() < 2:
@@ -34,6 +34,7 @@ def test_mul_mat_allreduce(sm100, tmp_path):
     assert [c["kernel"] for c in got["cases"][:4]] == ["matvec_q4k_ring+allreduce"] * 4, got["cases"]
     assert "ring" not in got["cases"][4]["kernel"]
     assert got["interleaved_worst_nmse"] <= 1e-6, got
+    assert got["argmax_ok"], got      # sm100_argmax_allreduce: global arg-max of a row-sharded vector, ties, an empty shard
 
 
 @pytest.mark.parametrize("exchange", ["nccl", "peer", "peer-unfused"])
