@@ -2,13 +2,13 @@
 //
 // The tensor-parallel decode needs two all-reduces of the hidden vector (16 KiB) per layer.  At that size a
 // collective is pure latency, so it is one kernel of one CTA per GPU instead of a library call: every rank stores
-// its vector into its slot of EVERY rank's receive area (plain 16-byte stores over NVLink), fences, raises a flag
-// next to it, waits - with a bound - until all ranks' flags for this step have arrived in its own memory, and adds
-// the slots in rank order (the same order everywhere: every rank gets the same bits).  No multicast, no loads from
-// peer memory, no library kernel on peer pointers.
+// its vector into its slot of EVERY rank's receive area (plain 8-byte stores over NVLink: a value and the step number
+// as its tag in one word, so that neither a fence nor a flag is needed - the scheme of NCCL's low-latency protocol),
+// then adds the slots in rank order (the same order everywhere: every rank gets the same bits), waiting - with a
+// bound - for each value's tag.  No multicast, no loads from peer memory, no library kernel on peer pointers.
 //
 // Two receive areas alternate by step: a rank can only be one step ahead of the slowest one (it needs that rank's
-// flag to finish a step), and a rank raises its flag for step s + 1 only after it has finished reading step s.
+// values to finish a step), and a rank sends its values for step s + 1 only after it has finished reading step s.
 //
 // This replaces the host-bounce copy the reference uses between devices (src/core/transport.cpp:53-146) on the
 // tensor-parallel path; the reference itself has no collective.
@@ -23,8 +23,7 @@ namespace {
 constexpr int AR_THREADS = 1024;
 
 struct ArArgs {
-    float * recv[AR_MAX_RANKS];       // every rank's receive area [2][world][capacity] (entry `rank` is the local one)
-    uint32_t * flags[AR_MAX_RANKS];   // every rank's flags [2][world]
+    uint2 * recv[AR_MAX_RANKS];       // every rank's receive area [2][world][capacity] of (value bits, step tag) (entry `rank` is the local one)
     uint32_t * counter;               // local: calls so far
     int * fault;                      // local: set when a wait ran out
     float * x;                        // in / out
@@ -32,59 +31,39 @@ struct ArArgs {
     uint32_t wait_limit;              // polls before the wait for a peer gives up
 };
 
-__device__ __forceinline__ void st_release_sys(uint32_t * p, uint32_t v) { asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory"); }
-__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t * p) {
-    uint32_t v;
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-    return v;
-}
-
 __global__ void __launch_bounds__(AR_THREADS, 1) allreduce_kernel(ArArgs a) {
     pdl_wait();
-    __shared__ uint32_t s_step;
     const int tid = threadIdx.x;
-    if (tid == 0) {
-        const uint32_t step = *a.counter + 1u;
-        *a.counter = step;
-        s_step = step;
-    }
-    __syncthreads();
-    const uint32_t step = s_step;
-    const int buf = (int) (step & 1u);
-    const int n4 = a.n >> 2;
-    // 1. my vector into my slot of every rank's receive area
-    const float4 * src = reinterpret_cast<const float4 *>(a.x);
-    for (int i = tid; i < n4; i += AR_THREADS) {
-        const float4 v = src[i];
-        for (int p = 0; p < a.world; ++p)
-            reinterpret_cast<float4 *>(a.recv[p] + ((size_t) buf * a.world + a.rank) * a.capacity)[i] = v;
-    }
-    __threadfence_system();
-    __syncthreads();
-    if (tid < a.world) st_release_sys(a.flags[tid] + buf * a.world + a.rank, step);
-    // 2. all ranks' flags for this step, bounded
-    if (tid < a.world) {
-        const uint32_t * f = a.flags[a.rank] + buf * a.world + tid;
-        bool ok = false;
-        for (uint32_t i = 0; i < a.wait_limit; ++i) {
-            if (ld_acquire_sys(f) == step) { ok = true; break; }
-            __nanosleep(100);
+    const uint32_t step = __ldcg(a.counter) + 1u;   // every thread reads it; thread 0 advances it at the end
+    const size_t buf = (size_t) (step & 1u) * a.world;
+    // 1. my vector into my slot of every rank's receive area, every value in one 8-byte word with the step as its tag
+    for (int i = tid; i < a.n; i += AR_THREADS) {
+        const uint32_t bits = __float_as_uint(a.x[i]);
+        for (int p = 0; p < a.world; ++p) {
+            uint2 * dst = a.recv[p] + (buf + a.rank) * a.capacity + i;
+            asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(dst), "r"(bits), "r"(step) : "memory");
         }
-        if (!ok) atomicExch(a.fault, 1 + tid);
     }
-    __syncthreads();
     pdl_launch_dependents();
-    // 3. sum of the slots in rank order
-    const float * mine = a.recv[a.rank] + (size_t) buf * a.world * a.capacity;
-    float4 * dst = reinterpret_cast<float4 *>(a.x);
-    for (int i = tid; i < n4; i += AR_THREADS) {
-        float4 acc = __ldcg(reinterpret_cast<const float4 *>(mine) + i);
-        for (int r = 1; r < a.world; ++r) {
-            const float4 v = __ldcg(reinterpret_cast<const float4 *>(mine + (size_t) r * a.capacity) + i);
-            acc.x = __fadd_rn(acc.x, v.x); acc.y = __fadd_rn(acc.y, v.y); acc.z = __fadd_rn(acc.z, v.z); acc.w = __fadd_rn(acc.w, v.w);
+    // 2. sum of the slots in rank order; a value is there when its tag equals this step (bounded wait)
+    const uint2 * mine = a.recv[a.rank] + buf * a.capacity;
+    for (int i = tid; i < a.n; i += AR_THREADS) {
+        float acc = 0.f;
+        for (int r = 0; r < a.world; ++r) {
+            const uint2 * src = mine + (size_t) r * a.capacity + i;
+            uint2 got;
+            asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(got.x), "=r"(got.y) : "l"(src) : "memory");
+            for (uint32_t spins = 0; got.y != step && spins < a.wait_limit; ++spins) {
+                if (spins > 32) __nanosleep(50);
+                asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(got.x), "=r"(got.y) : "l"(src) : "memory");
+            }
+            if (got.y != step) atomicExch(a.fault, 1 + r);
+            acc = r == 0 ? __uint_as_float(got.x) : __fadd_rn(acc, __uint_as_float(got.x));
         }
-        dst[i] = acc;
+        a.x[i] = acc;
     }
+    __syncthreads();
+    if (tid == 0) *a.counter = step;
 }
 
 // Greedy token over a row-sharded vocabulary head: every rank's best (logit, global index) goes to every rank as two
@@ -211,12 +190,12 @@ int sm100_ipc_close(void * device_ptr) {
     return ST_OK;
 }
 
-// area of one rank: [receive slots of sm100_allreduce_sum][its flags 256 B][counter, fault 256 B]
+// area of one rank: [receive slots of sm100_allreduce_sum: 8 bytes per value][256 B unused][counter, fault 256 B]
 //                   [receive slots of the fused matvec exchange: 8 bytes per value][its step counter and ticket 256 B]
 //                   [candidate slots and call counter of the greedy merge 512 B]
 size_t sm100_allreduce_area_bytes(int world, int capacity) {
     const size_t data = (size_t) 2 * world * capacity * sizeof(float);
-    return data + 256 + 256 + 2 * data + 256 + 512 /* candidate slots of the greedy merge [2][8][2 words], its call counter */;
+    return 2 * data + 256 + 256 + 2 * data + 256 + 512 /* candidate slots of the greedy merge [2][8][2 words], its call counter */;
 }
 
 int sm100_allreduce_create(int rank, int world, int capacity, void * const * areas, sm100_allreduce_t * out) {
@@ -228,12 +207,11 @@ int sm100_allreduce_create(int rank, int world, int capacity, void * const * are
     const size_t data = (size_t) 2 * world * capacity * sizeof(float);
     for (int p = 0; p < world; ++p) {
         if (areas[p] == nullptr) { delete c; return fail(ST_INVALID, "allreduce_create: area %d is null", p); }
-        c->args.recv[p] = (float *) areas[p];
-        c->args.flags[p] = (uint32_t *) ((uint8_t *) areas[p] + data);
+        c->args.recv[p] = (uint2 *) areas[p];
     }
-    c->args.counter = (uint32_t *) ((uint8_t *) areas[rank] + data + 256);
-    c->args.fault = (int *) ((uint8_t *) areas[rank] + data + 256 + 64);
-    const size_t fused = data + 512;
+    c->args.counter = (uint32_t *) ((uint8_t *) areas[rank] + 2 * data + 256);
+    c->args.fault = (int *) ((uint8_t *) areas[rank] + 2 * data + 256 + 64);
+    const size_t fused = 2 * data + 512;
     for (int p = 0; p < world; ++p) c->fuse.recv[p] = (uint2 *) ((uint8_t *) areas[p] + fused);
     c->fuse.step = (uint32_t *) ((uint8_t *) areas[rank] + fused + 2 * data);
     c->fuse.done = c->fuse.step + 16;
