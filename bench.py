@@ -342,7 +342,8 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         per_launch_us = ms_per_step * 1e3 / matvecs_per_step               # (at N > 1 this includes the all-reduce launches in between)
         achieved = per_launch_bytes / (per_launch_us * 1e-6) / 1e9
         kernel_name = (L.sm100_matvec_last_kernel() or b"").decode() if headline_kernel is None else headline_kernel
-        traffic, traffic_src = profiled_traffic(kernel_name)
+        # (the capture is of the unsharded launches: it says nothing about a rank's share)
+        traffic, traffic_src = profiled_traffic(kernel_name) if world == 1 else (None, None)
         out = {
             "metric": METRIC, "value": round(value, 1), "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": round(ms_per_step, 4), "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": ARITHMETIC,
