@@ -218,6 +218,16 @@ SM100_API int sm100_mul_mat_multi(sm100_stream_t s, int count, const int * dtype
  * caller runs the separate ops. */
 #define SM100_PROLOGUE_SWIGLU 1
 #define SM100_PROLOGUE_RMS_NORM 2
+/* The gate and up projections of a gated FFN with their SwiGLU in ONE launch: act = swiglu(W_gate . x, W_up . x), where x is
+ * `a` (prologue 0) or the (ADD_)RMS_NORM_MUL row of sm100_mul_mat_fused (SM100_PROLOGUE_RMS_NORM, with the same sum_out /
+ * x_out side outputs).  The kernel walks the row tiles of the two tensors alternately, so a CTA holds row i of gate and of up
+ * at the same time and writes the activation directly: the down projection that follows is a plain matvec, without a SwiGLU
+ * kernel in front of it and without every one of its CTAs evaluating SwiGLU over the whole row.  gate_out / up_out (optional)
+ * receive the projections themselves.  Same values as MUL_MAT_MULTI followed by GLU (include/scrapgpu/op.h:46, src/core/ref/ops.cpp:383-425).
+ * Packed Q4_K tensors [K, N] with N a multiple of 16; otherwise UNSUPPORTED (status 1) and the caller runs the separate ops. */
+SM100_API int sm100_mul_mat_glu(sm100_stream_t s, int prologue, const float * a, const float * b, const float * norm_w, float eps,
+                                float * sum_out, float * x_out, int dtype, int layout, const void * w_gate, const void * w_up,
+                                int64_t k, int64_t n, float * gate_out, float * up_out, float * act_out);
 SM100_API int sm100_mul_mat_fused(sm100_stream_t s, int prologue, const float * a, const float * b, const float * norm_w,
                                   float eps, float * sum_out, float * x_out, int count, const int * dtypes,
                                   const int * layouts, const void * const * ws, int64_t k, const int64_t * ns,

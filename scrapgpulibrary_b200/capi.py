@@ -81,6 +81,7 @@ def lib() -> C.CDLL:
         L.sm100_allreduce_sum.argtypes = [vp, vp, vp, i32]
         L.sm100_allreduce_set_wait_limit.argtypes = [vp, C.c_uint32]
         L.sm100_argmax_allreduce.argtypes = [vp, vp, vp, i64, i64, vp]
+        L.sm100_mul_mat_glu.argtypes = [vp, i32, vp, vp, vp, C.c_float, vp, vp, i32, i32, vp, vp, i64, i64, vp, vp, vp]
         L.sm100_mul_mat_allreduce.argtypes = [vp, vp, i32, vp, vp, i32, i32, vp, i64, i64, vp]
         L.sm100_allreduce_fault.argtypes = [vp, C.POINTER(i32)]
         L.sm100_allreduce_destroy.argtypes = [vp]

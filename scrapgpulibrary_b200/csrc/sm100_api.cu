@@ -8,7 +8,7 @@ namespace sm100 {
 int matvec(cudaStream_t s, int dtype, int layout, const void * w, int64_t w_row_stride, int64_t k, int64_t n, const float * x,
            int64_t ldx, int64_t m, float * y, int64_t ldy);
 int matvec_q4k_imma_multi(cudaStream_t s, int count, const void * const * ws, const int64_t * ns, int64_t k, const float * x, int64_t ldx,
-                          int64_t m, float * const * ys, const int64_t * ldys, bool * handled, const Q4KPrologue * pro);
+                          int64_t m, float * const * ys, const int64_t * ldys, bool * handled, const Q4KPrologue * pro, float * glu_out);
 const char * matvec_last_kernel();
 void matvec_note_kernel(const char * name);
 int matvec_q4k_ring_multi(cudaStream_t s, int count, const void * const * ws, const int64_t * ns, int64_t k, const float * x,
@@ -66,7 +66,7 @@ int sm100_mul_mat_multi(sm100_stream_t s, int count, const int * dtypes, const i
         bool handled = false;
         int st = matvec_q4k_ring_multi((cudaStream_t) s, grouped, gw, gn, k, x, gy, &handled, nullptr, nullptr);
         if (st != ST_OK) return st;
-        if (!handled) st = matvec_q4k_imma_multi((cudaStream_t) s, grouped, gw, gn, k, x, k, 1, gy, gld, &handled, nullptr);
+        if (!handled) st = matvec_q4k_imma_multi((cudaStream_t) s, grouped, gw, gn, k, x, k, 1, gy, gld, &handled, nullptr, nullptr);
         if (st != ST_OK) return st;
         if (!handled) in_group[0] = in_group[1] = in_group[2] = false;
     } else {
@@ -102,9 +102,30 @@ int sm100_mul_mat_fused(sm100_stream_t s, int prologue, const float * a, const f
     bool handled = false;
     int st = matvec_q4k_ring_multi((cudaStream_t) s, count, ws, ns, k, a, ys, &handled, &pro, nullptr);
     if (st != ST_OK) return st;
-    if (!handled) st = matvec_q4k_imma_multi((cudaStream_t) s, count, ws, ns, k, a, k, 1, ys, ld, &handled, &pro);
+    if (!handled) st = matvec_q4k_imma_multi((cudaStream_t) s, count, ws, ns, k, a, k, 1, ys, ld, &handled, &pro, nullptr);
     if (st != ST_OK) return st;
     if (!handled) return fail(ST_UNSUPPORTED, "mul_mat_fused: this shape is not served by the fused kernel; run the separate ops");
+    return ST_OK;
+}
+
+int sm100_mul_mat_glu(sm100_stream_t s, int prologue, const float * a, const float * b, const float * norm_w, float eps, float * sum_out, float * x_out,
+                      int dtype, int layout, const void * w_gate, const void * w_up, int64_t k, int64_t n, float * gate_out, float * up_out, float * act_out) {
+    if (a == nullptr || w_gate == nullptr || w_up == nullptr || act_out == nullptr || k <= 0 || n <= 0) return fail(ST_INVALID, "mul_mat_glu: null pointer or empty shape");
+    if (prologue != 0 && prologue != SM100_PROLOGUE_RMS_NORM) return fail(ST_INVALID, "mul_mat_glu: the prologue is 0 or SM100_PROLOGUE_RMS_NORM");
+    if (dtype != DT_Q4_K || layout != LAYOUT_PACKED || n % 16 != 0)
+        return fail(ST_UNSUPPORTED, "mul_mat_glu: served for packed Q4_K tensors with a multiple of 16 rows; run the separate ops");
+    if ((sum_out != nullptr && (sum_out == a || sum_out == b)) || (x_out != nullptr && (x_out == a || x_out == b)) || act_out == a || act_out == b)
+        return fail(ST_INVALID, "mul_mat_glu: the outputs must not alias the inputs (every CTA reads them while others write)");
+    Q4KPrologue pro = {};
+    pro.mode = prologue;
+    pro.a = a; pro.b = b; pro.norm_w = norm_w; pro.sum_out = sum_out; pro.x_out = x_out; pro.eps = eps;
+    const void * ws[2] = {w_gate, w_up};
+    const int64_t ns[2] = {n, n}, ld[2] = {n, n};
+    float * ys[2] = {gate_out, up_out};
+    bool handled = false;
+    const int st = matvec_q4k_imma_multi((cudaStream_t) s, 2, ws, ns, k, a, k, 1, ys, ld, &handled, prologue != 0 ? &pro : nullptr, act_out);
+    if (st != ST_OK) return st;
+    if (!handled) return fail(ST_UNSUPPORTED, "mul_mat_glu: this shape is not served by the fused kernel; run the separate ops");
     return ST_OK;
 }
 

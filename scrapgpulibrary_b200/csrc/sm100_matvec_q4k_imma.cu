@@ -58,12 +58,21 @@ struct IqArgs {
     int blocks;          // K / 256
     int chunks;          // ceil(blocks / blocks per chunk)
     int ring;            // slots per warp of the shared-memory ring
+    // gate / up mode (M = 1, two tensors of equal row counts): the row tiles of the two tensors alternate (even tiles gate, odd
+    // tiles up), so the two row groups of a CTA hold tile T of both at the same time and the epilogue writes
+    // act = swiglu(gate, up) (src/core/ref/ops.cpp:383-425, the arithmetic of swiglu_kernel); y[0], y[1] are written too when set
+    float * act;
 };
 
 __device__ __forceinline__ int nsb_of(const IqArgs & p) { return p.pairs * 2; }
 
 // tensor of a global row tile and the tile's index inside it
 __device__ __forceinline__ void iq_locate(const IqArgs & p, int rt, int & tensor, int & local) {
+    if (p.act != nullptr) {   // gate / up mode: the tensors' tiles alternate
+        tensor = rt & 1;
+        local = rt >> 1;
+        return;
+    }
     tensor = (rt >= p.tile_end[0] ? 1 : 0) + (rt >= p.tile_end[1] ? 1 : 0);
     local = rt - (tensor == 0 ? 0 : p.tile_end[tensor - 1]);
 }
@@ -487,7 +496,22 @@ __global__ void __launch_bounds__(IQ_THREADS, NB == 1 ? 2 : 1) matvec_q4k_imma(I
             my_red[(warp * 16 + g + 8) * 4 + t] = v1;
         }
         __syncthreads();
-        if (gtid < 64 && rt < p.n_tiles) {
+        if (M == 1 && p.act != nullptr) {
+            // group 0 holds tile T of gate, group 1 tile T of up (rt even / odd): one thread per row makes the activation
+            if (group == 0 && gtid < 16 && rt + 1 < p.n_tiles) {
+                const int row = gtid;
+                float vg = 0.f, vu = 0.f;
+#pragma unroll
+                for (int w = 0; w < IQ_WARPS; ++w) {
+                    vg += red[(w * 16 + row) * 4];
+                    vu += red[IQ_WARPS * 64 + (w * 16 + row) * 4];
+                }
+                const int64_t at = (int64_t) (rt >> 1) * 16 + row;
+                p.act[at] = __fmul_rn(__fdiv_rn(vg, __fadd_rn(1.0f, expf(-vg))), vu);
+                if (p.y[0] != nullptr) p.y[0][at] = vg;
+                if (p.y[1] != nullptr) p.y[1][at] = vu;
+            }
+        } else if (gtid < 64 && rt < p.n_tiles) {
             const int row = gtid >> 2, col = gtid & 3;
             if (col < M) {
                 float v = 0.f;
@@ -774,9 +798,12 @@ int iq_poll_fault() {
 
 // Q4_K packed matvec (1 or 2 activation columns) over the full 16-row tiles of up to three tensors that share
 // the activations; *handled = false when the shapes are left to the caller's other kernels.
+// glu_out (optional): ws are the gate and up tensors (equal row counts, one column); glu_out receives swiglu(gate, up), ys[0]
+// and ys[1] the projections themselves when they are non-null.
 int matvec_q4k_imma_multi(cudaStream_t s, int count, const void * const * ws, const int64_t * ns, int64_t k, const float * x, int64_t ldx,
-                          int64_t m, float * const * ys, const int64_t * ldys, bool * handled, const Q4KPrologue * pro) {
+                          int64_t m, float * const * ys, const int64_t * ldys, bool * handled, const Q4KPrologue * pro, float * glu_out) {
     *handled = false;
+    if (glu_out != nullptr && (count != 2 || m != 1 || ns[0] != ns[1] || ns[0] % 16 != 0 || ((uintptr_t) glu_out & 15) != 0)) return ST_OK;
     if (pro != nullptr && pro->mode != 0) {
         if (m != 1 || pro->a == nullptr) return ST_OK;
         const uintptr_t al = (uintptr_t) pro->a | (uintptr_t) pro->b | (uintptr_t) pro->norm_w | (uintptr_t) pro->sum_out | (uintptr_t) pro->x_out;
@@ -819,6 +846,7 @@ int matvec_q4k_imma_multi(cudaStream_t s, int count, const void * const * ws, co
     }
     a.x = x;
     a.ldx = ldx;
+    a.act = glu_out;
     if (pro != nullptr && pro->mode != 0) {
         a.prologue = pro->mode;
         a.pa = pro->a; a.pb = pro->b; a.pw = pro->norm_w; a.sum_out = pro->sum_out; a.x_out = pro->x_out; a.eps = pro->eps;
@@ -891,7 +919,7 @@ int matvec_q4k_imma_cols_tiles(cudaStream_t s, const void * w, int64_t k, int64_
 
 int matvec_q4k_imma_tiles(cudaStream_t s, const void * w, int64_t k, int64_t n, const float * x, int64_t ldx, int64_t m, float * y, int64_t ldy,
                           bool * handled) {
-    return matvec_q4k_imma_multi(s, 1, &w, &n, k, x, ldx, m, &y, &ldy, handled, nullptr);
+    return matvec_q4k_imma_multi(s, 1, &w, &n, k, x, ldx, m, &y, &ldy, handled, nullptr, nullptr);
 }
 
 }  // namespace sm100

@@ -155,6 +155,8 @@ class DecodeModel:
         self.fuse_swiglu = fuse and os.environ.get("SM100_FUSE_SWIGLU", "1") != "0"
         # the all-reduce of the row-parallel projections inside their matvec launch (sm100_mul_mat_allreduce)
         self.fuse_exchange = fuse and os.environ.get("SM100_TP_FUSED", "1") != "0"
+        # SwiGLU in the epilogue of the gate / up launch (sm100_mul_mat_glu) instead of in front of the down projection
+        self.fuse_glu = fuse and os.environ.get("SM100_FUSE_GLU", "1") != "0"
         c = cfg
         self.hq, self.hkv = c.heads // world, c.kv_heads // world
         self.q_dim, self.kv_dim, self.ffn = self.hq * c.head_dim, self.hkv * c.head_dim, c.ffn // world
@@ -345,6 +347,20 @@ class DecodeModel:
             if not self._mm_reduce(lw["wo"], 0, self.att, None, self.proj):
                 self._mm(lw["wo"], self.att, self.proj)
                 self._reduce(self.proj)
+            glu_done = False
+            if self.fuse and self.fuse_glu and lw["wgate"].dtype == Q4_K and lw["wup"].dtype == Q4_K and lw["wgate"].n == lw["wup"].n:
+                # ADD_RMS_NORM_MUL in the prologue, gate and up in one launch, SwiGLU in its epilogue: act comes out directly
+                st = L.sm100_mul_mat_glu(s, 2, _dev(x_cur), _dev(self.proj), _dev(lw["ffn_norm"]), c.eps, _dev(x_alt), None, Q4_K, 1,
+                                         _dev(lw["wgate"].data), _dev(lw["wup"].data), lw["wgate"].k, lw["wgate"].n, None, None, _dev(self.act))
+                if st != 1:    # 1 = UNSUPPORTED: the separate launches below
+                    chk(st, "mul_mat_glu")
+                    glu_done = True
+                    x_cur, x_alt = x_alt, x_cur
+            if glu_done:
+                if not self._mm_reduce(lw["wdown"], 0, self.act, None, self.proj):
+                    self._mm(lw["wdown"], self.act, self.proj)
+                    self._reduce(self.proj)
+                continue
             if self.fuse:
                 self._mm_fused(2, x_cur, self.proj, lw["ffn_norm"], x_alt, None, [lw["wgate"], lw["wup"]], [self.gate, self.up])
                 x_cur, x_alt = x_alt, x_cur

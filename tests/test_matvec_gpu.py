@@ -309,6 +309,58 @@ def test_mul_mat_fused_prologues(sm100, stream):
     assert sgref.nmse(outs[0], sgref.mul_mat(U.Q4_K, wd, k2, act[None])[0]) <= TOL
 
 
+@pytest.mark.parametrize("k,n,prologue", [(4096, 12288, 2), (1024, 48, 0), (4096, 1536, 2)], ids=["4096x12288_norm", "1024x48", "4096x1536_norm"])
+def test_mul_mat_glu(sm100, stream, k, n, prologue):
+    """sm100_mul_mat_glu: gate and up projections with SwiGLU in the epilogue of the same launch (and the residual add + RMS
+    norm in its prologue): gate, up and the activation equal, bit for bit, sm100_mul_mat_fused / sm100_mul_mat_multi over the
+    two tensors followed by sm100_swiglu; the activation within NMSE 1e-6 of the oracle's ops."""
+    import ctypes as C
+    L = sm100.lib()
+    rng = np.random.default_rng(60 + n)
+    wg = U.quantize(U.Q4_K, U.seeded_weights(500 + n, n, k))
+    wu = U.quantize(U.Q4_K, U.seeded_weights(501 + n, n, k))
+    a = (rng.standard_normal(k) * 3).astype(np.float32)
+    b = rng.standard_normal(k).astype(np.float32)
+    g = (1.0 + 0.1 * rng.standard_normal(k)).astype(np.float32)
+    bufs = {name: U.to_device(sm100, stream, arr) for name, arr in dict(a=a, b=b, g=g, wg=sm100.pack(U.Q4_K, k, wg), wu=sm100.pack(U.Q4_K, k, wu)).items()}
+    gate1, up1, act1, sum1 = (sm100.Buffer(4 * n), sm100.Buffer(4 * n), U.guarded_output(sm100, stream, n), sm100.Buffer(4 * k))
+    sm100.check(L.sm100_mul_mat_glu(stream.handle, prologue, bufs["a"].at(), bufs["b"].at() if prologue else None, bufs["g"].at() if prologue else None, 1e-6,
+                                    sum1.at() if prologue else None, None, U.Q4_K, 1, bufs["wg"].at(), bufs["wu"].at(), k, n, gate1.at(), up1.at(),
+                                    C.c_void_p(act1[1])), "mul_mat_glu")
+    stream.sync()
+    got_gate, got_up = gate1.download(stream, np.float32, n), up1.download(stream, np.float32, n)
+    got_act = U.read_guarded(sm100, stream, act1[0], n).copy()
+    # the separate launches
+    if prologue:
+        outs, s_out, _ = _fused(sm100, stream, 2, a, b, g, [wg, wu], k, True, False)
+        assert np.array_equal(sum1.download(stream, np.float32, k), s_out)
+        want_s, want_x = sgref.rms_norm(a[None], g, add=b[None])
+        x_ref = want_x
+    else:
+        gb, ub = sm100.Buffer(4 * n), sm100.Buffer(4 * n)
+        sm100.check(L.sm100_mul_mat_multi(stream.handle, 2, (C.c_int * 2)(U.Q4_K, U.Q4_K), (C.c_int * 2)(1, 1), (C.c_void_p * 2)(bufs["wg"].ptr, bufs["wu"].ptr),
+                                          k, (C.c_int64 * 2)(n, n), bufs["a"].at(), (C.c_void_p * 2)(gb.ptr, ub.ptr)), "mul_mat_multi")
+        stream.sync()
+        outs = [gb.download(stream, np.float32, n), ub.download(stream, np.float32, n)]
+        x_ref = a[None]
+    assert np.array_equal(got_gate, outs[0]) and np.array_equal(got_up, outs[1])
+    g2, u2, a2 = U.to_device(sm100, stream, outs[0]), U.to_device(sm100, stream, outs[1]), sm100.Buffer(4 * n)
+    sm100.check(L.sm100_swiglu(stream.handle, g2.at(), u2.at(), a2.at(), n), "swiglu")
+    stream.sync()
+    assert np.array_equal(got_act, a2.download(stream, np.float32, n))
+    want = sgref.swiglu(sgref.mul_mat(U.Q4_K, wg, k, x_ref)[0], sgref.mul_mat(U.Q4_K, wu, k, x_ref)[0])
+    assert sgref.nmse(got_act, want) <= TOL
+    # only the activation wanted
+    act3 = U.guarded_output(sm100, stream, n)
+    sm100.check(L.sm100_mul_mat_glu(stream.handle, prologue, bufs["a"].at(), bufs["b"].at() if prologue else None, bufs["g"].at() if prologue else None, 1e-6,
+                                    None, None, U.Q4_K, 1, bufs["wg"].at(), bufs["wu"].at(), k, n, None, None, C.c_void_p(act3[1])), "mul_mat_glu")
+    stream.sync()
+    assert np.array_equal(U.read_guarded(sm100, stream, act3[0], n), got_act)
+    # a row count that is not a multiple of 16 is refused
+    assert L.sm100_mul_mat_glu(stream.handle, 0, bufs["a"].at(), None, None, 0.0, None, None, U.Q4_K, 1, bufs["wg"].at(), bufs["wu"].at(), k, n - 8, None, None,
+                               C.c_void_p(act3[1])) == 1
+
+
 def test_mul_mat_fused_refuses_what_it_does_not_serve(sm100, stream):
     import ctypes as C
     k, n = 256, 24   # 24 rows: not whole 16-row tiles
