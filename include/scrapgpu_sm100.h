@@ -75,10 +75,11 @@ SM100_API int sm100_peer_access(int device, int peer);
  * collective; the tensor-parallel decode needs an all-reduce of the hidden vector after the row-parallel projections.
  * Each rank allocates one area of sm100_allreduce_area_bytes() with sm100_malloc, zero-fills it, exports it
  * (sm100_ipc_export), and opens the other ranks' handles (sm100_ipc_open); `areas` lists all ranks' areas as seen from
- * this process (entry `rank` = the local pointer).  sm100_allreduce_sum is one single-CTA kernel: stores to every
- * peer, a system-scope flag, a bounded wait for the peers' flags, and the sum in rank order (same bits on every rank).
- * Every rank must call it the same number of times.  A wait that runs out sets a fault (sm100_allreduce_fault != 0)
- * and the kernel returns; it never spins without bound. */
+ * this process (entry `rank` = the local pointer).  sm100_allreduce_sum is one single-CTA kernel: every value goes to every
+ * peer as one 8-byte store carrying the call number as its tag (no fence, no flag), then the slots are added in rank order
+ * (same bits on every rank) with a bounded wait for each value's tag.  Every rank must make the same sequence of calls on a
+ * context, from one stream at a time.  A wait that runs out sets a fault (sm100_allreduce_fault != 0) and the kernel
+ * returns; it never spins without bound. */
 typedef void * sm100_allreduce_t;
 SM100_API size_t sm100_ipc_handle_bytes(void);
 SM100_API int sm100_ipc_export(void * device_ptr, void * handle_out);

@@ -220,6 +220,7 @@ int sm100_stream_create(int device, sm100_stream_t * out) {
 int sm100_stream_destroy(int device, sm100_stream_t stream) {
     if (stream == nullptr) return ST_OK;
     SM100_CUDA(cudaSetDevice(device));
+    stream_tail_set((cudaStream_t) stream, TAIL_OTHER);   // a later stream may get the same handle
     SM100_CUDA(cudaStreamDestroy((cudaStream_t) stream));
     return ST_OK;
 }
