@@ -123,6 +123,10 @@ struct FusedCall {
     bool has_b = false, has_sum = false, has_x = false;
     float eps = 0.0f;
     std::vector<scrapgpu_tensor_desc> w, y;
+    // the two tensors are the gate and up projections of a GLU node that follows: its output comes out of the same launch
+    // (sm100_mul_mat_glu), y[0] and y[1] are written as well
+    bool has_glu = false;
+    scrapgpu_tensor_desc glu_out = {};
 };
 
 // What plan_execute runs in place of a group of consecutive nodes of the caller's list
@@ -1562,7 +1566,7 @@ void lower_plan(Plan & plan) {
         PlanStep step;
         step.nodes = items[i].covers;
         const PlanNode & a = items[i].node;
-        bool fused_away = false;
+        bool fused_away = false, glu_joined = false;
         if (i + 1 < items.size()) {
             const PlanNode & b = items[i + 1].node;
             const bool mm = b.desc.op == SCRAPGPU_OP_MUL_MAT || b.desc.op == SCRAPGPU_OP_MUL_MAT_MULTI;
@@ -1606,8 +1610,29 @@ void lower_plan(Plan & plan) {
                     if (descs_overlap(b.outputs[k], f.a) || (f.has_b && descs_overlap(b.outputs[k], f.b))) ok = false;
                 }
             }
+            // ... and a split SwiGLU over exactly these two projections joins the launch as its epilogue
+            if (ok && f.prologue == SM100_PROLOGUE_RMS_NORM && nw == 2 && i + 2 < items.size()) {
+                const PlanNode & gn = items[i + 2].node;
+                if (gn.desc.op == SCRAPGPU_OP_GLU && gn.inputs.size() == 2 && load_params<scrapgpu_glu_params>(&gn.desc).kind == SCRAPGPU_GLU_SWIGLU) {
+                    const scrapgpu_tensor_desc & act = gn.outputs[0];
+                    bool clear = same_tensor(gn.inputs[0], b.outputs[0]) && same_tensor(gn.inputs[1], b.outputs[1]) && single_row(act) &&
+                                 ne(b.inputs[0], 1) == ne(b.inputs[1], 1) && !descs_overlap(act, f.a) && !descs_overlap(act, b.outputs[0]) &&
+                                 !descs_overlap(act, b.outputs[1]);
+                    if (f.has_b) clear = clear && !descs_overlap(act, f.b);
+                    if (f.has_sum) clear = clear && !descs_overlap(act, f.sum_out);
+                    if (f.has_x) clear = clear && !descs_overlap(act, f.x_out);
+                    if (clear) {
+                        f.has_glu = true;
+                        f.glu_out = act;
+                    }
+                }
+            }
             if (ok) {
                 step.nodes.insert(step.nodes.end(), items[i + 1].covers.begin(), items[i + 1].covers.end());
+                if (f.has_glu) {
+                    step.nodes.insert(step.nodes.end(), items[i + 2].covers.begin(), items[i + 2].covers.end());
+                    glu_joined = true;
+                }
                 step.fused = (int) plan.fused.size();
                 plan.fused.push_back(std::move(f));
                 fused_away = true;
@@ -1618,7 +1643,7 @@ void lower_plan(Plan & plan) {
             plan.lowered.push_back(items[i].node);
         }
         plan.steps.push_back(std::move(step));
-        if (fused_away) ++i;
+        if (fused_away) i += glu_joined ? 2 : 1;
     }
 }
 
@@ -1653,7 +1678,14 @@ scrapgpu_status run_fused(Stream * s, const FusedCall & f) {
         for (size_t i = 0; i < n; ++i) bytes += weight_bytes(load_desc(f.w[i]));
         prof.reset(new ProfScope(s, std::string(f.prologue == SM100_PROLOGUE_RMS_NORM ? "RMS_NORM_MUL" : "GLU") + " + MUL_MAT " + dtype_name(dtypes[0]) + " packed mv x" + std::to_string(n), bytes));
     }
-    {
+    Ref go;
+    if (f.has_glu && (st = resolve(s, f.glu_out, go)) != SCRAPGPU_STATUS_OK) return st;
+    if (f.has_glu) {
+        Serialized scope(serial);
+        st = from_sm100(sm100_mul_mat_glu(s->cuda, f.prologue, (const float *) a.base(), f.has_b ? (const float *) b.base() : nullptr, (const float *) nw.base(), f.eps,
+                                          f.has_sum ? (float *) so.base() : nullptr, f.has_x ? (float *) xo.base() : nullptr, dtypes[0], 1, ws[0], ws[1],
+                                          ne(f.a, 0), ns[0], ys[0], ys[1], (float *) go.base()));
+    } else {
         Serialized scope(serial);
         st = from_sm100(sm100_mul_mat_fused(s->cuda, f.prologue, (const float *) a.base(), f.has_b ? (const float *) b.base() : nullptr,
                                             f.prologue == SM100_PROLOGUE_RMS_NORM ? (const float *) nw.base() : nullptr, f.eps,
@@ -1666,6 +1698,7 @@ scrapgpu_status run_fused(Stream * s, const FusedCall & f) {
         for (size_t i = 0; i < n; ++i) wrote(s, f.y[i]);
         if (f.has_sum) wrote(s, f.sum_out);
         if (f.has_x) wrote(s, f.x_out);
+        if (f.has_glu) wrote(s, f.glu_out);
     }
     return st;
 }

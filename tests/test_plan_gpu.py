@@ -92,8 +92,10 @@ class Layer:
             (abi.OP_GLU, T("gate", "up"), T("act"), abi.GluParams(0, abi.GLU_SWIGLU, 1, 0), 1),
             (abi.OP_MUL_MAT, T("wdown", "act"), T("down"), mm(), 1),
         ]
-        self.outputs = ["x1", "q", "k", "v", "kcache", "vcache", "o", "x2", "gate", "up", "down"]
-        self.elidable = ["t1", "xn1", "xn2", "act"]   # intermediates whose only readers are the following nodes
+        self.outputs = ["x1", "q", "k", "v", "kcache", "vcache", "o", "x2", "gate", "up", "act", "down"]
+        # intermediates whose only readers are the following nodes (act is not among them: the launch that makes gate and up
+        # also makes the SwiGLU activation and writes it out for the down projection)
+        self.elidable = ["t1", "xn1", "xn2"]
 
     def run_nodes(self):
         for op, ins, outs, params, _ in self.nodes:
@@ -150,7 +152,7 @@ def test_plan_matches_node_by_node_execution_and_replays_as_a_graph(both):
         gpu.sync()
         launches.append(P.scrapgpu_cuda_sm100_launch_count() - before)
         results.append(glayer.read(glayer.outputs + glayer.elidable))
-    # 15 nodes: ADD+RMS_NORM+MUL+3 MUL_MAT -> 1 launch, 2 SET_ROWS -> 2 (one op), o -> 1, ADD+RMS_NORM_MUL+2 MUL_MAT -> 1, GLU+down -> 1
+    # 15 nodes: ADD+RMS_NORM+MUL+3 MUL_MAT -> 1 launch, 2 SET_ROWS -> 2 (one op), o -> 1, ADD+RMS_NORM_MUL+2 MUL_MAT+GLU -> 1, down -> 1
     assert launches[0] <= 7, launches          # the step-by-step run counts its launches; replays launch a graph
     assert launches[2] == 0 and launches[3] == 0, launches
     for r in results[1:]:
@@ -168,7 +170,7 @@ def test_plan_matches_node_by_node_execution_and_replays_as_a_graph(both):
     for name in glayer.outputs:
         assert sgref.nmse(first[name], per_op[name]) <= 1e-6, name
         assert sgref.nmse(first[name], want_cpu[name]) <= 1e-6, name
-    # the caller said that t1, xn1, xn2 and act have no other reader: they were not written
+    # the caller said that t1, xn1 and xn2 have no other reader: they were not written
     for name in glayer.elidable:
         assert np.all(first[name] == -7.0), f"{name} was written although its only readers were fused with it"
     refapi.check(L.scrapgpu_plan_free(plan), "plan_free")
@@ -193,6 +195,6 @@ def test_plan_without_use_counts_keeps_every_intermediate(both):
         for name in ("t1", "x1", "x2"):
             assert np.array_equal(got[name].view(np.uint32), per_op[name].view(np.uint32)), name
         # (act = SwiGLU(gate, up): node by node `up` is the second of two consecutive MUL_MATs and comes from the ring
-        # kernel, in the plan gate and up are one fused launch of matvec_q4k_imma: same block sums, other order of addition)
+        # kernel, in the plan gate, up and act are one launch of matvec_q4k_imma: same block sums, other order of addition)
         assert sgref.nmse(got["act"], per_op["act"]) <= 1e-10
     refapi.check(L.scrapgpu_plan_free(plan), "plan_free")
