@@ -295,7 +295,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     head = None
     if dist is not None and not args.quick:
         try:
-            head = sharded_head(capi, rank, world, local_rank, dist)
+            head = sharded_head(capi, rank, world, local_rank, dist, allreduce)
         except Exception as e:
             head = {"error": f"{type(e).__name__}: {e}"[:300]}
 
@@ -588,10 +588,12 @@ def e2e_sharded(capi, stream, pool, order, enqueue_step, xs, ys, dist, warmup, s
                     "(sm100_memcpy_d2h, non-blocking), one sync; host clock, maximum over the ranks"}
 
 
-def sharded_head(capi, rank: int, world: int, local_rank: int, dist, reps: int = 50):
+def sharded_head(capi, rank: int, world: int, local_rank: int, dist, allreduce=None, reps: int = 50):
     """Q6_K output head, K = 4096, N = 151936 rows split evenly over the ranks (151936 / P is a multiple of the
     16-row tile for P = 2, 4, 8), each rank's slice of the logits all-gathered by NCCL.  One CUDA graph holds `reps`
-    rounds of matvec + all-gather; the time is the maximum over the ranks."""
+    rounds of matvec + all-gather; the time is the maximum over the ranks.  A second graph times the greedy form: the
+    matvec followed by the library's arg-max exchange (sm100_argmax_allreduce), which moves P candidates instead of the
+    logits."""
     import torch
     from scrapgpulibrary_b200 import synth
     k, n = 4096, 151936
@@ -636,8 +638,38 @@ def sharded_head(capi, rank: int, world: int, local_rank: int, dist, reps: int =
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms = float(t.item())
     total = algorithmic_bytes(33, k, n)
-    return {"ranks": world, "rows_per_rank": n_local, "us_per_round": round(ms * 1e3, 1), "gbps_aggregate": round(total / (ms * 1e-3) / 1e9, 1),
-            "collective": "NCCL all_gather_into_tensor of 151936 f32 logits"}
+    out = {"ranks": world, "rows_per_rank": n_local, "us_per_round": round(ms * 1e3, 1), "gbps_aggregate": round(total / (ms * 1e-3) / 1e9, 1),
+           "collective": "NCCL all_gather_into_tensor of 151936 f32 logits"}
+    if allreduce is not None:
+        token = torch.zeros(1, device=dev, dtype=torch.int32)
+
+        def greedy_round():
+            capi.check(L.sm100_mul_mat(handle, 33, 1, C.c_void_p(packed.data_ptr()), 0, k, n_local, C.c_void_p(x.data_ptr()), k, 1,
+                                       C.c_void_p(y_local.data_ptr()), n_local), "mul_mat")
+            capi.check(L.sm100_argmax_allreduce(allreduce.ctx, handle, C.c_void_p(y_local.data_ptr()), n_local, rank * n_local,
+                                                C.c_void_p(token.data_ptr())), "argmax_allreduce")
+        with torch.cuda.stream(ts):
+            greedy_round()
+        torch.cuda.synchronize(dev)
+        g2 = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g2, stream=ts):
+            for _ in range(reps):
+                greedy_round()
+        torch.cuda.synchronize(dev)
+        with torch.cuda.stream(ts):
+            g2.replay()
+        torch.cuda.synchronize(dev)
+        dist.barrier()
+        with torch.cuda.stream(ts):
+            e0.record()
+            g2.replay()
+            e1.record()
+        torch.cuda.synchronize(dev)
+        t = torch.tensor([e0.elapsed_time(e1) / reps], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        out["us_per_round_greedy"] = round(float(t.item()) * 1e3, 1)
+        out["greedy"] = "matvec + sm100_argmax_allreduce (local arg-max, P candidates exchanged by tagged peer stores): the token, not the logits"
+    return out
 
 
 def other_formats(capi, stream, reps: int = 20):

@@ -452,12 +452,9 @@ __global__ void __launch_bounds__(1024) argmax_kernel(const float * x, int64_t n
     pdl_launch_dependents();
     __shared__ float sv[32];
     __shared__ int si[32];
-    float best = -INFINITY;
-    int bi = 0x7fffffff;
-    for (int64_t i = threadIdx.x; i < n; i += blockDim.x) {
-        const float v = x[i];
-        if (v > best || bi == 0x7fffffff) { best = v; bi = (int) i; }  // increasing i: the first maximum wins
-    }
+    float best;
+    int bi;
+    argmax_scan(x, n, (int) threadIdx.x, (int) blockDim.x, best, bi);
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
         const float ov = __shfl_xor_sync(0xffffffffu, best, o);

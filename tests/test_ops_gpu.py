@@ -166,6 +166,14 @@ def test_set_rows_and_argmax(sm100, stream):
         sm100.check(lib.sm100_argmax(stream.handle, xb.at(), n, ob.at()), "argmax")
         stream.sync()
         assert int(ob.download(stream, np.int32, 1)[0]) == sgref.argmax(x) == n // 2
+    # a vector that does not start on a 16-byte boundary, ties inside one 16-byte group and in the ragged tail
+    x = U.seeded_acts(99, 1, 4100)[0]
+    x[[1001, 1002, 4098]] = x.max() + 2.0
+    xb = U.to_device(sm100, stream, x)
+    for skip, want in ((1, 1000), (0, 1001), (1003, 4098 - 1003)):
+        sm100.check(lib.sm100_argmax(stream.handle, C.c_void_p(xb.ptr + 4 * skip), 4100 - skip, ob.at()), "argmax")
+        stream.sync()
+        assert int(ob.download(stream, np.int32, 1)[0]) == want == sgref.argmax(x[skip:])
 
 
 def run_attention(capi, stream, q, k, v, causal, offset, scale, positions=None, mask=None, mask_heads=1):
