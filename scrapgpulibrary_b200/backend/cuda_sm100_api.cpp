@@ -837,7 +837,12 @@ struct ProfScope {
             return;
         }
         sm100_event_record(stop, s->cuda);
-        s->prof_pending.push_back({start, stop, key});
+        try {
+            s->prof_pending.push_back({start, stop, key});
+        } catch (...) {   // out of memory for the bookkeeping: this op goes untimed
+            sm100_event_destroy(start);
+            sm100_event_destroy(stop);
+        }
     }
     sm100_event_t event() {
         if (!s->prof_spare.empty()) {

@@ -47,17 +47,21 @@ __global__ void __launch_bounds__(AR_THREADS, 1) allreduce_kernel(ArArgs a) {
     pdl_launch_dependents();
     // 2. sum of the slots in rank order; a value is there when its tag equals this step (bounded wait)
     const uint2 * mine = a.recv[a.rank] + buf * a.capacity;
+    uint32_t limit = a.wait_limit;   // a thread waits out the bound once at most: after a give-up it only looks
     for (int i = tid; i < a.n; i += AR_THREADS) {
         float acc = 0.f;
         for (int r = 0; r < a.world; ++r) {
             const uint2 * src = mine + (size_t) r * a.capacity + i;
             uint2 got;
             asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(got.x), "=r"(got.y) : "l"(src) : "memory");
-            for (uint32_t spins = 0; got.y != step && spins < a.wait_limit; ++spins) {
+            for (uint32_t spins = 0; got.y != step && spins < limit; ++spins) {
                 if (spins > 32) __nanosleep(50);
                 asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(got.x), "=r"(got.y) : "l"(src) : "memory");
             }
-            if (got.y != step) atomicExch(a.fault, 1 + r);
+            if (got.y != step) {
+                atomicExch(a.fault, 1 + r);
+                limit = 0;
+            }
             acc = r == 0 ? __uint_as_float(got.x) : __fadd_rn(acc, __uint_as_float(got.x));
         }
         a.x[i] = acc;

@@ -447,6 +447,7 @@ __global__ void __launch_bounds__(RG_THREADS, 2) matvec_q4k_ring(RingArgs p, ArF
         // is there when its tag equals this step; the wait for it is bounded (about a second), a give-up raises the fault
         // word and the sum goes on with what is there
         const uint2 * mine = f.recv[f.rank] + (size_t) (ar_step & 1u) * f.world * f.capacity;
+        uint32_t limit = f.wait_limit;   // a thread waits out the bound once at most: after a give-up it only looks
         for (int idx = tid; idx < cta_rounds * p.groups * 16; idx += RG_THREADS) {
             const int r = idx / (p.groups * 16), rem = idx - r * (p.groups * 16);
             const int tile = blockIdx.x * p.groups + (rem >> 4) + r * tile_step;
@@ -456,11 +457,14 @@ __global__ void __launch_bounds__(RG_THREADS, 2) matvec_q4k_ring(RingArgs p, ArF
                 for (int q = 0; q < f.world; ++q) {
                     const uint2 * src = mine + (size_t) q * f.capacity + at;
                     uint2 got = rg_ld_tagged(src);
-                    for (uint32_t spins = 0; got.y != ar_step && spins < f.wait_limit; ++spins) {
+                    for (uint32_t spins = 0; got.y != ar_step && spins < limit; ++spins) {
                         if (spins > 32) __nanosleep(50);
                         got = rg_ld_tagged(src);
                     }
-                    if (got.y != ar_step) atomicExch(f.fault, 100 + q);
+                    if (got.y != ar_step) {
+                        atomicExch(f.fault, 100 + q);
+                        limit = 0;
+                    }
                     acc = q == 0 ? __uint_as_float(got.x) : __fadd_rn(acc, __uint_as_float(got.x));
                 }
                 p.y[0][at] = acc;
